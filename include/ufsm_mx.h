@@ -1,0 +1,131 @@
+/* ufsm_mx: B200 (sm_100a) implementation of ufsm's MX block-scaled 3-D convolution forward path, behind a C ABI.
+
+   Every pointer named "device" is CUDA device memory of the current device; all work is issued on the legacy default stream
+   and is synchronous in that stream, as in the reference (src/nn.h:1-2).  CUDA errors are latched, not returned: lp_check()
+   returns and clears the first message (src/lp_common.cuh:35-38, src/lp_f8wgrad.cu:140).  Invalid argument combinations print
+   to stderr and abort(), as the reference's entry points do (src/lp_f8fwd.cu:28,35,44).  There is no CPU fallback: without a
+   usable sm_100 device every compute entry latches an error.
+
+   Storage types (xbf / ybf / dt codes of src/nn_lp.h:50-54): 0 fp32, 1 bf16, 2 fp16, plane-major [n][C][D][H][W];
+   3 MX-fp8 (E4M3), 4 MX-fp4 (E2M1): channel-blocked codes data[n][blk][voxel][bw] (fp4: two nibbles a byte, low nibble first)
+   followed by the UE8M0 scale plane sc[n][blk][voxel], bw = 8 / 16 / 32 for C <= 8 / <= 16 / larger (src/lp_common.cuh:100-106,
+   132-134).  One addition: UMX_H16B (18) = fp16 in the same 32-channel blocking, [n][blk][voxel][32] halfs (NDHWC inside a
+   block; exactly NDHWC when C <= 32), the form in which a conv hands its output to the InstanceNorm apply. */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types of the reference interface ---- */
+typedef struct { int n, c, d, h, w; } shape5;                                              /* src/nn.h:21 */
+typedef struct { const float *gamma, *beta, *mean, *rstd; int G; int zs, zo, ns, zhw; } gnp_t;   /* src/nn_lp.h:15; G == 0: no transform */
+typedef struct { const void *x2; int c_split; void *y2; int o_split; int accum; gnp_t gp2; int16_t up, yD; unsigned sr; unsigned wkey;
+                 int zlo, zhi; int stored_stats; unsigned osr; int16_t zi0, Di, o_pad, zw0, zw1, yzo; } split_t;   /* src/nn_lp.h:32 */
+enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16B = 18 };
+
+/* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
+int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
+void *nn_malloc(size_t bytes);
+void nn_free(void *p);
+void nn_zero(void *p, size_t bytes);
+void nn_h2d(void *dst, const void *src, size_t bytes);
+void nn_d2h(void *dst, const void *src, size_t bytes);
+void nn_sync(void);
+const char *nn_check(void);              /* NULL, or the first error since the last call (same latch as lp_check) */
+const char *lp_check(void);              /* src/nn_lp.h:172 */
+void *nn_malloc_host(size_t bytes);      /* pinned host memory (cudaHostAlloc) for the window scheduler's staging buffers */
+void nn_free_host(void *p);
+
+/* ---- MX storage and the quantiser (src/nn_lp.h:110-118, 126; kernels src/lp_mx_cvt.cu:9-19, 59-79, 429-447) ---- */
+size_t lp_mx8_bytes(int N, int C, size_t S);
+size_t lp_mx4_bytes(int N, int C, size_t S);
+void lp_f32_to_mx8(const float *x, int N, int C, size_t S, void *y);                 /* x device fp32 [n][C][S] -> y device MX-fp8 */
+void lp_f32_to_mx4(const float *x, int N, int C, size_t S, void *y);
+void lp_h16_to_mx8(const void *x, int dt, int N, int C, size_t S, void *y);           /* dt 2 fp16 (1 bf16 aborts: not built) */
+void lp_h16_to_mx4(const void *x, int dt, int N, int C, size_t S, void *y);
+void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y);
+void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y);
+/* the same quantiser with 32-wide blocks whatever C (padding channels zero): the form the graph below keeps its tensors in */
+size_t umx_mx_bytes32(int bits, int N, int C, size_t S);
+void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits);   /* dt 0 fp32 / 2 fp16 plane-major */
+void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y);         /* -> plane-major fp32 */
+void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);                   /* blocked fp16 -> plane-major fp32 */
+
+/* ---- 3x3x3 stride-1 pad-1 conv forward, the reference's entry points (src/nn_lp.h:53-54; src/lp_f8fwd.cu:26-52,
+   src/lp_f4fwd.cu:30-51).  x: device, xbf 3 / 4 (MX, more than 16 channels so that rows are 32 wide) or 2 (fp16 plane-major,
+   quantised to the conv's MX format first); w: device fp32 [cout][cin][27]; b: device fp32 [cout] or NULL; y: ybf 2 (fp16
+   plane-major), 3 / 4 (MX, acc + bias requantised per 32 output channels) or UMX_H16B.  lp_conv_fwd_f8 multiplies E4M3 codes,
+   lp_conv_fwd_f4 E2M1 codes; an MX input of the other format aborts.  Supported subset: gp.G == 0, osum == NULL, and split_t
+   zero except wkey (prepared-weight memo key).  Anything else prints "not built" and aborts.  Returns 0. ---- */
+int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
+int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
+void lp_wmemo_clear(void);               /* src/nn_lp.h:57: drop the prepared weights kept under split_t.wkey */
+
+/* ---- graph operators (the InstanceNorm / LeakyReLU / transposed-conv semantics of src/xnet.h:85-98) ---- */
+enum { UMX_CONV3 = 0,      /* 3^3 stride 1 pad 1, w [co][ci][27]                         (xconv_init k3 s1 p1, src/nn_xnet.cu:615-637) */
+       UMX_CONV1 = 1,      /* 1^3, w [co][ci]                                            (xhead, src/nn_xnet.cu:1751-1756) */
+       UMX_DOWN2 = 2,      /* 2^3 stride 2 pad 0, w [co][ci][8]; input = space-to-depth copy (src/ink3dext_net.c:104-112) */
+       UMX_TCONV2 = 3 };   /* ConvTranspose3d k2 s2, w [ci][co][8]                       (xtconv3_init, src/nn_xnet.cu:650-662) */
+enum { UMX_OUT_H16B = 0,   /* y = fp16(acc + bias), blocked fp16 */
+       UMX_OUT_MX = 1,     /* y = MX(fp16(acc + bias)) into blocks [b0, ...) of an MX tensor with nb_dst blocks (xtconv_cat_q) */
+       UMX_OUT_PM32 = 2,   /* y = acc + bias, plane-major fp32 [n][co][S] */
+       UMX_OUT_PM16 = 3,   /* y = fp16(acc + bias), plane-major fp16 */
+       UMX_OUT_MXRAW = 4 };/* y = MX(acc + bias) without the fp16 rounding (the lp epilogue, src/lp_common.cuh:1465-1536) */
+typedef struct umx_conv umx_conv;
+/* w, bias: host fp32 in PyTorch order (bias NULL: zero).  bits: 8 (E4M3) or 4 (E2M1) for weights and activations alike. */
+umx_conv *umx_conv_create(int kind, const float *w, const float *bias, int co, int ci, int bits);
+umx_conv *umx_conv_create_dev(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits);   /* device weights */
+void umx_conv_free(umx_conv *c);
+/* x: MX tensor (32-wide blocks) of c->ci channels (UMX_DOWN2: the space-to-depth copy, 8 * ci channels at half resolution) on an
+   N x D x H x W grid.  y per out_mode; nb_dst / b0: block count of the destination tensor and first block written (0, 0: the
+   conv's own co).  part: optional device doubles for InstanceNorm partial sums (umx_stats_doubles), only with UMX_OUT_H16B.
+   UMX_TCONV2 writes the 2D x 2H x 2W grid.  Returns 0, or -1 after latching an error. */
+int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part);
+size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
+/* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
+   gamma / beta device arrays or NULL (1 / 0) */
+void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
+/* y = fp16(act(x a + b)) requantised to MX (k_inq, src/nn_xnet.cu:1577-1620): x blocked fp16 [n][C][S]; act 2 = LeakyReLU 0.01,
+   0 none; q: MX destination (bits) with nb_dst blocks, first block b0; q_s2d: optional second copy in 2x2x2 space-to-depth order
+   (an MX tensor of 8 C channels on the half grid, the input of UMX_DOWN2) or NULL; h: optional blocked fp16 copy or NULL.
+   coef NULL: identity (a = 1, b = 0). */
+void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h);
+
+/* ---- the BASELINE U-Net (five levels 32/64/128/256/320, two 3^3 convs + InstanceNorm + LeakyReLU 0.01 a level, 2^3 stride-2
+   down convs, ConvTranspose k2 s2 up, concat (up | skip), 1^3 head) and the sliding-window scheduler ---- */
+typedef struct { int L; int cw[8]; int nh; int P; int bits_first, bits_mid, bits_last; } umx_unet_cfg;
+typedef struct umx_unet umx_unet;
+size_t umx_unet_nweights(const umx_unet_cfg *cfg);               /* floats of the flat weight array, forward order, each conv's bias after its weights */
+umx_unet *umx_unet_create(const umx_unet_cfg *cfg, const float *weights_host, int max_batch);
+void umx_unet_free(umx_unet *u);
+/* x: device fp16 [N][1][P^3] (CT intensity / 255); logits: device fp32 [N][nh][P^3] (umx_unet_forward) or fp16 (.._h16).  0 on success. */
+int umx_unet_forward(umx_unet *u, const void *x_dev, int N, float *logits_dev);
+int umx_unet_forward_h16(umx_unet *u, const void *x_dev, int N, void *logits_dev);
+/* the call a user of the library makes: uint8 CT patches [N][P^3] on the host (pinned or pageable) -> fp16 logits [N][nh][P^3] on the
+   host; copies in, converts (x / 255 -> fp16), runs, copies out, synchronises.  0, or -1 with the message in lp_check(). */
+int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host);
+double umx_unet_flops(const umx_unet_cfg *cfg);                  /* 2 V_out C_in C_out taps summed over the convs, per patch */
+long umx_unet_launches(const umx_unet *u);                       /* kernels launched by the library since this object was created */
+long umx_launch_count(void);                                     /* kernels launched by the library in this process */
+void umx_u8_to_h16(const uint8_t *x_dev, size_t n, void *y_dev); /* CT bytes -> fp16 x / 255 */
+/* acc[c][z - zlo][y][x] += w logits[c][patch voxel], wsum += w with the separable Gaussian window w1d (device, P floats) for the
+   patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend, src/nn_ink3dext.cu:58-73) */
+void umx_blend_add(const void *logits_dev, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d_dev, float *acc_dev, float *wsum_dev);
+
+/* Sliding window over a V^3 uint8 volume (host): P^3 patches at stride P - overlap, Gaussian window sigma P / 8, patch layers
+   dealt to ranks by contiguous z-slabs of (z, y) patch rows (src/predict.c:2696-2717; blend src/nn_ink3dext.cu:58-73).  This rank
+   runs patches [first, first + count) in (z, y, x) order, blends them on the device, and returns weight * logits and weight for the
+   z planes [zlo, zhi) its patches touch (umx_window_extent): host arrays acc [nh][zhi - zlo][V][V] and wsum [zhi - zlo][V][V].  The
+   caller adds the planes that two ranks share and divides. */
+typedef struct { int V, P, overlap, nper, npatch; } umx_window;
+umx_window umx_window_make(int V, int P, int overlap);
+void umx_window_share(const umx_window *w, int rank, int world, int *first, int *count);
+void umx_window_origin(const umx_window *w, int idx, int *z0, int *y0, int *x0);
+void umx_window_extent(const umx_window *w, int first, int count, int *zlo, int *zhi);
+int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol_host, int first, int count, int batch, float *acc, float *wsum);
+
+#ifdef __cplusplus
+}
+#endif

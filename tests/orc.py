@@ -1,0 +1,209 @@
+"""numpy wrappers around the CPU oracle (oracle/liboracle.so).  Test infrastructure only."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORC_DIR = os.path.join(ROOT, "oracle")
+_o = None
+
+
+class UnetCfg(C.Structure):
+    _fields_ = [("L", C.c_int), ("cw", C.c_int * 8), ("nh", C.c_int), ("P", C.c_int), ("bits_first", C.c_int), ("bits_mid", C.c_int), ("bits_last", C.c_int)]
+
+
+def o():
+    global _o
+    if _o is None:
+        so = os.path.join(ORC_DIR, "liboracle.so")
+        if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(ORC_DIR, "mx_oracle.c")):
+            subprocess.run(["make", "-C", ORC_DIR], check=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        _o = C.CDLL(so)
+        _o.orc_mx_exp.restype = C.c_int
+        _o.orc_mx_exp.argtypes = [C.c_float, C.c_float]
+        for f in ("orc_enc_e4m3", "orc_enc_e2m1"):
+            getattr(_o, f).restype = C.c_uint
+            getattr(_o, f).argtypes = [C.c_float]
+        for f in ("orc_dec_e4m3", "orc_dec_e2m1", "orc_dec_scale"):
+            getattr(_o, f).restype = C.c_float
+            getattr(_o, f).argtypes = [C.c_uint]
+        _o.orc_mx_bytes.restype = C.c_size_t
+        _o.orc_mx_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_int]
+        _o.orc_unet_nweights.restype = C.c_size_t
+        _o.orc_threads.restype = C.c_int
+    return _o
+
+
+def ref():
+    """The reference's own conversions (oracle/_ref/libmxsw_ref.so), or None when it was not built."""
+    so = os.path.join(ORC_DIR, "_ref", "libmxsw_ref.so")
+    if not os.path.exists(so):
+        return None
+    r = C.CDLL(so)
+    r.ref_sweep_diff.restype = C.c_size_t
+    r.ref_sweep_diff.argtypes = [C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.c_size_t, C.POINTER(C.c_uint32)]
+    for f in ("ref_dec_e4m3", "ref_dec_e2m1"):
+        getattr(r, f).restype = C.c_float
+        getattr(r, f).argtypes = [C.c_uint]
+    return r
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def enc(x, bits):
+    x = f32(x).ravel()
+    y = np.empty(x.size, np.uint8)
+    (o().orc_enc_e2m1_n if bits == 4 else o().orc_enc_e4m3_n)(_p(x), C.c_size_t(x.size), _p(y))
+    return y
+
+
+def mx_bytes(bits, N, Cn, S, bw_force=0):
+    return o().orc_mx_bytes(bits, N, Cn, C.c_size_t(S), bw_force)
+
+
+def pm_to_mx(x, dt, N, Cn, S, bits, bw_force=0):
+    x = np.ascontiguousarray(x)
+    y = np.zeros(mx_bytes(bits, N, Cn, S, bw_force), np.uint8)
+    o().orc_pm_to_mx(_p(x), dt, N, Cn, C.c_size_t(S), bits, bw_force, _p(y))
+    return y
+
+
+def mx_to_pm(mx, bits, N, Cn, S, bw_force=0):
+    y = np.zeros(N * Cn * S, np.float32)
+    o().orc_mx_to_pm(_p(mx), bits, N, Cn, C.c_size_t(S), bw_force, _p(y))
+    return y
+
+
+def nb32(Cn):
+    return (Cn + 31) // 32
+
+
+def mx_to_blocked(mx, bits, N, Cn, S):
+    y = np.zeros(N * nb32(Cn) * S * 32, np.float32)
+    o().orc_mx_to_blocked(_p(mx), bits, N, Cn, C.c_size_t(S), _p(y))
+    return y
+
+
+def blocked_to_mx(x, bits, N, Cn, S):
+    x = f32(x)
+    y = np.zeros(N * nb32(Cn) * S * (32 * bits // 8 + 1), np.uint8)
+    o().orc_blocked_to_mx(_p(x), bits, N, Cn, C.c_size_t(S), _p(y))
+    return y
+
+
+def pm_to_blocked(x, N, Cn, S):
+    x = f32(x)
+    y = np.zeros(N * nb32(Cn) * S * 32, np.float32)
+    o().orc_pm_to_blocked(_p(x), N, Cn, C.c_size_t(S), _p(y))
+    return y
+
+
+def blocked_to_pm(x, N, Cn, S):
+    x = f32(x)
+    y = np.zeros(N * Cn * S, np.float32)
+    o().orc_blocked_to_pm(_p(x), N, Cn, C.c_size_t(S), _p(y))
+    return y
+
+
+def prep_w(w, Co, Ci, taps, bits, layout=0, want_codes=False):
+    w = f32(w)
+    Cip, Cop = nb32(Ci) * 32, nb32(Co) * 32
+    wdq = np.zeros(taps * Cip * Cop, np.float32)
+    if want_codes:
+        wq = np.zeros(taps * (Cip // 32) * Cop * 32, np.uint8)
+        ws = np.zeros(taps * (Cip // 32) * Cop, np.uint8)
+        o().orc_prep_w(_p(w), Co, Ci, taps, bits, layout, _p(wdq), _p(wq), _p(ws))
+        return wdq, wq, ws
+    o().orc_prep_w(_p(w), Co, Ci, taps, bits, layout, _p(wdq), None, None)
+    return wdq
+
+
+def conv_blocked(x, N, Ci, D, H, W, wdq, bias, Co, k, stride, pad):
+    x, wdq = f32(x), f32(wdq)
+    Do, Ho, Wo = (D + 2 * pad - k) // stride + 1, (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    y = np.zeros(N * nb32(Co) * Do * Ho * Wo * 32, np.float32)
+    b = f32(bias) if bias is not None else None
+    o().orc_conv_blocked(_p(x), N, Ci, D, H, W, _p(wdq), _p(b) if b is not None else None, Co, k, stride, pad, _p(y))
+    return y
+
+
+def tconv_blocked(x, N, Ci, D, H, W, wdq, bias, Co):
+    x, wdq = f32(x), f32(wdq)
+    y = np.zeros(N * nb32(Co) * D * H * W * 8 * 32, np.float32)
+    b = f32(bias) if bias is not None else None
+    o().orc_tconv_blocked(_p(x), N, Ci, D, H, W, _p(wdq), _p(b) if b is not None else None, Co, _p(y))
+    return y
+
+
+def round_h16(v):
+    v = f32(v).copy()
+    o().orc_round_h16(_p(v), C.c_size_t(v.size))
+    return v
+
+
+def in_sums(y, N, Cn, S):
+    y = f32(y)
+    s = np.zeros(N * Cn * 2, np.float64)
+    o().orc_in_sums(_p(y), N, Cn, C.c_size_t(S), _p(s))
+    return s
+
+
+def in_coef(sums, N, Cn, S, eps=1e-5):
+    coef = np.zeros(N * Cn * 2, np.float32)
+    o().orc_in_coef(_p(sums), N, Cn, C.c_double(S), None, None, C.c_float(eps), _p(coef))
+    return coef
+
+
+def in_apply(y, coef, N, Cn, S, act=2):
+    y, coef = f32(y), f32(coef)
+    out = np.zeros_like(y)
+    o().orc_in_apply(_p(y), _p(coef), N, Cn, C.c_size_t(S), act, _p(out))
+    return out
+
+
+def s2d_blocked(x, N, Cn, D, H, W):
+    x = f32(x)
+    y = np.zeros(x.size, np.float32)
+    o().orc_s2d_blocked(_p(x), N, Cn, D, H, W, _p(y))
+    return y
+
+
+def fake_quant_blocked(x, bits):
+    x = f32(x).copy()
+    o().orc_fake_quant_blocked(_p(x), C.c_size_t(x.size // 32), bits)
+    return x
+
+
+def unet_cfg(P, cw, nh=7, bits=(8, 8, 8)):
+    c = UnetCfg()
+    c.L = len(cw)
+    for i, v in enumerate(cw):
+        c.cw[i] = v
+    c.nh, c.P = nh, P
+    c.bits_first, c.bits_mid, c.bits_last = bits
+    return c
+
+
+def unet_nweights(cfg):
+    return o().orc_unet_nweights(C.byref(cfg))
+
+
+def unet_forward(cfg, weights, x16, N):
+    weights = f32(weights)
+    x16 = np.ascontiguousarray(x16, dtype=np.float16)
+    logits = np.zeros(N * cfg.nh * cfg.P ** 3, np.float32)
+    o().orc_unet_forward(C.byref(cfg), _p(weights), _p(x16), N, _p(logits), None, None)
+    return logits
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

@@ -1,0 +1,518 @@
+/* MX block-scaled implicit-GEMM 3-D convolution forward on the sm_100a tensor cores (tcgen05, TMEM accumulators, TMA staging).
+
+   GEMM view.  M = 128 output voxels of one tile (8 along x by 16 along y of one z plane), N = up to 128 output channels,
+   K = taps x input channels in steps of one MX block pair: 32 E4M3 bytes (kind::mxf8f6f4, one UE8M0 scale per row) or 64 E2M1
+   nibbles (kind::mxf4, two scales per row) per tcgen05.mma.  The activation tensor is the reference's channel-blocked MX
+   storage (src/lp_common.cuh:100-106), so one voxel's K step is 32 contiguous bytes (fp8) or two 16-byte rows of adjacent
+   blocks (fp4).
+
+   Operand staging.  A 3^3 conv loads, per (input block, dz), one halo plane of 18 x 10 voxels with TMA (out-of-range voxels are
+   zero-filled: that is the padding) as two 16-byte-wide planes [k half][y][x][16 B].  In that layout the canonical K-major
+   no-swizzle UMMA operand (8 rows x 16 B core matrices; stride 160 B between the 16 y groups, 2880 B between the K halves) of
+   every (dy, dx) tap is the same tile at a start address shifted by (dy * 10 + dx) * 16 bytes (the fp8 planes sit 2944 B apart so
+   that each TMA destination is 128-byte aligned), so nine MMAs reuse one load.
+   Weights are prepared once into the exact shared-memory image of a stage ([tap][k half][row][16 B] + scale bytes in the
+   TMEM scale layout) and arrive with one bulk copy.  1^3 convs (head, the 2^3 stride-2 down conv on a space-to-depth copy, the
+   transposed conv as a GEMM to 8 Cout columns) run the same pipeline with one tap and four K items a stage.
+
+   Scale factors.  tcgen05 block-scaled MMAs read scales from TMEM: row r of a 128-row operand at lane r % 32, column r / 32,
+   byte = scale id.  The scale of an A row depends on the tap (it is the shifted voxel's), so four epilogue warps gather, per
+   stage, the nine shifted scale sets from the scale plane into that layout in shared memory, and the MMA thread copies them to
+   TMEM with tcgen05.cp before issuing the stage's MMAs.  Out-of-range voxels get scale 1 (their codes are zero).
+
+   Roles (192 threads): warp 0 lane 0 = TMA producer; warp 1 = TMEM allocation, lane 0 = MMA issue; warps 2-5 = scale gather,
+   then the epilogue (tcgen05.ld of 32 channels per voxel = one MX block per thread: bias, fp16 store or MX requantisation,
+   InstanceNorm partial sums in fp64).  Every wait is bounded; a wait that gives up records (code, block, stage) in a device
+   flag, raises a block-wide abort flag and the block tears down normally. */
+#include "mx_common.cuh"
+#include "tc_ptx.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr int kSfBase = 128;        /* TMEM columns: [0, 128) accumulators, then two scale buffers of 40 (A 20 | B 20) */
+constexpr long long kWaitLimit = 4000000000ll;   /* clock cycles (about two seconds) */
+
+struct ConvArgs {
+    int N, D, H, W;                 /* the grid of GEMM rows */
+    int nkb;                        /* 32-channel blocks of the activation tensor */
+    int nki;                        /* K items per tap: nkb (fp8) or ceil(nkb / 2) (fp4) */
+    int taps, bits;
+    int cop, nt, ntiles_n;          /* GEMM columns (padded to 32), column tile, column tiles */
+    int tiles_x, tiles_y;
+    int ring;                       /* pipeline depth */
+    int stage_bytes, offW, offSFB, offA, offSFA;
+    int w_stage_bytes, nst;         /* packed weight bytes per stage, stages per column tile */
+    int items_max, ipq, nquad;      /* K items per stage, items per scale quad (4 fp8 / 2 fp4), quads per stage */
+    const uint8_t *x_sc;
+    const uint8_t *wpk;
+    const float *bias;
+    int out_mode, out_bits, nb_dst, b0, tconv, co_real, cob_t;   /* cob_t: blocks of one transposed-conv sub-voxel group */
+    void *y;
+    double *part;
+    int *err;
+};
+
+__device__ __forceinline__ void raise(const ConvArgs &a, volatile int *abort_flag, int code, int stage) {
+    if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)); a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
+    *abort_flag = 1;
+    __threadfence_block();
+}
+
+__global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const ConvArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    /* control block, then the stage ring at the next 1024-byte boundary */
+    uint64_t *bars = (uint64_t *)smem_raw;                       /* [0, ring) tma full, [ring, 2 ring) scale full, [2 ring, 3 ring) empty, 3 ring: accumulator full */
+    uint32_t *tmem_slot = (uint32_t *)(smem_raw + 256);
+    volatile int *abort_flag = (volatile int *)(smem_raw + 260);
+    uint8_t *stages = smem_raw + 1024;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int R = a.ring;
+    const uint32_t bar_tma = smem_u32(bars), bar_sf = bar_tma + 8 * R, bar_empty = bar_tma + 16 * R, bar_acc = bar_tma + 24 * R;
+
+    const int txy = blockIdx.x, tx = txy % a.tiles_x, ty = txy / a.tiles_x;
+    const int z = blockIdx.y;
+    const int n = blockIdx.z / a.ntiles_n, ntile = blockIdx.z % a.ntiles_n;
+    const int x0 = tx * 8, y0 = ty * 16;
+    const int n0 = ntile * a.nt, n_cur = min(a.nt, a.cop - n0);
+    const int nst = a.nst;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < R; i++) { mbar_init(bar_tma + 8 * i, 1); mbar_init(bar_sf + 8 * i, 128); mbar_init(bar_empty + 8 * i, 1); }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    /* a stage is live unless it is a 3^3 stage whose input plane lies outside the volume (it would add zeros) */
+    auto stage_live = [&](int st) -> bool { if (a.taps != 27) return true; const int zi = z + st % 3 - 1; return zi >= 0 && zi < a.D; };
+    auto stage_items = [&](int st) -> int { return a.taps == 27 ? 9 : min(4, a.nki - 4 * st); };
+
+    if (warp == 0) {
+        /* ---------------- TMA producer ---------------- */
+        if (lane == 0) {
+            tma_prefetch_desc(&map0); if (a.bits == 8) tma_prefetch_desc(&map1);
+            int it = 0;
+            const uint8_t *wbase = a.wpk + (size_t)ntile * nst * a.w_stage_bytes;
+            for (int st = 0; st < nst; st++) {
+                if (!stage_live(st)) continue;
+                const int s = it % R, ph = (it / R) & 1;
+                if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimit)) { raise(a, abort_flag, 1, st); break; }
+                uint8_t *sb = stages + (size_t)s * a.stage_bytes;
+                const uint32_t bar = bar_tma + 8 * s;
+                const int items = stage_items(st);
+                const int abytes = a.taps == 27 ? 5760 : items * 4096;
+                mbar_expect_tx(bar, (uint32_t)(abytes + a.w_stage_bytes));
+                bulk_g2s(smem_u32(sb + a.offW), wbase + (size_t)st * a.w_stage_bytes, (uint32_t)a.w_stage_bytes, bar);
+                if (a.taps == 27) {
+                    const int ki = st / 3, zi = z + st % 3 - 1;
+                    if (a.bits == 8) {
+                        const int zz = (n * a.nkb + ki) * a.D + zi;
+                        tma_load_4d(smem_u32(sb + a.offA), &map0, bar, 0, x0 - 1, y0 - 1, zz);
+                        tma_load_4d(smem_u32(sb + a.offA + 2944), &map1, bar, 0, x0 - 1, y0 - 1, zz);
+                    } else {
+                        tma_load_5d(smem_u32(sb + a.offA), &map0, bar, 0, x0 - 1, y0 - 1, zi, n * a.nkb + 2 * ki);
+                    }
+                } else {
+                    for (int j = 0; j < items; j++) {
+                        const int ki = 4 * st + j;
+                        if (a.bits == 8) {
+                            const int zz = (n * a.nkb + ki) * a.D + z;
+                            tma_load_4d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, x0, y0, zz);
+                            tma_load_4d(smem_u32(sb + a.offA + j * 4096 + 2048), &map1, bar, 0, x0, y0, zz);
+                        } else {
+                            tma_load_5d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, x0, y0, z, n * a.nkb + 2 * ki);
+                        }
+                    }
+                }
+                it++;
+            }
+        }
+    } else if (warp == 1) {
+        /* ---------------- MMA issue ---------------- */
+        int it = 0; bool ok = true;
+        for (int st = 0; st < nst && ok; st++) {
+            if (!stage_live(st)) continue;
+            const int s = it % R, ph = (it / R) & 1;
+            if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 2, st); ok = false; break; }
+            if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 3, st); ok = false; break; }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes);
+                const uint32_t sfa_t = tmem + kSfBase + (it & 1) * 40, sfb_t = sfa_t + 20;
+                const int items = stage_items(st), nq = (items + a.ipq - 1) / a.ipq;
+                for (int q = 0; q < nq; q++) {
+                    utccp_32x128b(sfa_t + 4 * q, smem_desc(sb + a.offSFA + 512 * q, 0, 128));
+                    utccp_32x128b(sfb_t + 4 * q, smem_desc(sb + a.offSFB + 512 * q, 0, 128));
+                }
+                for (int j = 0; j < items; j++) {
+                    uint32_t aaddr, albo, asbo;
+                    if (a.taps == 27) { aaddr = sb + a.offA + ((j / 3) * 10 + j % 3) * 16; albo = a.bits == 8 ? 2944 : 2880; asbo = 160; }
+                    else { aaddr = sb + a.offA + j * 4096; albo = 2048; asbo = 128; }
+                    const uint64_t ad = smem_desc(aaddr, albo, asbo);
+                    const uint64_t bd = smem_desc(sb + a.offW + j * a.nt * 32, a.nt * 16, 128);
+                    const int q = j / a.ipq, id = (j % a.ipq) * (4 / a.ipq);
+                    const uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
+                    if (a.bits == 8) umma_mxf8(tmem, ad, bd, idesc_mxf8(n_cur, id, id), acc, sfa_t + 4 * q, sfb_t + 4 * q);
+                    else umma_mxf4(tmem, ad, bd, idesc_mxf4(n_cur, id, id), acc, sfa_t + 4 * q, sfb_t + 4 * q);
+                }
+                umma_commit(bar_empty + 8 * s);
+            }
+            __syncwarp();
+            it++;
+        }
+        if (lane == 0) umma_commit(bar_acc);   /* also after a give-up: the epilogue must not wait for its full limit */
+        __syncwarp();
+    } else {
+        /* ---------------- scale gather, then epilogue ---------------- */
+        const int q4 = warp & 3, r = q4 * 32 + lane;             /* TMEM lane quarter of this warp; GEMM row of this thread */
+        const int ry = r >> 3, rx = r & 7;
+        const int oy = y0 + ry, ox = x0 + rx;
+        const bool row_ok = oy < a.H && ox < a.W;
+        const size_t S = (size_t)a.D * a.H * a.W;
+        int it = 0; bool ok = true;
+        for (int st = 0; st < nst && ok; st++) {
+            if (!stage_live(st)) continue;
+            const int s = it % R, ph = (it / R) & 1;
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimit)) { raise(a, abort_flag, 4, st); ok = false; break; }
+            uint32_t *sfa = (uint32_t *)(stages + (size_t)s * a.stage_bytes + a.offSFA);
+            const int items = stage_items(st);
+            uint32_t wq[5] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+            if (a.taps == 27) {
+                const int ki = st / 3, zi = z + st % 3 - 1;
+#pragma unroll
+                for (int j = 0; j < 9; j++) {
+                    const int iy = oy + j / 3 - 1, ix = ox + j % 3 - 1;
+                    const bool in = iy >= 0 && iy < a.H && ix >= 0 && ix < a.W;
+                    const size_t vox = ((size_t)zi * a.H + iy) * a.W + ix;
+                    if (a.bits == 8) {
+                        const unsigned b = in ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
+                        wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
+                    } else {
+                        const unsigned b0 = in ? a.x_sc[((size_t)n * a.nkb + 2 * ki) * S + vox] : 127u;
+                        const unsigned b1 = (in && 2 * ki + 1 < a.nkb) ? a.x_sc[((size_t)n * a.nkb + 2 * ki + 1) * S + vox] : 127u;
+                        const unsigned h = b0 | (b1 << 8);
+                        wq[j >> 1] = (wq[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | (h << (16 * (j & 1)));
+                    }
+                }
+            } else {
+                const size_t vox = ((size_t)z * a.H + oy) * a.W + ox;
+                for (int j = 0; j < items; j++) {
+                    const int ki = 4 * st + j;
+                    if (a.bits == 8) {
+                        const unsigned b = row_ok ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
+                        wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
+                    } else {
+                        const unsigned b0 = row_ok ? a.x_sc[((size_t)n * a.nkb + 2 * ki) * S + vox] : 127u;
+                        const unsigned b1 = (row_ok && 2 * ki + 1 < a.nkb) ? a.x_sc[((size_t)n * a.nkb + 2 * ki + 1) * S + vox] : 127u;
+                        const unsigned h = b0 | (b1 << 8);
+                        wq[j >> 1] = (wq[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | (h << (16 * (j & 1)));
+                    }
+                }
+            }
+            /* quad q: word (lane, column) = row 32 * column + lane -> this thread's word is at lane * 4 + quarter */
+#pragma unroll
+            for (int q = 0; q < 5; q++) if (q < a.nquad) sfa[q * 128 + lane * 4 + q4] = wq[q];
+            fence_proxy_async();
+            mbar_arrive(bar_sf + 8 * s);
+            it++;
+        }
+        /* ---- epilogue ---- */
+        if (!mbar_wait(bar_acc, 0, abort_flag, kWaitLimit)) raise(a, abort_flag, 5, 0);
+        tc_fence_after();
+        /* every epilogue thread reaches this barrier whatever happened above; a give-up raised the abort flag before it, so all
+           128 threads read the same value after it and take the same branch (the barrier inside the branch is then safe) */
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!*abort_flag) {
+            const int Ho = a.tconv ? 2 * a.H : a.H, Wo = a.tconv ? 2 * a.W : a.W;
+            const size_t So = a.tconv ? S * 8 : S;
+            const int T = a.D * a.tiles_x * a.tiles_y, tsp = z * (a.tiles_x * a.tiles_y) + txy;
+            double *spart = (double *)stages;                    /* [quarter][chunk][lane][2]; the ring is idle by now */
+            const int nchunk = n_cur >> 5;
+            for (int jc = 0; jc < nchunk; jc++) {
+                uint32_t rr[32];
+                tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(jc * 32), rr);
+                tmem_ld_wait();
+                float v[32];
+                const int cb_g = (n0 >> 5) + jc;                 /* 32-column block of the GEMM */
+#pragma unroll
+                for (int k = 0; k < 32; k++) v[k] = __fadd_rn(__uint_as_float(rr[k]), __ldg(a.bias + cb_g * 32 + k));
+                int ob = cb_g; size_t vo = ((size_t)z * a.H + oy) * a.W + ox;
+                if (a.tconv) {
+                    const int abc = cb_g / a.cob_t; ob = cb_g % a.cob_t;
+                    vo = ((size_t)(2 * z + (abc >> 2)) * Ho + 2 * oy + ((abc >> 1) & 1)) * Wo + 2 * ox + (abc & 1);
+                }
+                if (a.out_mode != UMX_OUT_PM32 && a.out_mode != UMX_OUT_MXRAW) {
+#pragma unroll
+                    for (int k = 0; k < 32; k++) v[k] = __half2float(__float2half_rn(v[k]));
+                }
+                if (row_ok) {
+                    const size_t ro = ((size_t)n * a.nb_dst + a.b0 + ob) * So + vo;
+                    if (a.out_mode == UMX_OUT_H16B) {
+                        uint4 o[4]; __half2 *op = (__half2 *)o;
+#pragma unroll
+                        for (int k = 0; k < 16; k++) op[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+                        uint4 *dst = (uint4 *)a.y + ro * 4;
+#pragma unroll
+                        for (int k = 0; k < 4; k++) dst[k] = o[k];
+                    } else if (a.out_mode == UMX_OUT_MX || a.out_mode == UMX_OUT_MXRAW) {
+                        unsigned w[8]; unsigned sbyte;
+                        uint8_t *yb = (uint8_t *)a.y;
+                        if (a.out_bits == 8) {
+                            sbyte = mx_encode_row32<8>(v, w);
+                            uint4 *dst = (uint4 *)(yb + ro * 32);
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]); dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                            yb[(size_t)a.N * a.nb_dst * So * 32 + ro] = (uint8_t)sbyte;
+                        } else {
+                            sbyte = mx_encode_row32<4>(v, w);
+                            *(uint4 *)(yb + ro * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                            yb[(size_t)a.N * a.nb_dst * So * 16 + ro] = (uint8_t)sbyte;
+                        }
+                    } else {
+                        for (int k = 0; k < 32; k++) {
+                            const int c = ob * 32 + k; if (c >= a.co_real) break;
+                            const size_t o = ((size_t)n * a.co_real + c) * So + vo;
+                            if (a.out_mode == UMX_OUT_PM32) ((float *)a.y)[o] = v[k]; else ((__half *)a.y)[o] = __float2half_rn(v[k]);
+                        }
+                    }
+                }
+                if (a.part) {
+                    /* per-channel sums over this warp's 32 rows: a butterfly that halves the array each step, ending with
+                       channel `lane` in every lane; fp64, fixed order */
+                    double s1[32], s2[32];
+#pragma unroll
+                    for (int k = 0; k < 32; k++) { const double t = row_ok ? (double)v[k] : 0.0; s1[k] = t; s2[k] = t * t; }
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) {
+                        const bool up = (lane & o) != 0;
+#pragma unroll
+                        for (int i = 0; i < o; i++) {
+                            const double k1 = up ? s1[i + o] : s1[i], g1 = up ? s1[i] : s1[i + o];
+                            const double k2 = up ? s2[i + o] : s2[i], g2 = up ? s2[i] : s2[i + o];
+                            s1[i] = k1 + __shfl_xor_sync(0xffffffffu, g1, o);
+                            s2[i] = k2 + __shfl_xor_sync(0xffffffffu, g2, o);
+                        }
+                    }
+                    spart[((q4 * 4 + jc) * 32 + lane) * 2] = s1[0];
+                    spart[((q4 * 4 + jc) * 32 + lane) * 2 + 1] = s2[0];
+                }
+            }
+            if (a.part) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                /* 128 threads: (chunk, lane) pairs; add the four quarters in order */
+                const int e = (int)threadIdx.x - 64;
+                if (e < nchunk * 32) {
+                    const int jc = e >> 5, l = e & 31;
+                    double t1 = 0.0, t2 = 0.0;
+#pragma unroll
+                    for (int qq = 0; qq < 4; qq++) { t1 += spart[((qq * 4 + jc) * 32 + l) * 2]; t2 += spart[((qq * 4 + jc) * 32 + l) * 2 + 1]; }
+                    double *dst = a.part + (((size_t)n * T + tsp) * a.cop + n0 + jc * 32 + l) * 2;
+                    dst[0] = t1; dst[1] = t2;
+                }
+            }
+        }
+    }
+    /* ---------------- teardown ---------------- */
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && warp == 0 && lane == 0) {
+        /* after a give-up: let this thread's own copies in flight land (bounded) before the block's shared memory is released */
+        for (int s = 0; s < R; s++) { const long long t0 = clock64(); while (!mbar_try(bar_tma + 8 * s, 0) && !mbar_try(bar_tma + 8 * s, 1) && clock64() - t0 < 20000000ll) { } }
+    }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
+}
+
+/* ---- weight preparation: fp32 weights -> the shared-memory image of every (column tile, stage): items x [k half][row][16 B]
+   codes, then the scale bytes in the TMEM scale layout (quad, lane, column, byte).  One thread per (column tile, stage, item, row).
+   Quantisation per (row, tap, 32 input channels) as the reference's prep_w8_k / prep_w4_k (src/lp_f8fwd.cu:54-71,
+   src/lp_f4fwd.cu:53-66). ---- */
+struct PrepArgs {
+    const float *w; uint8_t *wpk; const float *bias; float *bias_p;
+    int kind, co, ci, bits, cop, cob_t, nkb, nki, taps, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
+};
+__device__ __forceinline__ float prep_src(const PrepArgs &p, int row, int tap, int kb, int k) {
+    /* value of GEMM row `row`, tap `tap`, K block `kb`, element k (0 outside the real weights) */
+    if (kb >= p.nkb) return 0.f;
+    if (p.kind == UMX_CONV3) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + tap] : 0.f; }
+    if (p.kind == UMX_CONV1) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[(size_t)row * p.ci + ci] : 0.f; }
+    if (p.kind == UMX_DOWN2) {   /* K block = sub-voxel tap * blocks(ci) + block */
+        const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
+        return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 8 + t] : 0.f;
+    }
+    /* UMX_TCONV2: row = abc * (32 cob_t) + o, w [ci][co][8] */
+    const int abc = row / (32 * p.cob_t), o = row % (32 * p.cob_t), ci = kb * 32 + k;
+    return (o < p.co && ci < p.ci) ? p.w[((size_t)ci * p.co + o) * 8 + abc] : 0.f;
+}
+__global__ void __launch_bounds__(128) prep_w_k(const PrepArgs p) {
+    const size_t total = (size_t)p.ntiles_n * p.nst * p.items_max * p.nt;
+    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i == 0 && p.bias_p) for (int c = 0; c < p.cop; c++) {
+        float b = 0.f;
+        if (p.bias) { if (p.kind == UMX_TCONV2) { const int o = c % (32 * p.cob_t); b = o < p.co ? p.bias[o] : 0.f; } else b = c < p.co ? p.bias[c] : 0.f; }
+        p.bias_p[c] = b;
+    }
+    if (i >= total) return;
+    const int rl = (int)(i % p.nt), j = (int)((i / p.nt) % p.items_max), st = (int)((i / ((size_t)p.nt * p.items_max)) % p.nst), ntile = (int)(i / ((size_t)p.nt * p.items_max * p.nst));
+    const int row = ntile * p.nt + rl;
+    int tap, ki;
+    if (p.taps == 27) { ki = st / 3; tap = (st % 3) * 9 + j; } else { ki = 4 * st + j; tap = 0; }
+    uint8_t *stg = p.wpk + ((size_t)ntile * p.nst + st) * p.w_stage_bytes;
+    const bool live = row < p.cop && ki < p.nki;
+    unsigned w[8]; unsigned sb[2] = {127u, 127u};
+    float v[32];
+    if (p.bits == 8) {
+#pragma unroll
+        for (int k = 0; k < 32; k++) v[k] = live ? prep_src(p, row, tap, ki, k) : 0.f;
+        sb[0] = mx_encode_row32<8>(v, w);
+    } else {
+        unsigned w4[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+#pragma unroll
+            for (int k = 0; k < 32; k++) v[k] = live ? prep_src(p, row, tap, 2 * ki + h, k) : 0.f;
+            sb[h] = mx_encode_row32<4>(v, w4);
+#pragma unroll
+            for (int t = 0; t < 4; t++) w[4 * h + t] = w4[t];
+        }
+    }
+    if (!live) { sb[0] = 127u; sb[1] = 127u; }
+    uint4 *d0 = (uint4 *)(stg + ((size_t)(j * 2 + 0) * p.nt + rl) * 16), *d1 = (uint4 *)(stg + ((size_t)(j * 2 + 1) * p.nt + rl) * 16);
+    *d0 = make_uint4(w[0], w[1], w[2], w[3]); *d1 = make_uint4(w[4], w[5], w[6], w[7]);
+    uint8_t *sf = stg + (size_t)p.items_max * p.nt * 32;
+    const int q = j / p.ipq, l = rl & 31, c = rl >> 5;
+    if (p.bits == 8) sf[q * 512 + l * 16 + c * 4 + (j & 3)] = (uint8_t)sb[0];
+    else { sf[q * 512 + l * 16 + c * 4 + (j & 1) * 2] = (uint8_t)sb[0]; sf[q * 512 + l * 16 + c * 4 + (j & 1) * 2 + 1] = (uint8_t)sb[1]; }
+}
+
+typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+encode_fn get_encode() {
+    static encode_fn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr; cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) { umx_latch_msg("cuTensorMapEncodeTiled is not available from the driver"); return nullptr; }
+        fn = (encode_fn)p;
+    }
+    return fn;
+}
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}   // namespace
+
+struct umx_conv {
+    int kind, co, ci, bits;
+    int taps, nkb, nki, cop, cob_t, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
+    uint8_t *wpk; float *bias_p;
+};
+
+static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
+    if (!umx_ready("umx_conv_create")) return nullptr;
+    if ((bits != 8 && bits != 4) || kind < 0 || kind > 3 || co < 1 || ci < 1) { fprintf(stderr, "umx_conv_create: bad arguments (kind %d, co %d, ci %d, bits %d)\n", kind, co, ci, bits); abort(); }
+    umx_conv *c = (umx_conv *)calloc(1, sizeof *c);
+    c->kind = kind; c->co = co; c->ci = ci; c->bits = bits;
+    c->taps = kind == UMX_CONV3 ? 27 : 1;
+    const int nbi = ceil_div(ci, 32);
+    c->nkb = kind == UMX_DOWN2 ? 8 * nbi : nbi;
+    c->nki = bits == 8 ? c->nkb : ceil_div(c->nkb, 2);
+    c->cob_t = ceil_div(co, 32);
+    c->cop = (kind == UMX_TCONV2 ? 8 : 1) * c->cob_t * 32;
+    c->nt = c->cop >= 128 ? 128 : c->cop;               /* 32, 64, 96 or 128 */
+    c->ntiles_n = ceil_div(c->cop, c->nt);
+    c->items_max = c->taps == 27 ? 9 : 4;
+    c->ipq = bits == 8 ? 4 : 2;
+    c->nquad = ceil_div(c->items_max, c->ipq);
+    c->nst = c->taps == 27 ? 3 * c->nki : ceil_div(c->nki, 4);
+    c->w_stage_bytes = c->items_max * c->nt * 32 + c->nquad * 512;
+    const size_t wb = (size_t)c->ntiles_n * c->nst * c->w_stage_bytes;
+    c->wpk = (uint8_t *)nn_malloc(wb); c->bias_p = (float *)nn_malloc((size_t)c->cop * 4);
+    if (!c->wpk || !c->bias_p) { umx_conv_free(c); return nullptr; }
+    cudaMemset(c->wpk, 127, wb);   /* unused scale slots read as 1 */
+    PrepArgs p; memset(&p, 0, sizeof p);
+    p.w = w_dev; p.wpk = c->wpk; p.bias = bias_dev; p.bias_p = c->bias_p; p.kind = kind; p.co = co; p.ci = ci; p.bits = bits; p.cop = c->cop; p.cob_t = c->cob_t;
+    p.nkb = c->nkb; p.nki = c->nki; p.taps = c->taps; p.nt = c->nt; p.ntiles_n = c->ntiles_n; p.nst = c->nst; p.items_max = c->items_max; p.ipq = c->ipq; p.nquad = c->nquad; p.w_stage_bytes = c->w_stage_bytes;
+    const size_t total = (size_t)c->ntiles_n * c->nst * c->items_max * c->nt;
+    prep_w_k<<<(unsigned)((total + 127) / 128), 128>>>(p);
+    g_umx_launches++;
+    UMX_CK("umx_conv_create");
+    return c;
+}
+extern "C" umx_conv *umx_conv_create_dev(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) { return conv_build(kind, w_dev, bias_dev, co, ci, bits); }
+extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias, int co, int ci, int bits) {
+    if (!umx_ready("umx_conv_create")) return nullptr;
+    const size_t nw = (size_t)co * ci * (kind == UMX_CONV3 ? 27 : kind == UMX_CONV1 ? 1 : 8);
+    float *wd = (float *)nn_malloc(nw * 4), *bd = bias ? (float *)nn_malloc((size_t)co * 4) : nullptr;
+    if (!wd || (bias && !bd)) { nn_free(wd); nn_free(bd); return nullptr; }
+    nn_h2d(wd, w, nw * 4); if (bias) nn_h2d(bd, bias, (size_t)co * 4);
+    umx_conv *c = conv_build(kind, wd, bd, co, ci, bits);
+    cudaDeviceSynchronize();
+    nn_free(wd); nn_free(bd);
+    return c;
+}
+extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); free(c); }
+extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * D * ceil_div(H, 16) * ceil_div(W, 8) * (size_t)(ceil_div(co, 32) * 32) * 2; }
+
+extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part) {
+    if (!umx_ready("umx_conv_fwd")) return -1;
+    if (!c) { umx_latch_msg("umx_conv_fwd: no conv"); return -1; }
+    if (part && (out_mode != UMX_OUT_H16B || c->kind == UMX_TCONV2)) { fprintf(stderr, "umx_conv_fwd: partial sums only with a blocked fp16 output of a plain conv\n"); abort(); }
+    if ((out_mode == UMX_OUT_MX || out_mode == UMX_OUT_MXRAW) && out_bits != 8 && out_bits != 4) { fprintf(stderr, "umx_conv_fwd: MX output needs out_bits 8 or 4\n"); abort(); }
+    encode_fn enc = get_encode(); if (!enc) return -1;
+    ConvArgs a; memset(&a, 0, sizeof a);
+    a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.taps = c->taps; a.bits = c->bits;
+    a.cop = c->cop; a.nt = c->nt; a.ntiles_n = c->ntiles_n; a.tiles_x = ceil_div(W, 8); a.tiles_y = ceil_div(H, 16);
+    a.w_stage_bytes = c->w_stage_bytes; a.nst = c->nst; a.items_max = c->items_max; a.ipq = c->ipq; a.nquad = c->nquad;
+    const int abytes = c->taps == 27 ? 2944 * 2 : 4 * 4096;   /* fp8 3^3: the second 16-byte plane starts at the next 128-byte boundary after 2880 */
+    auto up128 = [](int v) { return (v + 127) & ~127; };
+    a.offW = 0; a.offSFB = c->items_max * c->nt * 32; a.offA = up128(c->w_stage_bytes); a.offSFA = a.offA + up128(abytes);
+    a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
+    const int budget = c->nt > 64 ? 200 * 1024 : 100 * 1024;   /* two blocks a multiprocessor for the narrow tiles */
+    a.ring = budget / a.stage_bytes; if (a.ring > 8) a.ring = 8; if (a.ring < 2) a.ring = 2;
+    const size_t S = (size_t)D * H * W;
+    const int rb = c->bits == 8 ? 32 : 16;
+    a.x_sc = (const uint8_t *)x + (size_t)N * c->nkb * S * rb;
+    a.wpk = c->wpk; a.bias = c->bias_p;
+    a.out_mode = out_mode; a.out_bits = out_bits; a.tconv = c->kind == UMX_TCONV2; a.co_real = c->co; a.cob_t = c->cob_t;
+    a.nb_dst = nb_dst ? nb_dst : c->cob_t; a.b0 = nb_dst ? b0 : 0;
+    a.y = y; a.part = part; a.err = umx_errflag();
+    if (!a.err) return -1;
+    /* tensor maps over the activation codes */
+    CUtensorMap m0, m1; memset(&m0, 0, sizeof m0); memset(&m1, 0, sizeof m1);
+    const cuuint32_t bx = c->taps == 27 ? 10 : 8, by = c->taps == 27 ? 18 : 16;
+    CUresult r0, r1 = CUDA_SUCCESS;
+    if (c->bits == 8) {
+        const cuuint64_t gd[4] = {16, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)D * N * c->nkb};
+        const cuuint64_t gs[3] = {32, (cuuint64_t)32 * W, (cuuint64_t)32 * W * H};
+        const cuuint32_t box[4] = {16, bx, by, 1}, es[4] = {1, 1, 1, 1};
+        r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        r1 = enc(&m1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)((const uint8_t *)x + 16), gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t gd[5] = {16, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)D, (cuuint64_t)N * c->nkb};
+        const cuuint64_t gs[4] = {16, (cuuint64_t)16 * W, (cuuint64_t)16 * W * H, (cuuint64_t)16 * S};
+        const cuuint32_t box[5] = {16, bx, by, 1, 2}, es[5] = {1, 1, 1, 1, 1};
+        r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        m1 = m0;
+    }
+    if (r0 != CUDA_SUCCESS || r1 != CUDA_SUCCESS) { char b[160]; snprintf(b, sizeof b, "umx_conv_fwd: cuTensorMapEncodeTiled failed (%d, %d) for %d x %d x %d x %d, %d blocks", (int)r0, (int)r1, N, D, H, W, c->nkb); umx_latch_msg(b); return -1; }
+    const size_t smem = 1024 + (size_t)a.ring * a.stage_bytes;
+    static size_t smem_set[16];
+    int dev = 0; cudaGetDevice(&dev); dev &= 15;
+    if (smem_set[dev] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(conv_mx_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+        if (e != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", e); return -1; }
+        smem_set[dev] = 227 * 1024;
+    }
+    const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n);
+    conv_mx_k<<<grid, kThreads, smem>>>(m0, m1, a);
+    g_umx_launches++;
+    UMX_CK("umx_conv_fwd");
+    return 0;
+}

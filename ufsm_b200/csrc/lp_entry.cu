@@ -1,0 +1,61 @@
+/* The reference's conv entry points lp_conv_fwd_f8 / lp_conv_fwd_f4 (src/nn_lp.h:53-54) on top of the tcgen05 conv: same
+   signature, storage codes and error behaviour; the prepared weights are memoised under split_t.wkey as the reference's fp4
+   kernel does (src/lp_f4fwd.cuh:748-770). */
+#include "mx_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+struct memo_t { unsigned wkey; const float *w, *b; int cout, cin, bits, dev; umx_conv *c; };
+static memo_t g_memo[256];
+static int g_nmemo = 0;
+
+extern "C" void lp_wmemo_clear(void) {
+    cudaDeviceSynchronize();
+    for (int i = 0; i < g_nmemo; i++) umx_conv_free(g_memo[i].c);
+    g_nmemo = 0;
+}
+static void not_built(const char *fn, const char *what) { fprintf(stderr, "%s: %s is not built in this library\n", fn, what); abort(); }
+
+static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
+    if (!umx_ready(fn)) return 0;
+    if (gp.G) not_built(fn, "the GroupNorm + SiLU input transform (gnp_t.G != 0)");
+    if (osum || Go) not_built(fn, "output GroupNorm statistics (osum)");
+    if (sp.x2 || sp.y2 || sp.accum || sp.gp2.G || sp.up || sp.yD || sp.sr || sp.osr || sp.zlo || sp.zhi || sp.stored_stats || sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yzo || sp.c_split || sp.o_split || sp.o_pad)
+        not_built(fn, "a non-zero split_t field other than wkey");
+    if (xs.c <= 16) not_built(fn, "an input of 16 channels or fewer (8 / 16-wide MX rows)");
+    const int mxin = bits == 8 ? UMX_MX8 : UMX_MX4;
+    if (xbf != UMX_F16 && xbf != mxin) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX-fp%d)\n", fn, xbf, bits); abort(); }
+    int out_mode, out_bits = 0;
+    if (ybf == UMX_F16) out_mode = UMX_OUT_PM16;
+    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; if (cout <= 16) not_built(fn, "an MX output of 16 channels or fewer"); }
+    else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
+    else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
+    const size_t S = (size_t)xs.d * xs.h * xs.w;
+    const void *xq = x;
+    if (xbf == UMX_F16) {
+        void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, xs.c, S));
+        if (!ws) return 0;
+        umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, bits);
+        xq = ws;
+    }
+    int dev = 0; cudaGetDevice(&dev);
+    umx_conv *c = nullptr; bool temp = true;
+    if (sp.wkey) {
+        for (int i = 0; i < g_nmemo; i++) { memo_t &m = g_memo[i]; if (m.wkey == sp.wkey && m.w == w && m.b == b && m.cout == cout && m.cin == xs.c && m.bits == bits && m.dev == dev) { c = m.c; break; } }
+        temp = false;
+    }
+    if (!c) {
+        c = umx_conv_create_dev(UMX_CONV3, w, b, cout, xs.c, bits);
+        if (!c) return 0;
+        if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout, xs.c, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
+    }
+    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr);
+    if (temp) { cudaDeviceSynchronize(); umx_conv_free(c); }
+    return 0;
+}
+extern "C" int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
+    return conv_fwd("lp_conv_fwd_f8", 8, x, xbf, xs, w, b, cout, y, ybf, gp, osum, Go, sp);
+}
+extern "C" int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
+    return conv_fwd("lp_conv_fwd_f4", 4, x, xbf, xs, w, b, cout, y, ybf, gp, osum, Go, sp);
+}

@@ -1,0 +1,76 @@
+/* Device helpers shared by the MX kernels: block exponent, element encoders / decoders, error latch. */
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/ufsm_mx.h"
+
+/* ---- error latch (host side; the convention of the reference's LPCK / lp_check, src/lp_common.cuh:35-38) ---- */
+void umx_latch(const char *where, cudaError_t e);
+void umx_latch_msg(const char *msg);
+int umx_ready(const char *where);   /* 1 when a usable sm_100 device is current; otherwise latches and returns 0 */
+#define UMX_CK(where) do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) umx_latch(where, e_); } while (0)
+void *umx_ws(int slot, size_t bytes);   /* per-device scratch that only grows (the role of the reference's nn_ws registry, src/nn.h:732-739) */
+int *umx_errflag(void);                 /* device int the kernels report bounded-wait failures into */
+int umx_errflag_read(void);             /* synchronises, reads and clears it */
+extern long g_umx_launches;
+
+/* ---- MX arithmetic ---- */
+/* exponent e of the block scale 2^e = exponent of amax / qmax rounded up, clamped to [-126, 126]; NaN / inf amax -> 128 (scale
+   byte 0xFF).  Same rule as src/lp_common.cuh:492-500. */
+__device__ __forceinline__ int mx_exp(float amax, float inv_qmax) {
+    const unsigned u = __float_as_uint(__fmul_rn(amax, inv_qmax));
+    if ((u & 0x7fffffffu) >= 0x7f800000u) return 128;
+    const int e = (int)((u >> 23) & 0xffu) - 127 + ((u & 0x7fffffu) != 0);
+    return max(-126, min(126, e));
+}
+__device__ __forceinline__ float exp2i(int e) { return __uint_as_float((unsigned)(127 + e) << 23); }
+/* NaN-propagating amax on the magnitude bits (src/lp_common.cuh:486) */
+__device__ __forceinline__ unsigned amax_u(unsigned a, float v) { return max(a, __float_as_uint(v) & 0x7fffffffu); }
+/* scale byte -> factor; 0xFF -> +inf, 0 -> 2^-127 */
+__device__ __forceinline__ float mx_scale(unsigned b) { b &= 0xffu; return b == 0xffu ? __uint_as_float(0x7f800000u) : b == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(b << 23); }
+
+/* four floats -> four e4m3 bytes (a lowest): cvt.rn.satfinite, the hardware conversion the reference's integer code mirrors */
+__device__ __forceinline__ unsigned cvt_e4m3x4(float a, float b, float c, float d) {
+    unsigned short lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (unsigned)lo | ((unsigned)hi << 16);
+}
+/* two floats -> one byte of two e2m1 nibbles (lo in the low nibble) */
+__device__ __forceinline__ unsigned cvt_e2m1x2(float lo, float hi) {
+    unsigned short r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return (unsigned)r & 0xffu;
+}
+__device__ __forceinline__ unsigned cvt_e2m1x8(const float *v, float m) {
+    return cvt_e2m1x2(v[0] * m, v[1] * m) | (cvt_e2m1x2(v[2] * m, v[3] * m) << 8) | (cvt_e2m1x2(v[4] * m, v[5] * m) << 16) | (cvt_e2m1x2(v[6] * m, v[7] * m) << 24);
+}
+__device__ __forceinline__ float dec_e4m3(unsigned b) {
+    const unsigned e = (b >> 3) & 15u, m = b & 7u;
+    if ((b & 0x7fu) == 0x7fu) return __uint_as_float(0x7fc00000u | ((b & 0x80u) << 24));
+    const float v = e ? (float)(8u + m) * __uint_as_float((117u + e) << 23) : (float)m * 0.001953125f;
+    return (b & 0x80u) ? -v : v;
+}
+__device__ __forceinline__ float dec_e2m1(unsigned n) {
+    const unsigned k = n & 7u;
+    const float v = (float)(k < 4u ? k : k == 4u ? 4u : k == 5u ? 6u : k == 6u ? 8u : 12u) * 0.5f;
+    return (n & 8u) ? -v : v;
+}
+/* a row of 32 floats -> MX codes: q8 receives 32 bytes (BITS 8: w[0..8)) or 16 bytes (BITS 4: w[0..4)); returns the scale byte */
+template <int BITS> __device__ __forceinline__ unsigned mx_encode_row32(const float *v, unsigned *w) {
+    unsigned am = 0u;
+#pragma unroll
+    for (int k = 0; k < 32; k++) am = amax_u(am, v[k]);
+    const int e = mx_exp(__uint_as_float(am), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
+    const float m = exp2i(-e);
+    if (BITS == 4) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = cvt_e2m1x8(v + 8 * j, m);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) w[j] = cvt_e4m3x4(v[4 * j] * m, v[4 * j + 1] * m, v[4 * j + 2] * m, v[4 * j + 3] * m);
+    }
+    return (unsigned)(e + 127) & 0xffu;
+}

@@ -1,0 +1,103 @@
+/* MX quantiser and inverse: plane-major fp32 / fp16 <-> channel-blocked MX-fp8 / MX-fp4 tensors.
+
+   HBM-bound passes.  A thread owns one (n, block, voxel) row, so the amax that defines the row's scale is local: consecutive
+   lanes own consecutive voxels, every channel plane is read in full sectors (32 lanes x 2 or 4 bytes), and a warp writes one
+   contiguous run of rows (32 x 32 B or 32 x 16 B) plus 32 contiguous scale bytes.  Algorithmic bytes per element: read 4 or 2,
+   write 1 + 1/32 (fp8) or 1/2 + 1/32 (fp4).  Semantics: src/lp_mx_cvt.cu:9-19, src/lp_mxops.cuh:46-68 of the reference. */
+#include "mx_common.cuh"
+
+__host__ __device__ static inline int mxbw(int C, int force) { return force > 0 ? force : C <= 8 ? 8 : C <= 16 ? 16 : 32; }
+
+template <typename T> __device__ __forceinline__ float ld_as_f32(const T *p);
+template <> __device__ __forceinline__ float ld_as_f32<float>(const float *p) { return __ldg(p); }
+template <> __device__ __forceinline__ float ld_as_f32<__half>(const __half *p) { return __half2float(__ldg(p)); }
+
+template <int BITS, typename TI>
+__global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw) {
+    const int nb = (C + bw - 1) / bw, rb = bw * BITS / 8;
+    const size_t rows = (size_t)N * nb * S;
+    uint8_t *sc = y + rows * rb;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t v = i % S; const int blk = (int)((i / S) % nb), n = (int)(i / (S * nb));
+        float r[32];
+#pragma unroll
+        for (int k = 0; k < 32; k++) { const int c = blk * bw + k; r[k] = (k < bw && c < C) ? ld_as_f32(x + ((size_t)n * C + c) * S + v) : 0.f; }
+        unsigned w[8];
+        const unsigned sb = mx_encode_row32<BITS>(r, w);
+        uint8_t *p = y + i * rb;
+        if (BITS == 8) {
+            if (bw == 32) { ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]); ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]); }
+            else if (bw == 16) ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            else ((uint2 *)p)[0] = make_uint2(w[0], w[1]);
+        } else {
+            if (bw == 32) ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            else if (bw == 16) ((uint2 *)p)[0] = make_uint2(w[0], w[1]);
+            else ((unsigned *)p)[0] = w[0];
+        }
+        sc[i] = (uint8_t)sb;
+    }
+}
+template <int BITS>
+__global__ void __launch_bounds__(256) mx_to_pm_k(const uint8_t *__restrict__ x, float *__restrict__ y, int N, int C, size_t S, int bw) {
+    const int nb = (C + bw - 1) / bw, rb = bw * BITS / 8;
+    const size_t rows = (size_t)N * nb * S;
+    const uint8_t *sc = x + rows * rb;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t v = i % S; const int blk = (int)((i / S) % nb), n = (int)(i / (S * nb));
+        const float s = mx_scale(sc[i]);
+        const uint8_t *p = x + i * rb;
+        for (int k = 0; k < bw; k++) {
+            const int c = blk * bw + k; if (c >= C) break;
+            const float e = BITS == 8 ? dec_e4m3(p[k]) : dec_e2m1((p[k >> 1] >> ((k & 1) * 4)) & 15u);
+            y[((size_t)n * C + c) * S + v] = e * s;
+        }
+    }
+}
+__global__ void __launch_bounds__(256) h16b_to_pm_k(const __half *__restrict__ x, float *__restrict__ y, int N, int C, size_t S) {
+    const int nb = (C + 31) / 32;
+    const size_t rows = (size_t)N * nb * S;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t v = i % S; const int blk = (int)((i / S) % nb), n = (int)(i / (S * nb));
+        for (int k = 0; k < 32; k++) { const int c = blk * 32 + k; if (c >= C) break; y[((size_t)n * C + c) * S + v] = __half2float(x[i * 32 + k]); }
+    }
+}
+
+static unsigned grid_for(size_t rows) { size_t g = (rows + 255) / 256; return (unsigned)(g > 148u * 64u ? 148u * 64u : g ? g : 1); }
+
+static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int bwf, const char *who) {
+    if (!umx_ready(who)) return;
+    if (dt != 0 && dt != 2) { fprintf(stderr, "%s: source type %d is not built (fp32 and fp16 only)\n", who, dt); abort(); }
+    const int bw = mxbw(C, bwf);
+    const size_t rows = (size_t)N * ((C + bw - 1) / bw) * S;
+    const unsigned g = grid_for(rows);
+    if (bits == 8) { if (dt == 2) pm_to_mx_k<8, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw); else pm_to_mx_k<8, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw); }
+    else { if (dt == 2) pm_to_mx_k<4, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw); else pm_to_mx_k<4, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw); }
+    g_umx_launches++;
+    UMX_CK(who);
+}
+static void from_mx(const void *x, int N, int C, size_t S, float *y, int bits, int bwf, const char *who) {
+    if (!umx_ready(who)) return;
+    const int bw = mxbw(C, bwf);
+    const size_t rows = (size_t)N * ((C + bw - 1) / bw) * S;
+    if (bits == 8) mx_to_pm_k<8><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw);
+    else mx_to_pm_k<4><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw);
+    g_umx_launches++;
+    UMX_CK(who);
+}
+extern "C" size_t lp_mx8_bytes(int N, int C, size_t S) { const int bw = mxbw(C, 0); return (size_t)N * ((C + bw - 1) / bw) * S * (bw + 1); }
+extern "C" size_t lp_mx4_bytes(int N, int C, size_t S) { const int bw = mxbw(C, 0); return (size_t)N * ((C + bw - 1) / bw) * S * (bw / 2 + 1); }
+extern "C" size_t umx_mx_bytes32(int bits, int N, int C, size_t S) { return (size_t)N * ((C + 31) / 32) * S * (32 * bits / 8 + 1); }
+extern "C" void lp_f32_to_mx8(const float *x, int N, int C, size_t S, void *y) { to_mx(x, 0, N, C, S, y, 8, 0, "lp_f32_to_mx8"); }
+extern "C" void lp_f32_to_mx4(const float *x, int N, int C, size_t S, void *y) { to_mx(x, 0, N, C, S, y, 4, 0, "lp_f32_to_mx4"); }
+extern "C" void lp_h16_to_mx8(const void *x, int dt, int N, int C, size_t S, void *y) { to_mx(x, dt, N, C, S, y, 8, 0, "lp_h16_to_mx8"); }
+extern "C" void lp_h16_to_mx4(const void *x, int dt, int N, int C, size_t S, void *y) { to_mx(x, dt, N, C, S, y, 4, 0, "lp_h16_to_mx4"); }
+extern "C" void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 8, 0, "lp_mx8_to_f32"); }
+extern "C" void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 4, 0, "lp_mx4_to_f32"); }
+extern "C" void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits) { to_mx(x, dt, N, C, S, y, bits, 32, "umx_pm_to_mx32"); }
+extern "C" void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, bits, 32, "umx_mx32_to_f32"); }
+extern "C" void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y) {
+    if (!umx_ready("umx_h16b_to_f32")) return;
+    h16b_to_pm_k<<<grid_for((size_t)N * ((C + 31) / 32) * S), 256>>>((const __half *)x, y, N, C, S);
+    g_umx_launches++;
+    UMX_CK("umx_h16b_to_f32");
+}

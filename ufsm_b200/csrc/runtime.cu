@@ -1,0 +1,101 @@
+/* Device runtime of the library: device selection, memory, the error latch, growing scratch buffers. */
+#include "mx_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+long g_umx_launches = 0;
+static thread_local char g_err[512];
+static thread_local int g_has_err = 0;
+static int g_ready[16];   /* per device: 0 unknown, 1 usable sm_100, -1 not usable */
+
+void umx_latch_msg(const char *msg) {
+    if (g_has_err) return;
+    snprintf(g_err, sizeof g_err, "%s", msg);
+    g_has_err = 1;
+}
+void umx_latch(const char *where, cudaError_t e) {
+    char b[512]; snprintf(b, sizeof b, "%s: %s", where, cudaGetErrorString(e));
+    umx_latch_msg(b);
+}
+int umx_ready(const char *where) {
+    int d = -1;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess || d < 0 || d >= 16) { char b[256]; snprintf(b, sizeof b, "%s: no CUDA device (%s); this library has no CPU path", where, cudaGetErrorString(e)); umx_latch_msg(b); cudaGetLastError(); return 0; }
+    if (!g_ready[d]) {
+        cudaDeviceProp p; e = cudaGetDeviceProperties(&p, d);
+        g_ready[d] = (e == cudaSuccess && p.major == 10) ? 1 : -1;
+    }
+    if (g_ready[d] < 0) { char b[256]; snprintf(b, sizeof b, "%s: device %d is not sm_100 (B200); this library has no other path", where, d); umx_latch_msg(b); return 0; }
+    return 1;
+}
+static int *g_flag[16];
+extern "C" const char *lp_check(void) {
+    int d = -1;
+    if (!g_has_err && cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 16 && g_flag[d]) umx_errflag_read();   /* a kernel's bounded wait that gave up */
+    if (!g_has_err) return nullptr;
+    g_has_err = 0;
+    return g_err;
+}
+extern "C" const char *nn_check(void) { return lp_check(); }
+extern "C" int nn_init(int device) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { umx_latch("nn_init", e); return -1; }
+    return umx_ready("nn_init") ? 0 : -1;
+}
+extern "C" void *nn_malloc(size_t bytes) {
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess) { umx_latch("nn_malloc", e); return nullptr; }
+    return p;
+}
+extern "C" void nn_free(void *p) { if (p) cudaFree(p); }
+extern "C" void nn_zero(void *p, size_t bytes) { cudaError_t e = cudaMemset(p, 0, bytes); if (e != cudaSuccess) umx_latch("nn_zero", e); }
+extern "C" void nn_h2d(void *dst, const void *src, size_t bytes) { cudaError_t e = cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice); if (e != cudaSuccess) umx_latch("nn_h2d", e); }
+extern "C" void nn_d2h(void *dst, const void *src, size_t bytes) { cudaError_t e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost); if (e != cudaSuccess) umx_latch("nn_d2h", e); }
+extern "C" void nn_sync(void) {
+    cudaError_t e = cudaDeviceSynchronize(); if (e != cudaSuccess) { umx_latch("nn_sync", e); return; }
+    int d = -1; if (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 16 && g_flag[d]) umx_errflag_read();
+}
+extern "C" void *nn_malloc_host(size_t bytes) {
+    void *p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault);
+    if (e != cudaSuccess) { umx_latch("nn_malloc_host", e); return nullptr; }
+    return p;
+}
+extern "C" void nn_free_host(void *p) { if (p) cudaFreeHost(p); }
+
+/* scratch: per device, per slot, grows on demand, never shrinks */
+enum { WS_SLOTS = 8 };
+static void *g_ws[16][WS_SLOTS];
+static size_t g_ws_bytes[16][WS_SLOTS];
+void *umx_ws(int slot, size_t bytes) {
+    int d = 0; cudaGetDevice(&d); d &= 15;
+    if (g_ws_bytes[d][slot] < bytes) {
+        if (g_ws[d][slot]) { cudaDeviceSynchronize(); cudaFree(g_ws[d][slot]); }
+        const size_t nb = bytes + bytes / 4 + 256;
+        cudaError_t e = cudaMalloc(&g_ws[d][slot], nb);
+        if (e != cudaSuccess) { umx_latch("umx_ws", e); g_ws[d][slot] = nullptr; g_ws_bytes[d][slot] = 0; return nullptr; }
+        g_ws_bytes[d][slot] = nb;
+    }
+    return g_ws[d][slot];
+}
+int *umx_errflag(void) {
+    int d = 0; cudaGetDevice(&d); d &= 15;
+    if (!g_flag[d]) {
+        if (cudaMalloc(&g_flag[d], 64) != cudaSuccess) { umx_latch_msg("umx_errflag: cudaMalloc failed"); return nullptr; }
+        cudaMemset(g_flag[d], 0, 64);
+    }
+    return g_flag[d];
+}
+int umx_errflag_read(void) {
+    int *f = umx_errflag(); if (!f) return -1;
+    int h[4] = {0, 0, 0, 0};
+    cudaError_t e = cudaMemcpy(h, f, sizeof h, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { umx_latch("umx_errflag_read", e); return -1; }
+    if (h[0]) {
+        char b[256]; snprintf(b, sizeof b, "conv kernel: bounded wait gave up (code %d, block %d, stage %d, info %d)", h[0], h[1], h[2], h[3]);
+        umx_latch_msg(b);
+        cudaMemset(f, 0, 64);
+    }
+    return h[0];
+}

@@ -1,0 +1,233 @@
+/* Host side (C23) of the BASELINE 3-D U-Net forward and of the sliding-window scheduler, on top of the C ABI of ufsm_mx.h.
+
+   Network (the InstanceNorm / LeakyReLU / transposed-conv graph of the reference's ink U-Net, src/ink3dext_net.c:189-231, with
+   the widths and layer list of the benchmark): per level two 3^3 convs, each conv -> fp16 store + InstanceNorm partial sums in
+   the conv epilogue -> coefficients -> fused apply (affine, LeakyReLU 0.01, fp16 rounding, MX requantisation for the next conv).
+   The second apply of an encoder level writes the skip half of the decoder's concat tensor directly and a space-to-depth copy
+   that turns the 2^3 stride-2 down conv into a 1^3 GEMM; the transposed conv is a GEMM to 8 Cout columns whose epilogue scatters
+   and requantises straight into the other half of the concat tensor (xtconv_cat_q, src/nn_xnet.cu:1775-1789).  Every tensor's MX
+   format is that of the conv that reads it.  All buffers are allocated once at creation. */
+#include "../../include/ufsm_mx.h"
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+void umx_u8_to_h16(const uint8_t *x, size_t n, void *y);
+void umx_blend_add(const void *logits, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, float *acc, float *wsum);
+long umx_launch_count(void);
+
+enum { MAXL = 8 };
+struct umx_unet {
+    umx_unet_cfg cfg; int maxN;
+    umx_conv *enc1[MAXL], *enc2[MAXL], *down[MAXL], *up[MAXL], *dec1[MAXL], *dec2[MAXL], *head;
+    int Dl[MAXL];
+    void *x_mx;              /* quantised network input (one channel in a 32-wide block) */
+    void *ybuf;              /* blocked fp16 conv output, reused by every conv */
+    double *part; float *coef;
+    void *act[MAXL];         /* MX activation between the two convs of a level (encoder and decoder reuse it) */
+    void *cat[MAXL];         /* MX concat (up | skip), 2 C_l channels; level L-1: the bottom activation, C channels */
+    void *s2d[MAXL];         /* space-to-depth copy of the skip, the down conv's input */
+    void *dn[MAXL];          /* MX output of down l-1 = input of enc l c1 (l >= 1) */
+    void *dec[MAXL];         /* MX output of dec l c2 */
+    void *x16, *xu8, *logits16;   /* staging for the host entry */
+    long launches0;
+};
+
+static size_t cube(int d) { return (size_t)d * d * d; }
+static size_t conv_nw(int co, int ci, int taps) { return (size_t)co * ci * taps + (size_t)co; }
+
+size_t umx_unet_nweights(const umx_unet_cfg *c) {
+    size_t n = 0;
+    for (int l = 0; l < c->L; l++) {
+        n += conv_nw(c->cw[l], l ? c->cw[l] : 1, 27) + conv_nw(c->cw[l], c->cw[l], 27);
+        if (l < c->L - 1) n += conv_nw(c->cw[l + 1], c->cw[l], 8);
+    }
+    for (int l = c->L - 2; l >= 0; l--) n += conv_nw(c->cw[l], c->cw[l + 1], 8) + conv_nw(c->cw[l], 2 * c->cw[l], 27) + conv_nw(c->cw[l], c->cw[l], 27);
+    return n + conv_nw(c->nh, c->cw[0], 1);
+}
+double umx_unet_flops(const umx_unet_cfg *c) {
+    double f = 0; int D = c->P;
+    int Dl[MAXL]; for (int l = 0; l < c->L; l++) { Dl[l] = D; D /= 2; }
+    for (int l = 0; l < c->L; l++) {
+        const double S = (double)cube(Dl[l]);
+        f += 2.0 * S * 27 * ((l ? c->cw[l] : 1) * (double)c->cw[l] + (double)c->cw[l] * c->cw[l]);
+        if (l < c->L - 1) f += 2.0 * (S / 8) * 8 * (double)c->cw[l] * c->cw[l + 1] * 2;   /* down l and up l */
+        if (l < c->L - 1) f += 2.0 * S * 27 * (2.0 * c->cw[l] * c->cw[l] + (double)c->cw[l] * c->cw[l]);
+    }
+    return f + 2.0 * (double)cube(c->P) * c->cw[0] * c->nh;
+}
+
+static umx_conv *mk(int kind, const float **wp, int co, int ci, int taps, int bits) {
+    const float *w = *wp, *b = w + (size_t)co * ci * taps;
+    *wp = b + co;
+    return umx_conv_create(kind, w, b, co, ci, bits);
+}
+void umx_unet_free(umx_unet *u) {
+    if (!u) return;
+    for (int l = 0; l < MAXL; l++) {
+        umx_conv_free(u->enc1[l]); umx_conv_free(u->enc2[l]); umx_conv_free(u->down[l]); umx_conv_free(u->up[l]); umx_conv_free(u->dec1[l]); umx_conv_free(u->dec2[l]);
+        nn_free(u->act[l]); nn_free(u->cat[l]); nn_free(u->s2d[l]); nn_free(u->dn[l]); nn_free(u->dec[l]);
+    }
+    umx_conv_free(u->head);
+    nn_free(u->x_mx); nn_free(u->ybuf); nn_free(u->part); nn_free(u->coef); nn_free(u->x16); nn_free(u->xu8); nn_free(u->logits16);
+    free(u);
+}
+umx_unet *umx_unet_create(const umx_unet_cfg *cfg, const float *weights, int max_batch) {
+    if (cfg->L < 2 || cfg->L > MAXL || max_batch < 1 || (cfg->P >> (cfg->L - 1)) < 1 || (cfg->P & ((1 << (cfg->L - 1)) - 1))) { fprintf(stderr, "umx_unet_create: bad configuration\n"); abort(); }
+    for (int l = 0; l < cfg->L; l++) if (cfg->cw[l] % 32) { fprintf(stderr, "umx_unet_create: widths must be multiples of 32\n"); abort(); }
+    umx_unet *u = calloc(1, sizeof *u);
+    u->cfg = *cfg; u->maxN = max_batch;
+    const int L = cfg->L, N = max_batch, bf = cfg->bits_first, bm = cfg->bits_mid, bl = cfg->bits_last;
+    for (int l = 0, D = cfg->P; l < L; l++, D /= 2) u->Dl[l] = D;
+    const float *wp = weights;
+    for (int l = 0; l < L; l++) {
+        u->enc1[l] = mk(UMX_CONV3, &wp, cfg->cw[l], l ? cfg->cw[l] : 1, 27, l ? bm : bf);
+        u->enc2[l] = mk(UMX_CONV3, &wp, cfg->cw[l], cfg->cw[l], 27, bm);
+        if (l < L - 1) u->down[l] = mk(UMX_DOWN2, &wp, cfg->cw[l + 1], cfg->cw[l], 8, bm);
+    }
+    for (int l = L - 2; l >= 0; l--) {
+        u->up[l] = mk(UMX_TCONV2, &wp, cfg->cw[l], cfg->cw[l + 1], 8, bm);
+        u->dec1[l] = mk(UMX_CONV3, &wp, cfg->cw[l], 2 * cfg->cw[l], 27, bm);
+        u->dec2[l] = mk(UMX_CONV3, &wp, cfg->cw[l], cfg->cw[l], 27, l ? bm : bl);
+    }
+    u->head = mk(UMX_CONV1, &wp, cfg->nh, cfg->cw[0], 1, bl);
+    /* buffers; every MX tensor is sized for 8-bit rows so one plan serves both formats */
+    size_t ymax = 0, pmax = 0; int cmax = 0;
+    for (int l = 0; l < L; l++) {
+        const size_t S = cube(u->Dl[l]); const int C = cfg->cw[l];
+        if ((size_t)C * S > ymax) ymax = (size_t)C * S;
+        const size_t pd = umx_stats_doubles(N, C, u->Dl[l], u->Dl[l], u->Dl[l]); if (pd > pmax) pmax = pd;
+        if (C > cmax) cmax = C;
+        u->act[l] = nn_malloc(umx_mx_bytes32(8, N, C, S));
+        u->cat[l] = nn_malloc(umx_mx_bytes32(8, N, l < L - 1 ? 2 * C : C, S));
+        if (l < L - 1) { u->s2d[l] = nn_malloc(umx_mx_bytes32(8, N, 8 * C, S / 8)); u->dec[l] = nn_malloc(umx_mx_bytes32(8, N, C, S)); }
+        if (l) u->dn[l] = nn_malloc(umx_mx_bytes32(8, N, C, S));
+    }
+    const size_t S0 = cube(cfg->P);
+    u->x_mx = nn_malloc(umx_mx_bytes32(8, N, 1, S0));
+    u->ybuf = nn_malloc((size_t)N * ymax * 2);
+    u->part = nn_malloc(pmax * sizeof(double));
+    u->coef = nn_malloc((size_t)N * cmax * 2 * sizeof(float));
+    u->x16 = nn_malloc((size_t)N * S0 * 2); u->xu8 = nn_malloc((size_t)N * S0);
+    u->logits16 = nn_malloc((size_t)N * cfg->nh * S0 * 2);
+    nn_sync();
+    const char *e = nn_check();
+    if (e) { fprintf(stderr, "umx_unet_create: %s\n", e); umx_unet_free(u); return nullptr; }
+    u->launches0 = umx_launch_count();
+    return u;
+}
+long umx_unet_launches(const umx_unet *u) { return umx_launch_count() - u->launches0; }
+
+/* conv -> blocked fp16 + partial sums -> coefficients -> apply into q (and q_s2d) */
+static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int N, int C, int D, void *q, int bits, int nb_dst, int b0, void *q_s2d) {
+    umx_conv_fwd(c, x, N, D, D, D, u->ybuf, UMX_OUT_H16B, 0, 0, 0, u->part);
+    umx_in_coef(u->part, N, C, D, D, D, nullptr, nullptr, 1e-5f, u->coef);
+    umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr);
+}
+static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) {
+    const umx_unet_cfg *c = &u->cfg; const int L = c->L, bm = c->bits_mid, bl = c->bits_last;
+    if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_forward: batch %d outside 1..%d\n", N, u->maxN); abort(); }
+    umx_pm_to_mx32(x_dev, UMX_F16, N, 1, cube(c->P), u->x_mx, c->bits_first);
+    for (int l = 0; l < L; l++) {
+        const int D = u->Dl[l], C = c->cw[l], nb = C / 32;
+        conv_norm(u, u->enc1[l], l ? u->dn[l] : u->x_mx, N, C, D, u->act[l], bm, 0, 0, nullptr);
+        if (l < L - 1) {
+            conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 2 * nb, nb, u->s2d[l]);
+            umx_conv_fwd(u->down[l], u->s2d[l], N, D / 2, D / 2, D / 2, u->dn[l + 1], UMX_OUT_MX, bm, 0, 0, nullptr);
+        } else conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 0, 0, nullptr);
+    }
+    const void *cur = u->cat[L - 1];
+    for (int l = L - 2; l >= 0; l--) {
+        const int D = u->Dl[l], C = c->cw[l], nb = C / 32, Dc = u->Dl[l + 1];
+        umx_conv_fwd(u->up[l], cur, N, Dc, Dc, Dc, u->cat[l], UMX_OUT_MX, bm, 2 * nb, 0, nullptr);
+        conv_norm(u, u->dec1[l], u->cat[l], N, C, D, u->act[l], l ? bm : bl, 0, 0, nullptr);
+        conv_norm(u, u->dec2[l], u->act[l], N, C, D, u->dec[l], l ? bm : bl, 0, 0, nullptr);
+        cur = u->dec[l];
+    }
+    umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : UMX_OUT_PM32, 0, 0, 0, nullptr);
+    return 0;
+}
+int umx_unet_forward(umx_unet *u, const void *x_dev, int N, float *logits_dev) { return forward(u, x_dev, N, logits_dev, UMX_F32); }
+int umx_unet_forward_h16(umx_unet *u, const void *x_dev, int N, void *logits_dev) { return forward(u, x_dev, N, logits_dev, UMX_F16); }
+/* uint8 CT patches on the host -> fp16 logits on the host: copy in, convert, forward, copy out */
+int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) {
+    const size_t S = cube(u->cfg.P);
+    nn_h2d(u->xu8, ct_host, (size_t)N * S);
+    umx_u8_to_h16(u->xu8, (size_t)N * S, u->x16);
+    forward(u, u->x16, N, u->logits16, UMX_F16);
+    nn_d2h(logits16_host, u->logits16, (size_t)N * u->cfg.nh * S * 2);
+    return nn_check() ? -1 : 0;
+}
+
+/* ---------------- sliding window ---------------- */
+umx_window umx_window_make(int V, int P, int overlap) {
+    umx_window w = {V, P, overlap, 1, 1};
+    const int stride = P - overlap;
+    w.nper = V <= P ? 1 : (V - P + stride - 1) / stride + 1;
+    w.npatch = w.nper * w.nper * w.nper;
+    return w;
+}
+/* patch idx in (z, y, x) order; the last patch of an axis is pulled back so it ends at the volume's edge */
+void umx_window_origin(const umx_window *w, int idx, int *z0, int *y0, int *x0) {
+    const int stride = w->P - w->overlap, n = w->nper;
+    const int iz = idx / (n * n), iy = (idx / n) % n, ix = idx % n;
+    const int lim = w->V > w->P ? w->V - w->P : 0;
+    *z0 = iz * stride < lim ? iz * stride : lim; *y0 = iy * stride < lim ? iy * stride : lim; *x0 = ix * stride < lim ? ix * stride : lim;
+}
+/* contiguous shares of the (z, y) patch rows: ranks get whole rows of nper patches, z-slab first (src/predict.c:2696-2717) */
+void umx_window_share(const umx_window *w, int rank, int world, int *first, int *count) {
+    const int rows = w->nper * w->nper, base = rows / world, extra = rows % world;
+    const int r0 = rank * base + (rank < extra ? rank : extra), nr = base + (rank < extra ? 1 : 0);
+    *first = r0 * w->nper; *count = nr * w->nper;
+}
+void umx_window_extent(const umx_window *w, int first, int count, int *zlo, int *zhi) {
+    int z0, y0, x0, z1;
+    if (count <= 0) { *zlo = 0; *zhi = 0; return; }
+    umx_window_origin(w, first, &z0, &y0, &x0); umx_window_origin(w, first + count - 1, &z1, &y0, &x0);
+    *zlo = z0; *zhi = (z1 + w->P < w->V ? z1 + w->P : w->V);
+}
+/* Runs patches [first, first + count): gathers each batch of uint8 patches from the host volume into pinned staging, uploads,
+   forwards, blends on the device into accumulators covering z planes [zlo, zhi) of the volume, and finally copies the
+   accumulators to acc [nh][zhi - zlo][V][V] and wsum [zhi - zlo][V][V] on the host. */
+int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int first, int count, int batch, float *acc, float *wsum) {
+    const int P = w->P, V = w->V, nh = u->cfg.nh;
+    if (P != u->cfg.P) { fprintf(stderr, "umx_window_run: patch size %d does not match the network's %d\n", P, u->cfg.P); abort(); }
+    if (batch < 1) batch = 1; if (batch > u->maxN) batch = u->maxN;
+    int zlo, zhi; umx_window_extent(w, first, count, &zlo, &zhi);
+    const int zext = zhi - zlo; if (zext <= 0) return 0;
+    const size_t PS = cube(P), plane = (size_t)V * V;
+    float w1d_h[1024]; if (P > 1024) abort();
+    { const double s = P / 8.0, c = (P - 1) / 2.0; for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
+    float *w1d = nn_malloc((size_t)P * 4), *dacc = nn_malloc((size_t)nh * zext * plane * 4), *dws = nn_malloc((size_t)zext * plane * 4);
+    float *logits = nn_malloc((size_t)batch * nh * PS * 4);
+    uint8_t *stage = nn_malloc_host((size_t)batch * PS);
+    if (!w1d || !dacc || !dws || !logits || !stage) { nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage); return -1; }
+    nn_h2d(w1d, w1d_h, (size_t)P * 4); nn_zero(dacc, (size_t)nh * zext * plane * 4); nn_zero(dws, (size_t)zext * plane * 4);
+    for (int p = first; p < first + count; p += batch) {
+        const int nb = p + batch <= first + count ? batch : first + count - p;
+        for (int i = 0; i < nb; i++) {
+            int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
+            uint8_t *dst = stage + (size_t)i * PS;
+            for (int z = 0; z < P; z++) for (int y = 0; y < P; y++) {
+                const int gz = z0 + z, gy = y0 + y;
+                uint8_t *row = dst + ((size_t)z * P + y) * P;
+                if (gz >= V || gy >= V) { memset(row, 0, (size_t)P); continue; }
+                const int nx = x0 + P <= V ? P : V - x0;
+                memcpy(row, vol + (size_t)gz * plane + (size_t)gy * V + x0, (size_t)nx);
+                if (nx < P) memset(row + nx, 0, (size_t)(P - nx));
+            }
+        }
+        nn_h2d(u->xu8, stage, (size_t)nb * PS);
+        umx_u8_to_h16(u->xu8, (size_t)nb * PS, u->x16);
+        forward(u, u->x16, nb, logits, UMX_F32);
+        for (int i = 0; i < nb; i++) {
+            int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
+            umx_blend_add(logits + (size_t)i * nh * PS, UMX_F32, nh, P, V, zlo, zext, z0, y0, x0, w1d, dacc, dws);
+        }
+    }
+    nn_d2h(acc, dacc, (size_t)nh * zext * plane * 4); nn_d2h(wsum, dws, (size_t)zext * plane * 4);
+    nn_sync();
+    nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage);
+    return nn_check() ? -1 : 0;
+}
