@@ -261,6 +261,10 @@ void orc_prep_w(const float *w, int Co, int Ci, int taps, int bits, int layout, 
 /* y[n][cob][vo][32] = bias + sum over taps and input channels of x (blocked, dequantised) times wdq ([taps][Cip][Cop]), fp32
    accumulation (the products of MX values are exact in fp32, so only the summation order is a choice: taps outer, channels inner).
    k in {1, 2, 3}, stride in {1, 2}, zero padding pad.  Index map as tests/test_mx4_wide.c:176-198. */
+static int g_order = 0;
+/* summation order of the taps: 0 ascending, 1 descending.  Both are "fp32 accumulation of the same dequantised operands"; running a
+   network both ways measures how far two correct implementations can drift apart through flipped roundings. */
+void orc_set_tap_order(int descending) { g_order = descending; }
 void orc_conv_blocked(const float *x, int N, int Ci, int D, int H, int W, const float *wdq, const float *bias, int Co,
                       int k, int stride, int pad, float *y) {
     const int Cip = (Ci + 31) / 32 * 32, Cop = (Co + 31) / 32 * 32, cbi = Cip / 32, cbo = Cop / 32;
@@ -271,7 +275,8 @@ void orc_conv_blocked(const float *x, int N, int Ci, int D, int H, int W, const 
         float *acc = (float *)malloc((size_t)Cop * sizeof(float));
         for (int ox = 0; ox < Wo; ox++) {
             for (int c = 0; c < Cop; c++) acc[c] = 0.f;
-            for (int kz = 0; kz < k; kz++) for (int ky = 0; ky < k; ky++) for (int kx = 0; kx < k; kx++) {
+            for (int tt = 0; tt < k * k * k; tt++) {
+                const int tq = g_order ? k * k * k - 1 - tt : tt, kz = tq / (k * k), ky = (tq / k) % k, kx = tq % k;
                 const int iz = oz * stride + kz - pad, iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
                 if (iz < 0 || iz >= D || iy < 0 || iy >= H || ix < 0 || ix >= W) continue;
                 const size_t iv = ((size_t)iz * H + iy) * W + ix;

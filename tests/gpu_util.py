@@ -1,0 +1,140 @@
+"""Helpers that run the library's entry points from numpy arrays and return numpy arrays (device memory through nn_malloc)."""
+import ctypes as C
+
+import numpy as np
+
+import orc
+import ufsm_b200
+from ufsm_b200 import DevBuf
+
+KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3}
+OUT_H16B, OUT_MX, OUT_PM32, OUT_PM16, OUT_MXRAW = 0, 1, 2, 3, 4
+
+
+def L():
+    return ufsm_b200.lib()
+
+
+def quantise_pm(x, dt, N, Cn, S, bits, wide32=False):
+    """plane-major fp32 (dt 0) / fp16 (dt 2) -> MX bytes via the reference-named entry points (or the 32-wide variant)."""
+    xd = DevBuf(data=x)
+    nbytes = L().umx_mx_bytes32(bits, N, Cn, S) if wide32 else (L().lp_mx8_bytes if bits == 8 else L().lp_mx4_bytes)(N, Cn, S)
+    yd = DevBuf(nbytes).fill(0xEE)
+    if wide32:
+        L().umx_pm_to_mx32(xd.ptr, dt, N, Cn, S, yd.ptr, bits)
+    elif dt == 0:
+        (L().lp_f32_to_mx8 if bits == 8 else L().lp_f32_to_mx4)(xd.ptr, N, Cn, S, yd.ptr)
+    else:
+        (L().lp_h16_to_mx8 if bits == 8 else L().lp_h16_to_mx4)(xd.ptr, dt, N, Cn, S, yd.ptr)
+    ufsm_b200.check()
+    return yd.download()
+
+
+def dequantise(mx, bits, N, Cn, S):
+    xd = DevBuf(data=mx)
+    yd = DevBuf(N * Cn * S * 4).fill(0xEE)
+    (L().lp_mx8_to_f32 if bits == 8 else L().lp_mx4_to_f32)(xd.ptr, N, Cn, S, yd.ptr)
+    ufsm_b200.check()
+    return yd.download(np.float32)
+
+
+class Conv:
+    def __init__(self, kind, w, b, co, ci, bits):
+        w = np.ascontiguousarray(w, np.float32)
+        bp = np.ascontiguousarray(b, np.float32) if b is not None else None
+        self.h = L().umx_conv_create(KIND[kind], w.ctypes.data, bp.ctypes.data if bp is not None else None, co, ci, bits)
+        ufsm_b200.check()
+        assert self.h
+        self.kind, self.co, self.ci, self.bits = kind, co, ci, bits
+
+    def fwd(self, x_mx, N, D, H, W, out_mode, out_bits=0, nb_dst=0, b0=0, want_part=False, dst=None):
+        """x_mx: numpy MX bytes (32-wide blocks).  Returns (output bytes as uint8 array, partial sums or None)."""
+        xd = DevBuf(data=x_mx)
+        f = 8 if self.kind == "tconv2" else 1
+        So = D * H * W * f
+        nbo = nb_dst if nb_dst else orc.nb32(self.co)
+        if out_mode == OUT_H16B:
+            nbytes = N * nbo * So * 64
+        elif out_mode in (OUT_MX, OUT_MXRAW):
+            nbytes = N * nbo * So * (32 * out_bits // 8 + 1)
+        elif out_mode == OUT_PM32:
+            nbytes = N * self.co * So * 4
+        else:
+            nbytes = N * self.co * So * 2
+        yd = dst if dst is not None else DevBuf(nbytes).fill(0xEE)
+        pd = None
+        if want_part:
+            pd = DevBuf(L().umx_stats_doubles(N, self.co, D, H, W) * 8).fill(0xEE)
+        rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, out_bits, nb_dst, b0, pd.ptr if pd else None)
+        ufsm_b200.check()
+        assert rc == 0
+        return yd.download(), (pd if want_part else None)
+
+    def free(self):
+        if self.h:
+            L().umx_conv_free(self.h)
+            self.h = None
+
+
+def h16b_to_blocked_f32(raw, n_elems=None):
+    return raw.view(np.float16).astype(np.float32)
+
+
+def in_coef(part, N, Cn, D, H, W, eps=1e-5):
+    cd = DevBuf(N * Cn * 8).fill(0xEE)
+    L().umx_in_coef(part.ptr, N, Cn, D, H, W, None, None, C.c_float(eps), cd.ptr)
+    ufsm_b200.check()
+    return cd.download(np.float32), cd
+
+
+def in_apply(y16_blocked, coef, N, Cn, D, H, W, act, bits, nb_dst=0, b0=0, want_s2d=False, want_h=False):
+    S = D * H * W
+    nb = orc.nb32(Cn)
+    xd = DevBuf(data=np.ascontiguousarray(y16_blocked, np.float16))
+    cd = DevBuf(data=np.ascontiguousarray(coef, np.float32)) if coef is not None else None
+    rb = 32 * bits // 8 + 1
+    qd = DevBuf(N * (nb_dst or nb) * S * rb).fill(0xEE)
+    sd = DevBuf(N * 8 * nb * (S // 8) * rb).fill(0xEE) if want_s2d else None
+    hd = DevBuf(N * nb * S * 64).fill(0xEE) if want_h else None
+    L().umx_in_apply(xd.ptr, cd.ptr if cd else None, N, Cn, D, H, W, act, qd.ptr, bits, nb_dst, b0, sd.ptr if sd else None, hd.ptr if hd else None)
+    ufsm_b200.check()
+    return qd.download(), (sd.download() if sd else None), (hd.download(np.float16) if hd else None)
+
+
+def make_cfg(P, cw, nh=7, bits=(8, 8, 8)):
+    c = ufsm_b200.UnetCfg()
+    c.L = len(cw)
+    for i, v in enumerate(cw):
+        c.cw[i] = v
+    c.nh, c.P = nh, P
+    c.bits_first, c.bits_mid, c.bits_last = bits
+    return c
+
+
+class Unet:
+    def __init__(self, cfg, weights, max_batch=1):
+        weights = np.ascontiguousarray(weights, np.float32)
+        assert weights.size == L().umx_unet_nweights(C.byref(cfg))
+        self.cfg = cfg
+        self.h = L().umx_unet_create(C.byref(cfg), weights.ctypes.data, max_batch)
+        assert self.h, (L().lp_check() or b"").decode()
+
+    def forward(self, x16, N):
+        xd = DevBuf(data=np.ascontiguousarray(x16, np.float16))
+        yd = DevBuf(N * self.cfg.nh * self.cfg.P ** 3 * 4).fill(0xEE)
+        rc = L().umx_unet_forward(self.h, xd.ptr, N, yd.ptr)
+        ufsm_b200.check()
+        assert rc == 0
+        return yd.download(np.float32)
+
+    def forward_host(self, ct_u8, N):
+        ct_u8 = np.ascontiguousarray(ct_u8, np.uint8)
+        out = np.empty(N * self.cfg.nh * self.cfg.P ** 3, np.float16)
+        rc = L().umx_unet_forward_host(self.h, ct_u8.ctypes.data, N, out.ctypes.data)
+        assert rc == 0, (L().lp_check() or b"").decode()
+        return out
+
+    def free(self):
+        if self.h:
+            L().umx_unet_free(self.h)
+            self.h = None

@@ -196,7 +196,16 @@ def unet_nweights(cfg):
     return o().orc_unet_nweights(C.byref(cfg))
 
 
-def unet_forward(cfg, weights, x16, N):
+def unet_forward(cfg, weights, x16, N, descending=False):
+    """descending: add the taps in the opposite order (another valid fp32 summation order of the same operands)."""
+    o().orc_set_tap_order(1 if descending else 0)
+    try:
+        return _unet_forward(cfg, weights, x16, N)
+    finally:
+        o().orc_set_tap_order(0)
+
+
+def _unet_forward(cfg, weights, x16, N):
     weights = f32(weights)
     x16 = np.ascontiguousarray(x16, dtype=np.float16)
     logits = np.zeros(N * cfg.nh * cfg.P ** 3, np.float32)

@@ -1,0 +1,62 @@
+"""GPU quantiser against the CPU oracle: codes and scale bytes bit-exact, through the reference-named entry points."""
+import numpy as np
+import pytest
+
+import gpu_util as G
+import orc
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def edge_values(n):
+    g = synth.rng(5)
+    v = g.standard_normal(n).astype(np.float32)
+    sp = np.array([0.0, -0.0, 448.0, -448.0, 464.0, 465.0, 6.0, 5.0, 7.0, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -10, 2.0 ** -126, 2.0 ** -140, 1e-30, 3e38, 0.25, 0.75,
+                   1.25, 1.75, 2.5, 3.5, 224.0, 224.5, 3.0, 12.0, 65504.0], np.float32)
+    idx = g.integers(0, n, 4 * sp.size)
+    v[idx] = np.tile(np.concatenate([sp, -sp]), 2)[: idx.size]
+    v[g.integers(0, n, n // 50)] *= np.float32(1e-4)      # blocks with tiny amax
+    v[g.integers(0, n, n // 50)] *= np.float32(1e3)
+    return v
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("N,Cn,S", [(1, 32, 4096), (2, 64, 1000), (1, 40, 777), (1, 4, 513), (3, 16, 300), (1, 1, 4096), (1, 320, 64)])
+def test_f32_to_mx(dev, bits, N, Cn, S):
+    x = edge_values(N * Cn * S)
+    got = G.quantise_pm(x, 0, N, Cn, S, bits)
+    want = orc.pm_to_mx(x, 0, N, Cn, S, bits)
+    assert got.size == want.size and np.array_equal(got, want), "%d bytes differ" % np.count_nonzero(got != want)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_h16_to_mx_and_back(dev, bits):
+    N, Cn, S = 1, 32, 32 ** 3
+    x = synth.act_h16(1, N * Cn * S)
+    got = G.quantise_pm(x, 2, N, Cn, S, bits)
+    assert np.array_equal(got, orc.pm_to_mx(x, 2, N, Cn, S, bits))
+    assert np.array_equal(G.dequantise(got, bits, N, Cn, S), orc.mx_to_pm(got, bits, N, Cn, S))
+    # the all-zero tensor: codes 0, scale byte 1 (exponent -126)
+    z = G.quantise_pm(np.zeros(N * Cn * 64, np.float16), 2, N, Cn, 64, bits)
+    assert np.all(z[: 64 * 32 * bits // 8] == 0) and np.all(z[64 * 32 * bits // 8:] == 1)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_nan_inf_blocks(dev, bits):
+    x = (0.5 * (np.arange(32 * 8) % 7)).astype(np.float32).reshape(32, 8)
+    x[5, 0], x[6, 1], x[7, 2] = np.nan, np.inf, -np.inf
+    got = G.quantise_pm(x, 0, 1, 32, 8, bits)
+    want = orc.pm_to_mx(x, 0, 1, 32, 8, bits)
+    assert np.array_equal(got, want)
+    d = G.dequantise(got, bits, 1, 32, 8).reshape(32, 8)
+    assert not np.isfinite(d[:, :3]).any() and np.isfinite(d[:, 3:]).all()
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_wide32_one_channel(dev, bits):
+    # the network input: one channel kept in a 32-wide block
+    S = 4096
+    x = (synth.ct_u8(9, S).astype(np.float32) / np.float32(255)).astype(np.float16)
+    got = G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True)
+    assert np.array_equal(got, orc.pm_to_mx(x, 2, 1, 1, S, bits, 32))

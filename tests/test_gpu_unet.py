@@ -1,0 +1,66 @@
+"""The U-Net forward on the GPU against the CPU oracle's forward, and size-independent properties at the benchmark's full size."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import gpu_util as G
+import orc
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def ct_patch(seed, n):
+    return (synth.ct_u8(seed, n).astype(np.float32) / np.float32(255)).astype(np.float16)
+
+
+@pytest.mark.parametrize("bits", [(8, 8, 8), (8, 4, 8)])
+@pytest.mark.parametrize("P,cw", [(16, [32, 64]), (32, [32, 64, 128])])
+def test_unet_small_against_oracle(dev, P, cw, bits):
+    """End-to-end logits against the oracle's forward.  Across layers the fp32 summation order flips a few MX codes (a 6 % step in
+    fp8) and a random-weight network amplifies them: the oracle run with its taps added in the opposite order, which is just as
+    correct, differs from itself by several per cent at these sizes.  The 1e-3 tolerance is therefore asserted per layer on
+    identical inputs (test_gpu_conv.py, test_unet_layers_teacher_forced); here the GPU must be as close to the oracle as the
+    oracle is to itself (twice its self-distance plus 1e-3)."""
+    w = synth.unet_weights(3, cw)
+    x = ct_patch(4, P ** 3)
+    ocfg = orc.unet_cfg(P, cw, 7, bits)
+    want = orc.unet_forward(ocfg, w, x, 1)
+    drift = orc.rel_l2(orc.unet_forward(ocfg, w, x, 1, descending=True), want)
+    u = G.Unet(G.make_cfg(P, cw, 7, bits), w, 1)
+    got = u.forward(x, 1)
+    u.free()
+    assert np.isfinite(got).all()
+    e = orc.rel_l2(got, want)
+    print("unet P=%d widths=%s bits=%s rel-L2 %.3g (oracle against itself with the other tap order: %.3g)" % (P, cw, bits, e, drift))
+    assert e < 2 * drift + 1e-3
+
+
+def test_unet_batch_and_determinism(dev):
+    P, cw = 16, [32, 64]
+    w = synth.unet_weights(5, cw)
+    x = np.concatenate([ct_patch(6, P ** 3), ct_patch(7, P ** 3)])
+    u = G.Unet(G.make_cfg(P, cw), w, 2)
+    both = u.forward(x, 2).reshape(2, -1)
+    a = u.forward(x[: P ** 3], 1)
+    b = u.forward(x[P ** 3:], 1)
+    assert np.array_equal(both[0], a) and np.array_equal(both[1], b)          # per-sample statistics: a batch is independent patches
+    assert np.array_equal(u.forward(x, 2).reshape(2, -1), both)               # run-to-run identical bytes
+    # the host entry: uint8 in, fp16 out
+    ct = np.concatenate([synth.ct_u8(6, P ** 3), synth.ct_u8(7, P ** 3)])
+    h = u.forward_host(ct, 2).reshape(2, -1)
+    assert np.array_equal(h, both.astype(np.float16))
+    u.free()
+
+
+def test_unet_full_size_properties(dev):
+    """Configuration 3 (128^3 patch, widths 32/64/128/256/320): finite, deterministic, and translation-consistent in the batch."""
+    P, cw = 128, [32, 64, 128, 256, 320]
+    w = synth.unet_weights(8, cw)
+    x = ct_patch(9, P ** 3)
+    u = G.Unet(G.make_cfg(P, cw), w, 1)
+    a = u.forward(x, 1)
+    assert np.isfinite(a).all() and a.std() > 0
+    assert np.array_equal(a, u.forward(x, 1))
+    u.free()
