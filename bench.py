@@ -1,0 +1,210 @@
+"""Benchmark of the MX block-scaled 3-D U-Net inference path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library on N B200s (N > 1: launched by torch.distributed.run)
+    python bench.py --impl reference --steps K --warmup W    # the CPU restatement of the reference's arithmetic on the host cores
+
+A step is one forward of the benchmark's configuration 3 (a 1 x 1 x 128^3 fp16 patch through the five-level U-Net, widths
+32/64/128/256/320, every conv MX-fp8 with E8M0 scales per 32 channels) on a batch of `--batch` independent patches per GPU, with
+seeded synthetic CT intensities and Kaiming-normal weights.  Patches are independent, so N GPUs run N times the patches (weak
+scaling) with no data-path collective; the only cross-rank traffic is the barrier and the max of the timings.  One JSON line is
+printed by rank 0."""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+CW = [32, 64, 128, 256, 320]
+P = 128
+NH = 7
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"], "which": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "which": "fallback"}
+
+
+class Clocks(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    def __init__(self, gpu):
+        super().__init__(daemon=True)
+        self.gpu, self.rows, self.stop = gpu, [], False
+        self.q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def run(self):
+        while not self.stop:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.q, "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [t.strip() for t in out.strip().split(",")]
+                if len(f) >= 6:
+                    self.rows.append(f)
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None, "reasons": reasons, "samples": len(self.rows)}
+
+
+def cpu_sample(steps, warmup):
+    """The oracle's forward of the same network on one full 128^3 patch, all host threads."""
+    import orc
+    import synth
+    Ps = P
+    cfg = orc.unet_cfg(Ps, CW, NH, (8, 8, 8))
+    w = synth.unet_weights(1, CW)
+    x = (synth.ct_u8(2, Ps ** 3).astype(np.float32) / np.float32(255)).astype(np.float16)
+    for _ in range(warmup):
+        orc.unet_forward(cfg, w, x, 1)
+    t0 = time.time()
+    for _ in range(steps):
+        orc.unet_forward(cfg, w, x, 1)
+    dt = (time.time() - t0) / steps
+    return Ps ** 3 / dt, dt, orc.o().orc_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    v, dt, cores = cpu_sample(steps, warmup)
+    line = {"impl": "reference", "metric": "unet_inference_voxels_per_s", "value": v, "unit": "voxels/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
+            "config": {"workload": "config 3: U-Net 32/64/128/256/320 forward, MX-fp8 E4M3 + E8M0/32, CPU restatement of the reference's emulated-MX arithmetic"},
+            "cpu_baseline": {"value": v, "unit": "voxels/s", "cores": cores, "kind": "port", "sample": "one full 128^3 patch per step; OpenMP"},
+            "e2e": {"value": v, "unit": "voxels/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_gpu(args):
+    import gpu_util as G
+    import synth
+    import ufsm_b200
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo", init_method="env://")
+    L = ufsm_b200.lib()
+    assert L.nn_init(local) == 0, (L.lp_check() or b"").decode()
+    B, S = args.batch, P ** 3
+    cfg = G.make_cfg(P, CW, NH, (8, 8, 8))
+    u = G.Unet(cfg, synth.unet_weights(1, CW), B)
+    ct = synth.ct_u8(100 + rank, B * S)
+    x16 = (ct.astype(np.float32) / np.float32(255)).astype(np.float16)
+    xd = ufsm_b200.DevBuf(data=x16)
+    yd = ufsm_b200.DevBuf(B * NH * S * 4)
+    hin, hout = L.nn_malloc_host(B * S), L.nn_malloc_host(B * NH * S * 2)
+    C.memmove(hin, ct.ctypes.data, B * S)
+    timer = L.umx_timer_new()
+
+    def barrier():
+        L.nn_sync()
+        if dist is not None:
+            dist.barrier()
+
+    def tmax(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    for _ in range(args.warmup):
+        L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
+    ufsm_b200.check()
+    clk = Clocks(local)
+    clk.start()
+    # ---- device-resident: K steps, events on the launching stream, barrier + synchronise on both sides, max over ranks
+    barrier()
+    n0 = L.umx_launch_count()
+    L.umx_timer_start(timer)
+    for _ in range(args.steps):
+        L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
+    ms = L.umx_timer_stop_ms(timer)
+    launches = L.umx_launch_count() - n0
+    barrier()
+    ms = tmax(ms)
+    # ---- end to end through the host entry: uint8 patches in pinned memory -> fp16 logits in pinned memory, every step
+    for _ in range(min(args.warmup, 2)):
+        L.umx_unet_forward_host(u.h, hin, B, hout)
+    barrier()
+    L.umx_timer_start(timer)
+    for _ in range(args.steps):
+        L.umx_unet_forward_host(u.h, hin, B, hout)
+    ms_e2e = tmax(L.umx_timer_stop_ms(timer))
+    barrier()
+    clk.stop = True
+    clk.join(2)
+    # ---- per-launch time of the dominant kernel (the tcgen05 conv), measured live with events around every conv launch
+    ms_conv, fl_conv = C.c_double(0), C.c_double(0)
+    L.umx_prof_begin()
+    for _ in range(args.steps):
+        L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
+    n_conv = L.umx_prof_end(C.byref(ms_conv), C.byref(fl_conv))
+    ufsm_b200.check()
+    if rank != 0:
+        return
+    pk = peaks()
+    vox = world * B * S * args.steps
+    flops_patch = L.umx_unet_flops(C.byref(cfg))
+    achieved = fl_conv.value / (ms_conv.value * 1e-3) / 1e12 if ms_conv.value > 0 else None
+    peak = 2.0 * pk["bf16_sustained"]
+    line = {
+        "metric": "unet_inference_voxels_per_s", "value": vox / (ms * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
+        "config": {"workload": "config 3: U-Net 32/64/128/256/320 forward on 1x1x128^3 fp16 patches, all convs MX-fp8 E4M3 + E8M0/32, fp32 accumulate", "patches_per_gpu_per_step": B,
+                   "l2": "per-step working set (69 MB per level-0 tensor, > 1 GB touched) exceeds the 126 MB L2", "conv_tflops_whole_step": world * B * flops_patch * args.steps / (ms * 1e-3) / 1e12},
+        "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "h2d_bytes_per_step": B * S, "d2h_bytes_per_step": B * NH * S * 2, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches), "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None, "traffic": None,
+                     "kernel": "conv_mx_k (all %d conv launches of a step: algorithmic 2*V*Cin*Cout*taps FLOPs / summed event time)" % (n_conv // max(args.steps, 1)),
+                     "peak_note": "2 x the %s bf16 sustained cuBLAS rate (fp8 runs at twice bf16); nominal dense fp8 4500" % pk["which"], "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
+                     "conv_share_of_step": ms_conv.value / max(args.steps, 1) / (ms / args.steps)},
+    }
+    if world == 1 and not args.no_cpu:
+        v, dt, cores = cpu_sample(1, 0)
+        line["cpu_baseline"] = {"value": v, "unit": "voxels/s", "cores": cores, "kind": "port", "sample": "one full 128^3 patch, %.1f s" % dt}
+    print(json.dumps(line), flush=True)
+    u.free()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="ufsm_b200")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -38,6 +38,16 @@ const char *lp_check(void);              /* src/nn_lp.h:172 */
 void *nn_malloc_host(size_t bytes);      /* pinned host memory (cudaHostAlloc) for the window scheduler's staging buffers */
 void nn_free_host(void *p);
 
+/* timing with CUDA events on the stream the library launches on (the legacy default stream) */
+void *umx_timer_new(void);
+void umx_timer_start(void *t);           /* synchronises, then records the start event */
+float umx_timer_stop_ms(void *t);        /* records the stop event, waits for it, returns the elapsed milliseconds */
+void umx_timer_free(void *t);
+/* between umx_prof_begin and umx_prof_end every conv kernel launch is bracketed by events: umx_prof_end returns the number of conv
+   launches, their summed device time (ms) and their summed algorithmic FLOPs (2 x output voxels x C_in x C_out x taps) */
+void umx_prof_begin(void);
+int umx_prof_end(double *ms, double *flops);
+
 /* ---- MX storage and the quantiser (src/nn_lp.h:110-118, 126; kernels src/lp_mx_cvt.cu:9-19, 59-79, 429-447) ---- */
 size_t lp_mx8_bytes(int N, int C, size_t S);
 size_t lp_mx4_bytes(int N, int C, size_t S);

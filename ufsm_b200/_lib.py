@@ -44,6 +44,12 @@ _SIG = {
     "lp_check": (C.c_char_p, []),
     "nn_malloc_host": (C.c_void_p, [C.c_size_t]),
     "nn_free_host": (None, [C.c_void_p]),
+    "umx_timer_new": (C.c_void_p, []),
+    "umx_timer_start": (None, [C.c_void_p]),
+    "umx_timer_stop_ms": (C.c_float, [C.c_void_p]),
+    "umx_timer_free": (None, [C.c_void_p]),
+    "umx_prof_begin": (None, []),
+    "umx_prof_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "lp_mx8_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_size_t]),
     "lp_mx4_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_size_t]),
     "lp_f32_to_mx8": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),

@@ -511,7 +511,11 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
         smem_set[dev] = 227 * 1024;
     }
     const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n);
+    /* algorithmic work: 2 x output voxels x real input channels x real output channels x taps (no credit for padding) */
+    const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * (c->taps == 27 ? 27.0 : 1.0);
+    const int pid = umx_prof_open(flops);
     conv_mx_k<<<grid, kThreads, smem>>>(m0, m1, a);
+    umx_prof_close(pid);
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");
     return 0;

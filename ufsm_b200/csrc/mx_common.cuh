@@ -15,6 +15,8 @@ void *umx_ws(int slot, size_t bytes);   /* per-device scratch that only grows (t
 int *umx_errflag(void);                 /* device int the kernels report bounded-wait failures into */
 int umx_errflag_read(void);             /* synchronises, reads and clears it */
 extern long g_umx_launches;
+int umx_prof_open(double flops);   /* conv launch timing (runtime.cu): returns a slot or -1 when profiling is off */
+void umx_prof_close(int id);
 
 /* ---- MX arithmetic ---- */
 /* exponent e of the block scale 2^e = exponent of amax / qmax rounded up, clamped to [-126, 126]; NaN / inf amax -> 128 (scale

@@ -99,3 +99,40 @@ int umx_errflag_read(void) {
     }
     return h[0];
 }
+
+/* ---- timing on the launching (legacy default) stream ---- */
+struct umx_timer { cudaEvent_t a, b; };
+extern "C" void *umx_timer_new(void) {
+    umx_timer *t = (umx_timer *)calloc(1, sizeof *t);
+    if (cudaEventCreate(&t->a) != cudaSuccess || cudaEventCreate(&t->b) != cudaSuccess) { umx_latch_msg("umx_timer_new: cudaEventCreate failed"); free(t); return nullptr; }
+    return t;
+}
+extern "C" void umx_timer_start(void *tv) { umx_timer *t = (umx_timer *)tv; cudaDeviceSynchronize(); cudaEventRecord(t->a, 0); }
+extern "C" float umx_timer_stop_ms(void *tv) {
+    umx_timer *t = (umx_timer *)tv; float ms = 0.f;
+    cudaEventRecord(t->b, 0);
+    cudaError_t e = cudaEventSynchronize(t->b);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, t->a, t->b);
+    if (e != cudaSuccess) { umx_latch("umx_timer_stop_ms", e); return -1.f; }
+    return ms;
+}
+extern "C" void umx_timer_free(void *tv) { umx_timer *t = (umx_timer *)tv; if (!t) return; cudaEventDestroy(t->a); cudaEventDestroy(t->b); free(t); }
+
+/* per-launch timing of the conv kernel: between umx_prof_begin and umx_prof_end every conv launch is bracketed by two events */
+enum { PROF_MAX = 8192 };
+static cudaEvent_t g_pev[2 * PROF_MAX];
+static double g_pflops[PROF_MAX];
+static int g_pn = 0, g_pon = 0, g_pmade = 0;
+extern "C" void umx_prof_begin(void) {
+    if (!g_pmade) { for (int i = 0; i < 2 * PROF_MAX; i++) cudaEventCreate(&g_pev[i]); g_pmade = 1; }
+    g_pn = 0; g_pon = 1;
+}
+int umx_prof_open(double flops) { if (!g_pon || g_pn >= PROF_MAX) return -1; g_pflops[g_pn] = flops; cudaEventRecord(g_pev[2 * g_pn], 0); return g_pn; }
+void umx_prof_close(int id) { if (id < 0) return; cudaEventRecord(g_pev[2 * id + 1], 0); g_pn = id + 1; }
+/* returns the number of conv launches seen; ms: their summed device time, flops: their summed algorithmic FLOPs */
+extern "C" int umx_prof_end(double *ms, double *flops) {
+    g_pon = 0; *ms = 0; *flops = 0;
+    cudaDeviceSynchronize();
+    for (int i = 0; i < g_pn; i++) { float t = 0.f; if (cudaEventElapsedTime(&t, g_pev[2 * i], g_pev[2 * i + 1]) == cudaSuccess) *ms += t; *flops += g_pflops[i]; }
+    return g_pn;
+}
