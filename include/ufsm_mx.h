@@ -97,6 +97,14 @@ size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part 
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */
 void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
+/* No counterpart in the reference.  The same coefficients as umx_in_coef, computed from the stored blocked-fp16 tensor y itself
+   (device, [n][blk][voxel][32] halfs) by a call that allocates nothing: for callers that must not touch the CUDA allocator (all memory
+   already handed to their own pool, allocation forbidden after start-up, or a loop where cudaMalloc's device-wide synchronisation is
+   not acceptable).  The partial sums live in a 4 MiB array built into the library's device image (one per GPU, held until exit), so
+   N x 64 x roundup32(C) x 2 doubles must fit in 524288 (N = 1: C <= 4096; N = 8: C <= 512); larger sizes return -1 with a message in
+   lp_check().  The first call on a device looks the array's address up (make it before any stream capture).  All calls on a device
+   share the array; calls that overlap on the GPU race, so issue them in order.  Returns 0 on success. */
+int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
 /* y = fp16(act(x a + b)) requantised to MX (k_inq, src/nn_xnet.cu:1577-1620): x blocked fp16 [n][C][S]; act 2 = LeakyReLU 0.01,
    0 none; q: MX destination (bits) with nb_dst blocks, first block b0; q_s2d: optional second copy in 2x2x2 space-to-depth order
    (an MX tensor of 8 C channels on the half grid, the input of UMX_DOWN2) or NULL; h: optional blocked fp16 copy or NULL.
