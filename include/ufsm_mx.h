@@ -24,6 +24,12 @@ typedef struct { const float *gamma, *beta, *mean, *rstd; int G; int zs, zo, ns,
 typedef struct { const void *x2; int c_split; void *y2; int o_split; int accum; gnp_t gp2; int16_t up, yD; unsigned sr; unsigned wkey;
                  int zlo, zhi; int stored_stats; unsigned osr; int16_t zi0, Di, o_pad, zw0, zw1, yzo; } split_t;   /* src/nn_lp.h:32 */
 enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16B = 18 };
+/* MX-fp8 code layouts.  REF: the reference's rows, [n][blk][voxel][32 B].  SPLIT: the same bytes as two 16-byte-wide planes per block,
+   [n][blk][half][voxel][16 B]; a halo row of ten voxels is then 160 contiguous bytes, which is what makes the TMA staging of the conv
+   efficient.  The graph keeps its fp8 tensors SPLIT; MX-fp4 rows are 16 bytes already, so both names mean the reference layout there.
+   The scale plane follows the codes unchanged in either layout. */
+enum { UMX_LAYOUT_REF = 0, UMX_LAYOUT_SPLIT = 1 };
+enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2 };   /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
 
 /* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
 int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
@@ -47,6 +53,7 @@ void umx_timer_free(void *t);
    launches, their summed device time (ms) and their summed algorithmic FLOPs (2 x output voxels x C_in x C_out x taps) */
 void umx_prof_begin(void);
 int umx_prof_end(double *ms, double *flops);
+int umx_prof_get(int i, double *ms, double *flops);   /* the i-th conv launch of the last profiled span; -1 past the end */
 
 /* ---- MX storage and the quantiser (src/nn_lp.h:110-118, 126; kernels src/lp_mx_cvt.cu:9-19, 59-79, 429-447) ---- */
 size_t lp_mx8_bytes(int N, int C, size_t S);
@@ -59,8 +66,9 @@ void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y);
 void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y);
 /* the same quantiser with 32-wide blocks whatever C (padding channels zero): the form the graph below keeps its tensors in */
 size_t umx_mx_bytes32(int bits, int N, int C, size_t S);
-void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits);   /* dt 0 fp32 / 2 fp16 plane-major */
-void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y);         /* -> plane-major fp32 */
+void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout);   /* dt 0 fp32 / 2 fp16 plane-major */
+void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y, int layout);         /* -> plane-major fp32 */
+void umx_mx_relayout(const void *src, int bits, int N, int C, size_t S, void *dst, int to_layout);   /* 32-wide MX tensor between the two layouts */
 void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);                   /* blocked fp16 -> plane-major fp32 */
 
 /* ---- 3x3x3 stride-1 pad-1 conv forward, the reference's entry points (src/nn_lp.h:53-54; src/lp_f8fwd.cu:26-52,
@@ -91,8 +99,9 @@ void umx_conv_free(umx_conv *c);
 /* x: MX tensor (32-wide blocks) of c->ci channels (UMX_DOWN2: the space-to-depth copy, 8 * ci channels at half resolution) on an
    N x D x H x W grid.  y per out_mode; nb_dst / b0: block count of the destination tensor and first block written (0, 0: the
    conv's own co).  part: optional device doubles for InstanceNorm partial sums (umx_stats_doubles), only with UMX_OUT_H16B.
-   UMX_TCONV2 writes the 2D x 2H x 2W grid.  Returns 0, or -1 after latching an error. */
-int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part);
+   UMX_TCONV2 writes the 2D x 2H x 2W grid.  flags: UMX_X_SPLIT / UMX_Y_SPLIT (an fp8 input in the reference layout is re-laid into
+   scratch first).  Returns 0, or -1 after latching an error. */
+int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags);
 size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */
@@ -108,8 +117,8 @@ int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const f
 /* y = fp16(act(x a + b)) requantised to MX (k_inq, src/nn_xnet.cu:1577-1620): x blocked fp16 [n][C][S]; act 2 = LeakyReLU 0.01,
    0 none; q: MX destination (bits) with nb_dst blocks, first block b0; q_s2d: optional second copy in 2x2x2 space-to-depth order
    (an MX tensor of 8 C channels on the half grid, the input of UMX_DOWN2) or NULL; h: optional blocked fp16 copy or NULL.
-   coef NULL: identity (a = 1, b = 0). */
-void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h);
+   coef NULL: identity (a = 1, b = 0).  layout: UMX_LAYOUT_REF / UMX_LAYOUT_SPLIT of q and q_s2d. */
+void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout);
 
 /* ---- the BASELINE U-Net (five levels 32/64/128/256/320, two 3^3 convs + InstanceNorm + LeakyReLU 0.01 a level, 2^3 stride-2
    down convs, ConvTranspose k2 s2 up, concat (up | skip), 1^3 head) and the sliding-window scheduler ---- */

@@ -15,13 +15,30 @@ def L():
     return ufsm_b200.lib()
 
 
-def quantise_pm(x, dt, N, Cn, S, bits, wide32=False):
+def to_split(mx, N, Cn, S, bits):
+    """MX bytes (32-wide blocks) from the reference layout to the split layout (fp8 only; fp4 rows are 16 bytes already)."""
+    if bits != 8:
+        return mx
+    rows = N * orc.nb32(Cn) * S
+    codes = mx[: rows * 32].reshape(N * orc.nb32(Cn), S, 2, 16).transpose(0, 2, 1, 3)
+    return np.concatenate([np.ascontiguousarray(codes).ravel(), mx[rows * 32:]])
+
+
+def from_split(mx, N, Cn, S, bits):
+    if bits != 8:
+        return mx
+    rows = N * orc.nb32(Cn) * S
+    codes = mx[: rows * 32].reshape(N * orc.nb32(Cn), 2, S, 16).transpose(0, 2, 1, 3)
+    return np.concatenate([np.ascontiguousarray(codes).ravel(), mx[rows * 32:]])
+
+
+def quantise_pm(x, dt, N, Cn, S, bits, wide32=False, layout=0):
     """plane-major fp32 (dt 0) / fp16 (dt 2) -> MX bytes via the reference-named entry points (or the 32-wide variant)."""
     xd = DevBuf(data=x)
     nbytes = L().umx_mx_bytes32(bits, N, Cn, S) if wide32 else (L().lp_mx8_bytes if bits == 8 else L().lp_mx4_bytes)(N, Cn, S)
     yd = DevBuf(nbytes).fill(0xEE)
     if wide32:
-        L().umx_pm_to_mx32(xd.ptr, dt, N, Cn, S, yd.ptr, bits)
+        L().umx_pm_to_mx32(xd.ptr, dt, N, Cn, S, yd.ptr, bits, layout)
     elif dt == 0:
         (L().lp_f32_to_mx8 if bits == 8 else L().lp_f32_to_mx4)(xd.ptr, N, Cn, S, yd.ptr)
     else:
@@ -47,9 +64,13 @@ class Conv:
         assert self.h
         self.kind, self.co, self.ci, self.bits = kind, co, ci, bits
 
-    def fwd(self, x_mx, N, D, H, W, out_mode, out_bits=0, nb_dst=0, b0=0, want_part=False, dst=None):
-        """x_mx: numpy MX bytes (32-wide blocks).  Returns (output bytes as uint8 array, partial sums or None)."""
-        xd = DevBuf(data=x_mx)
+    def fwd(self, x_mx, N, D, H, W, out_mode, out_bits=0, nb_dst=0, b0=0, want_part=False, dst=None, split=True):
+        """x_mx: numpy MX bytes (32-wide blocks, reference layout).  split: hand the conv fp8 tensors in the split layout (what the graph
+        does) and bring MX outputs back to the reference layout; otherwise the reference layout goes through the C ABI as it is.
+        Returns (output bytes as uint8 array, partial sums or None)."""
+        cin_t = (8 if self.kind == "down2" else 1) * orc.nb32(self.ci) * 32
+        xd = DevBuf(data=to_split(x_mx, N, cin_t, D * H * W, self.bits) if split else x_mx)
+        flags = 3 if split else 0
         f = 8 if self.kind == "tconv2" else 1
         So = D * H * W * f
         nbo = nb_dst if nb_dst else orc.nb32(self.co)
@@ -65,10 +86,13 @@ class Conv:
         pd = None
         if want_part:
             pd = DevBuf(L().umx_stats_doubles(N, self.co, D, H, W) * 8).fill(0xEE)
-        rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, out_bits, nb_dst, b0, pd.ptr if pd else None)
+        rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, out_bits, nb_dst, b0, pd.ptr if pd else None, flags)
         ufsm_b200.check()
         assert rc == 0
-        return yd.download(), (pd if want_part else None)
+        out = yd.download()
+        if split and out_mode in (OUT_MX, OUT_MXRAW):
+            out = from_split(out, N, nbo * 32, So, out_bits)
+        return out, (pd if want_part else None)
 
     def free(self):
         if self.h:
@@ -87,7 +111,7 @@ def in_coef(part, N, Cn, D, H, W, eps=1e-5):
     return cd.download(np.float32), cd
 
 
-def in_apply(y16_blocked, coef, N, Cn, D, H, W, act, bits, nb_dst=0, b0=0, want_s2d=False, want_h=False):
+def in_apply(y16_blocked, coef, N, Cn, D, H, W, act, bits, nb_dst=0, b0=0, want_s2d=False, want_h=False, split=True):
     S = D * H * W
     nb = orc.nb32(Cn)
     xd = DevBuf(data=np.ascontiguousarray(y16_blocked, np.float16))
@@ -96,9 +120,14 @@ def in_apply(y16_blocked, coef, N, Cn, D, H, W, act, bits, nb_dst=0, b0=0, want_
     qd = DevBuf(N * (nb_dst or nb) * S * rb).fill(0xEE)
     sd = DevBuf(N * 8 * nb * (S // 8) * rb).fill(0xEE) if want_s2d else None
     hd = DevBuf(N * nb * S * 64).fill(0xEE) if want_h else None
-    L().umx_in_apply(xd.ptr, cd.ptr if cd else None, N, Cn, D, H, W, act, qd.ptr, bits, nb_dst, b0, sd.ptr if sd else None, hd.ptr if hd else None)
+    L().umx_in_apply(xd.ptr, cd.ptr if cd else None, N, Cn, D, H, W, act, qd.ptr, bits, nb_dst, b0, sd.ptr if sd else None, hd.ptr if hd else None, 1 if split else 0)
     ufsm_b200.check()
-    return qd.download(), (sd.download() if sd else None), (hd.download(np.float16) if hd else None)
+    q, s2 = qd.download(), (sd.download() if sd else None)
+    if split:
+        q = from_split(q, N, (nb_dst or nb) * 32, S, bits)
+        if s2 is not None:
+            s2 = from_split(s2, N, 8 * nb * 32, S // 8, bits)
+    return q, s2, (hd.download(np.float16) if hd else None)
 
 
 def make_cfg(P, cw, nh=7, bits=(8, 8, 8)):

@@ -32,10 +32,10 @@ def oracle_conv(kind, x, w, b, N, Ci, D, H, W, Co, bits):
     return mx, orc.blocked_to_pm(acc, N, Co, 8 * S)
 
 
-def run_pm32(kind, mx, w, b, N, Ci, D, H, W, Co, bits):
+def run_pm32(kind, mx, w, b, N, Ci, D, H, W, Co, bits, split=True):
     c = G.Conv(kind, w, b, Co, Ci, bits)
     g = (D // 2, H // 2, W // 2) if kind == "down2" else (D, H, W)
-    raw, _ = c.fwd(mx, N, *g, G.OUT_PM32)
+    raw, _ = c.fwd(mx, N, *g, G.OUT_PM32, split=split)
     c.free()
     return raw.view(np.float32)
 
@@ -81,6 +81,21 @@ def test_conv_exact_operands_bit_identical(dev, kind, Ci, Co, D, H, W, bits):
     mx, want = oracle_conv(kind, x, w, b, 1, Ci, D, H, W, Co, bits)
     got = run_pm32(kind, mx, w, b, 1, Ci, D, H, W, Co, bits)
     assert np.array_equal(got, want), "%d of %d differ" % (np.count_nonzero(got != want), want.size)
+
+
+def test_reference_layout_input_and_output(dev):
+    # MX-fp8 tensors in the reference's own row layout (what lp_conv_fwd_f8 receives): same results as the split layout
+    N, Ci, Co, D, H, W = 1, 64, 64, 3, 19, 11
+    S = D * H * W
+    x = synth.rng(15).standard_normal(N * Ci * S).astype(np.float32)
+    w, b = synth.kaiming(16, Co, Ci, 27), synth.bias(17, Co, 0.1)
+    mx, want = oracle_conv("conv3", x, w, b, N, Ci, D, H, W, Co, 8)
+    got = run_pm32("conv3", mx, w, b, N, Ci, D, H, W, Co, 8, split=False)
+    assert np.array_equal(got, run_pm32("conv3", mx, w, b, N, Ci, D, H, W, Co, 8, split=True)) and orc.rel_l2(got, want) < TOL
+    c = G.Conv("conv3", w, b, Co, Ci, 8)
+    a = c.fwd(mx, N, D, H, W, G.OUT_MXRAW, 8, split=False)[0]
+    assert np.array_equal(a, c.fwd(mx, N, D, H, W, G.OUT_MXRAW, 8, split=True)[0])
+    c.free()
 
 
 @pytest.mark.parametrize("bits", [8, 4])

@@ -58,5 +58,6 @@ def test_wide32_one_channel(dev, bits):
     # the network input: one channel kept in a 32-wide block
     S = 4096
     x = (synth.ct_u8(9, S).astype(np.float32) / np.float32(255)).astype(np.float16)
-    got = G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True)
-    assert np.array_equal(got, orc.pm_to_mx(x, 2, 1, 1, S, bits, 32))
+    want = orc.pm_to_mx(x, 2, 1, 1, S, bits, 32)
+    assert np.array_equal(G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True), want)
+    assert np.array_equal(G.from_split(G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True, layout=1), 1, 32, S, bits), want)   # the split layout holds the same bytes

@@ -50,6 +50,7 @@ _SIG = {
     "umx_timer_free": (None, [C.c_void_p]),
     "umx_prof_begin": (None, []),
     "umx_prof_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "umx_prof_get": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "lp_mx8_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_size_t]),
     "lp_mx4_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_size_t]),
     "lp_f32_to_mx8": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
@@ -59,8 +60,9 @@ _SIG = {
     "lp_mx8_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "lp_mx4_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "umx_mx_bytes32": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_size_t]),
-    "umx_pm_to_mx32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
-    "umx_mx32_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
+    "umx_pm_to_mx32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int, C.c_int]),
+    "umx_mx_relayout": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
+    "umx_mx32_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
     "umx_h16b_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "lp_conv_fwd_f8": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, Gnp, C.c_void_p, C.c_int, Split]),
     "lp_conv_fwd_f4": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, Gnp, C.c_void_p, C.c_int, Split]),
@@ -68,11 +70,11 @@ _SIG = {
     "umx_conv_create": (C.c_void_p, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "umx_conv_create_dev": (C.c_void_p, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "umx_conv_free": (None, [C.c_void_p]),
-    "umx_conv_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "umx_conv_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "umx_stats_doubles": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "umx_in_coef": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p]),
     "umx_in_coef_static": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p]),
-    "umx_in_apply": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "umx_in_apply": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
     "umx_unet_nweights": (C.c_size_t, [C.POINTER(UnetCfg)]),
     "umx_unet_create": (C.c_void_p, [C.POINTER(UnetCfg), C.c_void_p, C.c_int]),
     "umx_unet_free": (None, [C.c_void_p]),

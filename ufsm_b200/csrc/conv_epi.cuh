@@ -1,0 +1,90 @@
+/* Pieces shared by the conv kernels: the prepared-conv object, the epilogue of one 32-channel chunk of one voxel row, and the
+   per-channel sums of a warp's 32 rows. */
+#pragma once
+#include "mx_common.cuh"
+
+struct umx_conv {
+    int kind, co, ci, bits;
+    int taps, nkb, nki, cop, cob_t, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
+    uint8_t *wpk; float *bias_p;
+};
+
+struct EpiArgs {
+    int N, D, H, W;                 /* the grid of GEMM rows */
+    int cop;                        /* GEMM columns, padded to 32 */
+    int out_mode, out_bits, nb_dst, b0, tconv, co_real, cob_t;   /* cob_t: blocks of one transposed-conv sub-voxel group */
+    int y_split;                    /* MX-fp8 output in the split layout [n][blk][half][voxel][16 B] */
+    void *y;
+    const float *bias;              /* [cop] */
+    double *part;                   /* InstanceNorm partial sums or NULL */
+};
+
+/* v: the 32 fp32 accumulators of GEMM row (n, z, oy, ox), 32-column block cb_g.  Adds the bias, rounds as the output mode asks (v keeps
+   the values as stored, which is what the statistics are taken from) and writes the row if it lies inside the volume. */
+__device__ __forceinline__ void epi_chunk(const EpiArgs &a, int n, int z, int oy, int ox, bool row_ok, int cb_g, float *v) {
+    const size_t S = (size_t)a.D * a.H * a.W;
+#pragma unroll
+    for (int k = 0; k < 32; k++) v[k] = __fadd_rn(v[k], __ldg(a.bias + cb_g * 32 + k));
+    int ob = cb_g; size_t vo = ((size_t)z * a.H + oy) * a.W + ox; size_t So = S;
+    if (a.tconv) {
+        const int abc = cb_g / a.cob_t, Ho = 2 * a.H, Wo = 2 * a.W; ob = cb_g % a.cob_t; So = S * 8;
+        vo = ((size_t)(2 * z + (abc >> 2)) * Ho + 2 * oy + ((abc >> 1) & 1)) * Wo + 2 * ox + (abc & 1);
+    }
+    if (a.out_mode != UMX_OUT_PM32 && a.out_mode != UMX_OUT_MXRAW) {
+#pragma unroll
+        for (int k = 0; k < 32; k++) v[k] = __half2float(__float2half_rn(v[k]));
+    }
+    if (!row_ok) return;
+    const size_t ro = ((size_t)n * a.nb_dst + a.b0 + ob) * So + vo;
+    if (a.out_mode == UMX_OUT_H16B) {
+        uint4 o[4]; __half2 *op = (__half2 *)o;
+#pragma unroll
+        for (int k = 0; k < 16; k++) op[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+        uint4 *dst = (uint4 *)a.y + ro * 4;
+#pragma unroll
+        for (int k = 0; k < 4; k++) dst[k] = o[k];
+    } else if (a.out_mode == UMX_OUT_MX || a.out_mode == UMX_OUT_MXRAW) {
+        unsigned w[8]; unsigned sbyte;
+        uint8_t *yb = (uint8_t *)a.y;
+        if (a.out_bits == 8) {
+            sbyte = mx_encode_row32<8>(v, w);
+            if (a.y_split) {
+                const size_t hp = ((size_t)n * a.nb_dst + a.b0 + ob) * 2;
+                *(uint4 *)(yb + (hp * So + vo) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(yb + ((hp + 1) * So + vo) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+                uint4 *dst = (uint4 *)(yb + ro * 32);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]); dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+            yb[(size_t)a.N * a.nb_dst * So * 32 + ro] = (uint8_t)sbyte;
+        } else {
+            sbyte = mx_encode_row32<4>(v, w);
+            *(uint4 *)(yb + ro * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            yb[(size_t)a.N * a.nb_dst * So * 16 + ro] = (uint8_t)sbyte;
+        }
+    } else {
+        for (int k = 0; k < 32; k++) {
+            const int c = ob * 32 + k; if (c >= a.co_real) break;
+            const size_t o = ((size_t)n * a.co_real + c) * So + vo;
+            if (a.out_mode == UMX_OUT_PM32) ((float *)a.y)[o] = v[k]; else ((__half *)a.y)[o] = __float2half_rn(v[k]);
+        }
+    }
+}
+/* per-channel sums over a warp's 32 rows: a butterfly that halves the array each step and leaves channel `lane` in every lane;
+   fp64, fixed order */
+__device__ __forceinline__ void epi_sums(const float *v, bool row_ok, int lane, double &sum, double &sumsq) {
+    double s1[32], s2[32];
+#pragma unroll
+    for (int k = 0; k < 32; k++) { const double t = row_ok ? (double)v[k] : 0.0; s1[k] = t; s2[k] = t * t; }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < o; i++) {
+            const double k1 = up ? s1[i + o] : s1[i], g1 = up ? s1[i] : s1[i + o];
+            const double k2 = up ? s2[i + o] : s2[i], g2 = up ? s2[i] : s2[i + o];
+            s1[i] = k1 + __shfl_xor_sync(0xffffffffu, g1, o);
+            s2[i] = k2 + __shfl_xor_sync(0xffffffffu, g2, o);
+        }
+    }
+    sum = s1[0]; sumsq = s2[0];
+}

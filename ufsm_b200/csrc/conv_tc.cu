@@ -24,7 +24,7 @@
    then the epilogue (tcgen05.ld of 32 channels per voxel = one MX block per thread: bias, fp16 store or MX requantisation,
    InstanceNorm partial sums in fp64).  Every wait is bounded; a wait that gives up records (code, block, stage) in a device
    flag, raises a block-wide abort flag and the block tears down normally. */
-#include "mx_common.cuh"
+#include "conv_epi.cuh"
 #include "tc_ptx.cuh"
 #include <stdlib.h>
 #include <string.h>
@@ -49,10 +49,7 @@ struct ConvArgs {
     int items_max, ipq, nquad;      /* K items per stage, items per scale quad (4 fp8 / 2 fp4), quads per stage */
     const uint8_t *x_sc;
     const uint8_t *wpk;
-    const float *bias;
-    int out_mode, out_bits, nb_dst, b0, tconv, co_real, cob_t;   /* cob_t: blocks of one transposed-conv sub-voxel group */
-    void *y;
-    double *part;
+    EpiArgs e;
     int *err;
 };
 
@@ -62,7 +59,8 @@ __device__ __forceinline__ void raise(const ConvArgs &a, volatile int *abort_fla
     __threadfence_block();
 }
 
-__global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const ConvArgs a) {
+template <int BITS>
+__global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CUtensorMap map0, const ConvArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     /* control block, then the stage ring at the next 1024-byte boundary */
     uint64_t *bars = (uint64_t *)smem_raw;                       /* [0, ring) tma full, [ring, 2 ring) scale full, [2 ring, 3 ring) empty, 3 ring: accumulator full */
@@ -100,7 +98,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
     if (warp == 0) {
         /* ---------------- TMA producer ---------------- */
         if (lane == 0) {
-            tma_prefetch_desc(&map0); if (a.bits == 8) tma_prefetch_desc(&map1);
+            tma_prefetch_desc(&map0);
             int it = 0;
             const uint8_t *wbase = a.wpk + (size_t)ntile * nst * a.w_stage_bytes;
             for (int st = 0; st < nst; st++) {
@@ -113,25 +111,14 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 const int abytes = a.taps == 27 ? 5760 : items * 4096;
                 mbar_expect_tx(bar, (uint32_t)(abytes + a.w_stage_bytes));
                 bulk_g2s(smem_u32(sb + a.offW), wbase + (size_t)st * a.w_stage_bytes, (uint32_t)a.w_stage_bytes, bar);
+                /* two 16-byte-wide planes per K item (fp8: the halves of block ki; fp4: blocks 2 ki and 2 ki + 1) */
                 if (a.taps == 27) {
                     const int ki = st / 3, zi = z + st % 3 - 1;
-                    if (a.bits == 8) {
-                        const int zz = (n * a.nkb + ki) * a.D + zi;
-                        tma_load_4d(smem_u32(sb + a.offA), &map0, bar, 0, x0 - 1, y0 - 1, zz);
-                        tma_load_4d(smem_u32(sb + a.offA + 2944), &map1, bar, 0, x0 - 1, y0 - 1, zz);
-                    } else {
-                        tma_load_5d(smem_u32(sb + a.offA), &map0, bar, 0, x0 - 1, y0 - 1, zi, n * a.nkb + 2 * ki);
-                    }
+                    tma_load_4d(smem_u32(sb + a.offA), &map0, bar, (x0 - 1) * 16, y0 - 1, zi, BITS == 8 ? (n * a.nkb + ki) * 2 : n * a.nkb + 2 * ki);
                 } else {
                     for (int j = 0; j < items; j++) {
                         const int ki = 4 * st + j;
-                        if (a.bits == 8) {
-                            const int zz = (n * a.nkb + ki) * a.D + z;
-                            tma_load_4d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, x0, y0, zz);
-                            tma_load_4d(smem_u32(sb + a.offA + j * 4096 + 2048), &map1, bar, 0, x0, y0, zz);
-                        } else {
-                            tma_load_5d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, x0, y0, z, n * a.nkb + 2 * ki);
-                        }
+                        tma_load_4d(smem_u32(sb + a.offA + j * 4096), &map0, bar, x0 * 16, y0, z, BITS == 8 ? (n * a.nkb + ki) * 2 : n * a.nkb + 2 * ki);
                     }
                 }
                 it++;
@@ -154,17 +141,10 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                     utccp_32x128b(sfa_t + 4 * q, smem_desc(sb + a.offSFA + 512 * q, 0, 128));
                     utccp_32x128b(sfb_t + 4 * q, smem_desc(sb + a.offSFB + 512 * q, 0, 128));
                 }
-                for (int j = 0; j < items; j++) {
-                    uint32_t aaddr, albo, asbo;
-                    if (a.taps == 27) { aaddr = sb + a.offA + ((j / 3) * 10 + j % 3) * 16; albo = a.bits == 8 ? 2944 : 2880; asbo = 160; }
-                    else { aaddr = sb + a.offA + j * 4096; albo = 2048; asbo = 128; }
-                    const uint64_t ad = smem_desc(aaddr, albo, asbo);
-                    const uint64_t bd = smem_desc(sb + a.offW + j * a.nt * 32, a.nt * 16, 128);
-                    const int q = j / a.ipq, id = (j % a.ipq) * (4 / a.ipq);
-                    const uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
-                    if (a.bits == 8) umma_mxf8(tmem, ad, bd, idesc_mxf8(n_cur, id, id), acc, sfa_t + 4 * q, sfb_t + 4 * q);
-                    else umma_mxf4(tmem, ad, bd, idesc_mxf4(n_cur, id, id), acc, sfa_t + 4 * q, sfb_t + 4 * q);
-                }
+                const uint32_t idesc0 = BITS == 8 ? idesc_mxf8(n_cur, 0, 0) : idesc_mxf4(n_cur, 0, 0);
+                const uint32_t b_lo = desc_lo(sb + a.offW, (uint32_t)a.nt * 16), b_hi = desc_hi(128);
+                if (a.taps == 27) issue_items<BITS, 9, true>(tmem, desc_lo(sb + a.offA, 2880), desc_hi(160), b_lo, b_hi, (uint32_t)a.nt * 2, 0, idesc0, sfa_t, sfb_t, it == 0, 9);
+                else issue_items<BITS, 4, false>(tmem, desc_lo(sb + a.offA, 2048), desc_hi(128), b_lo, b_hi, (uint32_t)a.nt * 2, 256, idesc0, sfa_t, sfb_t, it == 0, items);
                 umma_commit(bar_empty + 8 * s);
             }
             __syncwarp();
@@ -194,7 +174,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                     const int iy = oy + j / 3 - 1, ix = ox + j % 3 - 1;
                     const bool in = iy >= 0 && iy < a.H && ix >= 0 && ix < a.W;
                     const size_t vox = ((size_t)zi * a.H + iy) * a.W + ix;
-                    if (a.bits == 8) {
+                    if (BITS == 8) {
                         const unsigned b = in ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
                         wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
                     } else {
@@ -208,7 +188,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 const size_t vox = ((size_t)z * a.H + oy) * a.W + ox;
                 for (int j = 0; j < items; j++) {
                     const int ki = 4 * st + j;
-                    if (a.bits == 8) {
+                    if (BITS == 8) {
                         const unsigned b = row_ok ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
                         wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
                     } else {
@@ -233,8 +213,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
            128 threads read the same value after it and take the same branch (the barrier inside the branch is then safe) */
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (!*abort_flag) {
-            const int Ho = a.tconv ? 2 * a.H : a.H, Wo = a.tconv ? 2 * a.W : a.W;
-            const size_t So = a.tconv ? S * 8 : S;
             const int T = a.D * a.tiles_x * a.tiles_y, tsp = z * (a.tiles_x * a.tiles_y) + txy;
             double *spart = (double *)stages;                    /* [quarter][chunk][lane][2]; the ring is idle by now */
             const int nchunk = n_cur >> 5;
@@ -243,70 +221,17 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(jc * 32), rr);
                 tmem_ld_wait();
                 float v[32];
-                const int cb_g = (n0 >> 5) + jc;                 /* 32-column block of the GEMM */
 #pragma unroll
-                for (int k = 0; k < 32; k++) v[k] = __fadd_rn(__uint_as_float(rr[k]), __ldg(a.bias + cb_g * 32 + k));
-                int ob = cb_g; size_t vo = ((size_t)z * a.H + oy) * a.W + ox;
-                if (a.tconv) {
-                    const int abc = cb_g / a.cob_t; ob = cb_g % a.cob_t;
-                    vo = ((size_t)(2 * z + (abc >> 2)) * Ho + 2 * oy + ((abc >> 1) & 1)) * Wo + 2 * ox + (abc & 1);
-                }
-                if (a.out_mode != UMX_OUT_PM32 && a.out_mode != UMX_OUT_MXRAW) {
-#pragma unroll
-                    for (int k = 0; k < 32; k++) v[k] = __half2float(__float2half_rn(v[k]));
-                }
-                if (row_ok) {
-                    const size_t ro = ((size_t)n * a.nb_dst + a.b0 + ob) * So + vo;
-                    if (a.out_mode == UMX_OUT_H16B) {
-                        uint4 o[4]; __half2 *op = (__half2 *)o;
-#pragma unroll
-                        for (int k = 0; k < 16; k++) op[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
-                        uint4 *dst = (uint4 *)a.y + ro * 4;
-#pragma unroll
-                        for (int k = 0; k < 4; k++) dst[k] = o[k];
-                    } else if (a.out_mode == UMX_OUT_MX || a.out_mode == UMX_OUT_MXRAW) {
-                        unsigned w[8]; unsigned sbyte;
-                        uint8_t *yb = (uint8_t *)a.y;
-                        if (a.out_bits == 8) {
-                            sbyte = mx_encode_row32<8>(v, w);
-                            uint4 *dst = (uint4 *)(yb + ro * 32);
-                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]); dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-                            yb[(size_t)a.N * a.nb_dst * So * 32 + ro] = (uint8_t)sbyte;
-                        } else {
-                            sbyte = mx_encode_row32<4>(v, w);
-                            *(uint4 *)(yb + ro * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                            yb[(size_t)a.N * a.nb_dst * So * 16 + ro] = (uint8_t)sbyte;
-                        }
-                    } else {
-                        for (int k = 0; k < 32; k++) {
-                            const int c = ob * 32 + k; if (c >= a.co_real) break;
-                            const size_t o = ((size_t)n * a.co_real + c) * So + vo;
-                            if (a.out_mode == UMX_OUT_PM32) ((float *)a.y)[o] = v[k]; else ((__half *)a.y)[o] = __float2half_rn(v[k]);
-                        }
-                    }
-                }
-                if (a.part) {
-                    /* per-channel sums over this warp's 32 rows: a butterfly that halves the array each step, ending with
-                       channel `lane` in every lane; fp64, fixed order */
-                    double s1[32], s2[32];
-#pragma unroll
-                    for (int k = 0; k < 32; k++) { const double t = row_ok ? (double)v[k] : 0.0; s1[k] = t; s2[k] = t * t; }
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) {
-                        const bool up = (lane & o) != 0;
-#pragma unroll
-                        for (int i = 0; i < o; i++) {
-                            const double k1 = up ? s1[i + o] : s1[i], g1 = up ? s1[i] : s1[i + o];
-                            const double k2 = up ? s2[i + o] : s2[i], g2 = up ? s2[i] : s2[i + o];
-                            s1[i] = k1 + __shfl_xor_sync(0xffffffffu, g1, o);
-                            s2[i] = k2 + __shfl_xor_sync(0xffffffffu, g2, o);
-                        }
-                    }
-                    spart[((q4 * 4 + jc) * 32 + lane) * 2] = s1[0];
-                    spart[((q4 * 4 + jc) * 32 + lane) * 2 + 1] = s2[0];
+                for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[k]);
+                epi_chunk(a.e, n, z, oy, ox, row_ok, (n0 >> 5) + jc, v);
+                if (a.e.part) {
+                    double s1, s2;
+                    epi_sums(v, row_ok, lane, s1, s2);
+                    spart[((q4 * 4 + jc) * 32 + lane) * 2] = s1;
+                    spart[((q4 * 4 + jc) * 32 + lane) * 2 + 1] = s2;
                 }
             }
-            if (a.part) {
+            if (a.e.part) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 /* 128 threads: (chunk, lane) pairs; add the four quarters in order */
                 const int e = (int)threadIdx.x - 64;
@@ -315,7 +240,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                     double t1 = 0.0, t2 = 0.0;
 #pragma unroll
                     for (int qq = 0; qq < 4; qq++) { t1 += spart[((qq * 4 + jc) * 32 + l) * 2]; t2 += spart[((qq * 4 + jc) * 32 + l) * 2 + 1]; }
-                    double *dst = a.part + (((size_t)n * T + tsp) * a.cop + n0 + jc * 32 + l) * 2;
+                    double *dst = a.e.part + (((size_t)n * T + tsp) * a.cop + n0 + jc * 32 + l) * 2;
                     dst[0] = t1; dst[1] = t2;
                 }
             }
@@ -408,11 +333,9 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }   // namespace
 
-struct umx_conv {
-    int kind, co, ci, bits;
-    int taps, nkb, nki, cop, cob_t, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
-    uint8_t *wpk; float *bias_p;
-};
+int umx_conv_r_fits(const umx_conv *c);
+int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, int N, int D, int H, int W, const EpiArgs &e);
+
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
     if (!umx_ready("umx_conv_create")) return nullptr;
@@ -460,7 +383,7 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
 extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); free(c); }
 extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * D * ceil_div(H, 16) * ceil_div(W, 8) * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
-extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part) {
+extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags) {
     if (!umx_ready("umx_conv_fwd")) return -1;
     if (!c) { umx_latch_msg("umx_conv_fwd: no conv"); return -1; }
     if (part && (out_mode != UMX_OUT_H16B || c->kind == UMX_TCONV2)) { fprintf(stderr, "umx_conv_fwd: partial sums only with a blocked fp16 output of a plain conv\n"); abort(); }
@@ -470,7 +393,7 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.taps = c->taps; a.bits = c->bits;
     a.cop = c->cop; a.nt = c->nt; a.ntiles_n = c->ntiles_n; a.tiles_x = ceil_div(W, 8); a.tiles_y = ceil_div(H, 16);
     a.w_stage_bytes = c->w_stage_bytes; a.nst = c->nst; a.items_max = c->items_max; a.ipq = c->ipq; a.nquad = c->nquad;
-    const int abytes = c->taps == 27 ? 2944 * 2 : 4 * 4096;   /* fp8 3^3: the second 16-byte plane starts at the next 128-byte boundary after 2880 */
+    const int abytes = c->taps == 27 ? 5760 : 4 * 4096;
     auto up128 = [](int v) { return (v + 127) & ~127; };
     a.offW = 0; a.offSFB = c->items_max * c->nt * 32; a.offA = up128(c->w_stage_bytes); a.offSFA = a.offA + up128(abytes);
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
@@ -479,42 +402,53 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     const size_t S = (size_t)D * H * W;
     const int rb = c->bits == 8 ? 32 : 16;
     a.x_sc = (const uint8_t *)x + (size_t)N * c->nkb * S * rb;
-    a.wpk = c->wpk; a.bias = c->bias_p;
-    a.out_mode = out_mode; a.out_bits = out_bits; a.tconv = c->kind == UMX_TCONV2; a.co_real = c->co; a.cob_t = c->cob_t;
-    a.nb_dst = nb_dst ? nb_dst : c->cob_t; a.b0 = nb_dst ? b0 : 0;
-    a.y = y; a.part = part; a.err = umx_errflag();
+    a.wpk = c->wpk;
+    a.e.N = N; a.e.D = D; a.e.H = H; a.e.W = W; a.e.cop = c->cop; a.e.bias = c->bias_p;
+    a.e.out_mode = out_mode; a.e.out_bits = out_bits; a.e.tconv = c->kind == UMX_TCONV2; a.e.co_real = c->co; a.e.cob_t = c->cob_t;
+    a.e.nb_dst = nb_dst ? nb_dst : c->cob_t; a.e.b0 = nb_dst ? b0 : 0;
+    a.e.y = y; a.e.part = part; a.e.y_split = (flags & UMX_Y_SPLIT) != 0; a.err = umx_errflag();
     if (!a.err) return -1;
-    /* tensor maps over the activation codes */
-    CUtensorMap m0, m1; memset(&m0, 0, sizeof m0); memset(&m1, 0, sizeof m1);
-    const cuuint32_t bx = c->taps == 27 ? 10 : 8, by = c->taps == 27 ? 18 : 16;
-    CUresult r0, r1 = CUDA_SUCCESS;
-    if (c->bits == 8) {
-        const cuuint64_t gd[4] = {16, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)D * N * c->nkb};
-        const cuuint64_t gs[3] = {32, (cuuint64_t)32 * W, (cuuint64_t)32 * W * H};
-        const cuuint32_t box[4] = {16, bx, by, 1}, es[4] = {1, 1, 1, 1};
-        r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        r1 = enc(&m1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)((const uint8_t *)x + 16), gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else {
-        const cuuint64_t gd[5] = {16, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)D, (cuuint64_t)N * c->nkb};
-        const cuuint64_t gs[4] = {16, (cuuint64_t)16 * W, (cuuint64_t)16 * W * H, (cuuint64_t)16 * S};
-        const cuuint32_t box[5] = {16, bx, by, 1, 2}, es[5] = {1, 1, 1, 1, 1};
-        r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        m1 = m0;
+    /* tensor map over the activation codes seen as 16-byte-wide planes [plane][z][y][x * 16 B]: fp8 in the split layout has two planes a
+       block, fp4 one.  A box is (10 or 8 voxels) x (18 or 16 rows) x 1 plane of z x 2 planes; voxels outside the volume read as zero. */
+    if (c->bits == 8 && !(flags & UMX_X_SPLIT)) {   /* reference layout: re-lay the codes into scratch first */
+        void *ws = umx_ws(1, umx_mx_bytes32(8, N, c->nkb * 32, S));
+        if (!ws) return -1;
+        umx_mx_relayout(x, 8, N, c->nkb * 32, S, ws, UMX_LAYOUT_SPLIT);
+        x = ws; a.x_sc = (const uint8_t *)x + (size_t)N * c->nkb * S * 32;
     }
-    if (r0 != CUDA_SUCCESS || r1 != CUDA_SUCCESS) { char b[160]; snprintf(b, sizeof b, "umx_conv_fwd: cuTensorMapEncodeTiled failed (%d, %d) for %d x %d x %d x %d, %d blocks", (int)r0, (int)r1, N, D, H, W, c->nkb); umx_latch_msg(b); return -1; }
+    CUtensorMap m0; memset(&m0, 0, sizeof m0);
+    {
+        const cuuint32_t bx = c->taps == 27 ? 10 : 8, by = c->taps == 27 ? 18 : 16;
+        const cuuint64_t gd[4] = {(cuuint64_t)W * 16, (cuuint64_t)H, (cuuint64_t)D, (cuuint64_t)N * c->nkb * (c->bits == 8 ? 2 : 1)};
+        const cuuint64_t gs[3] = {(cuuint64_t)W * 16, (cuuint64_t)W * H * 16, (cuuint64_t)S * 16};
+        const cuuint32_t box[4] = {bx * 16, by, 1, 2}, es[4] = {1, 1, 1, 1};
+        const CUresult r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r0 != CUDA_SUCCESS) { char b[160]; snprintf(b, sizeof b, "umx_conv_fwd: cuTensorMapEncodeTiled failed (%d) for %d x %d x %d x %d, %d blocks", (int)r0, N, D, H, W, c->nkb); umx_latch_msg(b); return -1; }
+    }
+    /* algorithmic work: 2 x output voxels x real input channels x real output channels x taps (no credit for padding) */
+    const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * (c->taps == 27 ? 27.0 : 1.0);
+    static int force_v1 = -1;
+    if (force_v1 < 0) { const char *ev = getenv("UMX_CONV_V1"); force_v1 = ev && *ev && *ev != '0'; }
+    if (!force_v1 && umx_conv_r_fits(c)) {   /* resident weights: the persistent z-marching kernel */
+        const int pid = umx_prof_open(flops);
+        const int rc = umx_conv_fwd_r(c, x, &m0, N, D, H, W, a.e);
+        umx_prof_close(pid);
+        g_umx_launches++;
+        UMX_CK("umx_conv_fwd");
+        return rc;
+    }
     const size_t smem = 1024 + (size_t)a.ring * a.stage_bytes;
     static size_t smem_set[16];
     int dev = 0; cudaGetDevice(&dev); dev &= 15;
     if (smem_set[dev] < smem) {
-        cudaError_t e = cudaFuncSetAttribute(conv_mx_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+        cudaError_t e = cudaFuncSetAttribute(conv_mx_k<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(conv_mx_k<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
         if (e != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", e); return -1; }
         smem_set[dev] = 227 * 1024;
     }
     const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n);
-    /* algorithmic work: 2 x output voxels x real input channels x real output channels x taps (no credit for padding) */
-    const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * (c->taps == 27 ? 27.0 : 1.0);
     const int pid = umx_prof_open(flops);
-    conv_mx_k<<<grid, kThreads, smem>>>(m0, m1, a);
+    if (c->bits == 8) conv_mx_k<8><<<grid, kThreads, smem>>>(m0, a); else conv_mx_k<4><<<grid, kThreads, smem>>>(m0, a);
     umx_prof_close(pid);
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");

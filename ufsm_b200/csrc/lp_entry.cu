@@ -35,7 +35,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     if (xbf == UMX_F16) {
         void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, xs.c, S));
         if (!ws) return 0;
-        umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, bits);
+        umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, bits, UMX_LAYOUT_SPLIT);
         xq = ws;
     }
     int dev = 0; cudaGetDevice(&dev);
@@ -49,7 +49,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         if (!c) return 0;
         if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout, xs.c, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
     }
-    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr);
+    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xbf == UMX_F16 ? UMX_X_SPLIT : 0);   /* MX tensors of the reference interface keep the reference layout */
     if (temp) { cudaDeviceSynchronize(); umx_conv_free(c); }
     return 0;
 }

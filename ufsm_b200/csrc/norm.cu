@@ -31,7 +31,7 @@ extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int 
 
 template <int BITS>
 __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, const float2 *__restrict__ coef, int N, int C, int D, int H, int W, int act,
-                                                  uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout) {
+                                                  uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout, int split) {
     const int nb = (C + 31) / 32; const size_t S = (size_t)D * H * W, rows = (size_t)N * nb * S;
     constexpr int RB = 32 * BITS / 8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
@@ -66,9 +66,14 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
         const unsigned sb = mx_encode_row32<BITS>(f, w);
         if (q) {
             const size_t ro = ((size_t)n * nb_dst + b0 + blk) * S + v;
-            uint8_t *p = q + ro * RB;
-            ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            if (BITS == 8 && split) {
+                const size_t hp = ((size_t)n * nb_dst + b0 + blk) * 2;
+                *(uint4 *)(q + (hp * S + v) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(q + ((hp + 1) * S + v) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+                uint8_t *p = q + ro * RB;
+                ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
             q[(size_t)N * nb_dst * S * RB + ro] = (uint8_t)sb;
         }
         if (q2) {   /* space-to-depth copy: block (tap * nb + blk) at the coarse voxel */
@@ -76,20 +81,25 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
             const int tap = ((zz & 1) * 2 + (yy & 1)) * 2 + (xx & 1);
             const size_t Sc = S / 8, vc = ((size_t)(zz >> 1) * (H >> 1) + (yy >> 1)) * (W >> 1) + (xx >> 1);
             const size_t ro = ((size_t)n * 8 * nb + tap * nb + blk) * Sc + vc;
-            uint8_t *p = q2 + ro * RB;
-            ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            if (BITS == 8 && split) {
+                const size_t hp = ((size_t)n * 8 * nb + tap * nb + blk) * 2;
+                *(uint4 *)(q2 + (hp * Sc + vc) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(q2 + ((hp + 1) * Sc + vc) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+                uint8_t *p = q2 + ro * RB;
+                ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
             q2[(size_t)N * 8 * nb * Sc * RB + ro] = (uint8_t)sb;
         }
     }
 }
-extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h) {
+extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout) {
     if (!umx_ready("umx_in_apply")) return;
     if (q_s2d && ((D | H | W) & 1)) { fprintf(stderr, "umx_in_apply: the space-to-depth copy needs even D, H, W\n"); abort(); }
     const int nb = (C + 31) / 32; if (!nb_dst) { nb_dst = nb; b0 = 0; }
     const size_t rows = (size_t)N * nb * D * H * W; size_t g = (rows + 255) / 256; if (g > 148u * 32u) g = 148u * 32u; if (!g) g = 1;
-    if (bits == 8) in_apply_k<8><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h);
-    else in_apply_k<4><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h);
+    if (bits == 8) in_apply_k<8><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT);
+    else in_apply_k<4><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT);
     g_umx_launches++;
     UMX_CK("umx_in_apply");
 }

@@ -13,7 +13,7 @@ template <> __device__ __forceinline__ float ld_as_f32<float>(const float *p) { 
 template <> __device__ __forceinline__ float ld_as_f32<__half>(const __half *p) { return __half2float(__ldg(p)); }
 
 template <int BITS, typename TI>
-__global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw) {
+__global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw, int split) {
     const int nb = (C + bw - 1) / bw, rb = bw * BITS / 8;
     const size_t rows = (size_t)N * nb * S;
     uint8_t *sc = y + rows * rb;
@@ -26,7 +26,10 @@ __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint
         const unsigned sb = mx_encode_row32<BITS>(r, w);
         uint8_t *p = y + i * rb;
         if (BITS == 8) {
-            if (bw == 32) { ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]); ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]); }
+            if (bw == 32 && split) {   /* two 16-byte planes per block: [n][blk][half][voxel][16 B] */
+                const size_t hp = (i / S) * 2;
+                *(uint4 *)(y + (hp * S + v) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(y + ((hp + 1) * S + v) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else if (bw == 32) { ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]); ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]); }
             else if (bw == 16) ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
             else ((uint2 *)p)[0] = make_uint2(w[0], w[1]);
         } else {
@@ -38,7 +41,7 @@ __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint
     }
 }
 template <int BITS>
-__global__ void __launch_bounds__(256) mx_to_pm_k(const uint8_t *__restrict__ x, float *__restrict__ y, int N, int C, size_t S, int bw) {
+__global__ void __launch_bounds__(256) mx_to_pm_k(const uint8_t *__restrict__ x, float *__restrict__ y, int N, int C, size_t S, int bw, int split) {
     const int nb = (C + bw - 1) / bw, rb = bw * BITS / 8;
     const size_t rows = (size_t)N * nb * S;
     const uint8_t *sc = x + rows * rb;
@@ -48,7 +51,7 @@ __global__ void __launch_bounds__(256) mx_to_pm_k(const uint8_t *__restrict__ x,
         const uint8_t *p = x + i * rb;
         for (int k = 0; k < bw; k++) {
             const int c = blk * bw + k; if (c >= C) break;
-            const float e = BITS == 8 ? dec_e4m3(p[k]) : dec_e2m1((p[k >> 1] >> ((k & 1) * 4)) & 15u);
+            const float e = BITS == 8 ? dec_e4m3(split ? x[(((i / S) * 2 + (k >> 4)) * S + v) * 16 + (k & 15)] : p[k]) : dec_e2m1((p[k >> 1] >> ((k & 1) * 4)) & 15u);
             y[((size_t)n * C + c) * S + v] = e * s;
         }
     }
@@ -64,23 +67,23 @@ __global__ void __launch_bounds__(256) h16b_to_pm_k(const __half *__restrict__ x
 
 static unsigned grid_for(size_t rows) { size_t g = (rows + 255) / 256; return (unsigned)(g > 148u * 64u ? 148u * 64u : g ? g : 1); }
 
-static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int bwf, const char *who) {
+static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int bwf, const char *who, int split = 0) {
     if (!umx_ready(who)) return;
     if (dt != 0 && dt != 2) { fprintf(stderr, "%s: source type %d is not built (fp32 and fp16 only)\n", who, dt); abort(); }
     const int bw = mxbw(C, bwf);
     const size_t rows = (size_t)N * ((C + bw - 1) / bw) * S;
     const unsigned g = grid_for(rows);
-    if (bits == 8) { if (dt == 2) pm_to_mx_k<8, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw); else pm_to_mx_k<8, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw); }
-    else { if (dt == 2) pm_to_mx_k<4, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw); else pm_to_mx_k<4, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw); }
+    if (bits == 8) { if (dt == 2) pm_to_mx_k<8, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<8, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
+    else { if (dt == 2) pm_to_mx_k<4, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<4, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
     g_umx_launches++;
     UMX_CK(who);
 }
-static void from_mx(const void *x, int N, int C, size_t S, float *y, int bits, int bwf, const char *who) {
+static void from_mx(const void *x, int N, int C, size_t S, float *y, int bits, int bwf, const char *who, int split = 0) {
     if (!umx_ready(who)) return;
     const int bw = mxbw(C, bwf);
     const size_t rows = (size_t)N * ((C + bw - 1) / bw) * S;
-    if (bits == 8) mx_to_pm_k<8><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw);
-    else mx_to_pm_k<4><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw);
+    if (bits == 8) mx_to_pm_k<8><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw, split);
+    else mx_to_pm_k<4><<<grid_for(rows), 256>>>((const uint8_t *)x, y, N, C, S, bw, split);
     g_umx_launches++;
     UMX_CK(who);
 }
@@ -93,11 +96,28 @@ extern "C" void lp_h16_to_mx8(const void *x, int dt, int N, int C, size_t S, voi
 extern "C" void lp_h16_to_mx4(const void *x, int dt, int N, int C, size_t S, void *y) { to_mx(x, dt, N, C, S, y, 4, 0, "lp_h16_to_mx4"); }
 extern "C" void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 8, 0, "lp_mx8_to_f32"); }
 extern "C" void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 4, 0, "lp_mx4_to_f32"); }
-extern "C" void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits) { to_mx(x, dt, N, C, S, y, bits, 32, "umx_pm_to_mx32"); }
-extern "C" void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, bits, 32, "umx_mx32_to_f32"); }
+extern "C" void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout) { to_mx(x, dt, N, C, S, y, bits, 32, "umx_pm_to_mx32", layout == UMX_LAYOUT_SPLIT && bits == 8); }
+extern "C" void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y, int layout) { from_mx(x, N, C, S, y, bits, 32, "umx_mx32_to_f32", layout == UMX_LAYOUT_SPLIT && bits == 8); }
 extern "C" void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y) {
     if (!umx_ready("umx_h16b_to_f32")) return;
     h16b_to_pm_k<<<grid_for((size_t)N * ((C + 31) / 32) * S), 256>>>((const __half *)x, y, N, C, S);
     g_umx_launches++;
     UMX_CK("umx_h16b_to_f32");
+}
+
+/* MX-fp8 codes between the reference layout [n][blk][voxel][32 B] and the split layout [n][blk][half][voxel][16 B]; the scale plane is
+   copied as it is.  One thread per 16-byte half row. */
+__global__ void __launch_bounds__(256) relayout8_k(const uint4 *__restrict__ src, uint4 *__restrict__ dst, size_t rows, size_t S, int to_split) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * 2; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i >> 1, h = i & 1, sp = ((r / S) * 2 + h) * S + r % S;       /* reference index i = 2 r + h; split index sp */
+        if (to_split) dst[sp] = __ldg(src + i); else dst[i] = __ldg(src + sp);
+    }
+}
+extern "C" void umx_mx_relayout(const void *src, int bits, int N, int C, size_t S, void *dst, int to_layout) {
+    if (!umx_ready("umx_mx_relayout")) return;
+    const size_t rows = (size_t)N * ((C + 31) / 32) * S, rb = bits == 8 ? 32 : 16;
+    if (bits == 8) { relayout8_k<<<grid_for(rows * 2), 256>>>((const uint4 *)src, (uint4 *)dst, rows, S, to_layout == UMX_LAYOUT_SPLIT); g_umx_launches++; }
+    else cudaMemcpyAsync(dst, src, rows * rb, cudaMemcpyDeviceToDevice, 0);
+    cudaMemcpyAsync((uint8_t *)dst + rows * rb, (const uint8_t *)src + rows * rb, rows, cudaMemcpyDeviceToDevice, 0);
+    UMX_CK("umx_mx_relayout");
 }

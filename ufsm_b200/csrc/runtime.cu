@@ -136,3 +136,10 @@ extern "C" int umx_prof_end(double *ms, double *flops) {
     for (int i = 0; i < g_pn; i++) { float t = 0.f; if (cudaEventElapsedTime(&t, g_pev[2 * i], g_pev[2 * i + 1]) == cudaSuccess) *ms += t; *flops += g_pflops[i]; }
     return g_pn;
 }
+/* after umx_prof_end: device time (ms) and algorithmic FLOPs of the i-th conv launch seen; returns 0, or -1 past the end */
+extern "C" int umx_prof_get(int i, double *ms, double *flops) {
+    if (i < 0 || i >= g_pn) return -1;
+    float t = 0.f; cudaEventElapsedTime(&t, g_pev[2 * i], g_pev[2 * i + 1]);
+    *ms = t; *flops = g_pflops[i];
+    return 0;
+}

@@ -85,3 +85,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+/* ---- cheap descriptor arithmetic for the MMA issue loop: a descriptor is (hi << 32) | lo with lo = (address >> 4) | (lbo >> 4) << 16 and
+   hi = (sbo >> 4) | version; moving the start address by b bytes adds b >> 4 to lo (shared memory is below 256 KB, so no carry) ---- */
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) { return ((addr & 0x3ffffu) >> 4) | ((lbo >> 4) << 16); }
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return (sbo >> 4) | (1u << 14); }
+__device__ __forceinline__ uint64_t desc_make(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+/* the MMAs of `ITEMS` K items that share accumulator, scale buffers and a fixed A / B address step per item:
+   item j reads A at a_lo + a_step(j), B at b_lo + j * b_step; fp8: four items a scale quad (scale id = j % 4); fp4: two (id = 2 (j % 2)) */
+template <int BITS, int ITEMS, bool TAPS3>
+__device__ __forceinline__ void issue_items(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t b_step, uint32_t a_step1,
+                                            uint32_t idesc0, uint32_t sfa_t, uint32_t sfb_t, bool fresh, int nitems) {
+#pragma unroll
+    for (int j = 0; j < ITEMS; j++) {
+        if (j < nitems) {
+            constexpr int IPQ = BITS == 8 ? 4 : 2;
+            const int q = j / IPQ, id = (j % IPQ) * (4 / IPQ);
+            const uint32_t aoff = TAPS3 ? (uint32_t)((j / 3) * 10 + j % 3) : (uint32_t)j * a_step1;
+            const uint64_t ad = desc_make(a_lo + aoff, a_hi), bd = desc_make(b_lo + (uint32_t)j * b_step, b_hi);
+            const uint32_t idesc = idesc0 | ((uint32_t)id << 4) | ((uint32_t)id << 29);
+            const uint32_t acc = (fresh && j == 0) ? 0u : 1u;
+            if (BITS == 8) umma_mxf8(d_tmem, ad, bd, idesc, acc, sfa_t + 4 * q, sfb_t + 4 * q);
+            else umma_mxf4(d_tmem, ad, bd, idesc, acc, sfa_t + 4 * q, sfb_t + 4 * q);
+        }
+    }
+}

@@ -6,7 +6,8 @@
    The second apply of an encoder level writes the skip half of the decoder's concat tensor directly and a space-to-depth copy
    that turns the 2^3 stride-2 down conv into a 1^3 GEMM; the transposed conv is a GEMM to 8 Cout columns whose epilogue scatters
    and requantises straight into the other half of the concat tensor (xtconv_cat_q, src/nn_xnet.cu:1775-1789).  Every tensor's MX
-   format is that of the conv that reads it.  All buffers are allocated once at creation. */
+   format is that of the conv that reads it; MX-fp8 tensors are kept in the split layout (two 16-byte planes per block).  All buffers are allocated once at
+   creation. */
 #include "../../include/ufsm_mx.h"
 #include <math.h>
 #include <stdio.h>
@@ -121,31 +122,31 @@ long umx_unet_launches(const umx_unet *u) { return umx_launch_count() - u->launc
 
 /* conv -> blocked fp16 + partial sums -> coefficients -> apply into q (and q_s2d) */
 static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int N, int C, int D, void *q, int bits, int nb_dst, int b0, void *q_s2d) {
-    umx_conv_fwd(c, x, N, D, D, D, u->ybuf, UMX_OUT_H16B, 0, 0, 0, u->part);
+    umx_conv_fwd(c, x, N, D, D, D, u->ybuf, UMX_OUT_H16B, 0, 0, 0, u->part, UMX_X_SPLIT);
     umx_in_coef(u->part, N, C, D, D, D, nullptr, nullptr, 1e-5f, u->coef);
-    umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr);
+    umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr, UMX_LAYOUT_SPLIT);
 }
 static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) {
     const umx_unet_cfg *c = &u->cfg; const int L = c->L, bm = c->bits_mid, bl = c->bits_last;
     if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_forward: batch %d outside 1..%d\n", N, u->maxN); abort(); }
-    umx_pm_to_mx32(x_dev, UMX_F16, N, 1, cube(c->P), u->x_mx, c->bits_first);
+    umx_pm_to_mx32(x_dev, UMX_F16, N, 1, cube(c->P), u->x_mx, c->bits_first, UMX_LAYOUT_SPLIT);
     for (int l = 0; l < L; l++) {
         const int D = u->Dl[l], C = c->cw[l], nb = C / 32;
         conv_norm(u, u->enc1[l], l ? u->dn[l] : u->x_mx, N, C, D, u->act[l], bm, 0, 0, nullptr);
         if (l < L - 1) {
             conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 2 * nb, nb, u->s2d[l]);
-            umx_conv_fwd(u->down[l], u->s2d[l], N, D / 2, D / 2, D / 2, u->dn[l + 1], UMX_OUT_MX, bm, 0, 0, nullptr);
+            umx_conv_fwd(u->down[l], u->s2d[l], N, D / 2, D / 2, D / 2, u->dn[l + 1], UMX_OUT_MX, bm, 0, 0, nullptr, UMX_X_SPLIT | UMX_Y_SPLIT);
         } else conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 0, 0, nullptr);
     }
     const void *cur = u->cat[L - 1];
     for (int l = L - 2; l >= 0; l--) {
         const int D = u->Dl[l], C = c->cw[l], nb = C / 32, Dc = u->Dl[l + 1];
-        umx_conv_fwd(u->up[l], cur, N, Dc, Dc, Dc, u->cat[l], UMX_OUT_MX, bm, 2 * nb, 0, nullptr);
+        umx_conv_fwd(u->up[l], cur, N, Dc, Dc, Dc, u->cat[l], UMX_OUT_MX, bm, 2 * nb, 0, nullptr, UMX_X_SPLIT | UMX_Y_SPLIT);
         conv_norm(u, u->dec1[l], u->cat[l], N, C, D, u->act[l], l ? bm : bl, 0, 0, nullptr);
         conv_norm(u, u->dec2[l], u->act[l], N, C, D, u->dec[l], l ? bm : bl, 0, 0, nullptr);
         cur = u->dec[l];
     }
-    umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : UMX_OUT_PM32, 0, 0, 0, nullptr);
+    umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : UMX_OUT_PM32, 0, 0, 0, nullptr, UMX_X_SPLIT);
     return 0;
 }
 int umx_unet_forward(umx_unet *u, const void *x_dev, int N, float *logits_dev) { return forward(u, x_dev, N, logits_dev, UMX_F32); }
