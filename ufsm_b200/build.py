@@ -10,7 +10,7 @@ CU = ["runtime.cu", "quant.cu", "norm.cu", "conv_tc.cu", "conv_tcr.cu", "lp_entr
 C = ["unet.c"]
 NVCC = os.environ.get("UFSM_NVCC", "/usr/local/cuda/bin/nvcc")
 GCC = os.environ.get("UFSM_GCC", "gcc")
-NVFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
+NVFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"] + os.environ.get("UFSM_NVCC_EXTRA", "").split()
 
 
 def _newer(src, dst):

@@ -1,5 +1,4 @@
-/* Pieces shared by the conv kernels: the prepared-conv object, the epilogue of one 32-channel chunk of one voxel row, and the
-   per-channel sums of a warp's 32 rows. */
+/* Pieces shared by the conv kernels: the prepared-conv object and the epilogue of one 32-channel chunk of one voxel row. */
 #pragma once
 #include "mx_common.cuh"
 
@@ -7,6 +6,7 @@ struct umx_conv {
     int kind, co, ci, bits;
     int taps, nkb, nki, cop, cob_t, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
     uint8_t *wpk; float *bias_p;
+    uint8_t *wr;                    /* weight image of the z-marching kernel, or NULL */
 };
 
 struct EpiArgs {
@@ -16,7 +16,6 @@ struct EpiArgs {
     int y_split;                    /* MX-fp8 output in the split layout [n][blk][half][voxel][16 B] */
     void *y;
     const float *bias;              /* [cop] */
-    double *part;                   /* InstanceNorm partial sums or NULL */
 };
 
 /* v: the 32 fp32 accumulators of GEMM row (n, z, oy, ox), 32-column block cb_g.  Adds the bias, rounds as the output mode asks (v keeps
@@ -68,23 +67,4 @@ __device__ __forceinline__ void epi_chunk(const EpiArgs &a, int n, int z, int oy
             if (a.out_mode == UMX_OUT_PM32) ((float *)a.y)[o] = v[k]; else ((__half *)a.y)[o] = __float2half_rn(v[k]);
         }
     }
-}
-/* per-channel sums over a warp's 32 rows: a butterfly that halves the array each step and leaves channel `lane` in every lane;
-   fp64, fixed order */
-__device__ __forceinline__ void epi_sums(const float *v, bool row_ok, int lane, double &sum, double &sumsq) {
-    double s1[32], s2[32];
-#pragma unroll
-    for (int k = 0; k < 32; k++) { const double t = row_ok ? (double)v[k] : 0.0; s1[k] = t; s2[k] = t * t; }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        const bool up = (lane & o) != 0;
-#pragma unroll
-        for (int i = 0; i < o; i++) {
-            const double k1 = up ? s1[i + o] : s1[i], g1 = up ? s1[i] : s1[i + o];
-            const double k2 = up ? s2[i + o] : s2[i], g2 = up ? s2[i] : s2[i + o];
-            s1[i] = k1 + __shfl_xor_sync(0xffffffffu, g1, o);
-            s2[i] = k2 + __shfl_xor_sync(0xffffffffu, g2, o);
-        }
-    }
-    sum = s1[0]; sumsq = s2[0];
 }

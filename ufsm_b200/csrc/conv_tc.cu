@@ -21,8 +21,8 @@
    TMEM with tcgen05.cp before issuing the stage's MMAs.  Out-of-range voxels get scale 1 (their codes are zero).
 
    Roles (192 threads): warp 0 lane 0 = TMA producer; warp 1 = TMEM allocation, lane 0 = MMA issue; warps 2-5 = scale gather,
-   then the epilogue (tcgen05.ld of 32 channels per voxel = one MX block per thread: bias, fp16 store or MX requantisation,
-   InstanceNorm partial sums in fp64).  Every wait is bounded; a wait that gives up records (code, block, stage) in a device
+   then the epilogue (tcgen05.ld of 32 channels per voxel = one MX block per thread: bias, fp16 store or MX requantisation;
+   InstanceNorm partial sums are taken by a separate pass over the stored output).  Every wait is bounded; a wait that gives up records (code, block, stage) in a device
    flag, raises a block-wide abort flag and the block tears down normally. */
 #include "conv_epi.cuh"
 #include "tc_ptx.cuh"
@@ -209,12 +209,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
         /* ---- epilogue ---- */
         if (!mbar_wait(bar_acc, 0, abort_flag, kWaitLimit)) raise(a, abort_flag, 5, 0);
         tc_fence_after();
-        /* every epilogue thread reaches this barrier whatever happened above; a give-up raised the abort flag before it, so all
-           128 threads read the same value after it and take the same branch (the barrier inside the branch is then safe) */
-        asm volatile("bar.sync 1, 128;" ::: "memory");
         if (!*abort_flag) {
-            const int T = a.D * a.tiles_x * a.tiles_y, tsp = z * (a.tiles_x * a.tiles_y) + txy;
-            double *spart = (double *)stages;                    /* [quarter][chunk][lane][2]; the ring is idle by now */
             const int nchunk = n_cur >> 5;
             for (int jc = 0; jc < nchunk; jc++) {
                 uint32_t rr[32];
@@ -224,25 +219,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
 #pragma unroll
                 for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[k]);
                 epi_chunk(a.e, n, z, oy, ox, row_ok, (n0 >> 5) + jc, v);
-                if (a.e.part) {
-                    double s1, s2;
-                    epi_sums(v, row_ok, lane, s1, s2);
-                    spart[((q4 * 4 + jc) * 32 + lane) * 2] = s1;
-                    spart[((q4 * 4 + jc) * 32 + lane) * 2 + 1] = s2;
-                }
-            }
-            if (a.e.part) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                /* 128 threads: (chunk, lane) pairs; add the four quarters in order */
-                const int e = (int)threadIdx.x - 64;
-                if (e < nchunk * 32) {
-                    const int jc = e >> 5, l = e & 31;
-                    double t1 = 0.0, t2 = 0.0;
-#pragma unroll
-                    for (int qq = 0; qq < 4; qq++) { t1 += spart[((qq * 4 + jc) * 32 + l) * 2]; t2 += spart[((qq * 4 + jc) * 32 + l) * 2 + 1]; }
-                    double *dst = a.e.part + (((size_t)n * T + tsp) * a.cop + n0 + jc * 32 + l) * 2;
-                    dst[0] = t1; dst[1] = t2;
-                }
             }
         }
     }
@@ -334,7 +310,9 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 }   // namespace
 
 int umx_conv_r_fits(const umx_conv *c);
-int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, int N, int D, int H, int W, const EpiArgs &e);
+uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev);
+int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc, int N, int D, int H, int W, const EpiArgs &e);
+void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part);
 
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
@@ -365,6 +343,7 @@ static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev,
     const size_t total = (size_t)c->ntiles_n * c->nst * c->items_max * c->nt;
     prep_w_k<<<(unsigned)((total + 127) / 128), 128>>>(p);
     g_umx_launches++;
+    c->wr = umx_conv_r_prepare(c, w_dev);
     UMX_CK("umx_conv_create");
     return c;
 }
@@ -380,8 +359,9 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
     nn_free(wd); nn_free(bd);
     return c;
 }
-extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); free(c); }
-extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * D * ceil_div(H, 16) * ceil_div(W, 8) * (size_t)(ceil_div(co, 32) * 32) * 2; }
+extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); free(c); }
+int umx_stats_chunks(int D, int H, int W);
+extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * umx_stats_chunks(D, H, W) * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
 extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags) {
     if (!umx_ready("umx_conv_fwd")) return -1;
@@ -406,7 +386,7 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     a.e.N = N; a.e.D = D; a.e.H = H; a.e.W = W; a.e.cop = c->cop; a.e.bias = c->bias_p;
     a.e.out_mode = out_mode; a.e.out_bits = out_bits; a.e.tconv = c->kind == UMX_TCONV2; a.e.co_real = c->co; a.e.cob_t = c->cob_t;
     a.e.nb_dst = nb_dst ? nb_dst : c->cob_t; a.e.b0 = nb_dst ? b0 : 0;
-    a.e.y = y; a.e.part = part; a.e.y_split = (flags & UMX_Y_SPLIT) != 0; a.err = umx_errflag();
+    a.e.y = y; a.e.y_split = (flags & UMX_Y_SPLIT) != 0; a.err = umx_errflag();
     if (!a.err) return -1;
     /* tensor map over the activation codes seen as 16-byte-wide planes [plane][z][y][x * 16 B]: fp8 in the split layout has two planes a
        block, fp4 one.  A box is (10 or 8 voxels) x (18 or 16 rows) x 1 plane of z x 2 planes; voxels outside the volume read as zero. */
@@ -429,13 +409,17 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * (c->taps == 27 ? 27.0 : 1.0);
     static int force_v1 = -1;
     if (force_v1 < 0) { const char *ev = getenv("UMX_CONV_V1"); force_v1 = ev && *ev && *ev != '0'; }
-    if (!force_v1 && umx_conv_r_fits(c)) {   /* resident weights: the persistent z-marching kernel */
+    /* InstanceNorm statistics are a separate pass over the stored output (umx_in_part below) */
+    if (!force_v1 && c->wr) {   /* resident weights: the persistent z-marching kernel, when the geometry allows */
         const int pid = umx_prof_open(flops);
-        const int rc = umx_conv_fwd_r(c, x, &m0, N, D, H, W, a.e);
-        umx_prof_close(pid);
-        g_umx_launches++;
-        UMX_CK("umx_conv_fwd");
-        return rc;
+        const int rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e);
+        if (rc <= 0) {
+            umx_prof_close(pid);
+            g_umx_launches++;
+            UMX_CK("umx_conv_fwd");
+            if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
+            return rc;
+        }
     }
     const size_t smem = 1024 + (size_t)a.ring * a.stage_bytes;
     static size_t smem_set[16];
@@ -452,5 +436,6 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     umx_prof_close(pid);
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");
+    if (part) umx_in_part(y, N, c->co, D, H, W, part);
     return 0;
 }

@@ -4,8 +4,8 @@
    (src/nn_xnet.cu:1565-1570, 1577-1620) with 32-channel UE8M0 blocks. */
 #include "mx_common.cuh"
 
-/* partial sums: part[((n * T + t) * Cop + c) * 2 + {0, 1}], T spatial tiles, Cop = C rounded up to 32.  One block per (c, n); the
-   tile sums are added in a fixed order (strided per thread, then a fixed tree), so the result does not depend on scheduling. */
+/* partial sums: part[((n * T + t) * Cop + c) * 2 + {0, 1}], T voxel chunks, Cop = C rounded up to 32.  One block per (c, n); the
+   chunk sums are added in a fixed order (strided per thread, then a fixed tree), so the result does not depend on scheduling. */
 __global__ void __launch_bounds__(256) in_coef_k(const double *__restrict__ part, int C, int Cop, int T, double S, const float *gamma, const float *beta, float eps, float *coef) {
     const int c = blockIdx.x, n = blockIdx.y;
     double s = 0.0, q = 0.0;
@@ -21,9 +21,44 @@ __global__ void __launch_bounds__(256) in_coef_k(const double *__restrict__ part
         coef[2 * ((size_t)n * C + c) + 1] = __fmaf_rn(-(float)m, a, beta ? beta[c] : 0.f);
     }
 }
+/* voxel chunks per (sample, channel) of the partial sums: about 2048 voxels each, at most 512 */
+int umx_stats_chunks(int D, int H, int W) { const size_t S = (size_t)D * H * W; const size_t t = S / 2048; return t < 1 ? 1 : t > 512 ? 512 : (int)t; }
+
+/* partial sums of chunk t of block blk of sample n of a blocked fp16 tensor: part[((n * T + t) * Cop + c) * 2 + {0, 1}].  A thread owns
+   one channel and every eighth voxel of the chunk (a warp reads one voxel's 64-byte row); the eight phases are added in a fixed order.
+   HBM-bound: reads 2 B per element. */
+__global__ void __launch_bounds__(256) in_part_k(const __half *__restrict__ y, size_t S, int T, double *__restrict__ part) {
+    const int t = blockIdx.x, blk = blockIdx.y, n = blockIdx.z, nb = gridDim.y, Cop = nb * 32;
+    const int c = threadIdx.x & 31, ph = threadIdx.x >> 5;
+    const size_t v0 = S * t / T, v1 = S * (t + 1) / T;
+    const __half *p = y + ((size_t)n * nb + blk) * S * 32 + c;
+    double s = 0.0, q = 0.0;
+    size_t v = v0 + ph;
+    for (; v + 24 < v1; v += 32) {   /* four loads in flight */
+        const float x0 = __half2float(p[v * 32]), x1 = __half2float(p[(v + 8) * 32]), x2 = __half2float(p[(v + 16) * 32]), x3 = __half2float(p[(v + 24) * 32]);
+        s += (double)x0; q += (double)x0 * x0; s += (double)x1; q += (double)x1 * x1; s += (double)x2; q += (double)x2 * x2; s += (double)x3; q += (double)x3 * x3;
+    }
+    for (; v < v1; v += 8) { const double x = (double)__half2float(p[v * 32]); s += x; q += x * x; }
+    __shared__ double ss[8][32], sq[8][32];
+    ss[ph][c] = s; sq[ph][c] = q;
+    __syncthreads();
+    if (ph == 0) {
+        for (int k = 1; k < 8; k++) { s += ss[k][c]; q += sq[k][c]; }
+        double *d = part + (((size_t)n * T + t) * Cop + blk * 32 + c) * 2;
+        d[0] = s; d[1] = q;
+    }
+}
+/* InstanceNorm partial sums of a stored blocked-fp16 conv output (what umx_conv_fwd runs after the conv when it is given `part`) */
+void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part) {
+    if (!umx_ready("umx_in_part")) return;
+    const int T = umx_stats_chunks(D, H, W);
+    in_part_k<<<dim3(T, (C + 31) / 32, N), 256>>>((const __half *)y, (size_t)D * H * W, T, part);
+    g_umx_launches++;
+    UMX_CK("umx_in_part");
+}
 extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef) {
     if (!umx_ready("umx_in_coef")) return;
-    const int T = D * ((H + 15) / 16) * ((W + 7) / 8), Cop = (C + 31) / 32 * 32;
+    const int T = umx_stats_chunks(D, H, W), Cop = (C + 31) / 32 * 32;
     in_coef_k<<<dim3(C, N), 256>>>(part, C, Cop, T, (double)D * H * W, gamma, beta, eps, coef);
     g_umx_launches++;
     UMX_CK("umx_in_coef");
