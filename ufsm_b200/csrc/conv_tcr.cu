@@ -24,6 +24,7 @@
 
 #ifdef UMX_KPROF
 #define KP(...) __VA_ARGS__
+#define KMAX(slot, dt, where) do { long long d_ = (dt); long long *q_ = a.prof + (size_t)blockIdx.x * 16 + (slot); if (d_ > q_[0]) { q_[0] = d_; q_[1] = (where); } } while (0)
 #else
 #define KP(...)
 #endif
@@ -61,6 +62,7 @@ static_assert(sizeof(StageRec) == 128, "stage record is 128 bytes");
 
 __device__ __forceinline__ void raise_r(const ConvRArgs &a, volatile int *abort_flag, int code, int stage) {
     if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)blockIdx.x; a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
+    if (!*abort_flag) atomicCAS(a.err + 4 + code, 0, stage + 1);   /* which roles gave up on their own (not because another raised the flag), and where */
     *abort_flag = 1;
     __threadfence_block();
 }
@@ -92,7 +94,9 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         fence_barrier_init();
         fence_proxy_async();
     }
+    KP(const long long ta0 = clock64();)
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols); tmem_relinquish(); }
+    KP(if (threadIdx.x == 32) { a.prof[(size_t)blockIdx.x * 16 + 14] = clock64() - ta0; })
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 for (int zi = zlo; zi <= zhi && ok; zi++) for (int ki = 0; ki < a.nki; ki++) {
                     KP(const long long pw0 = clock64();)
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 1, it); ok = false; break; }
-                    KP(p_wait += clock64() - pw0;)
+                    KP(p_wait += clock64() - pw0; KMAX(0, clock64() - pw0, it);)
                     /* the record: planes z = zi + 1 - dz for dz = 0, 1, 2 that belong to the job, as runs of consecutive TMEM slots */
                     StageRec *r = recs + s;
                     uint32_t nseg0 = 0, nseg = 0, nwait = 0, ncommit = 0;
@@ -146,7 +150,6 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 }
                 pcj += ze - zb;
             }
-            KP(if (a.prof && blockIdx.x == 0) { a.prof[0] = clock64() - p_t0; a.prof[1] = p_wait; a.prof[2] = it; })
         }
     } else if (warp == 1) {
         /* ---------------- MMA issue: follows the records; the common stage is straight-line code ---------------- */
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
             KP(const long long mw0 = clock64();)
             if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 2, it); ok = false; break; }
             if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 3, it); ok = false; break; }
-            KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
+            KP(const long long mw1 = clock64(); m_full += mw1 - mw0; if (lane == 0) KMAX(2, mw1 - mw0, it);)
             const StageRec *r = recs + s;
             const uint4 h0 = *(const uint4 *)r;                  /* counts, ki, last */
             const uint32_t counts = h0.x, nwait = (counts >> 16) & 0xffu;
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 if (nwait > 1 && !mbar_wait(r->wait[1][0], r->wait[1][1], abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 7, it); ok = false; break; }
             }
             tc_fence_after();
-            KP(const long long mw2 = clock64(); m_acce += mw2 - mw1;)
+            KP(const long long mw2 = clock64(); m_acce += mw2 - mw1; if (lane == 0) KMAX(4, mw2 - mw1, it);)
             if (lane == 0) {
                 const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes);
                 const uint32_t sfa_t = tmem + (uint32_t)a.sfa_base + (uint32_t)(it & 1) * 20u;
@@ -216,17 +219,17 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                                      idn | ((uint32_t)id << 4) | ((uint32_t)id << 29), 1u, sfa_t + 4 * q, sfb1 + (uint32_t)q * sfb_per_q);
                     }
                 }
+                /* read what is still needed from the record first: the commit below hands the stage, record included, back to the producer */
+                const uint32_t nc = counts >> 24, cb0 = r->commit[0], cb1 = r->commit[1];
+                if (nc > 0) umma_commit(cb0);
+                if (nc > 1) umma_commit(cb1);
                 umma_commit(bar_empty + 8 * s);
-                const uint32_t nc = counts >> 24;
-                if (nc > 0) umma_commit(r->commit[0]);
-                if (nc > 1) umma_commit(r->commit[1]);
             }
             __syncwarp();
-            KP(m_issue += clock64() - mw2;)
+            KP(m_issue += clock64() - mw2; if (lane == 0) KMAX(6, clock64() - mw2, it);)
             it++; if (++s == R) { s = 0; ph ^= 1; }
             if (h0.z) break;
         }
-        KP(if (a.prof && blockIdx.x == 0 && lane == 0) { a.prof[4] = clock64() - m_t0; a.prof[5] = m_full; a.prof[6] = m_acce; a.prof[7] = m_issue; })
     } else if (warp < 4) {
         /* ---------------- A scale layout: warp 2 takes the even stages, warp 3 the odd ones ----------------
            The TMA left 18 rows of a 32-byte window of scale bytes (two windows for fp4); row r of the tile needs, for tap (dy, dx), the
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 if (!my) continue;
                 KP(const long long gw0 = clock64();)
                 if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it); ok = false; break; }
-                KP(g_wait += clock64() - gw0;)
+                KP(g_wait += clock64() - gw0; if (lane == 0) KMAX(8 + 2 * sfw, clock64() - gw0, it);)
                 uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
                 const uint8_t *sw = stg + a.offSW;
                 uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
@@ -270,7 +273,6 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 if (lane == 0) mbar_arrive(bar_sf + 8 * cs);
             }
         }
-        KP(if (a.prof && blockIdx.x == 0 && warp == 2 && lane == 0) { a.prof[8] = clock64() - g_t0; a.prof[9] = g_wait; })
     } else {
         /* ---------------- epilogue: one output plane of one tile at a time ---------------- */
         const int q4 = warp & 3, r = q4 * 32 + lane, ry = r >> 3, rx = r & 7;
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 const int slot = NS - 1 - pcm;
                 KP(const long long ew0 = clock64();)
                 if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc); dead = true; break; }
-                KP(e_wait += clock64() - ew0;)
+                KP(e_wait += clock64() - ew0; if (threadIdx.x == 128) KMAX(12, clock64() - ew0, pc);)
                 tc_fence_after();
                 uint32_t rr[2][32];
                 tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(slot * a.nt), rr[0]);
@@ -304,7 +306,6 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 if (++pcm == NS) { pcm = 0; pph ^= 1; }
             }
         }
-        KP(if (a.prof && blockIdx.x == 0 && threadIdx.x == 128) { a.prof[12] = clock64() - e_t0; a.prof[13] = e_wait; a.prof[14] = pc; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -447,13 +448,14 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     }
     const int grid = a.njobs < slots ? a.njobs : slots;
 #ifdef UMX_KPROF
-    a.prof = (long long *)umx_ws(7, 256); cudaMemset(a.prof, 0, 256);
+    a.prof = (long long *)umx_ws(7, (size_t)grid * 128); cudaMemset(a.prof, 0, (size_t)grid * 128);
 #endif
     if (c->bits == 8) conv_mxr_k<8><<<grid, kThreadsR, smem>>>(*m0, ms, a); else conv_mxr_k<4><<<grid, kThreadsR, smem>>>(*m0, ms, a);
 #ifdef UMX_KPROF
-    { long long h[16]; cudaMemcpy(h, a.prof, 128, cudaMemcpyDeviceToHost);
-      fprintf(stderr, "kprof: producer total %lld wait %lld stages %lld | mma total %lld full %lld acce %lld issue %lld | gather total %lld wait %lld | epi total %lld wait %lld planes %lld | grid %d jobs %d zc %d ring %d slots %d tmem %d\n",
-              h[0], h[1], h[2], h[4], h[5], h[6], h[7], h[8], h[9], h[12], h[13], h[14], grid, a.njobs, a.zc, a.ring, a.nslot, a.tmem_cols); }
+    { static long long hb[512 * 16]; cudaMemcpy(hb, a.prof, (size_t)grid * 128, cudaMemcpyDeviceToHost);
+      const char *nm[8] = {"producer", "mma-full", "mma-slot", "mma-issue", "gather0", "gather1", "epilogue", "alloc"};
+      for (int k = 0; k < 8; k++) { long long best = -1; int bb = 0; for (int b = 0; b < grid; b++) if (hb[b * 16 + 2 * k] > best) { best = hb[b * 16 + 2 * k]; bb = b; }
+        if (best > 2000000) fprintf(stderr, "kprof: longest %s wait %lld cycles in block %d at %lld (grid %d jobs %d zc %d ring %d slots %d tmem %d nki %d nt %d)\n", nm[k], best, bb, hb[bb * 16 + 2 * k + 1], grid, a.njobs, a.zc, a.ring, a.nslot, a.tmem_cols, a.nki, a.nt); } }
 #endif
     return 0;
 }

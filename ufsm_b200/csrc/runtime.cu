@@ -89,11 +89,11 @@ int *umx_errflag(void) {
 }
 int umx_errflag_read(void) {
     int *f = umx_errflag(); if (!f) return -1;
-    int h[4] = {0, 0, 0, 0};
+    int h[16] = {0};
     cudaError_t e = cudaMemcpy(h, f, sizeof h, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { umx_latch("umx_errflag_read", e); return -1; }
     if (h[0]) {
-        char b[256]; snprintf(b, sizeof b, "conv kernel: bounded wait gave up (code %d, block %d, stage %d, info %d)", h[0], h[1], h[2], h[3]);
+        char b[384]; snprintf(b, sizeof b, "conv kernel: bounded wait gave up (code %d, block %d, stage %d, thread %d; per role 1 producer %d, 2 mma-tma %d, 3 mma-scales %d, 4 gather %d, 5 epilogue %d, 6 weights %d, 7 mma-slot %d)", h[0], h[1], h[2], h[3], h[5], h[6], h[7], h[8], h[9], h[10], h[11]);
         umx_latch_msg(b);
         cudaMemset(f, 0, 64);
     }
