@@ -85,6 +85,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+/* zero 32 consecutive columns of this warp's 32 TMEM lanes */
+__device__ __forceinline__ void tmem_zero32(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 ::"r"(taddr), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 /* ---- cheap descriptor arithmetic for the MMA issue loop: a descriptor is (hi << 32) | lo with lo = (address >> 4) | (lbo >> 4) << 16 and
    hi = (sbo >> 4) | version; moving the start address by b bytes adds b >> 4 to lo (shared memory is below 256 KB, so no carry) ---- */
