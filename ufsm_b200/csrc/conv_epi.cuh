@@ -7,6 +7,7 @@ struct umx_conv {
     int taps, nkb, nki, cop, cob_t, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
     uint8_t *wpk; float *bias_p;
     uint8_t *wr;                    /* weight image of the z-marching kernel, or NULL */
+    uint8_t *wp;                    /* weight image of the one-tap streaming kernel, or NULL */
 };
 
 struct EpiArgs {
@@ -67,4 +68,23 @@ __device__ __forceinline__ void epi_chunk(const EpiArgs &a, int n, int z, int oy
             if (a.out_mode == UMX_OUT_PM32) ((float *)a.y)[o] = v[k]; else ((__half *)a.y)[o] = __float2half_rn(v[k]);
         }
     }
+}
+
+/* ---- weight preparation shared by the conv kernels: where GEMM row `row`, tap `tap`, K block `kb`, element k comes from ---- */
+struct PrepArgs {
+    const float *w; uint8_t *wpk; const float *bias; float *bias_p;
+    int kind, co, ci, bits, cop, cob_t, nkb, nki, taps, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
+};
+__device__ __forceinline__ float prep_src(const PrepArgs &p, int row, int tap, int kb, int k) {
+    /* value of GEMM row `row`, tap `tap`, K block `kb`, element k (0 outside the real weights) */
+    if (kb >= p.nkb) return 0.f;
+    if (p.kind == UMX_CONV3) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + tap] : 0.f; }
+    if (p.kind == UMX_CONV1) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[(size_t)row * p.ci + ci] : 0.f; }
+    if (p.kind == UMX_DOWN2) {   /* K block = sub-voxel tap * blocks(ci) + block */
+        const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
+        return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 8 + t] : 0.f;
+    }
+    /* UMX_TCONV2: row = abc * (32 cob_t) + o, w [ci][co][8] */
+    const int abc = row / (32 * p.cob_t), o = row % (32 * p.cob_t), ci = kb * 32 + k;
+    return (o < p.co && ci < p.ci) ? p.w[((size_t)ci * p.co + o) * 8 + abc] : 0.f;
 }

@@ -236,23 +236,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
    codes, then the scale bytes in the TMEM scale layout (quad, lane, column, byte).  One thread per (column tile, stage, item, row).
    Quantisation per (row, tap, 32 input channels) as the reference's prep_w8_k / prep_w4_k (src/lp_f8fwd.cu:54-71,
    src/lp_f4fwd.cu:53-66). ---- */
-struct PrepArgs {
-    const float *w; uint8_t *wpk; const float *bias; float *bias_p;
-    int kind, co, ci, bits, cop, cob_t, nkb, nki, taps, nt, ntiles_n, nst, items_max, ipq, nquad, w_stage_bytes;
-};
-__device__ __forceinline__ float prep_src(const PrepArgs &p, int row, int tap, int kb, int k) {
-    /* value of GEMM row `row`, tap `tap`, K block `kb`, element k (0 outside the real weights) */
-    if (kb >= p.nkb) return 0.f;
-    if (p.kind == UMX_CONV3) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + tap] : 0.f; }
-    if (p.kind == UMX_CONV1) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[(size_t)row * p.ci + ci] : 0.f; }
-    if (p.kind == UMX_DOWN2) {   /* K block = sub-voxel tap * blocks(ci) + block */
-        const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
-        return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 8 + t] : 0.f;
-    }
-    /* UMX_TCONV2: row = abc * (32 cob_t) + o, w [ci][co][8] */
-    const int abc = row / (32 * p.cob_t), o = row % (32 * p.cob_t), ci = kb * 32 + k;
-    return (o < p.co && ci < p.ci) ? p.w[((size_t)ci * p.co + o) * 8 + abc] : 0.f;
-}
 __global__ void __launch_bounds__(128) prep_w_k(const PrepArgs p) {
     const size_t total = (size_t)p.ntiles_n * p.nst * p.items_max * p.nt;
     const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
@@ -313,6 +296,8 @@ int umx_conv_r_fits(const umx_conv *c);
 uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev);
 int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc, int N, int D, int H, int W, const EpiArgs &e);
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part);
+uint8_t *umx_conv_p_prepare(const umx_conv *c, const float *w_dev);
+int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, int H, int W, const EpiArgs &e);
 
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
@@ -344,6 +329,7 @@ static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev,
     prep_w_k<<<(unsigned)((total + 127) / 128), 128>>>(p);
     g_umx_launches++;
     c->wr = umx_conv_r_prepare(c, w_dev);
+    c->wp = umx_conv_p_prepare(c, w_dev);
     UMX_CK("umx_conv_create");
     return c;
 }
@@ -359,7 +345,7 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
     nn_free(wd); nn_free(bd);
     return c;
 }
-extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); free(c); }
+extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); free(c); }
 int umx_stats_chunks(int D, int H, int W);
 extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * umx_stats_chunks(D, H, W) * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
@@ -413,6 +399,17 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     if (!force_v1 && c->wr) {   /* resident weights: the persistent z-marching kernel, when the geometry allows */
         const int pid = umx_prof_open(flops);
         const int rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e);
+        if (rc <= 0) {
+            umx_prof_close(pid);
+            g_umx_launches++;
+            UMX_CK("umx_conv_fwd");
+            if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
+            return rc;
+        }
+    }
+    if (!force_v1 && c->wp) {   /* one tap, resident weights: the streaming kernel */
+        const int pid = umx_prof_open(flops);
+        const int rc = umx_conv_fwd_p(c, x, (void *)enc, N, D, H, W, a.e);
         if (rc <= 0) {
             umx_prof_close(pid);
             g_umx_launches++;

@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         fence_barrier_init();
         fence_proxy_async();
     }
+    KP(const long long ta0 = clock64(); long long tg0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg0));)
     if ((int)threadIdx.x < a.nt) bias_s[threadIdx.x] = a.e.bias[threadIdx.x];
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 it++; if (++s == R) { s = 0; ph ^= 1; }
                 if (last) break;
             }
-            KP({ long long *q = a.prof + (size_t)blockIdx.x * 32; q[18] = m_full; q[19] = m_acce; q[20] = m_issue; q[21] = clock64() - m_t0; })
+            KP({ long long *q = a.prof + (size_t)blockIdx.x * 32; q[18] = m_full; q[19] = m_acce; q[20] = m_issue; q[21] = clock64() - m_t0; q[28] = m_t0 - ta0; q[29] = clock64() - ta0; long long tg1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg1)); q[30] = tg1 - tg0; })
         }
     } else if (warp < 4) {
         /* ---------------- A scale layout: warp 2 takes the even stages, warp 3 the odd ones ----------------
@@ -490,9 +491,10 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     if (c->bits == 8) conv_mxr_k<8><<<grid, kThreadsR, smem>>>(*m0, ms, a); else conv_mxr_k<4><<<grid, kThreadsR, smem>>>(*m0, ms, a);
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
-      double t[12] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 12; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
-      fprintf(stderr, "kprof: grid %d units %lld ring %d slots %d tmem %d nki %d nt %d smem %zu | per block: stages %.0f planes %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f\n",
-              grid, a.units, a.ring, a.nslot, a.tmem_cols, a.nki, a.nt, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7]); }
+      double t[15] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 15; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
+      long long mx = 0; for (int b = 0; b < grid; b++) if (hb[b * 32 + 29] > mx) mx = hb[b * 32 + 29];
+      fprintf(stderr, "kprof: grid %d units %lld ring %d slots %d tmem %d nki %d nt %d smem %zu | per block: stages %.0f planes %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f | prologue %.0f block %.0f = %.0f ns (max block %lld clk)\n",
+              grid, a.units, a.ring, a.nslot, a.tmem_cols, a.nki, a.nt, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7], t[12], t[13], t[14], mx); }
 #endif
     return 0;
 }
