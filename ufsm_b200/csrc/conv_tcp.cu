@@ -13,16 +13,22 @@
    consecutive, so the tile is re-read from L2, not from HBM.  Accumulators alternate between TMEM slots; the epilogue is the
    generic one (bias, fp16 / MX / plane-major output, the transposed conv's scatter).
 
-   Roles (256 threads): warp 0 lane 0 producer, warp 1 lane 0 MMA issue (the warp allocates TMEM), warp 2 scale layout, warp 3
-   idle, warps 4-7 epilogue.  All waits are bounded as in conv_mx_k. */
+   Roles (384 threads): warp 0 lane 0 producer, warp 1 lane 0 MMA issue (the warp allocates TMEM), warp 2 scale layout, warp 3
+   idle, warps 4-11 epilogue (two groups).  All waits are bounded as in conv_mx_k. */
 #include "conv_epi.cuh"
 #include "tc_ptx.cuh"
 #include <stdlib.h>
 #include <string.h>
 
+#ifdef UMX_KPROF
+#define KP(...) __VA_ARGS__
+#else
+#define KP(...)
+#endif
+
 namespace {
 
-constexpr int kThreadsP = 256;
+constexpr int kThreadsP = 384;
 constexpr int kMaxSlotsP = 8;
 constexpr long long kWaitLimitP = 4000000000ll;
 
@@ -37,6 +43,8 @@ struct ConvPArgs {
     const uint8_t *wp;
     EpiArgs e;
     int *err;
+    long long *prof;
+    int dbg;
 };
 
 __device__ __forceinline__ void raise_p(const ConvPArgs &a, volatile int *abort_flag, int code, int stage) {
@@ -60,7 +68,7 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < R; i++) { mbar_init(bar_tma + 8 * i, 1); mbar_init(bar_sf + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-        for (int i = 0; i < kMaxSlotsP; i++) { mbar_init(bar_accf + 8 * i, 1); mbar_init(bar_acce + 8 * i, 128); }
+        for (int i = 0; i < kMaxSlotsP; i++) { mbar_init(bar_accf + 8 * i, 1); mbar_init(bar_acce + 8 * i, 8); }
         mbar_init(bar_w, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -80,11 +88,15 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
             for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wp + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
             int s = 0, ph = 0, it = 0; bool ok = true;
+            KP(long long p_wait = 0; const long long p_t0 = clock64();)
+            /* job = (row tile, column tile), column tile fastest; the indices advance incrementally (no division per job) */
+            int ntile = (int)(j0 % a.ntiles), n = (int)((j0 / a.ntiles) / a.rtiles_per_n), tin = (int)((j0 / a.ntiles) % a.rtiles_per_n);
             for (long long job = j0; job < j1 && ok; job++) {
-                const long long rt = job / a.ntiles; const int n = (int)(rt / a.rtiles_per_n); const long long tin = rt - (long long)n * a.rtiles_per_n;
-                const int cx = (int)(tin * 256), pl0 = BITS == 8 ? n * a.nkb * 2 : n * a.nkb, cs = (int)(tin * 128), pls = n * a.nkb;
+                const int cx = tin * 256, pl0 = BITS == 8 ? n * a.nkb * 2 : n * a.nkb, cs = tin * 128, pls = n * a.nkb;
                 for (int g = 0; g < a.ngroups; g++) {
+                    KP(const long long pw0 = clock64();)
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 1, it); ok = false; break; }
+                    KP(p_wait += clock64() - pw0;)
                     const int items = min(4, a.nki - 4 * g);
                     const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes), bar = bar_tma + 8 * s;
                     mbar_expect_tx(bar, (uint32_t)(items * 4096 + a.sw_rows * 128));
@@ -92,7 +104,9 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                     tma_load_2d(sb + a.offSW, &maps, bar, cs, pls + a.sw_rows * g);
                     it++; if (++s == R) { s = 0; ph ^= 1; }
                 }
+                if (++ntile == a.ntiles) { ntile = 0; if (++tin == (int)a.rtiles_per_n) { tin = 0; n++; } }
             }
+            KP(a.prof[(size_t)blockIdx.x * 32 + 16] = p_wait; a.prof[(size_t)blockIdx.x * 32 + 17] = clock64() - p_t0; a.prof[(size_t)blockIdx.x * 32 + 24] = it;)
         }
     } else if (warp == 1) {
         /* ---------------- MMA issue ---------------- */
@@ -110,14 +124,19 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             const uint32_t b_lo0 = desc_lo(wbase, (uint32_t)a.ntp * 16), b_item = 2u * (uint32_t)a.ntp, b_tile = (uint32_t)a.nki * b_item;
             int s = 0, ph = 0, it = 0, slot = 0, sph = 0;
             long long job = j0; int ntile = (int)(j0 % a.ntiles);
+            KP(long long m_full = 0, m_acce = 0, m_issue = 0; const long long m_t0 = clock64();)
             while (ok && job < j1) {
                 const int n_cur = min(a.ntp, a.cop - ntile * a.ntp);
                 const uint32_t idn = idesc_b | ((uint32_t)(n_cur >> 3) << 17), d = tmem + (uint32_t)(slot * a.ntp);
+                KP(const long long ma0 = clock64();)
                 if (!mbar_wait(bar_acce + 8 * slot, (uint32_t)(sph ^ 1), abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 7, it); break; }
+                KP(m_acce += clock64() - ma0;)
                 for (int g = 0; g < a.ngroups; g++) {
+                    KP(const long long mw0 = clock64();)
                     if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 3, it); ok = false; break; }
                     if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 2, it); ok = false; break; }
                     tc_fence_after();
+                    KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
                     const uint32_t a_lo = a_lo0 + (uint32_t)s * a_step, sfa_t = tmem + (uint32_t)a.sfa_base + ((uint32_t)it & 1u) * 8u;
                     const uint32_t sfb_t = tmem + (uint32_t)a.sfb_base + (uint32_t)((ntile * a.ngroups + g) * NQ * 4);
                     const uint32_t bb = b_lo0 + (uint32_t)ntile * b_tile + (uint32_t)(4 * g) * b_item;
@@ -133,18 +152,23 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                     }
                     if (g == a.ngroups - 1) umma_commit(bar_accf + 8 * slot);
                     umma_commit(bar_empty + 8 * s);
+                    KP(m_issue += clock64() - mw1;)
                     it++; if (++s == R) { s = 0; ph ^= 1; }
                 }
                 if (++slot == NS) { slot = 0; sph ^= 1; }
                 job++; if (++ntile == a.ntiles) ntile = 0;
             }
+            KP({ long long *q = a.prof + (size_t)blockIdx.x * 32; q[18] = m_full; q[19] = m_acce; q[20] = m_issue; q[21] = clock64() - m_t0; })
         }
     } else if (warp == 2) {
         /* ---------------- A scale layout: the window holds, per block of the stage, the scale bytes of the 128 rows ---------------- */
         int s = 0, ph = 0, it = 0; bool ok = true;
         const long long nst = (j1 - j0) * a.ngroups;
+        KP(long long g_wait = 0; const long long g_t0 = clock64();)
         for (long long i = 0; i < nst && ok; i++) {
+            KP(const long long gw0 = clock64();)
             if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitP)) { if (lane == 0) raise_p(a, abort_flag, 4, it); ok = false; break; }
+            KP(g_wait += clock64() - gw0;)
             uint8_t *stg = stages + (size_t)s * a.stage_bytes;
             const uint8_t *sw = stg + a.offSW;
             uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
@@ -161,36 +185,45 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             if (lane == 0) mbar_arrive(bar_sf + 8 * s);
             it++; if (++s == R) { s = 0; ph ^= 1; }
         }
+        KP(if (lane == 0) { a.prof[(size_t)blockIdx.x * 32 + 22] = g_wait; a.prof[(size_t)blockIdx.x * 32 + 25] = clock64() - g_t0; })
     } else if (warp >= 4) {
-        /* ---------------- epilogue ---------------- */
-        const int q4 = warp & 3, r = q4 * 32 + lane;
+        /* ---------------- epilogue: two groups of four warps; a job of two 32-column chunks gives one to each group, jobs of one chunk
+           alternate between the groups.  Both groups wait for and release every accumulator slot. ---------------- */
+        const int q4 = warp & 3, eg = (warp - 4) >> 2, r = q4 * 32 + lane;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
         int slot = 0, sph = 0, pc = 0; bool dead = false;
-        long long job = j0; int ntile = (int)(j0 % a.ntiles);
+        long long job = j0; int ntile = (int)(j0 % a.ntiles), n = (int)((j0 / a.ntiles) / a.rtiles_per_n), tin = (int)((j0 / a.ntiles) % a.rtiles_per_n);
+        const unsigned Su = (unsigned)a.S, HWu = (unsigned)a.HW, Wu = (unsigned)a.W;
+        KP(long long e_wait = 0, e_ld = 0, e_epi = 0; const long long e_t0 = clock64();)
         for (; job < j1 && !dead; job++, pc++) {
-            const long long rt = job / a.ntiles; const int n = (int)(rt / a.rtiles_per_n); const long long vo = (rt - (long long)n * a.rtiles_per_n) * 128 + r;
-            const bool row_ok = vo < a.S;
-            const int z = (int)(vo / a.HW), rem = (int)(vo - (long long)z * a.HW), oy = rem / a.W, ox = rem - oy * a.W;
             const int n_cur = min(a.ntp, a.cop - ntile * a.ntp), nchunk = n_cur >> 5;
+            const bool mine = nchunk > 1 ? true : (pc & 1) == eg;
+            const int jc = nchunk > 1 ? eg : 0;
+            KP(const long long ew0 = clock64();)
             if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)sph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 5, pc); dead = true; break; }
+            KP(const long long ew1 = clock64(); e_wait += ew1 - ew0;)
             tc_fence_after();
-            uint32_t rr[2][32];
-            const uint32_t tcol = tlane + (uint32_t)(slot * a.ntp);
-            tmem_ld32(tcol, rr[0]);
-            if (nchunk > 1) tmem_ld32(tcol + 32, rr[1]);
-            tmem_ld_wait();
+            uint32_t rr[32];
+            if (mine) { tmem_ld32(tlane + (uint32_t)(slot * a.ntp + jc * 32), rr); tmem_ld_wait(); }
             tc_fence_before();
-            mbar_arrive(bar_acce + 8 * slot);
-#pragma unroll
-            for (int jc = 0; jc < 2; jc++) if (jc < nchunk) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acce + 8 * slot);     /* one arrival per warp: arrivals on one barrier serialise */
+            KP(const long long ew2 = clock64(); e_ld += ew2 - ew1;)
+            if (mine) {
+                const unsigned vo = (unsigned)tin * 128u + (unsigned)r;
+                const bool row_ok = vo < Su;
+                const unsigned zu = vo / HWu, rem = vo - zu * HWu, oyu = rem / Wu;
                 float v[32];
 #pragma unroll
-                for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[jc][k]);
-                epi_chunk(a.e, n, z, oy, ox, row_ok, ntile * (a.ntp >> 5) + jc, v);
+                for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[k]);
+                KP(if (a.dbg & 1) { float sacc = 0.f; for (int k = 0; k < 32; k++) sacc += v[k]; if (sacc == 123.456f) ((float *)a.e.y)[0] = sacc; } else)
+                epi_chunk(a.e, n, (int)zu, (int)oyu, (int)(rem - oyu * Wu), (a.dbg & 2) ? false : row_ok, ntile * (a.ntp >> 5) + jc, v);
             }
+            KP(e_epi += clock64() - ew2;)
             if (++slot == NS) { slot = 0; sph ^= 1; }
-            if (++ntile == a.ntiles) ntile = 0;
+            if (++ntile == a.ntiles) { ntile = 0; if (++tin == (int)a.rtiles_per_n) { tin = 0; n++; } }
         }
+        KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; a.prof[(size_t)blockIdx.x * 32 + 28] = e_ld; a.prof[(size_t)blockIdx.x * 32 + 29] = e_epi; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -271,7 +304,7 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     PGeo g; ConvPArgs a; memset(&a, 0, sizeof a);
     const size_t S = (size_t)D * H * W;
-    if (!c->wp || !p_geometry(c, &g) || (S & 15)) return 1;       /* the scale plane's rows must be multiples of 16 bytes */
+    if (!c->wp || !p_geometry(c, &g) || (S & 15) || S > (size_t)1 << 30) return 1;       /* the scale plane's rows must be multiples of 16 bytes */
     a.N = N; a.nkb = c->nkb; a.nki = c->nki; a.bits = c->bits; a.cop = c->cop; a.ntp = g.ntp; a.ntiles = g.ntiles; a.ngroups = g.ngroups;
     a.S = (long long)S; a.rtiles_per_n = (long long)((S + 127) / 128); a.jobs = (long long)N * a.rtiles_per_n * g.ntiles; a.HW = H * W; a.W = W;
     a.w_codes = g.w_codes; a.w_bytes = g.w_bytes; a.nquad = g.nq;
@@ -311,6 +344,16 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     const long long slots = (long long)sms * (two ? 2 : 1);
     const int grid = (int)(a.jobs < slots ? a.jobs : slots);
     const size_t smem = (size_t)a.off_ring + (size_t)a.ring * a.stage_bytes;
+#ifdef UMX_KPROF
+    a.dbg = getenv("UMX_DBG") ? atoi(getenv("UMX_DBG")) : 0;
+    a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
+#endif
     if (c->bits == 8) conv_mxp_k<8><<<grid, kThreadsP, smem>>>(m0, ms, a); else conv_mxp_k<4><<<grid, kThreadsP, smem>>>(m0, ms, a);
+#ifdef UMX_KPROF
+    { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
+      double t[14] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 14; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
+      fprintf(stderr, "kprof-p: kind %d grid %d jobs %lld ring %d slots %d tmem %d nki %d ntp %d ntiles %d smem %zu | per block: stages %.0f jobs %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f ld %.0f epi %.0f\n",
+              c->kind, grid, a.jobs, a.ring, a.nslot, a.tmem_cols, a.nki, a.ntp, a.ntiles, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7], t[12], t[13]); }
+#endif
     return 0;
 }

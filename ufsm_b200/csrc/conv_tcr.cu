@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < R; i++) { mbar_init(bar_tma + 8 * i, 1); mbar_init(bar_sf + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-        for (int i = 0; i < kMaxSlots; i++) { mbar_init(bar_accf + 8 * i, 1); mbar_init(bar_acce + 8 * i, 128); }
+        for (int i = 0; i < kMaxSlots; i++) { mbar_init(bar_accf + 8 * i, 1); mbar_init(bar_acce + 8 * i, 4); }
         mbar_init(bar_w, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -292,7 +292,8 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         }
         tmem_st_wait();
         tc_fence_before();
-        for (int sl = 0; sl < NS; sl++) mbar_arrive(bar_acce + 8 * sl);
+        __syncwarp();
+        if (lane == 0) for (int sl = 0; sl < NS; sl++) mbar_arrive(bar_acce + 8 * sl);     /* one arrival per warp: arrivals on one barrier serialise */
         int pcm = 0, pph = 0, pc = 0; bool dead = false;        /* pcm = plane count mod slots, pph = its wrap parity */
         const size_t S = (size_t)a.D * a.H * a.W;
         KP(long long e_wait = 0; const long long e_t0 = clock64();)
@@ -315,7 +316,8 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                 if (nchunk > 1) tmem_zero32(tcol + 32);
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(bar_acce + 8 * slot);          /* the slot is free as soon as it is in registers and zeroed */
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acce + 8 * slot);          /* the slot is free as soon as it is in registers and zeroed */
                 if (a.fast_h16) {
                     /* fp16 blocked output [n][block][voxel][32]: bias, one rounding, four 16-byte stores per 32 channels */
                     if (row_ok) {

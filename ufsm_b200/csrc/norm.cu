@@ -21,38 +21,52 @@ __global__ void __launch_bounds__(256) in_coef_k(const double *__restrict__ part
         coef[2 * ((size_t)n * C + c) + 1] = __fmaf_rn(-(float)m, a, beta ? beta[c] : 0.f);
     }
 }
-/* voxel chunks per (sample, channel) of the partial sums: about 2048 voxels each, at most 512 */
-int umx_stats_chunks(int D, int H, int W) { const size_t S = (size_t)D * H * W; const size_t t = S / 2048; return t < 1 ? 1 : t > 512 ? 512 : (int)t; }
+/* voxel chunks per (sample, channel) of the partial sums: about 1024 voxels each, at most 2048 */
+int umx_stats_chunks(int D, int H, int W) { const size_t S = (size_t)D * H * W; const size_t t = S / 1024; return t < 1 ? 1 : t > 2048 ? 2048 : (int)t; }
 
 /* partial sums of chunk t of block blk of sample n of a blocked fp16 tensor: part[((n * T + t) * Cop + c) * 2 + {0, 1}].  A thread owns
-   one channel and every eighth voxel of the chunk (a warp reads one voxel's 64-byte row); the eight phases are added in a fixed order.
-   HBM-bound: reads 2 B per element. */
-__global__ void __launch_bounds__(256) in_part_k(const __half *__restrict__ y, size_t S, int T, double *__restrict__ part) {
+   eight channels (one 16-byte load) of every 64th voxel of the chunk, four loads in flight, so a warp reads 512 contiguous bytes per
+   load; the 64 phases are added in a fixed order.  fp64 throughout: sums of fp16 values and of their squares are then exact to the
+   last bits whatever the order.  HBM-bound: reads 2 B per element. */
+__global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, size_t S, int T, double *__restrict__ part) {
     const int t = blockIdx.x, blk = blockIdx.y, n = blockIdx.z, nb = gridDim.y, Cop = nb * 32;
-    const int c = threadIdx.x & 31, ph = threadIdx.x >> 5;
+    const int qd = threadIdx.x & 3, ph = threadIdx.x >> 2;
     const size_t v0 = S * t / T, v1 = S * (t + 1) / T;
-    const __half *p = y + ((size_t)n * nb + blk) * S * 32 + c;
-    double s = 0.0, q = 0.0;
+    const uint4 *p = y + ((size_t)n * nb + blk) * S * 4 + qd;
+    double s[8], q[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) { s[k] = 0.0; q[k] = 0.0; }
+    auto add = [&](const uint4 &r) {
+        const __half2 *h = (const __half2 *)&r;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(h[k]);
+            const double a = (double)f.x, b = (double)f.y;
+            s[2 * k] += a; q[2 * k] = fma(a, a, q[2 * k]); s[2 * k + 1] += b; q[2 * k + 1] = fma(b, b, q[2 * k + 1]);
+        }
+    };
     size_t v = v0 + ph;
-    for (; v + 24 < v1; v += 32) {   /* four loads in flight */
-        const float x0 = __half2float(p[v * 32]), x1 = __half2float(p[(v + 8) * 32]), x2 = __half2float(p[(v + 16) * 32]), x3 = __half2float(p[(v + 24) * 32]);
-        s += (double)x0; q += (double)x0 * x0; s += (double)x1; q += (double)x1 * x1; s += (double)x2; q += (double)x2 * x2; s += (double)x3; q += (double)x3 * x3;
+    for (; v + 192 < v1; v += 256) {
+        const uint4 r0 = __ldg(p + v * 4), r1 = __ldg(p + (v + 64) * 4), r2 = __ldg(p + (v + 128) * 4), r3 = __ldg(p + (v + 192) * 4);
+        add(r0); add(r1); add(r2); add(r3);
     }
-    for (; v < v1; v += 8) { const double x = (double)__half2float(p[v * 32]); s += x; q += x * x; }
-    __shared__ double ss[8][32], sq[8][32];
-    ss[ph][c] = s; sq[ph][c] = q;
+    for (; v < v1; v += 64) { const uint4 r0 = __ldg(p + v * 4); add(r0); }
+    __shared__ double ss[64][33], sq[64][33];
+#pragma unroll
+    for (int k = 0; k < 8; k++) { ss[ph][qd * 8 + k] = s[k]; sq[ph][qd * 8 + k] = q[k]; }
     __syncthreads();
-    if (ph == 0) {
-        for (int k = 1; k < 8; k++) { s += ss[k][c]; q += sq[k][c]; }
-        double *d = part + (((size_t)n * T + t) * Cop + blk * 32 + c) * 2;
-        d[0] = s; d[1] = q;
+    if (threadIdx.x < 64) {
+        const int c = threadIdx.x & 31; double (*src)[33] = threadIdx.x < 32 ? ss : sq;
+        double acc = 0.0;
+        for (int k = 0; k < 64; k++) acc += src[k][c];
+        part[(((size_t)n * T + t) * Cop + blk * 32 + c) * 2 + (threadIdx.x >> 5)] = acc;
     }
 }
 /* InstanceNorm partial sums of a stored blocked-fp16 conv output (what umx_conv_fwd runs after the conv when it is given `part`) */
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part) {
     if (!umx_ready("umx_in_part")) return;
     const int T = umx_stats_chunks(D, H, W);
-    in_part_k<<<dim3(T, (C + 31) / 32, N), 256>>>((const __half *)y, (size_t)D * H * W, T, part);
+    in_part_k<<<dim3(T, (C + 31) / 32, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part);
     g_umx_launches++;
     UMX_CK("umx_in_part");
 }
@@ -64,67 +78,74 @@ extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int 
     UMX_CK("umx_in_coef");
 }
 
+/* Four threads per voxel row, eight channels (one 16-byte load) each; a block walks a run of voxels of one (sample, block), so the
+   sixteen coefficients a thread needs stay in registers.  The row's amax is combined with two shuffles.  grid = (voxel chunks,
+   blocks, samples). */
 template <int BITS>
-__global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, const float2 *__restrict__ coef, int N, int C, int D, int H, int W, int act,
-                                                  uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout, int split) {
-    const int nb = (C + 31) / 32; const size_t S = (size_t)D * H * W, rows = (size_t)N * nb * S;
+__global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, const float2 *__restrict__ coef, int C, int D, int H, int W, int act,
+                                                  uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout, int split, int T) {
+    const int N = gridDim.z, nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z;
+    const size_t S = (size_t)D * H * W;
+    const int qd = threadIdx.x & 3, ph = threadIdx.x >> 2;
     constexpr int RB = 32 * BITS / 8;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t v = i % S; const int blk = (int)((i / S) % nb), n = (int)(i / (S * nb));
-        uint4 raw[4];
+    float ca[8], cb[8]; bool live[8];
 #pragma unroll
-        for (int j = 0; j < 4; j++) raw[j] = __ldg(x + i * 4 + j);
-        const __half2 *hp = (const __half2 *)raw;
-        float f[32];
+    for (int k = 0; k < 8; k++) {
+        const int c = blk * 32 + qd * 8 + k;
+        live[k] = c < C; ca[k] = 1.f; cb[k] = 0.f;
+        if (coef && live[k]) { const float2 ab = __ldg(coef + (size_t)n * C + c); ca[k] = ab.x; cb[k] = ab.y; }
+    }
+    const bool has_coef = coef != nullptr;
+    const size_t v0 = S * blockIdx.x / T, v1 = S * (blockIdx.x + 1) / T;
+    const uint4 *xp = x + ((size_t)n * nb + blk) * S * 4 + qd;
+    uint4 *hp_out = hout ? hout + ((size_t)n * nb + blk) * S * 4 + qd : nullptr;
+    const size_t drow = (size_t)n * nb_dst + b0 + blk;
+    for (size_t vb = v0; vb < v1; vb += 64) {
+        const size_t v = vb + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (ok) raw = __ldg(xp + v * 4);
+        const __half2 *hp = (const __half2 *)&raw;
+        float f[8]; uint4 o; __half2 *op = (__half2 *)&o;
 #pragma unroll
-        for (int k = 0; k < 16; k++) { const float2 t = __half22float2(hp[k]); f[2 * k] = t.x; f[2 * k + 1] = t.y; }
-#pragma unroll
-        for (int k = 0; k < 32; k++) {
-            const int c = blk * 32 + k;
-            float g = 0.f;
-            if (c < C) {
-                g = f[k];
-                if (coef) { const float2 ab = __ldg(coef + (size_t)n * C + c); g = __fmaf_rn(g, ab.x, ab.y); }
-                if (act == 2) g = g < 0.f ? __fmul_rn(0.01f, g) : g;
-                g = __half2float(__float2half_rn(g));
-            }
-            f[k] = g;
+        for (int k = 0; k < 4; k++) {
+            const float2 t = __half22float2(hp[k]);
+            float g0 = t.x, g1 = t.y;
+            if (has_coef) { g0 = __fmaf_rn(g0, ca[2 * k], cb[2 * k]); g1 = __fmaf_rn(g1, ca[2 * k + 1], cb[2 * k + 1]); }
+            if (act == 2) { g0 = g0 < 0.f ? __fmul_rn(0.01f, g0) : g0; g1 = g1 < 0.f ? __fmul_rn(0.01f, g1) : g1; }
+            if (!live[2 * k]) g0 = 0.f;
+            if (!live[2 * k + 1]) g1 = 0.f;
+            op[k] = __floats2half2_rn(g0, g1);
+            const float2 r = __half22float2(op[k]);
+            f[2 * k] = r.x; f[2 * k + 1] = r.y;
         }
-        if (hout) {
-            uint4 o[4]; __half2 *op = (__half2 *)o;
+        if (hp_out && ok) hp_out[v * 4] = o;
+        unsigned am = 0u;
 #pragma unroll
-            for (int k = 0; k < 16; k++) op[k] = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
-#pragma unroll
-            for (int j = 0; j < 4; j++) hout[i * 4 + j] = o[j];
-        }
-        unsigned w[8];
-        const unsigned sb = mx_encode_row32<BITS>(f, w);
+        for (int k = 0; k < 8; k++) am = amax_u(am, f[k]);
+        am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        const int e = mx_exp(__uint_as_float(am), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
+        const float m = exp2i(-e);
+        const unsigned sb = (unsigned)(e + 127) & 0xffu;
+        unsigned w0, w1 = 0u;
+        if (BITS == 8) { w0 = cvt_e4m3x4(f[0] * m, f[1] * m, f[2] * m, f[3] * m); w1 = cvt_e4m3x4(f[4] * m, f[5] * m, f[6] * m, f[7] * m); }
+        else w0 = cvt_e2m1x8(f, m);
+        if (!ok) continue;
         if (q) {
-            const size_t ro = ((size_t)n * nb_dst + b0 + blk) * S + v;
-            if (BITS == 8 && split) {
-                const size_t hp = ((size_t)n * nb_dst + b0 + blk) * 2;
-                *(uint4 *)(q + (hp * S + v) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(q + ((hp + 1) * S + v) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-                uint8_t *p = q + ro * RB;
-                ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            }
-            q[(size_t)N * nb_dst * S * RB + ro] = (uint8_t)sb;
+            if (BITS == 8 && split) *(uint2 *)(q + ((drow * 2 + (qd >> 1)) * S + v) * 16 + (qd & 1) * 8) = make_uint2(w0, w1);
+            else if (BITS == 8) *(uint2 *)(q + (drow * S + v) * 32 + qd * 8) = make_uint2(w0, w1);
+            else *(unsigned *)(q + (drow * S + v) * 16 + qd * 4) = w0;
+            if (qd == 0) q[(size_t)N * nb_dst * S * RB + drow * S + v] = (uint8_t)sb;
         }
         if (q2) {   /* space-to-depth copy: block (tap * nb + blk) at the coarse voxel */
-            const int xx = (int)(v % W), yy = (int)((v / W) % H), zz = (int)(v / ((size_t)W * H));
+            const unsigned vu = (unsigned)v, xx = vu % (unsigned)W, t1 = vu / (unsigned)W, yy = t1 % (unsigned)H, zz = t1 / (unsigned)H;
             const int tap = ((zz & 1) * 2 + (yy & 1)) * 2 + (xx & 1);
             const size_t Sc = S / 8, vc = ((size_t)(zz >> 1) * (H >> 1) + (yy >> 1)) * (W >> 1) + (xx >> 1);
-            const size_t ro = ((size_t)n * 8 * nb + tap * nb + blk) * Sc + vc;
-            if (BITS == 8 && split) {
-                const size_t hp = ((size_t)n * 8 * nb + tap * nb + blk) * 2;
-                *(uint4 *)(q2 + (hp * Sc + vc) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(q2 + ((hp + 1) * Sc + vc) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-                uint8_t *p = q2 + ro * RB;
-                ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                if (BITS == 8) ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            }
-            q2[(size_t)N * 8 * nb * Sc * RB + ro] = (uint8_t)sb;
+            const size_t ro = (size_t)n * 8 * nb + tap * nb + blk;
+            if (BITS == 8 && split) *(uint2 *)(q2 + ((ro * 2 + (qd >> 1)) * Sc + vc) * 16 + (qd & 1) * 8) = make_uint2(w0, w1);
+            else if (BITS == 8) *(uint2 *)(q2 + (ro * Sc + vc) * 32 + qd * 8) = make_uint2(w0, w1);
+            else *(unsigned *)(q2 + (ro * Sc + vc) * 16 + qd * 4) = w0;
+            if (qd == 0) q2[(size_t)N * 8 * nb * Sc * RB + ro * Sc + vc] = (uint8_t)sb;
         }
     }
 }
@@ -132,9 +153,14 @@ extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int
     if (!umx_ready("umx_in_apply")) return;
     if (q_s2d && ((D | H | W) & 1)) { fprintf(stderr, "umx_in_apply: the space-to-depth copy needs even D, H, W\n"); abort(); }
     const int nb = (C + 31) / 32; if (!nb_dst) { nb_dst = nb; b0 = 0; }
-    const size_t rows = (size_t)N * nb * D * H * W; size_t g = (rows + 255) / 256; if (g > 148u * 32u) g = 148u * 32u; if (!g) g = 1;
-    if (bits == 8) in_apply_k<8><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT);
-    else in_apply_k<4><<<(unsigned)g, 256>>>((const uint4 *)x, (const float2 *)coef, N, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT);
+    const size_t S = (size_t)D * H * W;
+    if (S >= ((size_t)1 << 31)) { fprintf(stderr, "umx_in_apply: more than 2^31 voxels per sample\n"); abort(); }
+    if (!S || !N) return;
+    /* runs of about 1024 voxels, enough blocks to fill the machine */
+    size_t T = (S + 1023) / 1024; if (T > 65535) T = 65535;
+    const dim3 grid((unsigned)T, (unsigned)nb, (unsigned)N);
+    if (bits == 8) in_apply_k<8><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT, (int)T);
+    else in_apply_k<4><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT, (int)T);
     g_umx_launches++;
     UMX_CK("umx_in_apply");
 }

@@ -20,10 +20,11 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
-    for (;;) {
+    for (int spins = 0;; spins++) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > limit) return false;
+        if (spins > 4) __nanosleep(64);      /* a long wait backs off so that polling warps leave the issue slots and the shared-memory pipe to the others */
     }
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
