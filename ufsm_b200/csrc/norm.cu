@@ -78,10 +78,15 @@ extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int 
     UMX_CK("umx_in_coef");
 }
 
+/* NaN-propagating max of magnitudes in one instruction */
+__device__ __forceinline__ float amax_nan(float a, float v) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(fabsf(v))); return r; }
+
 /* Four threads per voxel row, eight channels (one 16-byte load) each; a block walks a run of voxels of one (sample, block), so the
    sixteen coefficients a thread needs stay in registers.  The row's amax is combined with two shuffles.  grid = (voxel chunks,
-   blocks, samples). */
-template <int BITS>
+   blocks, samples).  This pass is bound by instruction issue (about ten instructions an element for the affine map, the
+   activation, two roundings and the MX encode), so the variants are compiled apart: COEF (affine map present), FULL (all 32
+   channels of every block are real), S2D (second, space-to-depth destination). */
+template <int BITS, bool COEF, bool FULL, bool S2D>
 __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, const float2 *__restrict__ coef, int C, int D, int H, int W, int act,
                                                   uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout, int split, int T) {
     const int N = gridDim.z, nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z;
@@ -92,62 +97,78 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int c = blk * 32 + qd * 8 + k;
-        live[k] = c < C; ca[k] = 1.f; cb[k] = 0.f;
-        if (coef && live[k]) { const float2 ab = __ldg(coef + (size_t)n * C + c); ca[k] = ab.x; cb[k] = ab.y; }
+        live[k] = FULL || c < C; ca[k] = 1.f; cb[k] = 0.f;
+        if (COEF && live[k]) { const float2 ab = __ldg(coef + (size_t)n * C + c); ca[k] = ab.x; cb[k] = ab.y; }
     }
-    const bool has_coef = coef != nullptr;
+    const float slope = act == 2 ? 0.01f : 1.f;           /* LeakyReLU as max(g, slope g); slope 1 leaves g as it is */
     const size_t v0 = S * blockIdx.x / T, v1 = S * (blockIdx.x + 1) / T;
     const uint4 *xp = x + ((size_t)n * nb + blk) * S * 4 + qd;
     uint4 *hp_out = hout ? hout + ((size_t)n * nb + blk) * S * 4 + qd : nullptr;
     const size_t drow = (size_t)n * nb_dst + b0 + blk;
-    for (size_t vb = v0; vb < v1; vb += 64) {
-        const size_t v = vb + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (ok) raw = __ldg(xp + v * 4);
-        const __half2 *hp = (const __half2 *)&raw;
-        float f[8]; uint4 o; __half2 *op = (__half2 *)&o;
+    /* destination of this thread's 8 (fp8) or 4 (fp4) code bytes of voxel v: base + v * stride */
+    uint8_t *qb = nullptr; int qs = 0;
+    if (q) {
+        if (BITS == 8 && split) { qb = q + (drow * 2 + (qd >> 1)) * S * 16 + (qd & 1) * 8; qs = 16; }
+        else if (BITS == 8) { qb = q + drow * S * 32 + qd * 8; qs = 32; }
+        else { qb = q + drow * S * 16 + qd * 4; qs = 16; }
+    }
+    uint8_t *qsc = q ? q + (size_t)N * nb_dst * S * RB + drow * S : nullptr;
+    for (size_t vb = v0; vb < v1; vb += 256) {
+        /* four rows a thread per trip, their loads issued together */
+        uint4 raws[4];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const float2 t = __half22float2(hp[k]);
-            float g0 = t.x, g1 = t.y;
-            if (has_coef) { g0 = __fmaf_rn(g0, ca[2 * k], cb[2 * k]); g1 = __fmaf_rn(g1, ca[2 * k + 1], cb[2 * k + 1]); }
-            if (act == 2) { g0 = g0 < 0.f ? __fmul_rn(0.01f, g0) : g0; g1 = g1 < 0.f ? __fmul_rn(0.01f, g1) : g1; }
-            if (!live[2 * k]) g0 = 0.f;
-            if (!live[2 * k + 1]) g1 = 0.f;
-            op[k] = __floats2half2_rn(g0, g1);
-            const float2 r = __half22float2(op[k]);
-            f[2 * k] = r.x; f[2 * k + 1] = r.y;
-        }
-        if (hp_out && ok) hp_out[v * 4] = o;
-        unsigned am = 0u;
+        for (int u = 0; u < 4; u++) { const size_t v = vb + u * 64 + ph; raws[u] = v < v1 ? __ldg(xp + v * 4) : make_uint4(0u, 0u, 0u, 0u); }
 #pragma unroll
-        for (int k = 0; k < 8; k++) am = amax_u(am, f[k]);
-        am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
-        am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
-        const int e = mx_exp(__uint_as_float(am), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
-        const float m = exp2i(-e);
-        const unsigned sb = (unsigned)(e + 127) & 0xffu;
-        unsigned w0, w1 = 0u;
-        if (BITS == 8) { w0 = cvt_e4m3x4(f[0] * m, f[1] * m, f[2] * m, f[3] * m); w1 = cvt_e4m3x4(f[4] * m, f[5] * m, f[6] * m, f[7] * m); }
-        else w0 = cvt_e2m1x8(f, m);
-        if (!ok) continue;
-        if (q) {
-            if (BITS == 8 && split) *(uint2 *)(q + ((drow * 2 + (qd >> 1)) * S + v) * 16 + (qd & 1) * 8) = make_uint2(w0, w1);
-            else if (BITS == 8) *(uint2 *)(q + (drow * S + v) * 32 + qd * 8) = make_uint2(w0, w1);
-            else *(unsigned *)(q + (drow * S + v) * 16 + qd * 4) = w0;
-            if (qd == 0) q[(size_t)N * nb_dst * S * RB + drow * S + v] = (uint8_t)sb;
-        }
-        if (q2) {   /* space-to-depth copy: block (tap * nb + blk) at the coarse voxel */
-            const unsigned vu = (unsigned)v, xx = vu % (unsigned)W, t1 = vu / (unsigned)W, yy = t1 % (unsigned)H, zz = t1 / (unsigned)H;
-            const int tap = ((zz & 1) * 2 + (yy & 1)) * 2 + (xx & 1);
-            const size_t Sc = S / 8, vc = ((size_t)(zz >> 1) * (H >> 1) + (yy >> 1)) * (W >> 1) + (xx >> 1);
-            const size_t ro = (size_t)n * 8 * nb + tap * nb + blk;
-            if (BITS == 8 && split) *(uint2 *)(q2 + ((ro * 2 + (qd >> 1)) * Sc + vc) * 16 + (qd & 1) * 8) = make_uint2(w0, w1);
-            else if (BITS == 8) *(uint2 *)(q2 + (ro * Sc + vc) * 32 + qd * 8) = make_uint2(w0, w1);
-            else *(unsigned *)(q2 + (ro * Sc + vc) * 16 + qd * 4) = w0;
-            if (qd == 0) q2[(size_t)N * 8 * nb * Sc * RB + ro * Sc + vc] = (uint8_t)sb;
+        for (int u = 0; u < 4; u++) {
+            const size_t v = vb + u * 64 + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
+            const __half2 *hp = (const __half2 *)&raws[u];
+            float f[8]; uint4 o; __half2 *op = (__half2 *)&o;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float2 t = __half22float2(hp[k]);
+                float g0 = t.x, g1 = t.y;
+                if (COEF) { g0 = __fmaf_rn(g0, ca[2 * k], cb[2 * k]); g1 = __fmaf_rn(g1, ca[2 * k + 1], cb[2 * k + 1]); }
+                g0 = g0 < 0.f ? __fmul_rn(slope, g0) : g0; g1 = g1 < 0.f ? __fmul_rn(slope, g1) : g1;
+                if (!FULL) { if (!live[2 * k]) g0 = 0.f; if (!live[2 * k + 1]) g1 = 0.f; }
+                op[k] = __floats2half2_rn(g0, g1);
+                const float2 r = __half22float2(op[k]);
+                f[2 * k] = r.x; f[2 * k + 1] = r.y;
+            }
+            if (hp_out && ok) hp_out[v * 4] = o;
+            float amf = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) amf = amax_nan(amf, f[k]);
+            unsigned am = __float_as_uint(amf) & 0x7fffffffu;
+            am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            const int e = mx_exp(__uint_as_float(am), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
+            const float m = exp2i(-e);
+            const unsigned sb = (unsigned)(e + 127) & 0xffu;
+            unsigned w0, w1 = 0u;
+            if (BITS == 8) { w0 = cvt_e4m3x4(f[0] * m, f[1] * m, f[2] * m, f[3] * m); w1 = cvt_e4m3x4(f[4] * m, f[5] * m, f[6] * m, f[7] * m); }
+            else w0 = cvt_e2m1x8(f, m);
+            if (!ok) continue;
+            if (qb) {
+                if (BITS == 8) *(uint2 *)(qb + v * qs) = make_uint2(w0, w1); else *(unsigned *)(qb + v * qs) = w0;
+                if (qd == 0) qsc[v] = (uint8_t)sb;
+            }
+            if (S2D) {   /* space-to-depth copy: block (tap * nb + blk) at the coarse voxel */
+                const unsigned vu = (unsigned)v, xx = vu % (unsigned)W, t1 = vu / (unsigned)W, yy = t1 % (unsigned)H, zz = t1 / (unsigned)H;
+                const int tap = ((zz & 1) * 2 + (yy & 1)) * 2 + (xx & 1);
+                const size_t Sc = S / 8, vc = ((size_t)(zz >> 1) * (H >> 1) + (yy >> 1)) * (W >> 1) + (xx >> 1);
+                const size_t ro = (size_t)n * 8 * nb + tap * nb + blk;
+                if (BITS == 8 && split) *(uint2 *)(q2 + ((ro * 2 + (qd >> 1)) * Sc + vc) * 16 + (qd & 1) * 8) = make_uint2(w0, w1);
+                else if (BITS == 8) *(uint2 *)(q2 + (ro * Sc + vc) * 32 + qd * 8) = make_uint2(w0, w1);
+                else *(unsigned *)(q2 + (ro * Sc + vc) * 16 + qd * 4) = w0;
+                if (qd == 0) q2[(size_t)N * 8 * nb * Sc * RB + ro * Sc + vc] = (uint8_t)sb;
+            }
         }
     }
+}
+template <int BITS, bool COEF, bool FULL>
+static void in_apply_launch(dim3 grid, const void *x, const float *coef, int C, int D, int H, int W, int act, void *q, int nb_dst, int b0, void *q_s2d, void *h, int split, int T) {
+    if (q_s2d) in_apply_k<BITS, COEF, FULL, true><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, split, T);
+    else in_apply_k<BITS, COEF, FULL, false><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, nullptr, (uint4 *)h, split, T);
 }
 extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout) {
     if (!umx_ready("umx_in_apply")) return;
@@ -159,8 +180,11 @@ extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int
     /* runs of about 1024 voxels, enough blocks to fill the machine */
     size_t T = (S + 1023) / 1024; if (T > 65535) T = 65535;
     const dim3 grid((unsigned)T, (unsigned)nb, (unsigned)N);
-    if (bits == 8) in_apply_k<8><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT, (int)T);
-    else in_apply_k<4><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, layout == UMX_LAYOUT_SPLIT, (int)T);
+    const int split = layout == UMX_LAYOUT_SPLIT, full = (C & 31) == 0;
+#define UMX_APPLY(B, CO, FU) in_apply_launch<B, CO, FU>(grid, x, coef, C, D, H, W, act, q, nb_dst, b0, q_s2d, h, split, (int)T)
+    if (bits == 8) { if (coef) { if (full) UMX_APPLY(8, true, true); else UMX_APPLY(8, true, false); } else { if (full) UMX_APPLY(8, false, true); else UMX_APPLY(8, false, false); } }
+    else { if (coef) { if (full) UMX_APPLY(4, true, true); else UMX_APPLY(4, true, false); } else { if (full) UMX_APPLY(4, false, true); else UMX_APPLY(4, false, false); } }
+#undef UMX_APPLY
     g_umx_launches++;
     UMX_CK("umx_in_apply");
 }

@@ -12,22 +12,26 @@ template <typename T> __device__ __forceinline__ float ld_as_f32(const T *p);
 template <> __device__ __forceinline__ float ld_as_f32<float>(const float *p) { return __ldg(p); }
 template <> __device__ __forceinline__ float ld_as_f32<__half>(const __half *p) { return __half2float(__ldg(p)); }
 
+/* grid = (voxel chunks, blocks, samples): no index division per row; consecutive threads take consecutive voxels, so the plane-major
+   reads and the row writes are both coalesced */
 template <int BITS, typename TI>
 __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw, int split) {
-    const int nb = (C + bw - 1) / bw, rb = bw * BITS / 8;
-    const size_t rows = (size_t)N * nb * S;
+    const int nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z, rb = bw * BITS / 8;
+    const size_t rows = (size_t)N * nb * S, row0 = ((size_t)n * nb + blk) * S;
     uint8_t *sc = y + rows * rb;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t v = i % S; const int blk = (int)((i / S) % nb), n = (int)(i / (S * nb));
+    const TI *xb = x + ((size_t)n * C + (size_t)blk * bw) * S;
+    const int nch = min(bw, C - blk * bw);
+    for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v < S; v += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = row0 + v;
         float r[32];
 #pragma unroll
-        for (int k = 0; k < 32; k++) { const int c = blk * bw + k; r[k] = (k < bw && c < C) ? ld_as_f32(x + ((size_t)n * C + c) * S + v) : 0.f; }
+        for (int k = 0; k < 32; k++) r[k] = k < nch ? ld_as_f32(xb + (size_t)k * S + v) : 0.f;
         unsigned w[8];
         const unsigned sb = mx_encode_row32<BITS>(r, w);
         uint8_t *p = y + i * rb;
         if (BITS == 8) {
             if (bw == 32 && split) {   /* two 16-byte planes per block: [n][blk][half][voxel][16 B] */
-                const size_t hp = (i / S) * 2;
+                const size_t hp = ((size_t)n * nb + blk) * 2;
                 *(uint4 *)(y + (hp * S + v) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(y + ((hp + 1) * S + v) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
             } else if (bw == 32) { ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]); ((uint4 *)p)[1] = make_uint4(w[4], w[5], w[6], w[7]); }
             else if (bw == 16) ((uint4 *)p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -71,8 +75,10 @@ static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bi
     if (!umx_ready(who)) return;
     if (dt != 0 && dt != 2) { fprintf(stderr, "%s: source type %d is not built (fp32 and fp16 only)\n", who, dt); abort(); }
     const int bw = mxbw(C, bwf);
-    const size_t rows = (size_t)N * ((C + bw - 1) / bw) * S;
-    const unsigned g = grid_for(rows);
+    const int nb = (C + bw - 1) / bw;
+    if (!S || !N) return;
+    size_t gx = (S + 255) / 256; if (gx > 148u * 16u) gx = 148u * 16u;
+    const dim3 g((unsigned)gx, (unsigned)nb, (unsigned)N);
     if (bits == 8) { if (dt == 2) pm_to_mx_k<8, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<8, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
     else { if (dt == 2) pm_to_mx_k<4, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<4, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
     g_umx_launches++;
