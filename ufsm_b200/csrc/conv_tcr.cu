@@ -41,7 +41,7 @@ constexpr long long kWaitLimitR = 4000000000ll;
 
 struct ConvRArgs {
     int N, D, H, W, nkb, nki, bits, nt;
-    int tiles_x, tiles;
+    int tiles_x, tiles, ncol, gcol;              /* column tiles of nt channels; blocks per column tile */
     long long units;                             /* N x tiles x D output planes of one tile, split evenly over the grid */
     int ring, stage_bytes, offSW, offSFA;
     int w_bytes, w_codes, nquad, gt, goff1, goff2, nslot;
@@ -87,7 +87,8 @@ template <int BITS> __device__ __forceinline__ void issue_group(uint32_t d, uint
 /* the block's piece of the plane list, u in [u0, u1) with u = (sample * tiles + tile) * D + z, cut into runs along z */
 struct Piece { long long u, u1; };
 __device__ __forceinline__ Piece piece_of_block(const ConvRArgs &a) {
-    Piece p; p.u = a.units * (long long)blockIdx.x / (long long)gridDim.x; p.u1 = a.units * ((long long)blockIdx.x + 1) / (long long)gridDim.x; return p;
+    const long long b = (long long)(blockIdx.x % a.gcol);      /* blocks [k gcol, (k + 1) gcol) share column tile k and split the plane list */
+    Piece p; p.u = a.units * b / (long long)a.gcol; p.u1 = a.units * (b + 1) / (long long)a.gcol; return p;
 }
 struct Run { int n, txy, zb, ze; };
 __device__ __forceinline__ Run next_run(const ConvRArgs &a, Piece &p) {
@@ -123,7 +124,8 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         fence_proxy_async();
     }
     KP(const long long ta0 = clock64(); long long tg0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg0));)
-    if ((int)threadIdx.x < a.nt) bias_s[threadIdx.x] = a.e.bias[threadIdx.x];
+    const int ctile = (int)blockIdx.x / a.gcol;
+    if ((int)threadIdx.x < a.nt) bias_s[threadIdx.x] = a.e.bias[ctile * a.nt + threadIdx.x];
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         if (lane == 0) {
             tma_prefetch_desc(&map0); tma_prefetch_desc(&maps);
             mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
-            for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wr + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
+            for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wr + (size_t)ctile * a.w_bytes + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
             const uint32_t nt = (uint32_t)a.nt, bstep9 = 9u * 2u * 3u * nt;            /* B descriptor step of one input block: nine taps of two halves of 3 nt rows */
             const uint32_t b_lo0 = desc_lo(smem_u32(wsm), 3u * nt * 16u);
             const uint32_t idesc_b = (BITS == 8 ? idesc_mxf8(0, 0, 0) : idesc_mxf4(0, 0, 0)), ntn = (nt >> 3) << 17;
@@ -324,7 +326,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                         const size_t vo = ((size_t)z * a.H + oy) * a.W + ox;
 #pragma unroll
                         for (int jc = 0; jc < 2; jc++) if (jc < nchunk) {
-                            uint4 *dst = (uint4 *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + jc) * S + vo) * 4;
+                            uint4 *dst = (uint4 *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * nchunk + jc) * S + vo) * 4;
                             const float4 *bs = (const float4 *)(bias_s + jc * 32);
 #pragma unroll
                             for (int k = 0; k < 4; k++) {
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                         float v[32];
 #pragma unroll
                         for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[jc][k]);
-                        epi_chunk(a.e, rn.n, z, oy, ox, row_ok, jc, v);
+                        epi_chunk(a.e, rn.n, z, oy, ox, row_ok, ctile * nchunk + jc, v);
                     }
                 }
                 if (++pcm == NS) { pcm = 0; pph ^= 1; }
@@ -368,11 +370,12 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
    4-column boundary of TMEM (a one-column offset faults with "misaligned address"), hence one re-based image per starting dz.
    Quantisation per (row, tap, 32 input channels) as the reference's prep_w8_k / prep_w4_k (src/lp_f8fwd.cu:54-71, src/lp_f4fwd.cu:53-66).
    One thread per (item, dy dx, dz, channel). */
-__global__ void __launch_bounds__(128) prep_wr_k(const float *__restrict__ w, uint8_t *__restrict__ wr, int co, int ci, int bits, int nt, int nkb, int nki, int nquad, int gt, int goff1, int goff2, int w_codes) {
+__global__ void __launch_bounds__(128) prep_wr_k(const float *__restrict__ w, uint8_t *__restrict__ wr_all, int co, int ci, int bits, int nt, int nkb, int nki, int nquad, int gt, int goff1, int goff2, int w_codes, int w_bytes) {
     const int total = nki * 9 * 3 * nt, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int c = i % nt, dz = (i / nt) % 3, j = (i / (3 * nt)) % 9, ki = i / (27 * nt);
-    const int tap = dz * 9 + j, R3 = 3 * nt, row = dz * nt + c;
+    uint8_t *wr = wr_all + (size_t)blockIdx.y * w_bytes;      /* one image per column tile */
+    const int cl = i % nt, c = blockIdx.y * nt + cl, dz = (i / nt) % 3, j = (i / (3 * nt)) % 9, ki = i / (27 * nt);
+    const int tap = dz * 9 + j, R3 = 3 * nt, row = dz * nt + cl;
     unsigned wd[8], sb[2] = {127u, 127u};
     float v[32];
     if (bits == 8) {
@@ -404,34 +407,43 @@ __global__ void __launch_bounds__(128) prep_wr_k(const float *__restrict__ w, ui
 
 /* geometry of the weight image; 0 when the z-marching kernel cannot run this conv (3^3 only, one column tile of at most 64 channels,
    codes + scales resident in shared memory, B scales resident in TMEM beside at least four accumulator slots) */
-struct RGeo { int w_codes, w_bytes, gt, goff1, goff2, tmem_cols, nslot, sfa_base, sfa_cols, sfb_base; };
-static int r_geometry(const umx_conv *c, RGeo *g) {
-    if (c->kind != UMX_CONV3 || c->ntiles_n != 1 || c->nt > 64) return 0;
-    const int g0 = (3 * c->nt + 127) / 128, g1 = (2 * c->nt + 127) / 128, g2 = (c->nt + 127) / 128;
+struct RGeo { int nt, ncol, w_codes, w_bytes, gt, goff1, goff2, tmem_cols, nslot, sfa_base, sfa_cols, sfb_base; };
+static int r_geometry_nt(const umx_conv *c, int nt, RGeo *g) {
+    if (c->cop % nt) return 0;
+    g->nt = nt; g->ncol = c->cop / nt;
+    const int g0 = (3 * nt + 127) / 128, g1 = (2 * nt + 127) / 128, g2 = (nt + 127) / 128;
     g->goff1 = g0; g->goff2 = g0 + g1; g->gt = g0 + g1 + g2;
-    g->w_codes = c->nki * 9 * 2 * 3 * c->nt * 16;
+    g->w_codes = c->nki * 9 * 2 * 3 * nt * 16;
     g->w_bytes = g->w_codes + c->nki * c->nquad * g->gt * 512;
     if (g->w_bytes > 136 * 1024) return 0;
     g->sfa_cols = c->nquad * 4;
     const int fixed = 2 * g->sfa_cols + c->nki * c->nquad * g->gt * 4;
     /* 256 columns (two blocks a multiprocessor) when that leaves four slots, else the whole 512 */
-    g->tmem_cols = (256 - fixed) / c->nt >= 4 ? 256 : 512;
-    g->nslot = (g->tmem_cols - fixed) / c->nt;
+    g->tmem_cols = (256 - fixed) / nt >= 4 ? 256 : 512;
+    g->nslot = (g->tmem_cols - fixed) / nt;
     if (g->nslot > kMaxSlots) g->nslot = kMaxSlots;
     if (g->nslot < 4) return 0;
-    g->sfa_base = g->nslot * c->nt; g->sfb_base = g->sfa_base + 2 * g->sfa_cols;
+    g->sfa_base = g->nslot * nt; g->sfb_base = g->sfa_base + 2 * g->sfa_cols;
     return 1;
+}
+/* the widest column tile (64 or 32 channels) whose weight image fits; wider layers run as several column tiles, each on its own
+   share of the blocks (the input is then read once per column tile, from L2 when it fits there) */
+static int r_geometry(const umx_conv *c, RGeo *g) {
+    if (c->kind != UMX_CONV3) return 0;
+    if (c->cop <= 64 && r_geometry_nt(c, c->cop, g)) return 1;
+    if (r_geometry_nt(c, 64, g)) return 1;
+    return r_geometry_nt(c, 32, g);
 }
 int umx_conv_r_fits(const umx_conv *c) { RGeo g; return r_geometry(c, &g); }
 /* builds the weight image from device fp32 weights [co][ci][27]; called once when the conv is created */
 uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev) {
     RGeo g;
     if (!r_geometry(c, &g)) return nullptr;
-    uint8_t *wr = (uint8_t *)nn_malloc((size_t)g.w_bytes);
+    uint8_t *wr = (uint8_t *)nn_malloc((size_t)g.w_bytes * g.ncol);
     if (!wr) return nullptr;
-    cudaMemset(wr, 127, (size_t)g.w_bytes);
-    const int total = c->nki * 27 * c->nt;
-    prep_wr_k<<<(total + 127) / 128, 128>>>(w_dev, wr, c->co, c->ci, c->bits, c->nt, c->nkb, c->nki, c->nquad, g.gt, g.goff1, g.goff2, g.w_codes);
+    cudaMemset(wr, 127, (size_t)g.w_bytes * g.ncol);
+    const int total = c->nki * 27 * g.nt;
+    prep_wr_k<<<dim3((total + 127) / 128, g.ncol), 128>>>(w_dev, wr, c->co, c->ci, c->bits, g.nt, c->nkb, c->nki, c->nquad, g.gt, g.goff1, g.goff2, g.w_codes, g.w_bytes);
     g_umx_launches++;
     return wr;
 }
@@ -445,7 +457,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     if (!r_geometry(c, &g) || !c->wr || (W & 15)) return 1;      /* the scale window needs rows that are multiples of 16 bytes */
     a.w_codes = g.w_codes; a.w_bytes = g.w_bytes; a.gt = g.gt; a.goff1 = g.goff1 * 4; a.goff2 = g.goff2 * 4;   /* TMEM column offsets of the dz >= 1, 2 images */
     a.tmem_cols = g.tmem_cols; a.nslot = g.nslot; a.sfa_base = g.sfa_base; a.sfa_cols = g.sfa_cols; a.sfb_base = g.sfb_base;
-    a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.bits = c->bits; a.nt = c->nt;
+    a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.bits = c->bits; a.nt = g.nt; a.ncol = g.ncol;
     a.tiles_x = (W + 7) / 8; a.tiles = a.tiles_x * ((H + 15) / 16);
     a.units = (long long)N * a.tiles * D;
     a.nquad = c->nquad;
@@ -465,8 +477,10 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     const int room = (two ? 113 : 227) * 1024 - a.off_ring;
     a.ring = room / a.stage_bytes; if (a.ring > 12) a.ring = 12;
     if (a.ring < 3) return 1;
-    const long long slots = (long long)sms * (two ? 2 : 1);
-    const int grid = (int)(a.units < slots ? a.units : slots);
+    const long long slots = (long long)sms * (two ? 2 : 1) / g.ncol;      /* blocks per column tile */
+    if (slots < 1) return 1;
+    a.gcol = (int)(a.units < slots ? a.units : slots);
+    const int grid = a.gcol * g.ncol;
     const size_t S = (size_t)D * H * W;
     uint8_t *x_sc = (uint8_t *)x + (size_t)N * c->nkb * S * (c->bits == 8 ? 32 : 16);   /* the scale plane follows the codes in either layout */
     CUtensorMap ms; memset(&ms, 0, sizeof ms);
