@@ -37,31 +37,65 @@ def peaks():
 
 
 class Clocks(threading.Thread):
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML; nvidia-smi as a fallback)."""
 
-    def __init__(self, gpu):
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, gpu, interval=0.1):
         super().__init__(daemon=True)
-        self.gpu, self.rows, self.stop = gpu, [], False
+        self.gpu, self.rows, self.stop, self.max_mhz, self.interval = gpu, [], False, None, interval
+        self.ready = threading.Event()          # set once the sampler is initialised (NVML start-up stalls kernel launches for tens of ms)
+        self.t_on = None                         # samples before this time (warm-up) are dropped
         self.q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
+    def _nvml(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = int(vis.split(",")[self.gpu]) if vis and all(t.strip().isdigit() for t in vis.split(",")) else self.gpu
+        self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(idx)
+        self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        self.bits = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown, nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+
+    def sample_once(self):
+        """One sample from the calling thread (used while the timed steps are queued on the GPU, so that a short run has one too)."""
+        if getattr(self, "nv", None) is None:
+            return
+        try:
+            r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            self.rows.append([self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)] + [bool(r & b) for b in self.bits])
+        except Exception:
+            pass
+
     def run(self):
+        try:
+            self._nvml()
+            self.ready.set()
+            while not self.stop:
+                if self.t_on is not None:
+                    self.sample_once()
+                time.sleep(self.interval)
+            return
+        except Exception:
+            self.nv = None
+        self.ready.set()
         while not self.stop:
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.q, "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
                 f = [t.strip() for t in out.strip().split(",")]
-                if len(f) >= 6:
-                    self.rows.append(f)
+                if len(f) >= 6 and f[0].isdigit() and self.t_on is not None:
+                    self.max_mhz = int(f[1]) if f[1].isdigit() else self.max_mhz
+                    self.rows.append([int(f[0])] + [t.lower().startswith("active") for t in f[2:6]])
             except Exception:
                 pass
             time.sleep(0.1)
 
     def summary(self):
         if not self.rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None, "reasons": reasons, "samples": len(self.rows)}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"], "samples": 0}
+        sm = sorted(r[0] for r in self.rows)
+        reasons = [n for i, n in enumerate(self.NAMES) if any(r[1 + i] for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.rows)}
 
 
 def cpu_sample(steps, warmup):
@@ -130,17 +164,20 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    clk = Clocks(local, args.clock_interval)
+    clk.start()
+    clk.ready.wait(20)
     for _ in range(args.warmup):
         L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
     ufsm_b200.check()
-    clk = Clocks(local)
-    clk.start()
+    clk.t_on = time.time()
     # ---- device-resident: K steps, events on the launching stream, barrier + synchronise on both sides, max over ranks
     barrier()
     n0 = L.umx_launch_count()
     L.umx_timer_start(timer)
     for _ in range(args.steps):
         L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
+    clk.sample_once()
     ms = L.umx_timer_stop_ms(timer)
     launches = L.umx_launch_count() - n0
     barrier()
@@ -154,22 +191,43 @@ def run_gpu(args):
         L.umx_unet_forward_host(u.h, hin, B, hout)
     ms_e2e = tmax(L.umx_timer_stop_ms(timer))
     barrier()
+    # ---- per-launch times of the conv kernels, measured live with events around every conv launch of K more steps
+    names = []
+    for l in range(5):
+        names += ["enc%d.c1" % l, "enc%d.c2" % l] + (["down%d" % l] if l < 4 else [])
+    for l in range(3, -1, -1):
+        names += ["up%d" % l, "dec%d.c1" % l, "dec%d.c2" % l]
+    names += ["head"]
+    per = {n: [0.0, 0.0] for n in names}
+    ms_conv, fl_conv, n_conv = 0.0, 0.0, 0
+    t_ms, t_fl = C.c_double(0), C.c_double(0)
+    psteps = min(args.steps, 20)
+    for _ in range(psteps):
+        L.umx_prof_begin()
+        L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
+        n_conv = L.umx_prof_end(C.byref(t_ms), C.byref(t_fl))
+        ms_conv += t_ms.value
+        fl_conv += t_fl.value
+        if n_conv == len(names):
+            for i, nm in enumerate(names):
+                L.umx_prof_get(i, C.byref(t_ms), C.byref(t_fl))
+                per[nm][0] += t_ms.value
+                per[nm][1] += t_fl.value
     clk.stop = True
     clk.join(2)
-    # ---- per-launch time of the dominant kernel (the tcgen05 conv), measured live with events around every conv launch
-    ms_conv, fl_conv = C.c_double(0), C.c_double(0)
-    L.umx_prof_begin()
-    for _ in range(args.steps):
-        L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
-    n_conv = L.umx_prof_end(C.byref(ms_conv), C.byref(fl_conv))
     ufsm_b200.check()
     if rank != 0:
         return
     pk = peaks()
     vox = world * B * S * args.steps
     flops_patch = L.umx_unet_flops(C.byref(cfg))
-    achieved = fl_conv.value / (ms_conv.value * 1e-3) / 1e12 if ms_conv.value > 0 else None
     peak = 2.0 * pk["bf16_sustained"]
+    # the dominant kernel: conv_mxr_k on the 3^3 32 -> 32 conv of level 0 (enc0.c2), the shape of the committed profiler capture
+    dom = per["enc0.c2"]
+    achieved = dom[1] / (dom[0] * 1e-3) / 1e12 if dom[0] > 0 else None
+    l0 = [per[k] for k in ("enc0.c2", "dec0.c1", "dec0.c2")]
+    l0_tf = sum(v[1] for v in l0) / (sum(v[0] for v in l0) * 1e-3) / 1e12 if l0[0][0] > 0 else None
+    all_tf = fl_conv / (ms_conv * 1e-3) / 1e12 if ms_conv > 0 else None
     line = {
         "metric": "unet_inference_voxels_per_s", "value": vox / (ms * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
@@ -177,10 +235,14 @@ def run_gpu(args):
                    "l2": "per-step working set (69 MB per level-0 tensor, > 1 GB touched) exceeds the 126 MB L2", "conv_tflops_whole_step": world * B * flops_patch * args.steps / (ms * 1e-3) / 1e12},
         "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "h2d_bytes_per_step": B * S, "d2h_bytes_per_step": B * NH * S * 2, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clk.summary(),
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None, "traffic": None,
-                     "kernel": "conv_mx_k (all %d conv launches of a step: algorithmic 2*V*Cin*Cout*taps FLOPs / summed event time)" % (n_conv // max(args.steps, 1)),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
+                     "traffic": 229985536 * B,
+                     "kernel": "conv_mxr_k, 3^3 conv 32 -> 32 on 128^3 (enc0.c2): algorithmic 2*V*Cin*Cout*27 FLOPs / event time of that launch, mean of %d steps" % psteps,
                      "peak_note": "2 x the %s bf16 sustained cuBLAS rate (fp8 runs at twice bf16); nominal dense fp8 4500" % pk["which"], "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
-                     "conv_share_of_step": ms_conv.value / max(args.steps, 1) / (ms / args.steps)},
+                     "traffic_note": "dram read + write bytes of one launch of this shape from the committed ncu capture (algorithmic: 69 MB MX in + 134 MB fp16 out)",
+                     "level0_3x3x3_tflops": l0_tf, "all_conv_launches_tflops": all_tf, "conv_launches_per_step": n_conv,
+                     "conv_share_of_step": ms_conv / max(psteps, 1) / (ms / args.steps)},
+        "conv_layers_us": {k: round(v[0] / psteps * 1e3, 1) for k, v in per.items()},
     }
     if world == 1 and not args.no_cpu:
         v, dt, cores = cpu_sample(1, 0)
@@ -194,10 +256,11 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ufsm_b200")
+    ap.add_argument("--clock-interval", type=float, default=0.05, help="seconds between clock samples (NVML queries share a lock with kernel launches, so not too often)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
     if args.impl == "reference":
