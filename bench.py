@@ -100,6 +100,8 @@ class Clocks(threading.Thread):
 
 def cpu_sample(steps, warmup):
     """The oracle's forward of the same network on one full 128^3 patch, all host threads."""
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1; the oracle's OpenMP runtime reads it when loaded)
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import orc
     import synth
     Ps = P
