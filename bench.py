@@ -185,12 +185,17 @@ def run_gpu(args):
     barrier()
     ms = tmax(ms)
     # ---- end to end through the host entry: uint8 patches in pinned memory -> fp16 logits in pinned memory, every step
-    for _ in range(min(args.warmup, 2)):
-        L.umx_unet_forward_host(u.h, hin, B, hout)
+    # (the queued form of the host entry: each step uploads its own patch and downloads its own logits; the copies of one step overlap
+    # the forward of the next; two result buffers so that a step's logits stay readable while the next step runs)
+    hout2 = L.nn_malloc_host(B * NH * S * 2)
+    for i in range(max(2, min(args.warmup, 4))):
+        L.umx_unet_submit_host(u.h, hin, B, hout if i & 1 else hout2)
+    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
     barrier()
     L.umx_timer_start(timer)
-    for _ in range(args.steps):
-        L.umx_unet_forward_host(u.h, hin, B, hout)
+    for i in range(args.steps):
+        L.umx_unet_submit_host(u.h, hin, B, hout if i & 1 else hout2)
+    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
     ms_e2e = tmax(L.umx_timer_stop_ms(timer))
     barrier()
     # ---- per-launch times of the conv kernels, measured live with events around every conv launch of K more steps

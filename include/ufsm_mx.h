@@ -41,6 +41,14 @@ void nn_d2h(void *dst, const void *src, size_t bytes);
 void nn_sync(void);
 const char *nn_check(void);              /* NULL, or the first error since the last call (same latch as lp_check) */
 const char *lp_check(void);              /* src/nn_lp.h:172 */
+void *umx_stream_new(void);               /* non-blocking copy stream, events and stream-ordered copies used by umx_unet_submit_host */
+void umx_stream_free(void *stream);
+void *umx_event_new(void);
+void umx_event_free(void *ev);
+void umx_event_record(void *ev, void *stream);           /* stream NULL: the legacy default stream */
+void umx_stream_wait(void *stream, void *ev);
+void umx_stream_sync(void *stream);
+void umx_copy_async(void *dst, const void *src, size_t bytes, int to_device, void *stream);
 void *nn_malloc_host(size_t bytes);      /* pinned host memory (cudaHostAlloc) for the window scheduler's staging buffers */
 void nn_free_host(void *p);
 
@@ -133,6 +141,11 @@ int umx_unet_forward_h16(umx_unet *u, const void *x_dev, int N, void *logits_dev
 /* the call a user of the library makes: uint8 CT patches [N][P^3] on the host (pinned or pageable) -> fp16 logits [N][nh][P^3] on the
    host; copies in, converts (x / 255 -> fp16), runs, copies out, synchronises.  0, or -1 with the message in lp_check(). */
 int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host);
+/* the same work, queued: returns once copies and kernels are enqueued; the upload of this call's patches and the download of its logits
+   overlap the forward of the neighbouring calls (two slots in flight).  Pinned host buffers, valid (and the logits unread) until
+   umx_unet_wait returns.  No counterpart in the reference, whose predict overlaps I/O with a reader thread (src/predict.c:1772-1841). */
+int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host);
+int umx_unet_wait(umx_unet *u);
 double umx_unet_flops(const umx_unet_cfg *cfg);                  /* 2 V_out C_in C_out taps summed over the convs, per patch */
 long umx_unet_launches(const umx_unet *u);                       /* kernels launched by the library since this object was created */
 long umx_launch_count(void);                                     /* kernels launched by the library in this process */

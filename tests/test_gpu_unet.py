@@ -54,6 +54,31 @@ def test_unet_batch_and_determinism(dev):
     u.free()
 
 
+def test_unet_queued_host_entry(dev):
+    """umx_unet_submit_host / umx_unet_wait: five patches in flight through the two slots give the bytes of the synchronous entry."""
+    import ctypes as C
+    import ufsm_b200
+    L = G.L()
+    P, cw, n = 32, [32, 64], 5
+    u = G.Unet(G.make_cfg(P, cw), synth.unet_weights(11, cw), 1)
+    S, nh = P ** 3, 7
+    cts = [synth.ct_u8(20 + i, S) for i in range(n)]
+    want = [u.forward_host(c, 1) for c in cts]
+    hin, hout = L.nn_malloc_host(n * S), L.nn_malloc_host(n * nh * S * 2)
+    for i, c in enumerate(cts):
+        C.memmove(hin + i * S, c.ctypes.data, S)
+    C.memset(hout, 0xEE, n * nh * S * 2)
+    for i in range(n):
+        assert L.umx_unet_submit_host(u.h, hin + i * S, 1, hout + i * nh * S * 2) == 0
+    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
+    got = np.ctypeslib.as_array((C.c_uint16 * (n * nh * S)).from_address(hout)).view(np.float16).reshape(n, -1)
+    for i in range(n):
+        assert np.array_equal(got[i], want[i]), i
+    L.nn_free_host(hin)
+    L.nn_free_host(hout)
+    u.free()
+
+
 def test_unet_full_size_properties(dev):
     """Configuration 3 (128^3 patch, widths 32/64/128/256/320): finite, deterministic, and translation-consistent in the batch."""
     P, cw = 128, [32, 64, 128, 256, 320]

@@ -81,6 +81,16 @@ _SIG = {
     "umx_unet_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_forward_h16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_unet_submit_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_unet_wait": (C.c_int, [C.c_void_p]),
+    "umx_stream_new": (C.c_void_p, []),
+    "umx_stream_free": (None, [C.c_void_p]),
+    "umx_event_new": (C.c_void_p, []),
+    "umx_event_free": (None, [C.c_void_p]),
+    "umx_event_record": (None, [C.c_void_p, C.c_void_p]),
+    "umx_stream_wait": (None, [C.c_void_p, C.c_void_p]),
+    "umx_stream_sync": (None, [C.c_void_p]),
+    "umx_copy_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "umx_unet_flops": (C.c_double, [C.POINTER(UnetCfg)]),
     "umx_unet_launches": (C.c_long, [C.c_void_p]),
     "umx_launch_count": (C.c_long, []),

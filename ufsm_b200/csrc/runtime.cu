@@ -64,6 +64,21 @@ extern "C" void *nn_malloc_host(size_t bytes) {
 }
 extern "C" void nn_free_host(void *p) { if (p) cudaFreeHost(p); }
 
+/* ---- copy streams and events for the host entry that overlaps the copies of one patch with the forward of the next.  Streams are
+   non-blocking (they do not synchronise with the legacy default stream the kernels run on); the order is made with events. ---- */
+extern "C" void *umx_stream_new(void) { cudaStream_t s = nullptr; cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking); if (e != cudaSuccess) { umx_latch("umx_stream_new", e); return nullptr; } return (void *)s; }
+extern "C" void umx_stream_free(void *s) { if (s) cudaStreamDestroy((cudaStream_t)s); }
+extern "C" void *umx_event_new(void) { cudaEvent_t ev = nullptr; cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); if (e != cudaSuccess) { umx_latch("umx_event_new", e); return nullptr; } return (void *)ev; }
+extern "C" void umx_event_free(void *ev) { if (ev) cudaEventDestroy((cudaEvent_t)ev); }
+/* stream NULL = the legacy default stream */
+extern "C" void umx_event_record(void *ev, void *stream) { cudaError_t e = cudaEventRecord((cudaEvent_t)ev, (cudaStream_t)stream); if (e != cudaSuccess) umx_latch("umx_event_record", e); }
+extern "C" void umx_stream_wait(void *stream, void *ev) { cudaError_t e = cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0); if (e != cudaSuccess) umx_latch("umx_stream_wait", e); }
+extern "C" void umx_stream_sync(void *stream) { cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream); if (e != cudaSuccess) umx_latch("umx_stream_sync", e); }
+extern "C" void umx_copy_async(void *dst, const void *src, size_t bytes, int to_device, void *stream) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e != cudaSuccess) umx_latch("umx_copy_async", e);
+}
+
 /* scratch: per device, per slot, grows on demand, never shrinks */
 enum { WS_SLOTS = 8 };
 static void *g_ws[16][WS_SLOTS];

@@ -32,6 +32,10 @@ struct umx_unet {
     void *dn[MAXL];          /* MX output of down l-1 = input of enc l c1 (l >= 1) */
     void *dec[MAXL];         /* MX output of dec l c2 */
     void *x16, *xu8, *logits16;   /* staging for the host entry */
+    /* the pipelined host entry: two slots of input bytes and fp16 logits, a copy-in and a copy-out stream, and per slot the events
+       "input uploaded", "input consumed", "logits ready", "logits downloaded" */
+    void *pxu8[2], *plog[2], *s_in, *s_out, *ev_up[2], *ev_used[2], *ev_ready[2], *ev_down[2];
+    long seq; int pipe_ok;
     long launches0;
 };
 
@@ -72,6 +76,8 @@ void umx_unet_free(umx_unet *u) {
     }
     umx_conv_free(u->head);
     nn_free(u->x_mx); nn_free(u->ybuf); nn_free(u->part); nn_free(u->coef); nn_free(u->x16); nn_free(u->xu8); nn_free(u->logits16);
+    for (int k = 0; k < 2; k++) { nn_free(u->pxu8[k]); nn_free(u->plog[k]); umx_event_free(u->ev_up[k]); umx_event_free(u->ev_used[k]); umx_event_free(u->ev_ready[k]); umx_event_free(u->ev_down[k]); }
+    umx_stream_free(u->s_in); umx_stream_free(u->s_out);
     free(u);
 }
 umx_unet *umx_unet_create(const umx_unet_cfg *cfg, const float *weights, int max_batch) {
@@ -158,6 +164,51 @@ int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logi
     umx_u8_to_h16(u->xu8, (size_t)N * S, u->x16);
     forward(u, u->x16, N, u->logits16, UMX_F16);
     nn_d2h(logits16_host, u->logits16, (size_t)N * u->cfg.nh * S * 2);
+    return nn_check() ? -1 : 0;
+}
+/* The same work, queued: returns once the copies and kernels are enqueued.  The upload of this call's patches and the download of its
+   logits run on two copy streams and overlap the forward of the neighbouring calls (two slots, so at most two calls are in flight;
+   a third waits on the device, not on the host).  ct_host and logits16_host should be pinned and must stay valid, and logits16_host
+   unread, until umx_unet_wait returns.  0, or -1 with the message in lp_check(). */
+static int pipe_init(umx_unet *u) {
+    if (u->pipe_ok) return 0;
+    const size_t S = cube(u->cfg.P);
+    u->s_in = umx_stream_new(); u->s_out = umx_stream_new();
+    for (int k = 0; k < 2; k++) {
+        u->pxu8[k] = nn_malloc((size_t)u->maxN * S); u->plog[k] = nn_malloc((size_t)u->maxN * u->cfg.nh * S * 2);
+        u->ev_up[k] = umx_event_new(); u->ev_used[k] = umx_event_new(); u->ev_ready[k] = umx_event_new(); u->ev_down[k] = umx_event_new();
+        if (!u->pxu8[k] || !u->plog[k] || !u->ev_up[k] || !u->ev_used[k] || !u->ev_ready[k] || !u->ev_down[k]) return -1;
+    }
+    if (!u->s_in || !u->s_out) return -1;
+    u->pipe_ok = 1;
+    return 0;
+}
+int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) {
+    if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_submit_host: batch %d outside 1..%d\n", N, u->maxN); abort(); }
+    if (pipe_init(u)) return -1;
+    const size_t S = cube(u->cfg.P);
+    const int k = (int)(u->seq & 1);
+    /* upload: the slot's bytes of two calls ago have been converted */
+    umx_stream_wait(u->s_in, u->ev_used[k]);
+    umx_copy_async(u->pxu8[k], ct_host, (size_t)N * S, 1, u->s_in);
+    umx_event_record(u->ev_up[k], u->s_in);
+    /* forward on the legacy default stream: after the upload, and after the slot's logits of two calls ago have left */
+    umx_stream_wait(nullptr, u->ev_up[k]);
+    umx_u8_to_h16(u->pxu8[k], (size_t)N * S, u->x16);
+    umx_event_record(u->ev_used[k], nullptr);
+    umx_stream_wait(nullptr, u->ev_down[k]);
+    forward(u, u->x16, N, u->plog[k], UMX_F16);
+    umx_event_record(u->ev_ready[k], nullptr);
+    /* download */
+    umx_stream_wait(u->s_out, u->ev_ready[k]);
+    umx_copy_async(logits16_host, u->plog[k], (size_t)N * u->cfg.nh * S * 2, 0, u->s_out);
+    umx_event_record(u->ev_down[k], u->s_out);
+    u->seq++;
+    return nn_check() ? -1 : 0;
+}
+int umx_unet_wait(umx_unet *u) {
+    if (u->pipe_ok) { umx_stream_sync(u->s_in); umx_stream_sync(u->s_out); }
+    nn_sync();
     return nn_check() ? -1 : 0;
 }
 
