@@ -114,6 +114,9 @@ size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part 
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */
 void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
+/* the partial sums of a stored blocked-fp16 tensor y and the coefficients in one launch (part: scratch of umx_stats_doubles doubles); the
+   same values as umx_conv_fwd's `part` followed by umx_in_coef up to fp64 summation order.  Calls on one device must not overlap. */
+void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, double *part, float *coef);
 /* No counterpart in the reference.  The same coefficients as umx_in_coef, computed from the stored blocked-fp16 tensor y itself
    (device, [n][blk][voxel][32] halfs) by a call that allocates nothing: for callers that must not touch the CUDA allocator (all memory
    already handed to their own pool, allocation forbidden after start-up, or a loop where cudaMalloc's device-wide synchronisation is

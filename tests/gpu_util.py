@@ -111,6 +111,16 @@ def in_coef(part, N, Cn, D, H, W, eps=1e-5):
     return cd.download(np.float32), cd
 
 
+def in_stats_coef(y16_blocked, N, Cn, D, H, W, eps=1e-5):
+    """statistics + coefficients of a stored blocked-fp16 tensor in one launch"""
+    yd = DevBuf(data=np.ascontiguousarray(y16_blocked, np.float16))
+    pd = DevBuf(L().umx_stats_doubles(N, Cn, D, H, W) * 8).fill(0xEE)
+    cd = DevBuf(N * Cn * 8).fill(0xEE)
+    L().umx_in_stats_coef(yd.ptr, N, Cn, D, H, W, None, None, C.c_float(eps), pd.ptr, cd.ptr)
+    ufsm_b200.check()
+    return cd.download(np.float32)
+
+
 def in_apply(y16_blocked, coef, N, Cn, D, H, W, act, bits, nb_dst=0, b0=0, want_s2d=False, want_h=False, split=True):
     S = D * H * W
     nb = orc.nb32(Cn)

@@ -157,6 +157,8 @@ def test_instance_norm_sums_and_apply(dev):
     coef, _ = G.in_coef(part, N, Co, D, H, W)
     want_coef = orc.in_coef(orc.in_sums(y, N, Co, S), N, Co, S)   # statistics of the stored values, fp64
     assert np.array_equal(coef, want_coef), "max diff %g" % np.abs(coef - want_coef).max()
+    for _ in range(2):      # the one-launch form (the ticket counters reset themselves: twice in a row)
+        assert np.array_equal(G.in_stats_coef(raw.view(np.float16), N, Co, D, H, W), want_coef)
     for bits in (8, 4):
         q, s2d, h = G.in_apply(y, coef, N, Co, D, H, W, 2, bits, want_h=True)
         a = orc.in_apply(y, coef, N, Co, S, 2)

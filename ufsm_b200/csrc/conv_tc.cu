@@ -51,7 +51,14 @@ struct ConvArgs {
     const uint8_t *wpk;
     EpiArgs e;
     int *err;
+    long long *prof;
 };
+
+#ifdef UMX_KPROF
+#define KP1(...) __VA_ARGS__
+#else
+#define KP1(...)
+#endif
 
 __device__ __forceinline__ void raise(const ConvArgs &a, volatile int *abort_flag, int code, int stage) {
     if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)); a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
@@ -127,11 +134,15 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
     } else if (warp == 1) {
         /* ---------------- MMA issue ---------------- */
         int it = 0; bool ok = true;
+        KP1(long long t_tma = 0, t_sf = 0, t_issue = 0; const long long t00 = clock64();)
         for (int st = 0; st < nst && ok; st++) {
             if (!stage_live(st)) continue;
             const int s = it % R, ph = (it / R) & 1;
+            KP1(const long long k0 = clock64();)
             if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 2, st); ok = false; break; }
+            KP1(const long long k1 = clock64(); t_tma += k1 - k0;)
             if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 3, st); ok = false; break; }
+            KP1(const long long k2 = clock64(); t_sf += k2 - k1;)
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes);
@@ -148,8 +159,10 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 umma_commit(bar_empty + 8 * s);
             }
             __syncwarp();
+            KP1(t_issue += clock64() - k2;)
             it++;
         }
+        KP1(if (lane == 0) { long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[0] = t_tma; q[1] = t_sf; q[2] = t_issue; q[3] = clock64() - t00; q[4] = it; })
         if (lane == 0) umma_commit(bar_acc);   /* also after a give-up: the epilogue must not wait for its full limit */
         __syncwarp();
     } else {
@@ -428,9 +441,18 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
         smem_set[dev] = 227 * 1024;
     }
     const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n);
+#ifdef UMX_KPROF
+    const size_t nblk = (size_t)grid.x * grid.y * grid.z;
+    a.prof = (long long *)umx_ws(7, nblk * 64); cudaMemset(a.prof, 0, nblk * 64);
+#endif
     const int pid = umx_prof_open(flops);
     if (c->bits == 8) conv_mx_k<8><<<grid, kThreads, smem>>>(m0, a); else conv_mx_k<4><<<grid, kThreads, smem>>>(m0, a);
     umx_prof_close(pid);
+#ifdef UMX_KPROF
+    { long long *hb = (long long *)malloc(nblk * 64); cudaMemcpy(hb, a.prof, nblk * 64, cudaMemcpyDeviceToHost);
+      double t[5] = {0}; for (size_t b = 0; b < nblk; b++) for (int k = 0; k < 5; k++) t[k] += (double)hb[b * 8 + k] / nblk;
+      fprintf(stderr, "kprof-v1: grid %u x %u x %u ring %d nst %d nt %d stage_bytes %d | mma thread: stages %.0f total %.0f wait-tma %.0f wait-sf %.0f issue %.0f\n", grid.x, grid.y, grid.z, a.ring, a.nst, a.nt, a.stage_bytes, t[4], t[3], t[0], t[1], t[2]); free(hb); }
+#endif
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");
     if (part) umx_in_part(y, N, c->co, D, H, W, part);

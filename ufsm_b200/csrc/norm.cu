@@ -21,14 +21,20 @@ __global__ void __launch_bounds__(256) in_coef_k(const double *__restrict__ part
         coef[2 * ((size_t)n * C + c) + 1] = __fmaf_rn(-(float)m, a, beta ? beta[c] : 0.f);
     }
 }
-/* voxel chunks per (sample, channel) of the partial sums: about 1024 voxels each, at most 2048 */
-int umx_stats_chunks(int D, int H, int W) { const size_t S = (size_t)D * H * W; const size_t t = S / 1024; return t < 1 ? 1 : t > 2048 ? 2048 : (int)t; }
+extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
+/* voxel chunks per (sample, channel) of the partial sums: about 1024 voxels each, at most 512 */
+int umx_stats_chunks(int D, int H, int W) { const size_t S = (size_t)D * H * W; const size_t t = S / 1024; return t < 1 ? 1 : t > 512 ? 512 : (int)t; }
 
 /* partial sums of chunk t of block blk of sample n of a blocked fp16 tensor: part[((n * T + t) * Cop + c) * 2 + {0, 1}].  A thread owns
    eight channels (one 16-byte load) of every 64th voxel of the chunk, four loads in flight, so a warp reads 512 contiguous bytes per
    load; the 64 phases are added in a fixed order.  fp64 throughout: sums of fp16 values and of their squares are then exact to the
    last bits whatever the order.  HBM-bound: reads 2 B per element. */
-__global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, size_t S, int T, double *__restrict__ part) {
+/* tickets of the fused finalise: one counter per (sample, block); the block that draws the last ticket finalises and resets it */
+__device__ unsigned g_stat_tickets[8192];
+
+template <bool FINAL>
+__global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, size_t S, int T, double *__restrict__ part,
+                                                 int C, const float *gamma, const float *beta, float eps, float *coef) {
     const int t = blockIdx.x, blk = blockIdx.y, n = blockIdx.z, nb = gridDim.y, Cop = nb * 32;
     const int qd = threadIdx.x & 3, ph = threadIdx.x >> 2;
     const size_t v0 = S * t / T, v1 = S * (t + 1) / T;
@@ -61,14 +67,55 @@ __global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, si
         for (int k = 0; k < 64; k++) acc += src[k][c];
         part[(((size_t)n * T + t) * Cop + blk * 32 + c) * 2 + (threadIdx.x >> 5)] = acc;
     }
+    if (!FINAL) return;
+    /* the last block of this (sample, block) to finish turns the partial sums into coefficients: eight threads a channel add
+       every eighth chunk, then the eight in order; the result does not depend on which block came last */
+    __shared__ unsigned last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) { const unsigned tk = atomicAdd(&g_stat_tickets[n * nb + blk], 1u); last = tk == (unsigned)T - 1u; if (last) g_stat_tickets[n * nb + blk] = 0u; }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    {
+        const int c = threadIdx.x & 31, g8 = threadIdx.x >> 5;
+        double a0 = 0.0, a1 = 0.0;
+        const double2 *pb = (const double2 *)part + ((size_t)n * T) * Cop + blk * 32 + c;
+        int k = g8;
+        for (; k + 24 < T; k += 32) {      /* four loads in flight; the order of the additions is fixed */
+            const double2 p0 = __ldcg(pb + (size_t)k * Cop), p1 = __ldcg(pb + (size_t)(k + 8) * Cop), p2 = __ldcg(pb + (size_t)(k + 16) * Cop), p3 = __ldcg(pb + (size_t)(k + 24) * Cop);
+            a0 += p0.x; a1 += p0.y; a0 += p1.x; a1 += p1.y; a0 += p2.x; a1 += p2.y; a0 += p3.x; a1 += p3.y;
+        }
+        for (; k < T; k += 8) { const double2 p0 = __ldcg(pb + (size_t)k * Cop); a0 += p0.x; a1 += p0.y; }
+        ss[g8][c] = a0; sq[g8][c] = a1;
+        __syncthreads();
+        if (g8 == 0 && blk * 32 + c < C) {
+            for (int k = 1; k < 8; k++) { a0 += ss[k][c]; a1 += sq[k][c]; }
+            const int ch = blk * 32 + c;
+            const double m = a0 / (double)S, v = fmax(a1 / (double)S - m * m, 0.0);
+            const float rs = (float)(1.0 / sqrt(v + (double)eps)), ca = __fmul_rn(rs, gamma ? gamma[ch] : 1.f);
+            coef[2 * ((size_t)n * C + ch)] = ca;
+            coef[2 * ((size_t)n * C + ch) + 1] = __fmaf_rn(-(float)m, ca, beta ? beta[ch] : 0.f);
+        }
+    }
 }
 /* InstanceNorm partial sums of a stored blocked-fp16 conv output (what umx_conv_fwd runs after the conv when it is given `part`) */
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part) {
     if (!umx_ready("umx_in_part")) return;
     const int T = umx_stats_chunks(D, H, W);
-    in_part_k<<<dim3(T, (C + 31) / 32, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part);
+    in_part_k<false><<<dim3(T, (C + 31) / 32, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part, C, nullptr, nullptr, 0.f, nullptr);
     g_umx_launches++;
     UMX_CK("umx_in_part");
+}
+/* statistics and coefficients of a stored blocked-fp16 tensor in one launch (part: scratch of umx_stats_doubles doubles).  Launches of
+   this function on one device must not overlap (they share the ticket counters); on one stream they never do. */
+extern "C" void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, double *part, float *coef) {
+    if (!umx_ready("umx_in_stats_coef")) return;
+    const int T = umx_stats_chunks(D, H, W), nb = (C + 31) / 32;
+    if ((size_t)N * nb > 8192) { umx_in_part(y, N, C, D, H, W, part); umx_in_coef(part, N, C, D, H, W, gamma, beta, eps, coef); return; }
+    in_part_k<true><<<dim3(T, nb, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part, C, gamma, beta, eps, coef);
+    g_umx_launches++;
+    UMX_CK("umx_in_stats_coef");
 }
 extern "C" void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef) {
     if (!umx_ready("umx_in_coef")) return;
