@@ -132,39 +132,49 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             }
         }
     } else if (warp == 1) {
-        /* ---------------- MMA issue ---------------- */
-        int it = 0; bool ok = true;
-        KP1(long long t_tma = 0, t_sf = 0, t_issue = 0; const long long t00 = clock64();)
-        for (int st = 0; st < nst && ok; st++) {
-            if (!stage_live(st)) continue;
-            const int s = it % R, ph = (it / R) & 1;
-            KP1(const long long k0 = clock64();)
-            if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 2, st); ok = false; break; }
-            KP1(const long long k1 = clock64(); t_tma += k1 - k0;)
-            if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { if (lane == 0) raise(a, abort_flag, 3, st); ok = false; break; }
-            KP1(const long long k2 = clock64(); t_sf += k2 - k1;)
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes);
+        /* ---------------- MMA issue: one thread; everything that does not change with the stage is worked out before the loop ---------------- */
+        if (lane == 0) {
+            int it = 0, s = 0, ph = 0; bool ok = true;
+            const uint32_t sb0 = smem_u32(stages), sstep = (uint32_t)a.stage_bytes >> 4;
+            const uint32_t sf_hi = desc_hi(128), b_hi = desc_hi(128), a_hi = a.taps == 27 ? desc_hi(160) : desc_hi(128);
+            const uint32_t sfa_lo0 = desc_lo(sb0 + a.offSFA, 0), sfb_lo0 = desc_lo(sb0 + a.offSFB, 0);
+            const uint32_t a_lo0 = desc_lo(sb0 + a.offA, a.taps == 27 ? 2880 : 2048), b_lo0 = desc_lo(sb0 + a.offW, (uint32_t)a.nt * 16);
+            const uint32_t idesc0 = BITS == 8 ? idesc_mxf8(n_cur, 0, 0) : idesc_mxf4(n_cur, 0, 0);
+            const uint32_t bstep = (uint32_t)a.nt * 2;
+            KP1(long long t_tma = 0, t_sf = 0, t_issue = 0; const long long t00 = clock64();)
+            for (int st = 0; st < nst && ok; st++) {
+                if (!stage_live(st)) continue;
+                KP1(const long long k0 = clock64();)
+                if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 3, st); ok = false; break; }
+                KP1(const long long k1 = clock64(); t_sf += k1 - k0;)
+                if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 2, st); ok = false; break; }
+                KP1(const long long k2 = clock64(); t_tma += k2 - k1;)
+                tc_fence_after();
+                const uint32_t so = (uint32_t)s * sstep;
                 const uint32_t sfa_t = tmem + kSfBase + (it & 1) * 40, sfb_t = sfa_t + 20;
-                const int items = stage_items(st), nq = (items + a.ipq - 1) / a.ipq;
-                for (int q = 0; q < nq; q++) {
-                    utccp_32x128b(sfa_t + 4 * q, smem_desc(sb + a.offSFA + 512 * q, 0, 128));
-                    utccp_32x128b(sfb_t + 4 * q, smem_desc(sb + a.offSFB + 512 * q, 0, 128));
+                if (a.taps == 27) {
+                    constexpr int NQ = BITS == 8 ? 3 : 5;
+#pragma unroll
+                    for (int q = 0; q < NQ; q++) {
+                        utccp_32x128b(sfa_t + 4 * q, desc_make(sfa_lo0 + so + 32u * q, sf_hi));
+                        utccp_32x128b(sfb_t + 4 * q, desc_make(sfb_lo0 + so + 32u * q, sf_hi));
+                    }
+                    issue_items<BITS, 9, true>(tmem, a_lo0 + so, a_hi, b_lo0 + so, b_hi, bstep, 0, idesc0, sfa_t, sfb_t, it == 0, 9);
+                } else {
+                    const int items = stage_items(st), nq = (items + a.ipq - 1) / a.ipq;
+                    for (int q = 0; q < nq; q++) {
+                        utccp_32x128b(sfa_t + 4 * q, desc_make(sfa_lo0 + so + 32u * q, sf_hi));
+                        utccp_32x128b(sfb_t + 4 * q, desc_make(sfb_lo0 + so + 32u * q, sf_hi));
+                    }
+                    issue_items<BITS, 4, false>(tmem, a_lo0 + so, a_hi, b_lo0 + so, b_hi, bstep, 256, idesc0, sfa_t, sfb_t, it == 0, items);
                 }
-                const uint32_t idesc0 = BITS == 8 ? idesc_mxf8(n_cur, 0, 0) : idesc_mxf4(n_cur, 0, 0);
-                const uint32_t b_lo = desc_lo(sb + a.offW, (uint32_t)a.nt * 16), b_hi = desc_hi(128);
-                if (a.taps == 27) issue_items<BITS, 9, true>(tmem, desc_lo(sb + a.offA, 2880), desc_hi(160), b_lo, b_hi, (uint32_t)a.nt * 2, 0, idesc0, sfa_t, sfb_t, it == 0, 9);
-                else issue_items<BITS, 4, false>(tmem, desc_lo(sb + a.offA, 2048), desc_hi(128), b_lo, b_hi, (uint32_t)a.nt * 2, 256, idesc0, sfa_t, sfb_t, it == 0, items);
                 umma_commit(bar_empty + 8 * s);
+                KP1(t_issue += clock64() - k2;)
+                it++; if (++s == R) { s = 0; ph ^= 1; }
             }
-            __syncwarp();
-            KP1(t_issue += clock64() - k2;)
-            it++;
+            KP1({ long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[0] = t_tma; q[1] = t_sf; q[2] = t_issue; q[3] = clock64() - t00; q[4] = it; })
+            umma_commit(bar_acc);   /* also after a give-up: the epilogue must not wait for its full limit */
         }
-        KP1(if (lane == 0) { long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[0] = t_tma; q[1] = t_sf; q[2] = t_issue; q[3] = clock64() - t00; q[4] = it; })
-        if (lane == 0) umma_commit(bar_acc);   /* also after a give-up: the epilogue must not wait for its full limit */
-        __syncwarp();
     } else {
         /* ---------------- scale gather, then epilogue ---------------- */
         const int q4 = warp & 3, r = q4 * 32 + lane;             /* TMEM lane quarter of this warp; GEMM row of this thread */
@@ -242,7 +252,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
         /* after a give-up: let this thread's own copies in flight land (bounded) before the block's shared memory is released */
         for (int s = 0; s < R; s++) { const long long t0 = clock64(); while (!mbar_try(bar_tma + 8 * s, 0) && !mbar_try(bar_tma + 8 * s, 1) && clock64() - t0 < 20000000ll) { } }
     }
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
+    if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
 }
 
 /* ---- weight preparation: fp32 weights -> the shared-memory image of every (column tile, stage): items x [k half][row][16 B]
