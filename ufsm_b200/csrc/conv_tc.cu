@@ -92,10 +92,12 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
         fence_barrier_init();
         fence_proxy_async();
     }
+    pdl_trigger();
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), kTmemCols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                                  /* from here on the block touches activations */
     const uint32_t tmem = *tmem_slot;
 
     /* a stage is live unless it is a 3^3 stage whose input plane lies outside the volume (it would add zeros) */
@@ -456,7 +458,7 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     a.prof = (long long *)umx_ws(7, nblk * 64); cudaMemset(a.prof, 0, nblk * 64);
 #endif
     const int pid = umx_prof_open(flops);
-    if (c->bits == 8) conv_mx_k<8><<<grid, kThreads, smem>>>(m0, a); else conv_mx_k<4><<<grid, kThreads, smem>>>(m0, a);
+    if (c->bits == 8) umx_launch(conv_mx_k<8>, grid, dim3(kThreads), smem, m0, a); else umx_launch(conv_mx_k<4>, grid, dim3(kThreads), smem, m0, a);
     umx_prof_close(pid);
 #ifdef UMX_KPROF
     { long long *hb = (long long *)malloc(nblk * 64); cudaMemcpy(hb, a.prof, nblk * 64, cudaMemcpyDeviceToHost);

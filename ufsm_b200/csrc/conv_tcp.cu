@@ -74,10 +74,17 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
         fence_barrier_init();
         fence_proxy_async();
     }
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        /* the weight image is a constant of the layer: it may load while the previous kernel of the stream is still running */
+        mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
+        for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wp + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
+    }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                                  /* from here on the block touches activations */
     const uint32_t tmem = *tmem_slot;
     const long long j0 = a.jobs * (long long)blockIdx.x / (long long)gridDim.x, j1 = a.jobs * ((long long)blockIdx.x + 1) / (long long)gridDim.x;
 
@@ -85,8 +92,6 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
         /* ---------------- producer ---------------- */
         if (lane == 0) {
             tma_prefetch_desc(&map0); tma_prefetch_desc(&maps);
-            mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
-            for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wp + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
             int s = 0, ph = 0, it = 0; bool ok = true;
             KP(long long p_wait = 0; const long long p_t0 = clock64();)
             /* job = (row tile, column tile), column tile fastest; the indices advance incrementally (no division per job) */
@@ -348,7 +353,7 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     a.dbg = getenv("UMX_DBG") ? atoi(getenv("UMX_DBG")) : 0;
     a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
 #endif
-    if (c->bits == 8) conv_mxp_k<8><<<grid, kThreadsP, smem>>>(m0, ms, a); else conv_mxp_k<4><<<grid, kThreadsP, smem>>>(m0, ms, a);
+    if (c->bits == 8) umx_launch(conv_mxp_k<8>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a); else umx_launch(conv_mxp_k<4>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a);
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
       double t[14] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 14; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;

@@ -126,10 +126,17 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
     KP(const long long ta0 = clock64(); long long tg0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg0));)
     const int ctile = (int)blockIdx.x / a.gcol;
     if ((int)threadIdx.x < a.nt) bias_s[threadIdx.x] = a.e.bias[ctile * a.nt + threadIdx.x];
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        /* the weight image is a constant of the layer: it may load while the previous kernel of the stream is still running */
+        mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
+        for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wr + (size_t)ctile * a.w_bytes + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
+    }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), (uint32_t)a.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                                  /* from here on the block touches activations */
     const uint32_t tmem = *tmem_slot;
     Piece piece = piece_of_block(a);
 
@@ -137,8 +144,6 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         /* ---------------- producer: stage records and TMA ---------------- */
         if (lane == 0) {
             tma_prefetch_desc(&map0); tma_prefetch_desc(&maps);
-            mbar_expect_tx(bar_w, (uint32_t)a.w_bytes);
-            for (int o = 0; o < a.w_bytes; o += 32768) bulk_g2s(smem_u32(wsm + o), a.wr + (size_t)ctile * a.w_bytes + o, (uint32_t)min(32768, a.w_bytes - o), bar_w);
             const uint32_t nt = (uint32_t)a.nt, bstep9 = 9u * 2u * 3u * nt;            /* B descriptor step of one input block: nine taps of two halves of 3 nt rows */
             const uint32_t b_lo0 = desc_lo(smem_u32(wsm), 3u * nt * 16u);
             const uint32_t idesc_b = (BITS == 8 ? idesc_mxf8(0, 0, 0) : idesc_mxf4(0, 0, 0)), ntn = (nt >> 3) << 17;
@@ -504,7 +509,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
 #ifdef UMX_KPROF
     a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
 #endif
-    if (c->bits == 8) conv_mxr_k<8><<<grid, kThreadsR, smem>>>(*m0, ms, a); else conv_mxr_k<4><<<grid, kThreadsR, smem>>>(*m0, ms, a);
+    if (c->bits == 8) umx_launch(conv_mxr_k<8>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a);
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
       double t[15] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 15; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;

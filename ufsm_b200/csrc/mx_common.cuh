@@ -18,6 +18,26 @@ extern long g_umx_launches;
 int umx_prof_open(double flops);   /* conv launch timing (runtime.cu): returns a slot or -1 when profiling is off */
 void umx_prof_close(int id);
 
+/* ---- programmatic dependent launch: a kernel launched through umx_launch may be scheduled while its predecessor in the stream is still
+   running; it calls pdl_wait() before its first access to memory the predecessor may write or read, and pdl_trigger() as early as it
+   likes to let its own successor be scheduled.  What is gained is the launch latency (and, in the conv kernels, the prologue: barrier
+   set-up, TMEM allocation, weight loads) of some 80 dependent launches per forward.  UMX_PDL=0 in the environment turns it off. ---- */
+int umx_pdl(void);
+#ifdef __CUDACC__
+#include <string.h>
+template <typename... KA, typename... A>
+static inline void umx_launch(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, A... args) {
+    cudaLaunchConfig_t cfg; memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = 0;
+    cudaLaunchAttribute at[1]; memset(at, 0, sizeof at);
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+    if (umx_pdl()) { cfg.attrs = at; cfg.numAttrs = 1; }
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...);
+}
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 /* ---- MX arithmetic ---- */
 /* exponent e of the block scale 2^e = exponent of amax / qmax rounded up, clamped to [-126, 126]; NaN / inf amax -> 128 (scale
    byte 0xFF).  Same rule as src/lp_common.cuh:492-500. */

@@ -35,6 +35,7 @@ __device__ unsigned g_stat_tickets[8192];
 template <bool FINAL>
 __global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, size_t S, int T, double *__restrict__ part,
                                                  int C, const float *gamma, const float *beta, float eps, float *coef) {
+    pdl_trigger(); pdl_wait();
     const int t = blockIdx.x, blk = blockIdx.y, n = blockIdx.z, nb = gridDim.y, Cop = nb * 32;
     const int qd = threadIdx.x & 3, ph = threadIdx.x >> 2;
     const size_t v0 = S * t / T, v1 = S * (t + 1) / T;
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, si
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part) {
     if (!umx_ready("umx_in_part")) return;
     const int T = umx_stats_chunks(D, H, W);
-    in_part_k<false><<<dim3(T, (C + 31) / 32, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part, C, nullptr, nullptr, 0.f, nullptr);
+    umx_launch(in_part_k<false>, dim3(T, (C + 31) / 32, N), dim3(256), 0, (const uint4 *)y, (size_t)D * H * W, T, part, C, (const float *)nullptr, (const float *)nullptr, 0.f, (float *)nullptr);
     g_umx_launches++;
     UMX_CK("umx_in_part");
 }
@@ -113,7 +114,7 @@ extern "C" void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int
     if (!umx_ready("umx_in_stats_coef")) return;
     const int T = umx_stats_chunks(D, H, W), nb = (C + 31) / 32;
     if ((size_t)N * nb > 8192) { umx_in_part(y, N, C, D, H, W, part); umx_in_coef(part, N, C, D, H, W, gamma, beta, eps, coef); return; }
-    in_part_k<true><<<dim3(T, nb, N), 256>>>((const uint4 *)y, (size_t)D * H * W, T, part, C, gamma, beta, eps, coef);
+    umx_launch(in_part_k<true>, dim3(T, nb, N), dim3(256), 0, (const uint4 *)y, (size_t)D * H * W, T, part, C, gamma, beta, eps, coef);
     g_umx_launches++;
     UMX_CK("umx_in_stats_coef");
 }
@@ -136,6 +137,7 @@ __device__ __forceinline__ float amax_nan(float a, float v) { float r; asm("max.
 template <int BITS, bool COEF, bool FULL, bool S2D>
 __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, const float2 *__restrict__ coef, int C, int D, int H, int W, int act,
                                                   uint8_t *__restrict__ q, int nb_dst, int b0, uint8_t *__restrict__ q2, uint4 *__restrict__ hout, int split, int T) {
+    pdl_trigger(); pdl_wait();
     const int N = gridDim.z, nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z;
     const size_t S = (size_t)D * H * W;
     const int qd = threadIdx.x & 3, ph = threadIdx.x >> 2;
@@ -214,8 +216,8 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
 }
 template <int BITS, bool COEF, bool FULL>
 static void in_apply_launch(dim3 grid, const void *x, const float *coef, int C, int D, int H, int W, int act, void *q, int nb_dst, int b0, void *q_s2d, void *h, int split, int T) {
-    if (q_s2d) in_apply_k<BITS, COEF, FULL, true><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, split, T);
-    else in_apply_k<BITS, COEF, FULL, false><<<grid, 256>>>((const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, nullptr, (uint4 *)h, split, T);
+    if (q_s2d) umx_launch(in_apply_k<BITS, COEF, FULL, true>, grid, dim3(256), 0, (const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)q_s2d, (uint4 *)h, split, T);
+    else umx_launch(in_apply_k<BITS, COEF, FULL, false>, grid, dim3(256), 0, (const uint4 *)x, (const float2 *)coef, C, D, H, W, act, (uint8_t *)q, nb_dst, b0, (uint8_t *)nullptr, (uint4 *)h, split, T);
 }
 extern "C" void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout) {
     if (!umx_ready("umx_in_apply")) return;

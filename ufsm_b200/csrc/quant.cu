@@ -16,6 +16,7 @@ template <> __device__ __forceinline__ float ld_as_f32<__half>(const __half *p) 
    reads and the row writes are both coalesced */
 template <int BITS, typename TI>
 __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw, int split) {
+    pdl_trigger(); pdl_wait();
     const int nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z, rb = bw * BITS / 8;
     const size_t rows = (size_t)N * nb * S, row0 = ((size_t)n * nb + blk) * S;
     uint8_t *sc = y + rows * rb;
@@ -79,8 +80,8 @@ static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bi
     if (!S || !N) return;
     size_t gx = (S + 255) / 256; if (gx > 148u * 16u) gx = 148u * 16u;
     const dim3 g((unsigned)gx, (unsigned)nb, (unsigned)N);
-    if (bits == 8) { if (dt == 2) pm_to_mx_k<8, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<8, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
-    else { if (dt == 2) pm_to_mx_k<4, __half><<<g, 256>>>((const __half *)x, (uint8_t *)y, N, C, S, bw, split); else pm_to_mx_k<4, float><<<g, 256>>>((const float *)x, (uint8_t *)y, N, C, S, bw, split); }
+    if (bits == 8) { if (dt == 2) umx_launch(pm_to_mx_k<8, __half>, g, dim3(256), 0, (const __half *)x, (uint8_t *)y, N, C, S, bw, split); else umx_launch(pm_to_mx_k<8, float>, g, dim3(256), 0, (const float *)x, (uint8_t *)y, N, C, S, bw, split); }
+    else { if (dt == 2) umx_launch(pm_to_mx_k<4, __half>, g, dim3(256), 0, (const __half *)x, (uint8_t *)y, N, C, S, bw, split); else umx_launch(pm_to_mx_k<4, float>, g, dim3(256), 0, (const float *)x, (uint8_t *)y, N, C, S, bw, split); }
     g_umx_launches++;
     UMX_CK(who);
 }

@@ -66,6 +66,7 @@ extern "C" void nn_free_host(void *p) { if (p) cudaFreeHost(p); }
 
 /* ---- copy streams and events for the host entry that overlaps the copies of one patch with the forward of the next.  Streams are
    non-blocking (they do not synchronise with the legacy default stream the kernels run on); the order is made with events. ---- */
+int umx_pdl(void) { static int v = -1; if (v < 0) { const char *e = getenv("UMX_PDL"); v = !(e && *e == '0'); } return v; }
 extern "C" void *umx_stream_new(void) { cudaStream_t s = nullptr; cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking); if (e != cudaSuccess) { umx_latch("umx_stream_new", e); return nullptr; } return (void *)s; }
 extern "C" void umx_stream_free(void *s) { if (s) cudaStreamDestroy((cudaStream_t)s); }
 extern "C" void *umx_event_new(void) { cudaEvent_t ev = nullptr; cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); if (e != cudaSuccess) { umx_latch("umx_event_new", e); return nullptr; } return (void *)ev; }
