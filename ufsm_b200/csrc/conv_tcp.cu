@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_wait();                                  /* from here on the block touches activations */
     const uint32_t tmem = *tmem_slot;
     const long long j0 = a.jobs * (long long)blockIdx.x / (long long)gridDim.x, j1 = a.jobs * ((long long)blockIdx.x + 1) / (long long)gridDim.x;
 
@@ -92,6 +91,8 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
         /* ---------------- producer ---------------- */
         if (lane == 0) {
             tma_prefetch_desc(&map0); tma_prefetch_desc(&maps);
+            pdl_wait();      /* the only role that reads activations from global memory; every other role's data comes through this thread's loads,
+                                so the weight load, the B scale copies and the zeroing of the accumulators overlap the previous kernel */
             int s = 0, ph = 0, it = 0; bool ok = true;
             KP(long long p_wait = 0; const long long p_t0 = clock64();)
             /* job = (row tile, column tile), column tile fastest; the indices advance incrementally (no division per job) */

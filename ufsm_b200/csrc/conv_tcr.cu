@@ -136,7 +136,6 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    pdl_wait();                                  /* from here on the block touches activations */
     const uint32_t tmem = *tmem_slot;
     Piece piece = piece_of_block(a);
 
@@ -144,6 +143,8 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         /* ---------------- producer: stage records and TMA ---------------- */
         if (lane == 0) {
             tma_prefetch_desc(&map0); tma_prefetch_desc(&maps);
+            pdl_wait();      /* the only role that reads activations from global memory; every other role's data comes through this thread's loads,
+                                so the weight load, the B scale copies and the zeroing of the accumulators overlap the previous kernel */
             const uint32_t nt = (uint32_t)a.nt, bstep9 = 9u * 2u * 3u * nt;            /* B descriptor step of one input block: nine taps of two halves of 3 nt rows */
             const uint32_t b_lo0 = desc_lo(smem_u32(wsm), 3u * nt * 16u);
             const uint32_t idesc_b = (BITS == 8 ? idesc_mxf8(0, 0, 0) : idesc_mxf4(0, 0, 0)), ntn = (nt >> 3) << 17;
