@@ -171,31 +171,45 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
         for (int u = 0; u < 4; u++) {
             const size_t v = vb + u * 64 + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
             const __half2 *hp = (const __half2 *)&raws[u];
-            float f[8]; uint4 o; __half2 *op = (__half2 *)&o;
+            uint4 o; __half2 *op = (__half2 *)&o;
 #pragma unroll
             for (int k = 0; k < 4; k++) {
                 const float2 t = __half22float2(hp[k]);
                 float g0 = t.x, g1 = t.y;
                 if (COEF) { g0 = __fmaf_rn(g0, ca[2 * k], cb[2 * k]); g1 = __fmaf_rn(g1, ca[2 * k + 1], cb[2 * k + 1]); }
-                g0 = g0 < 0.f ? __fmul_rn(slope, g0) : g0; g1 = g1 < 0.f ? __fmul_rn(slope, g1) : g1;
+                g0 = fmaxf(g0, __fmul_rn(slope, g0)); g1 = fmaxf(g1, __fmul_rn(slope, g1));      /* LeakyReLU for 0 < slope <= 1 (NaN stays NaN) */
                 if (!FULL) { if (!live[2 * k]) g0 = 0.f; if (!live[2 * k + 1]) g1 = 0.f; }
                 op[k] = __floats2half2_rn(g0, g1);
-                const float2 r = __half22float2(op[k]);
-                f[2 * k] = r.x; f[2 * k + 1] = r.y;
             }
             if (hp_out && ok) hp_out[v * 4] = o;
-            float amf = 0.f;
-#pragma unroll
-            for (int k = 0; k < 8; k++) amf = amax_nan(amf, f[k]);
-            unsigned am = __float_as_uint(amf) & 0x7fffffffu;
+            /* amax of the stored fp16 values, NaN-propagating, taken on the halves (exact: the conversion to fp32 is monotonic) */
+            __half2 a2 = __hmax2_nan(__hmax2_nan(__habs2(op[0]), __habs2(op[1])), __hmax2_nan(__habs2(op[2]), __habs2(op[3])));
+            const __half a1 = __hmax_nan(__low2half(a2), __high2half(a2));
+            unsigned am = __float_as_uint(__half2float(a1)) & 0x7fffffffu;
             am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
             am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
             const int e = mx_exp(__uint_as_float(am), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
-            const float m = exp2i(-e);
             const unsigned sb = (unsigned)(e + 127) & 0xffu;
             unsigned w0, w1 = 0u;
-            if (BITS == 8) { w0 = cvt_e4m3x4(f[0] * m, f[1] * m, f[2] * m, f[3] * m); w1 = cvt_e4m3x4(f[4] * m, f[5] * m, f[6] * m, f[7] * m); }
-            else w0 = cvt_e2m1x8(f, m);
+            if (BITS == 8 && e >= -15 && e <= 14) {
+                /* 2^-e is a normal fp16: scale the halves (exact, or below 2^-14 where E4M3 rounds to zero either way) and convert pairs */
+                const unsigned mh = (unsigned)(15 - e) << 10, m2 = mh | (mh << 16);
+                const __half2 mm = *(const __half2 *)&m2;
+                unsigned short c0, c1, c2, c3;
+                const __half2 s0 = __hmul2(op[0], mm), s1 = __hmul2(op[1], mm), s2 = __hmul2(op[2], mm), s3 = __hmul2(op[3], mm);
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c0) : "r"(*(const unsigned *)&s0));
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c1) : "r"(*(const unsigned *)&s1));
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c2) : "r"(*(const unsigned *)&s2));
+                asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c3) : "r"(*(const unsigned *)&s3));
+                w0 = (unsigned)c0 | ((unsigned)c1 << 16); w1 = (unsigned)c2 | ((unsigned)c3 << 16);
+            } else {
+                float f[8];
+#pragma unroll
+                for (int k = 0; k < 4; k++) { const float2 r = __half22float2(op[k]); f[2 * k] = r.x; f[2 * k + 1] = r.y; }
+                const float m = exp2i(-e);
+                if (BITS == 8) { w0 = cvt_e4m3x4(f[0] * m, f[1] * m, f[2] * m, f[3] * m); w1 = cvt_e4m3x4(f[4] * m, f[5] * m, f[6] * m, f[7] * m); }
+                else w0 = cvt_e2m1x8(f, m);
+            }
             if (!ok) continue;
             if (qb) {
                 if (BITS == 8) *(uint2 *)(qb + v * qs) = make_uint2(w0, w1); else *(unsigned *)(qb + v * qs) = w0;

@@ -3,6 +3,7 @@
 #include "mx_common.cuh"
 
 __global__ void __launch_bounds__(256) u8_to_h16_k(const uint8_t *__restrict__ x, __half *__restrict__ y, size_t n) {
+    pdl_trigger(); pdl_wait();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         y[i] = __float2half_rn(__fdiv_rn((float)x[i], 255.f));
 }
@@ -10,7 +11,7 @@ __global__ void __launch_bounds__(256) u8_to_h16_k(const uint8_t *__restrict__ x
 extern "C" void umx_u8_to_h16(const uint8_t *x, size_t n, void *y) {
     if (!umx_ready("umx_u8_to_h16")) return;
     size_t g = (n + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; if (!g) g = 1;
-    u8_to_h16_k<<<(unsigned)g, 256>>>(x, (__half *)y, n);
+    umx_launch(u8_to_h16_k, dim3((unsigned)g), dim3(256), 0, x, (__half *)y, n);
     g_umx_launches++;
     UMX_CK("umx_u8_to_h16");
 }
@@ -19,6 +20,7 @@ extern "C" void umx_u8_to_h16(const uint8_t *x, size_t n, void *y) {
 template <typename T>
 __global__ void __launch_bounds__(256) blend_add_k(const T *__restrict__ logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0,
                                                     const float *__restrict__ w1d, float *__restrict__ acc, float *__restrict__ wsum) {
+    pdl_trigger(); pdl_wait();
     const size_t PS = (size_t)P * P * P, plane = (size_t)V * V, AS = plane * zext;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < PS; i += (size_t)gridDim.x * blockDim.x) {
         const int x = (int)(i % P), y = (int)((i / P) % P), z = (int)(i / ((size_t)P * P));
@@ -33,8 +35,8 @@ __global__ void __launch_bounds__(256) blend_add_k(const T *__restrict__ logits,
 extern "C" void umx_blend_add(const void *logits, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, float *acc, float *wsum) {
     if (!umx_ready("umx_blend_add")) return;
     const size_t PS = (size_t)P * P * P; size_t g = (PS + 255) / 256; if (g > 148u * 16u) g = 148u * 16u;
-    if (fmt == UMX_F16) blend_add_k<__half><<<(unsigned)g, 256>>>((const __half *)logits, nh, P, V, zlo, zext, z0, y0, x0, w1d, acc, wsum);
-    else blend_add_k<float><<<(unsigned)g, 256>>>((const float *)logits, nh, P, V, zlo, zext, z0, y0, x0, w1d, acc, wsum);
+    if (fmt == UMX_F16) umx_launch(blend_add_k<__half>, dim3((unsigned)g), dim3(256), 0, (const __half *)logits, nh, P, V, zlo, zext, z0, y0, x0, w1d, acc, wsum);
+    else umx_launch(blend_add_k<float>, dim3((unsigned)g), dim3(256), 0, (const float *)logits, nh, P, V, zlo, zext, z0, y0, x0, w1d, acc, wsum);
     g_umx_launches++;
     UMX_CK("umx_blend_add");
 }
