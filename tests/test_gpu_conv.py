@@ -179,6 +179,24 @@ def test_apply_space_to_depth_and_concat(dev):
     assert np.array_equal(s2d, orc.blocked_to_mx(orc.s2d_blocked(a, N, Cn, D, H, W), 8, N, 8 * Cn, S // 8))
 
 
+def test_apply_scale_ranges(dev):
+    """The apply's requantiser across block scales: rows whose scale 2^-e is a normal fp16 take the packed-half path, very small and
+    very large rows (and inf / NaN rows) the fp32 path; all must match the oracle bit for bit."""
+    N, Cn, D, H, W = 1, 64, 2, 8, 16
+    S = D * H * W
+    r = synth.rng(91)
+    mag = 2.0 ** r.integers(-24, 16, (N, 2, S, 1)).astype(np.float64)               # per (block, voxel) magnitude from 2^-24 to 2^15
+    y = (r.standard_normal((N, 2, S, 32)) * mag).astype(np.float16)
+    y[0, 0, 5, 3] = np.float16(np.inf); y[0, 1, 7, 9] = np.float16(np.nan); y[0, 0, 9, :] = 0; y[0, 1, 11, 2] = np.float16(65504)
+    y = y.astype(np.float32).ravel()
+    coef = np.tile(np.array([1, 0], np.float32), N * Cn)                             # identity map: fmaf(x, 1, 0) == x
+    a = orc.in_apply(y, coef, N, Cn, S, 0)
+    for bits in (8, 4):
+        q, _, h = G.in_apply(y, coef, N, Cn, D, H, W, 0, bits, want_h=True)
+        assert np.array_equal(h.astype(np.float32), a, equal_nan=True)
+        assert np.array_equal(q, orc.blocked_to_mx(a, bits, N, Cn, S))
+
+
 def test_lp_conv_fwd_f8_config1(dev):
     """BASELINE configuration 1 through the reference's entry point: 1 x 32 x 64^3 fp16 N(0,1), 32 -> 32, MX-fp8, fp16 output."""
     import ctypes as C
