@@ -23,12 +23,35 @@ struct EpiArgs {
    the values as stored, which is what the statistics are taken from) and writes the row if it lies inside the volume. */
 __device__ __forceinline__ void epi_chunk(const EpiArgs &a, int n, int z, int oy, int ox, bool row_ok, int cb_g, float *v) {
     const size_t S = (size_t)a.D * a.H * a.W;
+    {
+        const float4 *bp = (const float4 *)(a.bias + cb_g * 32);
 #pragma unroll
-    for (int k = 0; k < 32; k++) v[k] = __fadd_rn(v[k], __ldg(a.bias + cb_g * 32 + k));
+        for (int k = 0; k < 8; k++) { const float4 b = __ldg(bp + k); v[4 * k] = __fadd_rn(v[4 * k], b.x); v[4 * k + 1] = __fadd_rn(v[4 * k + 1], b.y); v[4 * k + 2] = __fadd_rn(v[4 * k + 2], b.z); v[4 * k + 3] = __fadd_rn(v[4 * k + 3], b.w); }
+    }
     int ob = cb_g; size_t vo = ((size_t)z * a.H + oy) * a.W + ox; size_t So = S;
     if (a.tconv) {
         const int abc = cb_g / a.cob_t, Ho = 2 * a.H, Wo = 2 * a.W; ob = cb_g % a.cob_t; So = S * 8;
         vo = ((size_t)(2 * z + (abc >> 2)) * Ho + 2 * oy + ((abc >> 1) & 1)) * Wo + 2 * ox + (abc & 1);
+    }
+    if (a.out_mode == UMX_OUT_MX && a.out_bits == 8) {
+        /* fp16 rounding, then the requantiser on the packed halves */
+        if (!row_ok) return;
+        __half2 h[16];
+#pragma unroll
+        for (int k = 0; k < 16; k++) h[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+        unsigned w[8];
+        const unsigned sbyte = mx_encode_row32_h8(h, w);
+        uint8_t *yb = (uint8_t *)a.y;
+        const size_t ro = ((size_t)n * a.nb_dst + a.b0 + ob) * So + vo;
+        if (a.y_split) {
+            const size_t hp = ((size_t)n * a.nb_dst + a.b0 + ob) * 2;
+            *(uint4 *)(yb + (hp * So + vo) * 16) = make_uint4(w[0], w[1], w[2], w[3]); *(uint4 *)(yb + ((hp + 1) * So + vo) * 16) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            uint4 *dst = (uint4 *)(yb + ro * 32);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]); dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        yb[(size_t)a.N * a.nb_dst * So * 32 + ro] = (uint8_t)sbyte;
+        return;
     }
     if (a.out_mode != UMX_OUT_PM32 && a.out_mode != UMX_OUT_MXRAW) {
 #pragma unroll

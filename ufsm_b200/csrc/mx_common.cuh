@@ -80,6 +80,36 @@ __device__ __forceinline__ float dec_e2m1(unsigned n) {
     const float v = (float)(k < 4u ? k : k == 4u ? 4u : k == 5u ? 6u : k == 6u ? 8u : 12u) * 0.5f;
     return (n & 8u) ? -v : v;
 }
+/* a row of 32 fp16 values (16 packed pairs) -> MX-fp8 codes w[0..8) and the scale byte; the same bytes as mx_encode_row32<8> of the
+   values converted to fp32.  amax, scaling and conversion stay on packed halves when the block scale 2^-e is a normal fp16 (the product
+   is then exact, or below 2^-14 where E4M3 rounds to zero either way); other rows take the fp32 path. */
+__device__ __forceinline__ unsigned mx_encode_row32_h8(const __half2 *h, unsigned *w) {
+    __half2 a2 = __habs2(h[0]);
+#pragma unroll
+    for (int k = 1; k < 16; k++) a2 = __hmax2_nan(a2, __habs2(h[k]));
+    const float am = __half2float(__hmax_nan(__low2half(a2), __high2half(a2)));
+    const int e = mx_exp(__uint_as_float(__float_as_uint(am) & 0x7fffffffu), 1.f / 448.f);
+    if (e >= -15 && e <= 14) {
+        const unsigned mh = (unsigned)(15 - e) << 10, m2 = mh | (mh << 16);
+        const __half2 mm = *(const __half2 *)&m2;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const __half2 s0 = __hmul2(h[2 * j], mm), s1 = __hmul2(h[2 * j + 1], mm);
+            unsigned short c0, c1;
+            asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c0) : "r"(*(const unsigned *)&s0));
+            asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(c1) : "r"(*(const unsigned *)&s1));
+            w[j] = (unsigned)c0 | ((unsigned)c1 << 16);
+        }
+    } else {
+        const float m = exp2i(-e);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float2 p0 = __half22float2(h[2 * j]), p1 = __half22float2(h[2 * j + 1]);
+            w[j] = cvt_e4m3x4(p0.x * m, p0.y * m, p1.x * m, p1.y * m);
+        }
+    }
+    return (unsigned)(e + 127) & 0xffu;
+}
 /* a row of 32 floats -> MX codes: q8 receives 32 bytes (BITS 8: w[0..8)) or 16 bytes (BITS 4: w[0..4)); returns the scale byte */
 template <int BITS> __device__ __forceinline__ unsigned mx_encode_row32(const float *v, unsigned *w) {
     unsigned am = 0u;
