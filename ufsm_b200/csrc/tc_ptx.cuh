@@ -15,16 +15,22 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+/* the same with a suspend-time hint: the hardware parks the thread until the phase completes or about `ns` nanoseconds have passed, so a
+   waiting warp issues one instruction per `ns` instead of spinning through the issue slots the working warps need */
+__device__ __forceinline__ uint32_t mbar_try_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok;
+}
 /* Bounded wait: gives up after `limit` clock cycles or as soon as another role of the block has raised *abort_flag.  Returns false
    on give-up; the caller records where and leaves its loop, so a protocol error ends the kernel instead of hanging the GPU. */
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
-    for (int spins = 0;; spins++) {
-        if (mbar_try(bar, parity)) return true;
+    for (;;) {
+        if (mbar_try_hint(bar, parity, 2000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > limit) return false;
-        if (spins > 4) __nanosleep(64);      /* a long wait backs off so that polling warps leave the issue slots and the shared-memory pipe to the others */
     }
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
