@@ -29,7 +29,8 @@ enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16
    efficient.  The graph keeps its fp8 tensors SPLIT; MX-fp4 rows are 16 bytes already, so both names mean the reference layout there.
    The scale plane follows the codes unchanged in either layout. */
 enum { UMX_LAYOUT_REF = 0, UMX_LAYOUT_SPLIT = 1 };
-enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2 };   /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
+enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2,     /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
+       UMX_FAST_STATS = 4 };                 /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue (fp32 per thread, see there) */
 
 /* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
 int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
@@ -110,6 +111,13 @@ void umx_conv_free(umx_conv *c);
    UMX_TCONV2 writes the 2D x 2H x 2W grid.  flags: UMX_X_SPLIT / UMX_Y_SPLIT (an fp8 input in the reference layout is re-laid into
    scratch first).  Returns 0, or -1 after latching an error. */
 int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags);
+/* the conv with a blocked fp16 output followed by InstanceNorm: y as UMX_OUT_H16B and coef [N][co][2] = (a, b) of the stored values
+   (k_in_coef, src/nn_xnet.cu:1565-1570), in one call; part: scratch of umx_stats_doubles doubles.  By default the sums are taken by the
+   fp64 statistics pass (exact to the last bits, independent of batch size and block partition).  With UMX_FAST_STATS the resident-weight
+   conv kernel takes them in its epilogue: fp32 per thread over the block's planes, fp64 across threads and blocks; the coefficients then
+   agree with the exact ones to about 1e-6 relative and depend on the batch size and the number of multiprocessors (a run is still
+   reproducible byte for byte in a fixed configuration). */
+int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags);
 size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */

@@ -167,6 +167,26 @@ def test_instance_norm_sums_and_apply(dev):
     c.free()
 
 
+@pytest.mark.parametrize("N,Ci,Co,D,H,W", [(2, 32, 32, 5, 20, 16), (1, 64, 64, 4, 16, 32), (2, 32, 96, 3, 9, 16), (1, 128, 64, 3, 16, 16), (2, 32, 96, 3, 19, 11)])
+def test_conv_with_fused_norm(dev, N, Ci, Co, D, H, W):
+    """umx_conv_fwd_norm: the stored tensor is the conv's; the coefficients are those of its fp64 statistics, exactly by default and up to
+    the fp32 partial sums of the conv's epilogue with UMX_FAST_STATS (the last shape takes the general kernel either way: exact)."""
+    S = D * H * W
+    x = synth.rng(71).standard_normal(N * Ci * S).astype(np.float32)
+    w, b = synth.kaiming(72, Co, Ci, 27), synth.bias(73, Co, 0.1)
+    mx, _ = oracle_conv("conv3", x, w, b, N, Ci, D, H, W, Co, 8)
+    c = G.Conv("conv3", w, b, Co, Ci, 8)
+    raw, _ = c.fwd(mx, N, D, H, W, G.OUT_H16B)
+    want = orc.in_coef(orc.in_sums(raw.view(np.float16).astype(np.float32), N, Co, S), N, Co, S)
+    y, coef = c.fwd_norm(mx, N, D, H, W)                      # default: the exact statistics pass
+    assert np.array_equal(y.view(np.uint16), raw.view(np.uint16)) and np.array_equal(coef, want)
+    for _ in range(2):          # sums in the conv's epilogue; twice: the ticket counters reset themselves
+        y, coef = c.fwd_norm(mx, N, D, H, W, fast=True)
+        assert np.array_equal(y.view(np.uint16), raw.view(np.uint16))
+        assert np.allclose(coef, want, rtol=2e-5, atol=2e-6), "max diff %g" % np.abs(coef - want).max()
+    c.free()
+
+
 def test_apply_space_to_depth_and_concat(dev):
     N, Cn, D, H, W = 1, 64, 4, 6, 8
     S = D * H * W

@@ -319,7 +319,9 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 int umx_conv_r_fits(const umx_conv *c);
 uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev);
-int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc, int N, int D, int H, int W, const EpiArgs &e);
+int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc, int N, int D, int H, int W, const EpiArgs &e,
+                   double *part, const float *gamma, const float *beta, float eps, float *coef);
+extern "C" void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, double *part, float *coef);
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part);
 uint8_t *umx_conv_p_prepare(const umx_conv *c, const float *w_dev);
 int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, int H, int W, const EpiArgs &e);
@@ -372,9 +374,11 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
 }
 extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); free(c); }
 int umx_stats_chunks(int D, int H, int W);
-extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { return (size_t)N * umx_stats_chunks(D, H, W) * (size_t)(ceil_div(co, 32) * 32) * 2; }
+/* room for 512 partial sums per (sample, channel): the statistics pass uses up to that many voxel chunks, the fused conv epilogue one per block */
+extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
-extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags) {
+struct NormArgs { const float *gamma, *beta; float eps; float *coef; };
+static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags, const NormArgs *nrm) {
     if (!umx_ready("umx_conv_fwd")) return -1;
     if (!c) { umx_latch_msg("umx_conv_fwd: no conv"); return -1; }
     if (part && (out_mode != UMX_OUT_H16B || c->kind == UMX_TCONV2)) { fprintf(stderr, "umx_conv_fwd: partial sums only with a blocked fp16 output of a plain conv\n"); abort(); }
@@ -423,12 +427,15 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     /* InstanceNorm statistics are a separate pass over the stored output (umx_in_part below) */
     if (!force_v1 && c->wr) {   /* resident weights: the persistent z-marching kernel, when the geometry allows */
         const int pid = umx_prof_open(flops);
-        const int rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e);
+        int rc = (nrm && (flags & UMX_FAST_STATS)) ? umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, part, nrm->gamma, nrm->beta, nrm->eps, nrm->coef) : 1;
+        const bool fused = rc == 0;
+        if (rc > 0) rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, nullptr, nullptr, nullptr, 0.f, nullptr);
         if (rc <= 0) {
             umx_prof_close(pid);
             g_umx_launches++;
             UMX_CK("umx_conv_fwd");
-            if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
+            if (rc == 0 && nrm && !fused) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
+            else if (rc == 0 && part && !nrm) umx_in_part(y, N, c->co, D, H, W, part);
             return rc;
         }
     }
@@ -439,7 +446,8 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
             umx_prof_close(pid);
             g_umx_launches++;
             UMX_CK("umx_conv_fwd");
-            if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
+            if (rc == 0 && nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
+            else if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
             return rc;
         }
     }
@@ -467,6 +475,19 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
 #endif
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");
-    if (part) umx_in_part(y, N, c->co, D, H, W, part);
+    if (nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
+    else if (part) umx_in_part(y, N, c->co, D, H, W, part);
     return 0;
+}
+extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags) {
+    return conv_fwd_impl(c, x, N, D, H, W, y, out_mode, out_bits, nb_dst, b0, part, flags, nullptr);
+}
+/* conv -> blocked fp16 y, and the InstanceNorm coefficients (a, b) per (sample, channel) of that stored tensor; part: scratch of
+   umx_stats_doubles doubles.  The resident-weight kernel takes the sums in its epilogue (fp32 per thread and sample, fp64 across threads and
+   blocks); the other kernels are followed by the statistics pass.  gamma / beta: device arrays or NULL (1 / 0). */
+extern "C" int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags) {
+    if (!part || !coef) { fprintf(stderr, "umx_conv_fwd_norm: part and coef are required\n"); abort(); }
+    if (c && c->kind == UMX_TCONV2) { fprintf(stderr, "umx_conv_fwd_norm: not for the transposed conv\n"); abort(); }
+    const NormArgs nrm = {gamma, beta, eps, coef};
+    return conv_fwd_impl(c, x, N, D, H, W, y, UMX_OUT_H16B, 0, 0, 0, part, flags, &nrm);
 }

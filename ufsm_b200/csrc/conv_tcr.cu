@@ -48,6 +48,10 @@ struct ConvRArgs {
     int tmem_cols, sfa_base, sfa_cols, sfb_base; /* TMEM: accumulator slots from 0, two A scale buffers, B scales */
     int off_rec, off_bias, off_w, off_ring;
     int fast_h16;                                /* output is the fp16 blocked tensor of a plain conv: the short epilogue */
+    /* InstanceNorm statistics taken in that epilogue (coef != NULL): per-thread fp32 sums of the stored fp16 values over the block's planes
+       of a sample, reduced once per sample and block into part [n][gcol][cop][2] (fp64); the last block of a column tile to finish turns
+       the partial sums into coefficients (a, b) per (sample, channel) */
+    double *part; float *coef; const float *gamma, *beta; float eps; int cop, off_red;
     const uint8_t *wr;
     EpiArgs e;
     int *err;
@@ -99,8 +103,11 @@ __device__ __forceinline__ Run next_run(const ConvRArgs &a, Piece &p) {
     return r;
 }
 
-template <int BITS>
-__global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap maps, const ConvRArgs a) {
+__device__ unsigned g_conv_tickets[64];      /* one per column tile; the block that draws the last ticket finalises and resets it */
+
+/* NCH: 32-channel chunks of the column tile (1: two blocks per multiprocessor and at most 128 registers; 2: one block, more registers) */
+template <int BITS, int NCH>
+__global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap maps, const ConvRArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t *bars = (uint64_t *)smem_raw;
     uint32_t *tmem_slot = (uint32_t *)(smem_raw + 768);
@@ -111,14 +118,14 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int R = a.ring, NS = a.nslot;
     /* barriers: tma[R] (codes + scale window landed), sf[R] (A scales laid out), empty[R], accumulator full / empty per slot, weights */
-    const uint32_t bar_tma = smem_u32(bars), bar_sf = bar_tma + 8 * R, bar_empty = bar_tma + 16 * R, bar_accf = bar_tma + 24 * R, bar_acce = bar_accf + 8 * kMaxSlots, bar_w = bar_acce + 8 * kMaxSlots;
+    const uint32_t bar_tma = smem_u32(bars), bar_sf = bar_tma + 8 * R, bar_empty = bar_tma + 16 * R, bar_accf = bar_tma + 24 * R, bar_acce = bar_accf + 8 * kMaxSlots, bar_w = bar_acce + 8 * kMaxSlots, bar_red = bar_w + 8;
     constexpr int NQ = BITS == 8 ? 3 : 5;                  /* A scale quads per stage */
     constexpr uint32_t TX = 5760u + (BITS == 8 ? 576u : 1152u);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < R; i++) { mbar_init(bar_tma + 8 * i, 1); mbar_init(bar_sf + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
         for (int i = 0; i < kMaxSlots; i++) { mbar_init(bar_accf + 8 * i, 1); mbar_init(bar_acce + 8 * i, 4); }
-        mbar_init(bar_w, 1);
+        mbar_init(bar_w, 1); mbar_init(bar_red, 128);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
     } else {
         /* ---------------- epilogue: one output plane of one tile at a time ---------------- */
         const int q4 = warp & 3, r = q4 * 32 + lane, ry = r >> 3, rx = r & 7;
-        const int nchunk = a.nt >> 5;
+        constexpr int nchunk = NCH;
         const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
         /* every slot starts zeroed and released */
         for (int sl = 0; sl < NS; sl++) {
@@ -304,24 +311,60 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
         if (lane == 0) for (int sl = 0; sl < NS; sl++) mbar_arrive(bar_acce + 8 * sl);     /* one arrival per warp: arrivals on one barrier serialise */
         int pcm = 0, pph = 0, pc = 0; bool dead = false;        /* pcm = plane count mod slots, pph = its wrap parity */
         const size_t S = (size_t)a.D * a.H * a.W;
+        const bool stats = a.coef != nullptr;
+        const int et = (int)threadIdx.x - 128, bcol = (int)blockIdx.x % a.gcol;
+        float ssum[NCH * 32], ssq[NCH * 32];
+#pragma unroll
+        for (int k = 0; k < NCH * 32; k++) { ssum[k] = 0.f; ssq[k] = 0.f; }
+        float *red = (float *)(smem_raw + a.off_red);          /* [4 warps][nt][2] */
+        uint32_t red_ph = 0;
+        /* the 128 epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync: after a give-up nobody is left waiting for good) */
+        auto esync = [&]() { mbar_arrive(bar_red); if (!mbar_wait(bar_red, red_ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 8, pc); dead = true; } red_ph ^= 1u; };
+        /* writes this block's sums of sample n (or zeros) */
+        auto flush = [&](int n, bool have) {
+            if (have) {
+#pragma unroll
+                for (int k = 0; k < NCH * 32; k++) {
+                    float s0 = ssum[k], q0 = ssq[k];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); q0 += __shfl_xor_sync(0xffffffffu, q0, o); }
+                    if (lane == 0) { red[(q4 * a.nt + k) * 2] = s0; red[(q4 * a.nt + k) * 2 + 1] = q0; }
+                    ssum[k] = 0.f; ssq[k] = 0.f;
+                }
+            }
+            esync();
+            if (et < a.nt) {
+                double s0 = 0.0, q0 = 0.0;
+                if (have) for (int w4 = 0; w4 < 4; w4++) { s0 += (double)red[(w4 * a.nt + et) * 2]; q0 += (double)red[(w4 * a.nt + et) * 2 + 1]; }
+                double *d = a.part + (((size_t)n * a.gcol + bcol) * a.cop + ctile * a.nt + et) * 2;
+                d[0] = s0; d[1] = q0;
+            }
+            esync();
+        };
+        int n_cur = -1, n_next = 0;                             /* sample being accumulated; first sample without an entry yet */
         KP(long long e_wait = 0; const long long e_t0 = clock64();)
         while (piece.u < piece.u1 && !dead) {
             const Run rn = next_run(a, piece);
             const int ox = (rn.txy % a.tiles_x) * 8 + rx, oy = (rn.txy / a.tiles_x) * 16 + ry;
             const bool row_ok = oy < a.H && ox < a.W;
+            if (stats && rn.n != n_cur) {
+                if (n_cur >= 0) { flush(n_cur, true); n_next = n_cur + 1; }
+                for (; n_next < rn.n; n_next++) flush(n_next, false);
+                n_cur = rn.n;
+            }
             for (int z = rn.zb; z < rn.ze && !dead; z++, pc++) {
                 const int slot = NS - 1 - pcm;
                 KP(const long long ew0 = clock64();)
                 if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc); dead = true; break; }
                 KP(e_wait += clock64() - ew0;)
                 tc_fence_after();
-                uint32_t rr[2][32];
+                uint32_t rr[NCH][32];
                 const uint32_t tcol = tlane + (uint32_t)(slot * a.nt);
                 tmem_ld32(tcol, rr[0]);
-                if (nchunk > 1) tmem_ld32(tcol + 32, rr[1]);
+                if (NCH > 1) tmem_ld32(tcol + 32, rr[NCH - 1]);
                 tmem_ld_wait();
                 tmem_zero32(tcol);
-                if (nchunk > 1) tmem_zero32(tcol + 32);
+                if (NCH > 1) tmem_zero32(tcol + 32);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -331,30 +374,64 @@ __global__ void __launch_bounds__(kThreadsR, 2) conv_mxr_k(const __grid_constant
                     if (row_ok) {
                         const size_t vo = ((size_t)z * a.H + oy) * a.W + ox;
 #pragma unroll
-                        for (int jc = 0; jc < 2; jc++) if (jc < nchunk) {
-                            uint4 *dst = (uint4 *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * nchunk + jc) * S + vo) * 4;
+                        for (int jc = 0; jc < NCH; jc++) {
+                            uint4 *dst = (uint4 *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * NCH + jc) * S + vo) * 4;
                             const float4 *bs = (const float4 *)(bias_s + jc * 32);
 #pragma unroll
                             for (int k = 0; k < 4; k++) {
                                 const float4 b0 = bs[2 * k], b1 = bs[2 * k + 1];
-                                const __half2 h0 = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 0]), b0.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 1]), b0.y));
-                                const __half2 h1 = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 2]), b0.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 3]), b0.w));
-                                const __half2 h2 = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 4]), b1.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 5]), b1.y));
-                                const __half2 h3 = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 6]), b1.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 7]), b1.w));
-                                dst[k] = make_uint4(*(const uint32_t *)&h0, *(const uint32_t *)&h1, *(const uint32_t *)&h2, *(const uint32_t *)&h3);
+                                __half2 h[4];
+                                h[0] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 0]), b0.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 1]), b0.y));
+                                h[1] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 2]), b0.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 3]), b0.w));
+                                h[2] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 4]), b1.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 5]), b1.y));
+                                h[3] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 6]), b1.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 7]), b1.w));
+                                dst[k] = make_uint4(*(const uint32_t *)&h[0], *(const uint32_t *)&h[1], *(const uint32_t *)&h[2], *(const uint32_t *)&h[3]);
+                                if (stats) {
+#pragma unroll
+                                    for (int t = 0; t < 4; t++) {
+                                        const float2 f = __half22float2(h[t]);          /* the stored values */
+                                        const int ch = jc * 32 + 8 * k + 2 * t;
+                                        ssum[ch] += f.x; ssq[ch] = __fmaf_rn(f.x, f.x, ssq[ch]); ssum[ch + 1] += f.y; ssq[ch + 1] = __fmaf_rn(f.y, f.y, ssq[ch + 1]);
+                                    }
+                                }
                             }
                         }
                     }
                 } else {
 #pragma unroll
-                    for (int jc = 0; jc < 2; jc++) if (jc < nchunk) {
+                    for (int jc = 0; jc < NCH; jc++) {
                         float v[32];
 #pragma unroll
                         for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[jc][k]);
-                        epi_chunk(a.e, rn.n, z, oy, ox, row_ok, ctile * nchunk + jc, v);
+                        epi_chunk(a.e, rn.n, z, oy, ox, row_ok, ctile * NCH + jc, v);
                     }
                 }
                 if (++pcm == NS) { pcm = 0; pph ^= 1; }
+            }
+        }
+        if (stats && !dead) {
+            if (n_cur >= 0) { flush(n_cur, true); n_next = n_cur + 1; }
+            for (; n_next < a.N; n_next++) flush(n_next, false);
+            /* the last block of this column tile to get here turns the partial sums into coefficients; the order of the additions is
+               fixed (block 0, 1, ...), so the result does not depend on which block came last */
+            volatile unsigned &last = *(volatile unsigned *)(smem_raw + 776);
+            __threadfence();
+            esync();
+            if (et == 0) { const unsigned tk = atomicAdd(&g_conv_tickets[ctile], 1u); last = tk == (unsigned)a.gcol - 1u; if (last) g_conv_tickets[ctile] = 0u; }
+            esync();
+            if (last) {
+                __threadfence();
+                for (int i = et; i < a.N * a.nt; i += 128) {
+                    const int n = i / a.nt, c = ctile * a.nt + i % a.nt;
+                    if (c >= a.e.co_real) continue;
+                    double s0 = 0.0, q0 = 0.0;
+                    const double *pp = a.part + ((size_t)n * a.gcol * a.cop + c) * 2;
+                    for (int t = 0; t < a.gcol; t++) { s0 += __ldcg(pp + (size_t)t * a.cop * 2); q0 += __ldcg(pp + (size_t)t * a.cop * 2 + 1); }
+                    const double m = s0 / (double)S, v = fmax(q0 / (double)S - m * m, 0.0);
+                    const float rs = (float)(1.0 / sqrt(v + (double)a.eps)), ca = __fmul_rn(rs, a.gamma ? a.gamma[c] : 1.f);
+                    a.coef[2 * ((size_t)n * a.e.co_real + c)] = ca;
+                    a.coef[2 * ((size_t)n * a.e.co_real + c) + 1] = __fmaf_rn(-(float)m, ca, a.beta ? a.beta[c] : 0.f);
+                }
             }
         }
         KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; })
@@ -455,7 +532,10 @@ uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev) {
 }
 /* x: MX tensor (fp8 in the split layout); m0: tensor map over its codes; enc: the driver's tensor-map encoder (for the scale plane).
    Returns 1 when this kernel does not apply to the geometry (the caller then takes the general kernel), 0 after a launch, -1 on error. */
-int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc_v, int N, int D, int H, int W, const EpiArgs &e) {
+/* coef != NULL (only with the blocked fp16 output): InstanceNorm coefficients are produced by the same launch; part then holds N x (blocks per
+   column tile, at most 512) x cop x 2 doubles of scratch */
+int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc_v, int N, int D, int H, int W, const EpiArgs &e,
+                   double *part, const float *gamma, const float *beta, float eps, float *coef) {
     typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     ConvRArgs a; memset(&a, 0, sizeof a);
@@ -468,10 +548,12 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     a.units = (long long)N * a.tiles * D;
     a.nquad = c->nquad;
     a.fast_h16 = e.out_mode == UMX_OUT_H16B && !e.tconv;
+    if (coef && (!a.fast_h16 || !part || g.ncol > 64)) return 1;
+    a.part = part; a.coef = coef; a.gamma = gamma; a.beta = beta; a.eps = eps; a.cop = c->cop;
     /* the codes and the scale window are TMA destinations (128-byte aligned) */
     a.offSW = 5888; a.offSFA = a.offSW + (c->bits == 8 ? 640 : 1152);
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
-    a.off_rec = 1024; a.off_bias = a.off_rec + 12 * 64; a.off_w = a.off_bias + 256; a.off_ring = (a.off_w + a.w_bytes + 1023) & ~1023;
+    a.off_rec = 1024; a.off_bias = a.off_rec + 12 * 64; a.off_red = 2048; a.off_w = 4096; a.off_ring = (a.off_w + a.w_bytes + 1023) & ~1023;
     int dev = 0, sms = 148; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     /* two blocks a multiprocessor when shared memory (113 KB each) and TMEM (256 columns each) allow */
@@ -485,7 +567,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     if (a.ring < 3) return 1;
     const long long slots = (long long)sms * (two ? 2 : 1) / g.ncol;      /* blocks per column tile */
     if (slots < 1) return 1;
-    a.gcol = (int)(a.units < slots ? a.units : slots);
+    a.gcol = (int)(a.units < slots ? a.units : slots); if (a.gcol > 512) a.gcol = 512;
     const int grid = a.gcol * g.ncol;
     const size_t S = (size_t)D * H * W;
     uint8_t *x_sc = (uint8_t *)x + (size_t)N * c->nkb * S * (c->bits == 8 ? 32 : 16);   /* the scale plane follows the codes in either layout */
@@ -502,15 +584,18 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     const size_t smem = (size_t)a.off_ring + (size_t)a.ring * a.stage_bytes;
     static int attr_set[16];
     if (!attr_set[dev & 15]) {
-        cudaError_t er = cudaFuncSetAttribute(conv_mxr_k<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t er = cudaFuncSetAttribute(conv_mxr_k<8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
         attr_set[dev & 15] = 1;
     }
 #ifdef UMX_KPROF
     a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
 #endif
-    if (c->bits == 8) umx_launch(conv_mxr_k<8>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a);
+    if (g.nt == 32) { if (c->bits == 8) umx_launch(conv_mxr_k<8, 1>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4, 1>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); }
+    else { if (c->bits == 8) umx_launch(conv_mxr_k<8, 2>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4, 2>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); }
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
       double t[15] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 15; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
