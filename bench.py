@@ -220,6 +220,16 @@ def run_gpu(args):
                 L.umx_prof_get(i, C.byref(t_ms), C.byref(t_fl))
                 per[nm][0] += t_ms.value
                 per[nm][1] += t_fl.value
+    # ---- the same network with MX-fp4 interior convs (configuration 4's network, one patch per GPU), reported beside the headline
+    u4 = G.Unet(G.make_cfg(P, CW, NH, (8, 4, 8)), synth.unet_weights(1, CW), B)
+    for _ in range(3):
+        L.umx_unet_forward(u4.h, xd.ptr, B, yd.ptr)
+    barrier()
+    L.umx_timer_start(timer)
+    for _ in range(args.steps):
+        L.umx_unet_forward(u4.h, xd.ptr, B, yd.ptr)
+    ms_fp4 = tmax(L.umx_timer_stop_ms(timer))
+    u4.free()
     clk.stop = True
     clk.join(2)
     ufsm_b200.check()
@@ -250,6 +260,8 @@ def run_gpu(args):
                      "level0_3x3x3_tflops": l0_tf, "all_conv_launches_tflops": all_tf, "conv_launches_per_step": n_conv,
                      "conv_share_of_step": ms_conv / max(psteps, 1) / (ms / args.steps)},
         "conv_layers_us": {k: round(v[0] / psteps * 1e3, 1) for k, v in per.items()},
+        "mxfp4_interior": {"workload": "config 4's network (interior convs MX-fp4 E2M1, first and last MX-fp8), one 128^3 patch per GPU per step",
+                           "ms_per_step": ms_fp4 / args.steps, "value": vox / (ms_fp4 * 1e-3), "unit": "voxels/s"},
     }
     if world == 1 and not args.no_cpu:
         v, dt, cores = cpu_sample(1, 0)
