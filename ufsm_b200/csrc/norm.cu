@@ -53,6 +53,11 @@ __global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, si
         }
     };
     size_t v = v0 + ph;
+    for (; v + 448 < v1; v += 512) {      /* eight loads in flight */
+        const uint4 r0 = __ldg(p + v * 4), r1 = __ldg(p + (v + 64) * 4), r2 = __ldg(p + (v + 128) * 4), r3 = __ldg(p + (v + 192) * 4);
+        const uint4 r4 = __ldg(p + (v + 256) * 4), r5 = __ldg(p + (v + 320) * 4), r6 = __ldg(p + (v + 384) * 4), r7 = __ldg(p + (v + 448) * 4);
+        add(r0); add(r1); add(r2); add(r3); add(r4); add(r5); add(r6); add(r7);
+    }
     for (; v + 192 < v1; v += 256) {
         const uint4 r0 = __ldg(p + v * 4), r1 = __ldg(p + (v + 64) * 4), r2 = __ldg(p + (v + 128) * 4), r3 = __ldg(p + (v + 192) * 4);
         add(r0); add(r1); add(r2); add(r3);
