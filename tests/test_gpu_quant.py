@@ -61,3 +61,10 @@ def test_wide32_one_channel(dev, bits):
     want = orc.pm_to_mx(x, 2, 1, 1, S, bits, 32)
     assert np.array_equal(G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True), want)
     assert np.array_equal(G.from_split(G.quantise_pm(x, 2, 1, 1, S, bits, wide32=True, layout=1), 1, 32, S, bits), want)   # the split layout holds the same bytes
+    # special values in a one-channel block (its own code path): zeros, subnormals, the largest fp16, inf and NaN
+    x2 = x.copy()
+    x2[:8] = np.array([0.0, -0.0, 6e-8, -6.1e-5, 65504.0, np.inf, -np.inf, np.nan], np.float16)
+    want2 = orc.pm_to_mx(x2, 2, 1, 1, S, bits, 32)
+    assert np.array_equal(G.quantise_pm(x2, 2, 1, 1, S, bits, wide32=True), want2)
+    # narrow rows (the reference's 8-wide block for C <= 8) with one channel
+    assert np.array_equal(G.quantise_pm(x2, 2, 1, 1, S, bits), orc.pm_to_mx(x2, 2, 1, 1, S, bits))

@@ -24,11 +24,24 @@ __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint
     const int nch = min(bw, C - blk * bw);
     for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v < S; v += (size_t)gridDim.x * blockDim.x) {
         const size_t i = row0 + v;
-        float r[32];
+        unsigned w[8]; unsigned sb;
+        if (nch == 1) {
+            /* a block with one real channel (a one-channel stem): the same bytes as the general path, without the 31 zero lanes */
+            const float x0 = ld_as_f32(xb + v);
+            const int e = mx_exp(__uint_as_float(__float_as_uint(x0) & 0x7fffffffu), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
+            const float m = exp2i(-e);
+            sb = (unsigned)(e + 127) & 0xffu;
+            const float z = 0.f * m;                     /* 0, or NaN for an inf / NaN block (scale byte 0xFF), as the general path gives */
+            const unsigned zc = BITS == 8 ? cvt_e4m3x4(z, z, z, z) : cvt_e2m1x8((const float[8]){z, z, z, z, z, z, z, z}, 1.f);
 #pragma unroll
-        for (int k = 0; k < 32; k++) r[k] = k < nch ? ld_as_f32(xb + (size_t)k * S + v) : 0.f;
-        unsigned w[8];
-        const unsigned sb = mx_encode_row32<BITS>(r, w);
+            for (int k = 1; k < 8; k++) w[k] = zc;
+            w[0] = BITS == 8 ? cvt_e4m3x4(x0 * m, z, z, z) : ((zc & ~0xfu) | (cvt_e2m1x2(x0 * m, z) & 0xfu));
+        } else {
+            float r[32];
+#pragma unroll
+            for (int k = 0; k < 32; k++) r[k] = k < nch ? ld_as_f32(xb + (size_t)k * S + v) : 0.f;
+            sb = mx_encode_row32<BITS>(r, w);
+        }
         uint8_t *p = y + i * rb;
         if (BITS == 8) {
             if (bw == 32 && split) {   /* two 16-byte planes per block: [n][blk][half][voxel][16 B] */
