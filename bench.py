@@ -230,6 +230,29 @@ def run_gpu(args):
         L.umx_unet_forward(u4.h, xd.ptr, B, yd.ptr)
     ms_fp4 = tmax(L.umx_timer_stop_ms(timer))
     u4.free()
+    # ---- optional: configuration 5's sliding window over a synthetic V^3 uint8 volume (128^3 patches, overlap 16, Gaussian blend on the
+    # device), the patch rows dealt to the ranks by z-slab; wall clock around umx_window_run including the host-side patch gather, the
+    # uploads and the download of this rank's blended planes
+    win = None
+    if args.window:
+        Vw = args.window
+        vol = synth.ct_u8(500, Vw ** 3)
+        w = L.umx_window_make(Vw, P, 16)
+        f, cnt, lo, hi = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        L.umx_window_share(C.byref(w), rank, world, C.byref(f), C.byref(cnt))
+        L.umx_window_extent(C.byref(w), f.value, cnt.value, C.byref(lo), C.byref(hi))
+        zext = max(hi.value - lo.value, 1)
+        acc_p, wsum_p = L.nn_malloc_host(NH * zext * Vw * Vw * 4), L.nn_malloc_host(zext * Vw * Vw * 4)      # pinned result buffers
+        barrier()
+        t0 = time.time()
+        rc = L.umx_window_run(u.h, C.byref(w), vol.ctypes.data, f.value, cnt.value, B, acc_p, wsum_p)
+        assert rc == 0, (L.lp_check() or b"").decode()
+        dt = tmax(time.time() - t0)
+        win = {"workload": "config 5: %d^3 uint8 volume, 128^3 patches, overlap 16, %d patches, z-slab shares over %d GPU(s)" % (Vw, w.npatch, world),
+               "seconds": dt, "value": Vw ** 3 / dt, "unit": "volume voxels/s", "patches_per_s": w.npatch / dt}
+        L.nn_free_host(acc_p)
+        L.nn_free_host(wsum_p)
+        del vol
     clk.stop = True
     clk.join(2)
     ufsm_b200.check()
@@ -260,6 +283,7 @@ def run_gpu(args):
                      "level0_3x3x3_tflops": l0_tf, "all_conv_launches_tflops": all_tf, "conv_launches_per_step": n_conv,
                      "conv_share_of_step": ms_conv / max(psteps, 1) / (ms / args.steps)},
         "conv_layers_us": {k: round(v[0] / psteps * 1e3, 1) for k, v in per.items()},
+        "sliding_window": win,
         "mxfp4_interior": {"workload": "config 4's network (interior convs MX-fp4 E2M1, first and last MX-fp8), one 128^3 patch per GPU per step",
                            "ms_per_step": ms_fp4 / args.steps, "value": vox / (ms_fp4 * 1e-3), "unit": "voxels/s"},
     }
@@ -280,6 +304,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ufsm_b200")
     ap.add_argument("--clock-interval", type=float, default=0.05, help="seconds between clock samples (NVML queries share a lock with kernel launches, so not too often)")
+    ap.add_argument("--window", type=int, default=0, help="also run the sliding window over a synthetic V^3 volume (configuration 5 uses 1024)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -49,6 +49,7 @@ void umx_event_free(void *ev);
 void umx_event_record(void *ev, void *stream);           /* stream NULL: the legacy default stream */
 void umx_stream_wait(void *stream, void *ev);
 void umx_stream_sync(void *stream);
+void umx_event_sync(void *ev);                           /* the host waits for the event */
 void umx_copy_async(void *dst, const void *src, size_t bytes, int to_device, void *stream);
 void *nn_malloc_host(size_t bytes);      /* pinned host memory (cudaHostAlloc) for the window scheduler's staging buffers */
 void nn_free_host(void *p);

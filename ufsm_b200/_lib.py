@@ -92,6 +92,7 @@ _SIG = {
     "umx_event_record": (None, [C.c_void_p, C.c_void_p]),
     "umx_stream_wait": (None, [C.c_void_p, C.c_void_p]),
     "umx_stream_sync": (None, [C.c_void_p]),
+    "umx_event_sync": (None, [C.c_void_p]),
     "umx_copy_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "umx_unet_flops": (C.c_double, [C.POINTER(UnetCfg)]),
     "umx_unet_launches": (C.c_long, [C.c_void_p]),

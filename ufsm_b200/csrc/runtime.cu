@@ -74,6 +74,7 @@ extern "C" void umx_event_free(void *ev) { if (ev) cudaEventDestroy((cudaEvent_t
 /* stream NULL = the legacy default stream */
 extern "C" void umx_event_record(void *ev, void *stream) { cudaError_t e = cudaEventRecord((cudaEvent_t)ev, (cudaStream_t)stream); if (e != cudaSuccess) umx_latch("umx_event_record", e); }
 extern "C" void umx_stream_wait(void *stream, void *ev) { cudaError_t e = cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0); if (e != cudaSuccess) umx_latch("umx_stream_wait", e); }
+extern "C" void umx_event_sync(void *ev) { cudaError_t e = cudaEventSynchronize((cudaEvent_t)ev); if (e != cudaSuccess) umx_latch("umx_event_sync", e); }
 extern "C" void umx_stream_sync(void *stream) { cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream); if (e != cudaSuccess) umx_latch("umx_stream_sync", e); }
 extern "C" void umx_copy_async(void *dst, const void *src, size_t bytes, int to_device, void *stream) {
     cudaError_t e = cudaMemcpyAsync(dst, src, bytes, to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream);

@@ -255,14 +255,19 @@ int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int fir
     { const double s = P / 8.0, c = (P - 1) / 2.0; for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
     float *w1d = nn_malloc((size_t)P * 4), *dacc = nn_malloc((size_t)nh * zext * plane * 4), *dws = nn_malloc((size_t)zext * plane * 4);
     float *logits = nn_malloc((size_t)batch * nh * PS * 4);
-    uint8_t *stage = nn_malloc_host((size_t)batch * PS);
-    if (!w1d || !dacc || !dws || !logits || !stage) { nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage); return -1; }
+    /* two pinned staging buffers: the host gathers the next batch of patches from the volume while the GPU forwards the current one; the
+       upload runs on the copy stream and is ordered against the default stream with events (as in umx_unet_submit_host) */
+    uint8_t *stage[2] = {nn_malloc_host((size_t)batch * PS), nn_malloc_host((size_t)batch * PS)};
+    if (!w1d || !dacc || !dws || !logits || !stage[0] || !stage[1] || pipe_init(u)) { nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]); return -1; }
     nn_h2d(w1d, w1d_h, (size_t)P * 4); nn_zero(dacc, (size_t)nh * zext * plane * 4); nn_zero(dws, (size_t)zext * plane * 4);
-    for (int p = first; p < first + count; p += batch) {
-        const int nb = p + batch <= first + count ? batch : first + count - p;
+    nn_sync();
+    long j = 0;
+    for (int p = first; p < first + count; p += batch, j++) {
+        const int nb = p + batch <= first + count ? batch : first + count - p, k = (int)(j & 1);
+        if (j >= 2) umx_event_sync(u->ev_up[k]);                 /* the staging buffer's upload of two batches ago has finished */
         for (int i = 0; i < nb; i++) {
             int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
-            uint8_t *dst = stage + (size_t)i * PS;
+            uint8_t *dst = stage[k] + (size_t)i * PS;
             for (int z = 0; z < P; z++) for (int y = 0; y < P; y++) {
                 const int gz = z0 + z, gy = y0 + y;
                 uint8_t *row = dst + ((size_t)z * P + y) * P;
@@ -272,16 +277,21 @@ int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int fir
                 if (nx < P) memset(row + nx, 0, (size_t)(P - nx));
             }
         }
-        nn_h2d(u->xu8, stage, (size_t)nb * PS);
-        umx_u8_to_h16(u->xu8, (size_t)nb * PS, u->x16);
+        umx_stream_wait(u->s_in, u->ev_used[k]);                 /* the device copy of two batches ago has been converted */
+        umx_copy_async(u->pxu8[k], stage[k], (size_t)nb * PS, 1, u->s_in);
+        umx_event_record(u->ev_up[k], u->s_in);
+        umx_stream_wait(nullptr, u->ev_up[k]);
+        umx_u8_to_h16(u->pxu8[k], (size_t)nb * PS, u->x16);
+        umx_event_record(u->ev_used[k], nullptr);
         forward(u, u->x16, nb, logits, UMX_F32);
         for (int i = 0; i < nb; i++) {
             int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
             umx_blend_add(logits + (size_t)i * nh * PS, UMX_F32, nh, P, V, zlo, zext, z0, y0, x0, w1d, dacc, dws);
         }
     }
+    umx_stream_sync(u->s_in);
     nn_d2h(acc, dacc, (size_t)nh * zext * plane * 4); nn_d2h(wsum, dws, (size_t)zext * plane * 4);
     nn_sync();
-    nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage);
+    nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]);
     return nn_check() ? -1 : 0;
 }
