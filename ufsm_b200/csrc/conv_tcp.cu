@@ -54,7 +54,9 @@ __device__ __forceinline__ void raise_p(const ConvPArgs &a, volatile int *abort_
     __threadfence_block();
 }
 
-template <int BITS>
+/* EPI: the output mode known at compile time (0: any, read from the arguments; 1: plane-major fp32; 2: plane-major fp16; 3: MX-fp8 split
+   layout; 4: the same through the transposed conv's scatter), so that the epilogue's code is only what that mode needs */
+template <int BITS, int EPI>
 __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap maps, const ConvPArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t *bars = (uint64_t *)smem_raw;
@@ -222,8 +224,12 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                 float v[32];
 #pragma unroll
                 for (int k = 0; k < 32; k++) v[k] = __uint_as_float(rr[k]);
-                KP(if (a.dbg & 1) { float sacc = 0.f; for (int k = 0; k < 32; k++) sacc += v[k]; if (sacc == 123.456f) ((float *)a.e.y)[0] = sacc; } else)
-                epi_chunk(a.e, n, (int)zu, (int)oyu, (int)(rem - oyu * Wu), (a.dbg & 2) ? false : row_ok, ntile * (a.ntp >> 5) + jc, v);
+                EpiArgs e = a.e;
+                if (EPI == 1) { e.out_mode = UMX_OUT_PM32; e.tconv = 0; }
+                if (EPI == 2) { e.out_mode = UMX_OUT_PM16; e.tconv = 0; }
+                if (EPI == 3) { e.out_mode = UMX_OUT_MX; e.out_bits = 8; e.y_split = 1; e.tconv = 0; }
+                if (EPI == 4) { e.out_mode = UMX_OUT_MX; e.out_bits = 8; e.y_split = 1; e.tconv = 1; }
+                epi_chunk(e, n, (int)zu, (int)oyu, (int)(rem - oyu * Wu), row_ok, ntile * (a.ntp >> 5) + jc, v);
             }
             KP(e_epi += clock64() - ew2;)
             if (++slot == NS) { slot = 0; sph ^= 1; }
@@ -342,8 +348,11 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     static int attr_set[16];
     if (!attr_set[dev & 15]) {
-        cudaError_t er = cudaFuncSetAttribute(conv_mxp_k<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxp_k<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t er = cudaSuccess;
+#define UMX_P_ATTR(B, E) if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxp_k<B, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
+        UMX_P_ATTR(8, 0); UMX_P_ATTR(8, 1); UMX_P_ATTR(8, 2); UMX_P_ATTR(8, 3); UMX_P_ATTR(8, 4);
+        UMX_P_ATTR(4, 0); UMX_P_ATTR(4, 1); UMX_P_ATTR(4, 2); UMX_P_ATTR(4, 3); UMX_P_ATTR(4, 4);
+#undef UMX_P_ATTR
         if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
         attr_set[dev & 15] = 1;
     }
@@ -354,7 +363,14 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     a.dbg = getenv("UMX_DBG") ? atoi(getenv("UMX_DBG")) : 0;
     a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
 #endif
-    if (c->bits == 8) umx_launch(conv_mxp_k<8>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a); else umx_launch(conv_mxp_k<4>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a);
+    int epi = 0;
+    if (e.out_mode == UMX_OUT_PM32 && !e.tconv) epi = 1;
+    else if (e.out_mode == UMX_OUT_PM16 && !e.tconv) epi = 2;
+    else if (e.out_mode == UMX_OUT_MX && e.out_bits == 8 && e.y_split) epi = e.tconv ? 4 : 3;
+#define UMX_P_GO(B, E) umx_launch(conv_mxp_k<B, E>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a)
+    if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; default: UMX_P_GO(8, 0); } }
+    else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; default: UMX_P_GO(4, 0); } }
+#undef UMX_P_GO
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
       double t[14] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 14; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
