@@ -217,6 +217,27 @@ def test_apply_scale_ranges(dev):
         assert np.array_equal(q, orc.blocked_to_mx(a, bits, N, Cn, S))
 
 
+def test_config2_mxfp4_down_up_pair(dev):
+    """BASELINE configuration 2 at full size: 1 x 64 x 96^3 fp16 N(0,1); a 2^3 stride-2 conv 64 -> 128 (to 48^3), then a 2^3 stride-2
+    transposed conv 128 -> 64 (back to 96^3) on the fp16 result; E2M1 operands with an E8M0 scale per 32 channels, fp32 accumulate.  Each
+    layer against the oracle on identical MX operands."""
+    N, Ci, Cm, D = 1, 64, 128, 96
+    S, Sc = D ** 3, (D // 2) ** 3
+    x = synth.rng(201).standard_normal(N * Ci * S).astype(np.float16).astype(np.float32)
+    w1, b1 = synth.kaiming(202, Cm, Ci, 8), synth.bias(203, Cm, 0.01)
+    mxs, want1 = oracle_conv("down2", x, w1, b1, N, Ci, D, D, D, Cm, 4)
+    got1 = run_pm32("down2", mxs, w1, b1, N, Ci, D, D, D, Cm, 4)
+    e1 = orc.rel_l2(got1, want1)
+    y = got1.astype(np.float16).astype(np.float32)                  # the fp16 output of the first layer feeds the second
+    w2, b2 = synth.kaiming(204, Ci, Cm, 8, transposed=True), synth.bias(205, Ci, 0.01)
+    mx2, want2 = oracle_conv("tconv2", y, w2, b2, N, Cm, D // 2, D // 2, D // 2, Ci, 4)
+    got2 = run_pm32("tconv2", mx2, w2, b2, N, Cm, D // 2, D // 2, D // 2, Ci, 4)
+    e2 = orc.rel_l2(got2, want2)
+    print("configuration 2: down rel-L2 %.3g, up rel-L2 %.3g" % (e1, e2))
+    assert got1.size == N * Cm * Sc and got2.size == N * Ci * S
+    assert e1 < TOL and e2 < TOL
+
+
 def test_lp_conv_fwd_f8_config1(dev):
     """BASELINE configuration 1 through the reference's entry point: 1 x 32 x 64^3 fp16 N(0,1), 32 -> 32, MX-fp8, fp16 output."""
     import ctypes as C
