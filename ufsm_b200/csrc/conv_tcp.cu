@@ -55,7 +55,7 @@ __device__ __forceinline__ void raise_p(const ConvPArgs &a, volatile int *abort_
 }
 
 /* EPI: the output mode known at compile time (0: any, read from the arguments; 1: plane-major fp32; 2: plane-major fp16; 3: MX-fp8 split
-   layout; 4: the same through the transposed conv's scatter), so that the epilogue's code is only what that mode needs */
+   layout; 4: the same through the transposed conv's scatter; 5, 6: MX-fp4 likewise), so that the epilogue's code is only what that mode needs */
 template <int BITS, int EPI>
 __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap maps, const ConvPArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -229,6 +229,8 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                 if (EPI == 2) { e.out_mode = UMX_OUT_PM16; e.tconv = 0; }
                 if (EPI == 3) { e.out_mode = UMX_OUT_MX; e.out_bits = 8; e.y_split = 1; e.tconv = 0; }
                 if (EPI == 4) { e.out_mode = UMX_OUT_MX; e.out_bits = 8; e.y_split = 1; e.tconv = 1; }
+                if (EPI == 5) { e.out_mode = UMX_OUT_MX; e.out_bits = 4; e.tconv = 0; }
+                if (EPI == 6) { e.out_mode = UMX_OUT_MX; e.out_bits = 4; e.tconv = 1; }
                 epi_chunk(e, n, (int)zu, (int)oyu, (int)(rem - oyu * Wu), row_ok, ntile * (a.ntp >> 5) + jc, v);
             }
             KP(e_epi += clock64() - ew2;)
@@ -350,8 +352,8 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     if (!attr_set[dev & 15]) {
         cudaError_t er = cudaSuccess;
 #define UMX_P_ATTR(B, E) if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxp_k<B, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
-        UMX_P_ATTR(8, 0); UMX_P_ATTR(8, 1); UMX_P_ATTR(8, 2); UMX_P_ATTR(8, 3); UMX_P_ATTR(8, 4);
-        UMX_P_ATTR(4, 0); UMX_P_ATTR(4, 1); UMX_P_ATTR(4, 2); UMX_P_ATTR(4, 3); UMX_P_ATTR(4, 4);
+        UMX_P_ATTR(8, 0); UMX_P_ATTR(8, 1); UMX_P_ATTR(8, 2); UMX_P_ATTR(8, 3); UMX_P_ATTR(8, 4); UMX_P_ATTR(8, 5); UMX_P_ATTR(8, 6);
+        UMX_P_ATTR(4, 0); UMX_P_ATTR(4, 1); UMX_P_ATTR(4, 2); UMX_P_ATTR(4, 3); UMX_P_ATTR(4, 4); UMX_P_ATTR(4, 5); UMX_P_ATTR(4, 6);
 #undef UMX_P_ATTR
         if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
         attr_set[dev & 15] = 1;
@@ -367,9 +369,10 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     if (e.out_mode == UMX_OUT_PM32 && !e.tconv) epi = 1;
     else if (e.out_mode == UMX_OUT_PM16 && !e.tconv) epi = 2;
     else if (e.out_mode == UMX_OUT_MX && e.out_bits == 8 && e.y_split) epi = e.tconv ? 4 : 3;
+    else if (e.out_mode == UMX_OUT_MX && e.out_bits == 4) epi = e.tconv ? 6 : 5;
 #define UMX_P_GO(B, E) umx_launch(conv_mxp_k<B, E>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a)
-    if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; default: UMX_P_GO(8, 0); } }
-    else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; default: UMX_P_GO(4, 0); } }
+    if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; case 5: UMX_P_GO(8, 5); break; case 6: UMX_P_GO(8, 6); break; default: UMX_P_GO(8, 0); } }
+    else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; case 5: UMX_P_GO(4, 5); break; case 6: UMX_P_GO(4, 6); break; default: UMX_P_GO(4, 0); } }
 #undef UMX_P_GO
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
