@@ -155,7 +155,8 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
         if (COEF && live[k]) { const float2 ab = __ldg(coef + (size_t)n * C + c); ca[k] = ab.x; cb[k] = ab.y; }
     }
     const float slope = act == 2 ? 0.01f : 1.f;           /* LeakyReLU as max(g, slope g); slope 1 leaves g as it is */
-    const size_t v0 = S * blockIdx.x / T, v1 = S * (blockIdx.x + 1) / T;
+    const int pow2 = S2D && !(W & (W - 1)) && !(H & (H - 1)), wsh = pow2 ? __ffs(W) - 1 : -1, hsh = pow2 ? __ffs(H) - 1 : 0;
+    const unsigned v0 = (unsigned)(S * blockIdx.x / T), v1 = (unsigned)(S * (blockIdx.x + 1) / T);      /* S < 2^31: 32-bit voxel indices in the loop */
     const uint4 *xp = x + ((size_t)n * nb + blk) * S * 4 + qd;
     uint4 *hp_out = hout ? hout + ((size_t)n * nb + blk) * S * 4 + qd : nullptr;
     const size_t drow = (size_t)n * nb_dst + b0 + blk;
@@ -167,14 +168,14 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
         else { qb = q + drow * S * 16 + qd * 4; qs = 16; }
     }
     uint8_t *qsc = q ? q + (size_t)N * nb_dst * S * RB + drow * S : nullptr;
-    for (size_t vb = v0; vb < v1; vb += 256) {
+    for (unsigned vb = v0; vb < v1; vb += 256) {
         /* four rows a thread per trip, their loads issued together */
         uint4 raws[4];
 #pragma unroll
-        for (int u = 0; u < 4; u++) { const size_t v = vb + u * 64 + ph; raws[u] = v < v1 ? __ldg(xp + v * 4) : make_uint4(0u, 0u, 0u, 0u); }
+        for (int u = 0; u < 4; u++) { const unsigned v = vb + u * 64 + ph; raws[u] = v < v1 ? __ldg(xp + (size_t)v * 4) : make_uint4(0u, 0u, 0u, 0u); }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const size_t v = vb + u * 64 + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
+            const unsigned v = vb + u * 64 + ph; const bool ok = v < v1;      /* all 32 lanes stay for the shuffles */
             const __half2 *hp = (const __half2 *)&raws[u];
             uint4 o; __half2 *op = (__half2 *)&o;
 #pragma unroll
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
                 if (!FULL) { if (!live[2 * k]) g0 = 0.f; if (!live[2 * k + 1]) g1 = 0.f; }
                 op[k] = __floats2half2_rn(g0, g1);
             }
-            if (hp_out && ok) hp_out[v * 4] = o;
+            if (hp_out && ok) hp_out[(size_t)v * 4] = o;
             /* amax of the stored fp16 values, NaN-propagating, taken on the halves (exact: the conversion to fp32 is monotonic) */
             __half2 a2 = __hmax2_nan(__hmax2_nan(__habs2(op[0]), __habs2(op[1])), __hmax2_nan(__habs2(op[2]), __habs2(op[3])));
             const __half a1 = __hmax_nan(__low2half(a2), __high2half(a2));
@@ -217,11 +218,13 @@ __global__ void __launch_bounds__(256) in_apply_k(const uint4 *__restrict__ x, c
             }
             if (!ok) continue;
             if (qb) {
-                if (BITS == 8) *(uint2 *)(qb + v * qs) = make_uint2(w0, w1); else *(unsigned *)(qb + v * qs) = w0;
+                if (BITS == 8) *(uint2 *)(qb + (size_t)v * qs) = make_uint2(w0, w1); else *(unsigned *)(qb + (size_t)v * qs) = w0;
                 if (qd == 0) qsc[v] = (uint8_t)sb;
             }
             if (S2D) {   /* space-to-depth copy: block (tap * nb + blk) at the coarse voxel */
-                const unsigned vu = (unsigned)v, xx = vu % (unsigned)W, t1 = vu / (unsigned)W, yy = t1 % (unsigned)H, zz = t1 / (unsigned)H;
+                unsigned xx, yy, zz;
+                if (wsh >= 0) { xx = v & ((1u << wsh) - 1u); const unsigned t1 = v >> wsh; yy = t1 & ((1u << hsh) - 1u); zz = t1 >> hsh; }      /* W and H powers of two */
+                else { xx = v % (unsigned)W; const unsigned t1 = v / (unsigned)W; yy = t1 % (unsigned)H; zz = t1 / (unsigned)H; }
                 const int tap = ((zz & 1) * 2 + (yy & 1)) * 2 + (xx & 1);
                 const size_t Sc = S / 8, vc = ((size_t)(zz >> 1) * (H >> 1) + (yy >> 1)) * (W >> 1) + (xx >> 1);
                 const size_t ro = (size_t)n * 8 * nb + tap * nb + blk;
