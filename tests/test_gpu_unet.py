@@ -79,6 +79,26 @@ def test_unet_queued_host_entry(dev):
     u.free()
 
 
+def test_back_to_back_forwards_never_stall(dev):
+    """Soak: several hundred full-size forwards queued without a host sync between them.  A protocol error inside a conv kernel shows up
+    as a bounded wait that gives up (two seconds, reported through lp_check); one such error was timing dependent and appeared about once
+    in a hundred forwards only when launches ran back to back."""
+    L = G.L()
+    P, cw = 128, [32, 64, 128, 256, 320]
+    u = G.Unet(G.make_cfg(P, cw), synth.unet_weights(21, cw), 1)
+    xd = ufsm_b200.DevBuf(data=ct_patch(22, P ** 3))
+    yd = ufsm_b200.DevBuf(7 * P ** 3 * 4)
+    t = L.umx_timer_new()
+    for r in range(30):
+        L.umx_timer_start(t)
+        for _ in range(10):
+            assert L.umx_unet_forward(u.h, xd.ptr, 1, yd.ptr) == 0
+        ms = L.umx_timer_stop_ms(t)
+        e = L.lp_check()
+        assert not e and ms < 500, "round %d: %.1f ms for 10 forwards; %s" % (r, ms, e)
+    u.free()
+
+
 def test_unet_full_size_properties(dev):
     """Configuration 3 (128^3 patch, widths 32/64/128/256/320): finite, deterministic, and translation-consistent in the batch."""
     P, cw = 128, [32, 64, 128, 256, 320]

@@ -268,10 +268,14 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             for (int i = 0; i < nst && ok; i++) {
                 const int my = (it & 1) == sfw, cs = s, cph = ph;
                 it++; if (++s == R) { s = 0; ph ^= 1; }
-                if (!my) continue;
+                /* Both warps pass every stage's barrier in order, also for the stages the other warp lays out.  A warp that skipped them could
+                   come back to a ring slot a whole round later before the slot's first load had landed; a parity wait for the second round
+                   on a barrier still in its first phase is satisfied at once (it reads as the phase before the first), and the warp would lay
+                   out, and signal, a stage that does not exist yet. */
                 KP(const long long gw0 = clock64();)
                 if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it); ok = false; break; }
                 KP(g_wait += clock64() - gw0;)
+                if (!my) continue;
                 uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
                 const uint8_t *sw = stg + a.offSW;
                 uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
