@@ -7,6 +7,7 @@ import pytest
 import gpu_util as G
 import orc
 import synth
+import ufsm_b200
 
 pytestmark = pytest.mark.gpu
 
