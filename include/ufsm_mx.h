@@ -42,6 +42,9 @@ void nn_d2h(void *dst, const void *src, size_t bytes);
 void nn_sync(void);
 const char *nn_check(void);              /* NULL, or the first error since the last call (same latch as lp_check) */
 const char *lp_check(void);              /* src/nn_lp.h:172 */
+/* self-test of the kernels' bounded waits (no counterpart in the reference): a one-block kernel waits at most limit_clocks on a barrier nobody
+   arrives on and gives up as a conv role would; 0 when it ran, and lp_check() then reports "bounded wait gave up" */
+int umx_wait_selftest(long long limit_clocks);
 void *umx_stream_new(void);               /* non-blocking copy stream, events and stream-ordered copies used by umx_unet_submit_host */
 void umx_stream_free(void *stream);
 void *umx_event_new(void);

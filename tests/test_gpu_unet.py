@@ -80,6 +80,20 @@ def test_unet_queued_host_entry(dev):
     u.free()
 
 
+def test_bounded_wait_reports_and_context_survives(dev):
+    """A wait that runs out (a barrier nothing arrives on, limit one millisecond) is reported through lp_check and leaves the context usable."""
+    L = G.L()
+    assert L.umx_wait_selftest(2000000) == 0
+    L.nn_sync()
+    e = (L.lp_check() or b"").decode()
+    assert "bounded wait gave up" in e and "producer at stage 123" in e, e
+    assert not L.lp_check()
+    P, cw = 16, [32, 64]
+    u = G.Unet(G.make_cfg(P, cw), synth.unet_weights(5, cw), 1)
+    assert np.isfinite(u.forward(ct_patch(6, P ** 3), 1)).all()          # the next kernels run as usual
+    u.free()
+
+
 def test_back_to_back_forwards_never_stall(dev):
     """Soak: several hundred full-size forwards queued without a host sync between them.  A protocol error inside a conv kernel shows up
     as a bounded wait that gives up (two seconds, reported through lp_check); one such error was timing dependent and appeared about once

@@ -85,6 +85,7 @@ _SIG = {
     "umx_unet_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_submit_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_wait": (C.c_int, [C.c_void_p]),
+    "umx_wait_selftest": (C.c_int, [C.c_longlong]),
     "umx_stream_new": (C.c_void_p, []),
     "umx_stream_free": (None, [C.c_void_p]),
     "umx_event_new": (C.c_void_p, []),

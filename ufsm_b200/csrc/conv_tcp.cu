@@ -47,9 +47,11 @@ struct ConvPArgs {
     int dbg;
 };
 
-__device__ __forceinline__ void raise_p(const ConvPArgs &a, volatile int *abort_flag, int code, int stage) {
-    if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)blockIdx.x; a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
-    if (!*abort_flag) atomicCAS(a.err + 4 + code, 0, stage + 1);
+/* a wait gave up (its own limit, or another role's abort flag): the first to get here names the block; every role of that block then leaves
+   where it stood (stage, barrier, parity), which the host prints */
+__device__ __forceinline__ void raise_p(const ConvPArgs &a, volatile int *abort_flag, int code, int stage, uint32_t bar_off = 0, uint32_t parity = 0) {
+    if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)blockIdx.x; a.err[2] = stage; a.err[3] = (int)threadIdx.x; __threadfence(); }
+    if (((volatile int *)a.err)[1] == (int)blockIdx.x && code < 8) { int *d = a.err + 16 + 4 * code; d[0] = stage; d[1] = (int)bar_off; d[2] = (int)parity; d[3] = 1; }
     *abort_flag = 1;
     __threadfence_block();
 }

@@ -69,9 +69,11 @@ struct StageRec {
 };
 static_assert(sizeof(StageRec) == 64, "stage record is 64 bytes");
 
-__device__ __forceinline__ void raise_r(const ConvRArgs &a, volatile int *abort_flag, int code, int stage) {
-    if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)blockIdx.x; a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
-    if (!*abort_flag) atomicCAS(a.err + 4 + code, 0, stage + 1);   /* which roles gave up on their own (not because another raised the flag), and where */
+/* a wait gave up (its own limit, or another role's abort flag): the first to get here names the block; every role of that block then leaves
+   where it stood (stage, barrier, parity), which the host prints */
+__device__ __forceinline__ void raise_r(const ConvRArgs &a, volatile int *abort_flag, int code, int stage, uint32_t bar_off = 0, uint32_t parity = 0) {
+    if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)blockIdx.x; a.err[2] = stage; a.err[3] = (int)threadIdx.x; __threadfence(); }
+    if (((volatile int *)a.err)[1] == (int)blockIdx.x && code < 8) { int *d = a.err + 16 + 4 * code; d[0] = stage; d[1] = (int)bar_off; d[2] = (int)parity; d[3] = 1; }
     *abort_flag = 1;
     __threadfence_block();
 }
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     const uint32_t g1 = (uint32_t)(dzf == 0 ? 0 : dzf == 1 ? a.goff1 : a.goff2), g2 = (uint32_t)(dzf + n1 == 1 ? a.goff1 : a.goff2);
                     for (int ki = 0; ki < a.nki; ki++) {
                         KP(const long long pw0 = clock64();)
-                        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 1, it); ok = false; break; }
+                        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 1, it, bar_empty + 8 * s - bar_tma, ph ^ 1); ok = false; break; }
                         KP(p_wait += clock64() - pw0;)
                         const bool kl = ki == a.nki - 1;
                         const uint32_t bk = b_lo0 + (uint32_t)ki * bstep9, sk = sfb_t0 + (uint32_t)ki * sfb_per_ki;
@@ -226,14 +228,14 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             KP(long long m_full = 0, m_acce = 0, m_issue = 0; const long long m_t0 = clock64();)
             while (ok) {
                 KP(const long long mw0 = clock64();)
-                if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 3, it); break; }
-                if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 2, it); break; }
+                if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 3, it, bar_sf + 8 * s - bar_tma, ph); break; }
+                if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 2, it, 8 * s, ph); break; }
                 KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
                 /* the whole record goes to registers before anything is committed: committing `empty` hands the stage, record included, back to the producer */
                 const uint4 *r = (const uint4 *)(recs + s);
                 const uint4 g1 = r[0], g2 = r[1], wc = r[2]; const uint32_t last = r[3].x;
                 if (wc.x) {   /* a plane that starts here: its slot must have been read out and zeroed by the epilogue */
-                    if (!mbar_wait(wc.x & 0x7fffffffu, wc.x >> 31, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 7, it); break; }
+                    if (!mbar_wait(wc.x & 0x7fffffffu, wc.x >> 31, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 7, it, (wc.x & 0x7fffffffu) - bar_tma, wc.x >> 31); break; }
                     if (wc.y && !mbar_wait(wc.y & 0x7fffffffu, wc.y >> 31, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 7, it); break; }
                 }
                 tc_fence_after();
@@ -273,7 +275,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                    on a barrier still in its first phase is satisfied at once (it reads as the phase before the first), and the warp would lay
                    out, and signal, a stage that does not exist yet. */
                 KP(const long long gw0 = clock64();)
-                if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it); ok = false; break; }
+                if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it, 8 * cs, cph); ok = false; break; }
                 KP(g_wait += clock64() - gw0;)
                 if (!my) continue;
                 uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             for (int z = rn.zb; z < rn.ze && !dead; z++, pc++) {
                 const int slot = NS - 1 - pcm;
                 KP(const long long ew0 = clock64();)
-                if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc); dead = true; break; }
+                if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc, bar_accf + 8 * slot - bar_tma, pph); dead = true; break; }
                 KP(e_wait += clock64() - ew0;)
                 tc_fence_after();
                 uint32_t rr[NCH][32];
@@ -491,6 +493,26 @@ __global__ void __launch_bounds__(128) prep_wr_k(const float *__restrict__ w, ui
 }
 
 }   // namespace
+
+/* Self-test of the bounded wait and of its report: one block waits, for `limit_clocks` at most, on a barrier that nobody arrives on, gives
+   up, and leaves the same record a conv role would (role code 1, stage 123).  Returns 0 when the kernel ran; lp_check() then holds the
+   "bounded wait gave up" message.  The context stays usable. */
+__global__ void wait_selftest_k(ConvRArgs a, long long limit) {
+    __shared__ uint64_t bar; __shared__ int abort_s;
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_s = 0; fence_barrier_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(smem_u32(&bar), 0, &abort_s, limit)) raise_r(a, &abort_s, 1, 123, 0, 0);
+}
+extern "C" int umx_wait_selftest(long long limit_clocks) {
+    if (!umx_ready("umx_wait_selftest")) return -1;
+    if (limit_clocks < 1 || limit_clocks > 2000000000ll) limit_clocks = 2000000;
+    ConvRArgs a; memset(&a, 0, sizeof a);
+    a.err = umx_errflag(); if (!a.err) return -1;
+    wait_selftest_k<<<1, 32>>>(a, limit_clocks);
+    g_umx_launches++;
+    UMX_CK("umx_wait_selftest");
+    return 0;
+}
 
 /* geometry of the weight image; 0 when the z-marching kernel cannot run this conv (3^3 only, one column tile of at most 64 channels,
    codes + scales resident in shared memory, B scales resident in TMEM beside at least four accumulator slots) */

@@ -99,20 +99,26 @@ void *umx_ws(int slot, size_t bytes) {
 int *umx_errflag(void) {
     int d = 0; cudaGetDevice(&d); d &= 15;
     if (!g_flag[d]) {
-        if (cudaMalloc(&g_flag[d], 64) != cudaSuccess) { umx_latch_msg("umx_errflag: cudaMalloc failed"); return nullptr; }
-        cudaMemset(g_flag[d], 0, 64);
+        if (cudaMalloc(&g_flag[d], 256) != cudaSuccess) { umx_latch_msg("umx_errflag: cudaMalloc failed"); return nullptr; }
+        cudaMemset(g_flag[d], 0, 256);
     }
     return g_flag[d];
 }
 int umx_errflag_read(void) {
     int *f = umx_errflag(); if (!f) return -1;
-    int h[16] = {0};
+    int h[64] = {0};
     cudaError_t e = cudaMemcpy(h, f, sizeof h, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) { umx_latch("umx_errflag_read", e); return -1; }
     if (h[0]) {
-        char b[384]; snprintf(b, sizeof b, "conv kernel: bounded wait gave up (code %d, block %d, stage %d, thread %d; per role 1 producer %d, 2 mma-tma %d, 3 mma-scales %d, 4 gather %d, 5 epilogue %d, 6 weights %d, 7 mma-slot %d)", h[0], h[1], h[2], h[3], h[5], h[6], h[7], h[8], h[9], h[10], h[11]);
+        /* h[0..3]: the first wait that gave up (role code, block, stage, thread).  h[16 + 4 r ..]: where each role r of that block stood when
+           it left its loop: stage, barrier (byte offset in the block's barrier array), parity; a stage counter far from the others' points
+           at the role that broke the protocol. */
+        static const char *role[8] = {"?", "producer", "mma-tma", "mma-scales", "gather", "epilogue", "weights", "mma-slot"};
+        char b[500]; int n = snprintf(b, sizeof b, "conv kernel: bounded wait gave up (code %d, block %d, stage %d, thread %d;", h[0], h[1], h[2], h[3]);
+        for (int r = 1; r < 8 && n < (int)sizeof b - 60; r++) if (h[16 + 4 * r + 3]) n += snprintf(b + n, sizeof b - n, " %s at stage %d on barrier +%d parity %d;", role[r], h[16 + 4 * r], h[16 + 4 * r + 1], h[16 + 4 * r + 2]);
+        snprintf(b + n, sizeof b - n, ")");
         umx_latch_msg(b);
-        cudaMemset(f, 0, 64);
+        cudaMemset(f, 0, 256);
     }
     return h[0];
 }
