@@ -94,20 +94,21 @@ def test_bounded_wait_reports_and_context_survives(dev):
     u.free()
 
 
-def test_back_to_back_forwards_never_stall(dev):
+@pytest.mark.parametrize("bits,N,rounds", [((8, 8, 8), 1, 30), ((8, 4, 8), 2, 10)])
+def test_back_to_back_forwards_never_stall(dev, bits, N, rounds):
     """Soak: several hundred full-size forwards queued without a host sync between them.  A protocol error inside a conv kernel shows up
     as a bounded wait that gives up (two seconds, reported through lp_check); one such error was timing dependent and appeared about once
     in a hundred forwards only when launches ran back to back."""
     L = G.L()
     P, cw = 128, [32, 64, 128, 256, 320]
-    u = G.Unet(G.make_cfg(P, cw), synth.unet_weights(21, cw), 1)
-    xd = ufsm_b200.DevBuf(data=ct_patch(22, P ** 3))
-    yd = ufsm_b200.DevBuf(7 * P ** 3 * 4)
+    u = G.Unet(G.make_cfg(P, cw, 7, bits), synth.unet_weights(21, cw), N)
+    xd = ufsm_b200.DevBuf(data=ct_patch(22, N * P ** 3))
+    yd = ufsm_b200.DevBuf(N * 7 * P ** 3 * 4)
     t = L.umx_timer_new()
-    for r in range(30):
+    for r in range(rounds):
         L.umx_timer_start(t)
         for _ in range(10):
-            assert L.umx_unet_forward(u.h, xd.ptr, 1, yd.ptr) == 0
+            assert L.umx_unet_forward(u.h, xd.ptr, N, yd.ptr) == 0
         ms = L.umx_timer_stop_ms(t)
         e = L.lp_check()
         assert not e and ms < 500, "round %d: %.1f ms for 10 forwards; %s" % (r, ms, e)
