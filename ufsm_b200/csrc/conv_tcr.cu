@@ -46,7 +46,7 @@ struct ConvRArgs {
     int ring, stage_bytes, offSW, offSFA;
     int w_bytes, w_codes, nquad, gt, goff1, goff2, nslot;
     int tmem_cols, sfa_base, sfa_cols, sfb_base; /* TMEM: accumulator slots from 0, two A scale buffers, B scales */
-    int off_rec, off_bias, off_w, off_ring;
+    int off_rec, off_bias, off_stage, off_w, off_ring;   /* off_stage: 2 KB per epilogue warp and 32-channel chunk, the fp16 output rows on their way to coalesced stores */
     int fast_h16;                                /* output is the fp16 blocked tensor of a plain conv: the short epilogue */
     /* InstanceNorm statistics taken in that epilogue (coef != NULL): per-thread fp32 sums of the stored fp16 values over the block's planes
        of a sample, reduced once per sample and block into part [n][gcol][cop][2] (fp64); the last block of a column tile to finish turns
@@ -107,8 +107,9 @@ __device__ __forceinline__ Run next_run(const ConvRArgs &a, Piece &p) {
 
 __device__ unsigned g_conv_tickets[64];      /* one per column tile; the block that draws the last ticket finalises and resets it */
 
-/* NCH: 32-channel chunks of the column tile (1: two blocks per multiprocessor and at most 128 registers; 2: one block, more registers) */
-template <int BITS, int NCH>
+/* NCH: 32-channel chunks of the column tile (1: two blocks per multiprocessor and at most 128 registers; 2: one block, more registers);
+   STATS: the epilogue also takes the InstanceNorm sums */
+template <int BITS, int NCH, bool STATS>
 __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap maps, const ConvRArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint64_t *bars = (uint64_t *)smem_raw;
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             const uint32_t sfb_t0 = tmem + (uint32_t)a.sfb_base, sfb_per_ki = (uint32_t)(a.nquad * a.gt * 4);
             int s = 0, ph = 0, it = 0; bool ok = true;
             int pos = NS - 1; uint32_t wp = 1u;           /* ring position and wrap parity of the newest plane started so far */
-            KP(long long p_wait = 0; const long long p_t0 = clock64();)
+            KP(long long p_wait = 0, p_rec = 0; const long long p_t0 = clock64();)
             while (piece.u < piece.u1 && ok) {
                 const Run rn = next_run(a, piece);
                 const bool last_run = piece.u >= piece.u1;
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     for (int ki = 0; ki < a.nki; ki++) {
                         KP(const long long pw0 = clock64();)
                         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 1, it, bar_empty + 8 * s - bar_tma, ph ^ 1); ok = false; break; }
-                        KP(p_wait += clock64() - pw0;)
+                        KP(p_wait += clock64() - pw0; const long long pw1 = clock64();)
                         const bool kl = ki == a.nki - 1;
                         const uint32_t bk = b_lo0 + (uint32_t)ki * bstep9, sk = sfb_t0 + (uint32_t)ki * sfb_per_ki;
                         uint4 *r = (uint4 *)(recs + s);
@@ -196,6 +197,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                         r[2] = make_uint4(ki == 0 ? w0 : 0u, ki == 0 ? w1 : 0u, kl ? c0 : 0u, kl ? c1 : 0u);
                         r[3] = make_uint4((last_run && zi == zhi && kl) ? 1u : 0u, 0u, 0u, 0u);
                         const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes), bar = bar_tma + 8 * s;
+                        KP(p_rec += clock64() - pw1;)
                         mbar_expect_tx(bar, TX);
                         /* codes: two 16-byte-wide planes (fp8: the halves of block ki; fp4: blocks 2 ki and 2 ki + 1), 18 rows of 10 voxels;
                            scale bytes: 18 rows of a 32-byte window per block */
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     }
                 }
             }
-            KP(a.prof[(size_t)blockIdx.x * 32 + 16] = p_wait; a.prof[(size_t)blockIdx.x * 32 + 17] = clock64() - p_t0; a.prof[(size_t)blockIdx.x * 32 + 24] = it;)
+            KP(a.prof[(size_t)blockIdx.x * 32 + 16] = p_wait; a.prof[(size_t)blockIdx.x * 32 + 17] = clock64() - p_t0; a.prof[(size_t)blockIdx.x * 32 + 24] = it; a.prof[(size_t)blockIdx.x * 32 + 8] = p_rec;)
         }
     } else if (warp == 1) {
         /* ---------------- MMA issue: one thread follows the records; a stage is straight-line code ---------------- */
@@ -317,11 +319,11 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
         if (lane == 0) for (int sl = 0; sl < NS; sl++) mbar_arrive(bar_acce + 8 * sl);     /* one arrival per warp: arrivals on one barrier serialise */
         int pcm = 0, pph = 0, pc = 0; bool dead = false;        /* pcm = plane count mod slots, pph = its wrap parity */
         const size_t S = (size_t)a.D * a.H * a.W;
-        const bool stats = a.coef != nullptr;
+        constexpr bool stats = STATS;
         const int et = (int)threadIdx.x - 128, bcol = (int)blockIdx.x % a.gcol;
-        float ssum[NCH * 32], ssq[NCH * 32];
+        float ssum[STATS ? NCH * 32 : 1], ssq[STATS ? NCH * 32 : 1];
 #pragma unroll
-        for (int k = 0; k < NCH * 32; k++) { ssum[k] = 0.f; ssq[k] = 0.f; }
+        for (int k = 0; k < (STATS ? NCH * 32 : 1); k++) { ssum[k] = 0.f; ssq[k] = 0.f; }
         float *red = (float *)(smem_raw + a.off_red);          /* [4 warps][nt][2] */
         uint32_t red_ph = 0;
         /* the 128 epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync: after a give-up nobody is left waiting for good) */
@@ -330,7 +332,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
         auto flush = [&](int n, bool have) {
             if (have) {
 #pragma unroll
-                for (int k = 0; k < NCH * 32; k++) {
+                for (int k = 0; k < (STATS ? NCH * 32 : 1); k++) {
                     float s0 = ssum[k], q0 = ssq[k];
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); q0 += __shfl_xor_sync(0xffffffffu, q0, o); }
@@ -347,12 +349,23 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             }
             esync();
         };
+        /* fp16 rows on their way out: a thread converts one voxel (64 bytes per 32 channels), the warp's 32 rows pass through 2 KB of shared
+           memory (16-byte chunk c of row r at chunk c ^ (r / 2 % 4): no bank conflicts either way) and leave as four stores of 512 contiguous
+           bytes each (the eight voxels of one tile row) instead of 32 scattered 16-byte pieces per store */
+        uint8_t *stg = smem_raw + a.off_stage + q4 * (2048 * NCH);
+        uint8_t *stg_w = stg + lane * 64; const int swz = (lane >> 1) & 3;
+        const uint8_t *stg_r = stg + (lane >> 2) * 64 + (lane & 3) * 16;
+        const int cl = (lane & 3) ^ ((lane >> 3) & 3);          /* the chunk this lane finds there */
+        const size_t plane_b = (size_t)a.H * a.W * 64, row_b = (size_t)a.W * 64;
         int n_cur = -1, n_next = 0;                             /* sample being accumulated; first sample without an entry yet */
-        KP(long long e_wait = 0; const long long e_t0 = clock64();)
+        KP(long long e_wait = 0, e_ld = 0, e_zero = 0, e_store = 0; const long long e_t0 = clock64();)
         while (piece.u < piece.u1 && !dead) {
             const Run rn = next_run(a, piece);
-            const int ox = (rn.txy % a.tiles_x) * 8 + rx, oy = (rn.txy / a.tiles_x) * 16 + ry;
+            const int x0t = (rn.txy % a.tiles_x) * 8, y0t = (rn.txy / a.tiles_x) * 16;
+            const int ox = x0t + rx, oy = y0t + ry;
             const bool row_ok = oy < a.H && ox < a.W;
+            const int sy = y0t + q4 * 4;                        /* first of the four tile rows this warp stores */
+            uint8_t *run_dst = (uint8_t *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * NCH) * S + (size_t)sy * a.W + x0t + (lane >> 2)) * 64 + cl * 16;
             if (stats && rn.n != n_cur) {
                 if (n_cur >= 0) { flush(n_cur, true); n_next = n_cur + 1; }
                 for (; n_next < rn.n; n_next++) flush(n_next, false);
@@ -362,48 +375,61 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                 const int slot = NS - 1 - pcm;
                 KP(const long long ew0 = clock64();)
                 if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc, bar_accf + 8 * slot - bar_tma, pph); dead = true; break; }
-                KP(e_wait += clock64() - ew0;)
+                KP(e_wait += clock64() - ew0; const long long ew1 = clock64();)
                 tc_fence_after();
                 uint32_t rr[NCH][32];
                 const uint32_t tcol = tlane + (uint32_t)(slot * a.nt);
                 tmem_ld32(tcol, rr[0]);
                 if (NCH > 1) tmem_ld32(tcol + 32, rr[NCH - 1]);
                 tmem_ld_wait();
+                KP(const long long ew2 = clock64(); e_ld += ew2 - ew1;)
                 tmem_zero32(tcol);
                 if (NCH > 1) tmem_zero32(tcol + 32);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_acce + 8 * slot);          /* the slot is free as soon as it is in registers and zeroed */
                 if (a.fast_h16) {
-                    /* fp16 blocked output [n][block][voxel][32]: bias, one rounding, four 16-byte stores per 32 channels */
-                    if (row_ok) {
-                        const size_t vo = ((size_t)z * a.H + oy) * a.W + ox;
+                    /* fp16 blocked output [n][block][voxel][32]: bias, one rounding; the zeroing of the slot completes meanwhile */
+                    __syncwarp();                               /* the previous plane's rows have been read out of the staging buffer */
 #pragma unroll
-                        for (int jc = 0; jc < NCH; jc++) {
-                            uint4 *dst = (uint4 *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * NCH + jc) * S + vo) * 4;
-                            const float4 *bs = (const float4 *)(bias_s + jc * 32);
+                    for (int jc = 0; jc < NCH; jc++) {
+                        const float4 *bs = (const float4 *)(bias_s + jc * 32);
 #pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const float4 b0 = bs[2 * k], b1 = bs[2 * k + 1];
-                                __half2 h[4];
-                                h[0] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 0]), b0.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 1]), b0.y));
-                                h[1] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 2]), b0.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 3]), b0.w));
-                                h[2] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 4]), b1.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 5]), b1.y));
-                                h[3] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 6]), b1.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 7]), b1.w));
-                                dst[k] = make_uint4(*(const uint32_t *)&h[0], *(const uint32_t *)&h[1], *(const uint32_t *)&h[2], *(const uint32_t *)&h[3]);
-                                if (stats) {
+                        for (int k = 0; k < 4; k++) {
+                            const float4 b0 = bs[2 * k], b1 = bs[2 * k + 1];
+                            __half2 h[4];
+                            h[0] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 0]), b0.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 1]), b0.y));
+                            h[1] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 2]), b0.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 3]), b0.w));
+                            h[2] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 4]), b1.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 5]), b1.y));
+                            h[3] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 6]), b1.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 7]), b1.w));
+                            *(uint4 *)(stg_w + jc * 2048 + ((k ^ swz) << 4)) = make_uint4(*(const uint32_t *)&h[0], *(const uint32_t *)&h[1], *(const uint32_t *)&h[2], *(const uint32_t *)&h[3]);
+                            if (STATS && row_ok) {
 #pragma unroll
-                                    for (int t = 0; t < 4; t++) {
-                                        const float2 f = __half22float2(h[t]);          /* the stored values */
-                                        const int ch = jc * 32 + 8 * k + 2 * t;
-                                        ssum[ch] += f.x; ssq[ch] = __fmaf_rn(f.x, f.x, ssq[ch]); ssum[ch + 1] += f.y; ssq[ch + 1] = __fmaf_rn(f.y, f.y, ssq[ch + 1]);
-                                    }
+                                for (int t = 0; t < 4; t++) {
+                                    const float2 f = __half22float2(h[t]);          /* the stored values */
+                                    const int ch = STATS ? jc * 32 + 8 * k + 2 * t : 0;
+                                    ssum[ch] += f.x; ssq[ch] = __fmaf_rn(f.x, f.x, ssq[ch]); ssum[ch + (STATS ? 1 : 0)] += f.y; ssq[ch + (STATS ? 1 : 0)] = __fmaf_rn(f.y, f.y, ssq[ch + (STATS ? 1 : 0)]);
                                 }
                             }
                         }
                     }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acce + 8 * slot);          /* the slot is free once it is in registers and zeroed */
+                    KP(const long long ew3 = clock64(); e_zero += ew3 - ew2;)
+                    uint8_t *pz = run_dst + (size_t)z * plane_b;
+#pragma unroll
+                    for (int jc = 0; jc < NCH; jc++) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint4 v = *(const uint4 *)(stg_r + jc * 2048 + i * 512);
+                            if (sy + i < a.H) *(uint4 *)(pz + (size_t)jc * S * 64 + (size_t)i * row_b) = v;
+                        }
+                    }
+                    KP(e_store += clock64() - ew3;)
                 } else {
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acce + 8 * slot);
 #pragma unroll
                     for (int jc = 0; jc < NCH; jc++) {
                         float v[32];
@@ -440,7 +466,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                 }
             }
         }
-        KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; })
+        KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; a.prof[(size_t)blockIdx.x * 32 + 9] = e_ld; a.prof[(size_t)blockIdx.x * 32 + 10] = e_zero; a.prof[(size_t)blockIdx.x * 32 + 11] = e_store; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -579,7 +605,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     /* the codes and the scale window are TMA destinations (128-byte aligned) */
     a.offSW = 5888; a.offSFA = a.offSW + (c->bits == 8 ? 640 : 1152);
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
-    a.off_rec = 1024; a.off_bias = a.off_rec + 12 * 64; a.off_red = 2048; a.off_w = 4096; a.off_ring = (a.off_w + a.w_bytes + 1023) & ~1023;
+    a.off_rec = 1024; a.off_bias = a.off_rec + 12 * 64; a.off_stage = 2048; a.off_red = a.off_stage; a.off_w = a.off_stage + 8192 * (g.nt == 32 ? 1 : 2); a.off_ring = (a.off_w + a.w_bytes + 1023) & ~1023;
     int dev = 0, sms = 148; cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     /* two blocks a multiprocessor when shared memory (113 KB each) and TMEM (256 columns each) allow */
@@ -610,22 +636,33 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     const size_t smem = (size_t)a.off_ring + (size_t)a.ring * a.stage_bytes;
     static int attr_set[16];
     if (!attr_set[dev & 15]) {
-        cudaError_t er = cudaFuncSetAttribute(conv_mxr_k<8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxr_k<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
+        const void *ks[8] = {(const void *)conv_mxr_k<8, 1, false>, (const void *)conv_mxr_k<8, 2, false>, (const void *)conv_mxr_k<4, 1, false>, (const void *)conv_mxr_k<4, 2, false>,
+                             (const void *)conv_mxr_k<8, 1, true>, (const void *)conv_mxr_k<8, 2, true>, (const void *)conv_mxr_k<4, 1, true>, (const void *)conv_mxr_k<4, 2, true>};
+        for (int i = 0; i < 8; i++) {
+            const cudaError_t er = cudaFuncSetAttribute(ks[i], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
+        }
         attr_set[dev & 15] = 1;
     }
 #ifdef UMX_KPROF
     a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
 #endif
-    if (g.nt == 32) { if (c->bits == 8) umx_launch(conv_mxr_k<8, 1>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4, 1>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); }
-    else { if (c->bits == 8) umx_launch(conv_mxr_k<8, 2>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); else umx_launch(conv_mxr_k<4, 2>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); }
+    const int variant = (coef ? 4 : 0) | (c->bits == 8 ? 0 : 2) | (g.nt == 32 ? 0 : 1);
+    switch (variant) {
+    case 0: umx_launch(conv_mxr_k<8, 1, false>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 1: umx_launch(conv_mxr_k<8, 2, false>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 2: umx_launch(conv_mxr_k<4, 1, false>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 3: umx_launch(conv_mxr_k<4, 2, false>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 4: umx_launch(conv_mxr_k<8, 1, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 5: umx_launch(conv_mxr_k<8, 2, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    case 6: umx_launch(conv_mxr_k<4, 1, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    default: umx_launch(conv_mxr_k<4, 2, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
+    }
 #ifdef UMX_KPROF
     { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
       double t[15] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 15; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
       long long mx = 0; for (int b = 0; b < grid; b++) if (hb[b * 32 + 29] > mx) mx = hb[b * 32 + 29];
+      { double x[4] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 4; k++) x[k] += (double)hb[b * 32 + 8 + k] / grid; fprintf(stderr, "kprof+: producer record %.0f | epilogue ld %.0f zero %.0f store %.0f\n", x[0], x[1], x[2], x[3]); }
       fprintf(stderr, "kprof: grid %d units %lld ring %d slots %d tmem %d nki %d nt %d smem %zu | per block: stages %.0f planes %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f | prologue %.0f block %.0f = %.0f ns (max block %lld clk)\n",
               grid, a.units, a.ring, a.nslot, a.tmem_cols, a.nki, a.nt, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7], t[12], t[13], t[14], mx); }
 #endif
