@@ -54,6 +54,9 @@ CASES = [
     ("down2", 1, 64, 128, 2, 6, 10),
     ("tconv2", 1, 64, 32, 2, 9, 5),        # N = 8 x 32 columns, scattered
     ("tconv2", 1, 320, 256, 1, 4, 4),
+    ("conv3", 2, 256, 128, 3, 16, 16),     # a deep level: few tiles, eight input blocks split over the blocks of a tile
+    ("conv3", 1, 320, 320, 2, 8, 8),       # the bottleneck: ten input blocks, three column tiles
+    ("down2", 1, 256, 320, 4, 8, 8),       # K = 64 blocks in 16 stages, split
 ]
 
 
@@ -81,6 +84,20 @@ def test_conv_exact_operands_bit_identical(dev, kind, Ci, Co, D, H, W, bits):
     mx, want = oracle_conv(kind, x, w, b, 1, Ci, D, H, W, Co, bits)
     got = run_pm32(kind, mx, w, b, 1, Ci, D, H, W, Co, bits)
     assert np.array_equal(got, want), "%d of %d differ" % (np.count_nonzero(got != want), want.size)
+
+
+def test_k_split_is_batch_invariant(dev):
+    # the deep-level convs split K over several blocks per tile; the split is chosen per sample, so a sample's bytes do not depend on the batch
+    Ci, Co, D, H, W = 256, 256, 4, 16, 16
+    S = D * H * W
+    x = synth.rng(31).standard_normal(Ci * S).astype(np.float32)
+    w, b = synth.kaiming(32, Co, Ci, 27), synth.bias(33, Co, 0.1)
+    mx1 = orc.pm_to_mx(x, 0, 1, Ci, S, 8, 32)
+    mx2 = orc.pm_to_mx(np.concatenate([x, x]), 0, 2, Ci, S, 8, 32)
+    one = run_pm32("conv3", mx1, w, b, 1, Ci, D, H, W, Co, 8)
+    two = run_pm32("conv3", mx2, w, b, 2, Ci, D, H, W, Co, 8).reshape(2, -1)
+    assert np.array_equal(two[0], one.reshape(-1)) and np.array_equal(two[1], one.reshape(-1))
+    assert np.array_equal(one, run_pm32("conv3", mx1, w, b, 1, Ci, D, H, W, Co, 8))
 
 
 def test_reference_layout_input_and_output(dev):

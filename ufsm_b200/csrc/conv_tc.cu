@@ -49,10 +49,16 @@ struct ConvArgs {
     int items_max, ipq, nquad;      /* K items per stage, items per scale quad (4 fp8 / 2 fp4), quads per stage */
     const uint8_t *x_sc;
     const uint8_t *wpk;
+    /* K split: ksplit blocks share one output tile, each takes a contiguous range of the stages and leaves its fp32 accumulators in
+       ks_part [tile][split][32-column chunk][column quad][row][4] (a warp's 32 rows of one quad are 512 contiguous bytes); the block that draws the tile's last ticket adds the parts in split order and
+       runs the epilogue (no block waits for another; the order of the additions is fixed) */
+    int ksplit; float *ks_part; unsigned *ks_tickets;
     EpiArgs e;
     int *err;
     long long *prof;
 };
+
+__device__ unsigned g_ks_tickets[8192];      /* one per output tile of a split launch; the last block of a tile resets it */
 
 #ifdef UMX_KPROF
 #define KP1(...) __VA_ARGS__
@@ -76,18 +82,24 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
     uint8_t *stages = smem_raw + 1024;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int R = a.ring;
-    const uint32_t bar_tma = smem_u32(bars), bar_sf = bar_tma + 8 * R, bar_empty = bar_tma + 16 * R, bar_acc = bar_tma + 24 * R;
+    const uint32_t bar_tma = smem_u32(bars), bar_sf = bar_tma + 8 * R, bar_empty = bar_tma + 16 * R, bar_acc = bar_tma + 24 * R, bar_red = bar_acc + 8;
 
     const int txy = blockIdx.x, tx = txy % a.tiles_x, ty = txy / a.tiles_x;
     const int z = blockIdx.y;
-    const int n = blockIdx.z / a.ntiles_n, ntile = blockIdx.z % a.ntiles_n;
+    const int sp = (int)blockIdx.z % a.ksplit, bz = (int)blockIdx.z / a.ksplit;
+    const int n = bz / a.ntiles_n, ntile = bz % a.ntiles_n;
     const int x0 = tx * 8, y0 = ty * 16;
     const int n0 = ntile * a.nt, n_cur = min(a.nt, a.cop - n0);
-    const int nst = a.nst;
+    /* this block's stages: all of them, or its share (whole input items of a 3^3 conv, so that every share has a live stage) */
+    int st_lo = 0, st_hi = a.nst;
+    if (a.ksplit > 1) {
+        if (a.taps == 27) { st_lo = 3 * (a.nki * sp / a.ksplit); st_hi = 3 * (a.nki * (sp + 1) / a.ksplit); }
+        else { st_lo = a.nst * sp / a.ksplit; st_hi = a.nst * (sp + 1) / a.ksplit; }
+    }
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < R; i++) { mbar_init(bar_tma + 8 * i, 1); mbar_init(bar_sf + 8 * i, 128); mbar_init(bar_empty + 8 * i, 1); }
-        mbar_init(bar_acc, 1);
+        mbar_init(bar_acc, 1); mbar_init(bar_red, 128); mbar_init(bar_red + 8, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -109,8 +121,8 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
         if (lane == 0) {
             tma_prefetch_desc(&map0);
             int it = 0;
-            const uint8_t *wbase = a.wpk + (size_t)ntile * nst * a.w_stage_bytes;
-            for (int st = 0; st < nst; st++) {
+            const uint8_t *wbase = a.wpk + (size_t)ntile * a.nst * a.w_stage_bytes;
+            for (int st = st_lo; st < st_hi; st++) {
                 if (!stage_live(st)) continue;
                 const int s = it % R, ph = (it / R) & 1;
                 if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimit)) { raise(a, abort_flag, 1, st); break; }
@@ -144,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             const uint32_t idesc0 = BITS == 8 ? idesc_mxf8(n_cur, 0, 0) : idesc_mxf4(n_cur, 0, 0);
             const uint32_t bstep = (uint32_t)a.nt * 2;
             KP1(long long t_tma = 0, t_sf = 0, t_issue = 0; const long long t00 = clock64();)
-            for (int st = 0; st < nst && ok; st++) {
+            for (int st = st_lo; st < st_hi && ok; st++) {
                 if (!stage_live(st)) continue;
                 KP1(const long long k0 = clock64();)
                 if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 3, st); ok = false; break; }
@@ -185,7 +197,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
         const bool row_ok = oy < a.H && ox < a.W;
         const size_t S = (size_t)a.D * a.H * a.W;
         int it = 0; bool ok = true;
-        for (int st = 0; st < nst && ok; st++) {
+        for (int st = st_lo; st < st_hi && ok; st++) {
             if (!stage_live(st)) continue;
             const int s = it % R, ph = (it / R) & 1;
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimit)) { raise(a, abort_flag, 4, st); ok = false; break; }
@@ -232,10 +244,64 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             it++;
         }
         /* ---- epilogue ---- */
+        KP1(const long long e0 = clock64();)
         if (!mbar_wait(bar_acc, 0, abort_flag, kWaitLimit)) raise(a, abort_flag, 5, 0);
+        KP1(const long long e1 = clock64(); long long e2 = e1, e3 = e1;)
         tc_fence_after();
-        if (!*abort_flag) {
-            const int nchunk = n_cur >> 5;
+        const int nchunk = n_cur >> 5;
+        if (!*abort_flag && a.ksplit > 1) {
+            const size_t tile_id = ((size_t)bz * a.D + z) * gridDim.x + txy;
+            const size_t tile_f = (size_t)(a.nt >> 5) * 4096;                    /* floats of one part */
+            float *mine = a.ks_part + (tile_id * a.ksplit + sp) * tile_f + (size_t)r * 4;
+            for (int jc = 0; jc < nchunk; jc++) {
+                uint32_t rr[32];
+                tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(jc * 32), rr);
+                tmem_ld_wait();
+#pragma unroll
+                for (int k = 0; k < 8; k++) __stcg((uint4 *)(mine + (size_t)jc * 4096 + k * 512), make_uint4(rr[4 * k], rr[4 * k + 1], rr[4 * k + 2], rr[4 * k + 3]));
+            }
+            __threadfence();
+            KP1(e2 = clock64();)
+            volatile unsigned *last_s = (volatile unsigned *)(smem_raw + 264);
+            bool dead = false; uint32_t red_ph = 0;
+            /* the 128 epilogue threads meet on an mbarrier (a bounded wait) */
+            auto esync = [&]() { mbar_arrive(bar_red); if (!mbar_wait(bar_red, red_ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 6, 0); dead = true; } red_ph ^= 1u; };
+            esync();
+            if (r == 0) { const unsigned tk = atomicAdd(&a.ks_tickets[tile_id], 1u); const unsigned l = tk == (unsigned)a.ksplit - 1u; if (l) a.ks_tickets[tile_id] = 0u; *last_s = l; }
+            esync();
+            KP1(e3 = clock64();)
+            if (!dead && *last_s) {
+                /* the parts of one 32-column chunk (16 KB per split) come into the now idle stage ring with bulk copies, the next chunk's
+                   while this one goes through the epilogue: summing straight from global memory is a chain of L2 round trips */
+                __threadfence();
+                asm volatile("fence.proxy.async;" ::: "memory");
+                const uint32_t bar_ld = bar_red + 8;
+                const float *tile0 = a.ks_part + tile_id * a.ksplit * tile_f;
+                auto fetch = [&](int jc) {
+                    if (r == 0) {
+                        mbar_expect_tx(bar_ld, (uint32_t)a.ksplit * 16384u);
+                        for (int s2 = 0; s2 < a.ksplit; s2++) bulk_g2s(smem_u32(stages + (size_t)s2 * 16384), tile0 + (size_t)s2 * tile_f + (size_t)jc * 4096, 16384u, bar_ld);
+                    }
+                };
+                fetch(0);
+                for (int jc = 0; jc < nchunk && !dead; jc++) {
+                    if (!mbar_wait(bar_ld, (uint32_t)(jc & 1), abort_flag, kWaitLimit)) { raise(a, abort_flag, 7, jc); break; }
+                    float v[32];
+                    const float *p0 = (const float *)stages + (size_t)r * 4;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) { const float4 t = *(const float4 *)(p0 + k * 512); v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w; }
+                    for (int s2 = 1; s2 < a.ksplit; s2++) {
+                        const float *ps = p0 + (size_t)s2 * 4096;
+#pragma unroll
+                        for (int k = 0; k < 8; k++) { const float4 t = *(const float4 *)(ps + k * 512); v[4 * k] += t.x; v[4 * k + 1] += t.y; v[4 * k + 2] += t.z; v[4 * k + 3] += t.w; }
+                    }
+                    esync();                                   /* every thread has read the chunk: the ring may take the next one */
+                    if (dead) break;
+                    if (jc + 1 < nchunk) fetch(jc + 1);
+                    epi_chunk(a.e, n, z, oy, ox, row_ok, (n0 >> 5) + jc, v);
+                }
+            }
+        } else if (!*abort_flag) {
             for (int jc = 0; jc < nchunk; jc++) {
                 uint32_t rr[32];
                 tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(jc * 32), rr);
@@ -246,6 +312,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 epi_chunk(a.e, n, z, oy, ox, row_ok, (n0 >> 5) + jc, v);
             }
         }
+        KP1(if (threadIdx.x == 64) { long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[5] = e1 - e0; q[6] = e2 - e1; q[7] = clock64() - e3; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -392,7 +459,11 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     auto up128 = [](int v) { return (v + 127) & ~127; };
     a.offW = 0; a.offSFB = c->items_max * c->nt * 32; a.offA = up128(c->w_stage_bytes); a.offSFA = a.offA + up128(abytes);
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
-    const int budget = c->nt > 64 ? 200 * 1024 : 100 * 1024;   /* two blocks a multiprocessor for the narrow tiles */
+    int sms = 148; { int d0 = 0; cudaGetDevice(&d0); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d0); }
+    /* two blocks a multiprocessor (two issuing threads keep the tensor pipe busier than one) for the narrow tiles, and for the wide ones when
+       there are more blocks than multiprocessors; a deep ring for one block otherwise */
+    const long long blocks_all = (long long)a.tiles_x * a.tiles_y * D * N * a.ntiles_n;
+    const int budget = (c->nt > 64 && blocks_all <= sms) ? 200 * 1024 : 100 * 1024;
     a.ring = budget / a.stage_bytes; if (a.ring > 8) a.ring = 8; if (a.ring < 2) a.ring = 2;
     const size_t S = (size_t)D * H * W;
     const int rb = c->bits == 8 ? 32 : 16;
@@ -460,7 +531,30 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         if (e != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", e); return -1; }
         smem_set[dev] = 227 * 1024;
     }
-    const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n);
+    /* K split for the layers with fewer tiles than multiprocessors (the deep levels); chosen from one sample's geometry so that a sample's
+       result does not depend on the batch it is in */
+    a.ksplit = 1;
+    {
+        static int no_split = -1;
+        if (no_split < 0) { const char *ev = getenv("UMX_KSPLIT"); no_split = ev && *ev == '0'; }
+        const long long blocks1 = (long long)a.tiles_x * a.tiles_y * D * a.ntiles_n, tiles_all = blocks1 * N;
+        const int units = c->taps == 27 ? c->nki : c->nst;
+        long long ks = blocks1 > 0 ? sms / blocks1 : 1;
+        if (ks > units) ks = units;
+        if (ks > c->nst / 6) ks = c->nst / 6;              /* at least six stages a share: shorter shares cost more in the reduction than they save */
+        if (ks > 16) ks = 16;
+        /* the parts of a chunk are summed from the stage ring; the bound is that of the shallow ring, whatever ring this launch has, so that
+           the split does not change with the batch */
+        { int rs = 100 * 1024 / a.stage_bytes; if (rs > 8) rs = 8; if (rs < 2) rs = 2; const long long cap = (long long)rs * a.stage_bytes / 16384; if (ks > cap) ks = cap; }
+        if (!no_split && ks >= 2 && tiles_all <= 8192) {
+            const size_t bytes = (size_t)tiles_all * (size_t)ks * (size_t)(c->nt >> 5) * 4096 * 4;
+            void *ws = umx_ws(5, bytes);
+            if (!ws) return -1;
+            if (cudaGetSymbolAddress((void **)&a.ks_tickets, g_ks_tickets) != cudaSuccess) { umx_latch_msg("umx_conv_fwd: ticket array"); return -1; }
+            a.ksplit = (int)ks; a.ks_part = (float *)ws;
+        }
+    }
+    const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n * a.ksplit);
 #ifdef UMX_KPROF
     const size_t nblk = (size_t)grid.x * grid.y * grid.z;
     a.prof = (long long *)umx_ws(7, nblk * 64); cudaMemset(a.prof, 0, nblk * 64);
@@ -470,8 +564,8 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     umx_prof_close(pid);
 #ifdef UMX_KPROF
     { long long *hb = (long long *)malloc(nblk * 64); cudaMemcpy(hb, a.prof, nblk * 64, cudaMemcpyDeviceToHost);
-      double t[5] = {0}; for (size_t b = 0; b < nblk; b++) for (int k = 0; k < 5; k++) t[k] += (double)hb[b * 8 + k] / nblk;
-      fprintf(stderr, "kprof-v1: grid %u x %u x %u ring %d nst %d nt %d stage_bytes %d | mma thread: stages %.0f total %.0f wait-tma %.0f wait-sf %.0f issue %.0f\n", grid.x, grid.y, grid.z, a.ring, a.nst, a.nt, a.stage_bytes, t[4], t[3], t[0], t[1], t[2]); free(hb); }
+      double t[8] = {0}; long long mx7 = 0; for (size_t b = 0; b < nblk; b++) { for (int k = 0; k < 8; k++) t[k] += (double)hb[b * 8 + k] / nblk; if (hb[b * 8 + 7] > mx7) mx7 = hb[b * 8 + 7]; }
+      fprintf(stderr, "kprof-v1: grid %u x %u x %u ksplit %d ring %d nst %d nt %d stage_bytes %d | mma thread: stages %.0f total %.0f wait-tma %.0f wait-sf %.0f issue %.0f | epilogue: wait-acc %.0f part-store %.0f tail %.0f (max %lld)\n", grid.x, grid.y, grid.z, a.ksplit, a.ring, a.nst, a.nt, a.stage_bytes, t[4], t[3], t[0], t[1], t[2], t[5], t[6], t[7], mx7); free(hb); }
 #endif
     g_umx_launches++;
     UMX_CK("umx_conv_fwd");
