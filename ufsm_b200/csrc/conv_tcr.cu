@@ -619,6 +619,9 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     if (a.ring < 3) return 1;
     const long long slots = (long long)sms * (two ? 2 : 1) / g.ncol;      /* blocks per column tile */
     if (slots < 1) return 1;
+    /* A block pays two halo planes per run: with fewer than eight planes a block (counted for one sample, so that the choice of kernel does not
+       depend on the batch) the general kernel is faster.  Volumes with fewer planes than blocks are left here: nothing to gain either way. */
+    { const long long units1 = (long long)a.tiles * D; if (units1 >= slots && units1 < 8 * slots) return 1; }
     a.gcol = (int)(a.units < slots ? a.units : slots); if (a.gcol > 512) a.gcol = 512;
     const int grid = a.gcol * g.ncol;
     const size_t S = (size_t)D * H * W;
