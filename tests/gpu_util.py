@@ -7,7 +7,7 @@ import orc
 import ufsm_b200
 from ufsm_b200 import DevBuf
 
-KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3}
+KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
 OUT_H16B, OUT_MX, OUT_PM32, OUT_PM16, OUT_MXRAW = 0, 1, 2, 3, 4
 
 
@@ -73,6 +73,8 @@ class Conv:
         flags = 3 if split else 0
         f = 8 if self.kind == "tconv2" else 1
         So = D * H * W * f
+        if self.kind == "conv3s2":      # D, H, W are the input grid
+            So = ((D + 1) // 2) * ((H + 1) // 2) * ((W + 1) // 2)
         nbo = nb_dst if nb_dst else orc.nb32(self.co)
         if out_mode == OUT_H16B:
             nbytes = N * nbo * So * 64

@@ -28,6 +28,9 @@ def oracle_conv(kind, x, w, b, N, Ci, D, H, W, Co, bits):
         acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 8, bits), b, Co, 2, 2, 0)
         mxs = orc.blocked_to_mx(orc.s2d_blocked(xb, N, Ci, D, H, W), bits, N, 8 * orc.nb32(Ci) * 32, S // 8)
         return mxs, orc.blocked_to_pm(acc, N, Co, S // 8)
+    if kind == "conv3s2":
+        acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, bits), b, Co, 3, 2, 1)
+        return mx, orc.blocked_to_pm(acc, N, Co, ((D + 1) // 2) * ((H + 1) // 2) * ((W + 1) // 2))
     acc = orc.tconv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 8, bits, layout=1), b, Co)
     return mx, orc.blocked_to_pm(acc, N, Co, 8 * S)
 
@@ -58,6 +61,13 @@ CASES = [
     ("conv3", 1, 320, 320, 2, 8, 8),       # the bottleneck: ten input blocks, three column tiles
     ("down2", 1, 256, 320, 4, 8, 8),       # K = 64 blocks in 16 stages, split
 ]
+S2_CASES = [
+    # N, Ci, Co, D, H, W of the input grid
+    (1, 32, 32, 8, 32, 16),                # even grid, one input block
+    (2, 64, 96, 5, 19, 11),                # odd grid (the last output voxel sees one input voxel and padding), two blocks, batch 2
+    (1, 40, 33, 4, 6, 10),                 # channel counts that are not multiples of 32
+    (1, 128, 256, 4, 16, 16),              # 108 K items, two column tiles, K split
+]
 
 
 @pytest.mark.parametrize("bits", [8, 4])
@@ -72,6 +82,43 @@ def test_conv_parity(dev, kind, N, Ci, Co, D, H, W, bits):
     assert np.isfinite(got).all()
     e = orc.rel_l2(got, want)
     assert e < TOL, "relative L2 %.3g" % e
+
+
+@pytest.mark.parametrize("N,Ci,Co,D,H,W", S2_CASES)
+def test_conv3_stride2_parity(dev, N, Ci, Co, D, H, W):
+    x = synth.rng(41).standard_normal(N * Ci * D * H * W).astype(np.float32)
+    w, b = synth.kaiming(42, Co, Ci, 27), synth.bias(43, Co, 0.1)
+    mx, want = oracle_conv("conv3s2", x, w, b, N, Ci, D, H, W, Co, 8)
+    got = run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, 8)
+    assert got.size == want.size and np.isfinite(got).all()
+    e = orc.rel_l2(got, want)
+    assert e < TOL, "relative L2 %.3g" % e
+    assert np.array_equal(got, run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, 8, split=False))    # reference-layout input
+
+
+def test_conv3_stride2_exact_operands_and_lp_entry(dev):
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp
+    Ci, Co, D, H, W = 64, 40, 6, 18, 9
+    x = exact_operands(51, (Ci, D, H, W), 0).reshape(-1)
+    w = exact_operands(52, (Co, Ci, 27), 1)
+    b = (synth.rng(53).integers(-8, 8, Co) * 0.5).astype(np.float32)
+    mx, want = oracle_conv("conv3s2", x, w, b, 1, Ci, D, H, W, Co, 8)
+    got = run_pm32("conv3s2", mx, w, b, 1, Ci, D, H, W, Co, 8)
+    assert np.array_equal(got, want), "%d of %d differ" % (np.count_nonzero(got != want), want.size)
+    # the reference's entry point: fp16 plane-major in and out
+    L = ufsm_b200.lib()
+    Do, Ho, Wo = (D + 1) // 2, (H + 1) // 2, (W + 1) // 2
+    x16 = x.astype(np.float16)
+    xd, wd, bd = DevBuf(data=x16), DevBuf(data=w), DevBuf(data=b)
+    yd = DevBuf(Co * Do * Ho * Wo * 2).fill(0xEE)
+    rc = L.lp_conv_fwd_s2_f8(xd.ptr, 2, Shape5(1, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, Shape5(1, Co, Do, Ho, Wo), Gnp())
+    ufsm_b200.check()
+    assert rc == 0
+    mx16 = orc.pm_to_mx(x16, 2, 1, Ci, D * H * W, 8, 32)
+    acc = orc.conv_blocked(orc.mx_to_blocked(mx16, 8, 1, Ci, D * H * W), 1, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, 8), b, Co, 3, 2, 1)
+    want16 = orc.blocked_to_pm(orc.round_h16(acc), 1, Co, Do * Ho * Wo)
+    assert np.array_equal(yd.download(np.float16).astype(np.float32), want16)
 
 
 @pytest.mark.parametrize("bits", [8, 4])

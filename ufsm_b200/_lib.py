@@ -65,6 +65,7 @@ _SIG = {
     "umx_mx32_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
     "umx_h16b_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "lp_conv_fwd_f8": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, Gnp, C.c_void_p, C.c_int, Split]),
+    "lp_conv_fwd_s2_f8": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, Shape5, Gnp]),
     "lp_conv_fwd_f4": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, Gnp, C.c_void_p, C.c_int, Split]),
     "lp_wmemo_clear": (None, []),
     "umx_conv_create": (C.c_void_p, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),

@@ -103,6 +103,10 @@ __device__ __forceinline__ float prep_src(const PrepArgs &p, int row, int tap, i
     if (kb >= p.nkb) return 0.f;
     if (p.kind == UMX_CONV3) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + tap] : 0.f; }
     if (p.kind == UMX_CONV1) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[(size_t)row * p.ci + ci] : 0.f; }
+    if (p.kind == UMX_CONV3S2) {   /* K block = tap * blocks(ci) + block */
+        const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
+        return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + t] : 0.f;
+    }
     if (p.kind == UMX_DOWN2) {   /* K block = sub-voxel tap * blocks(ci) + block */
         const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
         return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 8 + t] : 0.f;

@@ -53,6 +53,8 @@ struct ConvArgs {
        ks_part [tile][split][32-column chunk][column quad][row][4] (a warp's 32 rows of one quad are 512 contiguous bytes); the block that draws the tile's last ticket adds the parts in split order and
        runs the epilogue (no block waits for another; the order of the additions is fixed) */
     int ksplit; float *ks_part; unsigned *ks_tickets;
+    /* 3^3 stride-2 pad-1 conv: K item = (tap, input block), each item's A tile is its own strided TMA load from the input grid Di x Hi x Wi */
+    int s2, nbi, Di, Hi, Wi;
     EpiArgs e;
     int *err;
     long long *prof;
@@ -139,6 +141,10 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 } else {
                     for (int j = 0; j < items; j++) {
                         const int ki = 4 * st + j;
+                        if (a.s2) {   /* every second voxel of the input, starting at 2 v + tap - 1 (voxels outside the grid arrive as zeros: the padding) */
+                            const int tap = ki / a.nbi, blk = ki - tap * a.nbi;
+                            tma_load_5d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, 2 * x0 + tap % 3 - 1, 2 * y0 + (tap / 3) % 3 - 1, 2 * z + tap / 9 - 1, (n * a.nbi + blk) * 2);
+                        } else
                         tma_load_4d(smem_u32(sb + a.offA + j * 4096), &map0, bar, x0 * 16, y0, z, BITS == 8 ? (n * a.nkb + ki) * 2 : n * a.nkb + 2 * ki);
                     }
                 }
@@ -225,7 +231,13 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 const size_t vox = ((size_t)z * a.H + oy) * a.W + ox;
                 for (int j = 0; j < items; j++) {
                     const int ki = 4 * st + j;
-                    if (BITS == 8) {
+                    if (a.s2) {
+                        const int tap = ki / a.nbi, blk = ki - tap * a.nbi;
+                        const int iz = 2 * z + tap / 9 - 1, iy = 2 * oy + (tap / 3) % 3 - 1, ix = 2 * ox + tap % 3 - 1;
+                        const bool in = row_ok && iz >= 0 && iz < a.Di && iy >= 0 && iy < a.Hi && ix >= 0 && ix < a.Wi;
+                        const unsigned b = in ? a.x_sc[((size_t)n * a.nbi + blk) * ((size_t)a.Di * a.Hi * a.Wi) + ((size_t)iz * a.Hi + iy) * a.Wi + ix] : 127u;
+                        wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
+                    } else if (BITS == 8) {
                         const unsigned b = row_ok ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
                         wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
                     } else {
@@ -396,12 +408,12 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, in
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
     if (!umx_ready("umx_conv_create")) return nullptr;
-    if ((bits != 8 && bits != 4) || kind < 0 || kind > 3 || co < 1 || ci < 1) { fprintf(stderr, "umx_conv_create: bad arguments (kind %d, co %d, ci %d, bits %d)\n", kind, co, ci, bits); abort(); }
+    if ((bits != 8 && bits != 4) || kind < 0 || kind > 4 || co < 1 || ci < 1 || (kind == UMX_CONV3S2 && bits != 8)) { fprintf(stderr, "umx_conv_create: bad arguments (kind %d, co %d, ci %d, bits %d)\n", kind, co, ci, bits); abort(); }
     umx_conv *c = (umx_conv *)calloc(1, sizeof *c);
     c->kind = kind; c->co = co; c->ci = ci; c->bits = bits;
     c->taps = kind == UMX_CONV3 ? 27 : 1;
     const int nbi = ceil_div(ci, 32);
-    c->nkb = kind == UMX_DOWN2 ? 8 * nbi : nbi;
+    c->nkb = kind == UMX_DOWN2 ? 8 * nbi : kind == UMX_CONV3S2 ? 27 * nbi : nbi;   /* K blocks of the GEMM: (sub-voxel or tap) x input blocks */
     c->nki = bits == 8 ? c->nkb : ceil_div(c->nkb, 2);
     c->cob_t = ceil_div(co, 32);
     c->cop = (kind == UMX_TCONV2 ? 8 : 1) * c->cob_t * 32;
@@ -430,7 +442,7 @@ static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev,
 extern "C" umx_conv *umx_conv_create_dev(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) { return conv_build(kind, w_dev, bias_dev, co, ci, bits); }
 extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias, int co, int ci, int bits) {
     if (!umx_ready("umx_conv_create")) return nullptr;
-    const size_t nw = (size_t)co * ci * (kind == UMX_CONV3 ? 27 : kind == UMX_CONV1 ? 1 : 8);
+    const size_t nw = (size_t)co * ci * ((kind == UMX_CONV3 || kind == UMX_CONV3S2) ? 27 : kind == UMX_CONV1 ? 1 : 8);
     float *wd = (float *)nn_malloc(nw * 4), *bd = bias ? (float *)nn_malloc((size_t)co * 4) : nullptr;
     if (!wd || (bias && !bd)) { nn_free(wd); nn_free(bd); return nullptr; }
     nn_h2d(wd, w, nw * 4); if (bias) nn_h2d(bd, bias, (size_t)co * 4);
@@ -452,6 +464,11 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     if ((out_mode == UMX_OUT_MX || out_mode == UMX_OUT_MXRAW) && out_bits != 8 && out_bits != 4) { fprintf(stderr, "umx_conv_fwd: MX output needs out_bits 8 or 4\n"); abort(); }
     encode_fn enc = get_encode(); if (!enc) return -1;
     ConvArgs a; memset(&a, 0, sizeof a);
+    /* the stride-2 3^3 conv is given its input grid; its GEMM rows are the output grid ceil(D / 2) x ceil(H / 2) x ceil(W / 2) */
+    const bool s2 = c->kind == UMX_CONV3S2;
+    const int Dx = D, Hx = H, Wx = W, nbx = s2 ? c->nkb / 27 : c->nkb;          /* grid and 32-channel blocks of the tensor x */
+    const size_t Sx = (size_t)Dx * Hx * Wx;
+    if (s2) { D = (D + 1) / 2; H = (H + 1) / 2; W = (W + 1) / 2; a.s2 = 1; a.nbi = nbx; a.Di = Dx; a.Hi = Hx; a.Wi = Wx; }
     a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.taps = c->taps; a.bits = c->bits;
     a.cop = c->cop; a.nt = c->nt; a.ntiles_n = c->ntiles_n; a.tiles_x = ceil_div(W, 8); a.tiles_y = ceil_div(H, 16);
     a.w_stage_bytes = c->w_stage_bytes; a.nst = c->nst; a.items_max = c->items_max; a.ipq = c->ipq; a.nquad = c->nquad;
@@ -467,7 +484,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     a.ring = budget / a.stage_bytes; if (a.ring > 8) a.ring = 8; if (a.ring < 2) a.ring = 2;
     const size_t S = (size_t)D * H * W;
     const int rb = c->bits == 8 ? 32 : 16;
-    a.x_sc = (const uint8_t *)x + (size_t)N * c->nkb * S * rb;
+    a.x_sc = (const uint8_t *)x + (size_t)N * nbx * Sx * rb;
     a.wpk = c->wpk;
     a.e.N = N; a.e.D = D; a.e.H = H; a.e.W = W; a.e.cop = c->cop; a.e.bias = c->bias_p;
     a.e.out_mode = out_mode; a.e.out_bits = out_bits; a.e.tconv = c->kind == UMX_TCONV2; a.e.co_real = c->co; a.e.cob_t = c->cob_t;
@@ -477,13 +494,20 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     /* tensor map over the activation codes seen as 16-byte-wide planes [plane][z][y][x * 16 B]: fp8 in the split layout has two planes a
        block, fp4 one.  A box is (10 or 8 voxels) x (18 or 16 rows) x 1 plane of z x 2 planes; voxels outside the volume read as zero. */
     if (c->bits == 8 && !(flags & UMX_X_SPLIT)) {   /* reference layout: re-lay the codes into scratch first */
-        void *ws = umx_ws(1, umx_mx_bytes32(8, N, c->nkb * 32, S));
+        void *ws = umx_ws(1, umx_mx_bytes32(8, N, nbx * 32, Sx));
         if (!ws) return -1;
-        umx_mx_relayout(x, 8, N, c->nkb * 32, S, ws, UMX_LAYOUT_SPLIT);
-        x = ws; a.x_sc = (const uint8_t *)x + (size_t)N * c->nkb * S * 32;
+        umx_mx_relayout(x, 8, N, nbx * 32, Sx, ws, UMX_LAYOUT_SPLIT);
+        x = ws; a.x_sc = (const uint8_t *)x + (size_t)N * nbx * Sx * 32;
     }
     CUtensorMap m0; memset(&m0, 0, sizeof m0);
-    {
+    if (s2) {
+        /* [plane][z][y][x][16 B] with a traversal stride of two voxels along x and y: a box of 16 x 32 voxel positions delivers 8 x 16 voxels */
+        const cuuint64_t gd[5] = {16, (cuuint64_t)Wx, (cuuint64_t)Hx, (cuuint64_t)Dx, (cuuint64_t)N * nbx * 2};
+        const cuuint64_t gs[4] = {16, (cuuint64_t)Wx * 16, (cuuint64_t)Wx * Hx * 16, (cuuint64_t)Sx * 16};
+        const cuuint32_t box[5] = {16, 16, 32, 1, 2}, es[5] = {1, 2, 2, 1, 1};
+        const CUresult r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r0 != CUDA_SUCCESS) { char b[160]; snprintf(b, sizeof b, "umx_conv_fwd: cuTensorMapEncodeTiled failed (%d) for the stride-2 map of %d x %d x %d x %d, %d blocks", (int)r0, N, Dx, Hx, Wx, nbx); umx_latch_msg(b); return -1; }
+    } else {
         const cuuint32_t bx = c->taps == 27 ? 10 : 8, by = c->taps == 27 ? 18 : 16;
         const cuuint64_t gd[4] = {(cuuint64_t)W * 16, (cuuint64_t)H, (cuuint64_t)D, (cuuint64_t)N * c->nkb * (c->bits == 8 ? 2 : 1)};
         const cuuint64_t gs[3] = {(cuuint64_t)W * 16, (cuuint64_t)W * H * 16, (cuuint64_t)S * 16};
@@ -492,7 +516,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         if (r0 != CUDA_SUCCESS) { char b[160]; snprintf(b, sizeof b, "umx_conv_fwd: cuTensorMapEncodeTiled failed (%d) for %d x %d x %d x %d, %d blocks", (int)r0, N, D, H, W, c->nkb); umx_latch_msg(b); return -1; }
     }
     /* algorithmic work: 2 x output voxels x real input channels x real output channels x taps (no credit for padding) */
-    const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * (c->taps == 27 ? 27.0 : 1.0);
+    const double flops = 2.0 * (double)N * S * (c->kind == UMX_DOWN2 ? 8.0 : 1.0) * c->ci * (double)c->co * (c->kind == UMX_TCONV2 ? 8.0 : 1.0) * ((c->taps == 27 || s2) ? 27.0 : 1.0);
     static int force_v1 = -1;
     if (force_v1 < 0) { const char *ev = getenv("UMX_CONV_V1"); force_v1 = ev && *ev && *ev != '0'; }
     /* InstanceNorm statistics are a separate pass over the stored output (umx_in_part below) */

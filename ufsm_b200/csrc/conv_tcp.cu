@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(128) prep_wp_k(const PrepArgs p, uint8_t *wp, 
 
 struct PGeo { int ntp, ntiles, ngroups, nq, w_codes, w_bytes; };
 static int p_geometry(const umx_conv *c, PGeo *g) {
-    if (c->kind == UMX_CONV3) return 0;
+    if (c->kind == UMX_CONV3 || c->kind == UMX_CONV3S2) return 0;
     g->ntp = c->cop >= 64 ? 64 : 32; g->ntiles = (c->cop + g->ntp - 1) / g->ntp; g->ngroups = (c->nki + 3) / 4; g->nq = c->bits == 8 ? 1 : 2;
     g->w_codes = g->ntiles * c->nki * 2 * g->ntp * 16;
     g->w_bytes = g->w_codes + g->ntiles * g->ngroups * g->nq * 512;

@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             while (ok) {
                 KP(const long long mw0 = clock64();)
                 if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 3, it, bar_sf + 8 * s - bar_tma, ph); break; }
-                if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 2, it, 8 * s, ph); break; }
+                /* no wait on the stage's load barrier here: the gather warp passed it before it laid the scales out and arrived on bar_sf */
                 KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
                 /* the whole record goes to registers before anything is committed: committing `empty` hands the stage, record included, back to the producer */
                 const uint4 *r = (const uint4 *)(recs + s);

@@ -1,5 +1,5 @@
-/* The reference's conv entry points lp_conv_fwd_f8 / lp_conv_fwd_f4 (src/nn_lp.h:53-54) on top of the tcgen05 conv: same
-   signature, storage codes and error behaviour; the prepared weights are memoised under split_t.wkey as the reference's fp4
+/* The reference's conv entry points lp_conv_fwd_f8 / lp_conv_fwd_f4 / lp_conv_fwd_s2_f8 (src/nn_lp.h:53-54, 104) on top of the tcgen05
+   conv: same signature, storage codes and error behaviour; the prepared weights are memoised under split_t.wkey as the reference's fp4
    kernel does (src/lp_f4fwd.cuh:748-770). */
 #include "mx_common.cuh"
 #include <stdlib.h>
@@ -58,4 +58,34 @@ extern "C" int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w,
 }
 extern "C" int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
     return conv_fwd("lp_conv_fwd_f4", 4, x, xbf, xs, w, b, cout, y, ybf, gp, osum, Go, sp);
+}
+
+extern "C" int lp_conv_fwd_s2_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, shape5 ys, gnp_t gp) {
+    const char *fn = "lp_conv_fwd_s2_f8";
+    if (!umx_ready(fn)) return 0;
+    if (gp.G) not_built(fn, "the GroupNorm + SiLU input transform (gnp_t.G != 0)");
+    if (xs.c <= 16) not_built(fn, "an input of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (xbf != UMX_F16 && xbf != UMX_MX8) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX-fp8)\n", fn, xbf); abort(); }
+    if (ys.n != xs.n || ys.c != cout || ys.d != (xs.d + 1) / 2 || ys.h != (xs.h + 1) / 2 || ys.w != (xs.w + 1) / 2) {
+        fprintf(stderr, "%s: output shape %d x %d x %d x %d x %d does not follow from the input\n", fn, ys.n, ys.c, ys.d, ys.h, ys.w); abort();
+    }
+    int out_mode, out_bits = 0;
+    if (ybf == UMX_F16) out_mode = UMX_OUT_PM16;
+    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; if (cout <= 16) not_built(fn, "an MX output of 16 channels or fewer"); }
+    else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
+    else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
+    const size_t S = (size_t)xs.d * xs.h * xs.w;
+    const void *xq = x;
+    if (xbf == UMX_F16) {
+        void *ws = umx_ws(0, umx_mx_bytes32(8, xs.n, xs.c, S));
+        if (!ws) return 0;
+        umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, 8, UMX_LAYOUT_SPLIT);
+        xq = ws;
+    }
+    umx_conv *c = umx_conv_create_dev(UMX_CONV3S2, w, b, cout, xs.c, 8);
+    if (!c) return 0;
+    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xbf == UMX_F16 ? UMX_X_SPLIT : 0);
+    cudaDeviceSynchronize();
+    umx_conv_free(c);
+    return 0;
 }

@@ -13,7 +13,7 @@ import numpy as np
 import ufsm_b200
 from ufsm_b200 import DevBuf
 
-KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3}
+KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
 OUT = {"h16b": 0, "mx": 1, "pm32": 2}
 
 
@@ -22,7 +22,7 @@ def main():
     ap.add_argument("--kind", default="conv3", choices=list(KIND))
     ap.add_argument("--ci", type=int, default=32)
     ap.add_argument("--co", type=int, default=32)
-    ap.add_argument("--size", type=int, default=128, help="edge of the cubic grid of GEMM rows (the conv's input grid; for down2 the output grid)")
+    ap.add_argument("--size", type=int, default=128, help="edge of the cubic grid of GEMM rows (the conv's input grid; for down2 the output grid; for conv3s2 the input grid, output = half)")
     ap.add_argument("--bits", type=int, default=8)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--out", default="h16b", choices=list(OUT))
@@ -35,7 +35,7 @@ def main():
     rb = 32 * a.bits // 8
     rng = np.random.default_rng(0)
     x = np.concatenate([rng.integers(0, 120, nbi * S * rb, dtype=np.uint8), rng.integers(100, 130, nbi * S, dtype=np.uint8)])
-    taps = {"conv3": 27, "conv1": 1, "down2": 8, "tconv2": 8}[a.kind]
+    taps = {"conv3": 27, "conv1": 1, "down2": 8, "tconv2": 8, "conv3s2": 27}[a.kind]
     w = (rng.standard_normal((a.co, a.ci, taps)) * np.sqrt(2.0 / (a.ci * taps))).astype(np.float32)
     if a.kind == "tconv2":
         w = np.ascontiguousarray(w.transpose(1, 0, 2))
@@ -44,7 +44,8 @@ def main():
     f = 8 if a.kind == "tconv2" else 1
     nbo = (a.co + 31) // 32
     mode = OUT[a.out]
-    nbytes = {0: nbo * S * f * 64, 1: nbo * S * f * (rb + 1), 2: a.co * S * f * 4}[mode]
+    So = ((D + 1) // 2) ** 3 if a.kind == "conv3s2" else S * f
+    nbytes = {0: nbo * So * 64, 1: nbo * So * (rb + 1), 2: a.co * So * 4}[mode]
     xd, yd = DevBuf(data=x), DevBuf(nbytes)
     best, ms, fl = 1e30, C.c_double(), C.c_double()
     for _ in range(a.reps):
