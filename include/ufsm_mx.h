@@ -150,6 +150,15 @@ int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const f
    coef NULL: identity (a = 1, b = 0).  layout: UMX_LAYOUT_REF / UMX_LAYOUT_SPLIT of q and q_s2d. */
 void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout);
 
+/* ---- GroupNorm statistics of an MX tensor (src/nn_lp.h:175-176, src/lp_mx_gnsums.cu:9-106; finalise: src/nn_elem.cu:5-11).  x: device, xdt 3 / 4,
+   reference layout, more than 16 channels.  sums: device, 2 N G slots of 24 bytes (the reference's exact fixed point, src/gnacc.cuh:9-27:
+   fraction in 2^-64, signed integer part, count of non-finite terms), zeroed by the caller; slot 2 (n G + g) takes the sum and the next one
+   the sum of squares of group g of sample n over the voxels [v0, v1).  Returns 0, -1 when the combination is not covered (16 channels or
+   fewer; G > 64 or C % G != 0 as in the reference).  umx_gn_finalize: mean and 1 / sqrt(max(var, 0) + eps) of NG groups of len elements. ---- */
+int lp_gn_sums_mx(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1);
+int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0, int cnt);
+void umx_gn_finalize(const double *sums, int NG, size_t len, float eps, float *mean, float *rstd);
+
 /* ---- the BASELINE U-Net (five levels 32/64/128/256/320, two 3^3 convs + InstanceNorm + LeakyReLU 0.01 a level, 2^3 stride-2
    down convs, ConvTranspose k2 s2 up, concat (up | skip), 1^3 head) and the sliding-window scheduler ---- */
 typedef struct { int L; int cw[8]; int nh; int P; int bits_first, bits_mid, bits_last; } umx_unet_cfg;

@@ -68,3 +68,61 @@ def test_wide32_one_channel(dev, bits):
     assert np.array_equal(G.quantise_pm(x2, 2, 1, 1, S, bits, wide32=True), want2)
     # narrow rows (the reference's 8-wide block for C <= 8) with one channel
     assert np.array_equal(G.quantise_pm(x2, 2, 1, 1, S, bits), orc.pm_to_mx(x2, 2, 1, 1, S, bits))
+
+
+def _slots(raw):
+    """decode the three-word fixed-point slots: fraction in 2^-64, signed integer part, count of non-finite terms"""
+    w = raw.view(np.uint64).reshape(-1, 3)
+    v = w[:, 1].astype(np.int64).astype(np.float64) + w[:, 0].astype(np.float64) * 2.0 ** -64
+    v[w[:, 2] != 0] = np.nan
+    return v
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("N,Cn,Gn,S", [(1, 32, 8, 5000), (2, 64, 8, 4097), (1, 40, 5, 777), (2, 96, 32, 1300), (1, 64, 64, 2000)])
+def test_gn_sums_mx(dev, bits, N, Cn, Gn, S):
+    import ufsm_b200
+    from ufsm_b200 import DevBuf
+    L = ufsm_b200.lib()
+    x = (synth.rng(61).standard_normal(N * Cn * S) * 3 + 1.5).astype(np.float32)
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, bits, 32)
+    dq = orc.mx_to_pm(mx, bits, N, Cn, S, 32).astype(np.float64).reshape(N, Gn, -1)
+    want = np.stack([dq.sum(2), (dq * dq).sum(2)], 2).reshape(-1)
+    xd, sd = DevBuf(data=mx), DevBuf(N * Gn * 2 * 24).fill(0)
+    dt = 3 if bits == 8 else 4
+    cut = S // 3
+    assert L.lp_gn_sums_mx(xd.ptr, dt, N, Cn, Gn, S, sd.ptr, 0, cut) == 0          # two spatial parts accumulate into the same slots
+    assert L.lp_gn_sums_mx(xd.ptr, dt, N, Cn, Gn, S, sd.ptr, cut, S) == 0
+    ufsm_b200.check()
+    got = _slots(sd.download())
+    assert np.allclose(got, want, rtol=1e-13, atol=1e-9), np.abs(got - want).max()
+    # a second run gives the same words (integer adds: no dependence on the order of the blocks)
+    s2 = DevBuf(N * Gn * 2 * 24).fill(0)
+    L.lp_gn_sums_mx(xd.ptr, dt, N, Cn, Gn, S, s2.ptr, 0, cut); L.lp_gn_sums_mx(xd.ptr, dt, N, Cn, Gn, S, s2.ptr, cut, S)
+    assert np.array_equal(sd.download(), s2.download())
+    # finalise
+    md, rd = DevBuf(N * Gn * 4), DevBuf(N * Gn * 4)
+    ln = (Cn // Gn) * S
+    L.umx_gn_finalize(sd.ptr, N * Gn, ln, np.float32(1e-5), md.ptr, rd.ptr)
+    ufsm_b200.check()
+    m = want[0::2] / ln
+    v = np.maximum(want[1::2] / ln - m * m, 0)
+    assert np.allclose(md.download(np.float32), m.astype(np.float32), rtol=1e-6, atol=1e-7)
+    assert np.allclose(rd.download(np.float32), (1 / np.sqrt(v + 1e-5)).astype(np.float32), rtol=1e-6)
+    # unsupported combinations answer -1 as the reference does
+    assert L.lp_gn_sums_mx(xd.ptr, dt, N, Cn, 7 if Cn % 7 else 9, S, sd.ptr, 0, S) == -1
+
+
+def test_gn_sums_mx_non_finite(dev):
+    import ufsm_b200
+    from ufsm_b200 import DevBuf
+    L = ufsm_b200.lib()
+    N, Cn, Gn, S = 1, 64, 2, 1024
+    x = synth.rng(62).standard_normal(N * Cn * S).astype(np.float32)
+    x[5 * S + 17] = np.inf                    # channel 5 (group 0): its block's scale byte becomes 0xFF
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, 8, 32)
+    xd, sd = DevBuf(data=mx), DevBuf(N * Gn * 2 * 24).fill(0)
+    assert L.lp_gn_sums_mx(xd.ptr, 3, N, Cn, Gn, S, sd.ptr, 0, S) == 0
+    ufsm_b200.check()
+    got = _slots(sd.download())
+    assert np.isnan(got[0]) and np.isnan(got[1]) and np.isfinite(got[2]) and np.isfinite(got[3])
