@@ -88,15 +88,16 @@ void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);          
    src/lp_f4fwd.cu:30-51).  x: device, xbf 3 / 4 (MX, more than 16 channels so that rows are 32 wide) or 2 (fp16 plane-major,
    quantised to the conv's MX format first); w: device fp32 [cout][cin][27]; b: device fp32 [cout] or NULL; y: ybf 2 (fp16
    plane-major), 3 / 4 (MX, acc + bias requantised per 32 output channels) or UMX_H16B.  lp_conv_fwd_f8 multiplies E4M3 codes,
-   lp_conv_fwd_f4 E2M1 codes; an MX input of the other format aborts.  Supported subset: gp.G == 0, osum == NULL, and split_t
-   zero except wkey (prepared-weight memo key).  Anything else prints "not built" and aborts.  Returns 0. ---- */
+   lp_conv_fwd_f4 E2M1 codes; an MX input of the other format aborts.  gp.G != 0: the GroupNorm + SiLU input transform
+   silu(fma(x, rstd gamma, beta - mean rstd gamma)) (src/lp_common.cuh:244-261, 474-482), applied and quantised to the conv's format in a
+   pass ahead of the conv (x may then be fp32 / fp16 plane-major or either MX format).  Supported subset otherwise: osum == NULL, split_t
+   zero except wkey (prepared-weight memo key), no slab-local GroupNorm (gp.ns <= 1).  Anything else prints "not built" and aborts.  Returns 0. ---- */
 int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 void lp_wmemo_clear(void);               /* src/nn_lp.h:57: drop the prepared weights kept under split_t.wkey */
 /* 3x3x3 stride-2 pad-1 conv forward (src/nn_lp.h:104; src/lp_s2.cu:647-754): E4M3 codes, fp32 accumulate.  x: xbf 3 (MX-fp8, more than 16
    channels) or 2 (fp16 plane-major, quantised first); ys: the output shape, which must be ceil(xs / 2) per axis; y: ybf 2, 3, 4 or UMX_H16B as
-   above.  gp.G != 0 (the GroupNorm + SiLU input transform) prints "not built" and aborts.  Weights are prepared on every call, as in the
-   reference.  Returns 0. */
+   above; gp as for lp_conv_fwd_f8.  Weights are prepared on every call, as in the reference.  Returns 0. */
 int lp_conv_fwd_s2_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, shape5 ys, gnp_t gp);
 
 /* ---- graph operators (the InstanceNorm / LeakyReLU / transposed-conv semantics of src/xnet.h:85-98) ---- */
@@ -155,6 +156,9 @@ void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, 
    fraction in 2^-64, signed integer part, count of non-finite terms), zeroed by the caller; slot 2 (n G + g) takes the sum and the next one
    the sum of squares of group g of sample n over the voxels [v0, v1).  Returns 0, -1 when the combination is not covered (16 channels or
    fewer; G > 64 or C % G != 0 as in the reference).  umx_gn_finalize: mean and 1 / sqrt(max(var, 0) + eps) of NG groups of len elements. ---- */
+/* y = MX(silu(groupnorm(x))) (src/nn_lp.h:134, src/lp_mx_gn.cu:4-31): x xdt 0 / 2 (fp32 / fp16 plane-major) or 3 / 4 (MX); y ydt 3 / 4; more than 16
+   channels; mean, rstd per (sample, group).  SiLU is evaluated with the accurate expf and an IEEE division (the reference: __expf). */
+void lp_gn_silu_apply_mx(const void *x, int xdt, shape5 s, int G, const float *gamma, const float *beta, const float *mean, const float *rstd, void *y, int ydt);
 int lp_gn_sums_mx(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1);
 int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0, int cnt);
 void umx_gn_finalize(const double *sums, int NG, size_t len, float eps, float *mean, float *rstd);

@@ -335,3 +335,89 @@ def test_lp_conv_fwd_f8_config1(dev):
     dq = orc.mx_to_pm(ym.download(), 8, N, Cn, S)
     assert orc.rel_l2(dq, want) < 0.04
     L.lp_wmemo_clear()
+
+
+def _gn_silu_oracle(dq, N, Cn, S, Gn, gamma, beta, mean, rstd, form):
+    """fp32 restatement: form 0 = ((x - mean) rstd) gamma + beta (src/lp_mx_gn.cu:17), form 1 = fma(x, a, b) with a = rstd gamma,
+    b = fma(-mean, a, beta) (src/lp_common.cuh:244-261, 474-476); then v / (1 + exp(-v))."""
+    f32 = np.float32
+    x = dq.reshape(N, Cn, S).astype(f32)
+    g = np.arange(Cn) // (Cn // Gn)
+    m, r = mean.reshape(N, Gn)[:, g][:, :, None].astype(f32), rstd.reshape(N, Gn)[:, g][:, :, None].astype(f32)
+    ga, be = gamma[None, :, None].astype(f32), beta[None, :, None].astype(f32)
+    if form == 0:
+        u = (((x - m) * r) * ga) + be
+    else:
+        a = r * ga
+        b = (be.astype(np.float64) - m.astype(np.float64) * a.astype(np.float64)).astype(f32)
+        u = (x.astype(np.float64) * a.astype(np.float64) + b.astype(np.float64)).astype(f32)
+    with np.errstate(over="ignore"):
+        return (u / (f32(1) + np.exp(-u, dtype=f32))).astype(f32).reshape(-1)
+
+
+def _gn_params(seed, N, Cn, Gn):
+    g = synth.rng(seed)
+    return ((1 + 0.2 * g.standard_normal(Cn)).astype(np.float32), (0.1 * g.standard_normal(Cn)).astype(np.float32),
+            (0.3 * g.standard_normal(N * Gn)).astype(np.float32), (0.5 + g.random(N * Gn)).astype(np.float32))
+
+
+@pytest.mark.parametrize("xdt,ybits", [(3, 8), (4, 4), (3, 4), (2, 8), (0, 4)])
+def test_gn_silu_apply_mx(dev, xdt, ybits):
+    """Tolerance: a transcendental (expf) sits between the operands and the requantiser, so codes may differ from the CPU evaluation where a
+    value lands on a rounding boundary: at most 2e-4 of the code bytes, and 1e-3 relative L2 on the decoded tensor."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5
+    L = ufsm_b200.lib()
+    N, Cn, Gn, D, H, W = 2, 64, 8, 3, 10, 12
+    S = D * H * W
+    x = (synth.rng(71).standard_normal(N * Cn * S) * 2).astype(np.float32)
+    gamma, beta, mean, rstd = _gn_params(72, N, Cn, Gn)
+    if xdt >= 3:
+        src = orc.pm_to_mx(x, 0, N, Cn, S, 8 if xdt == 3 else 4, 32)
+        dq = orc.mx_to_pm(src, 8 if xdt == 3 else 4, N, Cn, S, 32)
+    elif xdt == 2:
+        src = x.astype(np.float16); dq = src.astype(np.float32)
+    else:
+        src = x; dq = x
+    want_f = _gn_silu_oracle(dq, N, Cn, S, Gn, gamma, beta, mean, rstd, 0)
+    want = orc.pm_to_mx(want_f, 0, N, Cn, S, ybits, 32)
+    xd, yd = DevBuf(data=src), DevBuf(want.size).fill(0xEE)
+    bufs = [DevBuf(data=a) for a in (gamma, beta, mean, rstd)]
+    L.lp_gn_silu_apply_mx(xd.ptr, xdt, Shape5(N, Cn, D, H, W), Gn, bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bufs[3].ptr, yd.ptr, 3 if ybits == 8 else 4)
+    ufsm_b200.check()
+    got = yd.download()
+    assert got.size == want.size
+    assert np.count_nonzero(got != want) <= 2e-4 * want.size, "%d of %d bytes differ" % (np.count_nonzero(got != want), want.size)
+    assert orc.rel_l2(orc.mx_to_pm(got, ybits, N, Cn, S, 32), orc.mx_to_pm(want, ybits, N, Cn, S, 32)) < TOL
+
+
+@pytest.mark.parametrize("s2", [False, True])
+def test_conv_entry_with_gn_silu_input_transform(dev, s2):
+    """lp_conv_fwd_f8 / lp_conv_fwd_s2_f8 with gnp_t.G = 8: silu(fma(x, a, b)) quantised to MX-fp8, then the conv; fp16 plane-major out."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    N, Ci, Co, Gn, D, H, W = 1, 64, 32, 8, 4, 16, 16
+    S = D * H * W
+    x = (synth.rng(81).standard_normal(N * Ci * S) * 2).astype(np.float32)
+    w, b = synth.kaiming(82, Co, Ci, 27), synth.bias(83, Co, 0.1)
+    gamma, beta, mean, rstd = _gn_params(84, N, Ci, Gn)
+    mx = orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
+    act = _gn_silu_oracle(orc.mx_to_pm(mx, 8, N, Ci, S, 32), N, Ci, S, Gn, gamma, beta, mean, rstd, 1)
+    amx = orc.pm_to_mx(act, 0, N, Ci, S, 8, 32)
+    st = 2 if s2 else 1
+    Do, Ho, Wo = (D + st - 1) // st, (H + st - 1) // st, (W + st - 1) // st
+    acc = orc.conv_blocked(orc.mx_to_blocked(amx, 8, N, Ci, S), N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, 8), b, Co, 3, st, 1)
+    want = orc.blocked_to_pm(orc.round_h16(acc), N, Co, Do * Ho * Wo)
+    xd, wd, bd = DevBuf(data=mx), DevBuf(data=w), DevBuf(data=b)
+    bufs = [DevBuf(data=a) for a in (gamma, beta, mean, rstd)]
+    gp = Gnp(); gp.gamma, gp.beta, gp.mean, gp.rstd, gp.G = bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bufs[3].ptr, Gn
+    yd = DevBuf(N * Co * Do * Ho * Wo * 2).fill(0xEE)
+    if s2:
+        rc = L.lp_conv_fwd_s2_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, Shape5(N, Co, Do, Ho, Wo), gp)
+    else:
+        rc = L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, gp, None, 0, Split())
+    ufsm_b200.check()
+    assert rc == 0
+    e = orc.rel_l2(yd.download(np.float16).astype(np.float32), want)
+    assert e < TOL, "relative L2 %.3g" % e
