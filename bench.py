@@ -276,7 +276,7 @@ def run_gpu(args):
         "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "h2d_bytes_per_step": B * S, "d2h_bytes_per_step": B * NH * S * 2, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clk.summary(),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
-                     "traffic": 229985536 * B,
+                     "traffic": 260782592 * B,
                      "kernel": "conv_mxr_k, 3^3 conv 32 -> 32 on 128^3 (enc0.c2): algorithmic 2*V*Cin*Cout*27 FLOPs / event time of that launch, mean of %d steps" % psteps,
                      "peak_note": "2 x the %s bf16 sustained cuBLAS rate (fp8 runs at twice bf16); nominal dense fp8 4500" % pk["which"], "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
                      "traffic_note": "dram read + write bytes of one launch of this shape from the committed ncu capture (algorithmic: 69 MB MX in + 134 MB fp16 out)",
