@@ -476,7 +476,16 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     auto up128 = [](int v) { return (v + 127) & ~127; };
     a.offW = 0; a.offSFB = c->items_max * c->nt * 32; a.offA = up128(c->w_stage_bytes); a.offSFA = a.offA + up128(abytes);
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
-    int sms = 148; { int d0 = 0; cudaGetDevice(&d0); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d0); }
+    /* per device, looked up once: the multiprocessor count and the address of the ticket array */
+    static int sms_of[16]; static unsigned *tickets_of[16];
+    int d0 = 0; cudaGetDevice(&d0); d0 &= 15;
+    if (!sms_of[d0]) {
+        int v = 148; cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d0);
+        unsigned *t = nullptr;
+        if (cudaGetSymbolAddress((void **)&t, g_ks_tickets) != cudaSuccess) { umx_latch_msg("umx_conv_fwd: ticket array"); return -1; }
+        tickets_of[d0] = t; sms_of[d0] = v;
+    }
+    const int sms = sms_of[d0];
     /* two blocks a multiprocessor (two issuing threads keep the tensor pipe busier than one) for the narrow tiles, and for the wide ones when
        there are more blocks than multiprocessors; a deep ring for one block otherwise */
     const long long blocks_all = (long long)a.tiles_x * a.tiles_y * D * N * a.ntiles_n;
@@ -574,7 +583,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
             const size_t bytes = (size_t)tiles_all * (size_t)ks * (size_t)(c->nt >> 5) * 4096 * 4;
             void *ws = umx_ws(5, bytes);
             if (!ws) return -1;
-            if (cudaGetSymbolAddress((void **)&a.ks_tickets, g_ks_tickets) != cudaSuccess) { umx_latch_msg("umx_conv_fwd: ticket array"); return -1; }
+            a.ks_tickets = tickets_of[d0];
             a.ksplit = (int)ks; a.ks_part = (float *)ws;
         }
     }

@@ -349,7 +349,7 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     a.wp = c->wp; a.e = e; a.err = umx_errflag();
     if (!a.err) return -1;
     int dev = 0, sms = 148; cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    { static int sms_of[16]; if (!sms_of[dev & 15]) { int v = 148; cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); sms_of[dev & 15] = v; } sms = sms_of[dev & 15]; }   /* looked up once per device */
     static int attr_set[16];
     if (!attr_set[dev & 15]) {
         cudaError_t er = cudaSuccess;

@@ -607,7 +607,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     a.stage_bytes = (a.offSFA + c->nquad * 512 + 1023) & ~1023;
     a.off_rec = 1024; a.off_bias = a.off_rec + 12 * 64; a.off_stage = 2048; a.off_red = a.off_stage; a.off_w = a.off_stage + 8192 * (g.nt == 32 ? 1 : 2); a.off_ring = (a.off_w + a.w_bytes + 1023) & ~1023;
     int dev = 0, sms = 148; cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    { static int sms_of[16]; if (!sms_of[dev & 15]) { int v = 148; cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); sms_of[dev & 15] = v; } sms = sms_of[dev & 15]; }   /* looked up once per device */
     /* two blocks a multiprocessor when shared memory (113 KB each) and TMEM (256 columns each) allow */
     int two = g.tmem_cols == 256 && a.off_ring + 4 * a.stage_bytes <= 113 * 1024;
 #ifdef UMX_KPROF
