@@ -53,6 +53,9 @@ _SIG = {
     "umx_prof_get": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "lp_mx8_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_size_t]),
     "lp_gn_silu_apply_mx": (None, [C.c_void_p, C.c_int, Shape5, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "lp_up2_fwd_mx": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_int, Gnp]),
+    "lp_conv1_fwd_mx": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp]),
+    "lp_conv1_fwd_mx_h16": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp]),
     "lp_gn_sums_mx": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t]),
     "lp_gn_sums_mx_n": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_int]),
     "umx_gn_finalize": (None, [C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_void_p, C.c_void_p]),
