@@ -27,14 +27,18 @@ __global__ void __launch_bounds__(256) gn_silu_apply_k(const void *__restrict__ 
         const uint4 t0 = *(const uint4 *)(x + i * 32), t1 = *(const uint4 *)(x + i * 32 + 16);
         const unsigned wd[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
-        for (int k = 0; k < 32; k++) r[k] = dec_e4m3((wd[k >> 2] >> (8 * (k & 3))) & 0xffu) * fx;
+        for (int j = 0; j < 8; j++) dec_e4m3x4(wd[j], r + 4 * j);
+#pragma unroll
+        for (int k = 0; k < 32; k++) r[k] *= fx;
     } else if (XK == 4) {
         const uint8_t *x = (const uint8_t *)xv;
         const float fx = mx_scale(x[(size_t)N * nb * S * 16 + i]);
         const uint4 t0 = *(const uint4 *)(x + i * 16);
         const unsigned wd[4] = {t0.x, t0.y, t0.z, t0.w};
 #pragma unroll
-        for (int k = 0; k < 32; k++) r[k] = dec_e2m1((wd[k >> 3] >> (4 * (k & 7))) & 15u) * fx;
+        for (int j = 0; j < 4; j++) dec_e2m1x8(wd[j], r + 8 * j);
+#pragma unroll
+        for (int k = 0; k < 32; k++) r[k] *= fx;
     } else {
 #pragma unroll
         for (int k = 0; k < 32; k++) {

@@ -44,13 +44,19 @@ __global__ void __launch_bounds__(256) gn_sums_k(const uint8_t *__restrict__ x, 
         if (BITS == 8) {
             const uint4 t = __ldg((const uint4 *)(x + ri * 32 + 16 * h));
             const unsigned wd[4] = {t.x, t.y, t.z, t.w};
+            float r[16];
 #pragma unroll
-            for (int k = 0; k < 16; k++) { const double v = (double)(dec_e4m3((wd[k >> 2] >> (8 * (k & 3))) & 0xffu) * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
+            for (int j = 0; j < 4; j++) dec_e4m3x4(wd[j], r + 4 * j);
+#pragma unroll
+            for (int k = 0; k < 16; k++) { const double v = (double)(r[k] * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
         } else {
             const uint2 t = __ldg((const uint2 *)(x + ri * 16 + 8 * h));
             const unsigned wd[2] = {t.x, t.y};
+            float r[16];
 #pragma unroll
-            for (int k = 0; k < 16; k++) { const double v = (double)(dec_e2m1((wd[k >> 3] >> (4 * (k & 7))) & 15u) * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
+            for (int j = 0; j < 2; j++) dec_e2m1x8(wd[j], r + 8 * j);
+#pragma unroll
+            for (int k = 0; k < 16; k++) { const double v = (double)(r[k] * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
         }
     }
     __shared__ double w1[8][32], w2[8][32];

@@ -80,6 +80,21 @@ __device__ __forceinline__ float dec_e2m1(unsigned n) {
     const float v = (float)(k < 4u ? k : k == 4u ? 4u : k == 5u ? 6u : k == 6u ? 8u : 12u) * 0.5f;
     return (n & 8u) ? -v : v;
 }
+/* four e4m3 bytes / eight e2m1 nibbles of a word -> floats, through the hardware conversions to packed halves (every code is exact in fp16;
+   the e4m3 NaN code becomes a NaN) */
+__device__ __forceinline__ void dec_e4m3x4(unsigned w, float *o) {
+    unsigned lo, hi;
+    asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}" : "=r"(lo), "=r"(hi) : "r"(w));
+    const float2 f0 = __half22float2(*(const __half2 *)&lo), f1 = __half22float2(*(const __half2 *)&hi);
+    o[0] = f0.x; o[1] = f0.y; o[2] = f1.x; o[3] = f1.y;
+}
+__device__ __forceinline__ void dec_e2m1x8(unsigned w, float *o) {
+    unsigned h0, h1, h2, h3;
+    asm("{\n\t.reg .b8 a, b, c, d;\n\tmov.b32 {a, b, c, d}, %4;\n\tcvt.rn.f16x2.e2m1x2 %0, a;\n\tcvt.rn.f16x2.e2m1x2 %1, b;\n\tcvt.rn.f16x2.e2m1x2 %2, c;\n\tcvt.rn.f16x2.e2m1x2 %3, d;\n\t}"
+        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(w));
+    const float2 f0 = __half22float2(*(const __half2 *)&h0), f1 = __half22float2(*(const __half2 *)&h1), f2 = __half22float2(*(const __half2 *)&h2), f3 = __half22float2(*(const __half2 *)&h3);
+    o[0] = f0.x; o[1] = f0.y; o[2] = f1.x; o[3] = f1.y; o[4] = f2.x; o[5] = f2.y; o[6] = f3.x; o[7] = f3.y;
+}
 /* a row of 32 fp16 values (16 packed pairs) -> MX-fp8 codes w[0..8) and the scale byte; the same bytes as mx_encode_row32<8> of the
    values converted to fp32.  amax, scaling and conversion stay on packed halves when the block scale 2^-e is a normal fp16 (the product
    is then exact, or below 2^-14 where E4M3 rounds to zero either way); other rows take the fp32 path. */

@@ -17,13 +17,15 @@ template <int BITS> __device__ __forceinline__ void load_row32(const uint8_t *__
         const uint4 t0 = __ldg((const uint4 *)(x + i * 32)), t1 = __ldg((const uint4 *)(x + i * 32 + 16));
         const unsigned wd[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
-        for (int k = 0; k < 32; k++) r[k] = dec_e4m3((wd[k >> 2] >> (8 * (k & 3))) & 0xffu) * fx;
+        for (int j = 0; j < 8; j++) dec_e4m3x4(wd[j], r + 4 * j);
     } else {
         const uint4 t0 = __ldg((const uint4 *)(x + i * 16));
         const unsigned wd[4] = {t0.x, t0.y, t0.z, t0.w};
 #pragma unroll
-        for (int k = 0; k < 32; k++) r[k] = dec_e2m1((wd[k >> 3] >> (4 * (k & 7))) & 15u) * fx;
+        for (int j = 0; j < 4; j++) dec_e2m1x8(wd[j], r + 8 * j);
     }
+#pragma unroll
+    for (int k = 0; k < 32; k++) r[k] *= fx;
 }
 __device__ __forceinline__ float silu_ab(float x, float a, float b) { const float u = __fmaf_rn(x, a, b); return __fdiv_rn(u, __fadd_rn(1.f, expf(-u))); }
 
