@@ -105,6 +105,11 @@ def test_back_to_back_forwards_never_stall(dev, bits, N, rounds):
     xd = ufsm_b200.DevBuf(data=ct_patch(22, N * P ** 3))
     yd = ufsm_b200.DevBuf(N * 7 * P ** 3 * 4)
     t = L.umx_timer_new()
+    # one forward outside the timed rounds: the first use of a kernel variant loads it and scratch buffers grow to their final size,
+    # which on a busy host can take longer than the stall threshold below
+    assert L.umx_unet_forward(u.h, xd.ptr, N, yd.ptr) == 0
+    L.nn_sync()
+    assert not L.lp_check()
     for r in range(rounds):
         L.umx_timer_start(t)
         for _ in range(10):
