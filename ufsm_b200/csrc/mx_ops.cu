@@ -45,34 +45,32 @@ __global__ void __launch_bounds__(256) up2_mx_k(const uint8_t *__restrict__ x, u
     __syncthreads();
     const size_t vo = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (vo >= So) return;
-    const int ox = (int)(vo % Wo), oy = (int)((vo / Wo) % Ho), oz = (int)(vo / ((size_t)Wo * Ho));
-    /* per axis: the coarse voxel under the fine one (weight 3/4) and its neighbour on the fine voxel's side, clamped to the grid (1/4) */
-    const int mz[2] = {oz >> 1, min(max((oz >> 1) + ((oz & 1) ? 1 : -1), 0), D - 1)};
-    const int my[2] = {oy >> 1, min(max((oy >> 1) + ((oy & 1) ? 1 : -1), 0), H - 1)};
-    const int mx[2] = {ox >> 1, min(max((ox >> 1) + ((ox & 1) ? 1 : -1), 0), W - 1)};
-    const float wt[2] = {0.75f, 0.25f};
+    const int fx = (int)(vo % Wo), fy = (int)((vo / Wo) % Ho), fz = (int)(vo / ((size_t)Wo * Ho));
+    /* per axis the two source voxels of fine coordinate f on a grid of n: the coarse voxel under it (weight 3/4) and that voxel's
+       neighbour on f's side, clamped to the grid (weight 1/4) */
+    auto under = [](int f) { return f >> 1; };
+    auto beside = [](int f, int n) { const int t = (f >> 1) + ((f & 1) ? 1 : -1); return t < 0 ? 0 : (t >= n ? n - 1 : t); };
+    const int sz[2] = {under(fz), beside(fz, D)}, sy[2] = {under(fy), beside(fy, H)}, sx[2] = {under(fx), beside(fx, W)};
     constexpr int RBX = BX == 8 ? 32 : 16, RBY = BY == 8 ? 32 : 16;
     const uint8_t *sc = x + (size_t)N * nb * S * RBX;
     const int kmax = min(32, C - blk * 32);
     float acc[32];
 #pragma unroll
     for (int k = 0; k < 32; k++) acc[k] = 0.f;
+    /* the eight corners in (z, y, x) order, nearest first on each axis; one fma per corner and channel */
 #pragma unroll
-    for (int a = 0; a < 2; a++)
+    for (int t = 0; t < 8; t++) {
+        const int iz = t >> 2, iy = (t >> 1) & 1, ix = t & 1;
+        const float w3 = (iz ? 0.25f : 0.75f) * (iy ? 0.25f : 0.75f) * (ix ? 0.25f : 0.75f);
+        float r[32];
+        load_row32<BX>(x, sc, (size_t)nbk * S + ((size_t)sz[iz] * H + sy[iy]) * W + sx[ix], r);
+        if (gp.G) {
 #pragma unroll
-        for (int b = 0; b < 2; b++)
+            for (int k = 0; k < 32; k++) if (k < kmax) r[k] = silu_ab(r[k], ca[k], cb[k]);
+        }
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                float r[32];
-                const float w3 = wt[a] * wt[b] * wt[c];
-                load_row32<BX>(x, sc, (size_t)nbk * S + ((size_t)mz[a] * H + my[b]) * W + mx[c], r);
-                if (gp.G) {
-#pragma unroll
-                    for (int k = 0; k < 32; k++) if (k < kmax) r[k] = silu_ab(r[k], ca[k], cb[k]);
-                }
-#pragma unroll
-                for (int k = 0; k < 32; k++) acc[k] = __fmaf_rn(w3, r[k], acc[k]);
-            }
+        for (int k = 0; k < 32; k++) acc[k] = __fmaf_rn(w3, r[k], acc[k]);
+    }
     unsigned wq[8];
     const unsigned sb = mx_encode_row32<BY>(acc, wq);
     const size_t i = (size_t)nbk * So + vo;
