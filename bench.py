@@ -21,7 +21,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))       # orc.py: the CPU oracle, for the cpu_baseline leg and --impl reference only
 
 CW = [32, 64, 128, 256, 320]
 P = 128
@@ -98,12 +98,124 @@ class Clocks(threading.Thread):
         return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.rows)}
 
 
+KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
+OUT = {"h16b": 0, "mx": 1, "pm32": 2}
+
+
+def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0):
+    """One conv layer on a size^3 grid of GEMM rows (conv3s2: the input grid), MX input of arbitrary finite codes (fp8 in the split
+    layout), Kaiming-normal weights: best of `reps` device times of the conv launch (events around it) in microseconds, and the
+    algorithmic TFLOP/s (2 V Cin Cout taps)."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf
+    D, S = size, size ** 3
+    nbi = (ci + 31) // 32 * (8 if kind == "down2" else 1)
+    rb = 32 * bits // 8
+    rng = np.random.default_rng(seed)
+    x = np.concatenate([rng.integers(0, 120, nbi * S * rb, dtype=np.uint8), rng.integers(100, 130, nbi * S, dtype=np.uint8)])
+    taps = {"conv3": 27, "conv1": 1, "down2": 8, "tconv2": 8, "conv3s2": 27}[kind]
+    w = (rng.standard_normal((co, ci, taps)) * np.sqrt(2.0 / (ci * taps))).astype(np.float32)
+    if kind == "tconv2":
+        w = np.ascontiguousarray(w.transpose(1, 0, 2))
+    h = L.umx_conv_create(KIND[kind], w.ctypes.data, None, co, ci, bits)
+    ufsm_b200.check()
+    nbo, mode = (co + 31) // 32, OUT[out]
+    So = ((D + 1) // 2) ** 3 if kind == "conv3s2" else S * (8 if kind == "tconv2" else 1)
+    nbytes = {0: nbo * So * 64, 1: nbo * So * (rb + 1), 2: co * So * 4}[mode]
+    xd, yd = DevBuf(data=x), DevBuf(nbytes)
+    best, ms, fl = 1e30, C.c_double(), C.c_double()
+    for _ in range(reps):
+        L.umx_prof_begin()
+        rc = L.umx_conv_fwd(h, xd.ptr, 1, D, D, D, yd.ptr, mode, bits if mode == 1 else 0, 0, 0, None, 3)
+        L.umx_prof_end(C.byref(ms), C.byref(fl))
+        assert rc == 0
+        best = min(best, ms.value)
+    ufsm_b200.check()
+    L.umx_conv_free(h)
+    xd.free()
+    yd.free()
+    return best * 1e3, fl.value / best / 1e9, x.nbytes + nbytes
+
+
+def quantiser_time(L, Cn, size, bits, reps=5):
+    """plane-major fp16 -> MX (lp_h16_to_mx8 / 4): best device time in microseconds and algorithmic GB/s (2 B read, MX bytes written)"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf
+    S = size ** 3
+    x = np.random.default_rng(1).standard_normal(Cn * S).astype(np.float16)
+    xd = DevBuf(data=x)
+    nb = (L.lp_mx8_bytes if bits == 8 else L.lp_mx4_bytes)(1, Cn, S)
+    yd = DevBuf(nb)
+    t, best = L.umx_timer_new(), 1e30
+    for _ in range(reps):
+        L.umx_timer_start(t)
+        (L.lp_h16_to_mx8 if bits == 8 else L.lp_h16_to_mx4)(xd.ptr, 2, 1, Cn, S, yd.ptr)
+        best = min(best, L.umx_timer_stop_ms(t))
+    ufsm_b200.check()
+    L.umx_timer_free(t)
+    xd.free()
+    yd.free()
+    return best * 1e3, (x.nbytes + nb) / best / 1e6
+
+
+def run_layer(args):
+    """python bench.py --layer kind,ci,co,size[,bits[,out]]: one conv layer alone (also the command of the profiler captures under profiles/)"""
+    import ufsm_b200
+    f = args.layer.split(",")
+    kind, ci, co, size = f[0], int(f[1]), int(f[2]), int(f[3])
+    bits, out = (int(f[4]) if len(f) > 4 else 8), (f[5] if len(f) > 5 else "h16b")
+    L = ufsm_b200.lib()
+    assert L.nn_init(0) == 0, (L.lp_check() or b"").decode()
+    us, tf, nbytes = layer_time(L, kind, ci, co, size, bits, out, args.reps)
+    print("%s %d->%d on %d^3 MX-fp%d out %s: %.1f us, %.0f TFLOP/s, %.0f GB/s of operand + result bytes (kernel %d)" % (kind, ci, co, size, bits, out, us, tf, nbytes / us / 1e3, L.umx_conv_last_kernel()))
+
+
+def run_ops(args):
+    """python bench.py --ops c,size,bits: the elementwise MX operators of the reference interface and the quantiser, algorithmic GB/s"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp
+    f = args.ops.split(",")
+    Cn, D, bits = int(f[0]), int(f[1]), (int(f[2]) if len(f) > 2 else 8)
+    L = ufsm_b200.lib()
+    assert L.nn_init(0) == 0, (L.lp_check() or b"").decode()
+    Gn = 8
+    S, nb, rb, dt = D ** 3, (Cn + 31) // 32, 32 * bits // 8, 3 if bits == 8 else 4
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.integers(0, 120, nb * S * rb, dtype=np.uint8), rng.integers(120, 130, nb * S, dtype=np.uint8)])
+    xd, yd = DevBuf(data=x), DevBuf(nb * S * (rb + 1))
+    par = [DevBuf(data=v) for v in (np.ones(Cn, np.float32), np.zeros(Cn, np.float32), np.zeros(Gn, np.float32), np.ones(Gn, np.float32))]
+    gp = Gnp()
+    sums = DevBuf(Gn * 2 * 24).fill(0)
+    w = DevBuf(data=(rng.standard_normal((7, Cn)) / np.sqrt(Cn)).astype(np.float32))
+    logits = DevBuf(7 * S * 4)
+    Dh = D // 2
+    t = L.umx_timer_new()
+
+    def run(name, fn, nbytes):
+        best = 1e30
+        for _ in range(args.reps):
+            L.umx_timer_start(t)
+            fn()
+            best = min(best, L.umx_timer_stop_ms(t))
+        ufsm_b200.check()
+        print("%-22s %d ch on %d^3 MX-fp%d: %.1f us, %.0f GB/s (algorithmic %.1f MB)" % (name, Cn, D, bits, best * 1e3, nbytes / best / 1e6, nbytes / 1e6))
+
+    mxb = nb * S * (rb + 1)
+    run("lp_gn_sums_mx", lambda: L.lp_gn_sums_mx(xd.ptr, dt, 1, Cn, Gn, S, sums.ptr, 0, S), mxb)
+    run("lp_gn_silu_apply_mx", lambda: L.lp_gn_silu_apply_mx(xd.ptr, dt, Shape5(1, Cn, D, D, D), Gn, par[0].ptr, par[1].ptr, par[2].ptr, par[3].ptr, yd.ptr, dt), 2 * mxb)
+    run("lp_up2_fwd_mx", lambda: L.lp_up2_fwd_mx(xd.ptr, dt, Shape5(1, Cn, Dh, Dh, Dh), yd.ptr, dt, gp), mxb + mxb // 8)
+    run("lp_conv1_fwd_mx (7)", lambda: L.lp_conv1_fwd_mx(xd.ptr, dt, Shape5(1, Cn, D, D, D), w.ptr, None, 7, logits.ptr, gp), mxb + 7 * S * 4)
+    L.umx_timer_free(t)
+    us, gbs = quantiser_time(L, Cn, D, bits, args.reps)
+    print("%-22s %d ch on %d^3 fp16 -> MX-fp%d: %.1f us, %.0f GB/s" % ("lp_h16_to_mx", Cn, D, bits, us, gbs))
+
+
 def cpu_sample(steps, warmup):
     """The oracle's forward of the same network on one full 128^3 patch, all host threads."""
     # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1; the oracle's OpenMP runtime reads it when loaded)
     os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import orc
-    import synth
+    from ufsm_b200 import synth
     Ps = P
     cfg = orc.unet_cfg(Ps, CW, NH, (8, 8, 8))
     w = synth.unet_weights(1, CW)
@@ -132,9 +244,8 @@ def run_reference(args):
 
 
 def run_gpu(args):
-    import gpu_util as G
-    import synth
     import ufsm_b200
+    from ufsm_b200 import npapi as G, synth
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
     if world > 1:
@@ -253,6 +364,21 @@ def run_gpu(args):
         L.nn_free_host(acc_p)
         L.nn_free_host(wsum_p)
         del vol
+    # ---- single layers of configurations 1 and 2 and the quantiser (rank 0 reports them; parity of these shapes is in the tests)
+    extra = None
+    if rank == 0:
+        c1 = layer_time(L, "conv3", 32, 32, 64, 8, "h16b", 5)
+        c1m = layer_time(L, "conv3", 32, 32, 64, 8, "mx", 5)
+        d2 = layer_time(L, "down2", 64, 128, 48, 4, "h16b", 5)
+        u2 = layer_time(L, "tconv2", 128, 64, 48, 4, "h16b", 5)
+        q1 = quantiser_time(L, 32, 64, 8)
+        q0 = quantiser_time(L, 32, 128, 8)
+        q4 = quantiser_time(L, 32, 128, 4)
+        extra = {"config1_conv3_32x32_64cube_mxfp8": {"us": round(c1[0], 1), "tflops": round(c1[1], 1), "mx_out_us": round(c1m[0], 1), "mx_out_tflops": round(c1m[1], 1)},
+                 "config2_down2_64x128_to_48cube_mxfp4": {"us": round(d2[0], 1), "tflops": round(d2[1], 1), "gbs": round(d2[2] / d2[0] / 1e3)},
+                 "config2_tconv2_128x64_to_96cube_mxfp4": {"us": round(u2[0], 1), "tflops": round(u2[1], 1), "gbs": round(u2[2] / u2[0] / 1e3)},
+                 "quantiser_fp16_to_mx": {"config1_32x64cube_fp8": {"us": round(q1[0], 1), "gbs": round(q1[1])}, "32x128cube_fp8": {"us": round(q0[0], 1), "gbs": round(q0[1])},
+                                          "32x128cube_fp4": {"us": round(q4[0], 1), "gbs": round(q4[1])}, "note": "algorithmic bytes (2 B read + MX bytes written per element) / best event time"}}
     clk.stop = True
     clk.join(2)
     ufsm_b200.check()
@@ -261,7 +387,8 @@ def run_gpu(args):
     pk = peaks()
     vox = world * B * S * args.steps
     flops_patch = L.umx_unet_flops(C.byref(cfg))
-    peak = 2.0 * pk["bf16_sustained"]
+    # fp8 block-scaled MMAs run at twice the bf16 rate; the timed region is far below a second at full clock, so the burst figure applies
+    peak = 2.0 * pk["bf16_burst"]
     # the dominant kernel: conv_mxr_k on the 3^3 32 -> 32 conv of level 0 (enc0.c2), the shape of the committed profiler capture
     dom = per["enc0.c2"]
     achieved = dom[1] / (dom[0] * 1e-3) / 1e12 if dom[0] > 0 else None
@@ -278,12 +405,13 @@ def run_gpu(args):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
                      "traffic": 260782592 * B,
                      "kernel": "conv_mxr_k, 3^3 conv 32 -> 32 on 128^3 (enc0.c2): algorithmic 2*V*Cin*Cout*27 FLOPs / event time of that launch, mean of %d steps" % psteps,
-                     "peak_note": "2 x the %s bf16 sustained cuBLAS rate (fp8 runs at twice bf16); nominal dense fp8 4500" % pk["which"], "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
+                     "peak_note": "2 x the %s bf16 burst cuBLAS rate (fp8 runs at twice bf16; a timed region well under a second); nominal dense fp8 4500" % pk["which"], "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
                      "traffic_note": "dram read + write bytes of one launch of this shape from the committed ncu capture (algorithmic: 69 MB MX in + 134 MB fp16 out)",
                      "level0_3x3x3_tflops": l0_tf, "all_conv_launches_tflops": all_tf, "conv_launches_per_step": n_conv,
                      "conv_share_of_step": ms_conv / max(psteps, 1) / (ms / args.steps)},
         "conv_layers_us": {k: round(v[0] / psteps * 1e3, 1) for k, v in per.items()},
         "sliding_window": win,
+        "layers": extra,
         "mxfp4_interior": {"workload": "config 4's network (interior convs MX-fp4 E2M1, first and last MX-fp8), one 128^3 patch per GPU per step",
                            "ms_per_step": ms_fp4 / args.steps, "value": vox / (ms_fp4 * 1e-3), "unit": "voxels/s"},
     }
@@ -306,8 +434,15 @@ def main():
     ap.add_argument("--clock-interval", type=float, default=0.05, help="seconds between clock samples (NVML queries share a lock with kernel launches, so not too often)")
     ap.add_argument("--window", type=int, default=0, help="also run the sliding window over a synthetic V^3 volume (configuration 5 uses 1024)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--layer", default="", help="time one conv layer alone: kind,ci,co,size[,bits[,out]] with kind conv3 | conv1 | down2 | tconv2 | conv3s2, out h16b | mx | pm32")
+    ap.add_argument("--ops", default="", help="time the elementwise MX operators and the quantiser: c,size[,bits]")
+    ap.add_argument("--reps", type=int, default=5, help="repetitions of --layer / --ops (the best is printed)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.layer:
+        run_layer(args)
+    elif args.ops:
+        run_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

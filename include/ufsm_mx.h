@@ -131,6 +131,10 @@ int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, v
    reproducible byte for byte in a fixed configuration). */
 int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags);
 size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
+/* testing aid (no counterpart in the reference): at most `cap` thread blocks per column tile in the resident-weight 3^3 kernel (0: as many as
+   the device holds), so that a small volume is cut into the several-planes-a-block pieces that otherwise only 64^3 and larger volumes see */
+void umx_conv_r_block_cap(int cap);
+int umx_conv_last_kernel(void);          /* which kernel the last umx_conv_fwd on this thread's process launched: 0 general, 1 resident-weight 3^3, 2 one-tap streaming; -1 none yet */
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */
 void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
@@ -171,7 +175,7 @@ int lp_gn_sums_mx(const void *x, int xdt, int N, int C, int G, size_t S, double 
 int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0, int cnt);
 void umx_gn_finalize(const double *sums, int NG, size_t len, float eps, float *mean, float *rstd);
 
-/* ---- the BASELINE U-Net (five levels 32/64/128/256/320, two 3^3 convs + InstanceNorm + LeakyReLU 0.01 a level, 2^3 stride-2
+/* ---- the benchmark's U-Net (five levels 32/64/128/256/320, two 3^3 convs + InstanceNorm + LeakyReLU 0.01 a level, 2^3 stride-2
    down convs, ConvTranspose k2 s2 up, concat (up | skip), 1^3 head) and the sliding-window scheduler ---- */
 typedef struct { int L; int cw[8]; int nh; int P; int bits_first, bits_mid, bits_last; } umx_unet_cfg;
 typedef struct umx_unet umx_unet;

@@ -397,7 +397,7 @@ void orc_fake_quant_blocked(float *x, size_t rows, int bits) {
     free(q);
 }
 
-/* ------------------------------------------------------------------ the BASELINE U-Net forward */
+/* ------------------------------------------------------------------ the benchmark's U-Net forward */
 
 /* Five-level U-Net, widths cw[0..L), per level two 3^3 convs each followed by InstanceNorm(eps 1e-5, gamma 1, beta 0) + LeakyReLU 0.01,
    2^3 stride-2 down convs, ConvTranspose k2 s2 up, concat (up | skip), 1^3 head.  Every conv input is an MX tensor (bits_in[i] of
@@ -499,9 +499,10 @@ void orc_unet_forward(const orc_unet_cfg *c, const float *weights, const uint16_
 
 /* ------------------------------------------------------------------ sliding window */
 
-/* Gaussian window weight of a P^3 patch, sigma = P / 8 about the patch centre (src/ink3dext.c:8, src/nn_ink3dext.cu:58-73) */
+/* Gaussian window weight of a P^3 patch: exp(-(i - P / 2)^2 / (2 sigma^2)) per axis with sigma = P / 8 and the integer centre P / 2
+   (g1_init, src/nn_ink3dext.cu:48-56; src/ink3dext.c:8) */
 void orc_gauss_window(int P, float *w1d) {
-    const double s = P / 8.0, c = (P - 1) / 2.0;
+    const double s = P / 8.0, c = (double)(P / 2);
     for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d[i] = (float)exp(-0.5 * d * d); }
 }
 /* accumulate one patch: acc[ch][vol voxel] += w * logits, wsum[vol voxel] += w, for the patch with origin (z0, y0, x0) in a V^3 volume */

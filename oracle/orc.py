@@ -1,11 +1,12 @@
-"""numpy wrappers around the CPU oracle (oracle/liboracle.so).  Test infrastructure only."""
+"""numpy wrappers around the CPU oracle (liboracle.so beside this file).  Test infrastructure only: imported by the tests, the smoke
+test and the CPU-baseline legs of the benchmark, never by the library."""
 import ctypes as C
 import os
 import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))   # the repository root: this file sits in oracle/
 ORC_DIR = os.path.join(ROOT, "oracle")
 _o = None
 
@@ -216,3 +217,26 @@ def _unet_forward(cfg, weights, x16, N):
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def conv_case(kind, x, w, b, N, Ci, D, H, W, Co, bits):
+    """One conv layer on identical operands.  x: plane-major fp32 [N][Ci][S].  Returns (the MX bytes a conv under test reads, in the
+    reference layout with 32-wide blocks; the oracle's acc + bias as plane-major fp32 [N][Co][So])."""
+    S = D * H * W
+    mx = pm_to_mx(x, 0, N, Ci, S, bits, 32)
+    xb = mx_to_blocked(mx, bits, N, Ci, S)
+    if kind == "conv3":
+        acc = conv_blocked(xb, N, Ci, D, H, W, prep_w(w, Co, Ci, 27, bits), b, Co, 3, 1, 1)
+        return mx, blocked_to_pm(acc, N, Co, S)
+    if kind == "conv1":
+        acc = conv_blocked(xb, N, Ci, D, H, W, prep_w(w, Co, Ci, 1, bits), b, Co, 1, 1, 0)
+        return mx, blocked_to_pm(acc, N, Co, S)
+    if kind == "down2":
+        acc = conv_blocked(xb, N, Ci, D, H, W, prep_w(w, Co, Ci, 8, bits), b, Co, 2, 2, 0)
+        mxs = blocked_to_mx(s2d_blocked(xb, N, Ci, D, H, W), bits, N, 8 * nb32(Ci) * 32, S // 8)
+        return mxs, blocked_to_pm(acc, N, Co, S // 8)
+    if kind == "conv3s2":
+        acc = conv_blocked(xb, N, Ci, D, H, W, prep_w(w, Co, Ci, 27, bits), b, Co, 3, 2, 1)
+        return mx, blocked_to_pm(acc, N, Co, ((D + 1) // 2) * ((H + 1) // 2) * ((W + 1) // 2))
+    acc = tconv_blocked(xb, N, Ci, D, H, W, prep_w(w, Co, Ci, 8, bits, layout=1), b, Co)
+    return mx, blocked_to_pm(acc, N, Co, 8 * S)

@@ -13,34 +13,8 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3
 
 
-def oracle_conv(kind, x, w, b, N, Ci, D, H, W, Co, bits):
-    """x: plane-major fp32 [N][Ci][S].  Returns (MX bytes the GPU conv reads, oracle acc + bias as plane-major fp32 [N][Co][So])."""
-    S = D * H * W
-    mx = orc.pm_to_mx(x, 0, N, Ci, S, bits, 32)
-    xb = orc.mx_to_blocked(mx, bits, N, Ci, S)
-    if kind == "conv3":
-        acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, bits), b, Co, 3, 1, 1)
-        return mx, orc.blocked_to_pm(acc, N, Co, S)
-    if kind == "conv1":
-        acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 1, bits), b, Co, 1, 1, 0)
-        return mx, orc.blocked_to_pm(acc, N, Co, S)
-    if kind == "down2":
-        acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 8, bits), b, Co, 2, 2, 0)
-        mxs = orc.blocked_to_mx(orc.s2d_blocked(xb, N, Ci, D, H, W), bits, N, 8 * orc.nb32(Ci) * 32, S // 8)
-        return mxs, orc.blocked_to_pm(acc, N, Co, S // 8)
-    if kind == "conv3s2":
-        acc = orc.conv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, bits), b, Co, 3, 2, 1)
-        return mx, orc.blocked_to_pm(acc, N, Co, ((D + 1) // 2) * ((H + 1) // 2) * ((W + 1) // 2))
-    acc = orc.tconv_blocked(xb, N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 8, bits, layout=1), b, Co)
-    return mx, orc.blocked_to_pm(acc, N, Co, 8 * S)
-
-
-def run_pm32(kind, mx, w, b, N, Ci, D, H, W, Co, bits, split=True):
-    c = G.Conv(kind, w, b, Co, Ci, bits)
-    g = (D // 2, H // 2, W // 2) if kind == "down2" else (D, H, W)
-    raw, _ = c.fwd(mx, N, *g, G.OUT_PM32, split=split)
-    c.free()
-    return raw.view(np.float32)
+oracle_conv = orc.conv_case
+run_pm32 = G.run_pm32
 
 
 CASES = [
@@ -282,7 +256,7 @@ def test_apply_scale_ranges(dev):
 
 
 def test_config2_mxfp4_down_up_pair(dev):
-    """BASELINE configuration 2 at full size: 1 x 64 x 96^3 fp16 N(0,1); a 2^3 stride-2 conv 64 -> 128 (to 48^3), then a 2^3 stride-2
+    """The benchmark's configuration 2 at full size: 1 x 64 x 96^3 fp16 N(0,1); a 2^3 stride-2 conv 64 -> 128 (to 48^3), then a 2^3 stride-2
     transposed conv 128 -> 64 (back to 96^3) on the fp16 result; E2M1 operands with an E8M0 scale per 32 channels, fp32 accumulate.  Each
     layer against the oracle on identical MX operands."""
     N, Ci, Cm, D = 1, 64, 128, 96
@@ -303,7 +277,7 @@ def test_config2_mxfp4_down_up_pair(dev):
 
 
 def test_lp_conv_fwd_f8_config1(dev):
-    """BASELINE configuration 1 through the reference's entry point: 1 x 32 x 64^3 fp16 N(0,1), 32 -> 32, MX-fp8, fp16 output."""
+    """The benchmark's configuration 1 through the reference's entry point: 1 x 32 x 64^3 fp16 N(0,1), 32 -> 32, MX-fp8, fp16 output."""
     import ctypes as C
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp, Split
@@ -334,6 +308,47 @@ def test_lp_conv_fwd_f8_config1(dev):
     ufsm_b200.check()
     dq = orc.mx_to_pm(ym.download(), 8, N, Cn, S)
     assert orc.rel_l2(dq, want) < 0.04
+    L.lp_wmemo_clear()
+
+
+def test_lp_conv_fwd_f4_entry(dev):
+    """lp_conv_fwd_f4 (src/nn_lp.h:54, src/lp_f4fwd.cu:30-51): E2M1 operands.  fp16 plane-major in and out on configuration 1's tensor
+    (1 x 32 x 64^3) and on a 64 -> 64 layer; MX-fp4 in and out with the prepared weights memoised under split_t.wkey."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    for N, Ci, Co, D in ((1, 32, 32, 64), (2, 64, 64, 24)):
+        S = D ** 3
+        x16 = synth.act_h16(401, N * Ci * S)
+        w = synth.kaiming(402, Co, Ci, 27)
+        b = synth.bias(403, Co)
+        xd, wd, bd = DevBuf(data=x16), DevBuf(data=w), DevBuf(data=b)
+        yd = DevBuf(N * Co * S * 2).fill(0xEE)
+        rc = L.lp_conv_fwd_f4(xd.ptr, 2, Shape5(N, Ci, D, D, D), wd.ptr, bd.ptr, Co, yd.ptr, 2, Gnp(), None, 0, Split())
+        ufsm_b200.check()
+        assert rc == 0
+        got = yd.download(np.float16).astype(np.float32)
+        mx = orc.pm_to_mx(x16, 2, N, Ci, S, 4, 32)
+        acc = orc.conv_blocked(orc.mx_to_blocked(mx, 4, N, Ci, S), N, Ci, D, D, D, orc.prep_w(w, Co, Ci, 27, 4), b, Co, 3, 1, 1)
+        want = orc.blocked_to_pm(orc.round_h16(acc), N, Co, S)
+        e = orc.rel_l2(got, want)
+        assert e < TOL, "relative L2 %.3g" % e
+        # MX-fp4 in, MX-fp4 out, memoised weights: the output rows are the requantised accumulators (src/lp_common.cuh:1465-1536); against
+        # the oracle's rows of its own accumulators all but the rows where the summation order moved a value across a rounding boundary
+        xm = DevBuf(data=mx)
+        ym = DevBuf(L.lp_mx4_bytes(N, Co, S)).fill(0xEE)
+        sp = Split(); sp.wkey = 11 + Ci
+        outs = []
+        for _ in range(2):     # the second call takes the memoised weights
+            assert L.lp_conv_fwd_f4(xm.ptr, 4, Shape5(N, Ci, D, D, D), wd.ptr, bd.ptr, Co, ym.ptr, 4, Gnp(), None, 0, sp) == 0
+            ufsm_b200.check()
+            outs.append(ym.download())
+        assert np.array_equal(outs[0], outs[1])
+        want_mx = orc.blocked_to_mx(acc, 4, N, Co, S)
+        frac = np.mean(outs[0] != want_mx)
+        dq = orc.mx_to_pm(outs[0], 4, N, Co, S)
+        print("lp_conv_fwd_f4 %d -> %d on %d^3: fp16 out rel-L2 %.3g; MX-fp4 out: %.2e of the bytes differ from the oracle's rows" % (Ci, Co, D, e, frac))
+        assert frac < 1e-4 and orc.rel_l2(dq, orc.mx_to_pm(want_mx, 4, N, Co, S)) < 5e-3
     L.lp_wmemo_clear()
 
 

@@ -120,6 +120,133 @@ def test_back_to_back_forwards_never_stall(dev, bits, N, rounds):
     u.free()
 
 
+def split_weights(flat, cw, nh):
+    """(w, b) per conv in forward order from the flat array of umx_unet_nweights"""
+    out, o = {}, [0]
+
+    def take(name, co, ci, taps):
+        nw = co * ci * taps
+        out[name] = (flat[o[0]:o[0] + nw], flat[o[0] + nw:o[0] + nw + co])
+        o[0] += nw + co
+    L_ = len(cw)
+    for l in range(L_):
+        take("enc%d.c1" % l, cw[l], cw[l] if l else 1, 27)
+        take("enc%d.c2" % l, cw[l], cw[l], 27)
+        if l < L_ - 1:
+            take("down%d" % l, cw[l + 1], cw[l], 8)
+    for l in range(L_ - 2, -1, -1):
+        take("up%d" % l, cw[l], cw[l + 1], 8)
+        take("dec%d.c1" % l, cw[l], 2 * cw[l], 27)
+        take("dec%d.c2" % l, cw[l], cw[l], 27)
+    take("head", nh, cw[0], 1)
+    assert o[0] == flat.size
+    return out
+
+
+def mx_concat(a, Ca, b, Cb, S, bits):
+    """channel concat of two one-sample MX tensors (32-wide blocks, reference layout): codes of a then b, scales of a then b"""
+    rb = 32 * bits // 8
+    na, nb_ = orc.nb32(Ca) * S * rb, orc.nb32(Cb) * S * rb
+    return np.concatenate([a[:na], b[:nb_], a[na:], b[nb_:]])
+
+
+@pytest.mark.parametrize("bits", [(8, 8, 8), (8, 4, 8)])
+def test_unet_layers_teacher_forced(dev, bits):
+    """Configuration 3 / 4's network at full size (one 128^3 patch, widths 32/64/128/256/320), stage by stage through the C ABI, every
+    stage of the oracle fed the GPU stage's own input: each of the 27 convs within 1e-3 relative L2 of the oracle's fp32 accumulation of
+    the same MX operands (3^3 convs as the stored fp16 tensor, the others as fp32 accumulators); every other function of a stage bit for
+    bit: MX output of the down / up convs from the device's accumulators, InstanceNorm coefficients from the stored fp16 tensor, the
+    apply (affine, LeakyReLU, fp16, MX requantisation, space-to-depth copy) from the stored tensor and those coefficients.  The chain
+    of operator calls is the one the library's own forward makes, so its logits must be the bytes of umx_unet_forward; and those are
+    compared with the oracle's free-running forward under the drift bound of test_unet_small_against_oracle."""
+    P, cw, nh = 128, [32, 64, 128, 256, 320], 7
+    bf, bm, bl = bits
+    Lv = len(cw)
+    flat = synth.unet_weights(8, cw)
+    W = split_weights(flat, cw, nh)
+    x16 = ct_patch(9, P ** 3)
+    worst = {"conv": 0.0}
+
+    def conv_norm(name, x_mx, Ci, C, D, bits_in, bits_out, want_s2d=False):
+        S = D ** 3
+        w, b = W[name]
+        c = G.Conv("conv3", w, b, C, Ci, bits_in)
+        y, coef = c.fwd_norm(x_mx, 1, D, D, D)
+        c.free()
+        yf = y.astype(np.float32)
+        acc = orc.conv_blocked(orc.mx_to_blocked(x_mx, bits_in, 1, Ci, S), 1, Ci, D, D, D, orc.prep_w(w, C, Ci, 27, bits_in), b, C, 3, 1, 1)
+        e = orc.rel_l2(yf, orc.round_h16(acc))
+        worst["conv"] = max(worst["conv"], e)
+        assert e < 1e-3, "%s: relative L2 %.3g" % (name, e)
+        assert np.array_equal(coef, orc.in_coef(orc.in_sums(yf, 1, C, S), 1, C, S)), name + ": coefficients"
+        q, s2d, _ = G.in_apply(yf, coef, 1, C, D, D, D, 2, bits_out, want_s2d=want_s2d)
+        a = orc.in_apply(yf, coef, 1, C, S, 2)
+        assert np.array_equal(q, orc.blocked_to_mx(a, bits_out, 1, C, S)), name + ": apply"
+        if want_s2d:
+            assert np.array_equal(s2d, orc.blocked_to_mx(orc.s2d_blocked(a, 1, C, D, D, D), bits_out, 1, 8 * C, S // 8)), name + ": space-to-depth copy"
+        return q, s2d
+
+    def conv_mx(kind, name, x_mx, Ci, C, Dg, bits_, x_fine=None):
+        """down / up conv on the grid Dg^3 of its GEMM rows: fp32 accumulators against the oracle, then the MX output bit for bit from those
+        accumulators.  The down conv reads the space-to-depth copy (x_mx); the oracle convolves the fine tensor it is a permutation of."""
+        w, b = W[name]
+        c = G.Conv(kind, w, b, C, Ci, bits_)
+        acc = c.fwd(x_mx, 1, Dg, Dg, Dg, G.OUT_PM32)[0].view(np.float32)
+        q = c.fwd(x_mx, 1, Dg, Dg, Dg, G.OUT_MX, bits_)[0]
+        c.free()
+        So = Dg ** 3 * (8 if kind == "tconv2" else 1)
+        if kind == "down2":
+            Df = 2 * Dg
+            want = orc.conv_blocked(orc.mx_to_blocked(x_fine, bits_, 1, Ci, Df ** 3), 1, Ci, Df, Df, Df, orc.prep_w(w, C, Ci, 8, bits_), b, C, 2, 2, 0)
+        else:
+            want = orc.tconv_blocked(orc.mx_to_blocked(x_mx, bits_, 1, Ci, Dg ** 3), 1, Ci, Dg, Dg, Dg, orc.prep_w(w, C, Ci, 8, bits_, layout=1), b, C)
+        e = orc.rel_l2(acc, orc.blocked_to_pm(want, 1, C, So))
+        worst["conv"] = max(worst["conv"], e)
+        assert e < 1e-3, "%s: relative L2 %.3g" % (name, e)
+        assert np.array_equal(q, orc.blocked_to_mx(orc.round_h16(orc.pm_to_blocked(acc, 1, C, So)), bits_, 1, C, So)), name + ": MX output"
+        return q
+
+    S0 = P ** 3
+    cur = G.quantise_pm(x16, 2, 1, 1, S0, bf, wide32=True)
+    assert np.array_equal(cur, orc.pm_to_mx(x16, 2, 1, 1, S0, bf, 32))
+    skip, Ccur = {}, 1
+    for l in range(Lv):
+        D, C = P >> l, cw[l]
+        a, _ = conv_norm("enc%d.c1" % l, cur, Ccur, C, D, bm if l else bf, bm)
+        if l < Lv - 1:
+            skip[l], s2d = conv_norm("enc%d.c2" % l, a, C, C, D, bm, bm, want_s2d=True)
+            cur = conv_mx("down2", "down%d" % l, s2d, C, cw[l + 1], D // 2, bm, x_fine=skip[l])
+            Ccur = cw[l + 1]
+        else:
+            cur, _ = conv_norm("enc%d.c2" % l, a, C, C, D, bm, bm)
+    for l in range(Lv - 2, -1, -1):
+        D, C = P >> l, cw[l]
+        up = conv_mx("tconv2", "up%d" % l, cur, cw[l + 1], C, D // 2, bm)
+        cat = mx_concat(up, C, skip.pop(l), C, D ** 3, bm)
+        a, _ = conv_norm("dec%d.c1" % l, cat, 2 * C, C, D, bm, bm if l else bl)
+        cur, _ = conv_norm("dec%d.c2" % l, a, C, C, D, bm if l else bl, bm if l else bl)
+    w, b = W["head"]
+    c = G.Conv("conv1", w, b, nh, cw[0], bl)
+    logits = c.fwd(cur, 1, P, P, P, G.OUT_PM32)[0].view(np.float32)
+    c.free()
+    want = orc.blocked_to_pm(orc.conv_blocked(orc.mx_to_blocked(cur, bl, 1, cw[0], S0), 1, cw[0], P, P, P, orc.prep_w(w, nh, cw[0], 1, bl), b, nh, 1, 1, 0), 1, nh, S0)
+    e = orc.rel_l2(logits, want)
+    assert e < 1e-3, "head: relative L2 %.3g" % e
+    print("teacher-forced, bits %s: worst conv rel-L2 %.3g, head %.3g" % (bits, worst["conv"], e))
+    # the library's own forward makes the same calls: same bytes
+    u = G.Unet(G.make_cfg(P, cw, nh, bits), flat, 1)
+    full = u.forward(x16, 1)
+    u.free()
+    assert np.array_equal(full, logits), "umx_unet_forward differs from the chain of its operators"
+    # free-running against the oracle's forward at full size
+    ocfg = orc.unet_cfg(P, cw, nh, bits)
+    ow = orc.unet_forward(ocfg, flat, x16, 1)
+    drift = orc.rel_l2(orc.unet_forward(ocfg, flat, x16, 1, descending=True), ow)
+    ef = orc.rel_l2(full, ow)
+    print("free-running 128^3 forward, bits %s: rel-L2 %.3g against the oracle (the oracle against itself with the other tap order: %.3g)" % (bits, ef, drift))
+    assert ef < 2 * drift + 1e-3
+
+
 def test_unet_full_size_properties(dev):
     """Configuration 3 (128^3 patch, widths 32/64/128/256/320): finite, deterministic, and translation-consistent in the batch."""
     P, cw = 128, [32, 64, 128, 256, 320]

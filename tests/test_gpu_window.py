@@ -38,7 +38,7 @@ def test_window_blend_and_two_rank_shards(dev):
     assert (lo, hi) == (0, V) and np.isfinite(acc).all() and (ws > 0).all()
     # numpy restatement of the blend from the library's per-patch logits (host entry, fp16 -> the device path's fp32 logits differ by the
     # fp16 rounding only, so compare through the fp32 device entry)
-    sg, c = P / 8.0, (P - 1) / 2.0
+    sg, c = P / 8.0, float(P // 2)
     w1 = np.exp(-0.5 * ((np.arange(P) - c) / sg) ** 2).astype(np.float32)
     w3 = ((w1[:, None, None] * w1[None, :, None]).astype(np.float32) * w1[None, None, :]).astype(np.float32)
     want = np.zeros((NH, V, V, V), np.float32)

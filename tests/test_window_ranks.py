@@ -24,7 +24,7 @@ def _blend(L, w, first, count):
     L.umx_window_extent(C.byref(w), first, count, C.byref(lo), C.byref(hi))
     zext = hi.value - lo.value
     acc, ws = np.zeros((NH, zext, V, V), np.float32), np.zeros((zext, V, V), np.float32)
-    sg, c = P / 8.0, (P - 1) / 2.0
+    sg, c = P / 8.0, float(P // 2)
     w1 = np.exp(-0.5 * ((np.arange(P) - c) / sg) ** 2).astype(np.float32)
     w3 = ((w1[:, None, None] * w1[None, :, None]).astype(np.float32) * w1[None, None, :]).astype(np.float32)
     z, y, x = C.c_int(), C.c_int(), C.c_int()

@@ -30,14 +30,16 @@ def coefs_both_ways(L, seed, N, Ci, Co, D, H, W):
     ufsm_b200.check()
     assert rc == 0
     conv.free()
-    return out.download(np.float32), ref
+    want = orc.in_coef(orc.in_sums(yd.download(np.float16).astype(np.float32), N, Co, S), N, Co, S)   # the oracle's fp64 statistics of the stored tensor
+    return out.download(np.float32), ref, want
 
 
 def test_two_calls_in_a_row_match_the_existing_entry(dev):
     # the second call is smaller than the first: it must not see what the first left in the shared array
     for seed, shape in ((70, (2, 32, 96, 3, 19, 11)), (80, (1, 32, 40, 2, 7, 5))):
-        got, ref = coefs_both_ways(dev, seed, *shape)
+        got, ref, want = coefs_both_ways(dev, seed, *shape)
         assert np.isfinite(got).all()
+        assert np.array_equal(got, want), "max diff to the oracle %g" % np.abs(got - want).max()
         # the two paths add the same fp64 terms in different groupings: equal to a float32 rounding
         assert np.allclose(got, ref, rtol=3e-7, atol=3e-7 * np.abs(ref).max()), "max diff %g" % np.abs(got - ref).max()
 
@@ -48,3 +50,6 @@ def test_sizes_beyond_the_array_are_refused(dev):
     e = dev.lp_check()
     assert rc == -1 and e and b"built-in array" in e
     assert np.all(out.download() == 0xEE)                                                          # nothing ran
+    rc = dev.umx_in_coef_static(out.ptr, 1, 32, 0, 2, 2, None, None, C.c_float(1e-5), out.ptr)     # an empty grid
+    e = dev.lp_check()
+    assert rc == -1 and e and b"at least 1" in e

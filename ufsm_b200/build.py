@@ -1,5 +1,6 @@
 """Builds libufsm_mx.so in-tree: CUDA sources for sm_100a with nvcc, the C23 host code with gcc, one shared library with a C ABI."""
 import os
+import shutil
 import subprocess
 import sys
 
@@ -8,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libufsm_mx.so")
 CU = ["runtime.cu", "quant.cu", "norm.cu", "conv_tc.cu", "conv_tcr.cu", "conv_tcp.cu", "lp_entry.cu", "window.cu", "in_coef_static.cu", "gn_sums.cu", "gn_apply.cu", "mx_ops.cu"]
 C = ["unet.c"]
-NVCC = os.environ.get("UFSM_NVCC", "/usr/local/cuda/bin/nvcc")
+NVCC = os.environ.get("UFSM_NVCC") or shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
 GCC = os.environ.get("UFSM_GCC", "gcc")
 NVFLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"] + os.environ.get("UFSM_NVCC_EXTRA", "").split()
 

@@ -396,6 +396,7 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 }   // namespace
 
+void umx_conv_ks_tickets_reset(void) { void *p = nullptr; if (cudaGetSymbolAddress(&p, g_ks_tickets) == cudaSuccess && p) cudaMemset(p, 0, sizeof(unsigned) * 8192); }
 int umx_conv_r_fits(const umx_conv *c);
 uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev);
 int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void *enc, int N, int D, int H, int W, const EpiArgs &e,
@@ -437,6 +438,9 @@ static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev,
     c->wr = umx_conv_r_prepare(c, w_dev);
     c->wp = umx_conv_p_prepare(c, w_dev);
     UMX_CK("umx_conv_create");
+    /* the conv kernels read the prepared weights and the bias before their griddepcontrol.wait (they are layer constants that may load while
+       the previous kernel still runs), so the preparation kernels must have finished before a conv can be launched behind them */
+    cudaStreamSynchronize(0);
     return c;
 }
 extern "C" umx_conv *umx_conv_create_dev(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) { return conv_build(kind, w_dev, bias_dev, co, ci, bits); }
@@ -456,6 +460,8 @@ int umx_stats_chunks(int D, int H, int W);
 /* room for 512 partial sums per (sample, channel): the statistics pass uses up to that many voxel chunks, the fused conv epilogue one per block */
 extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
+static int g_last_kernel = -1;
+extern "C" int umx_conv_last_kernel(void) { return g_last_kernel; }
 struct NormArgs { const float *gamma, *beta; float eps; float *coef; };
 static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags, const NormArgs *nrm) {
     if (!umx_ready("umx_conv_fwd")) return -1;
@@ -536,7 +542,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         if (rc > 0) rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, nullptr, nullptr, nullptr, 0.f, nullptr);
         if (rc <= 0) {
             umx_prof_close(pid);
-            g_umx_launches++;
+            g_umx_launches++; g_last_kernel = 1;
             UMX_CK("umx_conv_fwd");
             if (rc == 0 && nrm && !fused) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
             else if (rc == 0 && part && !nrm) umx_in_part(y, N, c->co, D, H, W, part);
@@ -548,7 +554,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         const int rc = umx_conv_fwd_p(c, x, (void *)enc, N, D, H, W, a.e);
         if (rc <= 0) {
             umx_prof_close(pid);
-            g_umx_launches++;
+            g_umx_launches++; g_last_kernel = 2;
             UMX_CK("umx_conv_fwd");
             if (rc == 0 && nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
             else if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
@@ -600,7 +606,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
       double t[8] = {0}; long long mx7 = 0; for (size_t b = 0; b < nblk; b++) { for (int k = 0; k < 8; k++) t[k] += (double)hb[b * 8 + k] / nblk; if (hb[b * 8 + 7] > mx7) mx7 = hb[b * 8 + 7]; }
       fprintf(stderr, "kprof-v1: grid %u x %u x %u ksplit %d ring %d nst %d nt %d stage_bytes %d | mma thread: stages %.0f total %.0f wait-tma %.0f wait-sf %.0f issue %.0f | epilogue: wait-acc %.0f part-store %.0f tail %.0f (max %lld)\n", grid.x, grid.y, grid.z, a.ksplit, a.ring, a.nst, a.nt, a.stage_bytes, t[4], t[3], t[0], t[1], t[2], t[5], t[6], t[7], mx7); free(hb); }
 #endif
-    g_umx_launches++;
+    g_umx_launches++; g_last_kernel = 0;
     UMX_CK("umx_conv_fwd");
     if (nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
     else if (part) umx_in_part(y, N, c->co, D, H, W, part);

@@ -520,6 +520,9 @@ __global__ void __launch_bounds__(128) prep_wr_k(const float *__restrict__ w, ui
 
 }   // namespace
 
+/* after a bounded wait gave up, blocks may have left without drawing their ticket: the counters start from zero again */
+void umx_conv_r_tickets_reset(void) { void *p = nullptr; if (cudaGetSymbolAddress(&p, g_conv_tickets) == cudaSuccess && p) cudaMemset(p, 0, sizeof(unsigned) * 64); }
+
 /* Self-test of the bounded wait and of its report: one block waits, for `limit_clocks` at most, on a barrier that nobody arrives on, gives
    up, and leaves the same record a conv role would (role code 1, stage 123).  Returns 0 when the kernel ran; lp_check() then holds the
    "bounded wait gave up" message.  The context stays usable. */
@@ -569,6 +572,10 @@ static int r_geometry(const umx_conv *c, RGeo *g) {
     if (r_geometry_nt(c, 64, g)) return 1;
     return r_geometry_nt(c, 32, g);
 }
+/* upper bound on the blocks per column tile (0: as many as the device holds): lets a small grid be cut into the multi-run pieces, wrapped
+   slot windows and several-planes-a-block regime that otherwise only volumes with thousands of tile planes reach */
+static int g_r_block_cap = 0;
+extern "C" void umx_conv_r_block_cap(int cap) { g_r_block_cap = cap > 0 ? cap : 0; }
 int umx_conv_r_fits(const umx_conv *c) { RGeo g; return r_geometry(c, &g); }
 /* builds the weight image from device fp32 weights [co][ci][27]; called once when the conv is created */
 uint8_t *umx_conv_r_prepare(const umx_conv *c, const float *w_dev) {
@@ -617,8 +624,9 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     const int room = (two ? 113 : 227) * 1024 - a.off_ring;
     a.ring = room / a.stage_bytes; if (a.ring > 12) a.ring = 12;
     if (a.ring < 3) return 1;
-    const long long slots = (long long)sms * (two ? 2 : 1) / g.ncol;      /* blocks per column tile */
+    long long slots = (long long)sms * (two ? 2 : 1) / g.ncol;      /* blocks per column tile */
     if (slots < 1) return 1;
+    if (g_r_block_cap && slots > g_r_block_cap) slots = g_r_block_cap;
     /* A block pays two halo planes per run: with fewer than eight planes a block (counted for one sample, so that the choice of kernel does not
        depend on the batch) the general kernel is faster.  Volumes with fewer planes than blocks are left here: nothing to gain either way. */
     { const long long units1 = (long long)a.tiles * D; if (units1 >= slots && units1 < 8 * slots) return 1; }

@@ -60,12 +60,13 @@ __global__ void __launch_bounds__(64) in_coef_static_k(const double *__restrict_
 
 /* y: device, blocked fp16 [n][blk][voxel][32] of C channels on an N x D x H x W grid (what a conv stores with UMX_OUT_H16B);
    gamma / beta: device [C] or NULL; coef: device floats [N][C][2], the output.  Returns 0; -1 after latching an error when
-   N * 64 * (C rounded up to 32) * 2 exceeds UMX_STATIC_DOUBLES (e.g. N = 1: up to 4096 channels; N = 8: up to 512) or when no
-   usable device is current.  Calls no allocator of any kind. */
+   N * 64 * (C rounded up to 32) * 2 exceeds UMX_STATIC_DOUBLES (e.g. N = 1: up to 4096 channels; N = 8: up to 512), when a
+   dimension is below 1, when a launch failed, or when no usable device is current.  Calls no allocator of any kind. */
 extern "C" int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef) {
     if (!umx_ready("umx_in_coef_static")) return -1;
     const int nb = (C + 31) / 32, Cop = nb * 32, T = UMX_STATIC_CHUNKS;
     const size_t need = (size_t)N * T * Cop * 2;
+    if (D < 1 || H < 1 || W < 1) { umx_latch_msg("umx_in_coef_static: D, H and W must be at least 1"); return -1; }
     if (N < 1 || C < 1 || need > (size_t)UMX_STATIC_DOUBLES) {
         char b[256]; snprintf(b, sizeof b, "umx_in_coef_static: N = %d, C = %d needs %zu doubles of scratch; the built-in array holds %d (N x 64 x roundup32(C) x 2 must fit)", N, C, need, UMX_STATIC_DOUBLES);
         umx_latch_msg(b);
@@ -84,6 +85,7 @@ extern "C" int umx_in_coef_static(const void *y, int N, int C, int D, int H, int
     in_part_static_k<<<dim3(T, nb, N), 256>>>((const __half *)y, C, S, T, part);
     in_coef_static_k<<<dim3(C, N), 64>>>(part, C, Cop, T, (double)S, gamma, beta, eps, coef);
     g_umx_launches += 2;
-    UMX_CK("umx_in_coef_static");
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) { umx_latch("umx_in_coef_static", le); return -1; }
     return 0;
 }

@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(256) in_part_k(const uint4 *__restrict__ y, si
         }
     }
 }
+void umx_stat_tickets_reset(void) { void *p = nullptr; if (cudaGetSymbolAddress(&p, g_stat_tickets) == cudaSuccess && p) cudaMemset(p, 0, sizeof(unsigned) * 8192); }
 /* InstanceNorm partial sums of a stored blocked-fp16 conv output (what umx_conv_fwd runs after the conv when it is given `part`) */
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part) {
     if (!umx_ready("umx_in_part")) return;

@@ -29,6 +29,9 @@ int umx_ready(const char *where) {
     return 1;
 }
 static int *g_flag[16];
+void umx_conv_r_tickets_reset(void);
+void umx_conv_ks_tickets_reset(void);
+void umx_stat_tickets_reset(void);
 extern "C" const char *lp_check(void) {
     int d = -1;
     if (!g_has_err && cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 16 && g_flag[d]) umx_errflag_read();   /* a kernel's bounded wait that gave up */
@@ -118,6 +121,9 @@ int umx_errflag_read(void) {
         for (int r = 1; r < 8 && n < (int)sizeof b - 60; r++) if (h[16 + 4 * r + 3]) n += snprintf(b + n, sizeof b - n, " %s at stage %d on barrier +%d parity %d;", role[r], h[16 + 4 * r], h[16 + 4 * r + 1], h[16 + 4 * r + 2]);
         snprintf(b + n, sizeof b - n, ")");
         umx_latch_msg(b);
+        /* blocks that gave up left without drawing their tickets: zero the ticket counters of the kernels that finalise from the last block,
+           so that later launches count from zero again, then clear the flag */
+        umx_conv_r_tickets_reset(); umx_conv_ks_tickets_reset(); umx_stat_tickets_reset();
         cudaMemset(f, 0, 256);
     }
     return h[0];

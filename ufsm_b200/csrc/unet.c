@@ -1,4 +1,4 @@
-/* Host side (C23) of the BASELINE 3-D U-Net forward and of the sliding-window scheduler, on top of the C ABI of ufsm_mx.h.
+/* Host side (C23) of the benchmark's 3-D U-Net forward and of the sliding-window scheduler, on top of the C ABI of ufsm_mx.h.
 
    Network (the InstanceNorm / LeakyReLU / transposed-conv graph of the reference's ink U-Net, src/ink3dext_net.c:189-231, with
    the widths and layer list of the benchmark): per level two 3^3 convs, each conv -> fp16 store + InstanceNorm partial sums in
@@ -252,7 +252,8 @@ int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int fir
     const int zext = zhi - zlo; if (zext <= 0) return 0;
     const size_t PS = cube(P), plane = (size_t)V * V;
     float w1d_h[1024]; if (P > 1024) abort();
-    { const double s = P / 8.0, c = (P - 1) / 2.0; for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
+    { const double s = P / 8.0, c = (double)(P / 2);   /* the reference's centre: the integer P / 2 (g1_init, src/nn_ink3dext.cu:48-56) */
+      for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
     float *w1d = nn_malloc((size_t)P * 4), *dacc = nn_malloc((size_t)nh * zext * plane * 4), *dws = nn_malloc((size_t)zext * plane * 4);
     float *logits = nn_malloc((size_t)batch * nh * PS * 4);
     /* two pinned staging buffers: the host gathers the next batch of patches from the volume while the GPU forwards the current one; the
