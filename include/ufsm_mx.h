@@ -30,7 +30,7 @@ enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16
    The scale plane follows the codes unchanged in either layout. */
 enum { UMX_LAYOUT_REF = 0, UMX_LAYOUT_SPLIT = 1 };
 enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2,     /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
-       UMX_FAST_STATS = 4 };                 /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue (fp32 per thread, see there) */
+       UMX_STATS_EPILOGUE = 4 };             /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue where the kernel can (see there) */
 
 /* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
 int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
@@ -125,10 +125,14 @@ void umx_conv_free(umx_conv *c);
 int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags);
 /* the conv with a blocked fp16 output followed by InstanceNorm: y as UMX_OUT_H16B and coef [N][co][2] = (a, b) of the stored values
    (k_in_coef, src/nn_xnet.cu:1565-1570), in one call; part: scratch of umx_stats_doubles doubles.  By default the sums are taken by the
-   fp64 statistics pass (exact to the last bits, independent of batch size and block partition).  With UMX_FAST_STATS the resident-weight
-   conv kernel takes them in its epilogue: fp32 per thread over the block's planes, fp64 across threads and blocks; the coefficients then
-   agree with the exact ones to about 1e-6 relative and depend on the batch size and the number of multiprocessors (a run is still
-   reproducible byte for byte in a fixed configuration). */
+   statistics pass over the stored tensor (fp64 in a fixed order: exact to the last bits, independent of batch size and block partition).
+   With UMX_STATS_EPILOGUE the resident-weight 3^3 kernel takes them in its epilogue instead, as the reference's conv does (st_add,
+   src/nn_xnet.cu:262-268, 370-390: fp32 partial sums per thread, then fp64 atomics, whose order changes from run to run).  Here the order
+   is fixed and the result does not depend on the batch, on the number of multiprocessors or on how the planes fall to the blocks: per
+   channel the stored fp16 values (and their squares, exact in fp32) of one aligned 4 x 8 block of (y, x) voxels of a z plane are added in
+   fp32, first along y (in order), then along x in a butterfly (bit 4 first); everything above those 32-voxel units is exact 128-bit
+   fixed point.  These sums are within 32-voxel fp32 rounding (about 1e-7 relative) of the exact ones.  The epilogue's extra work costs
+   more than the pass saves on the benchmark's layers (measured), which is why it is not the default. */
 int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags);
 size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
 /* testing aid (no counterpart in the reference): at most `cap` thread blocks per column tile in the resident-weight 3^3 kernel (0: as many as

@@ -5,7 +5,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libufsm_mx.so")
+LIB_PATH = os.environ.get("UFSM_MX_LIB") or os.path.join(HERE, "libufsm_mx.so")     # UFSM_MX_LIB: another build of the library (e.g. one with the kernels' cycle counters)
 
 
 class Shape5(C.Structure):

@@ -457,8 +457,9 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
 }
 extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); free(c); }
 int umx_stats_chunks(int D, int H, int W);
-/* room for 512 partial sums per (sample, channel): the statistics pass uses up to that many voxel chunks, the fused conv epilogue one per block */
-extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 2; }
+/* room for 512 partial sums per (sample, channel): the statistics pass uses up to that many voxel chunks of two doubles, the conv epilogue one
+   entry of four 64-bit words per block */
+extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 4; }
 
 static int g_last_kernel = -1;
 extern "C" int umx_conv_last_kernel(void) { return g_last_kernel; }
@@ -537,7 +538,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     /* InstanceNorm statistics are a separate pass over the stored output (umx_in_part below) */
     if (!force_v1 && c->wr) {   /* resident weights: the persistent z-marching kernel, when the geometry allows */
         const int pid = umx_prof_open(flops);
-        int rc = (nrm && (flags & UMX_FAST_STATS)) ? umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, part, nrm->gamma, nrm->beta, nrm->eps, nrm->coef) : 1;
+        int rc = (nrm && (flags & UMX_STATS_EPILOGUE)) ? umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, part, nrm->gamma, nrm->beta, nrm->eps, nrm->coef) : 1;
         const bool fused = rc == 0;
         if (rc > 0) rc = umx_conv_fwd_r(c, x, &m0, (void *)enc, N, D, H, W, a.e, nullptr, nullptr, nullptr, 0.f, nullptr);
         if (rc <= 0) {
@@ -616,8 +617,8 @@ extern "C" int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int 
     return conv_fwd_impl(c, x, N, D, H, W, y, out_mode, out_bits, nb_dst, b0, part, flags, nullptr);
 }
 /* conv -> blocked fp16 y, and the InstanceNorm coefficients (a, b) per (sample, channel) of that stored tensor; part: scratch of
-   umx_stats_doubles doubles.  The resident-weight kernel takes the sums in its epilogue (fp32 per thread and sample, fp64 across threads and
-   blocks); the other kernels are followed by the statistics pass.  gamma / beta: device arrays or NULL (1 / 0). */
+   umx_stats_doubles doubles.  The resident-weight kernel takes the sums in its epilogue (fp32 inside 32-voxel units, exact above them);
+   only under UMX_STATS_EPILOGUE; otherwise, and for the other kernels, the conv is followed by the statistics pass.  gamma / beta: device arrays or NULL (1 / 0). */
 extern "C" int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags) {
     if (!part || !coef) { fprintf(stderr, "umx_conv_fwd_norm: part and coef are required\n"); abort(); }
     if (c && c->kind == UMX_TCONV2) { fprintf(stderr, "umx_conv_fwd_norm: not for the transposed conv\n"); abort(); }

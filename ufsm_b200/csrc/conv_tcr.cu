@@ -9,29 +9,50 @@
    position of the plane, descending), so one MMA of N = 3 x channels updates all three.  When that window wraps around the slot
    ring a stage issues two groups of MMAs.
 
-   What bounds this kernel is not the tensor pipe but instruction issue: a lone thread runs dependent code at one instruction per
-   four to five cycles, while an M = 128, N = 96, K = 32 MMA is 56 cycles of tensor-pipe time (48 of arithmetic; the A and B tiles
-   together exceed what shared memory delivers in 48 cycles).  So every role's per-stage program is kept short: (1) the producer
-   thread tracks slots and parities incrementally (no division) and hands the MMA thread a record with everything precomputed:
-   TMEM addresses, the N field of the instruction descriptor, B descriptor and B scale addresses, the barriers to wait for and to
-   commit; (2) the MMA thread's stage is a straight line of nine MMAs whose operands are a record field plus a constant; (3)
-   accumulators are never "fresh": the epilogue zeroes a slot after reading it, so every MMA accumulates; (4) the A scale factors
-   are gathered from a TMA-staged window in shared memory with no bounds logic (voxels outside the volume arrive as zero codes
-   with scale byte 0); (5) InstanceNorm statistics are not taken here but by a separate bandwidth-bound pass; (6) two blocks share
-   a multiprocessor when the weights are small enough, doubling the issue rate.
+
+   What bounds this kernel.  An M = 128, N = 96, K = 32 MMA occupies the tensor pipe for 56 clocks (48 of arithmetic; its 4 KB A tile and
+   3 KB B tile exceed what shared memory delivers in 48), and one thread cannot issue tcgen05.mma faster than one per 54 clocks whatever
+   N is; a scale copy or a commit costs the thread that issues it another 30 to 130 clocks while it takes next to nothing from the
+   pipe.  So the MMA thread issues nothing but MMAs and one commit per stage, and every role's per-stage program is kept short: (1) the
+   producer thread tracks slots and parities incrementally (no division) and hands the MMA thread a record with everything
+   precomputed: TMEM addresses, the N field of the instruction descriptor, B descriptor and B scale addresses, the barriers to wait
+   for; (2) the MMA thread's stage is three PTX blocks of three MMAs whose operands are a record field plus an immediate; (3)
+   accumulators are never "fresh": the epilogue zeroes a slot after reading it, so every MMA accumulates; (4) the A scale factors are
+   gathered from a TMA-staged window in shared memory with no bounds logic (voxels outside the volume arrive as zero codes with scale
+   byte 0) and copied to TMEM by the scale warps themselves, whose commit is what the MMA thread waits for; (5) the MMA thread's single
+   commit per stage lands on the stage's `empty` barrier; the scale warps, which wait for that barrier anyway before they reuse a TMEM
+   scale buffer, pass the completion of output planes on to the epilogue's accumulator-full barriers; (6) two blocks share a
+   multiprocessor when the weights are small enough: one block's waits are the other's issue time.
 
    Roles (256 threads): warp 0 lane 0 producer (records + TMA), warp 1 lane 0 MMA issue (the warp allocates TMEM), warps 2-3 scale
-   gather (alternate stages), warps 4-7 epilogue.  All waits are bounded as in conv_mx_k. */
+   layout, scale copies and completion relay (alternate stages), warps 4-7 epilogue.  All waits are bounded as in conv_mx_k. */
 #include "conv_epi.cuh"
 #include "tc_ptx.cuh"
 #include <stdlib.h>
 #include <string.h>
 
-#ifdef UMX_KPROF
-#define KP(...) __VA_ARGS__
-#else
-#define KP(...)
-#endif
+
+#define UMX_STR_(x) #x
+#define UMX_STR(x) UMX_STR_(x)
+/* operand numbers of the PTX blocks below: the five immediates of a tap follow one another */
+#define UMX_ADD1(o) UMX_CAT(UMX_N1_, o)
+#define UMX_ADD2(o) UMX_CAT(UMX_N2_, o)
+#define UMX_ADD3(o) UMX_CAT(UMX_N3_, o)
+#define UMX_ADD4(o) UMX_CAT(UMX_N4_, o)
+#define UMX_CAT_(a, b) a##b
+#define UMX_CAT(a, b) UMX_CAT_(a, b)
+#define UMX_N1_8 9
+#define UMX_N2_8 10
+#define UMX_N3_8 11
+#define UMX_N4_8 12
+#define UMX_N1_13 14
+#define UMX_N2_13 15
+#define UMX_N3_13 16
+#define UMX_N4_13 17
+#define UMX_N1_18 19
+#define UMX_N2_18 20
+#define UMX_N3_18 21
+#define UMX_N4_18 22
 
 namespace {
 
@@ -48,15 +69,13 @@ struct ConvRArgs {
     int tmem_cols, sfa_base, sfa_cols, sfb_base; /* TMEM: accumulator slots from 0, two A scale buffers, B scales */
     int off_rec, off_bias, off_stage, off_w, off_ring;   /* off_stage: 2 KB per epilogue warp and 32-channel chunk, the fp16 output rows on their way to coalesced stores */
     int fast_h16;                                /* output is the fp16 blocked tensor of a plain conv: the short epilogue */
-    /* InstanceNorm statistics taken in that epilogue (coef != NULL): per-thread fp32 sums of the stored fp16 values over the block's planes
-       of a sample, reduced once per sample and block into part [n][gcol][cop][2] (fp64); the last block of a column tile to finish turns
-       the partial sums into coefficients (a, b) per (sample, channel) */
+    /* InstanceNorm statistics taken in that epilogue (coef != NULL): sums of the stored fp16 values, fp32 inside 32-voxel units and exact above them,
+       written once per sample and block into part [n][gcol][cop][4] (sum and sum of squares as 128-bit fixed point in units of 2^-64); the last block
+       of a column tile to finish adds the blocks' entries (integer adds) and turns them into coefficients (a, b) per (sample, channel) */
     double *part; float *coef; const float *gamma, *beta; float eps; int cop, off_red;
     const uint8_t *wr;
     EpiArgs e;
     int *err;
-    long long *prof;                             /* cycle counters per block when built with UMX_KPROF */
-    int dbg;
 };
 
 /* what the MMA thread does for one stage; written by the producer thread */
@@ -77,18 +96,38 @@ __device__ __forceinline__ void raise_r(const ConvRArgs &a, volatile int *abort_
     *abort_flag = 1;
     __threadfence_block();
 }
-template <int BITS> __device__ __forceinline__ void mma_bs(uint32_t d, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t sfa, uint32_t sfb) {
-    if (BITS == 8) umma_mxf8(d, ad, bd, idesc, 1u, sfa, sfb); else umma_mxf4(d, ad, bd, idesc, 1u, sfa, sfb);
-}
-/* the nine (dy, dx) MMAs of one group: A views a_lo + (dy * 10 + dx), B tap j at bb + j * bstep, scale quads of four (fp8) or two (fp4) taps */
-template <int BITS> __device__ __forceinline__ void issue_group(uint32_t d, uint32_t idn, uint32_t bb, uint32_t sfb, uint32_t a_lo, uint32_t a_hi, uint32_t b_hi, uint32_t bstep, uint32_t sfa_t, uint32_t sfb_per_q) {
+/* Three of the nine (dy, dx) MMAs of a group in one PTX block: tap j reads the A view a_lo + (j / 3) * 10 + j % 3 and the B image
+   b_lo + j * BSTEP; the scale sets come in quads of four (fp8) or two (fp4) taps.  Everything that depends on the tap is an immediate, so
+   between two MMAs the issuing thread runs a handful of independent integer instructions that the assembler is free to hoist: a lone
+   thread runs dependent scalar code at four to five clocks an instruction, and every clock it spends between MMAs the tensor pipe idles. */
+template <int BITS, int BSTEP, int SFBQ, int J0>
+__device__ __forceinline__ void mma3(uint32_t d, uint32_t idn, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t sfa, uint32_t sfb) {
     constexpr int IPQ = BITS == 8 ? 4 : 2;
-#pragma unroll
-    for (int j = 0; j < 9; j++) {
-        const int q = j / IPQ, id = (j % IPQ) * (4 / IPQ);
-        mma_bs<BITS>(d, desc_make(a_lo + (uint32_t)((j / 3) * 10 + j % 3), a_hi), desc_make(bb + (uint32_t)j * bstep, b_hi),
-                     idn | ((uint32_t)id << 4) | ((uint32_t)id << 29), sfa_t + 4 * q, sfb + (uint32_t)q * sfb_per_q);
+#define UMX_TAP(j) "n"(((j) / 3) * 10 + (j) % 3), "n"((j) * BSTEP), "n"(((((j) % IPQ) * (4 / IPQ)) << 4) | ((((j) % IPQ) * (4 / IPQ)) << 29)), "n"(4 * ((j) / IPQ)), "n"(((j) / IPQ) * SFBQ)
+#define UMX_MMA_TEXT(KIND, o)                                                                                        \
+    "add.u32 ta, %2, %" #o ";\n\tmov.b64 da, {ta, %3};\n\t"                                                         \
+    "add.u32 tb, %4, %" UMX_STR(UMX_ADD1(o)) ";\n\tmov.b64 db, {tb, %5};\n\t"                                      \
+    "or.b32 ti, %1, %" UMX_STR(UMX_ADD2(o)) ";\n\t"                                                                   \
+    "add.u32 sa, %6, %" UMX_STR(UMX_ADD3(o)) ";\n\tadd.u32 sb, %7, %" UMX_STR(UMX_ADD4(o)) ";\n\t"                  \
+    "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, ti, [sa], [sb], p;\n\t"
+    if constexpr (BITS == 8) {
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 ta, tb, ti, sa, sb;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+                     UMX_MMA_TEXT("mxf8f6f4.block_scale", 8) UMX_MMA_TEXT("mxf8f6f4.block_scale", 13) UMX_MMA_TEXT("mxf8f6f4.block_scale", 18) "}"
+                     ::"r"(d), "r"(idn), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(sfa), "r"(sfb), UMX_TAP(J0), UMX_TAP(J0 + 1), UMX_TAP(J0 + 2) : "memory");
+    } else {
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 ta, tb, ti, sa, sb;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+                     UMX_MMA_TEXT("mxf4.block_scale.scale_vec::2X", 8) UMX_MMA_TEXT("mxf4.block_scale.scale_vec::2X", 13) UMX_MMA_TEXT("mxf4.block_scale.scale_vec::2X", 18) "}"
+                     ::"r"(d), "r"(idn), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(sfa), "r"(sfb), UMX_TAP(J0), UMX_TAP(J0 + 1), UMX_TAP(J0 + 2) : "memory");
     }
+#undef UMX_TAP
+#undef UMX_MMA_TEXT
+}
+/* the nine (dy, dx) MMAs of one group into the accumulator window at d (idn: the instruction descriptor with the window's N) */
+template <int BITS, int NT> __device__ __forceinline__ void issue_group(uint32_t d, uint32_t idn, uint32_t bb, uint32_t sfb, uint32_t a_lo, uint32_t a_hi, uint32_t b_hi, uint32_t sfa_t) {
+    constexpr int BSTEP = 2 * 3 * NT, SFBQ = 4 * ((3 * NT + 127) / 128 + (2 * NT + 127) / 128 + (NT + 127) / 128);
+    mma3<BITS, BSTEP, SFBQ, 0>(d, idn, a_lo, a_hi, bb, b_hi, sfa_t, sfb);
+    mma3<BITS, BSTEP, SFBQ, 3>(d, idn, a_lo, a_hi, bb, b_hi, sfa_t, sfb);
+    mma3<BITS, BSTEP, SFBQ, 6>(d, idn, a_lo, a_hi, bb, b_hi, sfa_t, sfb);
 }
 /* the block's piece of the plane list, u in [u0, u1) with u = (sample * tiles + tile) * D + z, cut into runs along z */
 struct Piece { long long u, u1; };
@@ -103,6 +142,47 @@ __device__ __forceinline__ Run next_run(const ConvRArgs &a, Piece &p) {
     r.n = (int)(col / a.tiles); r.txy = (int)(col - (long long)r.n * a.tiles);
     p.u += r.ze - r.zb;
     return r;
+}
+
+/* ---- InstanceNorm sums in the epilogue.  The unit of fp32 arithmetic is one aligned block of 4 x 8 (y, x) voxels of one z plane: the 32
+   voxels an epilogue warp holds.  Per channel the stored fp16 values (and their squares, which are exact in fp32) are added first along
+   y, ((v0 + v1) + v2) + v3, then along x in a butterfly, x bit 4 first, then 2, then 1.  Everything above that unit is exact: the unit
+   sums are accumulated as 128-bit fixed point in units of 2^-64 (integer adds: any order, any partition of the planes over blocks, any
+   batch gives the same words).  The sums are taken where the warp re-reads its staged rows for the coalesced store: there a lane
+   holds eight channels of the four voxels of one x, so the y sums need no exchange and the x butterfly runs over the eight lanes that
+   hold the same channels, each lane keeping half of its values per round: 7 shuffles per array instead of 31. ---- */
+__device__ __forceinline__ float x_butterfly(float (&v)[8], int x, int p4, int p2, int p1) {
+    {
+        const bool up = (x & 4) != 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) { const float send = up ? v[k] : v[k + 4], keep = up ? v[k + 4] : v[k]; v[k] = __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p4)); }
+    }
+    {
+        const bool up = (x & 2) != 0;
+#pragma unroll
+        for (int k = 0; k < 2; k++) { const float send = up ? v[k] : v[k + 2], keep = up ? v[k + 2] : v[k]; v[k] = __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p2)); }
+    }
+    const bool up = (x & 1) != 0;
+    const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
+    return __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p1));
+}
+/* (hi, lo) += x 2^64 for a finite |x| < 2^62 (values below 2^-64 in magnitude are cut off towards zero); anything else sets bad */
+__device__ __forceinline__ void fx_add(long long &hi, unsigned long long &lo, int &bad, float x) {
+    const unsigned u = __float_as_uint(x); const int ex = (int)((u >> 23) & 255u);
+    const unsigned long long m = (unsigned long long)((u & 0x7fffffu) | (ex ? 0x800000u : 0u));
+    const int sh = (ex ? ex : 1) - 150 + 64;                /* x = m 2^(sh - 64) */
+    if (ex == 255 || sh > 64 + 38) { bad = 1; return; }
+    unsigned long long vlo, vhi;
+    if (sh >= 64) { vhi = m << (sh - 64); vlo = 0ull; }
+    else if (sh > 0) { vlo = m << sh; vhi = m >> (64 - sh); }
+    else if (sh > -24) { vlo = m >> (-sh); vhi = 0ull; }
+    else { vlo = 0ull; vhi = 0ull; }
+    if (u >> 31) { vlo = ~vlo + 1ull; vhi = ~vhi + (vlo == 0ull ? 1ull : 0ull); }
+    const unsigned long long nlo = lo + vlo;
+    hi += (long long)(vhi + (nlo < lo ? 1ull : 0ull)); lo = nlo;
+}
+__device__ __forceinline__ void fx_add128(long long &hi, unsigned long long &lo, long long bhi, unsigned long long blo) {
+    const unsigned long long nlo = lo + blo; hi += bhi + (long long)(nlo < lo ? 1ull : 0ull); lo = nlo;
 }
 
 __device__ unsigned g_conv_tickets[64];      /* one per column tile; the block that draws the last ticket finalises and resets it */
@@ -133,7 +213,6 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
         fence_barrier_init();
         fence_proxy_async();
     }
-    KP(const long long ta0 = clock64(); long long tg0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg0));)
     const int ctile = (int)blockIdx.x / a.gcol;
     if ((int)threadIdx.x < a.nt) bias_s[threadIdx.x] = a.e.bias[ctile * a.nt + threadIdx.x];
     pdl_trigger();
@@ -161,7 +240,6 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             const uint32_t sfb_t0 = tmem + (uint32_t)a.sfb_base, sfb_per_ki = (uint32_t)(a.nquad * a.gt * 4);
             int s = 0, ph = 0, it = 0; bool ok = true;
             int pos = NS - 1; uint32_t wp = 1u;           /* ring position and wrap parity of the newest plane started so far */
-            KP(long long p_wait = 0, p_rec = 0; const long long p_t0 = clock64();)
             while (piece.u < piece.u1 && ok) {
                 const Run rn = next_run(a, piece);
                 const bool last_run = piece.u >= piece.u1;
@@ -181,23 +259,17 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                         if (f == 0) w0 = wf; else w1 = wf;
                     }
                     const int slot = NS - 1 - pos, n1 = min(cnt, NS - slot), n2 = cnt - n1;
-                    int so = slot + cnt - 1; if (so >= NS) so -= NS;
-                    const uint32_t c0 = zi - 1 >= zb ? bar_accf + 8u * (uint32_t)so : 0u;
-                    const uint32_t c1 = (zi == a.D - 1 && ze == a.D) ? bar_accf + 8u * (uint32_t)slot : 0u;
                     const uint32_t g1 = (uint32_t)(dzf == 0 ? 0 : dzf == 1 ? a.goff1 : a.goff2), g2 = (uint32_t)(dzf + n1 == 1 ? a.goff1 : a.goff2);
                     for (int ki = 0; ki < a.nki; ki++) {
-                        KP(const long long pw0 = clock64();)
                         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 1, it, bar_empty + 8 * s - bar_tma, ph ^ 1); ok = false; break; }
-                        KP(p_wait += clock64() - pw0; const long long pw1 = clock64();)
                         const bool kl = ki == a.nki - 1;
                         const uint32_t bk = b_lo0 + (uint32_t)ki * bstep9, sk = sfb_t0 + (uint32_t)ki * sfb_per_ki;
                         uint4 *r = (uint4 *)(recs + s);
                         r[0] = make_uint4(tmem + (uint32_t)slot * nt, idesc_b | (uint32_t)n1 * ntn, bk + (uint32_t)dzf * nt, sk + g1);
                         r[1] = make_uint4(tmem, n2 ? (idesc_b | (uint32_t)n2 * ntn) : 0u, bk + (uint32_t)(dzf + n1) * nt, sk + g2);
-                        r[2] = make_uint4(ki == 0 ? w0 : 0u, ki == 0 ? w1 : 0u, kl ? c0 : 0u, kl ? c1 : 0u);
+                        r[2] = make_uint4(ki == 0 ? w0 : 0u, ki == 0 ? w1 : 0u, 0u, 0u);
                         r[3] = make_uint4((last_run && zi == zhi && kl) ? 1u : 0u, 0u, 0u, 0u);
                         const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes), bar = bar_tma + 8 * s;
-                        KP(p_rec += clock64() - pw1;)
                         mbar_expect_tx(bar, TX);
                         /* codes: two 16-byte-wide planes (fp8: the halves of block ki; fp4: blocks 2 ki and 2 ki + 1), 18 rows of 10 voxels;
                            scale bytes: 18 rows of a 32-byte window per block */
@@ -207,7 +279,6 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     }
                 }
             }
-            KP(a.prof[(size_t)blockIdx.x * 32 + 16] = p_wait; a.prof[(size_t)blockIdx.x * 32 + 17] = clock64() - p_t0; a.prof[(size_t)blockIdx.x * 32 + 24] = it; a.prof[(size_t)blockIdx.x * 32 + 8] = p_rec;)
         }
     } else if (warp == 1) {
         /* ---------------- MMA issue: one thread follows the records; a stage is straight-line code ---------------- */
@@ -215,24 +286,21 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             bool ok = mbar_wait(bar_w, 0, abort_flag, kWaitLimitR);
             if (!ok) raise_r(a, abort_flag, 6, 0);
             tc_fence_after();
-            const uint32_t wbase = smem_u32(wsm), bstep = 2u * 3u * (uint32_t)a.nt;
+            const uint32_t wbase = smem_u32(wsm);
             const uint32_t a_hi = desc_hi(160), b_hi = desc_hi(128);
-            const uint32_t sfb_per_q = (uint32_t)(a.gt * 4);
             const uint32_t sf_hi = desc_hi(128);                     /* scale blocks: 32 rows of 16 bytes, 8-row groups 128 bytes apart */
             if (ok) {
                 /* the B scale factors of every (input block, tap quad, image, 128-row group): copied to TMEM once */
                 const int nsf = a.nki * a.nquad * a.gt;
                 for (int i = 0; i < nsf; i++) utccp_32x128b(tmem + a.sfb_base + i * 4, desc_make(desc_lo(wbase + a.w_codes + i * 512, 0), sf_hi));
             }
-            const uint32_t a_lo0 = desc_lo(smem_u32(stages), 2880), a_step = (uint32_t)a.stage_bytes >> 4, sfa_off = (uint32_t)a.offSFA >> 4;
+            const uint32_t a_lo0 = desc_lo(smem_u32(stages), 2880), a_step = (uint32_t)a.stage_bytes >> 4;
             const uint32_t sfa_t0 = tmem + (uint32_t)a.sfa_base, sfa_cols = (uint32_t)a.sfa_cols;
             int s = 0, ph = 0, it = 0;
-            KP(long long m_full = 0, m_acce = 0, m_issue = 0; const long long m_t0 = clock64();)
             while (ok) {
-                KP(const long long mw0 = clock64();)
+                /* the stage's A scales are in TMEM (the scale warp's copies have completed); that warp passed the stage's load barrier before
+                   it laid the scales out, so the codes have landed too */
                 if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 3, it, bar_sf + 8 * s - bar_tma, ph); break; }
-                /* no wait on the stage's load barrier here: the gather warp passed it before it laid the scales out and arrived on bar_sf */
-                KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
                 /* the whole record goes to registers before anything is committed: committing `empty` hands the stage, record included, back to the producer */
                 const uint4 *r = (const uint4 *)(recs + s);
                 const uint4 g1 = r[0], g2 = r[1], wc = r[2]; const uint32_t last = r[3].x;
@@ -241,69 +309,101 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     if (wc.y && !mbar_wait(wc.y & 0x7fffffffu, wc.y >> 31, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 7, it); break; }
                 }
                 tc_fence_after();
-                KP(const long long mw2 = clock64(); m_acce += mw2 - mw1;)
                 const uint32_t a_lo = a_lo0 + (uint32_t)s * a_step, sfa_t = sfa_t0 + ((uint32_t)it & 1u) * sfa_cols;
-#pragma unroll
-                for (int q = 0; q < NQ; q++) utccp_32x128b(sfa_t + 4 * q, desc_make((a_lo & 0xffffu) + sfa_off + 32u * q, sf_hi));
-                issue_group<BITS>(g1.x, g1.y, g1.z, g1.w, a_lo, a_hi, b_hi, bstep, sfa_t, sfb_per_q);
-                if (g2.y) issue_group<BITS>(g2.x, g2.y, g2.z, g2.w, a_lo, a_hi, b_hi, bstep, sfa_t, sfb_per_q);
-                if (wc.z) umma_commit(wc.z);
-                if (wc.w) umma_commit(wc.w);
+                issue_group<BITS, 32 * NCH>(g1.x, g1.y, g1.z, g1.w, a_lo, a_hi, b_hi, sfa_t);
+                if (g2.y) issue_group<BITS, 32 * NCH>(g2.x, g2.y, g2.z, g2.w, a_lo, a_hi, b_hi, sfa_t);
+                /* the one commit of a stage: "stage s has been consumed".  The producer reuses the ring slot on it, the scale warps reuse the
+                   stage's TMEM scale buffer on it and pass the news that output planes are complete on to the epilogue */
                 umma_commit(bar_empty + 8 * s);
-                KP(m_issue += clock64() - mw2;)
                 it++; if (++s == R) { s = 0; ph ^= 1; }
                 if (last) break;
             }
-            KP({ long long *q = a.prof + (size_t)blockIdx.x * 32; q[18] = m_full; q[19] = m_acce; q[20] = m_issue; q[21] = clock64() - m_t0; q[28] = m_t0 - ta0; q[29] = clock64() - ta0; long long tg1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tg1)); q[30] = tg1 - tg0; })
         }
     } else if (warp < 4) {
-        /* ---------------- A scale layout: warp 2 takes the even stages, warp 3 the odd ones ----------------
+        /* ---------------- A scales: warp 2 takes the even stages, warp 3 the odd ones ----------------
            The TMA left 18 rows of a 32-byte window of scale bytes (two windows for fp4); row r of the tile needs, for tap (dy, dx), the
-           byte at window row r / 8 + dy, column r % 8 + dx + (x0 - 1 - xa).  Four rows per lane (one per TMEM column of the quad). */
+           byte at window row r / 8 + dy, column r % 8 + dx + (x0 - 1 - xa).  Four rows per lane (one per TMEM column of the quad).  The
+           warp lays the nine shifted scale sets out in shared memory in the tcgen05.cp layout, and its lane 0 copies them to the TMEM
+           scale buffer of the stage's parity and commits: the MMA thread waits for that commit and issues nothing but MMAs (a scale copy
+           or a commit costs its issuing thread 30 to 130 clocks, an MMA of N = 96 occupies the tensor pipe for 56).
+
+           The same warps relay completions.  The MMA thread commits once per stage, on the stage's `empty` barrier.  A scale warp
+           waits for that barrier of stage it - 2 before it touches the TMEM scale buffer again (two buffers: the MMAs that read it must
+           have completed), and it knows which output planes that stage completed (the plane below the input plane, and the volume's
+           last plane with it), so it arrives on their accumulator-full barriers, which the epilogue waits on.  Both warps pass every
+           barrier of both kinds in order, also for the stages the other warp works on: a warp that skipped a phase of a barrier could
+           later take a wait for phase k + 2 as satisfied while the barrier is still in phase k + 1 (the parity reads the same). */
         const int sfw = warp - 2;
-        int it = 0, s = 0, ph = 0; bool ok = true;
-        KP(long long g_wait = 0; const long long g_t0 = clock64();)
+        const uint32_t sf_hi = desc_hi(128);
+        const uint32_t sfa_t = tmem + (uint32_t)a.sfa_base + (uint32_t)sfw * (uint32_t)a.sfa_cols;      /* this warp's stages all have parity sfw */
+        int it = 0, s = 0, ph = 0, s2 = 0, ph2 = 0; bool ok = true;
+        int done = 0;                       /* output planes completed by all stages before the current one */
+        int rel_first = 0, rel_n = 0;       /* the planes this warp's latest stage completes: relayed once that stage's commit has arrived */
+        /* stage j = it - 2 has been consumed: pass its barrier; the warp that laid it out tells the epilogue about its planes */
+        auto pass_empty = [&](bool mine) -> bool {
+            if (!mbar_wait(bar_empty + 8 * s2, ph2, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 2, it, bar_empty + 8 * s2 - bar_tma, ph2); return false; }
+            if (++s2 == R) { s2 = 0; ph2 ^= 1; }
+            if (mine && lane == 0) {
+                for (int k = 0; k < rel_n; k++) mbar_arrive(bar_accf + 8u * (uint32_t)(NS - 1 - (rel_first + k) % NS));
+            }
+            return true;
+        };
         while (piece.u < piece.u1 && ok) {
             const Run rn = next_run(a, piece);
             const int x0 = (rn.txy % a.tiles_x) * 8;
             const int zlo = max(0, rn.zb - 1), zhi = min(a.D - 1, rn.ze);
             const int xo = (x0 - 1) - (((x0 - 1) >> 4) << 4);     /* 7 or 15 */
-            const int nst = (zhi - zlo + 1) * a.nki;
-            for (int i = 0; i < nst && ok; i++) {
-                const int my = (it & 1) == sfw, cs = s, cph = ph;
-                it++; if (++s == R) { s = 0; ph ^= 1; }
-                /* Both warps pass every stage's barrier in order, also for the stages the other warp lays out.  A warp that skipped them could
-                   come back to a ring slot a whole round later before the slot's first load had landed; a parity wait for the second round
-                   on a barrier still in its first phase is satisfied at once (it reads as the phase before the first), and the warp would lay
-                   out, and signal, a stage that does not exist yet. */
-                KP(const long long gw0 = clock64();)
-                if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it, 8 * cs, cph); ok = false; break; }
-                KP(g_wait += clock64() - gw0;)
-                if (!my) continue;
-                uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
-                const uint8_t *sw = stg + a.offSW;
-                uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int r = q * 32 + lane;
-                    const uint8_t *p = sw + (r >> 3) * 32 + (r & 7) + xo;
-                    uint32_t wq[5] = {0, 0, 0, 0, 0};
-#pragma unroll
-                    for (int j = 0; j < 9; j++) {
-                        const uint32_t b0 = p[(j / 3) * 32 + j % 3];
-                        if (BITS == 8) wq[j >> 2] |= b0 << (8 * (j & 3));
-                        else { const uint32_t b1 = p[576 + (j / 3) * 32 + j % 3]; wq[j >> 1] |= (b0 | (b1 << 8)) << (16 * (j & 1)); }
+            for (int zi = zlo; zi <= zhi && ok; zi++) {
+                /* planes that the last stage of this input plane completes: the plane below it, and the volume's last plane with it */
+                const int nc = (zi - 1 >= rn.zb ? 1 : 0) + ((zi == a.D - 1 && rn.ze == a.D) ? 1 : 0);
+                for (int ki = 0; ki < a.nki && ok; ki++) {
+                    const bool my = (it & 1) == sfw; const int cs = s, cph = ph;
+                    if (!mbar_wait(bar_tma + 8 * cs, cph, abort_flag, kWaitLimitR)) { if (lane == 0) raise_r(a, abort_flag, 4, it, 8 * cs, cph); ok = false; break; }
+                    const int ncs = ki == a.nki - 1 ? nc : 0;
+                    if (!my) {
+                        if (it >= 2 && !pass_empty(false)) { ok = false; break; }
+                        done += ncs;
+                        it++; if (++s == R) { s = 0; ph ^= 1; }
+                        continue;
                     }
-                    /* quad qd: word (lane, column) = row 32 * column + lane */
+                    uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
+                    const uint8_t *sw = stg + a.offSW;
+                    uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
 #pragma unroll
-                    for (int qd = 0; qd < NQ; qd++) sfa[qd * 128 + lane * 4 + q] = wq[qd];
+                    for (int q = 0; q < 4; q++) {
+                        const int r = q * 32 + lane;
+                        const uint8_t *p = sw + (r >> 3) * 32 + (r & 7) + xo;
+                        uint32_t wq[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+                        for (int j = 0; j < 9; j++) {
+                            const uint32_t b0 = p[(j / 3) * 32 + j % 3];
+                            if (BITS == 8) wq[j >> 2] |= b0 << (8 * (j & 3));
+                            else { const uint32_t b1 = p[576 + (j / 3) * 32 + j % 3]; wq[j >> 1] |= (b0 | (b1 << 8)) << (16 * (j & 1)); }
+                        }
+                        /* quad qd: word (lane, column) = row 32 * column + lane */
+#pragma unroll
+                        for (int qd = 0; qd < NQ; qd++) sfa[qd * 128 + lane * 4 + q] = wq[qd];
+                    }
+                    fence_proxy_async();
+                    /* the scale sets are laid out; before they go to TMEM, the MMAs that read this buffer two stages ago must have completed */
+                    if (it >= 2 && !pass_empty(true)) { ok = false; break; }
+                    rel_first = done; rel_n = ncs;
+                    done += ncs;
+                    it++; if (++s == R) { s = 0; ph ^= 1; }
+                    __syncwarp();
+                    if (lane == 0) {
+                        tc_fence_after();
+                        const uint32_t src = desc_lo(smem_u32(sfa), 0);
+#pragma unroll
+                        for (int q = 0; q < NQ; q++) utccp_32x128b(sfa_t + 4 * q, desc_make(src + 32u * q, sf_hi));
+                        umma_commit(bar_sf + 8 * cs);
+                    }
+                    __syncwarp();
                 }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_sf + 8 * cs);
             }
         }
-        KP(if (lane == 0 && sfw == 0) { a.prof[(size_t)blockIdx.x * 32 + 22] = g_wait; a.prof[(size_t)blockIdx.x * 32 + 25] = clock64() - g_t0; })
+        /* the last two stages: their commits, and the planes of this warp's last stage */
+        for (int k = (it >= 2 ? 2 : it); k > 0 && ok; k--) { const bool my = ((it - k) & 1) == sfw; if (!pass_empty(my)) ok = false; }
     } else {
         /* ---------------- epilogue: one output plane of one tile at a time ---------------- */
         const int q4 = warp & 3, r = q4 * 32 + lane, ry = r >> 3, rx = r & 7;
@@ -321,31 +421,43 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
         const size_t S = (size_t)a.D * a.H * a.W;
         constexpr bool stats = STATS;
         const int et = (int)threadIdx.x - 128, bcol = (int)blockIdx.x % a.gcol;
-        float ssum[STATS ? NCH * 32 : 1], ssq[STATS ? NCH * 32 : 1];
+        const int cl = (lane & 3) ^ ((lane >> 3) & 3);          /* the 16-byte chunk of a staged row this lane finds when it re-reads the rows for the coalesced store (see below) */
+        /* statistics: x of this lane's voxels, the lanes that hold the same channels at x ^ 4, x ^ 2, x ^ 1, and the channel (of a 32-channel
+           chunk) whose unit sum this lane ends up with */
+        const int sx = lane >> 2;
+        const int sp4 = 4 * (sx ^ 4) + (cl ^ (((sx ^ 4) >> 1) & 3)), sp2 = 4 * (sx ^ 2) + (cl ^ (((sx ^ 2) >> 1) & 3)), sp1 = 4 * (sx ^ 1) + (cl ^ (((sx ^ 1) >> 1) & 3));
+        const int sch = 8 * cl + sx;
+        /* this lane's channels (sch, and sch + 32 of a 64-channel tile): sums and sums of squares of the sample in progress, 2^-64 fixed point */
+        long long s_hi[NCH], q_hi[NCH]; unsigned long long s_lo[NCH], q_lo[NCH]; int bad = 0;
 #pragma unroll
-        for (int k = 0; k < (STATS ? NCH * 32 : 1); k++) { ssum[k] = 0.f; ssq[k] = 0.f; }
-        float *red = (float *)(smem_raw + a.off_red);          /* [4 warps][nt][2] */
+        for (int k = 0; k < NCH; k++) { s_hi[k] = 0; q_hi[k] = 0; s_lo[k] = 0ull; q_lo[k] = 0ull; }
+        unsigned long long *red = (unsigned long long *)(smem_raw + a.off_red);          /* [4 warps][nt][4] */
         uint32_t red_ph = 0;
         /* the 128 epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync: after a give-up nobody is left waiting for good) */
         auto esync = [&]() { mbar_arrive(bar_red); if (!mbar_wait(bar_red, red_ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 8, pc); dead = true; } red_ph ^= 1u; };
-        /* writes this block's sums of sample n (or zeros) */
+        /* writes this block's sums of sample n (or zeros): four words per channel (sum hi, lo, squares hi, lo; hi = the largest 64-bit integer
+           marks a sum that met a non-finite value) */
         auto flush = [&](int n, bool have) {
+            esync();                                            /* every warp is done with the staging buffers the exchange area overlays */
             if (have) {
 #pragma unroll
-                for (int k = 0; k < (STATS ? NCH * 32 : 1); k++) {
-                    float s0 = ssum[k], q0 = ssq[k];
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); q0 += __shfl_xor_sync(0xffffffffu, q0, o); }
-                    if (lane == 0) { red[(q4 * a.nt + k) * 2] = s0; red[(q4 * a.nt + k) * 2 + 1] = q0; }
-                    ssum[k] = 0.f; ssq[k] = 0.f;
+                for (int k = 0; k < NCH; k++) {
+                    unsigned long long *d = red + ((size_t)(q4 * a.nt + k * 32 + sch)) * 4;
+                    d[0] = bad ? 0x7fffffffffffffffull : (unsigned long long)s_hi[k]; d[1] = s_lo[k]; d[2] = (unsigned long long)q_hi[k]; d[3] = q_lo[k];
+                    s_hi[k] = 0; q_hi[k] = 0; s_lo[k] = 0ull; q_lo[k] = 0ull;
                 }
+                bad = 0;
             }
             esync();
             if (et < a.nt) {
-                double s0 = 0.0, q0 = 0.0;
-                if (have) for (int w4 = 0; w4 < 4; w4++) { s0 += (double)red[(w4 * a.nt + et) * 2]; q0 += (double)red[(w4 * a.nt + et) * 2 + 1]; }
-                double *d = a.part + (((size_t)n * a.gcol + bcol) * a.cop + ctile * a.nt + et) * 2;
-                d[0] = s0; d[1] = q0;
+                long long sh = 0, qh = 0; unsigned long long sl = 0ull, ql = 0ull; bool nf = false;
+                if (have) for (int w4 = 0; w4 < 4; w4++) {
+                    const unsigned long long *r4 = red + ((size_t)(w4 * a.nt + et)) * 4;
+                    nf = nf || r4[0] == 0x7fffffffffffffffull;
+                    fx_add128(sh, sl, (long long)r4[0], r4[1]); fx_add128(qh, ql, (long long)r4[2], r4[3]);
+                }
+                unsigned long long *d = (unsigned long long *)a.part + (((size_t)n * a.gcol + bcol) * a.cop + ctile * a.nt + et) * 4;
+                d[0] = nf ? 0x7fffffffffffffffull : (unsigned long long)sh; d[1] = sl; d[2] = (unsigned long long)qh; d[3] = ql;
             }
             esync();
         };
@@ -355,10 +467,12 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
         uint8_t *stg = smem_raw + a.off_stage + q4 * (2048 * NCH);
         uint8_t *stg_w = stg + lane * 64; const int swz = (lane >> 1) & 3;
         const uint8_t *stg_r = stg + (lane >> 2) * 64 + (lane & 3) * 16;
-        const int cl = (lane & 3) ^ ((lane >> 3) & 3);          /* the chunk this lane finds there */
         const size_t plane_b = (size_t)a.H * a.W * 64, row_b = (size_t)a.W * 64;
-        int n_cur = -1, n_next = 0;                             /* sample being accumulated; first sample without an entry yet */
-        KP(long long e_wait = 0, e_ld = 0, e_zero = 0, e_store = 0; const long long e_t0 = clock64();)
+        /* sample being accumulated and the first sample this block has planes of.  Nothing is written to `part` before the block has taken a plane
+           out of TMEM: this kernel may have been started while its predecessor in the stream, which can be a conv that shares `part`, was still
+           running, and only the producer thread waits for the predecessor; a plane in TMEM means that wait is over.  So the zero entries of the
+           samples this block has no planes of are written at the end. */
+        int n_cur = -1, n_first = -1;
         while (piece.u < piece.u1 && !dead) {
             const Run rn = next_run(a, piece);
             const int x0t = (rn.txy % a.tiles_x) * 8, y0t = (rn.txy / a.tiles_x) * 16;
@@ -367,22 +481,18 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             const int sy = y0t + q4 * 4;                        /* first of the four tile rows this warp stores */
             uint8_t *run_dst = (uint8_t *)a.e.y + (((size_t)rn.n * a.e.nb_dst + a.e.b0 + ctile * NCH) * S + (size_t)sy * a.W + x0t + (lane >> 2)) * 64 + cl * 16;
             if (stats && rn.n != n_cur) {
-                if (n_cur >= 0) { flush(n_cur, true); n_next = n_cur + 1; }
-                for (; n_next < rn.n; n_next++) flush(n_next, false);
+                if (n_cur >= 0) flush(n_cur, true); else n_first = rn.n;
                 n_cur = rn.n;
             }
             for (int z = rn.zb; z < rn.ze && !dead; z++, pc++) {
                 const int slot = NS - 1 - pcm;
-                KP(const long long ew0 = clock64();)
                 if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)pph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 5, pc, bar_accf + 8 * slot - bar_tma, pph); dead = true; break; }
-                KP(e_wait += clock64() - ew0; const long long ew1 = clock64();)
                 tc_fence_after();
                 uint32_t rr[NCH][32];
                 const uint32_t tcol = tlane + (uint32_t)(slot * a.nt);
                 tmem_ld32(tcol, rr[0]);
                 if (NCH > 1) tmem_ld32(tcol + 32, rr[NCH - 1]);
                 tmem_ld_wait();
-                KP(const long long ew2 = clock64(); e_ld += ew2 - ew1;)
                 tmem_zero32(tcol);
                 if (NCH > 1) tmem_zero32(tcol + 32);
                 if (a.fast_h16) {
@@ -400,31 +510,38 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                             h[2] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 4]), b1.x), __fadd_rn(__uint_as_float(rr[jc][8 * k + 5]), b1.y));
                             h[3] = __floats2half2_rn(__fadd_rn(__uint_as_float(rr[jc][8 * k + 6]), b1.z), __fadd_rn(__uint_as_float(rr[jc][8 * k + 7]), b1.w));
                             *(uint4 *)(stg_w + jc * 2048 + ((k ^ swz) << 4)) = make_uint4(*(const uint32_t *)&h[0], *(const uint32_t *)&h[1], *(const uint32_t *)&h[2], *(const uint32_t *)&h[3]);
-                            if (STATS && row_ok) {
-#pragma unroll
-                                for (int t = 0; t < 4; t++) {
-                                    const float2 f = __half22float2(h[t]);          /* the stored values */
-                                    const int ch = STATS ? jc * 32 + 8 * k + 2 * t : 0;
-                                    ssum[ch] += f.x; ssq[ch] = __fmaf_rn(f.x, f.x, ssq[ch]); ssum[ch + (STATS ? 1 : 0)] += f.y; ssq[ch + (STATS ? 1 : 0)] = __fmaf_rn(f.y, f.y, ssq[ch + (STATS ? 1 : 0)]);
-                                }
-                            }
                         }
                     }
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_acce + 8 * slot);          /* the slot is free once it is in registers and zeroed */
-                    KP(const long long ew3 = clock64(); e_zero += ew3 - ew2;)
                     uint8_t *pz = run_dst + (size_t)z * plane_b;
 #pragma unroll
                     for (int jc = 0; jc < NCH; jc++) {
+                        float sv[8], sq[8];                    /* this lane's eight channels: sums over the four voxels of its x */
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
                             const uint4 v = *(const uint4 *)(stg_r + jc * 2048 + i * 512);
-                            if (sy + i < a.H) *(uint4 *)(pz + (size_t)jc * S * 64 + (size_t)i * row_b) = v;
+                            const bool in = sy + i < a.H;
+                            if (in) *(uint4 *)(pz + (size_t)jc * S * 64 + (size_t)i * row_b) = v;
+                            if (STATS) {
+                                const __half2 *hp = (const __half2 *)&v;
+#pragma unroll
+                                for (int t = 0; t < 4; t++) {
+                                    float2 f = __half22float2(hp[t]);
+                                    if (!in) { f.x = 0.f; f.y = 0.f; }
+                                    if (i == 0) { sv[2 * t] = f.x; sv[2 * t + 1] = f.y; sq[2 * t] = __fmul_rn(f.x, f.x); sq[2 * t + 1] = __fmul_rn(f.y, f.y); }
+                                    else { sv[2 * t] = __fadd_rn(sv[2 * t], f.x); sv[2 * t + 1] = __fadd_rn(sv[2 * t + 1], f.y);
+                                           sq[2 * t] = __fadd_rn(sq[2 * t], __fmul_rn(f.x, f.x)); sq[2 * t + 1] = __fadd_rn(sq[2 * t + 1], __fmul_rn(f.y, f.y)); }
+                                }
+                            }
+                        }
+                        if (STATS) {
+                            fx_add(s_hi[jc], s_lo[jc], bad, x_butterfly(sv, sx, sp4, sp2, sp1));
+                            fx_add(q_hi[jc], q_lo[jc], bad, x_butterfly(sq, sx, sp4, sp2, sp1));
                         }
                     }
-                    KP(e_store += clock64() - ew3;)
                 } else {
                     tmem_st_wait();
                     tc_fence_before();
@@ -442,8 +559,8 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
             }
         }
         if (stats && !dead) {
-            if (n_cur >= 0) { flush(n_cur, true); n_next = n_cur + 1; }
-            for (; n_next < a.N; n_next++) flush(n_next, false);
+            if (n_cur >= 0) flush(n_cur, true);
+            for (int n = 0; n < a.N; n++) if (n_cur < 0 || n < n_first || n > n_cur) flush(n, false);
             /* the last block of this column tile to get here turns the partial sums into coefficients; the order of the additions is
                fixed (block 0, 1, ...), so the result does not depend on which block came last */
             volatile unsigned &last = *(volatile unsigned *)(smem_raw + 776);
@@ -456,9 +573,16 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                 for (int i = et; i < a.N * a.nt; i += 128) {
                     const int n = i / a.nt, c = ctile * a.nt + i % a.nt;
                     if (c >= a.e.co_real) continue;
-                    double s0 = 0.0, q0 = 0.0;
-                    const double *pp = a.part + ((size_t)n * a.gcol * a.cop + c) * 2;
-                    for (int t = 0; t < a.gcol; t++) { s0 += __ldcg(pp + (size_t)t * a.cop * 2); q0 += __ldcg(pp + (size_t)t * a.cop * 2 + 1); }
+                    long long sh = 0, qh = 0; unsigned long long sl = 0ull, ql = 0ull; bool nf = false;
+                    const unsigned long long *pp = (const unsigned long long *)a.part + ((size_t)n * a.gcol * a.cop + c) * 4;
+                    for (int t = 0; t < a.gcol; t++) {
+                        const unsigned long long *r4 = pp + (size_t)t * a.cop * 4;
+                        const unsigned long long w0 = __ldcg(r4), w1 = __ldcg(r4 + 1), w2 = __ldcg(r4 + 2), w3 = __ldcg(r4 + 3);
+                        nf = nf || w0 == 0x7fffffffffffffffull;
+                        fx_add128(sh, sl, (long long)w0, w1); fx_add128(qh, ql, (long long)w2, w3);
+                    }
+                    const double nan_ = __longlong_as_double(0x7ff8000000000000ll);
+                    const double s0 = nf ? nan_ : (double)sh + (double)sl * 5.42101086242752217e-20, q0 = nf ? nan_ : (double)qh + (double)ql * 5.42101086242752217e-20;
                     const double m = s0 / (double)S, v = fmax(q0 / (double)S - m * m, 0.0);
                     const float rs = (float)(1.0 / sqrt(v + (double)a.eps)), ca = __fmul_rn(rs, a.gamma ? a.gamma[c] : 1.f);
                     a.coef[2 * ((size_t)n * a.e.co_real + c)] = ca;
@@ -466,7 +590,6 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                 }
             }
         }
-        KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; a.prof[(size_t)blockIdx.x * 32 + 9] = e_ld; a.prof[(size_t)blockIdx.x * 32 + 10] = e_zero; a.prof[(size_t)blockIdx.x * 32 + 11] = e_store; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -616,11 +739,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     int dev = 0, sms = 148; cudaGetDevice(&dev);
     { static int sms_of[16]; if (!sms_of[dev & 15]) { int v = 148; cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); sms_of[dev & 15] = v; } sms = sms_of[dev & 15]; }   /* looked up once per device */
     /* two blocks a multiprocessor when shared memory (113 KB each) and TMEM (256 columns each) allow */
-    int two = g.tmem_cols == 256 && a.off_ring + 4 * a.stage_bytes <= 113 * 1024;
-#ifdef UMX_KPROF
-    a.dbg = getenv("UMX_DBG") ? atoi(getenv("UMX_DBG")) : 0;
-    if (a.dbg & 4) two = 0;
-#endif
+    const int two = g.tmem_cols == 256 && a.off_ring + 4 * a.stage_bytes <= 113 * 1024;
     const int room = (two ? 113 : 227) * 1024 - a.off_ring;
     a.ring = room / a.stage_bytes; if (a.ring > 12) a.ring = 12;
     if (a.ring < 3) return 1;
@@ -629,7 +748,7 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     if (g_r_block_cap && slots > g_r_block_cap) slots = g_r_block_cap;
     /* A block pays two halo planes per run: with fewer than eight planes a block (counted for one sample, so that the choice of kernel does not
        depend on the batch) the general kernel is faster.  Volumes with fewer planes than blocks are left here: nothing to gain either way. */
-    { const long long units1 = (long long)a.tiles * D; if (units1 >= slots && units1 < 8 * slots) return 1; }
+    { const long long units1 = (long long)a.tiles * D; if (g.ncol > 1 && units1 >= slots && units1 < 8 * slots) return 1; }
     a.gcol = (int)(a.units < slots ? a.units : slots); if (a.gcol > 512) a.gcol = 512;
     const int grid = a.gcol * g.ncol;
     const size_t S = (size_t)D * H * W;
@@ -655,9 +774,6 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
         }
         attr_set[dev & 15] = 1;
     }
-#ifdef UMX_KPROF
-    a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
-#endif
     const int variant = (coef ? 4 : 0) | (c->bits == 8 ? 0 : 2) | (g.nt == 32 ? 0 : 1);
     switch (variant) {
     case 0: umx_launch(conv_mxr_k<8, 1, false>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
@@ -669,13 +785,5 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
     case 6: umx_launch(conv_mxr_k<4, 1, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
     default: umx_launch(conv_mxr_k<4, 2, true>, dim3(grid), dim3(kThreadsR), smem, *m0, ms, a); break;
     }
-#ifdef UMX_KPROF
-    { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
-      double t[15] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 15; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
-      long long mx = 0; for (int b = 0; b < grid; b++) if (hb[b * 32 + 29] > mx) mx = hb[b * 32 + 29];
-      { double x[4] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 4; k++) x[k] += (double)hb[b * 32 + 8 + k] / grid; fprintf(stderr, "kprof+: producer record %.0f | epilogue ld %.0f zero %.0f store %.0f\n", x[0], x[1], x[2], x[3]); }
-      fprintf(stderr, "kprof: grid %d units %lld ring %d slots %d tmem %d nki %d nt %d smem %zu | per block: stages %.0f planes %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f | prologue %.0f block %.0f = %.0f ns (max block %lld clk)\n",
-              grid, a.units, a.ring, a.nslot, a.tmem_cols, a.nki, a.nt, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7], t[12], t[13], t[14], mx); }
-#endif
     return 0;
 }

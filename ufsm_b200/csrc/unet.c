@@ -128,10 +128,10 @@ long umx_unet_launches(const umx_unet *u) { return umx_launch_count() - u->launc
 
 /* conv -> blocked fp16 + partial sums -> coefficients -> apply into q (and q_s2d) */
 static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int N, int C, int D, void *q, int bits, int nb_dst, int b0, void *q_s2d) {
-    /* UMX_FAST_STATS=1 in the environment: InstanceNorm sums in the conv's epilogue (see umx_conv_fwd_norm); off by default */
-    static int fast = -1;
-    if (fast < 0) { const char *e = getenv("UMX_FAST_STATS"); fast = e && *e == '1'; }
-    umx_conv_fwd_norm(c, x, N, D, D, D, u->ybuf, u->part, nullptr, nullptr, 1e-5f, u->coef, UMX_X_SPLIT | (fast ? UMX_FAST_STATS : 0));
+    /* UMX_STATS_EPILOGUE=1 in the environment: InstanceNorm sums in the conv's epilogue (see umx_conv_fwd_norm); off by default */
+    static int epi = -1;
+    if (epi < 0) { const char *e = getenv("UMX_STATS_EPILOGUE"); epi = e && *e == '1'; }
+    umx_conv_fwd_norm(c, x, N, D, D, D, u->ybuf, u->part, nullptr, nullptr, 1e-5f, u->coef, UMX_X_SPLIT | (epi ? UMX_STATS_EPILOGUE : 0));
     umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr, UMX_LAYOUT_SPLIT);
 }
 static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) {

@@ -100,13 +100,13 @@ class Conv:
             out = from_split(out, N, nbo * 32, So, out_bits)
         return out, (pd if want_part else None)
 
-    def fwd_norm(self, x_mx, N, D, H, W, eps=1e-5, fast=False):
+    def fwd_norm(self, x_mx, N, D, H, W, eps=1e-5, epilogue_stats=False):
         """conv -> blocked fp16 + InstanceNorm coefficients in one call; returns (fp16 blocked values, coef [N * co * 2])"""
         xd = DevBuf(data=to_split(x_mx, N, nb32(self.ci) * 32, D * H * W, self.bits))
         yd = DevBuf(N * nb32(self.co) * D * H * W * 64).fill(0xEE)
         pd = DevBuf(L().umx_stats_doubles(N, self.co, D, H, W) * 8).fill(0xEE)
         cd = DevBuf(N * self.co * 8).fill(0xEE)
-        rc = L().umx_conv_fwd_norm(self.h, xd.ptr, N, D, H, W, yd.ptr, pd.ptr, None, None, C.c_float(eps), cd.ptr, 3 | (4 if fast else 0))
+        rc = L().umx_conv_fwd_norm(self.h, xd.ptr, N, D, H, W, yd.ptr, pd.ptr, None, None, C.c_float(eps), cd.ptr, 3 | (4 if epilogue_stats else 0))
         _check()
         assert rc == 0
         return yd.download(np.float16), cd.download(np.float32)
