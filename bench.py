@@ -210,6 +210,72 @@ def run_ops(args):
     print("%-22s %d ch on %d^3 fp16 -> MX-fp%d: %.1f us, %.0f GB/s" % ("lp_h16_to_mx", Cn, D, bits, us, gbs))
 
 
+def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
+    from ufsm_b200 import synth
+    w = L.umx_window_make(Vw, P, 16)
+    plan = L.umx_wplan_create(C.byref(w), rank, world, NH)
+    f, cnt, lo, hi = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    L.umx_wplan_info(plan, C.byref(f), C.byref(cnt), C.byref(lo), C.byref(hi))
+    zext = hi.value - lo.value
+    slab = synth.sheet_slab(500, Vw, lo.value, hi.value)                    # this rank's planes of the volume only
+    vol_ptr = slab.ctypes.data - lo.value * Vw * Vw                           # addressed with volume coordinates; only [lo, hi) is read
+    out_bytes = NH * zext * Vw * Vw
+    out_host = L.nn_malloc_host(out_bytes)
+    sends, recvs = [], []
+    if world > 1:
+        import torch
+        torch.cuda.set_device(local)
+        nccl = dist.new_group(backend="nccl")
+        rb = L.umx_wplan_row_bytes(plan) // 8
+        for peer in range(world):
+            ns, nr = L.umx_wplan_rows(plan, peer, 0, None), L.umx_wplan_rows(plan, peer, 1, None)
+            if ns:
+                sends.append((peer, torch.empty(ns * rb, dtype=torch.int64, device="cuda")))
+            if nr:
+                recvs.append((peer, torch.empty(nr * rb, dtype=torch.int64, device="cuda")))
+        warm = torch.zeros(1, device="cuda")
+        dist.all_reduce(warm, group=nccl)                                        # communicator set-up outside the timed region
+        torch.cuda.synchronize()
+    barrier()
+    L.umx_timer_start(timer)
+    rc = L.umx_window_run_fx(u.h, plan, vol_ptr, B, 100, out_host)
+    assert rc == 0, (L.lp_check() or b"").decode()
+    if world > 1:
+        import torch
+        for peer, t in sends:
+            assert L.umx_wplan_pack(plan, peer, t.data_ptr()) == 0
+        ops = [dist.P2POp(dist.isend, t, peer, group=nccl) for peer, t in sends] + [dist.P2POp(dist.irecv, t, peer, group=nccl) for peer, t in recvs]
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+            torch.cuda.synchronize()
+        for peer, t in recvs:
+            assert L.umx_wplan_add(plan, peer, t.data_ptr()) == 0
+    assert L.umx_wplan_finish(plan, out_host) == 0, (L.lp_check() or b"").decode()
+    ms = tmax(L.umx_timer_stop_ms(timer))
+    # a checksum of the rows this rank delivered, so that runs at different rank counts can be compared (the volume is the same bytes)
+    mode = np.zeros((zext, Vw), np.uint8)
+    L.umx_wplan_mode(plan, mode.ctypes.data)
+    out = np.ctypeslib.as_array((C.c_uint8 * out_bytes).from_address(out_host)).reshape(NH, zext, Vw, Vw)
+    mine = (mode == 1) | (mode == 2)
+    csum = int(out[:, mine, :].astype(np.uint64).sum())
+    nshared = int(sum(t.numel() for _, t in sends) * 8)
+    counts = [cnt.value]
+    if dist is not None:
+        import torch
+        t = torch.tensor([csum, cnt.value, nshared], dtype=torch.int64)
+        g = [torch.zeros(3, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(g, t)
+        csum, counts, nshared = int(sum(int(x[0]) for x in g)), [int(x[1]) for x in g], int(sum(int(x[2]) for x in g))
+    L.umx_wplan_free(plan)
+    L.nn_free_host(out_host)
+    dt = ms * 1e-3
+    return {"workload": "config 5: %d^3 uint8 sheet volume, 128^3 patches, overlap 16 (stride 112), %d patches, Gaussian blend, (z, y) patch rows dealt by z-slab over %d GPU(s)" % (Vw, w.npatch, world),
+            "scaling": "strong", "seconds": dt, "value": Vw ** 3 / dt, "unit": "volume voxels/s", "patches_per_s": w.npatch / dt, "patches_per_rank": counts,
+            "output": "uint8 round(254 sigmoid(blended logit)), %d head channels, %d bytes to the host in all" % (NH, NH * Vw ** 3), "bytes_exchanged_between_ranks": nshared,
+            "volume_checksum": csum, "timing": "CUDA events on the launching stream around the whole run of a rank (forwards, blend, emit, copies to pinned host memory, exchange), max over ranks"}
+
+
 def cpu_sample(steps, warmup):
     """The oracle's forward of the same network on one full 128^3 patch, all host threads."""
     # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1; the oracle's OpenMP runtime reads it when loaded)
@@ -341,29 +407,14 @@ def run_gpu(args):
         L.umx_unet_forward(u4.h, xd.ptr, B, yd.ptr)
     ms_fp4 = tmax(L.umx_timer_stop_ms(timer))
     u4.free()
-    # ---- optional: configuration 5's sliding window over a synthetic V^3 uint8 volume (128^3 patches, overlap 16, Gaussian blend on the
-    # device), the patch rows dealt to the ranks by z-slab; wall clock around umx_window_run including the host-side patch gather, the
-    # uploads and the download of this rank's blended planes
+    # ---- configuration 5: the sliding window over a synthetic V^3 uint8 sheet volume (128^3 patches, overlap 16, Gaussian blend), STRONG scaling:
+    # the (z, y) patch rows are dealt to the ranks by z-slab, every rank forwards and blends its share on its GPU (exact 64-bit sums), rows of the
+    # volume that two ranks touch are handed to the lower rank over NCCL send / receive (the one exchange step of this path), and the finished
+    # uint8 volume (round(254 sigmoid(logit)), the reference's predict output) lands in pinned host memory.  Timed with events on the launching
+    # stream from the first patch to the last byte on the host, max over ranks.
     win = None
     if args.window:
-        Vw = args.window
-        vol = synth.ct_u8(500, Vw ** 3)
-        w = L.umx_window_make(Vw, P, 16)
-        f, cnt, lo, hi = C.c_int(), C.c_int(), C.c_int(), C.c_int()
-        L.umx_window_share(C.byref(w), rank, world, C.byref(f), C.byref(cnt))
-        L.umx_window_extent(C.byref(w), f.value, cnt.value, C.byref(lo), C.byref(hi))
-        zext = max(hi.value - lo.value, 1)
-        acc_p, wsum_p = L.nn_malloc_host(NH * zext * Vw * Vw * 4), L.nn_malloc_host(zext * Vw * Vw * 4)      # pinned result buffers
-        barrier()
-        t0 = time.time()
-        rc = L.umx_window_run(u.h, C.byref(w), vol.ctypes.data, f.value, cnt.value, B, acc_p, wsum_p)
-        assert rc == 0, (L.lp_check() or b"").decode()
-        dt = tmax(time.time() - t0)
-        win = {"workload": "config 5: %d^3 uint8 volume, 128^3 patches, overlap 16, %d patches, z-slab shares over %d GPU(s)" % (Vw, w.npatch, world),
-               "seconds": dt, "value": Vw ** 3 / dt, "unit": "volume voxels/s", "patches_per_s": w.npatch / dt}
-        L.nn_free_host(acc_p)
-        L.nn_free_host(wsum_p)
-        del vol
+        win = run_window(L, u, rank, world, local, dist, args.window, B, timer, tmax, barrier)
     # ---- single layers of configurations 1 and 2 and the quantiser (rank 0 reports them; parity of these shapes is in the tests)
     extra = None
     if rank == 0:
@@ -432,7 +483,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="ufsm_b200")
     ap.add_argument("--clock-interval", type=float, default=0.05, help="seconds between clock samples (NVML queries share a lock with kernel launches, so not too often)")
-    ap.add_argument("--window", type=int, default=0, help="also run the sliding window over a synthetic V^3 volume (configuration 5 uses 1024)")
+    ap.add_argument("--window", type=int, default=1024, help="edge of the synthetic volume of the sliding-window run (configuration 5: 1024); 0 skips it")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--layer", default="", help="time one conv layer alone: kind,ci,co,size[,bits[,out]] with kind conv3 | conv1 | down2 | tconv2 | conv3s2, out h16b | mx | pm32")
     ap.add_argument("--ops", default="", help="time the elementwise MX operators and the quantiser: c,size[,bits]")

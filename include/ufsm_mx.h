@@ -201,21 +201,43 @@ double umx_unet_flops(const umx_unet_cfg *cfg);                  /* 2 V_out C_in
 long umx_unet_launches(const umx_unet *u);                       /* kernels launched by the library since this object was created */
 long umx_launch_count(void);                                     /* kernels launched by the library in this process */
 void umx_u8_to_h16(const uint8_t *x_dev, size_t n, void *y_dev); /* CT bytes -> fp16 x / 255 */
-/* acc[c][z - zlo][y][x] += w logits[c][patch voxel], wsum += w with the separable Gaussian window w1d (device, P floats) for the
-   patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend, src/nn_ink3dext.cu:58-73) */
+/* the reference's blend arithmetic, kept as an operator of its own: acc[c][z - zlo][y][x] = fma(w, logits[c][patch voxel], acc), wsum += w with
+   the separable Gaussian window w1d (device, P floats) for the patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend,
+   src/nn_ink3dext.cu:58-73); fp32 sums, so the result depends on the order of the calls */
 void umx_blend_add(const void *logits_dev, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d_dev, float *acc_dev, float *wsum_dev);
 
-/* Sliding window over a V^3 uint8 volume (host): P^3 patches at stride P - overlap, Gaussian window sigma P / 8, patch layers
-   dealt to ranks by contiguous z-slabs of (z, y) patch rows (src/predict.c:2696-2717; blend src/nn_ink3dext.cu:58-73).  This rank
-   runs patches [first, first + count) in (z, y, x) order, blends them on the device, and returns weight * logits and weight for the
-   z planes [zlo, zhi) its patches touch (umx_window_extent): host arrays acc [nh][zhi - zlo][V][V] and wsum [zhi - zlo][V][V].  The
-   caller adds the planes that two ranks share and divides. */
+/* Sliding window over a V^3 uint8 volume (host): P^3 patches at stride P - overlap, Gaussian window sigma P / 8 about the integer centre
+   P / 2, the (z, y) rows of the patch grid dealt to ranks in contiguous shares, z-slab first (src/predict.c:2696-2717; blend and emit
+   src/nn_ink3dext.cu:48-73, 77-100).  A rank forwards its patches and blends them on its device into 64-bit fixed-point sums (a term is
+   the exact product of the fp32 window weight and the fp32 logit rounded to a multiple of 2^-46; integer sums: the result does not
+   depend on the order, the batch or the partition, which the reference's fp32 atomics cannot promise).  Rows (z, y) of the volume that
+   only this rank's patches touch are normalised and converted on the device and copied to the host while later patches run; a row
+   that several ranks touch belongs to the lowest of them: the others hand over their partial sums of it (umx_wplan_pack ->
+   transport of the caller's choice -> umx_wplan_add), and umx_wplan_finish emits those rows.  What reaches the host is the finished
+   volume: out [nh][zhi - zlo][V][V] of fp16 blended logits (UMX_F16) or of uint8 round(254 sigmoid(logit)), 255 where no patch covers
+   a voxel (UMX_U8OUT; k_i3_emit).  With one rank nothing is shared and umx_window_run_fx alone delivers the whole volume. */
+enum { UMX_U8OUT = 100 };
 typedef struct { int V, P, overlap, nper, npatch; } umx_window;
 umx_window umx_window_make(int V, int P, int overlap);
-void umx_window_share(const umx_window *w, int rank, int world, int *first, int *count);
-void umx_window_origin(const umx_window *w, int idx, int *z0, int *y0, int *x0);
+void umx_window_share(const umx_window *w, int rank, int world, int *first, int *count);      /* this rank's patches [first, first + count) in (z, y, x) order */
+void umx_window_origin(const umx_window *w, int idx, int *z0, int *y0, int *x0);             /* the last patch of an axis is pulled back so that it ends at the volume's edge */
 void umx_window_extent(const umx_window *w, int first, int count, int *zlo, int *zhi);
-int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol_host, int first, int count, int batch, float *acc, float *wsum);
+typedef struct umx_wplan umx_wplan;
+umx_wplan *umx_wplan_create(const umx_window *w, int rank, int world, int nh);               /* host only: shares, ownership of the rows, exchange lists (at most 64 ranks) */
+void umx_wplan_free(umx_wplan *p);
+void umx_wplan_info(const umx_wplan *p, int *first, int *count, int *zlo, int *zhi);
+long umx_wplan_rows(const umx_wplan *p, int peer, int dir, int *zy);                        /* rows handed to (dir 0) / received from (dir 1) `peer`; zy: optional, 2 ints a row (z, y), ascending */
+void umx_wplan_mode(const umx_wplan *p, uint8_t *mode);                                     /* mode [zhi - zlo][V]: 0 not this rank's patches, 1 this rank's alone (umx_window_run_fx delivers it), 2 this rank's, shared (umx_wplan_finish), 3 a lower rank's */
+size_t umx_wplan_row_bytes(const umx_wplan *p);                                             /* bytes of one exchanged row: (nh + 1) x V 64-bit sums */
+int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol_host, int batch, int out_fmt, void *out_host);
+int umx_wplan_pack(umx_wplan *p, int peer, void *buf_dev);
+int umx_wplan_add(umx_wplan *p, int peer, const void *buf_dev);
+int umx_wplan_finish(umx_wplan *p, void *out_host);
+/* the device operators underneath (acc [nh][zext][V][V], wsum [zext][V][V] 64-bit sums of an extent of zext planes from plane zlo) */
+void umx_blend_add_fx(const float *logits_dev, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d_dev, long long *acc_dev, long long *wsum_dev);
+void umx_emit_fx(const long long *acc_dev, const long long *wsum_dev, const uint8_t *mode_dev, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out_dev);
+void umx_emit_rows_fx(const long long *acc_dev, const long long *wsum_dev, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out_dev);
+void umx_rows_fx(long long *acc_dev, long long *wsum_dev, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf_dev);
 
 #ifdef __cplusplus
 }

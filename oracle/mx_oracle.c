@@ -564,3 +564,31 @@ void orc_blend_add(const float *logits, int nh, int P, int V, int z0, int y0, in
         wsum[gv] += w;
     }
 }
+
+/* The library's exact blend (its answer to the run-to-run changing fp32 atomics of k_i3_blend, src/nn_ink3dext.cu:58-73): a term is the
+   exact product of the reference's fp32 window weight w1d[z] w1d[y] w1d[x] and the fp32 logit, rounded once to a multiple of 2^-46 and
+   added as a 64-bit integer.  acc [nh][V^3], wsum [V^3]. */
+void orc_blend_add_fx(const float *logits, int nh, int P, int V, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum) {
+    const size_t VS = (size_t)V * V * V, PS = (size_t)P * P * P;
+#pragma omp parallel for
+    for (int z = 0; z < P; z++) for (int y = 0; y < P; y++) for (int x = 0; x < P; x++) {
+        const int gz = z0 + z, gy = y0 + y, gx = x0 + x;
+        if (gz >= V || gy >= V || gx >= V) continue;
+        const float w3 = (w1d[z] * w1d[y]) * w1d[x];
+        const double w = (double)w3 * 70368744177664.0;
+        const size_t gv = ((size_t)gz * V + gy) * V + gx, pv = ((size_t)z * P + y) * P + x;
+        for (int c = 0; c < nh; c++) { const double t = w * (double)logits[(size_t)c * PS + pv]; acc[(size_t)c * VS + gv] += fabs(t) < 9.0e18 ? llrint(t) : 0; }
+        wsum[gv] += llrint(w);
+    }
+}
+/* the blended volume: l = (float)(sum / weight); fmt 2: fp16 logits; otherwise uint8 round(254 p), p = 1 / (1 + exp(-l)), 255 where nothing covers
+   the voxel (k_i3_emit, src/nn_ink3dext.cu:77-100) */
+void orc_emit_fx(const long long *acc, const long long *wsum, int nh, size_t nvox, int fmt, void *out) {
+#pragma omp parallel for
+    for (size_t v = 0; v < nvox; v++) for (int c = 0; c < nh; c++) {
+        const size_t o = (size_t)c * nvox + v; const long long ws = wsum[v];
+        const float l = ws > 0 ? (float)((double)acc[o] / (double)ws) : 0.f;
+        if (fmt == 2) ((h16 *)out)[o] = (h16)l;
+        else ((uint8_t *)out)[o] = ws > 0 ? (uint8_t)lrintf((1.f / (1.f + expf(-l))) * 254.f) : 255;
+    }
+}

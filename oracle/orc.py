@@ -222,6 +222,24 @@ def _unet_forward(cfg, weights, x16, N):
     return logits
 
 
+def gauss_window(P):
+    w = np.zeros(P, np.float32)
+    o().orc_gauss_window(P, _p(w))
+    return w
+
+
+def blend_add_fx(logits, nh, P, V, z0, y0, x0, w1d, acc, wsum):
+    """acc [nh][V^3] int64, wsum [V^3] int64, updated in place"""
+    o().orc_blend_add_fx(_p(f32(logits)), nh, P, V, z0, y0, x0, _p(w1d), _p(acc), _p(wsum))
+
+
+def emit_fx(acc, wsum, nh, fmt):
+    """fmt 2: fp16 blended logits, else uint8"""
+    out = np.zeros(acc.size, np.float16 if fmt == 2 else np.uint8)
+    o().orc_emit_fx(_p(acc), _p(wsum), nh, C.c_size_t(wsum.size), fmt, _p(out))
+    return out
+
+
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

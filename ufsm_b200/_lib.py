@@ -114,7 +114,20 @@ _SIG = {
     "umx_window_share": (None, [C.POINTER(Window), C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "umx_window_origin": (None, [C.POINTER(Window), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "umx_window_extent": (None, [C.POINTER(Window), C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
-    "umx_window_run": (C.c_int, [C.c_void_p, C.POINTER(Window), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "umx_wplan_create": (C.c_void_p, [C.POINTER(Window), C.c_int, C.c_int, C.c_int]),
+    "umx_wplan_free": (None, [C.c_void_p]),
+    "umx_wplan_info": (None, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "umx_wplan_rows": (C.c_long, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "umx_wplan_mode": (None, [C.c_void_p, C.c_void_p]),
+    "umx_wplan_row_bytes": (C.c_size_t, [C.c_void_p]),
+    "umx_window_run_fx": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "umx_wplan_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_wplan_add": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_wplan_finish": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "umx_blend_add_fx": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "umx_emit_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "umx_emit_rows_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "umx_rows_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
 }
 SYMBOLS = tuple(_SIG)
 _lib = None

@@ -15,6 +15,10 @@
 #include <string.h>
 
 void umx_u8_to_h16(const uint8_t *x, size_t n, void *y);
+void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum);
+void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out);
+void umx_emit_rows_fx(const long long *acc, const long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out);
+void umx_rows_fx(long long *acc, long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf);
 void umx_blend_add(const void *logits, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, float *acc, float *wsum);
 long umx_launch_count(void);
 
@@ -241,33 +245,146 @@ void umx_window_extent(const umx_window *w, int first, int count, int *zlo, int 
     umx_window_origin(w, first, &z0, &y0, &x0); umx_window_origin(w, first + count - 1, &z1, &y0, &x0);
     *zlo = z0; *zhi = (z1 + w->P < w->V ? z1 + w->P : w->V);
 }
-/* Runs patches [first, first + count): gathers each batch of uint8 patches from the host volume into pinned staging, uploads,
-   forwards, blends on the device into accumulators covering z planes [zlo, zhi) of the volume, and finally copies the
-   accumulators to acc [nh][zhi - zlo][V][V] and wsum [zhi - zlo][V][V] on the host. */
-int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int first, int count, int batch, float *acc, float *wsum) {
-    const int P = w->P, V = w->V, nh = u->cfg.nh;
-    if (P != u->cfg.P) { fprintf(stderr, "umx_window_run: patch size %d does not match the network's %d\n", P, u->cfg.P); abort(); }
+/* ---------------- the sliding window with exact blending and a share per rank ----------------
+   A rank forwards its contiguous share of the (z, y) patch rows and blends the logits into 64-bit fixed-point accumulators on its device
+   (umx_blend_add_fx: integer sums, so the result does not depend on the order, the batch or the partition).  A row (z, y) of the volume
+   that only this rank's patches touch is final as soon as the rank's patch layer moves on: it is normalised and converted on the device
+   and copied to the host while the next patches are forwarded.  A row that several ranks touch belongs to the lowest of them: the
+   others hand their partial sums of it over (umx_wplan_pack on their side, umx_wplan_add on the owner's, the transport between the two
+   devices is the caller's: a peer copy, a send / receive, or host memory), and umx_wplan_finish emits those rows last.  What crosses to
+   the host is the finished volume, 1 or 2 bytes per voxel and head channel. */
+enum { WP_MAXPEER = 64 };
+typedef struct umx_wplan umx_wplan;
+struct umx_wplan {
+    umx_window w; int rank, world, first, count, zlo, zhi, nh;
+    uint8_t *mode;                    /* host [zext][V]: 0 not touched by this rank, 1 this rank's alone, 2 this rank's, shared with higher ranks, 3 a lower rank's */
+    long nsend[WP_MAXPEER], nrecv[WP_MAXPEER], nmine2; int *send_zy[WP_MAXPEER], *recv_zy[WP_MAXPEER], *mine2_zy;   /* (z - zlo, y) pairs in ascending order */
+    long long *acc, *wsum; uint8_t *mode_dev; void *out_dev; int out_fmt; float *w1d; int *zy_dev; long zy_cap;
+    void *ev_emit;
+};
+static void wp_rows_of_rank(const umx_window *w, int rank, int world, int *first, int *count) { umx_window_share(w, rank, world, first, count); }
+umx_wplan *umx_wplan_create(const umx_window *w, int rank, int world, int nh) {
+    if (world < 1 || world > WP_MAXPEER || rank < 0 || rank >= world || nh < 1) { fprintf(stderr, "umx_wplan_create: rank %d of %d (at most %d ranks)\n", rank, world, WP_MAXPEER); abort(); }
+    umx_wplan *p = calloc(1, sizeof *p);
+    p->w = *w; p->rank = rank; p->world = world; p->nh = nh;
+    wp_rows_of_rank(w, rank, world, &p->first, &p->count);
+    umx_window_extent(w, p->first, p->count, &p->zlo, &p->zhi);
+    const int V = w->V, P = w->P, zext = p->zhi - p->zlo;
+    if (zext <= 0) return p;
+    /* which ranks touch a row (z, y) of this rank's extent: one bit a rank */
+    uint64_t *mask = calloc((size_t)zext * V, sizeof *mask);
+    for (int r = 0; r < world; r++) {
+        int f, c; wp_rows_of_rank(w, r, world, &f, &c);
+        for (int row = f / w->nper; row < (f + c) / w->nper; row++) {
+            int z0, y0, x0; umx_window_origin(w, row * w->nper, &z0, &y0, &x0);
+            const int za = z0 > p->zlo ? z0 : p->zlo, zb = (z0 + P < p->zhi ? z0 + P : p->zhi), yb = y0 + P < V ? y0 + P : V;
+            for (int z = za; z < zb; z++) for (int y = y0; y < yb; y++) mask[(size_t)(z - p->zlo) * V + y] |= (uint64_t)1 << r;
+        }
+    }
+    p->mode = malloc((size_t)zext * V);
+    const uint64_t me = (uint64_t)1 << rank;
+    for (int pass = 0; pass < 2; pass++) {       /* count, then fill */
+        long ns[WP_MAXPEER] = {0}, nr[WP_MAXPEER] = {0}, n2 = 0;
+        for (size_t i = 0; i < (size_t)zext * V; i++) {
+            const uint64_t m = mask[i]; const int z = (int)(i / V), y = (int)(i % V);
+            if (!(m & me)) { p->mode[i] = 0; continue; }
+            const int owner = __builtin_ctzll(m);
+            if (owner == rank) {
+                p->mode[i] = m == me ? 1 : 2;
+                if (m != me) {
+                    if (pass) { p->mine2_zy[2 * n2] = z; p->mine2_zy[2 * n2 + 1] = y; }
+                    n2++;
+                    for (int r = rank + 1; r < world; r++) if (m >> r & 1) { if (pass) { p->recv_zy[r][2 * nr[r]] = z; p->recv_zy[r][2 * nr[r] + 1] = y; } nr[r]++; }
+                }
+            } else {
+                p->mode[i] = 3;
+                if (pass) { p->send_zy[owner][2 * ns[owner]] = z; p->send_zy[owner][2 * ns[owner] + 1] = y; }
+                ns[owner]++;
+            }
+        }
+        if (!pass) {
+            p->nmine2 = n2; p->mine2_zy = malloc((size_t)(n2 ? n2 : 1) * 2 * sizeof(int));
+            for (int r = 0; r < world; r++) {
+                p->nsend[r] = ns[r]; p->nrecv[r] = nr[r];
+                p->send_zy[r] = ns[r] ? malloc((size_t)ns[r] * 2 * sizeof(int)) : nullptr; p->recv_zy[r] = nr[r] ? malloc((size_t)nr[r] * 2 * sizeof(int)) : nullptr;
+            }
+        }
+    }
+    free(mask);
+    return p;
+}
+void umx_wplan_free(umx_wplan *p) {
+    if (!p) return;
+    for (int r = 0; r < WP_MAXPEER; r++) { free(p->send_zy[r]); free(p->recv_zy[r]); }
+    free(p->mine2_zy); free(p->mode);
+    nn_free(p->acc); nn_free(p->wsum); nn_free(p->mode_dev); nn_free(p->out_dev); nn_free(p->w1d); nn_free(p->zy_dev); umx_event_free(p->ev_emit);
+    free(p);
+}
+void umx_wplan_info(const umx_wplan *p, int *first, int *count, int *zlo, int *zhi) { *first = p->first; *count = p->count; *zlo = p->zlo; *zhi = p->zhi; }
+/* rows this rank hands to `peer` (dir 0) or receives from it (dir 1); zy (optional, host): 2 ints a row, (z, y) in volume coordinates */
+long umx_wplan_rows(const umx_wplan *p, int peer, int dir, int *zy) {
+    if (peer < 0 || peer >= p->world) return 0;
+    const long n = dir ? p->nrecv[peer] : p->nsend[peer]; const int *src = dir ? p->recv_zy[peer] : p->send_zy[peer];
+    if (zy) for (long i = 0; i < n; i++) { zy[2 * i] = src[2 * i] + p->zlo; zy[2 * i + 1] = src[2 * i + 1]; }
+    return n;
+}
+/* who has each row (z, y) of this rank's extent, mode [zhi - zlo][V]: 0 no patch of this rank touches it, 1 this rank's alone (delivered by
+   umx_window_run_fx), 2 this rank's, shared with higher ranks (delivered by umx_wplan_finish), 3 a lower rank's (not delivered here) */
+void umx_wplan_mode(const umx_wplan *p, uint8_t *mode) { if (p->mode) memcpy(mode, p->mode, (size_t)(p->zhi - p->zlo) * p->w.V); }
+size_t umx_wplan_row_bytes(const umx_wplan *p) { return (size_t)(p->nh + 1) * p->w.V * sizeof(long long); }
+static int *wp_zy_to_dev(umx_wplan *p, const int *zy, long n) {
+    if (n > p->zy_cap) { nn_sync(); nn_free(p->zy_dev); p->zy_cap = n + n / 4 + 16; p->zy_dev = nn_malloc((size_t)p->zy_cap * 2 * sizeof(int)); if (!p->zy_dev) { p->zy_cap = 0; return nullptr; } }
+    nn_h2d(p->zy_dev, zy, (size_t)n * 2 * sizeof(int));
+    return p->zy_dev;
+}
+static int wp_alloc(umx_wplan *p, int out_fmt) {
+    const int V = p->w.V, P = p->w.P, zext = p->zhi - p->zlo; const size_t plane = (size_t)V * V;
+    if (!p->acc) {
+        p->acc = nn_malloc((size_t)p->nh * zext * plane * 8); p->wsum = nn_malloc((size_t)zext * plane * 8);
+        p->mode_dev = nn_malloc((size_t)zext * V); p->w1d = nn_malloc((size_t)P * 4); p->ev_emit = umx_event_new();
+        if (!p->acc || !p->wsum || !p->mode_dev || !p->w1d || !p->ev_emit) return -1;
+        float w1d_h[1024]; if (P > 1024) abort();
+        { const double s = P / 8.0, c = (double)(P / 2);   /* the reference's centre: the integer P / 2 (g1_init, src/nn_ink3dext.cu:48-56) */
+          for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
+        nn_h2d(p->w1d, w1d_h, (size_t)P * 4); nn_h2d(p->mode_dev, p->mode, (size_t)zext * V);
+    }
+    if (!p->out_dev || p->out_fmt != out_fmt) { nn_sync(); nn_free(p->out_dev); p->out_dev = nn_malloc((size_t)p->nh * zext * plane * (out_fmt == UMX_F16 ? 2 : 1)); p->out_fmt = out_fmt; if (!p->out_dev) return -1; }
+    nn_zero(p->acc, (size_t)p->nh * zext * plane * 8); nn_zero(p->wsum, (size_t)zext * plane * 8);
+    return nn_check() ? -1 : 0;
+}
+/* emit the rows that are this rank's alone in planes [za, zb) of the extent and queue their copy to out_host [nh][zext][V][V] on the copy stream */
+static void wp_emit_slab(umx_unet *u, umx_wplan *p, int za, int zb, void *out_host) {
+    if (zb <= za) return;
+    const int V = p->w.V, zext = p->zhi - p->zlo; const size_t plane = (size_t)V * V, el = p->out_fmt == UMX_F16 ? 2 : 1;
+    umx_emit_fx(p->acc, p->wsum, p->mode_dev, 1, p->nh, V, zext, za, zb, p->out_fmt, p->out_dev);
+    umx_event_record(p->ev_emit, nullptr);
+    umx_stream_wait(u->s_out, p->ev_emit);
+    for (int c = 0; c < p->nh; c++) {
+        const size_t o = ((size_t)c * zext + za) * plane * el;
+        umx_copy_async((uint8_t *)out_host + o, (uint8_t *)p->out_dev + o, (size_t)(zb - za) * plane * el, 0, u->s_out);
+    }
+}
+/* Forwards this rank's patches of the volume (vol_host: the V^3 uint8 volume; only the planes of the rank's extent are read), blends them,
+   and delivers the rows that are this rank's alone to out_host [nh][zhi - zlo][V][V] (pinned), out_fmt UMX_F16 (blended logits) or UMX_U8OUT
+   (round(254 sigmoid)).  Rows shared with other ranks are left to umx_wplan_pack / umx_wplan_add / umx_wplan_finish.  Returns 0, or -1 with
+   the message in lp_check(). */
+int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol, int batch, int out_fmt, void *out_host) {
+    const umx_window *w = &p->w; const int P = w->P, V = w->V, nh = u->cfg.nh;
+    if (P != u->cfg.P || nh != p->nh) { fprintf(stderr, "umx_window_run_fx: patch size %d / %d heads do not match the network's %d / %d\n", P, p->nh, u->cfg.P, nh); abort(); }
     if (batch < 1) batch = 1; if (batch > u->maxN) batch = u->maxN;
-    int zlo, zhi; umx_window_extent(w, first, count, &zlo, &zhi);
-    const int zext = zhi - zlo; if (zext <= 0) return 0;
+    const int zext = p->zhi - p->zlo; if (zext <= 0 || p->count <= 0) return 0;
     const size_t PS = cube(P), plane = (size_t)V * V;
-    float w1d_h[1024]; if (P > 1024) abort();
-    { const double s = P / 8.0, c = (double)(P / 2);   /* the reference's centre: the integer P / 2 (g1_init, src/nn_ink3dext.cu:48-56) */
-      for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
-    float *w1d = nn_malloc((size_t)P * 4), *dacc = nn_malloc((size_t)nh * zext * plane * 4), *dws = nn_malloc((size_t)zext * plane * 4);
+    if (wp_alloc(p, out_fmt) || pipe_init(u)) return -1;
     float *logits = nn_malloc((size_t)batch * nh * PS * 4);
-    /* two pinned staging buffers: the host gathers the next batch of patches from the volume while the GPU forwards the current one; the
-       upload runs on the copy stream and is ordered against the default stream with events (as in umx_unet_submit_host) */
     uint8_t *stage[2] = {nn_malloc_host((size_t)batch * PS), nn_malloc_host((size_t)batch * PS)};
-    if (!w1d || !dacc || !dws || !logits || !stage[0] || !stage[1] || pipe_init(u)) { nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]); return -1; }
-    nn_h2d(w1d, w1d_h, (size_t)P * 4); nn_zero(dacc, (size_t)nh * zext * plane * 4); nn_zero(dws, (size_t)zext * plane * 4);
+    if (!logits || !stage[0] || !stage[1]) { nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]); return -1; }
     nn_sync();
-    long j = 0;
-    for (int p = first; p < first + count; p += batch, j++) {
-        const int nb = p + batch <= first + count ? batch : first + count - p, k = (int)(j & 1);
+    long j = 0; int z_done = p->zlo, z_layer = -1;
+    for (int q = p->first; q < p->first + p->count; q += batch, j++) {
+        const int nb = q + batch <= p->first + p->count ? batch : p->first + p->count - q, k = (int)(j & 1);
         if (j >= 2) umx_event_sync(u->ev_up[k]);                 /* the staging buffer's upload of two batches ago has finished */
         for (int i = 0; i < nb; i++) {
-            int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
+            int z0, y0, x0; umx_window_origin(w, q + i, &z0, &y0, &x0);
             uint8_t *dst = stage[k] + (size_t)i * PS;
             for (int z = 0; z < P; z++) for (int y = 0; y < P; y++) {
                 const int gz = z0 + z, gy = y0 + y;
@@ -286,13 +403,47 @@ int umx_window_run(umx_unet *u, const umx_window *w, const uint8_t *vol, int fir
         umx_event_record(u->ev_used[k], nullptr);
         forward(u, u->x16, nb, logits, UMX_F32);
         for (int i = 0; i < nb; i++) {
-            int z0, y0, x0; umx_window_origin(w, p + i, &z0, &y0, &x0);
-            umx_blend_add(logits + (size_t)i * nh * PS, UMX_F32, nh, P, V, zlo, zext, z0, y0, x0, w1d, dacc, dws);
+            int z0, y0, x0; umx_window_origin(w, q + i, &z0, &y0, &x0);
+            if (z0 != z_layer) {      /* a new patch layer: the planes below it have their last contribution from this rank */
+                if (z_layer >= 0 && z0 > z_done) { wp_emit_slab(u, p, z_done - p->zlo, z0 - p->zlo, out_host); z_done = z0; }
+                z_layer = z0;
+            }
+            umx_blend_add_fx(logits + (size_t)i * nh * PS, nh, P, V, p->zlo, zext, z0, y0, x0, p->w1d, p->acc, p->wsum);
         }
     }
-    umx_stream_sync(u->s_in);
-    nn_d2h(acc, dacc, (size_t)nh * zext * plane * 4); nn_d2h(wsum, dws, (size_t)zext * plane * 4);
+    wp_emit_slab(u, p, z_done - p->zlo, zext, out_host);
+    umx_stream_sync(u->s_in); umx_stream_sync(u->s_out);
     nn_sync();
-    nn_free(w1d); nn_free(dacc); nn_free(dws); nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]);
+    nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]);
+    return nn_check() ? -1 : 0;
+}
+/* this rank's partial sums of the rows it hands to `peer`, compact, into buf_dev (device, umx_wplan_rows(p, peer, 0, NULL) x umx_wplan_row_bytes bytes) */
+int umx_wplan_pack(umx_wplan *p, int peer, void *buf_dev) {
+    const long n = p->nsend[peer]; if (n <= 0) return 0;
+    int *zy = wp_zy_to_dev(p, p->send_zy[peer], n); if (!zy) return -1;
+    umx_rows_fx(p->acc, p->wsum, zy, n, p->nh, p->w.V, p->zhi - p->zlo, 0, buf_dev);
+    nn_sync();
+    return nn_check() ? -1 : 0;
+}
+/* adds the partial sums that `peer` packed for this rank (buf_dev on this rank's device) */
+int umx_wplan_add(umx_wplan *p, int peer, const void *buf_dev) {
+    const long n = p->nrecv[peer]; if (n <= 0) return 0;
+    int *zy = wp_zy_to_dev(p, p->recv_zy[peer], n); if (!zy) return -1;
+    umx_rows_fx(p->acc, p->wsum, zy, n, p->nh, p->w.V, p->zhi - p->zlo, 1, (void *)buf_dev);
+    nn_sync();
+    return nn_check() ? -1 : 0;
+}
+/* after every umx_wplan_add: the rows this rank shares with higher ranks, into out_host */
+int umx_wplan_finish(umx_wplan *p, void *out_host) {
+    const long n = p->nmine2; if (n <= 0) return 0;
+    const int V = p->w.V, zext = p->zhi - p->zlo; const size_t el = p->out_fmt == UMX_F16 ? 2 : 1, plane = (size_t)V * V, rowb = (size_t)V * el;
+    int *zy = wp_zy_to_dev(p, p->mine2_zy, n); if (!zy) return -1;
+    void *cd = nn_malloc((size_t)n * p->nh * rowb); uint8_t *ch = nn_malloc_host((size_t)n * p->nh * rowb);
+    if (!cd || !ch) { nn_free(cd); nn_free_host(ch); return -1; }
+    umx_emit_rows_fx(p->acc, p->wsum, zy, n, p->nh, V, zext, p->out_fmt, cd);
+    nn_d2h(ch, cd, (size_t)n * p->nh * rowb);
+    for (long r = 0; r < n; r++) for (int c = 0; c < p->nh; c++)
+        memcpy((uint8_t *)out_host + (((size_t)c * zext + p->mine2_zy[2 * r]) * plane + (size_t)p->mine2_zy[2 * r + 1] * V) * el, ch + ((size_t)r * p->nh + c) * rowb, rowb);
+    nn_free(cd); nn_free_host(ch);
     return nn_check() ? -1 : 0;
 }

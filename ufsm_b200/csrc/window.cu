@@ -40,5 +40,101 @@ extern "C" void umx_blend_add(const void *logits, int fmt, int nh, int P, int V,
     g_umx_launches++;
     UMX_CK("umx_blend_add");
 }
+
+/* ---- exact blending.  The reference adds w x logit in fp32 with atomics, in whatever order the threads arrive (k_i3_blend), so its sums change
+   from run to run in the last bits.  Here a term is the exact product of the fp32 window weight and the fp32 logit, rounded once to a
+   multiple of 2^-46 and added as a 64-bit integer: integer sums do not depend on the order of the patches, on the batch they were
+   forwarded in or on which rank forwarded them, so the partial sums of two ranks add up to the single-rank sums bit for bit.
+   (|sum| < 2^17; a weight is at least exp(-24) = 2^-34.6, so even the volume's corner voxels keep 11 significant bits of weight.) ---- */
+#define UMX_FX_SCALE 70368744177664.0      /* 2^46 */
+__global__ void __launch_bounds__(256) blend_fx_k(const float *__restrict__ logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0,
+                                                   const float *__restrict__ w1d, long long *__restrict__ acc, long long *__restrict__ wsum) {
+    pdl_trigger(); pdl_wait();
+    const size_t PS = (size_t)P * P * P, plane = (size_t)V * V, AS = plane * zext;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < PS; i += (size_t)gridDim.x * blockDim.x) {
+        const int x = (int)(i % P), y = (int)((i / P) % P), z = (int)(i / ((size_t)P * P));
+        const int gz = z0 + z - zlo, gy = y0 + y, gx = x0 + x;
+        if (gz < 0 || gz >= zext || gy >= V || gx >= V) continue;
+        const double w = (double)__fmul_rn(__fmul_rn(w1d[z], w1d[y]), w1d[x]) * UMX_FX_SCALE;      /* the reference's fp32 weight, scaled */
+        const size_t gv = (size_t)gz * plane + (size_t)gy * V + gx;
+        for (int c = 0; c < nh; c++) {
+            const double t = w * (double)logits[(size_t)c * PS + i];        /* exact: 24 x 24 bits, the scale a power of two */
+            acc[(size_t)c * AS + gv] += fabs(t) < 9.0e18 ? __double2ll_rn(t) : 0ll;
+        }
+        wsum[gv] += __double2ll_rn(w);
+    }
+}
+extern "C" void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum) {
+    if (!umx_ready("umx_blend_add_fx")) return;
+    const size_t PS = (size_t)P * P * P; size_t g = (PS + 255) / 256; if (g > 148u * 16u) g = 148u * 16u;
+    umx_launch(blend_fx_k, dim3((unsigned)g), dim3(256), 0, logits, nh, P, V, zlo, zext, z0, y0, x0, w1d, acc, wsum);
+    g_umx_launches++;
+    UMX_CK("umx_blend_add_fx");
+}
+/* the blended value of the rows (z, y) with mode[z][y] == want, z in [za, zb) of the accumulators' extent: l = sum / weight (in fp64, rounded to
+   fp32), then fmt UMX_F16: the logit as fp16; any other fmt (uint8): round(254 p) with p = 1 / (1 + exp(-l)), 255 where no patch covers the voxel
+   (k_i3_emit, src/nn_ink3dext.cu:77-100).  out [nh][zext][V][V]. */
+__global__ void __launch_bounds__(256) emit_fx_k(const long long *__restrict__ acc, const long long *__restrict__ wsum, const uint8_t *__restrict__ mode, int want,
+                                                  int nh, int V, int zext, int za, int zb, int fmt, void *__restrict__ out) {
+    pdl_trigger(); pdl_wait();
+    const size_t plane = (size_t)V * V, AS = plane * zext, n = (size_t)(zb - za) * plane;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t gv = (size_t)za * plane + i;
+        if (mode[gv / V] != want) continue;
+        const long long ws = wsum[gv];
+        for (int c = 0; c < nh; c++) {
+            const size_t o = (size_t)c * AS + gv;
+            const float l = ws > 0 ? (float)((double)acc[o] / (double)ws) : 0.f;
+            if (fmt == UMX_F16) ((__half *)out)[o] = __float2half_rn(l);
+            else ((uint8_t *)out)[o] = ws > 0 ? (uint8_t)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-l))), 254.f)) : (uint8_t)255;
+        }
+    }
+}
+extern "C" void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out) {
+    if (!umx_ready("umx_emit_fx") || zb <= za) return;
+    const size_t n = (size_t)(zb - za) * V * V; size_t g = (n + 255) / 256; if (g > 148u * 32u) g = 148u * 32u;
+    umx_launch(emit_fx_k, dim3((unsigned)g), dim3(256), 0, acc, wsum, mode, want, nh, V, zext, za, zb, fmt, out);
+    g_umx_launches++;
+    UMX_CK("umx_emit_fx");
+}
+/* the same values for a list of rows (z, y), compact: out [row][nh][V] */
+__global__ void __launch_bounds__(256) emit_rows_fx_k(const long long *__restrict__ acc, const long long *__restrict__ wsum, const int *__restrict__ zy, long nrows, int nh, int V, int zext, int fmt, void *__restrict__ out) {
+    pdl_trigger(); pdl_wait();
+    const size_t plane = (size_t)V * V, AS = plane * zext, per = (size_t)nh * V, n = (size_t)nrows * per;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / per, k = i - r * per; const int c = (int)(k / V), x = (int)(k - (size_t)c * V);
+        const size_t gv = (size_t)zy[2 * r] * plane + (size_t)zy[2 * r + 1] * V + x;
+        const long long ws = wsum[gv];
+        const float l = ws > 0 ? (float)((double)acc[(size_t)c * AS + gv] / (double)ws) : 0.f;
+        if (fmt == UMX_F16) ((__half *)out)[i] = __float2half_rn(l);
+        else ((uint8_t *)out)[i] = ws > 0 ? (uint8_t)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-l))), 254.f)) : (uint8_t)255;
+    }
+}
+extern "C" void umx_emit_rows_fx(const long long *acc, const long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out) {
+    if (!umx_ready("umx_emit_rows_fx") || nrows <= 0) return;
+    const size_t n = (size_t)nrows * nh * V; size_t g = (n + 255) / 256; if (g > 148u * 32u) g = 148u * 32u;
+    umx_launch(emit_rows_fx_k, dim3((unsigned)g), dim3(256), 0, acc, wsum, zy_dev, nrows, nh, V, zext, fmt, out);
+    g_umx_launches++;
+    UMX_CK("umx_emit_rows_fx");
+}
+/* rows (z, y) of the accumulators to or from a compact buffer buf [row][nh + 1][V] (the weight sum last): dir 0 copies the rows out, dir 1 adds
+   the buffer's rows into the accumulators.  zy: device, 2 ints a row, z relative to the accumulators' first plane. */
+__global__ void __launch_bounds__(256) rows_fx_k(long long *__restrict__ acc, long long *__restrict__ wsum, const int *__restrict__ zy, long nrows, int nh, int V, int zext, int dir, long long *__restrict__ buf) {
+    pdl_trigger(); pdl_wait();
+    const size_t plane = (size_t)V * V, AS = plane * zext, per = (size_t)(nh + 1) * V, n = (size_t)nrows * per;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / per, k = i - r * per; const int c = (int)(k / V), x = (int)(k - (size_t)c * V);
+        const size_t gv = (size_t)zy[2 * r] * plane + (size_t)zy[2 * r + 1] * V + x;
+        long long *cell = c < nh ? acc + (size_t)c * AS + gv : wsum + gv;
+        if (dir) *cell += buf[i]; else buf[i] = *cell;
+    }
+}
+extern "C" void umx_rows_fx(long long *acc, long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf) {
+    if (!umx_ready("umx_rows_fx") || nrows <= 0) return;
+    const size_t n = (size_t)nrows * (nh + 1) * V; size_t g = (n + 255) / 256; if (g > 148u * 32u) g = 148u * 32u;
+    umx_launch(rows_fx_k, dim3((unsigned)g), dim3(256), 0, acc, wsum, zy_dev, nrows, nh, V, zext, dir, buf);
+    g_umx_launches++;
+    UMX_CK("umx_rows_fx");
+}
 extern "C" long umx_launch_count(void) { return g_umx_launches; }
 extern "C" int umx_peek_device_error(void) { return umx_errflag_read(); }

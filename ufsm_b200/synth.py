@@ -56,3 +56,21 @@ def sheet_volume(seed, V, spacing=12.0, thickness=4.0, sigma=1.5):
     r = np.sqrt(yy * yy + xx * xx)
     sheet = ((r % spacing) < thickness).astype(np.float32) * 100.0 + 45.0
     return np.clip(np.rint(noise + sheet[None, :, :]), 0, 255).astype(np.uint8)
+
+
+def sheet_slab(seed, V, z0, z1, spacing=12.0, thickness=4.0, sigma=1.5):
+    """Planes [z0, z1) of the same kind of volume, made plane by plane so that a rank can build its own slab of a 1024^3 volume: the blurred
+    noise is one 64^3 block blurred with periodic boundaries and tiled (period 64 along every axis), the sheets depend on (y, x) only."""
+    from scipy.ndimage import gaussian_filter
+    B = 64
+    noise = gaussian_filter(rng(seed).standard_normal((B, B, B)).astype(np.float32), sigma, mode="wrap") * 60.0
+    yy, xx = np.meshgrid(np.arange(V, dtype=np.float32) - V / 2, np.arange(V, dtype=np.float32) - V / 2, indexing="ij")
+    sheet = ((np.sqrt(yy * yy + xx * xx) % spacing) < thickness).astype(np.float32) * 100.0 + 45.0
+    reps = (V + B - 1) // B
+    out = np.empty((z1 - z0, V, V), np.uint8)
+    made = {}
+    for z in range(z0, z1):
+        if z % B not in made:
+            made[z % B] = np.clip(np.rint(np.tile(noise[z % B], (reps, reps))[:V, :V] + sheet), 0, 255).astype(np.uint8)
+        out[z - z0] = made[z % B]
+    return out
