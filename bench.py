@@ -236,6 +236,7 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
         warm = torch.zeros(1, device="cuda")
         dist.all_reduce(warm, group=nccl)                                        # communicator set-up outside the timed region
         torch.cuda.synchronize()
+    assert L.umx_wplan_prepare(plan, u.h, B, 100) == 0, (L.lp_check() or b"").decode()      # buffers of the run, allocated once per volume
     barrier()
     L.umx_timer_start(timer)
     rc = L.umx_window_run_fx(u.h, plan, vol_ptr, B, 100, out_host)
@@ -476,6 +477,10 @@ def run_gpu(args):
 
 
 def main():
+    # libraries loaded below (NCCL among them) may print to stdout; the one JSON line goes to the real stdout, everything else to stderr
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(real_stdout, "w")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

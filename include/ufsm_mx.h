@@ -54,6 +54,7 @@ void umx_stream_wait(void *stream, void *ev);
 void umx_stream_sync(void *stream);
 void umx_event_sync(void *ev);                           /* the host waits for the event */
 void umx_copy_async(void *dst, const void *src, size_t bytes, int to_device, void *stream);
+void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t height, int to_device, void *stream);
 void *nn_malloc_host(size_t bytes);      /* pinned host memory (cudaHostAlloc) for the window scheduler's staging buffers */
 void nn_free_host(void *p);
 
@@ -229,13 +230,14 @@ void umx_wplan_info(const umx_wplan *p, int *first, int *count, int *zlo, int *z
 long umx_wplan_rows(const umx_wplan *p, int peer, int dir, int *zy);                        /* rows handed to (dir 0) / received from (dir 1) `peer`; zy: optional, 2 ints a row (z, y), ascending */
 void umx_wplan_mode(const umx_wplan *p, uint8_t *mode);                                     /* mode [zhi - zlo][V]: 0 not this rank's patches, 1 this rank's alone (umx_window_run_fx delivers it), 2 this rank's, shared (umx_wplan_finish), 3 a lower rank's */
 size_t umx_wplan_row_bytes(const umx_wplan *p);                                             /* bytes of one exchanged row: (nh + 1) x V 64-bit sums */
+int umx_wplan_prepare(umx_wplan *p, umx_unet *u, int batch, int out_fmt);                    /* optional: allocate everything a run needs ahead of it */
 int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol_host, int batch, int out_fmt, void *out_host);
 int umx_wplan_pack(umx_wplan *p, int peer, void *buf_dev);
 int umx_wplan_add(umx_wplan *p, int peer, const void *buf_dev);
 int umx_wplan_finish(umx_wplan *p, void *out_host);
 /* the device operators underneath (acc [nh][zext][V][V], wsum [zext][V][V] 64-bit sums of an extent of zext planes from plane zlo) */
 void umx_blend_add_fx(const float *logits_dev, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d_dev, long long *acc_dev, long long *wsum_dev);
-void umx_emit_fx(const long long *acc_dev, const long long *wsum_dev, const uint8_t *mode_dev, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out_dev);
+void umx_emit_fx(const long long *acc_dev, const long long *wsum_dev, const uint8_t *mode_dev, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out_dev);
 void umx_emit_rows_fx(const long long *acc_dev, const long long *wsum_dev, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out_dev);
 void umx_rows_fx(long long *acc_dev, long long *wsum_dev, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf_dev);
 

@@ -104,6 +104,7 @@ _SIG = {
     "umx_stream_wait": (None, [C.c_void_p, C.c_void_p]),
     "umx_stream_sync": (None, [C.c_void_p]),
     "umx_event_sync": (None, [C.c_void_p]),
+    "umx_copy2d_async": (None, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p]),
     "umx_copy_async": (None, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "umx_unet_flops": (C.c_double, [C.POINTER(UnetCfg)]),
     "umx_unet_launches": (C.c_long, [C.c_void_p]),
@@ -120,12 +121,13 @@ _SIG = {
     "umx_wplan_rows": (C.c_long, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "umx_wplan_mode": (None, [C.c_void_p, C.c_void_p]),
     "umx_wplan_row_bytes": (C.c_size_t, [C.c_void_p]),
+    "umx_wplan_prepare": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "umx_window_run_fx": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "umx_wplan_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "umx_wplan_add": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "umx_wplan_finish": (C.c_int, [C.c_void_p, C.c_void_p]),
     "umx_blend_add_fx": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
-    "umx_emit_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "umx_emit_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "umx_emit_rows_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "umx_rows_fx": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
 }

@@ -84,6 +84,12 @@ extern "C" void umx_copy_async(void *dst, const void *src, size_t bytes, int to_
     if (e != cudaSuccess) umx_latch("umx_copy_async", e);
 }
 
+/* height rows of width bytes, the rows dpitch / spitch bytes apart */
+extern "C" void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t height, int to_device, void *stream) {
+    cudaError_t e = cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, height, to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e != cudaSuccess) umx_latch("umx_copy2d_async", e);
+}
+
 /* scratch: per device, per slot, grows on demand, never shrinks */
 enum { WS_SLOTS = 8 };
 static void *g_ws[16][WS_SLOTS];

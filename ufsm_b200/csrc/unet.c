@@ -16,7 +16,8 @@
 
 void umx_u8_to_h16(const uint8_t *x, size_t n, void *y);
 void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum);
-void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out);
+void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out);
+void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t height, int to_device, void *stream);
 void umx_emit_rows_fx(const long long *acc, const long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out);
 void umx_rows_fx(long long *acc, long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf);
 void umx_blend_add(const void *logits, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, float *acc, float *wsum);
@@ -259,7 +260,7 @@ struct umx_wplan {
     umx_window w; int rank, world, first, count, zlo, zhi, nh;
     uint8_t *mode;                    /* host [zext][V]: 0 not touched by this rank, 1 this rank's alone, 2 this rank's, shared with higher ranks, 3 a lower rank's */
     long nsend[WP_MAXPEER], nrecv[WP_MAXPEER], nmine2; int *send_zy[WP_MAXPEER], *recv_zy[WP_MAXPEER], *mine2_zy;   /* (z - zlo, y) pairs in ascending order */
-    long long *acc, *wsum; uint8_t *mode_dev; void *out_dev; int out_fmt; float *w1d; int *zy_dev; long zy_cap;
+    long long *acc, *wsum; uint8_t *mode_dev; void *out_dev, *fin_dev; uint8_t *fin_host, *stage[2]; float *logits; int out_fmt, batch; float *w1d; int *zy_dev; long zy_cap;
     void *ev_emit;
 };
 static void wp_rows_of_rank(const umx_window *w, int rank, int world, int *first, int *count) { umx_window_share(w, rank, world, first, count); }
@@ -317,7 +318,8 @@ void umx_wplan_free(umx_wplan *p) {
     if (!p) return;
     for (int r = 0; r < WP_MAXPEER; r++) { free(p->send_zy[r]); free(p->recv_zy[r]); }
     free(p->mine2_zy); free(p->mode);
-    nn_free(p->acc); nn_free(p->wsum); nn_free(p->mode_dev); nn_free(p->out_dev); nn_free(p->w1d); nn_free(p->zy_dev); umx_event_free(p->ev_emit);
+    nn_free(p->acc); nn_free(p->wsum); nn_free(p->mode_dev); nn_free(p->out_dev); nn_free(p->fin_dev); nn_free(p->logits); nn_free(p->w1d); nn_free(p->zy_dev); umx_event_free(p->ev_emit);
+    nn_free_host(p->fin_host); nn_free_host(p->stage[0]); nn_free_host(p->stage[1]);
     free(p);
 }
 void umx_wplan_info(const umx_wplan *p, int *first, int *count, int *zlo, int *zhi) { *first = p->first; *count = p->count; *zlo = p->zlo; *zhi = p->zhi; }
@@ -337,7 +339,7 @@ static int *wp_zy_to_dev(umx_wplan *p, const int *zy, long n) {
     nn_h2d(p->zy_dev, zy, (size_t)n * 2 * sizeof(int));
     return p->zy_dev;
 }
-static int wp_alloc(umx_wplan *p, int out_fmt) {
+static int wp_alloc(umx_wplan *p, int out_fmt, int batch, size_t PS) {
     const int V = p->w.V, P = p->w.P, zext = p->zhi - p->zlo; const size_t plane = (size_t)V * V;
     if (!p->acc) {
         p->acc = nn_malloc((size_t)p->nh * zext * plane * 8); p->wsum = nn_malloc((size_t)zext * plane * 8);
@@ -348,20 +350,40 @@ static int wp_alloc(umx_wplan *p, int out_fmt) {
           for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
         nn_h2d(p->w1d, w1d_h, (size_t)P * 4); nn_h2d(p->mode_dev, p->mode, (size_t)zext * V);
     }
-    if (!p->out_dev || p->out_fmt != out_fmt) { nn_sync(); nn_free(p->out_dev); p->out_dev = nn_malloc((size_t)p->nh * zext * plane * (out_fmt == UMX_F16 ? 2 : 1)); p->out_fmt = out_fmt; if (!p->out_dev) return -1; }
-    nn_zero(p->acc, (size_t)p->nh * zext * plane * 8); nn_zero(p->wsum, (size_t)zext * plane * 8);
+    if (!p->out_dev || p->out_fmt != out_fmt) {
+        const size_t el = out_fmt == UMX_F16 ? 2 : 1;
+        nn_sync(); nn_free(p->out_dev); nn_free(p->fin_dev); nn_free_host(p->fin_host);
+        p->out_dev = nn_malloc((size_t)p->nh * zext * plane * el); p->out_fmt = out_fmt;
+        p->fin_dev = nn_malloc((size_t)(p->nmine2 ? p->nmine2 : 1) * p->nh * V * el); p->fin_host = nn_malloc_host((size_t)(p->nmine2 ? p->nmine2 : 1) * p->nh * V * el);
+        if (!p->out_dev || !p->fin_dev || !p->fin_host) return -1;
+    }
+    if (p->batch < batch) {
+        nn_sync(); nn_free(p->logits); nn_free_host(p->stage[0]); nn_free_host(p->stage[1]);
+        p->logits = nn_malloc((size_t)batch * p->nh * PS * 4); p->stage[0] = nn_malloc_host((size_t)batch * PS); p->stage[1] = nn_malloc_host((size_t)batch * PS); p->batch = batch;
+        if (!p->logits || !p->stage[0] || !p->stage[1]) { p->batch = 0; return -1; }
+    }
     return nn_check() ? -1 : 0;
 }
-/* emit the rows that are this rank's alone in planes [za, zb) of the extent and queue their copy to out_host [nh][zext][V][V] on the copy stream */
-static void wp_emit_slab(umx_unet *u, umx_wplan *p, int za, int zb, void *out_host) {
-    if (zb <= za) return;
+/* allocates what a run of this plan needs (the sums, the output image, staging buffers) so that umx_window_run_fx itself allocates nothing;
+   optional: the run does it when it has not been done */
+int umx_wplan_prepare(umx_wplan *p, umx_unet *u, int batch, int out_fmt) {
+    if (p->zhi <= p->zlo) return 0;
+    if (batch < 1) batch = 1; if (batch > u->maxN) batch = u->maxN;
+    if (wp_alloc(p, out_fmt, batch, cube(p->w.P)) || pipe_init(u)) return -1;
+    nn_sync();
+    return nn_check() ? -1 : 0;
+}
+/* emit the rows that are this rank's alone in the box z in [za, zb) (planes of the extent), y in [ya, yb), and queue their copy to out_host
+   [nh][zext][V][V] on the copy stream: per head channel one 2-D copy of (yb - ya) V contiguous elements a plane */
+static void wp_emit_box(umx_unet *u, umx_wplan *p, int za, int zb, int ya, int yb, void *out_host) {
+    if (zb <= za || yb <= ya) return;
     const int V = p->w.V, zext = p->zhi - p->zlo; const size_t plane = (size_t)V * V, el = p->out_fmt == UMX_F16 ? 2 : 1;
-    umx_emit_fx(p->acc, p->wsum, p->mode_dev, 1, p->nh, V, zext, za, zb, p->out_fmt, p->out_dev);
+    umx_emit_fx(p->acc, p->wsum, p->mode_dev, 1, p->nh, V, zext, za, zb, ya, yb, p->out_fmt, p->out_dev);
     umx_event_record(p->ev_emit, nullptr);
     umx_stream_wait(u->s_out, p->ev_emit);
     for (int c = 0; c < p->nh; c++) {
-        const size_t o = ((size_t)c * zext + za) * plane * el;
-        umx_copy_async((uint8_t *)out_host + o, (uint8_t *)p->out_dev + o, (size_t)(zb - za) * plane * el, 0, u->s_out);
+        const size_t o = (((size_t)c * zext + za) * plane + (size_t)ya * V) * el;
+        umx_copy2d_async((uint8_t *)out_host + o, plane * el, (uint8_t *)p->out_dev + o, plane * el, (size_t)(yb - ya) * V * el, (size_t)(zb - za), 0, u->s_out);
     }
 }
 /* Forwards this rank's patches of the volume (vol_host: the V^3 uint8 volume; only the planes of the rank's extent are read), blends them,
@@ -374,12 +396,12 @@ int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol, int batch, 
     if (batch < 1) batch = 1; if (batch > u->maxN) batch = u->maxN;
     const int zext = p->zhi - p->zlo; if (zext <= 0 || p->count <= 0) return 0;
     const size_t PS = cube(P), plane = (size_t)V * V;
-    if (wp_alloc(p, out_fmt) || pipe_init(u)) return -1;
-    float *logits = nn_malloc((size_t)batch * nh * PS * 4);
-    uint8_t *stage[2] = {nn_malloc_host((size_t)batch * PS), nn_malloc_host((size_t)batch * PS)};
-    if (!logits || !stage[0] || !stage[1]) { nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]); return -1; }
-    nn_sync();
-    long j = 0; int z_done = p->zlo, z_layer = -1;
+    if (wp_alloc(p, out_fmt, batch, PS) || pipe_init(u)) return -1;
+    float *logits = p->logits; uint8_t **stage = p->stage;
+    nn_zero(p->acc, (size_t)nh * zext * plane * 8); nn_zero(p->wsum, (size_t)zext * plane * 8);
+    /* emission: [ra, rb) the planes from the end of the previous layer's own planes to the origin of the next layer (no later layer touches
+       them), lz the current layer's origin, y_done the first row of those planes not delivered yet */
+    long j = 0; int lz = -1, ra = p->zlo, rb = p->zlo, y_done = 0, y_row = -1;
     for (int q = p->first; q < p->first + p->count; q += batch, j++) {
         const int nb = q + batch <= p->first + p->count ? batch : p->first + p->count - q, k = (int)(j & 1);
         if (j >= 2) umx_event_sync(u->ev_up[k]);                 /* the staging buffer's upload of two batches ago has finished */
@@ -404,17 +426,22 @@ int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol, int batch, 
         forward(u, u->x16, nb, logits, UMX_F32);
         for (int i = 0; i < nb; i++) {
             int z0, y0, x0; umx_window_origin(w, q + i, &z0, &y0, &x0);
-            if (z0 != z_layer) {      /* a new patch layer: the planes below it have their last contribution from this rank */
-                if (z_layer >= 0 && z0 > z_done) { wp_emit_slab(u, p, z_done - p->zlo, z0 - p->zlo, out_host); z_done = z0; }
-                z_layer = z0;
+            if (z0 != lz) {           /* a new patch layer: what is left of the previous layer's own planes has had its last contribution from this rank */
+                if (lz >= 0) { wp_emit_box(u, p, ra - p->zlo, rb - p->zlo, y_done, V, out_host); ra = rb; }
+                lz = z0; y_done = 0; y_row = y0;
+                const int nn2 = w->nper * w->nper, nxt = ((q + i) / nn2 + 1) * nn2;      /* the first patch of the next layer */
+                rb = p->zhi;
+                if (nxt < w->npatch) { int za, ya, xa; umx_window_origin(w, nxt, &za, &ya, &xa); if (za < rb) rb = za; }
+                if (rb < ra) rb = ra;
+            } else if (y0 != y_row) { /* a new patch row of the layer: the rows below its first row are complete in the layer's own planes */
+                wp_emit_box(u, p, ra - p->zlo, rb - p->zlo, y_done, y0, out_host); y_done = y0; y_row = y0;
             }
             umx_blend_add_fx(logits + (size_t)i * nh * PS, nh, P, V, p->zlo, zext, z0, y0, x0, p->w1d, p->acc, p->wsum);
         }
     }
-    wp_emit_slab(u, p, z_done - p->zlo, zext, out_host);
+    wp_emit_box(u, p, ra - p->zlo, zext, y_done, V, out_host);
     umx_stream_sync(u->s_in); umx_stream_sync(u->s_out);
     nn_sync();
-    nn_free(logits); nn_free_host(stage[0]); nn_free_host(stage[1]);
     return nn_check() ? -1 : 0;
 }
 /* this rank's partial sums of the rows it hands to `peer`, compact, into buf_dev (device, umx_wplan_rows(p, peer, 0, NULL) x umx_wplan_row_bytes bytes) */
@@ -438,12 +465,11 @@ int umx_wplan_finish(umx_wplan *p, void *out_host) {
     const long n = p->nmine2; if (n <= 0) return 0;
     const int V = p->w.V, zext = p->zhi - p->zlo; const size_t el = p->out_fmt == UMX_F16 ? 2 : 1, plane = (size_t)V * V, rowb = (size_t)V * el;
     int *zy = wp_zy_to_dev(p, p->mine2_zy, n); if (!zy) return -1;
-    void *cd = nn_malloc((size_t)n * p->nh * rowb); uint8_t *ch = nn_malloc_host((size_t)n * p->nh * rowb);
-    if (!cd || !ch) { nn_free(cd); nn_free_host(ch); return -1; }
+    void *cd = p->fin_dev; uint8_t *ch = p->fin_host;
+    if (!cd || !ch) return -1;
     umx_emit_rows_fx(p->acc, p->wsum, zy, n, p->nh, V, zext, p->out_fmt, cd);
     nn_d2h(ch, cd, (size_t)n * p->nh * rowb);
     for (long r = 0; r < n; r++) for (int c = 0; c < p->nh; c++)
         memcpy((uint8_t *)out_host + (((size_t)c * zext + p->mine2_zy[2 * r]) * plane + (size_t)p->mine2_zy[2 * r + 1] * V) * el, ch + ((size_t)r * p->nh + c) * rowb, rowb);
-    nn_free(cd); nn_free_host(ch);
     return nn_check() ? -1 : 0;
 }

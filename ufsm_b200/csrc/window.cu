@@ -71,15 +71,15 @@ extern "C" void umx_blend_add_fx(const float *logits, int nh, int P, int V, int 
     g_umx_launches++;
     UMX_CK("umx_blend_add_fx");
 }
-/* the blended value of the rows (z, y) with mode[z][y] == want, z in [za, zb) of the accumulators' extent: l = sum / weight (in fp64, rounded to
+/* the blended value of the rows (z, y) with mode[z][y] == want, z in [za, zb) of the accumulators' extent and y in [ya, yb): l = sum / weight (in fp64, rounded to
    fp32), then fmt UMX_F16: the logit as fp16; any other fmt (uint8): round(254 p) with p = 1 / (1 + exp(-l)), 255 where no patch covers the voxel
    (k_i3_emit, src/nn_ink3dext.cu:77-100).  out [nh][zext][V][V]. */
 __global__ void __launch_bounds__(256) emit_fx_k(const long long *__restrict__ acc, const long long *__restrict__ wsum, const uint8_t *__restrict__ mode, int want,
-                                                  int nh, int V, int zext, int za, int zb, int fmt, void *__restrict__ out) {
+                                                  int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *__restrict__ out) {
     pdl_trigger(); pdl_wait();
-    const size_t plane = (size_t)V * V, AS = plane * zext, n = (size_t)(zb - za) * plane;
+    const size_t plane = (size_t)V * V, AS = plane * zext, slab = (size_t)(yb - ya) * V, n = (size_t)(zb - za) * slab;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t gv = (size_t)za * plane + i;
+        const size_t zz = i / slab, gv = ((size_t)za + zz) * plane + (size_t)ya * V + (i - zz * slab);
         if (mode[gv / V] != want) continue;
         const long long ws = wsum[gv];
         for (int c = 0; c < nh; c++) {
@@ -90,10 +90,10 @@ __global__ void __launch_bounds__(256) emit_fx_k(const long long *__restrict__ a
         }
     }
 }
-extern "C" void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int fmt, void *out) {
-    if (!umx_ready("umx_emit_fx") || zb <= za) return;
-    const size_t n = (size_t)(zb - za) * V * V; size_t g = (n + 255) / 256; if (g > 148u * 32u) g = 148u * 32u;
-    umx_launch(emit_fx_k, dim3((unsigned)g), dim3(256), 0, acc, wsum, mode, want, nh, V, zext, za, zb, fmt, out);
+extern "C" void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out) {
+    if (!umx_ready("umx_emit_fx") || zb <= za || yb <= ya) return;
+    const size_t n = (size_t)(zb - za) * (yb - ya) * V; size_t g = (n + 255) / 256; if (g > 148u * 32u) g = 148u * 32u;
+    umx_launch(emit_fx_k, dim3((unsigned)g), dim3(256), 0, acc, wsum, mode, want, nh, V, zext, za, zb, ya, yb, fmt, out);
     g_umx_launches++;
     UMX_CK("umx_emit_fx");
 }
