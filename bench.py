@@ -234,13 +234,19 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
             if nr:
                 recvs.append((peer, torch.empty(nr * rb, dtype=torch.int64, device="cuda")))
         warm = torch.zeros(1, device="cuda")
-        dist.all_reduce(warm, group=nccl)                                        # communicator set-up outside the timed region
+        dist.all_reduce(warm, group=nccl)                                        # communicator set-up outside the timed region ...
+        wops = [dist.P2POp(dist.isend, s_[:8], peer, group=nccl) for peer, s_ in sends] + [dist.P2POp(dist.irecv, r_[:8], peer, group=nccl) for peer, r_ in recvs]
+        if wops:                                                                  # ... and the point-to-point channels of the pairs that exchange rows
+            for r in dist.batch_isend_irecv(wops):
+                r.wait()
         torch.cuda.synchronize()
     assert L.umx_wplan_prepare(plan, u.h, B, 100) == 0, (L.lp_check() or b"").decode()      # buffers of the run, allocated once per volume
     barrier()
     L.umx_timer_start(timer)
+    t_a = time.time()
     rc = L.umx_window_run_fx(u.h, plan, vol_ptr, B, 100, out_host)
     assert rc == 0, (L.lp_check() or b"").decode()
+    t_b = time.time()
     if world > 1:
         import torch
         for peer, t in sends:
@@ -252,8 +258,11 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
             torch.cuda.synchronize()
         for peer, t in recvs:
             assert L.umx_wplan_add(plan, peer, t.data_ptr()) == 0
+    t_c = time.time()
     assert L.umx_wplan_finish(plan, out_host) == 0, (L.lp_check() or b"").decode()
+    t_d = time.time()
     ms = tmax(L.umx_timer_stop_ms(timer))
+    phases = {"forward_blend_emit_s": round(t_b - t_a, 4), "exchange_s": round(t_c - t_b, 4), "finish_shared_rows_s": round(t_d - t_c, 4)}
     # a checksum of the rows this rank delivered, so that runs at different rank counts can be compared (the volume is the same bytes)
     mode = np.zeros((zext, Vw), np.uint8)
     L.umx_wplan_mode(plan, mode.ctypes.data)
@@ -274,7 +283,7 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
     return {"workload": "config 5: %d^3 uint8 sheet volume, 128^3 patches, overlap 16 (stride 112), %d patches, Gaussian blend, (z, y) patch rows dealt by z-slab over %d GPU(s)" % (Vw, w.npatch, world),
             "scaling": "strong", "seconds": dt, "value": Vw ** 3 / dt, "unit": "volume voxels/s", "patches_per_s": w.npatch / dt, "patches_per_rank": counts,
             "output": "uint8 round(254 sigmoid(blended logit)), %d head channels, %d bytes to the host in all" % (NH, NH * Vw ** 3), "bytes_exchanged_between_ranks": nshared,
-            "volume_checksum": csum, "timing": "CUDA events on the launching stream around the whole run of a rank (forwards, blend, emit, copies to pinned host memory, exchange), max over ranks"}
+            "volume_checksum": csum, "rank0_phases_wall": phases, "timing": "CUDA events on the launching stream around the whole run of a rank (forwards, blend, emit, copies to pinned host memory, exchange), max over ranks"}
 
 
 def cpu_sample(steps, warmup):
