@@ -375,16 +375,23 @@ def run_gpu(args):
     # (the queued form of the host entry: each step uploads its own patch and downloads its own logits; the copies of one step overlap
     # the forward of the next; two result buffers so that a step's logits stay readable while the next step runs)
     hout2 = L.nn_malloc_host(B * NH * S * 2)
-    for i in range(max(2, min(args.warmup, 4))):
-        L.umx_unet_submit_host(u.h, hin, B, hout if i & 1 else hout2)
-    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
-    barrier()
-    L.umx_timer_start(timer)
-    for i in range(args.steps):
-        L.umx_unet_submit_host(u.h, hin, B, hout if i & 1 else hout2)
-    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
-    ms_e2e = tmax(L.umx_timer_stop_ms(timer))
-    barrier()
+
+    def e2e_run(submit):
+        for i in range(max(2, min(args.warmup, 4))):
+            submit(u.h, hin, B, hout if i & 1 else hout2)
+        assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
+        barrier()
+        L.umx_timer_start(timer)
+        for i in range(args.steps):
+            submit(u.h, hin, B, hout if i & 1 else hout2)
+        assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
+        v = tmax(L.umx_timer_stop_ms(timer))
+        barrier()
+        return v
+    # the result a step delivers: the uint8 probabilities round(254 sigmoid(logit)) that the reference's predict writes (converted on the device);
+    # the same with the raw fp16 logits (twice the bytes back) is reported beside it
+    ms_e2e = e2e_run(L.umx_unet_submit_host_u8)
+    ms_e2e16 = e2e_run(L.umx_unet_submit_host)
     # ---- per-launch times of the conv kernels, measured live with events around every conv launch of K more steps
     names = []
     for l in range(5):
@@ -461,7 +468,9 @@ def run_gpu(args):
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8", "data": "synthetic",
         "config": {"workload": "config 3: U-Net 32/64/128/256/320 forward on 1x1x128^3 fp16 patches, all convs MX-fp8 E4M3 + E8M0/32, fp32 accumulate", "patches_per_gpu_per_step": B,
                    "l2": "per-step working set (69 MB per level-0 tensor, > 1 GB touched) exceeds the 126 MB L2", "conv_tflops_whole_step": world * B * flops_patch * args.steps / (ms * 1e-3) / 1e12},
-        "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "h2d_bytes_per_step": B * S, "d2h_bytes_per_step": B * NH * S * 2, "ms_per_step": ms_e2e / args.steps},
+        "e2e": {"value": vox / (ms_e2e * 1e-3), "unit": "voxels/s", "h2d_bytes_per_step": B * S, "d2h_bytes_per_step": B * NH * S, "ms_per_step": ms_e2e / args.steps,
+                "call": "umx_unet_submit_host_u8 / umx_unet_wait: uint8 CT patch in pinned host memory -> uint8 probabilities (7 heads) in pinned host memory",
+                "with_fp16_logits_out": {"value": vox / (ms_e2e16 * 1e-3), "ms_per_step": ms_e2e16 / args.steps, "d2h_bytes_per_step": B * NH * S * 2}},
         "gpu_launches": int(launches), "clocks": clk.summary(),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
                      "traffic": 260782592 * B,

@@ -197,11 +197,14 @@ int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logi
    overlap the forward of the neighbouring calls (two slots in flight).  Pinned host buffers, valid (and the logits unread) until
    umx_unet_wait returns.  No counterpart in the reference, whose predict overlaps I/O with a reader thread (src/predict.c:1772-1841). */
 int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host);
+/* the same with the output as uint8 probabilities round(254 sigmoid(logit)) [N][nh][P^3], converted on the device: half the bytes back to the host */
+int umx_unet_submit_host_u8(umx_unet *u, const uint8_t *ct_host, int N, uint8_t *prob_host);
 int umx_unet_wait(umx_unet *u);
 double umx_unet_flops(const umx_unet_cfg *cfg);                  /* 2 V_out C_in C_out taps summed over the convs, per patch */
 long umx_unet_launches(const umx_unet *u);                       /* kernels launched by the library since this object was created */
 long umx_launch_count(void);                                     /* kernels launched by the library in this process */
 void umx_u8_to_h16(const uint8_t *x_dev, size_t n, void *y_dev); /* CT bytes -> fp16 x / 255 */
+void umx_h16_to_prob_u8(const void *x_dev, size_t n, uint8_t *y_dev);   /* fp16 logits -> uint8 round(254 sigmoid), the probability bytes predict writes */
 /* the reference's blend arithmetic, kept as an operator of its own: acc[c][z - zlo][y][x] = fma(w, logits[c][patch voxel], acc), wsum += w with
    the separable Gaussian window w1d (device, P floats) for the patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend,
    src/nn_ink3dext.cu:58-73); fp32 sums, so the result depends on the order of the calls */

@@ -75,6 +75,17 @@ def test_unet_queued_host_entry(dev):
     got = np.ctypeslib.as_array((C.c_uint16 * (n * nh * S)).from_address(hout)).view(np.float16).reshape(n, -1)
     for i in range(n):
         assert np.array_equal(got[i], want[i]), i
+    # the uint8 form: round(254 sigmoid(logit)) of those fp16 logits, converted on the device (the device's expf may move a value on a rounding
+    # boundary by one against numpy's)
+    hp = L.nn_malloc_host(n * nh * S)
+    for i in range(n):
+        assert L.umx_unet_submit_host_u8(u.h, hin + i * S, 1, hp + i * nh * S) == 0
+    assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
+    prob = np.ctypeslib.as_array((C.c_uint8 * (n * nh * S)).from_address(hp)).reshape(n, -1)
+    wantp = np.rint(np.float32(254) * (np.float32(1) / (np.float32(1) + np.exp(-got.astype(np.float32))))).astype(np.int32)
+    d = np.abs(prob.astype(np.int32) - wantp)
+    assert d.max() <= 1 and np.mean(d != 0) < 1e-3
+    L.nn_free_host(hp)
     L.nn_free_host(hin)
     L.nn_free_host(hout)
     u.free()

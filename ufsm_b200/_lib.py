@@ -93,6 +93,8 @@ _SIG = {
     "umx_unet_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_forward_h16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_unet_submit_host_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "umx_h16_to_prob_u8": (None, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "umx_unet_submit_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_wait": (C.c_int, [C.c_void_p]),
     "umx_wait_selftest": (C.c_int, [C.c_longlong]),

@@ -15,6 +15,7 @@
 #include <string.h>
 
 void umx_u8_to_h16(const uint8_t *x, size_t n, void *y);
+void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y);
 void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum);
 void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out);
 void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t height, int to_device, void *stream);
@@ -39,7 +40,7 @@ struct umx_unet {
     void *x16, *xu8, *logits16;   /* staging for the host entry */
     /* the pipelined host entry: two slots of input bytes and fp16 logits, a copy-in and a copy-out stream, and per slot the events
        "input uploaded", "input consumed", "logits ready", "logits downloaded" */
-    void *pxu8[2], *plog[2], *s_in, *s_out, *ev_up[2], *ev_used[2], *ev_ready[2], *ev_down[2];
+    void *pxu8[2], *plog[2], *pprob[2], *s_in, *s_out, *ev_up[2], *ev_used[2], *ev_ready[2], *ev_down[2];
     long seq; int pipe_ok;
     long launches0;
 };
@@ -81,7 +82,7 @@ void umx_unet_free(umx_unet *u) {
     }
     umx_conv_free(u->head);
     nn_free(u->x_mx); nn_free(u->ybuf); nn_free(u->part); nn_free(u->coef); nn_free(u->x16); nn_free(u->xu8); nn_free(u->logits16);
-    for (int k = 0; k < 2; k++) { nn_free(u->pxu8[k]); nn_free(u->plog[k]); umx_event_free(u->ev_up[k]); umx_event_free(u->ev_used[k]); umx_event_free(u->ev_ready[k]); umx_event_free(u->ev_down[k]); }
+    for (int k = 0; k < 2; k++) { nn_free(u->pxu8[k]); nn_free(u->plog[k]); nn_free(u->pprob[k]); umx_event_free(u->ev_up[k]); umx_event_free(u->ev_used[k]); umx_event_free(u->ev_ready[k]); umx_event_free(u->ev_down[k]); }
     umx_stream_free(u->s_in); umx_stream_free(u->s_out);
     free(u);
 }
@@ -182,15 +183,15 @@ static int pipe_init(umx_unet *u) {
     const size_t S = cube(u->cfg.P);
     u->s_in = umx_stream_new(); u->s_out = umx_stream_new();
     for (int k = 0; k < 2; k++) {
-        u->pxu8[k] = nn_malloc((size_t)u->maxN * S); u->plog[k] = nn_malloc((size_t)u->maxN * u->cfg.nh * S * 2);
+        u->pxu8[k] = nn_malloc((size_t)u->maxN * S); u->plog[k] = nn_malloc((size_t)u->maxN * u->cfg.nh * S * 2); u->pprob[k] = nn_malloc((size_t)u->maxN * u->cfg.nh * S);
         u->ev_up[k] = umx_event_new(); u->ev_used[k] = umx_event_new(); u->ev_ready[k] = umx_event_new(); u->ev_down[k] = umx_event_new();
-        if (!u->pxu8[k] || !u->plog[k] || !u->ev_up[k] || !u->ev_used[k] || !u->ev_ready[k] || !u->ev_down[k]) return -1;
+        if (!u->pxu8[k] || !u->plog[k] || !u->pprob[k] || !u->ev_up[k] || !u->ev_used[k] || !u->ev_ready[k] || !u->ev_down[k]) return -1;
     }
     if (!u->s_in || !u->s_out) return -1;
     u->pipe_ok = 1;
     return 0;
 }
-int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) {
+static int submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host, int as_u8) {
     if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_submit_host: batch %d outside 1..%d\n", N, u->maxN); abort(); }
     if (pipe_init(u)) return -1;
     const size_t S = cube(u->cfg.P);
@@ -205,14 +206,18 @@ int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logit
     umx_event_record(u->ev_used[k], nullptr);
     umx_stream_wait(nullptr, u->ev_down[k]);
     forward(u, u->x16, N, u->plog[k], UMX_F16);
+    if (as_u8) umx_h16_to_prob_u8(u->plog[k], (size_t)N * u->cfg.nh * S, u->pprob[k]);
     umx_event_record(u->ev_ready[k], nullptr);
     /* download */
     umx_stream_wait(u->s_out, u->ev_ready[k]);
-    umx_copy_async(logits16_host, u->plog[k], (size_t)N * u->cfg.nh * S * 2, 0, u->s_out);
+    if (as_u8) umx_copy_async(logits16_host, u->pprob[k], (size_t)N * u->cfg.nh * S, 0, u->s_out);
+    else umx_copy_async(logits16_host, u->plog[k], (size_t)N * u->cfg.nh * S * 2, 0, u->s_out);
     umx_event_record(u->ev_down[k], u->s_out);
     u->seq++;
     return nn_check() ? -1 : 0;
 }
+int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) { return submit_host(u, ct_host, N, logits16_host, 0); }
+int umx_unet_submit_host_u8(umx_unet *u, const uint8_t *ct_host, int N, uint8_t *prob_host) { return submit_host(u, ct_host, N, prob_host, 1); }
 int umx_unet_wait(umx_unet *u) {
     if (u->pipe_ok) { umx_stream_sync(u->s_in); umx_stream_sync(u->s_out); }
     nn_sync();

@@ -15,6 +15,20 @@ extern "C" void umx_u8_to_h16(const uint8_t *x, size_t n, void *y) {
     g_umx_launches++;
     UMX_CK("umx_u8_to_h16");
 }
+/* fp16 logits -> uint8 round(254 / (1 + exp(-l))): the per-patch form of the reference's probability output (pred_place_k, src/nn_elem.cu:1117-1125,
+   rounds 255 p + 0.5 down; the blended path's k_i3_emit uses round(254 p), which is what this library uses throughout) */
+__global__ void __launch_bounds__(256) h16_to_prob_u8_k(const __half *__restrict__ x, uint8_t *__restrict__ y, size_t n) {
+    pdl_trigger(); pdl_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = (uint8_t)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-__half2float(x[i])))), 254.f));
+}
+extern "C" void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y) {
+    if (!umx_ready("umx_h16_to_prob_u8")) return;
+    size_t g = (n + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; if (!g) g = 1;
+    umx_launch(h16_to_prob_u8_k, dim3((unsigned)g), dim3(256), 0, (const __half *)x, y, n);
+    g_umx_launches++;
+    UMX_CK("umx_h16_to_prob_u8");
+}
 /* acc[c][z - zlo][y][x] += w(z) w(y) w(x) logits[c][patch voxel], wsum likewise, for the patch at (z0, y0, x0); one thread per patch
    voxel, channels looped (patches are added one launch at a time, so no two threads touch the same accumulator) */
 template <typename T>
