@@ -198,12 +198,15 @@ def run_ops(args):
             fn()
             best = min(best, L.umx_timer_stop_ms(t))
         ufsm_b200.check()
-        print("%-22s %d ch on %d^3 MX-fp%d: %.1f us, %.0f GB/s (algorithmic %.1f MB)" % (name, Cn, D, bits, best * 1e3, nbytes / best / 1e6, nbytes / 1e6))
+        print("%-24s %d ch on %d^3 MX-fp%d: %.1f us, %.0f GB/s (algorithmic %.1f MB)" % (name, Cn, D, bits, best * 1e3, nbytes / best / 1e6, nbytes / 1e6))
 
     mxb = nb * S * (rb + 1)
     run("lp_gn_sums_mx", lambda: L.lp_gn_sums_mx(xd.ptr, dt, 1, Cn, Gn, S, sums.ptr, 0, S), mxb)
     run("lp_gn_silu_apply_mx", lambda: L.lp_gn_silu_apply_mx(xd.ptr, dt, Shape5(1, Cn, D, D, D), Gn, par[0].ptr, par[1].ptr, par[2].ptr, par[3].ptr, yd.ptr, dt), 2 * mxb)
     run("lp_up2_fwd_mx", lambda: L.lp_up2_fwd_mx(xd.ptr, dt, Shape5(1, Cn, Dh, Dh, Dh), yd.ptr, dt, gp), mxb + mxb // 8)
+    gpg = Gnp()
+    gpg.gamma, gpg.beta, gpg.mean, gpg.rstd, gpg.G = par[0].ptr, par[1].ptr, par[2].ptr, par[3].ptr, Gn
+    run("lp_up2_fwd_mx (gn+silu)", lambda: L.lp_up2_fwd_mx(xd.ptr, dt, Shape5(1, Cn, Dh, Dh, Dh), yd.ptr, dt, gpg), mxb + mxb // 8)
     run("lp_conv1_fwd_mx (7)", lambda: L.lp_conv1_fwd_mx(xd.ptr, dt, Shape5(1, Cn, D, D, D), w.ptr, None, 7, logits.ptr, gp), mxb + 7 * S * 4)
     L.umx_timer_free(t)
     us, gbs = quantiser_time(L, Cn, D, bits, args.reps)

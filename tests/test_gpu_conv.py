@@ -387,14 +387,15 @@ def _gn_params(seed, N, Cn, Gn):
             (0.3 * g.standard_normal(N * Gn)).astype(np.float32), (0.5 + g.random(N * Gn)).astype(np.float32))
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 8, 3, 10, 12), (1, 40, 5, 5, 21, 23)])      # the second: several runs of voxels, a ragged channel block
 @pytest.mark.parametrize("xdt,ybits", [(3, 8), (4, 4), (3, 4), (2, 8), (0, 4)])
-def test_gn_silu_apply_mx(dev, xdt, ybits):
+def test_gn_silu_apply_mx(dev, xdt, ybits, shape):
     """Tolerance: a transcendental (expf) sits between the operands and the requantiser, so codes may differ from the CPU evaluation where a
     value lands on a rounding boundary: at most 2e-4 of the code bytes, and 1e-3 relative L2 on the decoded tensor."""
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5
     L = ufsm_b200.lib()
-    N, Cn, Gn, D, H, W = 2, 64, 8, 3, 10, 12
+    N, Cn, Gn, D, H, W = shape
     S = D * H * W
     x = (synth.rng(71).standard_normal(N * Cn * S) * 2).astype(np.float32)
     gamma, beta, mean, rstd = _gn_params(72, N, Cn, Gn)

@@ -62,12 +62,14 @@ def up2_oracle(dq, N, Cn, D, H, W, ab=None):
     return acc.reshape(-1)
 
 
-@pytest.mark.parametrize("xbits,ybits,gn", [(8, 8, False), (4, 4, False), (8, 4, False), (4, 8, False), (8, 8, True)])
-def test_up2_fwd_mx(dev, xbits, ybits, gn):
+# the second shape spans several tiles of the kernel on every axis (4 x 4 x 16 cells of the dual grid), with ragged last tiles
+@pytest.mark.parametrize("shape", [(2, 40, 5, 3, 5, 7), (1, 64, 8, 6, 9, 35)])
+@pytest.mark.parametrize("xbits,ybits,gn", [(8, 8, False), (4, 4, False), (8, 4, False), (4, 8, False), (8, 8, True), (4, 4, True)])
+def test_up2_fwd_mx(dev, xbits, ybits, gn, shape):
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp
     L = ufsm_b200.lib()
-    N, Cn, Gn, D, H, W = 2, 40, 5, 3, 5, 7
+    N, Cn, Gn, D, H, W = shape
     S = D * H * W
     x = (synth.rng(91).standard_normal(N * Cn * S) * 2).astype(f32)
     mx = orc.pm_to_mx(x, 0, N, Cn, S, xbits, 32)
@@ -89,12 +91,12 @@ def test_up2_fwd_mx(dev, xbits, ybits, gn):
         assert bad == 0, "%d of %d bytes differ" % (bad, want.size)
 
 
-@pytest.mark.parametrize("bits,Ci,Co,N,h16,gn", [(8, 32, 7, 1, False, False), (4, 64, 16, 2, False, False), (8, 40, 3, 1, True, False), (8, 64, 32, 1, False, False), (8, 64, 7, 2, False, True)])
+@pytest.mark.parametrize("bits,Ci,Co,N,h16,gn", [(8, 32, 7, 1, False, False), (4, 64, 16, 2, False, False), (8, 40, 3, 1, True, False), (8, 64, 32, 2, False, False), (8, 64, 7, 2, False, True), (4, 96, 10, 1, False, True)])
 def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp
     L = ufsm_b200.lib()
-    D, H, W = 3, 9, 11
+    D, H, W = 5, 9, 13                # 585 voxels: a full trip of 512 a block and a ragged one
     S = D * H * W
     x = (synth.rng(95).standard_normal(N * Ci * S) * 2).astype(f32)
     w = (synth.rng(96).standard_normal((Co, Ci)) / np.sqrt(Ci)).astype(f32)

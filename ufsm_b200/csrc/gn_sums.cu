@@ -1,80 +1,105 @@
-/* GroupNorm statistics of MX tensors: lp_gn_sums_mx (src/nn_lp.h:175, src/lp_mx_gnsums.cu:9-106) and the finalise step
-   (gn_finalize_k, src/nn_elem.cu:5-11).
+/* GroupNorm statistics of MX tensors: lp_gn_sums_mx (src/nn_lp.h:175) and the finalise step (src/nn_elem.cu:5-11).
 
-   A sum lives in a slot of three 64-bit words, the reference's exact fixed point (src/gnacc.cuh:9-27): word 0 the fraction in units of
-   2^-64, word 1 the signed integer part (two's complement together with word 0), word 2 a count of non-finite contributions.  Blocks add
-   their partial sums with integer atomics, so the result does not depend on the order in which blocks finish.  Inside a block the
-   arithmetic is fp64 in a fixed order (per thread over its rows, then lanes, then warps): decoded MX values are products of a 4- or
-   2-bit mantissa and a power of two, so the fp64 sums of values and squares carry no rounding error for any realistic tensor. */
-#include "mx_common.cuh"
+   A sum lives in a slot of three 64-bit words.  The slot is a data format of the reference interface, written by these entry points and
+   read by the caller's other kernels (src/gnacc.cuh:9-27), so its meaning is the reference's: words 0 and 1 are one 128-bit two's
+   complement integer in units of 2^-64 (word 0 the low half, i.e. the fraction; word 1 the whole part), word 2 counts contributions that
+   were not finite or reached 2^62, after which the sum reads as NaN.  Blocks add into it with integer atomics, so the words do not
+   depend on the order in which blocks finish.
+
+   Inside a block the sums are exact as well, for any realistic tensor.  A lane owns eight channels of its rows (mx_rows.cuh).  Where these
+   lie in one group (C / G a multiple of 8) it adds the row's eight codes in fp32, which is exact: MX-fp8 codes are multiples of 2^-9 below
+   2^9, so the partial sums need 21 bits; the squares of the codes go through fp64 fma, and one fp64 fma per row and sum applies the row's
+   power-of-two scale (squared for the squares).  Otherwise it keeps fp64 sums per channel.  Lanes, then warps, are combined in fp64. */
+#include "mx_rows.cuh"
 
 namespace {
 
+/* v, rounded down to a multiple of 2^-64, added to slot i */
 __device__ __forceinline__ void slot_add(double *base, size_t i, double v) {
     unsigned long long *w = (unsigned long long *)base + 3 * i;
-    if (!(fabs(v) < 4.611686018427387904e18)) { atomicAdd(&w[2], 1ull); return; }      /* NaN, inf, or beyond 2^62: the sum reads as NaN */
-    const double fl = floor(v);
-    const unsigned long long frac = (unsigned long long)((v - fl) * 18446744073709551616.0);   /* [0, 1) scaled by 2^64, exact */
-    const long long whole = (long long)fl;
-    if (frac) { const unsigned long long old = atomicAdd(&w[0], frac); if (old + frac < old) atomicAdd(&w[1], 1ull); }   /* carry */
-    if (whole) atomicAdd(&w[1], (unsigned long long)whole);
+    const unsigned long long bits = (unsigned long long)__double_as_longlong(v);
+    const int ex = (int)((bits >> 52) & 0x7ffu);
+    if (ex >= 1023 + 62) { atomicAdd(&w[2], 1ull); return; }                  /* NaN, inf, or 2^62 and beyond */
+    if (ex == 0) return;                                                       /* zero (fp64 subnormals are below 2^-64) */
+    /* |v| = m 2^(ex - 1075) = m 2^sh units of 2^-64, m the 53-bit significand */
+    const unsigned long long m = (bits & 0xfffffffffffffull) | (1ull << 52);
+    const int sh = ex - 1075 + 64;
+    unsigned long long lo, hi; bool cut = false;
+    if (sh >= 64) { lo = 0ull; hi = m << (sh - 64); }
+    else if (sh > 0) { lo = m << sh; hi = m >> (64 - sh); }
+    else if (sh > -53) { lo = m >> -sh; hi = 0ull; cut = (m & ((1ull << -sh) - 1ull)) != 0ull; }
+    else { lo = 0ull; hi = 0ull; cut = true; }
+    if (bits >> 63) {                                                          /* negative: round away from zero, then negate */
+        if (cut) { lo++; if (!lo) hi++; }
+        lo = ~lo + 1ull; hi = ~hi + (lo == 0ull ? 1ull : 0ull);
+    }
+    if (lo) { const unsigned long long old = atomicAdd(&w[0], lo); if (old + lo < old) hi++; }
+    if (hi) atomicAdd(&w[1], hi);
 }
 __device__ __forceinline__ double slot_get(const double *base, size_t i) {
     const unsigned long long *w = (const unsigned long long *)base + 3 * i;
     if (w[2]) return __longlong_as_double(0x7ff8000000000000ll);
-    return (double)(long long)w[1] + (double)w[0] * 5.42101086242752217e-20;
+    return __ll2double_rn((long long)w[1]) + __ull2double_rn(w[0]) * 5.42101086242752217e-20;     /* 2^-64 */
 }
 
-/* block = (voxel slab, 32-channel block, sample); two threads a row (16 channels each), rows 128 apart */
-template <int BITS>
-__global__ void __launch_bounds__(256) gn_sums_k(const uint8_t *__restrict__ x, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0) {
-    const int nb = (C + 31) / 32, blk = blockIdx.y, n = n0 + (int)blockIdx.z, h = threadIdx.x & 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int RB = BITS == 8 ? 32 : 16;
+/* block = (run of voxels, 32-channel block, sample); ONE: a lane's eight channels share a group */
+template <int BITS, bool ONE>
+__global__ void __launch_bounds__(256) gn_sums_rows_k(const uint8_t *__restrict__ x, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0) {
+    const int nb = (C + 31) / 32, blk = blockIdx.y, n = n0 + (int)blockIdx.z, q = threadIdx.x & 3, ph = threadIdx.x >> 2, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int RB = BITS == 8 ? 32 : 16, NA = ONE ? 1 : 8;
     size_t q0 = S * blockIdx.x / gridDim.x, q1 = S * (blockIdx.x + 1) / gridDim.x;
     if (q0 < v0) q0 = v0;
     if (q1 > v1) q1 = v1;
-    const uint8_t *sc = x + (size_t)N * nb * S * RB;
+    const uint8_t *xs = x + (size_t)N * nb * S * RB;
     const size_t rbase = ((size_t)n * nb + blk) * S;
-    double s1[16], s2[16];
+    double s1[NA], s2[NA];
 #pragma unroll
-    for (int k = 0; k < 16; k++) { s1[k] = 0.0; s2[k] = 0.0; }
-    for (size_t q = q0 + (threadIdx.x >> 1); q < q1; q += 128) {
-        const size_t ri = rbase + q;
-        const float fx = mx_scale(__ldg(sc + ri));
-        if (BITS == 8) {
-            const uint4 t = __ldg((const uint4 *)(x + ri * 32 + 16 * h));
-            const unsigned wd[4] = {t.x, t.y, t.z, t.w};
-            float r[16];
+    for (int k = 0; k < NA; k++) { s1[k] = 0.0; s2[k] = 0.0; }
+    for (size_t vb = q0; vb < q1; vb += 256) {
+        uint2 raw[4]; unsigned sb[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) dec_e4m3x4(wd[j], r + 4 * j);
+        for (int u = 0; u < 4; u++) {
+            const size_t v = vb + u * 64 + ph;
+            raw[u] = make_uint2(0u, 0u); sb[u] = 127u;             /* rows past the end count as zeros */
+            if (v < q1) { raw[u] = qrow_ld<BITS>(x, rbase + v, q); sb[u] = __ldg(xs + rbase + v); }
+        }
 #pragma unroll
-            for (int k = 0; k < 16; k++) { const double v = (double)(r[k] * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
-        } else {
-            const uint2 t = __ldg((const uint2 *)(x + ri * 16 + 8 * h));
-            const unsigned wd[2] = {t.x, t.y};
-            float r[16];
+        for (int u = 0; u < 4; u++) {
+            float r[8];
+            if (ONE) {
+                qrow_dec<BITS>(raw[u], 1.f, r);                   /* the bare codes */
+                const float t1 = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+                double t2 = 0.0;
 #pragma unroll
-            for (int j = 0; j < 2; j++) dec_e2m1x8(wd[j], r + 8 * j);
+                for (int k = 0; k < 8; k++) { const double p = (double)r[k]; t2 = fma(p, p, t2); }
+                const double f = (double)mx_scale(sb[u]);
+                s1[0] = fma((double)t1, f, s1[0]); s2[0] = fma(t2, f * f, s2[0]);
+            } else {
+                qrow_dec<BITS>(raw[u], mx_scale(sb[u]), r);
 #pragma unroll
-            for (int k = 0; k < 16; k++) { const double v = (double)(r[k] * fx); s1[k] += v; s2[k] = fma(v, v, s2[k]); }
+                for (int k = 0; k < 8; k++) { const double p = (double)r[k]; s1[k] += p; s2[k] = fma(p, p, s2[k]); }
+            }
         }
     }
-    __shared__ double w1[8][32], w2[8][32];
+    /* lanes of equal q (same channels), then the eight warps */
+    __shared__ double w1[8][4][NA], w2[8][4][NA];
 #pragma unroll
-    for (int k = 0; k < 16; k++) {
+    for (int k = 0; k < NA; k++) {
         double a = s1[k], b = s2[k];
 #pragma unroll
-        for (int o = 16; o >= 2; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
-        if (lane < 2) { w1[warp][16 * h + k] = a; w2[warp][16 * h + k] = b; }
+        for (int o = 16; o >= 4; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+        if (lane < 4) { w1[warp][q][k] = a; w2[warp][q][k] = b; }
     }
     __syncthreads();
-    const int ch = blk * 32 + (int)threadIdx.x;
-    if (threadIdx.x < 32 && ch < C) {
-        double a = 0.0, b = 0.0;
+    if (threadIdx.x < 4 * NA) {
+        const int qq = threadIdx.x / NA, k = threadIdx.x % NA, ch = blk * 32 + qq * 8 + (ONE ? 0 : k);
+        if (ch < C) {
+            double a = 0.0, b = 0.0;
 #pragma unroll
-        for (int w = 0; w < 8; w++) { a += w1[w][threadIdx.x]; b += w2[w][threadIdx.x]; }
-        const size_t o = 2 * ((size_t)n * G + ch / (C / G));
-        slot_add(sums, o, a); slot_add(sums, o + 1, b);
+            for (int w = 0; w < 8; w++) { a += w1[w][qq][k]; b += w2[w][qq][k]; }
+            const size_t o = 2 * ((size_t)n * G + ch / (C / G));
+            slot_add(sums, o, a); slot_add(sums, o + 1, b);
+        }
     }
 }
 
@@ -96,15 +121,18 @@ extern "C" int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size
     if ((xdt != UMX_MX8 && xdt != UMX_MX4) || C <= 16 || G < 1 || G > 64 || C % G || n0 < 0 || n0 + cnt > N) return -1;
     if (cnt <= 0 || v1 <= v0 || !S) return 0;
     const int nb = (C + 31) / 32;
-    /* slabs of about 4096 voxels, at least about 160 blocks in all, at least 512 voxels each, at most 1024 per (block, sample) */
-    const size_t ny = (size_t)nb * cnt;
-    size_t slabs = S / 4096; const size_t want = (160 + ny - 1) / ny, most = S / 512 > 0 ? S / 512 : 1;
-    if (slabs < want) slabs = want;
-    if (slabs > most) slabs = most;
-    if (slabs > 1024) slabs = 1024;
-    const dim3 grid((unsigned)slabs, (unsigned)nb, (unsigned)cnt);
-    if (xdt == UMX_MX8) gn_sums_k<8><<<grid, 256>>>((const uint8_t *)x, N, C, G, S, sums, v0, v1, n0);
-    else gn_sums_k<4><<<grid, 256>>>((const uint8_t *)x, N, C, G, S, sums, v0, v1, n0);
+    /* runs of about 8192 voxels of S (32 trips a block; a block ends in 2 x 4 or 2 x 32 slot additions), fewer where that leaves the
+       machine short of blocks, never under 256 voxels */
+    const size_t ny = (size_t)nb * cnt, fill = (4 * 148 + ny - 1) / ny, most = (S + 255) / 256;
+    size_t runs = (S + 8191) / 8192;
+    if (runs < fill) runs = fill;
+    if (runs > most) runs = most;
+    if (runs > 65535) runs = 65535;
+    const dim3 grid((unsigned)runs, (unsigned)nb, (unsigned)cnt);
+    const bool one = (C / G) % 8 == 0;
+    const uint8_t *xq = (const uint8_t *)x;
+    if (xdt == UMX_MX8) { if (one) gn_sums_rows_k<8, true><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); else gn_sums_rows_k<8, false><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); }
+    else { if (one) gn_sums_rows_k<4, true><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); else gn_sums_rows_k<4, false><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); }
     g_umx_launches++;
     UMX_CK("lp_gn_sums_mx");
     return 0;

@@ -1,130 +1,213 @@
 /* Elementwise operators of the reference interface on MX tensors (32-wide rows, reference layout):
-     lp_up2_fwd_mx        exact-2x trilinear upsample, optionally of silu(gn(x))      (src/nn_lp.h:136, src/lp_mx_gn.cu:32-72, 151-173)
-     lp_conv1_fwd_mx      1^3 conv with fp32 weights to fp32 plane-major logits        (src/nn_lp.h:138, src/lp_mx_conv1.cu:4-22, 422-444)
+     lp_up2_fwd_mx        exact-2x trilinear upsample, optionally of silu(gn(x))      (src/nn_lp.h:136; arithmetic of src/lp_mx_gn.cu:32-72)
+     lp_conv1_fwd_mx      1^3 conv with fp32 weights to fp32 plane-major logits        (src/nn_lp.h:138; arithmetic of src/lp_mx_conv1.cu:4-22)
      lp_conv1_fwd_mx_h16  the same with fp16 logits                                      (src/nn_lp.h:139)
-   The arithmetic order is the reference's: the upsample adds its eight terms with fma in (z, y, x) order, near neighbour first; the 1^3
-   conv starts from the bias and adds w[co][ci] x[ci] with fma in ascending ci.  Both are bit-equal to a CPU evaluation of that order when no
-   GroupNorm is asked for; with gnp_t.G != 0 the input goes through silu(fma(x, a, b)) first (accurate expf; see gn_apply.cu). */
-#include "mx_common.cuh"
+   What is kept of the reference is the order of the roundings, which fixes the bytes: a fine voxel is the sum of its eight coarse corners,
+   one fma each onto a zero accumulator, z outermost and x innermost with the nearer corner first on every axis; a logit starts from its
+   bias and takes w[co][ci] x[ci] with one fma per input channel in ascending order.  Both are bit-equal to a CPU evaluation of that order
+   when no GroupNorm is asked for; with gnp_t.G != 0 the input goes through silu(fma(x, a, b)) first (accurate expf).
+
+   The kernels are laid out for this machine.  The upsample works on the dual grid: the 2 x 2 x 2 fine voxels that lie between eight coarse
+   neighbours all blend those same eight rows, so a block decodes (and activates) a halo tile of coarse rows once into shared memory, and
+   four lanes a cell then march along z holding the two coarse planes of the cell in registers: four shared-memory rows fetched per eight
+   rows written.  The 1^3 conv is one accumulator chain per (voxel, output) by definition, so a thread owns voxels; it takes two of them
+   per trip against one broadcast read of the weights, and the output count is a template parameter in fours. */
+#include "mx_rows.cuh"
 #include <cuda_fp16.h>
 
 namespace {
 
-/* row i of an MX tensor (BITS bits) decoded to 32 floats */
-template <int BITS> __device__ __forceinline__ void load_row32(const uint8_t *__restrict__ x, const uint8_t *__restrict__ sc, size_t i, float *r) {
-    const float fx = mx_scale(__ldg(sc + i));
-    if (BITS == 8) {
-        const uint4 t0 = __ldg((const uint4 *)(x + i * 32)), t1 = __ldg((const uint4 *)(x + i * 32 + 16));
-        const unsigned wd[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-#pragma unroll
-        for (int j = 0; j < 8; j++) dec_e4m3x4(wd[j], r + 4 * j);
-    } else {
-        const uint4 t0 = __ldg((const uint4 *)(x + i * 16));
-        const unsigned wd[4] = {t0.x, t0.y, t0.z, t0.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) dec_e2m1x8(wd[j], r + 8 * j);
-    }
-#pragma unroll
-    for (int k = 0; k < 32; k++) r[k] *= fx;
-}
-__device__ __forceinline__ float silu_ab(float x, float a, float b) { const float u = __fmaf_rn(x, a, b); return __fdiv_rn(u, __fadd_rn(1.f, expf(-u))); }
+/* ---------------------------------------------------------------- upsample ---------------------------------------------------------------- */
+constexpr int UZ = 4, UY = 4, UX = 16;                   /* dual cells of a block: 64 quads, each marching UZ cells */
+constexpr int HZ = UZ + 1, HY = UY + 1, HX = UX + 1;     /* coarse rows staged: the cells' corners */
+constexpr int UP2_ROWS = HZ * HY * HX;
+constexpr size_t UP2_SMEM = (size_t)UP2_ROWS * 32 * sizeof(float);
 
-/* grid (fine voxels / 256, sample x block) */
-template <int BX, int BY>
-__global__ void __launch_bounds__(256) up2_mx_k(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int N, int C, int D, int H, int W, gnp_t gp) {
-    const int nb = (C + 31) / 32, Do = 2 * D, Ho = 2 * H, Wo = 2 * W;
-    const size_t S = (size_t)D * H * W, So = 8 * S;
-    const int nbk = blockIdx.y, n = nbk / nb, blk = nbk % nb;
-    __shared__ float ca[32], cb[32];
-    if (threadIdx.x < 32) {
-        const int c = blk * 32 + (int)threadIdx.x;
-        float a = 1.f, b = 0.f;
-        if (gp.G && c < C) { const int ng = n * gp.G + c / (C / gp.G); a = __fmul_rn(gp.rstd[ng], gp.gamma[c]); b = __fmaf_rn(-gp.mean[ng], a, gp.beta[c]); }
-        ca[threadIdx.x] = a; cb[threadIdx.x] = b;
-    }
-    __syncthreads();
-    const size_t vo = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    if (vo >= So) return;
-    const int fx = (int)(vo % Wo), fy = (int)((vo / Wo) % Ho), fz = (int)(vo / ((size_t)Wo * Ho));
-    /* per axis the two source voxels of fine coordinate f on a grid of n: the coarse voxel under it (weight 3/4) and that voxel's
-       neighbour on f's side, clamped to the grid (weight 1/4) */
-    auto under = [](int f) { return f >> 1; };
-    auto beside = [](int f, int n) { const int t = (f >> 1) + ((f & 1) ? 1 : -1); return t < 0 ? 0 : (t >= n ? n - 1 : t); };
-    const int sz[2] = {under(fz), beside(fz, D)}, sy[2] = {under(fy), beside(fy, H)}, sx[2] = {under(fx), beside(fx, W)};
+__device__ __forceinline__ int clampi(int v, int hi) { return v < 0 ? 0 : (v > hi ? hi : v); }
+
+/* Dual cell (a, b, c), a in [-1, D - 1] and likewise b, c, has the corners {a, a + 1} x {b, b + 1} x {c, c + 1} clamped to the grid and
+   the fine voxels 2 a + 1 (nearer corner a) and 2 a + 2 (nearer corner a + 1) per axis; the first and last cell of an axis hold one
+   fine voxel of the grid each.  A staged row lives at tile[8 s + f]: eight float4, lane q's channels at f = q ^ 4 (s & 1) and f ^ 4, so
+   that two neighbouring rows read by eight lanes cover all the banks.
+   grid (tiles, sample x block) */
+template <int BX, int BY, bool GN>
+__global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int N, int C, int D, int H, int W, int tx, int ty, gnp_t gp) {
+    extern __shared__ __align__(16) float4 tile[];
+    const int nb = (C + 31) / 32, nbk = blockIdx.y, n = nbk / nb, blk = nbk % nb;
+    int t = blockIdx.x;
+    const int c0 = (t % tx) * UX - 1; t /= tx;
+    const int b0 = (t % ty) * UY - 1, a0 = (t / ty) * UZ - 1;
+    const int q = threadIdx.x & 3, quad = threadIdx.x >> 2;
+    const size_t S = (size_t)D * H * W;
     constexpr int RBX = BX == 8 ? 32 : 16, RBY = BY == 8 ? 32 : 16;
-    const uint8_t *sc = x + (size_t)N * nb * S * RBX;
-    const int kmax = min(32, C - blk * 32);
-    float acc[32];
-#pragma unroll
-    for (int k = 0; k < 32; k++) acc[k] = 0.f;
-    /* the eight corners in (z, y, x) order, nearest first on each axis; one fma per corner and channel */
-#pragma unroll
-    for (int t = 0; t < 8; t++) {
-        const int iz = t >> 2, iy = (t >> 1) & 1, ix = t & 1;
-        const float w3 = (iz ? 0.25f : 0.75f) * (iy ? 0.25f : 0.75f) * (ix ? 0.25f : 0.75f);
-        float r[32];
-        load_row32<BX>(x, sc, (size_t)nbk * S + ((size_t)sz[iz] * H + sy[iy]) * W + sx[ix], r);
-        if (gp.G) {
-#pragma unroll
-            for (int k = 0; k < 32; k++) if (k < kmax) r[k] = silu_ab(r[k], ca[k], cb[k]);
-        }
-#pragma unroll
-        for (int k = 0; k < 32; k++) acc[k] = __fmaf_rn(w3, r[k], acc[k]);
-    }
-    unsigned wq[8];
-    const unsigned sb = mx_encode_row32<BY>(acc, wq);
-    const size_t i = (size_t)nbk * So + vo;
-    *(uint4 *)(y + i * RBY) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
-    if (BY == 8) *(uint4 *)(y + i * 32 + 16) = make_uint4(wq[4], wq[5], wq[6], wq[7]);
-    y[(size_t)N * nb * So * RBY + i] = (uint8_t)sb;
-}
+    const uint8_t *xs = x + (size_t)N * nb * S * RBX;
 
-/* one thread per voxel; weights [ci][16] and the GroupNorm coefficients [n][ci] in shared memory */
-template <int BITS, typename YT>
-__global__ void __launch_bounds__(256) conv1_mx_k(const uint8_t *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b, YT *__restrict__ y,
-                                                  int N, int Ci, int Co, size_t S, gnp_t gp) {
-    extern __shared__ __align__(16) float c1s[];
-    float *sw = c1s; float2 *sab = (float2 *)(c1s + (size_t)16 * Ci);
-    const int nb = (Ci + 31) / 32;
-    for (int i = threadIdx.x; i < 16 * Ci; i += blockDim.x) { const int ci = i >> 4, co = i & 15; sw[i] = co < Co ? w[(size_t)co * Ci + ci] : 0.f; }
-    if (gp.G) for (int i = threadIdx.x; i < N * Ci; i += blockDim.x) {
-        const int n = i / Ci, ci = i % Ci, ng = n * gp.G + ci / (Ci / gp.G);
-        const float a = __fmul_rn(gp.rstd[ng], gp.gamma[ci]);
-        sab[i] = make_float2(a, __fmaf_rn(-gp.mean[ng], a, gp.beta[ci]));
+    float ca[8], cb[8]; bool live[8];
+    if (GN) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int c = blk * 32 + q * 8 + k;
+            live[k] = c < C; ca[k] = 1.f; cb[k] = 0.f;
+            if (live[k]) { const int ng = n * gp.G + c / (C / gp.G); ca[k] = __fmul_rn(gp.rstd[ng], gp.gamma[c]); cb[k] = __fmaf_rn(-gp.mean[ng], ca[k], gp.beta[c]); }
+        }
+    }
+    /* stage: loads of all trips first, then decode (+ activation) and store */
+    constexpr int TRIPS = (UP2_ROWS + 63) / 64;
+    uint2 raw[TRIPS]; unsigned sb[TRIPS];
+#pragma unroll
+    for (int u = 0; u < TRIPS; u++) {
+        const int s = u * 64 + quad;
+        raw[u] = make_uint2(0u, 0u); sb[u] = 127u;
+        if (s < UP2_ROWS) {
+            const int ix = s % HX, iy = (s / HX) % HY, iz = s / (HX * HY);
+            const size_t row = (size_t)nbk * S + ((size_t)clampi(a0 + iz, D - 1) * H + clampi(b0 + iy, H - 1)) * W + clampi(c0 + ix, W - 1);
+            raw[u] = qrow_ld<BX>(x, row, q); sb[u] = __ldg(xs + row);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < TRIPS; u++) {
+        const int s = u * 64 + quad;
+        float r[8];
+        qrow_dec<BX>(raw[u], mx_scale(sb[u]), r);
+        if (GN) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) if (live[k]) r[k] = silu_ab(r[k], ca[k], cb[k]);
+        }
+        if (s < UP2_ROWS) {
+            const int f = q ^ ((s & 1) << 2);
+            tile[8 * s + f] = make_float4(r[0], r[1], r[2], r[3]);
+            tile[8 * s + (f ^ 4)] = make_float4(r[4], r[5], r[6], r[7]);
+        }
     }
     __syncthreads();
-    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    if (i >= (size_t)N * S) return;
-    const int n = (int)(i / S); const size_t v = i % S;
-    constexpr int RB = BITS == 8 ? 32 : 16;
-    const uint8_t *sc = x + (size_t)N * nb * S * RB;
-    float acc[16];
+
+    const int lb = quad / UX, lc = quad % UX, b = b0 + lb, c = c0 + lc;
+    const int Do = 2 * D, Ho = 2 * H, Wo = 2 * W;
+    const size_t So = 8 * S;
+    uint8_t *ys = y + (size_t)N * nb * So * RBY;
+    float pl[2][2][2][8];                                   /* [plane of the cell][y corner][x corner][channel] */
+    auto fetch = [&](int iz, float (*dst)[2][8]) {
 #pragma unroll
-    for (int co = 0; co < 16; co++) acc[co] = (b && co < Co) ? b[co] : 0.f;
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int s = (iz * HY + lb + j) * HX + lc + i, f = q ^ ((s & 1) << 2);
+                const float4 lo = tile[8 * s + f], hi = tile[8 * s + (f ^ 4)];
+                dst[j][i][0] = lo.x; dst[j][i][1] = lo.y; dst[j][i][2] = lo.z; dst[j][i][3] = lo.w;
+                dst[j][i][4] = hi.x; dst[j][i][5] = hi.y; dst[j][i][6] = hi.z; dst[j][i][7] = hi.w;
+            }
+    };
+    fetch(0, pl[0]);
+#pragma unroll
+    for (int la = 0; la < UZ; la++) {
+        /* the cell's lower plane sits in pl[la & 1], the upper one is fetched into the other half */
+        fetch(la + 1, pl[(la + 1) & 1]);
+        const int a = a0 + la;
+        if (a > D - 1) break;                               /* the same for the whole block */
+#pragma unroll
+        for (int oz = 0; oz < 2; oz++)
+#pragma unroll
+            for (int oy = 0; oy < 2; oy++) {
+                const int fz = 2 * a + 1 + oz, fy = 2 * b + 1 + oy;
+                const bool okzy = fz >= 0 && fz < Do && fy >= 0 && fy < Ho;
+                uint2 wq[2]; unsigned sq[2];
+#pragma unroll
+                for (int ox = 0; ox < 2; ox++) {
+                    float acc[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) acc[k] = 0.f;
+                    /* corner order: z outermost, the nearer corner first on each axis.  An odd fine coordinate (o = 0) is nearer to the
+                       cell's lower corner, an even one (o = 1) to the upper */
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int iz = e >> 2, iy = (e >> 1) & 1, ix = e & 1;
+                        const float w3 = (iz ? 0.25f : 0.75f) * (iy ? 0.25f : 0.75f) * (ix ? 0.25f : 0.75f);
+                        const float *src = pl[(la + (oz ^ iz)) & 1][oy ^ iy][ox ^ ix];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) acc[k] = __fmaf_rn(w3, src[k], acc[k]);
+                    }
+                    sq[ox] = qrow_enc<BY>(acc, wq[ox]);
+                }
+                const int fx0 = 2 * c + 1;
+                const size_t row = (size_t)nbk * So + ((size_t)fz * Ho + fy) * Wo + fx0;     /* meaningful only where stored */
+                if (okzy && fx0 >= 0 && fx0 < Wo) qrow_st<BY>(y, row, q, wq[0]);
+                if (okzy && fx0 + 1 < Wo) qrow_st<BY>(y, row + 1, q, wq[1]);
+                if (okzy && q < 2 && fx0 + q >= 0 && fx0 + q < Wo) ys[row + q] = (uint8_t)(q ? sq[1] : sq[0]);   /* two lanes, two neighbouring scale bytes */
+            }
+    }
+}
+
+/* ---------------------------------------------------------------- 1^3 conv ---------------------------------------------------------------- */
+/* grid (voxels / 512, sample); outputs co0 + [0, Co) of co_all; weights as [ci][4 CO4] and the sample's GroupNorm coefficients [ci] in
+   shared memory, every read of them a broadcast */
+template <int BITS, int CO4, bool GN, typename YT>
+__global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias, YT *__restrict__ y,
+                                                   int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
+    extern __shared__ __align__(16) float4 c1sm[];
+    float4 *sw = c1sm; float2 *sab = (float2 *)(c1sm + (size_t)Ci * CO4);
+    constexpr int CO = 4 * CO4, RB = BITS == 8 ? 32 : 16, WORDS = RB / 4;
+    const int nb = (Ci + 31) / 32, n = blockIdx.y;
+    for (int i = threadIdx.x; i < Ci * CO; i += 256) { const int ci = i / CO, co = i % CO; ((float *)sw)[i] = co < Co ? w[(size_t)co * Ci + ci] : 0.f; }
+    if (GN) for (int ci = threadIdx.x; ci < Ci; ci += 256) {
+        const int ng = n * gp.G + ci / (Ci / gp.G);
+        const float a = __fmul_rn(gp.rstd[ng], gp.gamma[ci]);
+        sab[ci] = make_float2(a, __fmaf_rn(-gp.mean[ng], a, gp.beta[ci]));
+    }
+    __syncthreads();
+    const size_t v0 = (size_t)blockIdx.x * 512 + threadIdx.x;
+    const bool ok[2] = {v0 < S, v0 + 256 < S};
+    const uint8_t *xs = x + (size_t)N * nb * S * RB;
+    float acc[2][CO];
+#pragma unroll
+    for (int co = 0; co < CO; co++) { const float b0 = (bias && co < Co) ? bias[co] : 0.f; acc[0][co] = b0; acc[1][co] = b0; }
     for (int blk = 0; blk < nb; blk++) {
-        float r[32];
-        load_row32<BITS>(x, sc, ((size_t)n * nb + blk) * S + v, r);
-        const int kmax = min(32, Ci - blk * 32);
+        unsigned wd[2][WORDS]; float fx[2];
 #pragma unroll
-        for (int k = 0; k < 32; k++) {
-            if (k < kmax) {
-                const int ci = blk * 32 + k;
-                const float xv = gp.G ? silu_ab(r[k], sab[n * Ci + ci].x, sab[n * Ci + ci].y) : r[k];
-                const float4 *wr = (const float4 *)(sw + 16 * ci);
+        for (int u = 0; u < 2; u++) {
+            const size_t row = ((size_t)n * nb + blk) * S + v0 + 256 * u;
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const float4 t = wr[q];
-                    acc[4 * q] = __fmaf_rn(t.x, xv, acc[4 * q]); acc[4 * q + 1] = __fmaf_rn(t.y, xv, acc[4 * q + 1]);
-                    acc[4 * q + 2] = __fmaf_rn(t.z, xv, acc[4 * q + 2]); acc[4 * q + 3] = __fmaf_rn(t.w, xv, acc[4 * q + 3]);
+            for (int j = 0; j < WORDS; j += 4) {
+                const uint4 t4 = ok[u] ? __ldg((const uint4 *)(x + row * RB) + j / 4) : make_uint4(0u, 0u, 0u, 0u);
+                wd[u][j] = t4.x; wd[u][j + 1] = t4.y; wd[u][j + 2] = t4.z; wd[u][j + 3] = t4.w;
+            }
+            fx[u] = mx_scale(ok[u] ? __ldg(xs + row) : 127u);
+        }
+        const int cend = min(32, Ci - blk * 32);
+#pragma unroll
+        for (int h = 0; h < 4; h++) {                       /* eight channels at a time */
+            if (8 * h >= cend) break;
+            float r[2][8];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                if (BITS == 8) { dec_e4m3x4(wd[u][2 * h], r[u]); dec_e4m3x4(wd[u][2 * h + 1], r[u] + 4); } else dec_e2m1x8(wd[u][h], r[u]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) r[u][k] *= fx[u];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int ci = blk * 32 + 8 * h + k;
+                if (8 * h + k < cend) {
+                    float x0 = r[0][k], x1 = r[1][k];
+                    if (GN) { const float2 ab = sab[ci]; x0 = silu_ab(x0, ab.x, ab.y); x1 = silu_ab(x1, ab.x, ab.y); }
+#pragma unroll
+                    for (int j = 0; j < CO4; j++) {
+                        const float4 t4 = sw[ci * CO4 + j];
+                        acc[0][4 * j] = __fmaf_rn(t4.x, x0, acc[0][4 * j]); acc[0][4 * j + 1] = __fmaf_rn(t4.y, x0, acc[0][4 * j + 1]);
+                        acc[0][4 * j + 2] = __fmaf_rn(t4.z, x0, acc[0][4 * j + 2]); acc[0][4 * j + 3] = __fmaf_rn(t4.w, x0, acc[0][4 * j + 3]);
+                        acc[1][4 * j] = __fmaf_rn(t4.x, x1, acc[1][4 * j]); acc[1][4 * j + 1] = __fmaf_rn(t4.y, x1, acc[1][4 * j + 1]);
+                        acc[1][4 * j + 2] = __fmaf_rn(t4.z, x1, acc[1][4 * j + 2]); acc[1][4 * j + 3] = __fmaf_rn(t4.w, x1, acc[1][4 * j + 3]);
+                    }
                 }
             }
         }
     }
 #pragma unroll
-    for (int co = 0; co < 16; co++) if (co < Co) {
-        const size_t o = ((size_t)n * Co + co) * S + v;
-        if (sizeof(YT) == 4) ((float *)y)[o] = acc[co]; else ((__half *)y)[o] = __float2half_rn(acc[co]);
-    }
+    for (int u = 0; u < 2; u++)
+#pragma unroll
+        for (int co = 0; co < CO; co++) if (co < Co && ok[u]) {
+            const size_t o = ((size_t)n * co_all + co0 + co) * S + v0 + 256 * u;
+            if (sizeof(YT) == 4) ((float *)y)[o] = acc[u][co]; else ((__half *)y)[o] = __float2half_rn(acc[u][co]);
+        }
 }
 
 void gp_check(const char *fn, gnp_t gp, int C) {
@@ -132,25 +215,50 @@ void gp_check(const char *fn, gnp_t gp, int C) {
     if (gp.G && (gp.G < 1 || C % gp.G)) { fprintf(stderr, "%s: %d channels in %d groups\n", fn, C, gp.G); abort(); }
 }
 
+template <int BX, int BY, bool GN> void up2_launch(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp) {
+    static bool sized = false;      /* per instantiation; the attribute belongs to the function, any device of this process */
+    if (!sized) { cudaFuncSetAttribute(up2_dual_k<BX, BY, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UP2_SMEM); sized = true; }
+    up2_dual_k<BX, BY, GN><<<grid, 256, UP2_SMEM>>>(x, y, xs.n, xs.c, xs.d, xs.h, xs.w, tx, ty, gp);
+}
+template <int BX, int BY> void up2_gn(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp) {
+    if (gp.G) up2_launch<BX, BY, true>(grid, x, y, xs, tx, ty, gp); else up2_launch<BX, BY, false>(grid, x, y, xs, tx, ty, gp);
+}
+
+template <int BITS, int CO4, typename YT>
+void conv1_launch(dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
+    if (gp.G) conv1_vox_k<BITS, CO4, true, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp);
+    else conv1_vox_k<BITS, CO4, false, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp);
+}
+template <int BITS, typename YT>
+void conv1_co(int co4, dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
+    switch (co4) {
+    case 1: conv1_launch<BITS, 1, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
+    case 2: conv1_launch<BITS, 2, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
+    case 3: conv1_launch<BITS, 3, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
+    default: conv1_launch<BITS, 4, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
+    }
+}
+
 template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, YT *y, gnp_t gp) {
     if (!umx_ready(fn)) return;
     if (xdt != UMX_MX8 && xdt != UMX_MX4) { fprintf(stderr, "%s: input dtype %d is not MX\n", fn, xdt); abort(); }
     if (xs.c <= 16) { fprintf(stderr, "%s: an input of 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
+    if (cout < 1 || (cout > 16 && cout % 16)) { fprintf(stderr, "%s: cout %d is neither 1..16 nor a multiple of 16\n", fn, cout); abort(); }
+    if (xs.n > 65535) { fprintf(stderr, "%s: %d samples\n", fn, xs.n); abort(); }
     gp_check(fn, gp, xs.c);
     const size_t S = (size_t)xs.d * xs.h * xs.w;
-    if (cout > 16 && cout % 16 == 0 && xs.n == 1) {     /* more outputs: passes of 16, as the reference */
-        for (int c0 = 0; c0 < cout; c0 += 16) conv1_fwd<YT>(fn, x, xdt, xs, w + (size_t)c0 * xs.c, b ? b + c0 : nullptr, 16, y + (size_t)c0 * S, gp);
-        return;
+    if (!S || !xs.n) return;
+    const dim3 grid((unsigned)((S + 511) / 512), (unsigned)xs.n);
+    /* more than 16 outputs: passes of 16 over the same input (the reference's rule, src/lp_mx_conv1.cu:422-444) */
+    for (int c0 = 0; c0 < cout; c0 += 16) {
+        const int co = min(16, cout - c0), co4 = (co + 3) / 4;
+        const size_t smem = (size_t)xs.c * co4 * 16 + (gp.G ? (size_t)xs.c * 8 : 0);
+        if (smem > 48 * 1024) { fprintf(stderr, "%s: %d input channels need more shared memory than this kernel has\n", fn, xs.c); abort(); }
+        const float *wp = w + (size_t)c0 * xs.c, *bp = b ? b + c0 : nullptr;
+        if (xdt == UMX_MX8) conv1_co<8, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp);
+        else conv1_co<4, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp);
+        g_umx_launches++;
     }
-    if (cout < 1 || cout > 16) { fprintf(stderr, "%s: cout %d > 16\n", fn, cout); abort(); }
-    const size_t smem = (size_t)16 * xs.c * 4 + (gp.G ? (size_t)xs.n * xs.c * 8 : 0);
-    if (smem > 48 * 1024) { fprintf(stderr, "%s: %d samples of %d channels need more shared memory than this kernel has\n", fn, xs.n, xs.c); abort(); }
-    const size_t rows = (size_t)xs.n * S;
-    if (!rows) return;
-    const unsigned blocks = (unsigned)((rows + 255) / 256);
-    if (xdt == UMX_MX8) conv1_mx_k<8, YT><<<blocks, 256, smem>>>((const uint8_t *)x, w, b, y, xs.n, xs.c, cout, S, gp);
-    else conv1_mx_k<4, YT><<<blocks, 256, smem>>>((const uint8_t *)x, w, b, y, xs.n, xs.c, cout, S, gp);
-    g_umx_launches++;
     UMX_CK(fn);
 }
 
@@ -162,12 +270,14 @@ extern "C" void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int yd
     if ((xdt != UMX_MX8 && xdt != UMX_MX4) || (ydt != UMX_MX8 && ydt != UMX_MX4)) { fprintf(stderr, "%s: dtypes %d -> %d are not MX\n", fn, xdt, ydt); abort(); }
     if (xs.c <= 16) { fprintf(stderr, "%s: 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
     gp_check(fn, gp, xs.c);
-    const size_t So = 8 * (size_t)xs.d * xs.h * xs.w;
-    if (!So || !xs.n) return;
-    const dim3 grid((unsigned)((So + 255) / 256), (unsigned)(xs.n * ((xs.c + 31) / 32)));
+    if (!xs.n || !xs.d || !xs.h || !xs.w) return;
+    const int tx = (xs.w + 1 + UX - 1) / UX, ty = (xs.h + 1 + UY - 1) / UY, tz = (xs.d + 1 + UZ - 1) / UZ;      /* D + 1 dual cells an axis */
+    const size_t tiles = (size_t)tx * ty * tz, nbk = (size_t)xs.n * ((xs.c + 31) / 32);
+    if (tiles > 0x7fffffffu || nbk > 65535) { fprintf(stderr, "%s: %zu tiles x %zu (sample, block) pairs exceed the grid\n", fn, tiles, nbk); abort(); }
+    const dim3 grid((unsigned)tiles, (unsigned)nbk);
     const uint8_t *xq = (const uint8_t *)x; uint8_t *yq = (uint8_t *)y;
-    if (xdt == UMX_MX4) { if (ydt == UMX_MX4) up2_mx_k<4, 4><<<grid, 256>>>(xq, yq, xs.n, xs.c, xs.d, xs.h, xs.w, gp); else up2_mx_k<4, 8><<<grid, 256>>>(xq, yq, xs.n, xs.c, xs.d, xs.h, xs.w, gp); }
-    else { if (ydt == UMX_MX4) up2_mx_k<8, 4><<<grid, 256>>>(xq, yq, xs.n, xs.c, xs.d, xs.h, xs.w, gp); else up2_mx_k<8, 8><<<grid, 256>>>(xq, yq, xs.n, xs.c, xs.d, xs.h, xs.w, gp); }
+    if (xdt == UMX_MX4) { if (ydt == UMX_MX4) up2_gn<4, 4>(grid, xq, yq, xs, tx, ty, gp); else up2_gn<4, 8>(grid, xq, yq, xs, tx, ty, gp); }
+    else { if (ydt == UMX_MX4) up2_gn<8, 4>(grid, xq, yq, xs, tx, ty, gp); else up2_gn<8, 8>(grid, xq, yq, xs, tx, ty, gp); }
     g_umx_launches++;
     UMX_CK(fn);
 }
