@@ -3,8 +3,9 @@
    src/lp_common.cuh:244-261, 474-482), which the conv entry points run ahead of the conv when gnp_t.G != 0.
 
    The reference evaluates SiLU with approximate intrinsics (__expf, or tanh.approx in the fused staging: about 2^-11 relative); here it
-   is v / (1 + expf(-v)) with the accurate expf and an IEEE division, so that the result agrees with a CPU evaluation of the definition to
-   an ulp or two and MX codes differ from that evaluation's only where a value sits on a rounding boundary.
+   is v * rcp(1 + ex2(-v log2 e)) with the two hardware approximations (silu_hw, mx_rows.cuh: about 1e-6 relative), so that MX codes
+   differ from a CPU evaluation of the definition only where a value sits within that distance of a rounding boundary.  An exact expf
+   and an IEEE division cost some 40 instructions an element and held this pass to a tenth of the memory rate.
 
    Four lanes a row (mx_rows.cuh), four rows a thread per trip with their loads issued together; a lane keeps the normalisation
    constants of its eight channels in registers for the whole run of voxels. */
@@ -22,23 +23,26 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
     const int q = threadIdx.x & 3, ph = threadIdx.x >> 2, cpg = C / G;
     constexpr int RBY = BY == 8 ? 32 : 16;
     /* per channel: FORM 0 (mean, rstd, gamma, beta) in (k0, k1, k2, k3); FORM 1 (a, b) in (k0, k1) */
-    float k0[8], k1[8], k2[8], k3[8]; bool live[8];
+    float2 k0[4], k1[4], k2[4], k3[4]; bool live[8];         /* FORM 0: k0 holds -mean */
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int c = blk * 32 + q * 8 + k;
-        live[k] = c < C; k0[k] = k1[k] = k2[k] = k3[k] = 0.f;
+        float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+        live[k] = c < C;
         if (live[k]) {
             const int ng = n * G + c / cpg;
-            if (FORM == 0) { k0[k] = mean[ng]; k1[k] = rstd[ng]; k2[k] = gamma[c]; k3[k] = beta[c]; }
-            else { k0[k] = __fmul_rn(rstd[ng], gamma[c]); k1[k] = __fmaf_rn(-mean[ng], k0[k], beta[c]); }
+            if (FORM == 0) { t0 = -mean[ng]; t1 = rstd[ng]; t2 = gamma[c]; t3 = beta[c]; }
+            else { t0 = __fmul_rn(rstd[ng], gamma[c]); t1 = __fmaf_rn(-mean[ng], t0, beta[c]); }
         }
+        if (k & 1) { k0[k >> 1].y = t0; k1[k >> 1].y = t1; k2[k >> 1].y = t2; k3[k >> 1].y = t3; }
+        else { k0[k >> 1].x = t0; k1[k >> 1].x = t1; k2[k >> 1].x = t2; k3[k >> 1].x = t3; }
     }
     const size_t nbk = (size_t)n * nb + blk, v0 = S * blockIdx.x / T, v1 = S * (blockIdx.x + 1) / T;
     const uint8_t *xq = (const uint8_t *)xv;
     const uint8_t *xs = XK == 8 ? xq + (size_t)N * nb * S * 32 : xq + (size_t)N * nb * S * 16;
     uint8_t *ys = y + (size_t)N * nb * S * RBY;
     for (size_t vb = v0; vb < v1; vb += 256) {
-        float r[4][8];
+        float2 r[4][4];
         if (XK == 8 || XK == 4) {
             uint2 raw[4]; unsigned sb[4];
 #pragma unroll
@@ -57,7 +61,8 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     const size_t o = ((size_t)n * C + blk * 32 + q * 8 + k) * S + v;
-                    r[u][k] = (live[k] && v < v1) ? (XK == 0 ? __ldg((const float *)xv + o) : __half2float(__ldg((const __half *)xv + o))) : 0.f;
+                    const float t = (live[k] && v < v1) ? (XK == 0 ? __ldg((const float *)xv + o) : __half2float(__ldg((const __half *)xv + o))) : 0.f;
+                    if (k & 1) r[u][k >> 1].y = t; else r[u][k >> 1].x = t;
                 }
             }
         }
@@ -65,11 +70,11 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
         for (int u = 0; u < 4; u++) {
             const size_t v = vb + u * 64 + ph;
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                float t;
-                if (FORM == 0) t = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(r[u][k], k0[k]), k1[k]), k2[k]), k3[k]);
-                else t = __fmaf_rn(r[u][k], k0[k], k1[k]);
-                r[u][k] = live[k] ? __fdiv_rn(t, __fadd_rn(1.f, expf(-t))) : 0.f;
+            for (int j = 0; j < 4; j++) {
+                float2 t;
+                if (FORM == 0) t = __fadd2_rn(__fmul2_rn(__fmul2_rn(__fadd2_rn(r[u][j], k0[j]), k1[j]), k2[j]), k3[j]);     /* x + (-mean) is x - mean */
+                else t = __ffma2_rn(r[u][j], k0[j], k1[j]);
+                r[u][j] = make_float2(live[2 * j] ? silu_hw(t.x) : 0.f, live[2 * j + 1] ? silu_hw(t.y) : 0.f);
             }
             uint2 w;
             const unsigned sb = qrow_enc<BY>(r[u], w);       /* every lane, also those past the end of the run */

@@ -8,8 +8,7 @@
 
    Inside a block the sums are exact as well, for any realistic tensor.  A lane owns eight channels of its rows (mx_rows.cuh).  Where these
    lie in one group (C / G a multiple of 8) it adds the row's eight codes in fp32, which is exact: MX-fp8 codes are multiples of 2^-9 below
-   2^9, so the partial sums need 21 bits; the squares of the codes go through fp64 fma, and one fp64 fma per row and sum applies the row's
-   power-of-two scale (squared for the squares).  Otherwise it keeps fp64 sums per channel.  Lanes, then warps, are combined in fp64. */
+   2^9, so the partial sums need 21 bits; the squares of the codes go through fp64 fma, and one fp64 fma per row and sum applies the row's power-of-two scale (squared for the squares).  Otherwise it keeps fp64 sums per channel.  Lanes, then warps, are combined in fp64. */
 #include "mx_rows.cuh"
 
 namespace {
@@ -65,19 +64,20 @@ __global__ void __launch_bounds__(256) gn_sums_rows_k(const uint8_t *__restrict_
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            float r[8];
+            float2 r[4];
             if (ONE) {
                 qrow_dec<BITS>(raw[u], 1.f, r);                   /* the bare codes */
-                const float t1 = ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+                const float2 h01 = __fadd2_rn(r[0], r[1]), h23 = __fadd2_rn(r[2], r[3]), h = __fadd2_rn(h01, h23);
+                const float t1 = h.x + h.y;
                 double t2 = 0.0;
 #pragma unroll
-                for (int k = 0; k < 8; k++) { const double p = (double)r[k]; t2 = fma(p, p, t2); }
+                for (int j = 0; j < 4; j++) { const double px = (double)r[j].x, py = (double)r[j].y; t2 = fma(px, px, t2); t2 = fma(py, py, t2); }
                 const double f = (double)mx_scale(sb[u]);
                 s1[0] = fma((double)t1, f, s1[0]); s2[0] = fma(t2, f * f, s2[0]);
             } else {
                 qrow_dec<BITS>(raw[u], mx_scale(sb[u]), r);
 #pragma unroll
-                for (int k = 0; k < 8; k++) { const double p = (double)r[k]; s1[k] += p; s2[k] = fma(p, p, s2[k]); }
+                for (int k = 0; k < 8; k++) { const double p = (double)((k & 1) ? r[k >> 1].y : r[k >> 1].x); s1[k] += p; s2[k] = fma(p, p, s2[k]); }
             }
         }
     }
@@ -121,10 +121,10 @@ extern "C" int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size
     if ((xdt != UMX_MX8 && xdt != UMX_MX4) || C <= 16 || G < 1 || G > 64 || C % G || n0 < 0 || n0 + cnt > N) return -1;
     if (cnt <= 0 || v1 <= v0 || !S) return 0;
     const int nb = (C + 31) / 32;
-    /* runs of about 8192 voxels of S (32 trips a block; a block ends in 2 x 4 or 2 x 32 slot additions), fewer where that leaves the
-       machine short of blocks, never under 256 voxels */
-    const size_t ny = (size_t)nb * cnt, fill = (4 * 148 + ny - 1) / ny, most = (S + 255) / 256;
-    size_t runs = (S + 8191) / 8192;
+    /* runs of about 2048 voxels of S (eight trips a block; a block ends in 2 x 4 or 2 x 32 slot additions), fewer where that leaves
+       the machine short of blocks, never under 256 voxels */
+    const size_t ny = (size_t)nb * cnt, fill = (8 * 148 + ny - 1) / ny, most = (S + 255) / 256;
+    size_t runs = (S + 2047) / 2048;
     if (runs < fill) runs = fill;
     if (runs > most) runs = most;
     if (runs > 65535) runs = 65535;

@@ -42,10 +42,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 /* exponent e of the block scale 2^e = exponent of amax / qmax rounded up, clamped to [-126, 126]; NaN / inf amax -> 128 (scale
    byte 0xFF).  Same rule as src/lp_common.cuh:492-500. */
 __device__ __forceinline__ int mx_exp(float amax, float inv_qmax) {
-    const unsigned u = __float_as_uint(__fmul_rn(amax, inv_qmax));
-    if ((u & 0x7fffffffu) >= 0x7f800000u) return 128;
-    const int e = (int)((u >> 23) & 0xffu) - 127 + ((u & 0x7fffffu) != 0);
-    return max(-126, min(126, e));
+    const unsigned u = __float_as_uint(__fmul_rn(amax, inv_qmax)) & 0x7fffffffu;
+    if (u >= 0x7f800000u) return 128;
+    const int eb = (int)((u + 0x7fffffu) >> 23);            /* the biased exponent, one more when the mantissa is not zero */
+    return max(1, min(253, eb)) - 127;
 }
 __device__ __forceinline__ float exp2i(int e) { return __uint_as_float((unsigned)(127 + e) << 23); }
 /* NaN-propagating amax on the magnitude bits (src/lp_common.cuh:486) */

@@ -5,7 +5,7 @@
    What is kept of the reference is the order of the roundings, which fixes the bytes: a fine voxel is the sum of its eight coarse corners,
    one fma each onto a zero accumulator, z outermost and x innermost with the nearer corner first on every axis; a logit starts from its
    bias and takes w[co][ci] x[ci] with one fma per input channel in ascending order.  Both are bit-equal to a CPU evaluation of that order
-   when no GroupNorm is asked for; with gnp_t.G != 0 the input goes through silu(fma(x, a, b)) first (accurate expf).
+   when no GroupNorm is asked for; with gnp_t.G != 0 the input goes through silu(fma(x, a, b)) first (silu_hw, mx_rows.cuh).
 
    The kernels are laid out for this machine.  The upsample works on the dual grid: the 2 x 2 x 2 fine voxels that lie between eight coarse
    neighbours all blend those same eight rows, so a block decodes (and activates) a halo tile of coarse rows once into shared memory, and
@@ -42,13 +42,15 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
     constexpr int RBX = BX == 8 ? 32 : 16, RBY = BY == 8 ? 32 : 16;
     const uint8_t *xs = x + (size_t)N * nb * S * RBX;
 
-    float ca[8], cb[8]; bool live[8];
+    float2 ca[4], cb[4]; bool live[8];
     if (GN) {
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             const int c = blk * 32 + q * 8 + k;
-            live[k] = c < C; ca[k] = 1.f; cb[k] = 0.f;
-            if (live[k]) { const int ng = n * gp.G + c / (C / gp.G); ca[k] = __fmul_rn(gp.rstd[ng], gp.gamma[c]); cb[k] = __fmaf_rn(-gp.mean[ng], ca[k], gp.beta[c]); }
+            float a = 1.f, b = 0.f;
+            live[k] = c < C;
+            if (live[k]) { const int ng = n * gp.G + c / (C / gp.G); a = __fmul_rn(gp.rstd[ng], gp.gamma[c]); b = __fmaf_rn(-gp.mean[ng], a, gp.beta[c]); }
+            if (k & 1) { ca[k >> 1].y = a; cb[k >> 1].y = b; } else { ca[k >> 1].x = a; cb[k >> 1].x = b; }
         }
     }
     /* stage: loads of all trips first, then decode (+ activation) and store */
@@ -67,34 +69,40 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
 #pragma unroll
     for (int u = 0; u < TRIPS; u++) {
         const int s = u * 64 + quad;
-        float r[8];
+        float2 r[4];
         qrow_dec<BX>(raw[u], mx_scale(sb[u]), r);
         if (GN) {
 #pragma unroll
-            for (int k = 0; k < 8; k++) if (live[k]) r[k] = silu_ab(r[k], ca[k], cb[k]);
+            for (int j = 0; j < 4; j++) { const float2 a2 = silu_ab2(r[j], ca[j], cb[j]); if (live[2 * j]) r[j].x = a2.x; if (live[2 * j + 1]) r[j].y = a2.y; }
         }
         if (s < UP2_ROWS) {
             const int f = q ^ ((s & 1) << 2);
-            tile[8 * s + f] = make_float4(r[0], r[1], r[2], r[3]);
-            tile[8 * s + (f ^ 4)] = make_float4(r[4], r[5], r[6], r[7]);
+            tile[8 * s + f] = make_float4(r[0].x, r[0].y, r[1].x, r[1].y);
+            tile[8 * s + (f ^ 4)] = make_float4(r[2].x, r[2].y, r[3].x, r[3].y);
         }
     }
     __syncthreads();
 
-    const int lb = quad / UX, lc = quad % UX, b = b0 + lb, c = c0 + lc;
+    const int lb = quad / UX, lc = quad % UX;
     const int Do = 2 * D, Ho = 2 * H, Wo = 2 * W;
-    const size_t So = 8 * S;
-    uint8_t *ys = y + (size_t)N * nb * So * RBY;
-    float pl[2][2][2][8];                                   /* [plane of the cell][y corner][x corner][channel] */
-    auto fetch = [&](int iz, float (*dst)[2][8]) {
+    const size_t So = 8 * S;                                /* below 2^31: voxel offsets inside a (sample, block) are 32-bit */
+    /* the first fine voxel of the quad's cells on y and x, which of the two per axis lie in the grid, and this lane's store addresses
+       for voxel 0 of its (sample, block): codes, and (lanes 0 and 1) the scale byte of the cell's first / second x voxel */
+    const int fy0 = 2 * (b0 + lb) + 1, fx0 = 2 * (c0 + lc) + 1;
+    const bool vy[2] = {fy0 >= 0 && fy0 < Ho, fy0 + 1 < Ho}, vx[2] = {fx0 >= 0 && fx0 < Wo, fx0 + 1 < Wo};
+    uint8_t *yq = y + (size_t)nbk * So * RBY + q * (RBY / 4);
+    uint8_t *ysq = y + (size_t)N * nb * So * RBY + (size_t)nbk * So + (q & 1);
+    const bool vs = q < 2 && vx[q & 1];
+    float2 pl[2][2][2][4];                                  /* [plane of the cell][y corner][x corner][channel pair] */
+    auto fetch = [&](int iz, float2 (*dst)[2][4]) {
 #pragma unroll
         for (int j = 0; j < 2; j++)
 #pragma unroll
             for (int i = 0; i < 2; i++) {
                 const int s = (iz * HY + lb + j) * HX + lc + i, f = q ^ ((s & 1) << 2);
                 const float4 lo = tile[8 * s + f], hi = tile[8 * s + (f ^ 4)];
-                dst[j][i][0] = lo.x; dst[j][i][1] = lo.y; dst[j][i][2] = lo.z; dst[j][i][3] = lo.w;
-                dst[j][i][4] = hi.x; dst[j][i][5] = hi.y; dst[j][i][6] = hi.z; dst[j][i][7] = hi.w;
+                dst[j][i][0] = make_float2(lo.x, lo.y); dst[j][i][1] = make_float2(lo.z, lo.w);
+                dst[j][i][2] = make_float2(hi.x, hi.y); dst[j][i][3] = make_float2(hi.z, hi.w);
             }
     };
     fetch(0, pl[0]);
@@ -102,37 +110,35 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
     for (int la = 0; la < UZ; la++) {
         /* the cell's lower plane sits in pl[la & 1], the upper one is fetched into the other half */
         fetch(la + 1, pl[(la + 1) & 1]);
-        const int a = a0 + la;
-        if (a > D - 1) break;                               /* the same for the whole block */
+        const int fz0 = 2 * (a0 + la) + 1;                  /* cells past the grid compute and store nothing: no early exit, the loop stays unrolled and pl in registers */
+        const bool vz[2] = {fz0 >= 0 && fz0 < Do, fz0 + 1 < Do};
 #pragma unroll
         for (int oz = 0; oz < 2; oz++)
 #pragma unroll
             for (int oy = 0; oy < 2; oy++) {
-                const int fz = 2 * a + 1 + oz, fy = 2 * b + 1 + oy;
-                const bool okzy = fz >= 0 && fz < Do && fy >= 0 && fy < Ho;
+                const bool okzy = vz[oz] && vy[oy];
                 uint2 wq[2]; unsigned sq[2];
 #pragma unroll
                 for (int ox = 0; ox < 2; ox++) {
-                    float acc[8];
+                    float2 acc[4];
 #pragma unroll
-                    for (int k = 0; k < 8; k++) acc[k] = 0.f;
+                    for (int k = 0; k < 4; k++) acc[k] = make_float2(0.f, 0.f);
                     /* corner order: z outermost, the nearer corner first on each axis.  An odd fine coordinate (o = 0) is nearer to the
                        cell's lower corner, an even one (o = 1) to the upper */
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         const int iz = e >> 2, iy = (e >> 1) & 1, ix = e & 1;
                         const float w3 = (iz ? 0.25f : 0.75f) * (iy ? 0.25f : 0.75f) * (ix ? 0.25f : 0.75f);
-                        const float *src = pl[(la + (oz ^ iz)) & 1][oy ^ iy][ox ^ ix];
+                        const float2 *src = pl[(la + (oz ^ iz)) & 1][oy ^ iy][ox ^ ix];
 #pragma unroll
-                        for (int k = 0; k < 8; k++) acc[k] = __fmaf_rn(w3, src[k], acc[k]);
+                        for (int k = 0; k < 4; k++) acc[k] = __ffma2_rn(make_float2(w3, w3), src[k], acc[k]);
                     }
                     sq[ox] = qrow_enc<BY>(acc, wq[ox]);
                 }
-                const int fx0 = 2 * c + 1;
-                const size_t row = (size_t)nbk * So + ((size_t)fz * Ho + fy) * Wo + fx0;     /* meaningful only where stored */
-                if (okzy && fx0 >= 0 && fx0 < Wo) qrow_st<BY>(y, row, q, wq[0]);
-                if (okzy && fx0 + 1 < Wo) qrow_st<BY>(y, row + 1, q, wq[1]);
-                if (okzy && q < 2 && fx0 + q >= 0 && fx0 + q < Wo) ys[row + q] = (uint8_t)(q ? sq[1] : sq[0]);   /* two lanes, two neighbouring scale bytes */
+                const int vo = ((fz0 + oz) * Ho + fy0 + oy) * Wo + fx0;                       /* meaningful only where stored */
+                if (okzy && vx[0]) { if (BY == 8) *(uint2 *)(yq + (ptrdiff_t)vo * 32) = wq[0]; else *(unsigned *)(yq + (ptrdiff_t)vo * 16) = wq[0].x; }
+                if (okzy && vx[1]) { if (BY == 8) *(uint2 *)(yq + (ptrdiff_t)(vo + 1) * 32) = wq[1]; else *(unsigned *)(yq + (ptrdiff_t)(vo + 1) * 16) = wq[1].x; }
+                if (okzy && vs) ysq[vo] = (uint8_t)((q & 1) ? sq[1] : sq[0]);                 /* two lanes, two neighbouring scale bytes */
             }
     }
 }
@@ -157,7 +163,7 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
     const size_t v0 = (size_t)blockIdx.x * 512 + threadIdx.x;
     const bool ok[2] = {v0 < S, v0 + 256 < S};
     const uint8_t *xs = x + (size_t)N * nb * S * RB;
-    float acc[2][CO];
+    float acc[2][CO];                                       /* scalar fma: the packed form has the same pipe rate and needs the input twice */
 #pragma unroll
     for (int co = 0; co < CO; co++) { const float b0 = (bias && co < Co) ? bias[co] : 0.f; acc[0][co] = b0; acc[1][co] = b0; }
     for (int blk = 0; blk < nb; blk++) {
@@ -176,28 +182,28 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
 #pragma unroll
         for (int h = 0; h < 4; h++) {                       /* eight channels at a time */
             if (8 * h >= cend) break;
-            float r[2][8];
+            float2 r[2][4];
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                if (BITS == 8) { dec_e4m3x4(wd[u][2 * h], r[u]); dec_e4m3x4(wd[u][2 * h + 1], r[u] + 4); } else dec_e2m1x8(wd[u][h], r[u]);
-#pragma unroll
-                for (int k = 0; k < 8; k++) r[u][k] *= fx[u];
-            }
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
+            for (int u = 0; u < 2; u++) qrow_dec<BITS>(BITS == 8 ? make_uint2(wd[u][2 * h], wd[u][2 * h + 1]) : make_uint2(wd[u][h], 0u), fx[u], r[u]);
+            auto chan = [&](int k) {
                 const int ci = blk * 32 + 8 * h + k;
-                if (8 * h + k < cend) {
-                    float x0 = r[0][k], x1 = r[1][k];
-                    if (GN) { const float2 ab = sab[ci]; x0 = silu_ab(x0, ab.x, ab.y); x1 = silu_ab(x1, ab.x, ab.y); }
+                float x0 = (k & 1) ? r[0][k >> 1].y : r[0][k >> 1].x, x1 = (k & 1) ? r[1][k >> 1].y : r[1][k >> 1].x;
+                if (GN) { const float2 ab = sab[ci]; x0 = silu_hw(__fmaf_rn(x0, ab.x, ab.y)); x1 = silu_hw(__fmaf_rn(x1, ab.x, ab.y)); }
 #pragma unroll
-                    for (int j = 0; j < CO4; j++) {
-                        const float4 t4 = sw[ci * CO4 + j];
-                        acc[0][4 * j] = __fmaf_rn(t4.x, x0, acc[0][4 * j]); acc[0][4 * j + 1] = __fmaf_rn(t4.y, x0, acc[0][4 * j + 1]);
-                        acc[0][4 * j + 2] = __fmaf_rn(t4.z, x0, acc[0][4 * j + 2]); acc[0][4 * j + 3] = __fmaf_rn(t4.w, x0, acc[0][4 * j + 3]);
-                        acc[1][4 * j] = __fmaf_rn(t4.x, x1, acc[1][4 * j]); acc[1][4 * j + 1] = __fmaf_rn(t4.y, x1, acc[1][4 * j + 1]);
-                        acc[1][4 * j + 2] = __fmaf_rn(t4.z, x1, acc[1][4 * j + 2]); acc[1][4 * j + 3] = __fmaf_rn(t4.w, x1, acc[1][4 * j + 3]);
-                    }
+                for (int j = 0; j < CO4; j++) {
+                    const float4 t4 = sw[ci * CO4 + j];
+                    acc[0][4 * j] = __fmaf_rn(t4.x, x0, acc[0][4 * j]); acc[0][4 * j + 1] = __fmaf_rn(t4.y, x0, acc[0][4 * j + 1]);
+                    acc[0][4 * j + 2] = __fmaf_rn(t4.z, x0, acc[0][4 * j + 2]); acc[0][4 * j + 3] = __fmaf_rn(t4.w, x0, acc[0][4 * j + 3]);
+                    acc[1][4 * j] = __fmaf_rn(t4.x, x1, acc[1][4 * j]); acc[1][4 * j + 1] = __fmaf_rn(t4.y, x1, acc[1][4 * j + 1]);
+                    acc[1][4 * j + 2] = __fmaf_rn(t4.z, x1, acc[1][4 * j + 2]); acc[1][4 * j + 3] = __fmaf_rn(t4.w, x1, acc[1][4 * j + 3]);
                 }
+            };
+            if (8 * h + 8 <= cend) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) chan(k);
+            } else {                                            /* the ragged end of the last block */
+#pragma unroll
+                for (int k = 0; k < 8; k++) if (8 * h + k < cend) chan(k);
             }
         }
     }
@@ -271,6 +277,7 @@ extern "C" void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int yd
     if (xs.c <= 16) { fprintf(stderr, "%s: 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
     gp_check(fn, gp, xs.c);
     if (!xs.n || !xs.d || !xs.h || !xs.w) return;
+    if ((size_t)xs.d * xs.h * xs.w >= ((size_t)1 << 28)) { fprintf(stderr, "%s: 2^31 fine voxels per sample or more\n", fn); abort(); }
     const int tx = (xs.w + 1 + UX - 1) / UX, ty = (xs.h + 1 + UY - 1) / UY, tz = (xs.d + 1 + UZ - 1) / UZ;      /* D + 1 dual cells an axis */
     const size_t tiles = (size_t)tx * ty * tz, nbk = (size_t)xs.n * ((xs.c + 31) / 32);
     if (tiles > 0x7fffffffu || nbk > 65535) { fprintf(stderr, "%s: %zu tiles x %zu (sample, block) pairs exceed the grid\n", fn, tiles, nbk); abort(); }
