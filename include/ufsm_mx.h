@@ -80,7 +80,10 @@ void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y);
 void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y);
 /* the same quantiser with 32-wide blocks whatever C (padding channels zero): the form the graph below keeps its tensors in */
 size_t umx_mx_bytes32(int bits, int N, int C, size_t S);
-void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout);   /* dt 0 fp32 / 2 fp16 plane-major */
+void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout);   /* dt 0 fp32 / 1 bf16 / 2 fp16 plane-major */
+/* the same from two tensors, channels [0, c2) of the C from x and the rest from x2 (the concat input of split_t.x2 / c_split,
+   src/nn_lp.h:20: rows of 32 channels over the concatenated index); x2 NULL: one tensor */
+void umx_pm_to_mx32_cat(const void *x, const void *x2, int c2, int dt, int N, int C, size_t S, void *y, int bits, int layout);
 void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y, int layout);         /* -> plane-major fp32 */
 void umx_mx_relayout(const void *src, int bits, int N, int C, size_t S, void *dst, int to_layout);   /* 32-wide MX tensor between the two layouts */
 void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);                   /* blocked fp16 -> plane-major fp32 */

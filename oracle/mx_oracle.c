@@ -592,3 +592,69 @@ void orc_emit_fx(const long long *acc, const long long *wsum, int nh, size_t nvo
         else ((uint8_t *)out)[o] = ws > 0 ? (uint8_t)lrintf((1.f / (1.f + expf(-l))) * 254.f) : 255;
     }
 }
+
+/* ---- elementwise operators of the reference interface on dequantised tensors (plane-major fp32 [n][c][voxel]) ---- */
+
+/* GroupNorm + SiLU of a tensor, or of a channel segment of a larger tensor the G groups are counted over (its channel 0 is channel
+   c_off of C_all; gamma, beta, mean, rstd belong to the larger tensor).  form 0: ((x - mean) rstd) gamma + beta as lp_gn_silu_apply_mx
+   (src/lp_mx_gn.cu:17); form 1: fma(x, a, b), a = rstd gamma, b = fma(-mean, a, beta), the conv operand's transform (make_chan / act_ab,
+   src/lp_common.cuh:244-261, 474-476).  SiLU by its definition u / (1 + exp(-u)): the reference evaluates it with approximate
+   intrinsics, so implementations are compared with this one under a tolerance. */
+void orc_gn_silu(const float *x, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                 int form, int c_off, int C_all, float *y) {
+    const int cpg = C_all / G;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; n++)
+        for (int c = 0; c < C; c++) {
+            const int cl = c_off + c, ng = n * G + cl / cpg;
+            const float a = rstd[ng] * gamma[cl], b = fmaf(-mean[ng], a, beta[cl]);
+            const float *xp = x + ((size_t)n * C + c) * S; float *yp = y + ((size_t)n * C + c) * S;
+            for (size_t v = 0; v < S; v++) {
+                const float u = form == 0 ? (((xp[v] - mean[ng]) * rstd[ng]) * gamma[cl]) + beta[cl] : fmaf(xp[v], a, b);
+                yp[v] = u / (1.f + expf(-u));
+            }
+        }
+}
+
+/* exact-2x trilinear upsample (align_corners false, edges clamped) with the reference's order of roundings (up2_mx_k,
+   src/lp_mx_gn.cu:35-72; host blend of tests/test_mx4_wide.c:327-338): a fine voxel starts from zero and takes its eight coarse
+   corners with one fma each, z outermost, x innermost, on every axis the corner under the fine voxel (weight 3/4) before its
+   neighbour on the fine voxel's side (weight 1/4). */
+void orc_up2(const float *x, int N, int C, int D, int H, int W, float *y) {
+    const size_t S = (size_t)D * H * W;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int nc = 0; nc < N * C; nc++)
+        for (int fz = 0; fz < 2 * D; fz++) {
+            const float *xp = x + (size_t)nc * S; float *yp = y + (size_t)nc * 8 * S;
+            for (int fy = 0; fy < 2 * H; fy++)
+                for (int fx = 0; fx < 2 * W; fx++) {
+                    int s[3][2]; const int f[3] = {fz, fy, fx}, lim[3] = {D, H, W};
+                    for (int a = 0; a < 3; a++) {
+                        const int t = (f[a] >> 1) + ((f[a] & 1) ? 1 : -1);
+                        s[a][0] = f[a] >> 1; s[a][1] = t < 0 ? 0 : t >= lim[a] ? lim[a] - 1 : t;
+                    }
+                    float acc = 0.f;
+                    for (int e = 0; e < 8; e++) {
+                        const int iz = e >> 2, iy = (e >> 1) & 1, ix = e & 1;
+                        const float w3 = (iz ? 0.25f : 0.75f) * (iy ? 0.25f : 0.75f) * (ix ? 0.25f : 0.75f);
+                        acc = fmaf(w3, xp[((size_t)s[0][iz] * H + s[1][iy]) * W + s[2][ix]], acc);
+                    }
+                    yp[((size_t)fz * 2 * H + fy) * 2 * W + fx] = acc;
+                }
+        }
+}
+
+/* 1^3 conv with fp32 weights w [co][ci]: bias first, then one fma per input channel in ascending order (conv1_mx_k,
+   src/lp_mx_conv1.cu:4-22) */
+void orc_conv1(const float *x, const float *w, const float *b, int N, int Ci, int Co, size_t S, float *y) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; n++)
+        for (int co = 0; co < Co; co++) {
+            float *yp = y + ((size_t)n * Co + co) * S;
+            for (size_t v = 0; v < S; v++) yp[v] = b ? b[co] : 0.f;
+            for (int ci = 0; ci < Ci; ci++) {
+                const float wv = w[(size_t)co * Ci + ci]; const float *xp = x + ((size_t)n * Ci + ci) * S;
+                for (size_t v = 0; v < S; v++) yp[v] = fmaf(wv, xp[v], yp[v]);
+            }
+        }
+}

@@ -240,6 +240,32 @@ def emit_fx(acc, wsum, nh, fmt):
     return out
 
 
+def gn_silu(x, N, Cn, S, Gn, gamma, beta, mean, rstd, form, c_off=0, C_all=None):
+    """silu(groupnorm(x)) of a plane-major fp32 tensor (or of a channel segment of a tensor of C_all channels), flat fp32"""
+    x = f32(x)
+    y = np.empty(N * Cn * S, np.float32)
+    g, b, m, r = f32(gamma), f32(beta), f32(mean), f32(rstd)
+    o().orc_gn_silu(_p(x), N, Cn, C.c_size_t(S), Gn, _p(g), _p(b), _p(m), _p(r), form, c_off, Cn if C_all is None else C_all, _p(y))
+    return y
+
+
+def up2(x, N, Cn, D, H, W):
+    """exact-2x trilinear upsample in the reference's order of roundings, flat fp32 [N][Cn][2D][2H][2W]"""
+    x = f32(x)
+    y = np.empty(N * Cn * 8 * D * H * W, np.float32)
+    o().orc_up2(_p(x), N, Cn, D, H, W, _p(y))
+    return y
+
+
+def conv1(x, w, b, N, Ci, Co, S):
+    """1^3 conv with fp32 weights, bias first then ascending input channel, flat fp32 [N][Co][S]"""
+    x, w = f32(x), f32(w)
+    y = np.empty(N * Co * S, np.float32)
+    bb = f32(b) if b is not None else None
+    o().orc_conv1(_p(x), _p(w), _p(bb) if bb is not None else None, N, Ci, Co, C.c_size_t(S), _p(y))
+    return y
+
+
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

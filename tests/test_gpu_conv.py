@@ -364,21 +364,9 @@ def test_lp_conv_fwd_f4_entry(dev):
 
 
 def _gn_silu_oracle(dq, N, Cn, S, Gn, gamma, beta, mean, rstd, form):
-    """fp32 restatement: form 0 = ((x - mean) rstd) gamma + beta (src/lp_mx_gn.cu:17), form 1 = fma(x, a, b) with a = rstd gamma,
-    b = fma(-mean, a, beta) (src/lp_common.cuh:244-261, 474-476); then v / (1 + exp(-v))."""
-    f32 = np.float32
-    x = dq.reshape(N, Cn, S).astype(f32)
-    g = np.arange(Cn) // (Cn // Gn)
-    m, r = mean.reshape(N, Gn)[:, g][:, :, None].astype(f32), rstd.reshape(N, Gn)[:, g][:, :, None].astype(f32)
-    ga, be = gamma[None, :, None].astype(f32), beta[None, :, None].astype(f32)
-    if form == 0:
-        u = (((x - m) * r) * ga) + be
-    else:
-        a = r * ga
-        b = (be.astype(np.float64) - m.astype(np.float64) * a.astype(np.float64)).astype(f32)
-        u = (x.astype(np.float64) * a.astype(np.float64) + b.astype(np.float64)).astype(f32)
-    with np.errstate(over="ignore"):
-        return (u / (f32(1) + np.exp(-u, dtype=f32))).astype(f32).reshape(-1)
+    """form 0 = ((x - mean) rstd) gamma + beta (src/lp_mx_gn.cu:17), form 1 = fma(x, a, b) with a = rstd gamma, b = fma(-mean, a, beta)
+    (src/lp_common.cuh:244-261, 474-476); then v / (1 + exp(-v)): the oracle's orc_gn_silu"""
+    return orc.gn_silu(dq, N, Cn, S, Gn, gamma, beta, mean, rstd, form)
 
 
 def _gn_params(seed, N, Cn, Gn):

@@ -1,5 +1,5 @@
-"""GPU parity of the reference interface's elementwise MX operators (trilinear 2x upsample, 1^3 conv with fp32 weights) against numpy
-restatements of the reference's arithmetic order (src/lp_mx_gn.cu:32-72, src/lp_mx_conv1.cu:4-22)."""
+"""GPU parity of the reference interface's elementwise MX operators (trilinear 2x upsample, 1^3 conv with fp32 weights) against the
+oracle's restatements of the reference's arithmetic order (orc_up2, orc_conv1, orc_gn_silu; src/lp_mx_gn.cu:32-72, src/lp_mx_conv1.cu:4-22)."""
 import numpy as np
 import pytest
 
@@ -8,24 +8,6 @@ import synth
 
 pytestmark = pytest.mark.gpu
 f32, f64 = np.float32, np.float64
-
-
-def fma(a, b, c):
-    """fp32 fma through fp64 (the product is exact there; the double rounding of the sum differs from a true fma about once in 2^29)"""
-    return (a.astype(f64) * b.astype(f64) + c.astype(f64)).astype(f32)
-
-
-def silu_ab(x, a, b):
-    u = fma(x, a, b)
-    with np.errstate(over="ignore"):
-        return (u / (f32(1) + np.exp(-u, dtype=f32))).astype(f32)
-
-
-def gn_ab(N, Cn, Gn, gamma, beta, mean, rstd):
-    g = np.arange(Cn) // (Cn // Gn)
-    a = (rstd.reshape(N, Gn)[:, g] * gamma[None, :]).astype(f32)
-    b = (beta[None, :].astype(f64) - mean.reshape(N, Gn)[:, g].astype(f64) * a.astype(f64)).astype(f32)
-    return a, b
 
 
 def gn_params(seed, N, Cn, Gn):
@@ -42,26 +24,6 @@ def make_gp(Gn, arrays):
     return gp, bufs
 
 
-def up2_oracle(dq, N, Cn, D, H, W, ab=None):
-    x = dq.reshape(N, Cn, D, H, W).astype(f32)
-    if ab is not None:
-        x = silu_ab(x, ab[0][:, :, None, None, None], ab[1][:, :, None, None, None])
-
-    def idx(n):
-        o = np.arange(2 * n)
-        return o >> 1, np.clip((o >> 1) + np.where(o & 1, 1, -1), 0, n - 1)
-    mz, my, mx = idx(D), idx(H), idx(W)
-    wt = (f32(0.75), f32(0.25))
-    acc = np.zeros((N, Cn, 2 * D, 2 * H, 2 * W), f32)
-    for a in range(2):
-        for b in range(2):
-            for c in range(2):
-                w3 = f32(wt[a] * wt[b] * wt[c])
-                r = x[:, :, mz[a]][:, :, :, my[b]][:, :, :, :, mx[c]]
-                acc = fma(np.full_like(r, w3), r, acc)
-    return acc.reshape(-1)
-
-
 # the second shape spans several tiles of the kernel on every axis (4 x 4 x 16 cells of the dual grid), with ragged last tiles
 @pytest.mark.parametrize("shape", [(2, 40, 5, 3, 5, 7), (1, 64, 8, 6, 9, 35)])
 @pytest.mark.parametrize("xbits,ybits,gn", [(8, 8, False), (4, 4, False), (8, 4, False), (4, 8, False), (8, 8, True), (4, 4, True)])
@@ -74,12 +36,12 @@ def test_up2_fwd_mx(dev, xbits, ybits, gn, shape):
     x = (synth.rng(91).standard_normal(N * Cn * S) * 2).astype(f32)
     mx = orc.pm_to_mx(x, 0, N, Cn, S, xbits, 32)
     dq = orc.mx_to_pm(mx, xbits, N, Cn, S, 32)
-    gp, keep, ab = Gnp(), None, None
+    gp, keep = Gnp(), None
     if gn:
         pr = gn_params(92, N, Cn, Gn)
         gp, keep = make_gp(Gn, pr)
-        ab = gn_ab(N, Cn, Gn, *pr)
-    want = orc.pm_to_mx(up2_oracle(dq, N, Cn, D, H, W, ab), 0, N, Cn, 8 * S, ybits, 32)
+        dq = orc.gn_silu(dq, N, Cn, S, Gn, *pr, 1)
+    want = orc.pm_to_mx(orc.up2(dq, N, Cn, D, H, W), 0, N, Cn, 8 * S, ybits, 32)
     xd, yd = DevBuf(data=mx), DevBuf(want.size).fill(0xEE)
     L.lp_up2_fwd_mx(xd.ptr, 3 if xbits == 8 else 4, Shape5(N, Cn, D, H, W), yd.ptr, 3 if ybits == 8 else 4, gp)
     ufsm_b200.check()
@@ -102,16 +64,13 @@ def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
     w = (synth.rng(96).standard_normal((Co, Ci)) / np.sqrt(Ci)).astype(f32)
     b = (0.1 * synth.rng(97).standard_normal(Co)).astype(f32)
     mx = orc.pm_to_mx(x, 0, N, Ci, S, bits, 32)
-    dq = orc.mx_to_pm(mx, bits, N, Ci, S, 32).reshape(N, Ci, S)
+    dq = orc.mx_to_pm(mx, bits, N, Ci, S, 32)
     gp, keep = Gnp(), None
     if gn:
         pr = gn_params(98, N, Ci, 8)
         gp, keep = make_gp(8, pr)
-        a_, b_ = gn_ab(N, Ci, 8, *pr)
-        dq = silu_ab(dq, a_[:, :, None], b_[:, :, None])
-    acc = np.broadcast_to(b[None, :, None], (N, Co, S)).astype(f32).copy()
-    for ci in range(Ci):
-        acc = fma(np.broadcast_to(w[None, :, ci, None], acc.shape), np.broadcast_to(dq[:, None, ci, :], acc.shape), acc)
+        dq = orc.gn_silu(dq, N, Ci, S, 8, *pr, 1)
+    acc = orc.conv1(dq, w, b, N, Ci, Co, S).reshape(N, Co, S)
     xd, wd, bd = DevBuf(data=mx), DevBuf(data=w), DevBuf(data=b)
     yd = DevBuf(N * Co * S * (2 if h16 else 4)).fill(0xEE)
     fn = L.lp_conv1_fwd_mx_h16 if h16 else L.lp_conv1_fwd_mx
@@ -121,5 +80,5 @@ def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
     want = acc.astype(np.float16).astype(f32) if h16 else acc
     if gn:
         assert orc.rel_l2(got, want) < 1e-5
-    else:   # bit-equal up to the oracle's own double rounding (see fma above)
-        assert np.count_nonzero(got != want) <= 2 and np.allclose(got, want, rtol=3e-7, atol=1e-9)
+    else:
+        assert np.array_equal(got, want)

@@ -223,3 +223,35 @@ def test_unet_small_runs():
     y = orc.unet_forward(cfg, w, x, 1)
     assert np.isfinite(y).all() and y.std() > 0
     assert np.array_equal(y, orc.unet_forward(cfg, w, x, 1))
+
+
+def test_elementwise_operator_restatements():
+    """orc_up2, orc_conv1, orc_gn_silu against independent float64 evaluations"""
+    r = np.random.default_rng(5)
+    N, Cn, D, H, W = 2, 3, 3, 4, 5
+    S = D * H * W
+    x = r.standard_normal(N * Cn * S).astype(np.float32)
+    # trilinear 2x, align_corners false with clamped edges: the separable float64 form
+    def lin(a, axis):
+        n = a.shape[axis]
+        o = np.arange(2 * n)
+        near, far = o >> 1, np.clip((o >> 1) + np.where(o & 1, 1, -1), 0, n - 1)
+        return 0.75 * np.take(a, near, axis) + 0.25 * np.take(a, far, axis)
+    want = lin(lin(lin(x.reshape(N, Cn, D, H, W).astype(np.float64), 2), 3), 4)
+    got = orc.up2(x, N, Cn, D, H, W).reshape(want.shape)
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
+    assert np.array_equal(orc.up2(np.full(N * Cn * S, 1.5, np.float32), N, Cn, D, H, W), np.full(8 * N * Cn * S, 1.5, np.float32))   # weights sum to one exactly
+    w, b = r.standard_normal((4, Cn)).astype(np.float32), r.standard_normal(4).astype(np.float32)
+    c1 = orc.conv1(x, w, b, N, Cn, 4, S).reshape(N, 4, S)
+    assert np.allclose(c1, np.einsum("oc,ncs->nos", w.astype(np.float64), x.reshape(N, Cn, S).astype(np.float64)) + b[None, :, None], rtol=1e-5, atol=1e-5)
+    Gn = 3
+    gamma, beta = (1 + 0.2 * r.standard_normal(Cn)).astype(np.float32), (0.1 * r.standard_normal(Cn)).astype(np.float32)
+    mean, rstd = (0.3 * r.standard_normal(N * Gn)).astype(np.float32), (0.5 + r.random(N * Gn)).astype(np.float32)
+    u = ((x.reshape(N, Cn, S).astype(np.float64) - mean.reshape(N, Gn, 1)) * rstd.reshape(N, Gn, 1)) * gamma[None, :, None] + beta[None, :, None]
+    silu = u / (1 + np.exp(-u))
+    for form in (0, 1):
+        assert np.allclose(orc.gn_silu(x, N, Cn, S, Gn, gamma, beta, mean, rstd, form).reshape(N, Cn, S), silu, rtol=2e-6, atol=2e-6)
+    # a channel segment of a larger tensor takes the larger tensor's groups and parameters
+    whole = orc.gn_silu(x, N, Cn, S, Gn, gamma, beta, mean, rstd, 1).reshape(N, Cn, S)
+    seg = orc.gn_silu(np.ascontiguousarray(x.reshape(N, Cn, S)[:, 1:]), N, Cn - 1, S, Gn, gamma, beta, mean, rstd, 1, 1, Cn).reshape(N, Cn - 1, S)
+    assert np.array_equal(seg, whole[:, 1:])

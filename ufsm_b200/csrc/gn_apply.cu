@@ -18,9 +18,10 @@ namespace {
    grid (runs of voxels, 32-channel blocks, samples) */
 template <int XK, int BY, int FORM>
 __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ xv, uint8_t *__restrict__ y, int C, int G, size_t S,
-                                                      const float *__restrict__ gamma, const float *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd, int y_split) {
+                                                      const float *__restrict__ gamma, const float *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd, int y_split,
+                                                      int c_off, int cpg) {
     const int N = gridDim.z, nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z, T = gridDim.x;
-    const int q = threadIdx.x & 3, ph = threadIdx.x >> 2, cpg = C / G;
+    const int q = threadIdx.x & 3, ph = threadIdx.x >> 2;
     constexpr int RBY = BY == 8 ? 32 : 16;
     /* per channel: FORM 0 (mean, rstd, gamma, beta) in (k0, k1, k2, k3); FORM 1 (a, b) in (k0, k1) */
     float2 k0[4], k1[4], k2[4], k3[4]; bool live[8];         /* FORM 0: k0 holds -mean */
@@ -30,9 +31,9 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
         float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
         live[k] = c < C;
         if (live[k]) {
-            const int ng = n * G + c / cpg;
-            if (FORM == 0) { t0 = -mean[ng]; t1 = rstd[ng]; t2 = gamma[c]; t3 = beta[c]; }
-            else { t0 = __fmul_rn(rstd[ng], gamma[c]); t1 = __fmaf_rn(-mean[ng], t0, beta[c]); }
+            const int cl = c_off + c, ng = n * G + cl / cpg;       /* cl: the channel's index in the tensor the groups are counted over */
+            if (FORM == 0) { t0 = -mean[ng]; t1 = rstd[ng]; t2 = gamma[cl]; t3 = beta[cl]; }
+            else { t0 = __fmul_rn(rstd[ng], gamma[cl]); t1 = __fmaf_rn(-mean[ng], t0, beta[cl]); }
         }
         if (k & 1) { k0[k >> 1].y = t0; k1[k >> 1].y = t1; k2[k >> 1].y = t2; k3[k >> 1].y = t3; }
         else { k0[k >> 1].x = t0; k1[k >> 1].x = t1; k2[k >> 1].x = t2; k3[k >> 1].x = t3; }
@@ -88,18 +89,21 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
 }
 
 template <int XK, int BY>
-void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, size_t S, const float *gamma, const float *beta, const float *mean, const float *rstd, int y_split) {
-    if (form == 0) gn_silu_rows_k<XK, BY, 0><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split);
-    else gn_silu_rows_k<XK, BY, 1><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split);
+void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, size_t S, const float *gamma, const float *beta, const float *mean, const float *rstd, int y_split, int c_off, int cpg) {
+    if (form == 0) gn_silu_rows_k<XK, BY, 0><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg);
+    else gn_silu_rows_k<XK, BY, 1><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg);
 }
 
 }   // namespace
 
 /* x: xdt 0 (fp32 plane-major), 2 (fp16 plane-major), 3 / 4 (MX, reference layout, 32-wide rows); y: MX of `bits` bits, `layout` as in
-   umx_pm_to_mx32; form 0 / 1 as above.  Returns 0, -1 on an unsupported combination (the caller reports it). */
-int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
-                      void *y, int bits, int layout, int form) {
-    if (C <= 16 || G < 1 || C % G || (bits != 8 && bits != 4) || (xdt != UMX_F32 && xdt != UMX_F16 && xdt != UMX_MX8 && xdt != UMX_MX4)) return -1;
+   umx_pm_to_mx32; form 0 / 1 as above.  The tensor may be a channel segment of a larger one the G groups are counted over (a conv's
+   concat input with one GroupNorm over both parts): its channel 0 is channel c_off of C_all (0, C for a whole tensor); gamma, beta,
+   mean, rstd are the larger tensor's.  Returns 0, -1 on an unsupported combination (the caller reports it). */
+int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                          void *y, int bits, int layout, int form, int c_off, int C_all) {
+    if (C <= 16 || G < 1 || C_all % G || c_off < 0 || c_off + C > C_all || (bits != 8 && bits != 4) || (xdt != UMX_F32 && xdt != UMX_F16 && xdt != UMX_MX8 && xdt != UMX_MX4)) return -1;
+    const int cpg = C_all / G;
     const int nb = (C + 31) / 32;
     if (!N || !S) return 0;
     if (N > 65535 || nb > 65535) return -1;
@@ -108,11 +112,15 @@ int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, con
     const dim3 blocks((unsigned)T, (unsigned)nb, (unsigned)N);
     const int ys = bits == 8 && layout == UMX_LAYOUT_SPLIT;
     uint8_t *yb = (uint8_t *)y;
-#define UMX_GSA(XK) do { if (bits == 8) launch_form<XK, 8>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys); else launch_form<XK, 4>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys); } while (0)
+#define UMX_GSA(XK) do { if (bits == 8) launch_form<XK, 8>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg); else launch_form<XK, 4>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg); } while (0)
     if (xdt == UMX_MX8) UMX_GSA(8); else if (xdt == UMX_MX4) UMX_GSA(4); else if (xdt == UMX_F16) UMX_GSA(2); else UMX_GSA(0);
 #undef UMX_GSA
     g_umx_launches++;
     return 0;
+}
+int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                      void *y, int bits, int layout, int form) {
+    return umx_gn_silu_apply_seg(x, xdt, N, C, S, G, gamma, beta, mean, rstd, y, bits, layout, form, 0, C);
 }
 
 extern "C" void lp_gn_silu_apply_mx(const void *x, int xdt, shape5 s, int G, const float *gamma, const float *beta, const float *mean, const float *rstd, void *y, int ydt) {

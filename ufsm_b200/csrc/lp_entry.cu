@@ -1,6 +1,8 @@
 /* The reference's conv entry points lp_conv_fwd_f8 / lp_conv_fwd_f4 / lp_conv_fwd_s2_f8 (src/nn_lp.h:53-54, 104) on top of the tcgen05
    conv: same signature, storage codes and error behaviour; the prepared weights are memoised under split_t.wkey as the reference's fp4
-   kernel does (src/lp_f4fwd.cuh:748-770). */
+   kernel does (src/lp_f4fwd.cuh:748-770).  Of split_t (src/nn_lp.h:20-37): x2 / c_split / gp2 (concat input), up (the x part stored at
+   half resolution and read as its trilinear upsample), y2 / o_split (split output), stored_stats with osum / Go / zlo / zhi (GroupNorm
+   sums of the stored output); the other fields stop with "not built". */
 #include "mx_common.cuh"
 #include <stdlib.h>
 #include <string.h>
@@ -30,41 +32,185 @@ static const void *gn_input(const char *fn, const void *x, int xbf, shape5 xs, g
 }
 static void not_built(const char *fn, const char *what) { fprintf(stderr, "%s: %s is not built in this library\n", fn, what); abort(); }
 
+/* ---- split_t: concat input, upsampled input segment, split output, output statistics ----
+   These fields are served by composition: the conv's operand tensor is assembled in scratch from its segments, the conv runs on it,
+   and a split output is dealt out of a scratch tensor.  The arithmetic is the reference's (its kernels do the same steps while
+   staging: transform, blend, quantise rows of 32 channels to the MMA's format); the extra passes over memory are the price. */
+int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                          void *y, int bits, int layout, int form, int c_off, int C_all);
+extern "C" void umx_pm_to_mx32_cat(const void *x, const void *x2, int c2, int dt, int N, int C, size_t S, void *y, int bits, int layout);
+static inline int up32(int c) { return (c + 31) / 32 * 32; }
+
+/* blocks [0, nb_src) of every sample of an MX tensor (reference layout) to blocks [b0, b0 + nb_src) of one with nb_dst blocks, or back */
+static void mx_blocks_copy(uint8_t *dst, int nb_dst, int b0, const uint8_t *src, int nb_src, int N, size_t S, int bits, bool gather) {
+    const size_t rb = bits == 8 ? 32 : 16;
+    for (int n = 0; n < N; n++) {
+        uint8_t *dc = dst + ((size_t)n * nb_dst + b0) * S * rb, *ds = dst + (size_t)N * nb_dst * S * rb + ((size_t)n * nb_dst + b0) * S;
+        const uint8_t *sc = src + (size_t)n * nb_src * S * rb, *ss = src + (size_t)N * nb_src * S * rb + (size_t)n * nb_src * S;
+        if (gather) {          /* dst is the small tensor */
+            cudaMemcpyAsync((uint8_t *)sc, dc, (size_t)nb_src * S * rb, cudaMemcpyDeviceToDevice, 0);
+            cudaMemcpyAsync((uint8_t *)ss, ds, (size_t)nb_src * S, cudaMemcpyDeviceToDevice, 0);
+        } else {
+            cudaMemcpyAsync(dc, sc, (size_t)nb_src * S * rb, cudaMemcpyDeviceToDevice, 0);
+            cudaMemcpyAsync(ds, ss, (size_t)nb_src * S, cudaMemcpyDeviceToDevice, 0);
+        }
+    }
+}
+/* weights [co][ci][taps] and bias of the logical conv -> those of the conv on padded segments: input channel ci sits at ci (ci < cx) or
+   cxp + ci - cx, output channel co at co (co < ox) or oxp + co - ox; rows and columns of the padding are zero */
+__global__ void w_expand_k(const float *__restrict__ w, const float *__restrict__ b, float *__restrict__ wp, float *__restrict__ bp,
+                           int co_n, int ci_n, int taps, int cx, int cxp, int cip, int ox, int oxp, int cop) {
+    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x, n = (size_t)cop * cip * taps;
+    if (i < (size_t)cop) { const int p = (int)i, co = p < oxp ? (p < ox ? p : -1) : ox + p - oxp; bp[i] = (b && co >= 0 && co < co_n) ? b[co] : 0.f; }
+    if (i >= n) return;
+    const int t = (int)(i % taps), pi = (int)((i / taps) % cip), po = (int)(i / ((size_t)taps * cip));
+    const int ci = pi < cxp ? (pi < cx ? pi : -1) : cx + pi - cxp, co = po < oxp ? (po < ox ? po : -1) : ox + po - oxp;
+    wp[i] = (ci >= 0 && ci < ci_n && co >= 0 && co < co_n) ? w[((size_t)co * ci_n + ci) * taps + t] : 0.f;
+}
+
 static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
     if (!umx_ready(fn)) return 0;
-    if (osum || Go) not_built(fn, "output GroupNorm statistics (osum)");
-    if (sp.x2 || sp.y2 || sp.accum || sp.gp2.G || sp.up || sp.yD || sp.sr || sp.osr || sp.zlo || sp.zhi || sp.stored_stats || sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yzo || sp.c_split || sp.o_split || sp.o_pad)
-        not_built(fn, "a non-zero split_t field other than wkey");
-    if (xs.c <= 16) not_built(fn, "an input of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (sp.accum || sp.yD || sp.sr || sp.osr || sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yzo || sp.o_pad)
+        not_built(fn, "split_t.accum / sr / osr / zi0 / Di / zw0 / zw1 / yD / yzo / o_pad");
+    if (gp.G && (gp.ns > 1 || gp.zs || gp.zo || gp.zhw)) not_built(fn, "slab-local GroupNorm (gnp_t.ns / zs / zo / zhw)");
+    if (sp.gp2.G && (sp.gp2.ns > 1 || sp.gp2.zs || sp.gp2.zo || sp.gp2.zhw)) not_built(fn, "slab-local GroupNorm (split_t.gp2)");
+    if (sp.up && !sp.x2) { fprintf(stderr, "%s: split_t.up without x2\n", fn); abort(); }
+    if (sp.gp2.G && !sp.x2) { fprintf(stderr, "%s: split_t.gp2 without x2\n", fn); abort(); }
     const int mxin = bits == 8 ? UMX_MX8 : UMX_MX4;
-    if (!gp.G && xbf != UMX_F16 && xbf != mxin) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX-fp%d)\n", fn, xbf, bits); abort(); }
+    const bool x_mx = xbf == UMX_MX8 || xbf == UMX_MX4;
+    const int xb_bits = xbf == UMX_MX8 ? 8 : 4;
+    const int Ci = xs.c, Cx = sp.x2 ? sp.c_split : Ci, C2 = Ci - Cx;
+    if (sp.x2 && (Cx < 1 || C2 < 1)) { fprintf(stderr, "%s: c_split %d of %d input channels\n", fn, Cx, Ci); abort(); }
+    if (Ci <= 16 || (x_mx && sp.x2 && (Cx <= 16 || C2 <= 16))) not_built(fn, "an input (segment) of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (xbf != UMX_F16 && !x_mx) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX)\n", fn, xbf); abort(); }
+    const bool any_gn = gp.G || sp.gp2.G;
+    if (!any_gn && !sp.up && x_mx && xbf != mxin) { fprintf(stderr, "%s: an MX-fp%d input of an MX-fp%d conv needs a transform that requantises it\n", fn, xb_bits, bits); abort(); }
+    if (sp.up && (!x_mx || ((xs.d | xs.h | xs.w) & 1))) not_built(fn, "split_t.up of a plane-major tensor or onto an odd grid");
     int out_mode, out_bits = 0;
     if (ybf == UMX_F16) out_mode = UMX_OUT_PM16;
     else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; if (cout <= 16) not_built(fn, "an MX output of 16 channels or fewer"); }
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
-    const size_t S = (size_t)xs.d * xs.h * xs.w;
-    const void *xq = x;
-    if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, bits); if (!xq) return 0; xbf = UMX_F16; /* = already quantised into the split layout */ }
-    else if (xbf == UMX_F16) {
-        void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, xs.c, S));
-        if (!ws) return 0;
-        umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, bits, UMX_LAYOUT_SPLIT);
-        xq = ws;
+    const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
+    if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
+    if (sp.y2 && out_mode == UMX_OUT_H16B) not_built(fn, "a split output in blocked fp16");
+    if (sp.y2 && out_mode == UMX_OUT_MXRAW && (Ox <= 16 || O2 <= 16)) not_built(fn, "a split MX output with a part of 16 channels or fewer");
+    if (osum || Go) {
+        if (!osum || Go < 1) { fprintf(stderr, "%s: osum %p with %d groups\n", fn, (void *)osum, Go); abort(); }
+        if (out_mode != UMX_OUT_MXRAW || !sp.stored_stats) not_built(fn, "output statistics of the unrounded accumulators (osum needs an MX output and split_t.stored_stats)");
+        if (sp.y2) not_built(fn, "output statistics of a split output");
+        if (Go > 64 || cout % Go) { fprintf(stderr, "%s: %d output channels in %d groups\n", fn, cout, Go); abort(); }
     }
+    const size_t S = (size_t)xs.d * xs.h * xs.w;
+    if (!S || !xs.n) return 0;
+
+    /* ---- the operand tensor ---- */
+    const void *xq = x; int cin = Ci, xflags = 0;
+    const bool s2g = sp.x2 && sp.gp2.G;                       /* a GroupNorm per segment; otherwise gp counts its groups over all Ci channels */
+    if (!sp.x2) {
+        if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, bits); if (!xq) return 0; xflags = UMX_X_SPLIT; }
+        else if (xbf == UMX_F16) {
+            void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, Ci, S));
+            if (!ws) return 0;
+            umx_pm_to_mx32(x, UMX_F16, xs.n, Ci, S, ws, bits, UMX_LAYOUT_SPLIT);
+            xq = ws; xflags = UMX_X_SPLIT;
+        }
+    } else if (!x_mx && !any_gn) {                             /* two plane-major tensors: quantised in one pass, blocks over the concatenated index */
+        void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, Ci, S));
+        if (!ws) return 0;
+        umx_pm_to_mx32_cat(x, sp.x2, Cx, UMX_F16, xs.n, Ci, S, ws, bits, UMX_LAYOUT_SPLIT);
+        xq = ws; xflags = UMX_X_SPLIT;
+    } else {
+        /* segment by segment into an MX tensor of the conv's format (reference layout).  MX segments keep their own 32-channel blocks,
+           the x part padded to whole blocks (the reference's "per-tensor 32-channel segments", src/lp_f8fwd.cuh:617-623) */
+        if (!x_mx && (Cx & 31)) not_built(fn, "a GroupNorm transform of plane-major concat inputs split inside a 32-channel block");
+        const int CxP = up32(Cx), nbA = CxP / 32, nbB = up32(C2) / 32, nbT = nbA + nbB;
+        cin = nbT * 32;
+        uint8_t *T = (uint8_t *)umx_ws(6, umx_mx_bytes32(bits, xs.n, cin, S));
+        if (!T) return 0;
+        for (int seg = 0; seg < 2; seg++) {
+            const void *src = seg ? sp.x2 : x;
+            const int C = seg ? C2 : Cx, nbs = seg ? nbB : nbA, b0 = seg ? nbA : 0;
+            const gnp_t q = s2g ? (seg ? sp.gp2 : gp) : gp;
+            const int c_off = s2g ? 0 : (seg ? Cx : 0), C_all = s2g ? C : Ci;
+            const bool up = !seg && sp.up;
+            const uint8_t *blocks = nullptr;
+            if (up) {
+                if (q.G && !s2g) not_built(fn, "split_t.up with one GroupNorm over both input parts");
+                uint8_t *t = (uint8_t *)umx_ws(3, umx_mx_bytes32(bits, xs.n, C, S));
+                if (!t) return 0;
+                const shape5 cs = {xs.n, C, xs.d / 2, xs.h / 2, xs.w / 2};
+                lp_up2_fwd_mx(src, xbf, cs, t, mxin, q);        /* silu(gn(coarse)) blended, quantised to the conv's rows */
+                blocks = t;
+            } else if (q.G) {
+                uint8_t *t = (uint8_t *)umx_ws(3 + seg, umx_mx_bytes32(bits, xs.n, C, S));
+                if (!t) return 0;
+                if (umx_gn_silu_apply_seg(src, xbf, xs.n, C, S, q.G, q.gamma, q.beta, q.mean, q.rstd, t, bits, UMX_LAYOUT_REF, 1, c_off, C_all) != 0) {
+                    fprintf(stderr, "%s: the GroupNorm + SiLU input transform of a storage-%d segment of %d channels (%d groups over %d) is not built in this library\n", fn, xbf, C, q.G, C_all); abort();
+                }
+                blocks = t;
+            } else if (x_mx) {
+                if (xbf != mxin) { fprintf(stderr, "%s: an MX-fp%d input segment of an MX-fp%d conv without a transform\n", fn, xb_bits, bits); abort(); }
+                blocks = (const uint8_t *)src;
+            } else {
+                uint8_t *t = (uint8_t *)umx_ws(3 + seg, umx_mx_bytes32(bits, xs.n, C, S));
+                if (!t) return 0;
+                umx_pm_to_mx32(src, UMX_F16, xs.n, C, S, t, bits, UMX_LAYOUT_REF);
+                blocks = t;
+            }
+            mx_blocks_copy(T, nbT, b0, blocks, nbs, xs.n, S, bits, false);
+        }
+        xq = T;
+    }
+
+    /* ---- the conv on padded segments where a segment does not end on a block ---- */
+    const bool pad_in = sp.x2 && cin != Ci, mx_split_out = sp.y2 && out_mode == UMX_OUT_MXRAW, pad_out = mx_split_out && (Ox & 31);
+    const int OxP = pad_out ? up32(Ox) : Ox, cout_c = pad_out ? OxP + O2 : cout;
     int dev = 0; cudaGetDevice(&dev);
     umx_conv *c = nullptr; bool temp = true;
     if (sp.wkey) {
-        for (int i = 0; i < g_nmemo; i++) { memo_t &m = g_memo[i]; if (m.wkey == sp.wkey && m.w == w && m.b == b && m.cout == cout && m.cin == xs.c && m.bits == bits && m.dev == dev) { c = m.c; break; } }
+        for (int i = 0; i < g_nmemo; i++) { memo_t &m = g_memo[i]; if (m.wkey == sp.wkey && m.w == w && m.b == b && m.cout == cout_c && m.cin == cin && m.bits == bits && m.dev == dev) { c = m.c; break; } }
         temp = false;
     }
     if (!c) {
-        c = umx_conv_create_dev(UMX_CONV3, w, b, cout, xs.c, bits);
+        const float *wc = w, *bc = b;
+        if (pad_in || pad_out) {
+            const size_t nw = (size_t)cout_c * cin * 27;
+            float *wp = (float *)umx_ws(5, (nw + cout_c) * sizeof(float));     /* slot 5 is also the general kernel's K-split scratch: the weights are prepared (and the stream drained) before a launch asks for it */
+            if (!wp) return 0;
+            w_expand_k<<<(unsigned)((nw + 255) / 256), 256>>>(w, b, wp, wp + nw, cout, Ci, 27, pad_in ? Cx : Ci, pad_in ? up32(Cx) : Ci, cin, Ox, OxP, cout_c);
+            wc = wp; bc = wp + nw;
+        }
+        c = umx_conv_create_dev(UMX_CONV3, wc, bc, cout_c, cin, bits);
         if (!c) return 0;
-        if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout, xs.c, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
+        if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout_c, cin, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
     }
-    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xbf == UMX_F16 ? UMX_X_SPLIT : 0);   /* MX tensors of the reference interface keep the reference layout */
+    if (!sp.y2) {
+        umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xflags);   /* MX tensors of the reference interface keep the reference layout */
+    } else if (out_mode == UMX_OUT_PM16) {
+        __half *t = (__half *)umx_ws(4, (size_t)xs.n * cout * S * 2);
+        if (!t) return 0;
+        umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, t, out_mode, 0, 0, 0, nullptr, xflags);
+        for (int n = 0; n < xs.n; n++) {
+            cudaMemcpyAsync((__half *)y + (size_t)n * Ox * S, t + (size_t)n * cout * S, (size_t)Ox * S * 2, cudaMemcpyDeviceToDevice, 0);
+            cudaMemcpyAsync((__half *)sp.y2 + (size_t)n * O2 * S, t + ((size_t)n * cout + Ox) * S, (size_t)O2 * S * 2, cudaMemcpyDeviceToDevice, 0);
+        }
+    } else {
+        const int nb1 = up32(Ox) / 32, nb2 = up32(O2) / 32;
+        uint8_t *t = (uint8_t *)umx_ws(4, umx_mx_bytes32(out_bits, xs.n, (nb1 + nb2) * 32, S));
+        if (!t) return 0;
+        umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, t, out_mode, out_bits, 0, 0, nullptr, xflags);
+        mx_blocks_copy(t, nb1 + nb2, 0, (const uint8_t *)y, nb1, xs.n, S, out_bits, true);
+        mx_blocks_copy(t, nb1 + nb2, nb1, (const uint8_t *)sp.y2, nb2, xs.n, S, out_bits, true);
+    }
+    if (osum) {
+        /* statistics of the stored values (split_t.stored_stats) over the planes [zlo, D - zhi): exact sums into the caller's slots */
+        const size_t hw = (size_t)xs.h * xs.w, v0 = (size_t)sp.zlo * hw, v1 = S - (size_t)sp.zhi * hw;
+        if (sp.zlo < 0 || sp.zhi < 0 || sp.zlo + sp.zhi > xs.d) { fprintf(stderr, "%s: zlo %d + zhi %d of %d planes\n", fn, sp.zlo, sp.zhi, xs.d); abort(); }
+        if (lp_gn_sums_mx(y, ybf, xs.n, cout, Go, S, osum, v0, v1) != 0) { fprintf(stderr, "%s: output statistics of %d channels in %d groups\n", fn, cout, Go); abort(); }
+    }
     if (temp) { cudaDeviceSynchronize(); umx_conv_free(c); }
+    UMX_CK(fn);
     return 0;
 }
 extern "C" int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {

@@ -5,29 +5,33 @@
    contiguous run of rows (32 x 32 B or 32 x 16 B) plus 32 contiguous scale bytes.  Algorithmic bytes per element: read 4 or 2,
    write 1 + 1/32 (fp8) or 1/2 + 1/32 (fp4).  Semantics: src/lp_mx_cvt.cu:9-19, src/lp_mxops.cuh:46-68 of the reference. */
 #include "mx_common.cuh"
+#include <cuda_bf16.h>
 
 __host__ __device__ static inline int mxbw(int C, int force) { return force > 0 ? force : C <= 8 ? 8 : C <= 16 ? 16 : 32; }
 
 template <typename T> __device__ __forceinline__ float ld_as_f32(const T *p);
 template <> __device__ __forceinline__ float ld_as_f32<float>(const float *p) { return __ldg(p); }
 template <> __device__ __forceinline__ float ld_as_f32<__half>(const __half *p) { return __half2float(__ldg(p)); }
+template <> __device__ __forceinline__ float ld_as_f32<__nv_bfloat16>(const __nv_bfloat16 *p) { return __uint_as_float((unsigned)__ldg((const unsigned short *)p) << 16); }
 
 /* grid = (voxel chunks, blocks, samples): no index division per row; consecutive threads take consecutive voxels, so the plane-major
-   reads and the row writes are both coalesced */
+   reads and the row writes are both coalesced.  Channels from c2 on come from a second tensor x2 of C - c2 channels (a conv's concat
+   input, split_t.x2 / c_split of the reference: the 32-channel blocks run over the concatenated index); c2 = C without one. */
 template <int BITS, typename TI>
-__global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw, int split) {
+__global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint8_t *__restrict__ y, int N, int C, size_t S, int bw, int split, const TI *__restrict__ x2, int c2) {
     pdl_trigger(); pdl_wait();
     const int nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z, rb = bw * BITS / 8;
     const size_t rows = (size_t)N * nb * S, row0 = ((size_t)n * nb + blk) * S;
     uint8_t *sc = y + rows * rb;
-    const TI *xb = x + ((size_t)n * C + (size_t)blk * bw) * S;
-    const int nch = min(bw, C - blk * bw);
+    const TI *xb = x + ((size_t)n * c2 + (size_t)blk * bw) * S;                       /* channel k of the block: xb + k S while blk bw + k < c2 */
+    const TI *xb2 = x2 ? x2 + ((ptrdiff_t)n * (C - c2) + (ptrdiff_t)blk * bw - c2) * (ptrdiff_t)S : nullptr;   /* and xb2 + k S from there on */
+    const int nch = min(bw, C - blk * bw), k2 = c2 - blk * bw;
     for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v < S; v += (size_t)gridDim.x * blockDim.x) {
         const size_t i = row0 + v;
         unsigned w[8]; unsigned sb;
         if (nch == 1) {
             /* a block with one real channel (a one-channel stem): the same bytes as the general path, without the 31 zero lanes */
-            const float x0 = ld_as_f32(xb + v);
+            const float x0 = ld_as_f32((0 < k2 ? xb : xb2) + v);
             const int e = mx_exp(__uint_as_float(__float_as_uint(x0) & 0x7fffffffu), BITS == 4 ? 1.f / 6.f : 1.f / 448.f);
             const float m = exp2i(-e);
             sb = (unsigned)(e + 127) & 0xffu;
@@ -39,7 +43,7 @@ __global__ void __launch_bounds__(256) pm_to_mx_k(const TI *__restrict__ x, uint
         } else {
             float r[32];
 #pragma unroll
-            for (int k = 0; k < 32; k++) r[k] = k < nch ? ld_as_f32(xb + (size_t)k * S + v) : 0.f;
+            for (int k = 0; k < 32; k++) r[k] = k < nch ? ld_as_f32((k < k2 ? xb : xb2) + (ptrdiff_t)k * (ptrdiff_t)S + v) : 0.f;
             sb = mx_encode_row32<BITS>(r, w);
         }
         uint8_t *p = y + i * rb;
@@ -85,16 +89,19 @@ __global__ void __launch_bounds__(256) h16b_to_pm_k(const __half *__restrict__ x
 
 static unsigned grid_for(size_t rows) { size_t g = (rows + 255) / 256; return (unsigned)(g > 148u * 64u ? 148u * 64u : g ? g : 1); }
 
-static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int bwf, const char *who, int split = 0) {
+static void to_mx(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int bwf, const char *who, int split = 0, const void *x2 = nullptr, int c2 = 0) {
     if (!umx_ready(who)) return;
-    if (dt != 0 && dt != 2) { fprintf(stderr, "%s: source type %d is not built (fp32 and fp16 only)\n", who, dt); abort(); }
+    if (dt != 0 && dt != 1 && dt != 2) { fprintf(stderr, "%s: source type %d is not built (fp32, bf16 and fp16 only)\n", who, dt); abort(); }
+    if (!x2) c2 = C;
     const int bw = mxbw(C, bwf);
     const int nb = (C + bw - 1) / bw;
     if (!S || !N) return;
     size_t gx = (S + 255) / 256; if (gx > 148u * 16u) gx = 148u * 16u;
     const dim3 g((unsigned)gx, (unsigned)nb, (unsigned)N);
-    if (bits == 8) { if (dt == 2) umx_launch(pm_to_mx_k<8, __half>, g, dim3(256), 0, (const __half *)x, (uint8_t *)y, N, C, S, bw, split); else umx_launch(pm_to_mx_k<8, float>, g, dim3(256), 0, (const float *)x, (uint8_t *)y, N, C, S, bw, split); }
-    else { if (dt == 2) umx_launch(pm_to_mx_k<4, __half>, g, dim3(256), 0, (const __half *)x, (uint8_t *)y, N, C, S, bw, split); else umx_launch(pm_to_mx_k<4, float>, g, dim3(256), 0, (const float *)x, (uint8_t *)y, N, C, S, bw, split); }
+#define UMX_Q(B, T) umx_launch(pm_to_mx_k<B, T>, g, dim3(256), 0, (const T *)x, (uint8_t *)y, N, C, S, bw, split, (const T *)x2, c2)
+    if (bits == 8) { if (dt == 2) UMX_Q(8, __half); else if (dt == 1) UMX_Q(8, __nv_bfloat16); else UMX_Q(8, float); }
+    else { if (dt == 2) UMX_Q(4, __half); else if (dt == 1) UMX_Q(4, __nv_bfloat16); else UMX_Q(4, float); }
+#undef UMX_Q
     g_umx_launches++;
     UMX_CK(who);
 }
@@ -117,6 +124,11 @@ extern "C" void lp_h16_to_mx4(const void *x, int dt, int N, int C, size_t S, voi
 extern "C" void lp_mx8_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 8, 0, "lp_mx8_to_f32"); }
 extern "C" void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y) { from_mx(x, N, C, S, y, 4, 0, "lp_mx4_to_f32"); }
 extern "C" void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout) { to_mx(x, dt, N, C, S, y, bits, 32, "umx_pm_to_mx32", layout == UMX_LAYOUT_SPLIT && bits == 8); }
+/* the same from two tensors: channels [0, c2) of the C from x, the rest from x2 */
+extern "C" void umx_pm_to_mx32_cat(const void *x, const void *x2, int c2, int dt, int N, int C, size_t S, void *y, int bits, int layout) {
+    if (x2 && (c2 < 1 || c2 >= C)) { fprintf(stderr, "umx_pm_to_mx32_cat: split at channel %d of %d\n", c2, C); abort(); }
+    to_mx(x, dt, N, C, S, y, bits, 32, "umx_pm_to_mx32_cat", layout == UMX_LAYOUT_SPLIT && bits == 8, x2, c2);
+}
 extern "C" void umx_mx32_to_f32(const void *x, int bits, int N, int C, size_t S, float *y, int layout) { from_mx(x, N, C, S, y, bits, 32, "umx_mx32_to_f32", layout == UMX_LAYOUT_SPLIT && bits == 8); }
 extern "C" void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y) {
     if (!umx_ready("umx_h16b_to_f32")) return;
