@@ -81,6 +81,14 @@ void lp_mx4_to_f32(const void *x, int N, int C, size_t S, float *y);
 /* the same quantiser with 32-wide blocks whatever C (padding channels zero): the form the graph below keeps its tensors in */
 size_t umx_mx_bytes32(int bits, int N, int C, size_t S);
 void umx_pm_to_mx32(const void *x, int dt, int N, int C, size_t S, void *y, int bits, int layout);   /* dt 0 fp32 / 1 bf16 / 2 fp16 plane-major */
+/* an MX tensor of C <= 16 channels (rows of 8 or 16 channels, src/lp_common.cuh:132-134) as the same tensor with 32-wide rows
+   (to_wide) or back: the same codes and scale bytes, zeros behind them */
+void umx_mx_rewidth(const void *x, int bits, int N, int C, size_t S, void *y, int to_wide);
+/* src/nn_lp.h:164-165, src/lp_mx_cvt.cu:20-57: the network input of the reference's predict for planes [z0, z0 + nz) of a W x W CT
+   window (device pointers): channel 0 (ct - mean) isd, 1 zero, 2 / 3 the unit (dy, dx) away from the scroll axis at (-dyo[z], -dxo[z])
+   times axis (0: none), rounded to hd (2 fp16, 1 bf16, 0 fp32), stored as an MX tensor of 4 channels (8-wide rows) and depth nz */
+void lp_pred_input_mx(const uint8_t *ct, int W, float mean, float isd, const float *dyo, const float *dxo, int axis, int z0, int nz, void *y, int hd, int bits);
+void lp_pred_input_mx8(const uint8_t *ct, int W, float mean, float isd, const float *dyo, const float *dxo, int axis, int z0, int nz, void *y, int hd);
 /* the same from two tensors, channels [0, c2) of the C from x and the rest from x2 (the concat input of split_t.x2 / c_split,
    src/nn_lp.h:20: rows of 32 channels over the concatenated index); x2 NULL: one tensor */
 void umx_pm_to_mx32_cat(const void *x, const void *x2, int c2, int dt, int N, int C, size_t S, void *y, int bits, int layout);

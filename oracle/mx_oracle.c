@@ -658,3 +658,29 @@ void orc_conv1(const float *x, const float *w, const float *b, int N, int Ci, in
             }
         }
 }
+
+/* The network input of the reference's predict (pred_in_mx_k, src/lp_mx_cvt.cu:29-41) before its MX rows: out [4][nz W W] plane-major,
+   channel 0 the z-scored CT byte, 1 zero, 2 and 3 the unit direction (dy, dx) away from the scroll axis times `axis`, each rounded to
+   the 16-bit input type (hd 2 fp16, 1 bf16, 0 none).  The radius is sqrtf(fmaf(dy, dy, dx dx)) + 1e-6f. */
+static float round16(float v, int hd) {
+    if (hd == 2) return (float)(h16)v;
+    if (hd == 1) { uint32_t u; memcpy(&u, &v, 4); if ((u & 0x7fffffffu) > 0x7f800000u) u |= 0x00400000u; else u += 0x7fffu + ((u >> 16) & 1u); u &= 0xffff0000u; memcpy(&v, &u, 4); return v; }
+    return v;
+}
+void orc_pred_input(const uint8_t *ct, int W, float mean, float isd, const float *dyo, const float *dxo, int axis, int z0, int nz, int hd, float *out) {
+    const size_t S = (size_t)nz * W * W;
+#pragma omp parallel for schedule(static)
+    for (int zi = 0; zi < nz; zi++) {
+        const int z = z0 + zi;
+        for (int yy = 0; yy < W; yy++)
+            for (int xx = 0; xx < W; xx++) {
+                const size_t i = ((size_t)zi * W + yy) * W + xx;
+                const float dy = dyo[z] + (float)yy, dx = dxo[z] + (float)xx;
+                const float inv = axis ? (float)axis / (sqrtf(fmaf(dy, dy, dx * dx)) + 1e-6f) : 0.f;
+                out[i] = round16(((float)ct[(size_t)z * W * W + (size_t)yy * W + xx] - mean) * isd, hd);
+                out[S + i] = 0.f;
+                out[2 * S + i] = round16(dy * inv, hd);
+                out[3 * S + i] = round16(dx * inv, hd);
+            }
+    }
+}

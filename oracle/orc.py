@@ -266,6 +266,15 @@ def conv1(x, w, b, N, Ci, Co, S):
     return y
 
 
+def pred_input(ct, W, mean, isd, dyo, dxo, axis, z0, nz, hd):
+    """the predict network input of planes [z0, z0 + nz): flat fp32 [4][nz W W]"""
+    ct = np.ascontiguousarray(ct, dtype=np.uint8)
+    dyo, dxo = f32(dyo), f32(dxo)
+    out = np.empty(4 * nz * W * W, np.float32)
+    o().orc_pred_input(_p(ct), W, C.c_float(mean), C.c_float(isd), _p(dyo), _p(dxo), axis, z0, nz, hd, _p(out))
+    return out
+
+
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

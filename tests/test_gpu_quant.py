@@ -31,6 +31,17 @@ def test_f32_to_mx(dev, bits, N, Cn, S):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
+def test_bf16_source(dev, bits):
+    """lp_h16_to_mx8 / 4 with dt 1 (bf16 plane-major, src/nn_lp.h:113-116): a bf16 value is the fp32 value with the same upper 16 bits"""
+    N, Cn, S = 2, 40, 1500
+    x = edge_values(N * Cn * S)
+    hi = (x.view(np.uint32) >> 16).astype(np.uint16)                  # truncation is as good as any rounding for making test inputs
+    xf = (hi.astype(np.uint32) << 16).view(np.float32)
+    got = G.quantise_pm(hi, 1, N, Cn, S, bits)
+    assert np.array_equal(got, orc.pm_to_mx(xf, 0, N, Cn, S, bits))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
 def test_h16_to_mx_and_back(dev, bits):
     N, Cn, S = 1, 32, 32 ** 3
     x = synth.act_h16(1, N * Cn * S)

@@ -68,6 +68,9 @@ _SIG = {
     "lp_mx4_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, C.c_void_p]),
     "umx_mx_bytes32": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_size_t]),
     "umx_pm_to_mx32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int, C.c_int]),
+    "umx_mx_rewidth": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
+    "lp_pred_input_mx": (None, [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int]),
+    "lp_pred_input_mx8": (None, [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "umx_pm_to_mx32_cat": (None, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int, C.c_int]),
     "umx_mx_relayout": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),
     "umx_mx32_to_f32": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_int]),

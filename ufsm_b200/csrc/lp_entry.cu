@@ -68,6 +68,9 @@ __global__ void w_expand_k(const float *__restrict__ w, const float *__restrict_
     wp[i] = (ci >= 0 && ci < ci_n && co >= 0 && co < co_n) ? w[((size_t)co * ci_n + ci) * taps + t] : 0.f;
 }
 
+extern "C" void umx_mx_rewidth(const void *x, int bits, int N, int C, size_t S, void *y, int to_wide);
+static inline bool any_gn_(const gnp_t &gp, const split_t &sp) { return gp.G || sp.gp2.G; }
+
 static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
     if (!umx_ready(fn)) return 0;
     if (sp.accum || sp.yD || sp.sr || sp.osr || sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yzo || sp.o_pad)
@@ -81,16 +84,19 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     const int xb_bits = xbf == UMX_MX8 ? 8 : 4;
     const int Ci = xs.c, Cx = sp.x2 ? sp.c_split : Ci, C2 = Ci - Cx;
     if (sp.x2 && (Cx < 1 || C2 < 1)) { fprintf(stderr, "%s: c_split %d of %d input channels\n", fn, Cx, Ci); abort(); }
-    if (Ci <= 16 || (x_mx && sp.x2 && (Cx <= 16 || C2 <= 16))) not_built(fn, "an input (segment) of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (sp.x2 && x_mx && (Cx <= 16 || C2 <= 16)) not_built(fn, "a concat input with a part of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (Ci <= 16 && any_gn_(gp, sp)) not_built(fn, "a GroupNorm transform of an input of 16 channels or fewer");
     if (xbf != UMX_F16 && !x_mx) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX)\n", fn, xbf); abort(); }
     const bool any_gn = gp.G || sp.gp2.G;
     if (!any_gn && !sp.up && x_mx && xbf != mxin) { fprintf(stderr, "%s: an MX-fp%d input of an MX-fp%d conv needs a transform that requantises it\n", fn, xb_bits, bits); abort(); }
     if (sp.up && (!x_mx || ((xs.d | xs.h | xs.w) & 1))) not_built(fn, "split_t.up of a plane-major tensor or onto an odd grid");
     int out_mode, out_bits = 0;
     if (ybf == UMX_F16) out_mode = UMX_OUT_PM16;
-    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; if (cout <= 16) not_built(fn, "an MX output of 16 channels or fewer"); }
+    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; }
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
+    const bool narrow_out = out_mode == UMX_OUT_MXRAW && cout <= 16;      /* rows of 8 / 16 channels: written 32 wide into scratch, then narrowed */
+    if (narrow_out && (sp.y2 || osum)) not_built(fn, "a split output or output statistics with 16 output channels or fewer");
     const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
     if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
     if (sp.y2 && out_mode == UMX_OUT_H16B) not_built(fn, "a split output in blocked fp16");
@@ -108,7 +114,12 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     const void *xq = x; int cin = Ci, xflags = 0;
     const bool s2g = sp.x2 && sp.gp2.G;                       /* a GroupNorm per segment; otherwise gp counts its groups over all Ci channels */
     if (!sp.x2) {
-        if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, bits); if (!xq) return 0; xflags = UMX_X_SPLIT; }
+        if (x_mx && Ci <= 16) {                                /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
+            void *ws = umx_ws(3, umx_mx_bytes32(bits, xs.n, Ci, S));
+            if (!ws) return 0;
+            umx_mx_rewidth(x, bits, xs.n, Ci, S, ws, 1);
+            xq = ws;
+        } else if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, bits); if (!xq) return 0; xflags = UMX_X_SPLIT; }
         else if (xbf == UMX_F16) {
             void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, Ci, S));
             if (!ws) return 0;
@@ -185,7 +196,12 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         if (!c) return 0;
         if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout_c, cin, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
     }
-    if (!sp.y2) {
+    if (narrow_out) {
+        void *t = umx_ws(4, umx_mx_bytes32(out_bits, xs.n, cout, S));
+        if (!t) return 0;
+        umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, t, out_mode, out_bits, 0, 0, nullptr, xflags);
+        umx_mx_rewidth(t, out_bits, xs.n, cout, S, y, 0);
+    } else if (!sp.y2) {
         umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xflags);   /* MX tensors of the reference interface keep the reference layout */
     } else if (out_mode == UMX_OUT_PM16) {
         __half *t = (__half *)umx_ws(4, (size_t)xs.n * cout * S * 2);

@@ -153,3 +153,69 @@ extern "C" void umx_mx_relayout(const void *src, int bits, int N, int C, size_t 
     cudaMemcpyAsync((uint8_t *)dst + rows * rb, (const uint8_t *)src + rows * rb, rows, cudaMemcpyDeviceToDevice, 0);
     UMX_CK("umx_mx_relayout");
 }
+
+/* MX tensors of 16 channels or fewer keep rows of 8 or 16 channels in the reference's storage (src/lp_common.cuh:132-134).  Such a row
+   and the 32-wide row holding the same channels followed by zeros have the same amax, hence the same scale byte and the same codes:
+   widening and narrowing are copies.  One thread per row. */
+__global__ void __launch_bounds__(256) mx_rewidth_k(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t rows, int rb_src, int rb_dst) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned *s = (const unsigned *)(src + i * rb_src); unsigned *d = (unsigned *)(dst + i * rb_dst);
+        for (int k = 0; k < rb_dst / 4; k++) d[k] = k < rb_src / 4 ? __ldg(s + k) : 0u;
+        dst[rows * rb_dst + i] = __ldg(src + rows * rb_src + i);
+    }
+}
+/* x: an MX tensor of C <= 16 channels (one block of 8 or 16 a voxel) -> y: the same tensor with 32-wide rows (to_wide), or back */
+extern "C" void umx_mx_rewidth(const void *x, int bits, int N, int C, size_t S, void *y, int to_wide) {
+    if (!umx_ready("umx_mx_rewidth")) return;
+    if (C < 1 || C > 16 || (bits != 8 && bits != 4)) { fprintf(stderr, "umx_mx_rewidth: %d channels, %d bits\n", C, bits); abort(); }
+    const int bw = mxbw(C, 0), rn = bw * bits / 8, r32 = 32 * bits / 8;
+    const size_t rows = (size_t)N * S;
+    if (!rows) return;
+    mx_rewidth_k<<<grid_for(rows), 256>>>((const uint8_t *)x, (uint8_t *)y, rows, to_wide ? rn : r32, to_wide ? r32 : rn);
+    g_umx_launches++;
+    UMX_CK("umx_mx_rewidth");
+}
+
+/* lp_pred_input_mx (src/nn_lp.h:164-165, src/lp_mx_cvt.cu:20-57): the network input of the reference's predict for window planes
+   [z0, z0 + nz) of a W x W x depth CT window: channel 0 the z-scored CT byte, 1 zero, 2 and 3 the unit direction away from the scroll
+   axis (dy, dx) (axis 0: zeros; -1 flips it), each rounded to the 16-bit input type (hd 2 fp16, 1 bf16, 0 none), stored as MX rows of
+   one 8-channel block.  The radius is sqrt(fma(dy, dy, dx dx)) + 1e-6: the contraction a compiler picks for dy dy + dx dx, spelled out. */
+template <int HD> __device__ __forceinline__ float round16(float v) {
+    if (HD == 2) return __half2float(__float2half_rn(v));
+    if (HD == 1) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+template <int BITS, int HD>
+__global__ void __launch_bounds__(256) pred_input_k(const uint8_t *__restrict__ ct, int W, float mean, float isd, const float *__restrict__ dyo, const float *__restrict__ dxo,
+                                                    int axis, int z0, int nz, uint8_t *__restrict__ y) {
+    const size_t S = (size_t)nz * W * W, i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i >= S) return;
+    const int xx = (int)(i % W), yy = (int)((i / W) % W), z = z0 + (int)(i / ((size_t)W * W));
+    const float dy = __fadd_rn(__ldg(dyo + z), (float)yy), dx = __fadd_rn(__ldg(dxo + z), (float)xx);
+    const float inv = axis ? __fdiv_rn((float)axis, __fadd_rn(__fsqrt_rn(__fmaf_rn(dy, dy, __fmul_rn(dx, dx))), 1e-6f)) : 0.f;
+    float r[32];
+#pragma unroll
+    for (int k = 0; k < 32; k++) r[k] = 0.f;
+    r[0] = round16<HD>(__fmul_rn(__fsub_rn((float)__ldg(ct + (size_t)z * W * W + (size_t)yy * W + xx), mean), isd));
+    r[2] = round16<HD>(__fmul_rn(dy, inv)); r[3] = round16<HD>(__fmul_rn(dx, inv));
+    unsigned w[8];
+    const unsigned sb = mx_encode_row32<BITS>(r, w);        /* channels 4..31 are zeros: the row's first 8 codes are the 8-wide row's */
+    if (BITS == 8) *(uint2 *)(y + i * 8) = make_uint2(w[0], w[1]); else *(unsigned *)(y + i * 4) = w[0];
+    y[S * (BITS == 8 ? 8 : 4) + i] = (uint8_t)sb;
+}
+extern "C" void lp_pred_input_mx(const uint8_t *ct, int W, float mean, float isd, const float *dyo, const float *dxo, int axis, int z0, int nz, void *y, int hd, int bits) {
+    if (!umx_ready("lp_pred_input_mx")) return;
+    if ((bits != 8 && bits != 4) || hd < 0 || hd > 2) { fprintf(stderr, "lp_pred_input_mx: %d bits, 16-bit type %d\n", bits, hd); abort(); }
+    const size_t S = (size_t)(nz > 0 ? nz : 0) * W * W;
+    if (!S) return;
+    const unsigned g = (unsigned)((S + 255) / 256);
+#define UMX_PI(B, H) pred_input_k<B, H><<<g, 256>>>(ct, W, mean, isd, dyo, dxo, axis, z0, nz, (uint8_t *)y)
+    if (bits == 8) { if (hd == 2) UMX_PI(8, 2); else if (hd == 1) UMX_PI(8, 1); else UMX_PI(8, 0); }
+    else { if (hd == 2) UMX_PI(4, 2); else if (hd == 1) UMX_PI(4, 1); else UMX_PI(4, 0); }
+#undef UMX_PI
+    g_umx_launches++;
+    UMX_CK("lp_pred_input_mx");
+}
+extern "C" void lp_pred_input_mx8(const uint8_t *ct, int W, float mean, float isd, const float *dyo, const float *dxo, int axis, int z0, int nz, void *y, int hd) {
+    lp_pred_input_mx(ct, W, mean, isd, dyo, dxo, axis, z0, nz, y, hd, 8);
+}
