@@ -162,7 +162,7 @@ void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int W, const f
    already handed to their own pool, allocation forbidden after start-up, or a loop where cudaMalloc's device-wide synchronisation is
    not acceptable).  The partial sums live in a 4 MiB array built into the library's device image (one per GPU, held until exit), so
    N x 64 x roundup32(C) x 2 doubles must fit in 524288 (N = 1: C <= 4096; N = 8: C <= 512); larger sizes return -1 with a message in
-   lp_check().  The first call on a device looks the array's address up (make it before any stream capture).  All calls on a device
+   lp_check().  The first call on a device looks the array's address up.  All calls on a device
    share the array; calls that overlap on the GPU race, so issue them in order.  Returns 0 on success. */
 int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);
 /* y = fp16(act(x a + b)) requantised to MX (k_inq, src/nn_xnet.cu:1577-1620): x blocked fp16 [n][C][S]; act 2 = LeakyReLU 0.01,

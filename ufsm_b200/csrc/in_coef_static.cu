@@ -8,8 +8,8 @@
 
    The array: UMX_STATIC_DOUBLES doubles (4 MiB), file scope, present on every GPU that loads the library until the process exits.
    In host code its name is only a stand-in for the symbol, not a device address, so the address is taken once per device with
-   cudaGetSymbolAddress while that device is current (the first call on a device does this; make that first call before any stream
-   capture) and handed to the kernels as an ordinary pointer.
+   cudaGetSymbolAddress while that device is current (the first call on a device does this) and handed to the kernels as an ordinary
+   pointer.
 
    Sharing: every call on a device uses the same array and leaves its partial sums behind.  Nothing has to start at zero: a call
    writes every slot it later reads, so stale contents from an earlier (larger or smaller) call are never seen.  Two calls that overlap
