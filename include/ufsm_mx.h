@@ -139,12 +139,11 @@ int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, v
    (k_in_coef, src/nn_xnet.cu:1565-1570), in one call; part: scratch of umx_stats_doubles doubles.  By default the sums are taken by the
    statistics pass over the stored tensor (fp64 in a fixed order: exact to the last bits, independent of batch size and block partition).
    With UMX_STATS_EPILOGUE the resident-weight 3^3 kernel takes them in its epilogue instead, as the reference's conv does (st_add,
-   src/nn_xnet.cu:262-268, 370-390: fp32 partial sums per thread, then fp64 atomics, whose order changes from run to run).  Here the order
-   is fixed and the result does not depend on the batch, on the number of multiprocessors or on how the planes fall to the blocks: per
-   channel the stored fp16 values (and their squares, exact in fp32) of one aligned 4 x 8 block of (y, x) voxels of a z plane are added in
-   fp32, first along y (in order), then along x in a butterfly (bit 4 first); everything above those 32-voxel units is exact 128-bit
-   fixed point.  These sums are within 32-voxel fp32 rounding (about 1e-7 relative) of the exact ones.  The epilogue's extra work costs
-   more than the pass saves on the benchmark's layers (measured), which is why it is not the default. */
+   src/nn_xnet.cu:262-268, 370-390: fp32 partial sums per thread, then fp64 atomics, whose order changes from run to run).  Here they are
+   fp64 sums of the stored fp16 values and of their squares, which are exact for a sample of any realistic size, so the coefficients are
+   those of the pass, whatever the batch, the number of multiprocessors or the way the planes fall to the blocks.  The epilogue's extra
+   work (a conversion and two fp64 operations per element) costs more than the pass saves on the benchmark's layers (measured: the
+   level-0 conv goes from 72 to 120 us, the pass takes 33), which is why it is not the default. */
 int umx_conv_fwd_norm(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, double *part, const float *gamma, const float *beta, float eps, float *coef, int flags);
 size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part for a conv output on that grid */
 /* testing aid (no counterpart in the reference): at most `cap` thread blocks per column tile in the resident-weight 3^3 kernel (0: as many as

@@ -347,52 +347,6 @@ void orc_in_sums(const float *y, int N, int C, size_t S, double *sums) {
         sums[2 * (size_t)nc] = s; sums[2 * (size_t)nc + 1] = q;
     }
 }
-/* The same sums as a conv epilogue takes them (the reference's conv epilogue adds fp32 partial sums per thread and then fp64 atomics in an order
-   that changes from run to run, st_add, src/nn_xnet.cu:262-268; the library fixes the order): per channel, the stored values and their squares
-   (exact in fp32) of one aligned 4 x 8 block of (y, x) voxels of a z plane are added in fp32, first along y, ((v0 + v1) + v2) + v3, then
-   along x in a butterfly, x bit 4 first, then 2, then 1 (voxels outside the grid count as zero); the 32-voxel sums are accumulated
-   exactly, as 128-bit fixed point in units of 2^-64, and the total is (double) hi + (double) lo 2^-64. */
-static void fx_add_f32(long long *hi, unsigned long long *lo, int *bad, float x) {
-    unsigned u; memcpy(&u, &x, 4);
-    const int ex = (int)((u >> 23) & 255u);
-    const unsigned long long m = (unsigned long long)((u & 0x7fffffu) | (ex ? 0x800000u : 0u));
-    const int sh = (ex ? ex : 1) - 150 + 64;
-    if (ex == 255 || sh > 64 + 38) { *bad = 1; return; }
-    unsigned long long vlo, vhi;
-    if (sh >= 64) { vhi = m << (sh - 64); vlo = 0; }
-    else if (sh > 0) { vlo = m << sh; vhi = m >> (64 - sh); }
-    else if (sh > -24) { vlo = m >> (-sh); vhi = 0; }
-    else { vlo = 0; vhi = 0; }
-    if (u >> 31) { vlo = ~vlo + 1ull; vhi = ~vhi + (vlo == 0ull ? 1ull : 0ull); }
-    const unsigned long long nlo = *lo + vlo;
-    *hi += (long long)(vhi + (nlo < *lo ? 1ull : 0ull)); *lo = nlo;
-}
-static float unit32(const float *v) {      /* v[8 y + x] */
-    float t[8];
-    for (int x = 0; x < 8; x++) t[x] = ((v[x] + v[8 + x]) + v[16 + x]) + v[24 + x];
-    for (int h = 4; h >= 1; h >>= 1) for (int k = 0; k < h; k++) t[k] = t[k] + t[k + h];
-    return t[0];
-}
-void orc_in_sums_grouped(const float *y, int N, int C, int D, int H, int W, double *sums) {
-    const int nb = (C + 31) / 32; const size_t S = (size_t)D * H * W;
-#pragma omp parallel for
-    for (int nc = 0; nc < N * C; nc++) {
-        const int n = nc / C, c = nc % C;
-        const float *p = y + ((size_t)n * nb + c / 32) * S * 32 + c % 32;
-        long long sh = 0, qh = 0; unsigned long long sl = 0, ql = 0; int bad = 0;
-        for (int z = 0; z < D; z++) for (int y0 = 0; y0 < H; y0 += 4) for (int x0 = 0; x0 < W; x0 += 8) {
-            float v[32], q[32];
-            for (int l = 0; l < 32; l++) {
-                const int yy = y0 + l / 8, xx = x0 + l % 8;
-                v[l] = (yy < H && xx < W) ? p[(((size_t)z * H + yy) * W + xx) * 32] : 0.f;
-                q[l] = v[l] * v[l];
-            }
-            fx_add_f32(&sh, &sl, &bad, unit32(v)); fx_add_f32(&qh, &ql, &bad, unit32(q));
-        }
-        sums[2 * (size_t)nc] = bad ? NAN : (double)sh + (double)sl * 5.42101086242752217e-20;
-        sums[2 * (size_t)nc + 1] = bad ? NAN : (double)qh + (double)ql * 5.42101086242752217e-20;
-    }
-}
 /* coef [n][C][2]: a = rstd gamma, b = beta - mean a (src/nn_xnet.cu:1565-1570) */
 void orc_in_coef(const double *sums, int N, int C, double S, const float *gamma, const float *beta, float eps, float *coef) {
     for (int i = 0; i < N * C; i++) {

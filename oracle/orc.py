@@ -157,14 +157,6 @@ def in_sums(y, N, Cn, S):
     return s
 
 
-def in_sums_grouped(y, N, Cn, D, H, W):
-    """the sums as a conv epilogue takes them: fp32 inside aligned 4 x 8 (y, x) blocks of a plane, exact above"""
-    y = f32(y)
-    s = np.zeros(N * Cn * 2, np.float64)
-    o().orc_in_sums_grouped(_p(y), N, Cn, D, H, W, _p(s))
-    return s
-
-
 def in_coef(sums, N, Cn, S, eps=1e-5):
     coef = np.zeros(N * Cn * 2, np.float32)
     o().orc_in_coef(_p(sums), N, Cn, C.c_double(S), None, None, C.c_float(eps), _p(coef))

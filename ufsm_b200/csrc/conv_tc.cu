@@ -457,9 +457,9 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
 }
 extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); free(c); }
 int umx_stats_chunks(int D, int H, int W);
-/* room for 512 partial sums per (sample, channel): the statistics pass uses up to that many voxel chunks of two doubles, the conv epilogue one
-   entry of four 64-bit words per block */
-extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 4; }
+/* room for 512 partial sums of two doubles per (sample, channel): the statistics pass uses up to that many voxel chunks, the conv epilogue
+   one entry per block */
+extern "C" size_t umx_stats_doubles(int N, int co, int D, int H, int W) { (void)D; (void)H; (void)W; return (size_t)N * 512 * (size_t)(ceil_div(co, 32) * 32) * 2; }
 
 static int g_last_kernel = -1;
 extern "C" int umx_conv_last_kernel(void) { return g_last_kernel; }

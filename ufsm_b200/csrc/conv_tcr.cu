@@ -69,9 +69,9 @@ struct ConvRArgs {
     int tmem_cols, sfa_base, sfa_cols, sfb_base; /* TMEM: accumulator slots from 0, two A scale buffers, B scales */
     int off_rec, off_bias, off_stage, off_w, off_ring;   /* off_stage: 2 KB per epilogue warp and 32-channel chunk, the fp16 output rows on their way to coalesced stores */
     int fast_h16;                                /* output is the fp16 blocked tensor of a plain conv: the short epilogue */
-    /* InstanceNorm statistics taken in that epilogue (coef != NULL): sums of the stored fp16 values, fp32 inside 32-voxel units and exact above them,
-       written once per sample and block into part [n][gcol][cop][4] (sum and sum of squares as 128-bit fixed point in units of 2^-64); the last block
-       of a column tile to finish adds the blocks' entries (integer adds) and turns them into coefficients (a, b) per (sample, channel) */
+    /* InstanceNorm statistics taken in that epilogue (coef != NULL): fp64 sums of the stored fp16 values and of their squares, written once per
+       sample and block into part [n][gcol][cop][2]; the last block of a column tile to finish adds the blocks' entries in block order and
+       turns them into coefficients (a, b) per (sample, channel) */
     double *part; float *coef; const float *gamma, *beta; float eps; int cop, off_red;
     const uint8_t *wr;
     EpiArgs e;
@@ -144,45 +144,17 @@ __device__ __forceinline__ Run next_run(const ConvRArgs &a, Piece &p) {
     return r;
 }
 
-/* ---- InstanceNorm sums in the epilogue.  The unit of fp32 arithmetic is one aligned block of 4 x 8 (y, x) voxels of one z plane: the 32
-   voxels an epilogue warp holds.  Per channel the stored fp16 values (and their squares, which are exact in fp32) are added first along
-   y, ((v0 + v1) + v2) + v3, then along x in a butterfly, x bit 4 first, then 2, then 1.  Everything above that unit is exact: the unit
-   sums are accumulated as 128-bit fixed point in units of 2^-64 (integer adds: any order, any partition of the planes over blocks, any
-   batch gives the same words).  The sums are taken where the warp re-reads its staged rows for the coalesced store: there a lane
-   holds eight channels of the four voxels of one x, so the y sums need no exchange and the x butterfly runs over the eight lanes that
-   hold the same channels, each lane keeping half of its values per round: 7 shuffles per array instead of 31. ---- */
-__device__ __forceinline__ float x_butterfly(float (&v)[8], int x, int p4, int p2, int p1) {
-    {
-        const bool up = (x & 4) != 0;
-#pragma unroll
-        for (int k = 0; k < 4; k++) { const float send = up ? v[k] : v[k + 4], keep = up ? v[k + 4] : v[k]; v[k] = __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p4)); }
-    }
-    {
-        const bool up = (x & 2) != 0;
-#pragma unroll
-        for (int k = 0; k < 2; k++) { const float send = up ? v[k] : v[k + 2], keep = up ? v[k + 2] : v[k]; v[k] = __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p2)); }
-    }
-    const bool up = (x & 1) != 0;
-    const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
-    return __fadd_rn(keep, __shfl_sync(0xffffffffu, send, p1));
-}
-/* (hi, lo) += x 2^64 for a finite |x| < 2^62 (values below 2^-64 in magnitude are cut off towards zero); anything else sets bad */
-__device__ __forceinline__ void fx_add(long long &hi, unsigned long long &lo, int &bad, float x) {
-    const unsigned u = __float_as_uint(x); const int ex = (int)((u >> 23) & 255u);
-    const unsigned long long m = (unsigned long long)((u & 0x7fffffu) | (ex ? 0x800000u : 0u));
-    const int sh = (ex ? ex : 1) - 150 + 64;                /* x = m 2^(sh - 64) */
-    if (ex == 255 || sh > 64 + 38) { bad = 1; return; }
-    unsigned long long vlo, vhi;
-    if (sh >= 64) { vhi = m << (sh - 64); vlo = 0ull; }
-    else if (sh > 0) { vlo = m << sh; vhi = m >> (64 - sh); }
-    else if (sh > -24) { vlo = m >> (-sh); vhi = 0ull; }
-    else { vlo = 0ull; vhi = 0ull; }
-    if (u >> 31) { vlo = ~vlo + 1ull; vhi = ~vhi + (vlo == 0ull ? 1ull : 0ull); }
-    const unsigned long long nlo = lo + vlo;
-    hi += (long long)(vhi + (nlo < lo ? 1ull : 0ull)); lo = nlo;
-}
-__device__ __forceinline__ void fx_add128(long long &hi, unsigned long long &lo, long long bhi, unsigned long long blo) {
-    const unsigned long long nlo = lo + blo; hi += bhi + (long long)(nlo < lo ? 1ull : 0ull); lo = nlo;
+/* ---- InstanceNorm sums in the epilogue.  They are taken in fp64 where the warp re-reads its staged fp16 rows for the coalesced store:
+   there a lane holds eight channels of the four voxels of one x, and it keeps one (sum, sum of squares) pair per channel for the whole
+   sample.  A stored fp16 value and its square are exact in fp64 and so are their sums over a sample of any realistic size, so neither
+   the order of the planes nor their partition over blocks changes a bit, and the coefficients equal those of the separate fp64 pass
+   (in_part_k).  Per sample and block the eight lanes that hold the same channels are added with shuffles, then the four warps, then (by
+   the block that finishes last, in block order) the blocks. ---- */
+/* the sum over the eight lanes x = 0..7 that hold this lane's channels (partners p4, p2, p1: the lanes at x ^ 4, x ^ 2, x ^ 1) */
+__device__ __forceinline__ double lanes8_sum(double v, int p4, int p2, int p1) {
+    v += __shfl_sync(0xffffffffu, v, p4);
+    v += __shfl_sync(0xffffffffu, v, p2);
+    return v + __shfl_sync(0xffffffffu, v, p1);
 }
 
 __device__ unsigned g_conv_tickets[64];      /* one per column tile; the block that draws the last ticket finalises and resets it */
@@ -426,38 +398,42 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
            chunk) whose unit sum this lane ends up with */
         const int sx = lane >> 2;
         const int sp4 = 4 * (sx ^ 4) + (cl ^ (((sx ^ 4) >> 1) & 3)), sp2 = 4 * (sx ^ 2) + (cl ^ (((sx ^ 2) >> 1) & 3)), sp1 = 4 * (sx ^ 1) + (cl ^ (((sx ^ 1) >> 1) & 3));
-        const int sch = 8 * cl + sx;
-        /* this lane's channels (sch, and sch + 32 of a 64-channel tile): sums and sums of squares of the sample in progress, 2^-64 fixed point */
-        long long s_hi[NCH], q_hi[NCH]; unsigned long long s_lo[NCH], q_lo[NCH]; int bad = 0;
+        const int sch = 8 * cl + sx;                            /* the channel (of a 32-channel chunk) whose lane-group sum this lane writes out */
+        /* this lane's channels 8 cl .. 8 cl + 7 of each chunk: sums and sums of squares of the sample in progress */
+        double dsum[STATS ? NCH : 1][8], dsq[STATS ? NCH : 1][8];
+        if (STATS) {
 #pragma unroll
-        for (int k = 0; k < NCH; k++) { s_hi[k] = 0; q_hi[k] = 0; s_lo[k] = 0ull; q_lo[k] = 0ull; }
-        unsigned long long *red = (unsigned long long *)(smem_raw + a.off_red);          /* [4 warps][nt][4] */
+            for (int k = 0; k < NCH; k++)
+#pragma unroll
+                for (int t = 0; t < 8; t++) { dsum[k][t] = 0.0; dsq[k][t] = 0.0; }
+        }
+        double *red = (double *)(smem_raw + a.off_red);        /* [4 warps][nt][2] */
         uint32_t red_ph = 0;
         /* the 128 epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync: after a give-up nobody is left waiting for good) */
         auto esync = [&]() { mbar_arrive(bar_red); if (!mbar_wait(bar_red, red_ph, abort_flag, kWaitLimitR)) { raise_r(a, abort_flag, 8, pc); dead = true; } red_ph ^= 1u; };
-        /* writes this block's sums of sample n (or zeros): four words per channel (sum hi, lo, squares hi, lo; hi = the largest 64-bit integer
-           marks a sum that met a non-finite value) */
+        /* writes this block's sums of sample n (or zeros): (sum, sum of squares) per channel */
         auto flush = [&](int n, bool have) {
             esync();                                            /* every warp is done with the staging buffers the exchange area overlays */
-            if (have) {
+            if (STATS && have) {
 #pragma unroll
                 for (int k = 0; k < NCH; k++) {
-                    unsigned long long *d = red + ((size_t)(q4 * a.nt + k * 32 + sch)) * 4;
-                    d[0] = bad ? 0x7fffffffffffffffull : (unsigned long long)s_hi[k]; d[1] = s_lo[k]; d[2] = (unsigned long long)q_hi[k]; d[3] = q_lo[k];
-                    s_hi[k] = 0; q_hi[k] = 0; s_lo[k] = 0ull; q_lo[k] = 0ull;
+                    double ws = 0.0, wq = 0.0;
+#pragma unroll
+                    for (int t = 0; t < 8; t++) {
+                        const double a8 = lanes8_sum(dsum[k][t], sp4, sp2, sp1), q8 = lanes8_sum(dsq[k][t], sp4, sp2, sp1);
+                        if (t == sx) { ws = a8; wq = q8; }
+                        dsum[k][t] = 0.0; dsq[k][t] = 0.0;
+                    }
+                    double *d = red + ((size_t)(q4 * a.nt + k * 32 + sch)) * 2;
+                    d[0] = ws; d[1] = wq;
                 }
-                bad = 0;
             }
             esync();
             if (et < a.nt) {
-                long long sh = 0, qh = 0; unsigned long long sl = 0ull, ql = 0ull; bool nf = false;
-                if (have) for (int w4 = 0; w4 < 4; w4++) {
-                    const unsigned long long *r4 = red + ((size_t)(w4 * a.nt + et)) * 4;
-                    nf = nf || r4[0] == 0x7fffffffffffffffull;
-                    fx_add128(sh, sl, (long long)r4[0], r4[1]); fx_add128(qh, ql, (long long)r4[2], r4[3]);
-                }
-                unsigned long long *d = (unsigned long long *)a.part + (((size_t)n * a.gcol + bcol) * a.cop + ctile * a.nt + et) * 4;
-                d[0] = nf ? 0x7fffffffffffffffull : (unsigned long long)sh; d[1] = sl; d[2] = (unsigned long long)qh; d[3] = ql;
+                double ss = 0.0, qq = 0.0;
+                if (have) for (int w4 = 0; w4 < 4; w4++) { const double *r2 = red + ((size_t)(w4 * a.nt + et)) * 2; ss += r2[0]; qq += r2[1]; }
+                double *d = a.part + (((size_t)n * a.gcol + bcol) * a.cop + ctile * a.nt + et) * 2;
+                d[0] = ss; d[1] = qq;
             }
             esync();
         };
@@ -519,27 +495,21 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     uint8_t *pz = run_dst + (size_t)z * plane_b;
 #pragma unroll
                     for (int jc = 0; jc < NCH; jc++) {
-                        float sv[8], sq[8];                    /* this lane's eight channels: sums over the four voxels of its x */
 #pragma unroll
                         for (int i = 0; i < 4; i++) {
                             const uint4 v = *(const uint4 *)(stg_r + jc * 2048 + i * 512);
                             const bool in = sy + i < a.H;
                             if (in) *(uint4 *)(pz + (size_t)jc * S * 64 + (size_t)i * row_b) = v;
-                            if (STATS) {
+                            if (STATS && in) {
                                 const __half2 *hp = (const __half2 *)&v;
 #pragma unroll
                                 for (int t = 0; t < 4; t++) {
-                                    float2 f = __half22float2(hp[t]);
-                                    if (!in) { f.x = 0.f; f.y = 0.f; }
-                                    if (i == 0) { sv[2 * t] = f.x; sv[2 * t + 1] = f.y; sq[2 * t] = __fmul_rn(f.x, f.x); sq[2 * t + 1] = __fmul_rn(f.y, f.y); }
-                                    else { sv[2 * t] = __fadd_rn(sv[2 * t], f.x); sv[2 * t + 1] = __fadd_rn(sv[2 * t + 1], f.y);
-                                           sq[2 * t] = __fadd_rn(sq[2 * t], __fmul_rn(f.x, f.x)); sq[2 * t + 1] = __fadd_rn(sq[2 * t + 1], __fmul_rn(f.y, f.y)); }
+                                    const float2 f = __half22float2(hp[t]);
+                                    const double p0 = (double)f.x, p1 = (double)f.y;
+                                    dsum[jc][2 * t] += p0; dsq[jc][2 * t] = fma(p0, p0, dsq[jc][2 * t]);
+                                    dsum[jc][2 * t + 1] += p1; dsq[jc][2 * t + 1] = fma(p1, p1, dsq[jc][2 * t + 1]);
                                 }
                             }
-                        }
-                        if (STATS) {
-                            fx_add(s_hi[jc], s_lo[jc], bad, x_butterfly(sv, sx, sp4, sp2, sp1));
-                            fx_add(q_hi[jc], q_lo[jc], bad, x_butterfly(sq, sx, sp4, sp2, sp1));
                         }
                     }
                 } else {
@@ -573,16 +543,9 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                 for (int i = et; i < a.N * a.nt; i += 128) {
                     const int n = i / a.nt, c = ctile * a.nt + i % a.nt;
                     if (c >= a.e.co_real) continue;
-                    long long sh = 0, qh = 0; unsigned long long sl = 0ull, ql = 0ull; bool nf = false;
-                    const unsigned long long *pp = (const unsigned long long *)a.part + ((size_t)n * a.gcol * a.cop + c) * 4;
-                    for (int t = 0; t < a.gcol; t++) {
-                        const unsigned long long *r4 = pp + (size_t)t * a.cop * 4;
-                        const unsigned long long w0 = __ldcg(r4), w1 = __ldcg(r4 + 1), w2 = __ldcg(r4 + 2), w3 = __ldcg(r4 + 3);
-                        nf = nf || w0 == 0x7fffffffffffffffull;
-                        fx_add128(sh, sl, (long long)w0, w1); fx_add128(qh, ql, (long long)w2, w3);
-                    }
-                    const double nan_ = __longlong_as_double(0x7ff8000000000000ll);
-                    const double s0 = nf ? nan_ : (double)sh + (double)sl * 5.42101086242752217e-20, q0 = nf ? nan_ : (double)qh + (double)ql * 5.42101086242752217e-20;
+                    double s0 = 0.0, q0 = 0.0;
+                    const double *pp = a.part + ((size_t)n * a.gcol * a.cop + c) * 2;
+                    for (int t = 0; t < a.gcol; t++) { s0 += __ldcg(pp + (size_t)t * a.cop * 2); q0 += __ldcg(pp + (size_t)t * a.cop * 2 + 1); }
                     const double m = s0 / (double)S, v = fmax(q0 / (double)S - m * m, 0.0);
                     const float rs = (float)(1.0 / sqrt(v + (double)a.eps)), ca = __fmul_rn(rs, a.gamma ? a.gamma[c] : 1.f);
                     a.coef[2 * ((size_t)n * a.e.co_real + c)] = ca;
