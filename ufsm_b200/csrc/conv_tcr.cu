@@ -341,21 +341,23 @@ __global__ void __launch_bounds__(kThreadsR, NCH == 1 ? 2 : 1) conv_mxr_k(const 
                     uint8_t *stg = stages + (size_t)cs * a.stage_bytes;
                     const uint8_t *sw = stg + a.offSW;
                     uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
+                    uint32_t wq[4][5];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const int r = q * 32 + lane;
                         const uint8_t *p = sw + (r >> 3) * 32 + (r & 7) + xo;
-                        uint32_t wq[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+                        for (int t = 0; t < 5; t++) wq[q][t] = 0u;
 #pragma unroll
                         for (int j = 0; j < 9; j++) {
                             const uint32_t b0 = p[(j / 3) * 32 + j % 3];
-                            if (BITS == 8) wq[j >> 2] |= b0 << (8 * (j & 3));
-                            else { const uint32_t b1 = p[576 + (j / 3) * 32 + j % 3]; wq[j >> 1] |= (b0 | (b1 << 8)) << (16 * (j & 1)); }
+                            if (BITS == 8) wq[q][j >> 2] |= b0 << (8 * (j & 3));
+                            else { const uint32_t b1 = p[576 + (j / 3) * 32 + j % 3]; wq[q][j >> 1] |= (b0 | (b1 << 8)) << (16 * (j & 1)); }
                         }
-                        /* quad qd: word (lane, column) = row 32 * column + lane */
-#pragma unroll
-                        for (int qd = 0; qd < NQ; qd++) sfa[qd * 128 + lane * 4 + q] = wq[qd];
                     }
+                    /* quad qd: word (lane, column) = row 32 * column + lane; a lane's four columns are 16 contiguous bytes: one store */
+#pragma unroll
+                    for (int qd = 0; qd < NQ; qd++) *(uint4 *)(sfa + qd * 128 + lane * 4) = make_uint4(wq[0][qd], wq[1][qd], wq[2][qd], wq[3][qd]);
                     fence_proxy_async();
                     /* the scale sets are laid out; before they go to TMEM, the MMAs that read this buffer two stages ago must have completed */
                     if (it >= 2 && !pass_empty(true)) { ok = false; break; }
