@@ -17,14 +17,25 @@ extern "C" void umx_u8_to_h16(const uint8_t *x, size_t n, void *y) {
 }
 /* fp16 logits -> uint8 round(254 / (1 + exp(-l))): the per-patch form of the reference's probability output (pred_place_k, src/nn_elem.cu:1117-1125,
    rounds 255 p + 0.5 down; the blended path's k_i3_emit uses round(254 p), which is what this library uses throughout) */
+__device__ __forceinline__ unsigned prob_u8(float l) { return (unsigned)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-l))), 254.f)) & 0xffu; }
+/* eight values a thread: one 16-byte load, one 8-byte store (x and y 16- and 8-byte aligned); the tail one by one */
 __global__ void __launch_bounds__(256) h16_to_prob_u8_k(const __half *__restrict__ x, uint8_t *__restrict__ y, size_t n) {
     pdl_trigger(); pdl_wait();
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        y[i] = (uint8_t)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-__half2float(x[i])))), 254.f));
+    const size_t n8 = n / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = __ldg((const uint4 *)x + i);
+        const __half2 *h = (const __half2 *)&v;
+        unsigned w[2] = {0u, 0u};
+#pragma unroll
+        for (int k = 0; k < 4; k++) { const float2 f = __half22float2(h[k]); w[k >> 1] |= (prob_u8(f.x) | (prob_u8(f.y) << 8)) << (16 * (k & 1)); }
+        ((uint2 *)y)[i] = make_uint2(w[0], w[1]);
+    }
+    for (size_t i = n8 * 8 + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = (uint8_t)prob_u8(__half2float(x[i]));
 }
 extern "C" void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y) {
     if (!umx_ready("umx_h16_to_prob_u8")) return;
-    size_t g = (n + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; if (!g) g = 1;
+    if (((size_t)x & 15) || ((size_t)y & 7)) { fprintf(stderr, "umx_h16_to_prob_u8: x must be 16-byte and y 8-byte aligned\n"); abort(); }
+    size_t g = (n / 8 + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; if (!g) g = 1;
     umx_launch(h16_to_prob_u8_k, dim3((unsigned)g), dim3(256), 0, (const __half *)x, y, n);
     g_umx_launches++;
     UMX_CK("umx_h16_to_prob_u8");
