@@ -46,6 +46,10 @@ class Clocks(threading.Thread):
         self.gpu, self.rows, self.stop, self.max_mhz, self.interval = gpu, [], False, None, interval
         self.ready = threading.Event()          # set once the sampler is initialised (NVML start-up stalls kernel launches for tens of ms)
         self.t_on = None                         # samples before this time (warm-up) are dropped
+        self.periodic = False                    # the thread samples by itself only in long timed regions (the window run): an NVML query holds a
+                                                 # driver lock that kernel launches need, and a query that lands inside a 30 ms launch loop of several
+                                                 # ranks at once has stalled it for tens of ms; the short regions are sampled by the main thread
+                                                 # after their last launch, while the GPU is still working through them
         self.q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def _nvml(self):
@@ -56,6 +60,17 @@ class Clocks(threading.Thread):
         self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(idx)
         self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
         self.bits = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown, nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+
+    def sample_aside(self, n=1):
+        """n samples from a helper thread, started now: for the moment after the last launch of a short timed region, when the GPU is
+        still working through it and the launching thread goes on to wait for it (a query can take tens of ms on a busy host)."""
+        def go():
+            for _ in range(n):
+                self.sample_once()
+                time.sleep(0.002)
+        t = threading.Thread(target=go, daemon=True)
+        t.start()
+        return t
 
     def sample_once(self):
         """One sample from the calling thread (used while the timed steps are queued on the GPU, so that a short run has one too)."""
@@ -72,7 +87,7 @@ class Clocks(threading.Thread):
             self._nvml()
             self.ready.set()
             while not self.stop:
-                if self.t_on is not None:
+                if self.t_on is not None and self.periodic:
                     self.sample_once()
                 time.sleep(self.interval)
             return
@@ -83,7 +98,7 @@ class Clocks(threading.Thread):
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.q, "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
                 f = [t.strip() for t in out.strip().split(",")]
-                if len(f) >= 6 and f[0].isdigit() and self.t_on is not None:
+                if len(f) >= 6 and f[0].isdigit() and self.t_on is not None and self.periodic:
                     self.max_mhz = int(f[1]) if f[1].isdigit() else self.max_mhz
                     self.rows.append([int(f[0])] + [t.lower().startswith("active") for t in f[2:6]])
             except Exception:
@@ -369,8 +384,10 @@ def run_gpu(args):
     L.umx_timer_start(timer)
     for _ in range(args.steps):
         L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
-    clk.sample_once()
-    ms = L.umx_timer_stop_ms(timer)
+    L.umx_timer_mark(timer)            # the stop event sits behind the last launch; the GPU is still working through the steps,
+    side = clk.sample_aside(3)         # which is when the clocks and throttle reasons of this timed region are read
+    ms = L.umx_timer_read_ms(timer)
+    side.join(5)
     launches = L.umx_launch_count() - n0
     barrier()
     ms = tmax(ms)
@@ -387,8 +404,10 @@ def run_gpu(args):
         L.umx_timer_start(timer)
         for i in range(args.steps):
             submit(u.h, hin, B, hout if i & 1 else hout2)
-        assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
+        side = clk.sample_aside(2)
+        assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()       # waits for the last step's download: the timed work is complete
         v = tmax(L.umx_timer_stop_ms(timer))
+        side.join(5)
         barrier()
         return v
     # the result a step delivers: the uint8 probabilities round(254 sigmoid(logit)) that the reference's predict writes (converted on the device);
@@ -434,7 +453,9 @@ def run_gpu(args):
     # stream from the first patch to the last byte on the host, max over ranks.
     win = None
     if args.window:
+        clk.periodic = True
         win = run_window(L, u, rank, world, local, dist, args.window, B, timer, tmax, barrier)
+        clk.periodic = False
     # ---- single layers of configurations 1 and 2 and the quantiser (rank 0 reports them; parity of these shapes is in the tests)
     extra = None
     if rank == 0:

@@ -62,6 +62,8 @@ void nn_free_host(void *p);
 void *umx_timer_new(void);
 void umx_timer_start(void *t);           /* synchronises, then records the start event */
 float umx_timer_stop_ms(void *t);        /* records the stop event, waits for it, returns the elapsed milliseconds */
+void umx_timer_mark(void *t);            /* the same in two steps: record the stop event ... */
+float umx_timer_read_ms(void *t);        /* ... wait for it and return the elapsed milliseconds */
 void umx_timer_free(void *t);
 /* between umx_prof_begin and umx_prof_end every conv kernel launch is bracketed by events: umx_prof_end returns the number of conv
    launches, their summed device time (ms) and their summed algorithmic FLOPs (2 x output voxels x C_in x C_out x taps) */

@@ -47,6 +47,8 @@ _SIG = {
     "umx_timer_new": (C.c_void_p, []),
     "umx_timer_start": (None, [C.c_void_p]),
     "umx_timer_stop_ms": (C.c_float, [C.c_void_p]),
+    "umx_timer_mark": (None, [C.c_void_p]),
+    "umx_timer_read_ms": (C.c_float, [C.c_void_p]),
     "umx_timer_free": (None, [C.c_void_p]),
     "umx_prof_begin": (None, []),
     "umx_prof_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double)]),

@@ -151,6 +151,16 @@ extern "C" float umx_timer_stop_ms(void *tv) {
     if (e != cudaSuccess) { umx_latch("umx_timer_stop_ms", e); return -1.f; }
     return ms;
 }
+/* the two halves of umx_timer_stop_ms: record the stop event now; wait for it and read the time later (a caller that wants to do
+   host work, such as sampling clocks, while the timed launches are still running) */
+extern "C" void umx_timer_mark(void *tv) { cudaEventRecord(((umx_timer *)tv)->b, 0); }
+extern "C" float umx_timer_read_ms(void *tv) {
+    umx_timer *t = (umx_timer *)tv; float ms = 0.f;
+    cudaError_t e = cudaEventSynchronize(t->b);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, t->a, t->b);
+    if (e != cudaSuccess) { umx_latch("umx_timer_read_ms", e); return -1.f; }
+    return ms;
+}
 extern "C" void umx_timer_free(void *tv) { umx_timer *t = (umx_timer *)tv; if (!t) return; cudaEventDestroy(t->a); cudaEventDestroy(t->b); free(t); }
 
 /* per-launch timing of the conv kernel: between umx_prof_begin and umx_prof_end every conv launch is bracketed by two events */
