@@ -40,6 +40,8 @@ extern "C" const char *lp_check(void) {
     return g_err;
 }
 extern "C" const char *nn_check(void) { return lp_check(); }
+/* 1 when this thread has latched an error; unlike lp_check it neither reads the device's flag (a synchronising copy) nor clears the latch */
+extern "C" int umx_has_error(void) { return g_has_err; }
 extern "C" int nn_init(int device) {
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) { umx_latch("nn_init", e); return -1; }

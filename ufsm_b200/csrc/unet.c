@@ -15,6 +15,7 @@
 #include <string.h>
 
 void umx_u8_to_h16(const uint8_t *x, size_t n, void *y);
+int umx_has_error(void);
 void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y);
 void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum);
 void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out);
@@ -214,7 +215,7 @@ static int submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits1
     else umx_copy_async(logits16_host, u->plog[k], (size_t)N * u->cfg.nh * S * 2, 0, u->s_out);
     umx_event_record(u->ev_down[k], u->s_out);
     u->seq++;
-    return nn_check() ? -1 : 0;
+    return umx_has_error() ? -1 : 0;     /* launch errors latched so far; nothing here waits for the device (umx_unet_wait reports the rest) */
 }
 int umx_unet_submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) { return submit_host(u, ct_host, N, logits16_host, 0); }
 int umx_unet_submit_host_u8(umx_unet *u, const uint8_t *ct_host, int N, uint8_t *prob_host) { return submit_host(u, ct_host, N, prob_host, 1); }
