@@ -174,7 +174,7 @@ def test_unbuilt_fields_stop(dev):
     import subprocess
     import sys
     code = ("import ufsm_b200, ctypes as C\nfrom ufsm_b200 import Shape5, Gnp, Split\nL = ufsm_b200.lib()\nassert L.nn_init(0) == 0\n"
-            "sp = Split(); sp.accum = 1\nL.lp_conv_fwd_f8(None, 3, Shape5(1, 32, 4, 8, 16), None, None, 32, None, 3, Gnp(), None, 0, sp)\n")
+            "sp = Split(); sp.sr = 7\nL.lp_conv_fwd_f8(None, 3, Shape5(1, 32, 4, 8, 16), None, None, 32, None, 3, Gnp(), None, 0, sp)\n")
     r = subprocess.run([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=orc.ROOT)
     assert r.returncode != 0 and "not built" in r.stderr
 
@@ -222,3 +222,96 @@ def test_pred_input_mx_and_narrow_rows(dev, bits, hd, axis):
     got2 = od2.download()
     assert got2.size == want2.size and np.count_nonzero(got2 != want2) < 2e-3 * got2.size
     assert orc.rel_l2(orc.mx_to_pm(got2, bits, 1, 16, S), orc.mx_to_pm(want2, bits, 1, 16, S)) < (5e-3 if bits == 8 else 2e-2)
+
+
+def _full_conv(L, xbf, x_store, N, Ci, D, H, W, w, b, Co, ybf, gp=None):
+    """the whole-tensor conv through the same entry (itself checked against the oracle elsewhere in this suite): what a slab run must reproduce"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    S = D * H * W
+    nby = N * Co * S * 2 if ybf == 2 else orc.mx_bytes(8 if ybf == 3 else 4, N, Co, S, 32)
+    xd, wd, bd, yd = DevBuf(data=x_store), DevBuf(data=w), DevBuf(data=b), DevBuf(nby).fill(0xEE)
+    assert L.lp_conv_fwd_f8(xd.ptr, xbf, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, ybf, gp if gp is not None else Gnp(), None, 0, Split()) == 0
+    ufsm_b200.check()
+    return yd.download()
+
+
+@pytest.mark.parametrize("xbf,ybf,gn", [(3, 2, False), (2, 2, False), (3, 3, False), (3, 2, True)])
+def test_z_range_window_and_slab_output(dev, xbf, ybf, gn):
+    """split_t.zi0 / Di (a conv over planes of a deeper input), zw0 / zw1 (a window of output planes), yD / yzo (the output placed in a deeper
+    tensor): each run must give the planes of the whole-tensor conv, with zero padding only at the tensor's own ends."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    N, Ci, Co, D, H, W = 2, 32, 32, 12, 8, 16
+    S, hw = D * H * W, H * W
+    x = (synth.rng(231).standard_normal(N * Ci * S) * 2).astype(f32)
+    w, b = synth.kaiming(232, Co, Ci, 27), synth.bias(233, Co, 0.1)
+    xs = x.astype(np.float16) if xbf == 2 else orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
+    keep = []
+    gp = make_gp(8, gn_params(234, N, Ci, 8), keep) if gn else Gnp()
+    full = _full_conv(L, xbf, xs, N, Ci, D, H, W, w, b, Co, ybf, gp)
+    xd, wd, bd = DevBuf(data=xs), DevBuf(data=w), DevBuf(data=b)
+
+    def planes(buf, z0, z1):                 # planes [z0, z1) of a stored output tensor as a flat array (codes and scale rows for MX)
+        if ybf == 2:
+            return buf.view(np.float16).reshape(N * Co, D, hw)[:, z0:z1].copy()
+        rows = N * (Co // 32)
+        return np.concatenate([buf[:rows * S * 32].reshape(rows, D, hw * 32)[:, z0:z1].ravel(), buf[rows * S * 32:].reshape(rows, D, hw)[:, z0:z1].ravel()])
+
+    def same(a, c):
+        if ybf == 2:
+            return orc.rel_l2(a.astype(f32), c.astype(f32)) < 1e-5
+        return np.count_nonzero(a != c) < 1e-3 * a.size
+    # a window of output planes: the rest of y stays as it was
+    for z0, z1 in ((0, 4), (4, 8), (8, 12)):
+        yd = DevBuf(full.size).fill(0xEE)
+        sp = Split(); sp.zw0, sp.zw1 = z0, z1
+        assert L.lp_conv_fwd_f8(xd.ptr, xbf, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, ybf, gp, None, 0, sp) == 0
+        ufsm_b200.check()
+        got = yd.download()
+        assert same(planes(got, z0, z1), planes(full, z0, z1)), (z0, z1)
+        rest = np.ones(D, bool); rest[z0:z1] = False
+        other = got.view(np.float16).reshape(N * Co, D, hw)[:, rest].view(np.uint8) if ybf == 2 else got[:N * (Co // 32) * S * 32].reshape(-1, D, hw * 32)[:, rest]
+        assert (other == 0xEE).all()
+    # a z range of a deeper input, written as a tensor of its own depth, and (MX or fp16 alike) straight into the deep output tensor
+    for zi0, nz in ((0, 4), (4, 4), (8, 4), (2, 7)):
+        sp = Split(); sp.zi0, sp.Di = zi0, D
+        nby = N * Co * nz * hw * 2 if ybf == 2 else orc.mx_bytes(8, N, Co, nz * hw, 32)
+        yd = DevBuf(nby).fill(0xEE)
+        assert L.lp_conv_fwd_f8(xd.ptr, xbf, Shape5(N, Ci, nz, H, W), wd.ptr, bd.ptr, Co, yd.ptr, ybf, gp, None, 0, sp) == 0
+        sp.yD, sp.yzo = D, zi0
+        yd2 = DevBuf(full.size).fill(0xEE)
+        assert L.lp_conv_fwd_f8(xd.ptr, xbf, Shape5(N, Ci, nz, H, W), wd.ptr, bd.ptr, Co, yd2.ptr, ybf, gp, None, 0, sp) == 0
+        ufsm_b200.check()
+        want = planes(full, zi0, zi0 + nz)
+        got = yd.download()
+        got = got.view(np.float16).reshape(N * Co, nz, hw) if ybf == 2 else got
+        assert same(got.ravel() if ybf == 2 else got, want.ravel() if ybf == 2 else want), (zi0, nz)
+        assert same(planes(yd2.download(), zi0, zi0 + nz), want), (zi0, nz)
+
+
+def test_accumulate(dev):
+    """split_t.accum: y += conv (fp16 plane-major), also on a window of planes"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    N, Ci, Co, D, H, W = 1, 32, 32, 8, 8, 16
+    S = D * H * W
+    x = (synth.rng(241).standard_normal(N * Ci * S) * 2).astype(f32)
+    w, b = synth.kaiming(242, Co, Ci, 27), synth.bias(243, Co, 0.1)
+    xs = orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
+    full = _full_conv(L, 3, xs, N, Ci, D, H, W, w, b, Co, 2).view(np.float16).astype(f32)
+    y0 = synth.rng(244).standard_normal(N * Co * S).astype(np.float16)
+    xd, wd, bd = DevBuf(data=xs), DevBuf(data=w), DevBuf(data=b)
+    for zw in (None, (2, 6)):
+        yd = DevBuf(data=y0)
+        sp = Split(); sp.accum = 1
+        add = full.reshape(N * Co, D, -1).copy()
+        if zw:
+            sp.zw0, sp.zw1 = zw
+            add[:, :zw[0]] = 0; add[:, zw[1]:] = 0
+        assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, Gnp(), None, 0, sp) == 0
+        ufsm_b200.check()
+        want = (y0.astype(f32) + add.ravel()).astype(np.float16)
+        assert np.array_equal(yd.download(np.float16), want)

@@ -2,7 +2,8 @@
    conv: same signature, storage codes and error behaviour; the prepared weights are memoised under split_t.wkey as the reference's fp4
    kernel does (src/lp_f4fwd.cuh:748-770).  Of split_t (src/nn_lp.h:20-37): x2 / c_split / gp2 (concat input), up (the x part stored at
    half resolution and read as its trilinear upsample), y2 / o_split (split output), stored_stats with osum / Go / zlo / zhi (GroupNorm
-   sums of the stored output); the other fields stop with "not built". */
+   sums of the stored output), zi0 / Di, zw0 / zw1, yD / yzo (z range, z window, slab output), accum; sr / osr / o_pad stop with
+   "not built". */
 #include "mx_common.cuh"
 #include <stdlib.h>
 #include <string.h>
@@ -71,10 +72,106 @@ __global__ void w_expand_k(const float *__restrict__ w, const float *__restrict_
 extern "C" void umx_mx_rewidth(const void *x, int bits, int N, int C, size_t S, void *y, int to_wide);
 static inline bool any_gn_(const gnp_t &gp, const split_t &sp) { return gp.G || sp.gp2.G; }
 
+/* ---- z slabs (split_t.zi0 / Di, zw0 / zw1, yD / yzo) and accumulate ----
+   A conv over a range of z planes is the same conv on a copy of the input planes it reads: planes [first, first + nz) of every
+   (sample, channel block) of a tensor of depth D, zeros where the range leaves the tensor. */
+struct tdesc { size_t rows, plane_b, sc_rows; int rb; };     /* rows of `plane_b` bytes per z plane; MX: as many scale rows of H W bytes per plane */
+static tdesc tensor_desc(int bf, int N, int C, size_t hw) {
+    tdesc t = {0, 0, 0, 0};
+    if (bf == UMX_F16) { t.rows = (size_t)N * C; t.plane_b = hw * 2; }
+    else {
+        const int bits = bf == UMX_MX8 ? 8 : 4, bw = C <= 8 ? 8 : C <= 16 ? 16 : 32;
+        t.rb = bw * bits / 8; t.rows = (size_t)N * ((C + bw - 1) / bw); t.plane_b = hw * t.rb; t.sc_rows = t.rows;
+    }
+    return t;
+}
+static size_t tensor_bytes(const tdesc &t, int D, size_t hw) { return t.rows * D * t.plane_b + t.sc_rows * D * hw; }
+/* dst planes [dz, dz + nz) of depth Dd <- src planes [sz, sz + nz) of depth Ds (both ranges inside their tensors) */
+static void planes_copy(void *dst, int Dd, int dz, const void *src, int Ds, int sz, int nz, const tdesc &t, size_t hw) {
+    if (nz <= 0) return;
+    cudaMemcpy2DAsync((uint8_t *)dst + (size_t)dz * t.plane_b, (size_t)Dd * t.plane_b, (const uint8_t *)src + (size_t)sz * t.plane_b, (size_t)Ds * t.plane_b, (size_t)nz * t.plane_b, t.rows, cudaMemcpyDeviceToDevice, 0);
+    if (t.sc_rows) {
+        const uint8_t *ss = (const uint8_t *)src + t.rows * Ds * t.plane_b; uint8_t *ds = (uint8_t *)dst + t.rows * Dd * t.plane_b;
+        cudaMemcpy2DAsync(ds + (size_t)dz * hw, (size_t)Dd * hw, ss + (size_t)sz * hw, (size_t)Ds * hw, (size_t)nz * hw, t.sc_rows, cudaMemcpyDeviceToDevice, 0);
+    }
+}
+static void *slab_of(int slot, const void *x, int bf, int N, int C, int D, size_t hw, int first, int nz) {
+    const tdesc t = tensor_desc(bf, N, C, hw);
+    void *s = umx_ws(slot, tensor_bytes(t, nz, hw));
+    if (!s) return nullptr;
+    cudaMemsetAsync(s, 0, tensor_bytes(t, nz, hw), 0);          /* zero codes under a zero scale byte: the value 0 */
+    const int a = first < 0 ? 0 : first, e = first + nz > D ? D : first + nz;
+    planes_copy(s, nz, a - first, x, D, a, e - a, t, hw);
+    return s;
+}
+/* y (fp16 plane-major, n elements) += t */
+__global__ void __launch_bounds__(256) h16_add_k(__half *__restrict__ y, const __half *__restrict__ t, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = __float2half_rn(__fadd_rn(__half2float(y[i]), __half2float(t[i])));
+}
+
 static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
     if (!umx_ready(fn)) return 0;
-    if (sp.accum || sp.yD || sp.sr || sp.osr || sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yzo || sp.o_pad)
-        not_built(fn, "split_t.accum / sr / osr / zi0 / Di / zw0 / zw1 / yD / yzo / o_pad");
+    if (sp.sr || sp.osr || sp.o_pad) not_built(fn, "split_t.sr / osr / o_pad");
+    if (sp.accum) {
+        /* y += conv: the conv into scratch, then one rounding of the fp16 sum (the reference adds in its epilogue, src/lp_common.cuh:1567-1571,
+           and rounds once as well, but from the fp32 accumulator: the two can differ by the rounding of the conv's own fp16 result) */
+        if (ybf != UMX_F16 || sp.y2 || osum) not_built(fn, "split_t.accum with an output that is not one fp16 plane-major tensor, or with output statistics");
+        const int Dy = sp.yD ? sp.yD : xs.d;
+        const size_t ny = (size_t)xs.n * cout * Dy * xs.h * xs.w;
+        __half *t = (__half *)umx_ws(11, ny * 2);
+        if (!t) return 0;
+        if (sp.yD || sp.zw1) cudaMemsetAsync(t, 0, ny * 2, 0);     /* planes the conv does not write add nothing */
+        split_t s2 = sp; s2.accum = 0;
+        conv_fwd(fn, bits, x, xbf, xs, w, b, cout, t, ybf, gp, nullptr, 0, s2);
+        size_t g = (ny + 255) / 256; if (g > 148u * 16u) g = 148u * 16u;
+        if (ny) h16_add_k<<<(unsigned)g, 256>>>((__half *)y, t, ny);
+        UMX_CK(fn);
+        return 0;
+    }
+    if (sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yD || sp.yzo) {
+        if (sp.up || sp.y2 || osum || Go) not_built(fn, "a z range / z window / slab output together with split_t.up, a split output or output statistics");
+        if ((sp.Di || sp.zi0) && sp.zw1) not_built(fn, "a z range and a z window in one call");
+        if (ybf == UMX_H16B) not_built(fn, "a z range / z window with a blocked fp16 output");
+        const size_t hw = (size_t)xs.h * xs.w;
+        const int Din = sp.Di ? sp.Di : xs.d;                                   /* depth of the input tensors */
+        const int z0 = sp.zw1 ? sp.zw0 : 0, z1 = sp.zw1 ? sp.zw1 : xs.d;         /* output planes of this launch, in the launch's own counting */
+        if (z0 < 0 || z1 > xs.d || z1 <= z0) { fprintf(stderr, "%s: z window [%d, %d) of %d planes\n", fn, z0, z1, xs.d); abort(); }
+        const int nz = z1 - z0, Dy = sp.yD ? sp.yD : xs.d, yz = z0 + sp.yzo;
+        if (yz < 0 || yz + nz > Dy) { fprintf(stderr, "%s: output planes [%d, %d) of a depth-%d tensor\n", fn, yz, yz + nz, Dy); abort(); }
+        const int Cx = sp.x2 ? sp.c_split : xs.c;
+        /* the conv on nz + 2 planes: input planes z0 + zi0 - 1 .. z1 + zi0; its first and last output plane are thrown away */
+        const int first = z0 + sp.zi0 - 1;
+        const void *xa = slab_of(8, x, xbf, xs.n, Cx, Din, hw, first, nz + 2);
+        if (!xa) return 0;
+        split_t s2 = sp; s2.zi0 = s2.Di = s2.zw0 = s2.zw1 = s2.yD = s2.yzo = 0;
+        if (gp.G || sp.gp2.G) {
+            /* the transform belongs to the voxels of the tensor; the planes beyond its ends stay zero (the reference stages them as zeros): transform
+               the slab here, clear those planes again, and hand the conv a plain MX tensor */
+            if (sp.x2 || xs.c <= 16) not_built(fn, "a GroupNorm transform on a z range of a concat input or of 16 channels or fewer");
+            const int mxf = bits == 8 ? UMX_MX8 : UMX_MX4;
+            const tdesc tm = tensor_desc(mxf, xs.n, xs.c, hw);
+            uint8_t *g = (uint8_t *)umx_ws(9, tensor_bytes(tm, nz + 2, hw));
+            if (!g) return 0;
+            if (umx_gn_silu_apply_seg(xa, xbf, xs.n, xs.c, (size_t)(nz + 2) * hw, gp.G, gp.gamma, gp.beta, gp.mean, gp.rstd, g, bits, UMX_LAYOUT_REF, 1, 0, xs.c) != 0) not_built(fn, "this GroupNorm transform");
+            const int lo = first < 0 ? -first : 0, hi = first + nz + 2 > Din ? first + nz + 2 - Din : 0;      /* planes before / after the tensor */
+            for (int side = 0; side < 2; side++) {
+                const int np = side ? hi : lo, p0 = side ? nz + 2 - hi : 0;
+                if (!np) continue;
+                cudaMemset2DAsync(g + (size_t)p0 * tm.plane_b, (size_t)(nz + 2) * tm.plane_b, 0, (size_t)np * tm.plane_b, tm.rows, 0);
+                cudaMemset2DAsync(g + tm.rows * (nz + 2) * tm.plane_b + (size_t)p0 * hw, (size_t)(nz + 2) * hw, 0, (size_t)np * hw, tm.sc_rows, 0);
+            }
+            xa = g; xbf = mxf; gp.G = 0;
+        }
+        if (sp.x2) { s2.x2 = slab_of(9, sp.x2, xbf, xs.n, xs.c - Cx, Din, hw, z0 + sp.zi0 - 1, nz + 2); if (!s2.x2) return 0; }
+        shape5 s5 = xs; s5.d = nz + 2;
+        const tdesc ty = tensor_desc(ybf, xs.n, cout, hw);
+        void *t = umx_ws(10, tensor_bytes(ty, nz + 2, hw));
+        if (!t) return 0;
+        conv_fwd(fn, bits, xa, xbf, s5, w, b, cout, t, ybf, gp, nullptr, 0, s2);
+        planes_copy(y, Dy, yz, t, nz + 2, 1, nz, ty, hw);
+        UMX_CK(fn);
+        return 0;
+    }
     if (gp.G && (gp.ns > 1 || gp.zs || gp.zo || gp.zhw)) not_built(fn, "slab-local GroupNorm (gnp_t.ns / zs / zo / zhw)");
     if (sp.gp2.G && (sp.gp2.ns > 1 || sp.gp2.zs || sp.gp2.zo || sp.gp2.zhw)) not_built(fn, "slab-local GroupNorm (split_t.gp2)");
     if (sp.up && !sp.x2) { fprintf(stderr, "%s: split_t.up without x2\n", fn); abort(); }
