@@ -57,16 +57,10 @@ struct ConvArgs {
     int s2, nbi, Di, Hi, Wi;
     EpiArgs e;
     int *err;
-    long long *prof;
 };
 
 __device__ unsigned g_ks_tickets[8192];      /* one per output tile of a split launch; the last block of a tile resets it */
 
-#ifdef UMX_KPROF
-#define KP1(...) __VA_ARGS__
-#else
-#define KP1(...)
-#endif
 
 __device__ __forceinline__ void raise(const ConvArgs &a, volatile int *abort_flag, int code, int stage) {
     if (atomicCAS(a.err, 0, code) == 0) { a.err[1] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)); a.err[2] = stage; a.err[3] = (int)threadIdx.x; }
@@ -161,14 +155,10 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             const uint32_t a_lo0 = desc_lo(sb0 + a.offA, a.taps == 27 ? 2880 : 2048), b_lo0 = desc_lo(sb0 + a.offW, (uint32_t)a.nt * 16);
             const uint32_t idesc0 = BITS == 8 ? idesc_mxf8(n_cur, 0, 0) : idesc_mxf4(n_cur, 0, 0);
             const uint32_t bstep = (uint32_t)a.nt * 2;
-            KP1(long long t_tma = 0, t_sf = 0, t_issue = 0; const long long t00 = clock64();)
             for (int st = st_lo; st < st_hi && ok; st++) {
                 if (!stage_live(st)) continue;
-                KP1(const long long k0 = clock64();)
                 if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 3, st); ok = false; break; }
-                KP1(const long long k1 = clock64(); t_sf += k1 - k0;)
                 if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimit)) { raise(a, abort_flag, 2, st); ok = false; break; }
-                KP1(const long long k2 = clock64(); t_tma += k2 - k1;)
                 tc_fence_after();
                 const uint32_t so = (uint32_t)s * sstep;
                 const uint32_t sfa_t = tmem + kSfBase + (it & 1) * 40, sfb_t = sfa_t + 20;
@@ -189,10 +179,8 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                     issue_items<BITS, 4, false>(tmem, a_lo0 + so, a_hi, b_lo0 + so, b_hi, bstep, 256, idesc0, sfa_t, sfb_t, it == 0, items);
                 }
                 umma_commit(bar_empty + 8 * s);
-                KP1(t_issue += clock64() - k2;)
                 it++; if (++s == R) { s = 0; ph ^= 1; }
             }
-            KP1({ long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[0] = t_tma; q[1] = t_sf; q[2] = t_issue; q[3] = clock64() - t00; q[4] = it; })
             umma_commit(bar_acc);   /* also after a give-up: the epilogue must not wait for its full limit */
         }
     } else {
@@ -256,9 +244,7 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             it++;
         }
         /* ---- epilogue ---- */
-        KP1(const long long e0 = clock64();)
         if (!mbar_wait(bar_acc, 0, abort_flag, kWaitLimit)) raise(a, abort_flag, 5, 0);
-        KP1(const long long e1 = clock64(); long long e2 = e1, e3 = e1;)
         tc_fence_after();
         const int nchunk = n_cur >> 5;
         if (!*abort_flag && a.ksplit > 1) {
@@ -273,7 +259,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 for (int k = 0; k < 8; k++) __stcg((uint4 *)(mine + (size_t)jc * 4096 + k * 512), make_uint4(rr[4 * k], rr[4 * k + 1], rr[4 * k + 2], rr[4 * k + 3]));
             }
             __threadfence();
-            KP1(e2 = clock64();)
             volatile unsigned *last_s = (volatile unsigned *)(smem_raw + 264);
             bool dead = false; uint32_t red_ph = 0;
             /* the 128 epilogue threads meet on an mbarrier (a bounded wait) */
@@ -281,7 +266,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
             esync();
             if (r == 0) { const unsigned tk = atomicAdd(&a.ks_tickets[tile_id], 1u); const unsigned l = tk == (unsigned)a.ksplit - 1u; if (l) a.ks_tickets[tile_id] = 0u; *last_s = l; }
             esync();
-            KP1(e3 = clock64();)
             if (!dead && *last_s) {
                 /* the parts of one 32-column chunk (16 KB per split) come into the now idle stage ring with bulk copies, the next chunk's
                    while this one goes through the epilogue: summing straight from global memory is a chain of L2 round trips */
@@ -324,7 +308,6 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 epi_chunk(a.e, n, z, oy, ox, row_ok, (n0 >> 5) + jc, v);
             }
         }
-        KP1(if (threadIdx.x == 64) { long long *q = a.prof + (size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 8; q[5] = e1 - e0; q[6] = e2 - e1; q[7] = clock64() - e3; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -595,18 +578,9 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         }
     }
     const dim3 grid(a.tiles_x * a.tiles_y, D, N * a.ntiles_n * a.ksplit);
-#ifdef UMX_KPROF
-    const size_t nblk = (size_t)grid.x * grid.y * grid.z;
-    a.prof = (long long *)umx_ws(7, nblk * 64); cudaMemset(a.prof, 0, nblk * 64);
-#endif
     const int pid = umx_prof_open(flops);
     if (c->bits == 8) umx_launch(conv_mx_k<8>, grid, dim3(kThreads), smem, m0, a); else umx_launch(conv_mx_k<4>, grid, dim3(kThreads), smem, m0, a);
     umx_prof_close(pid);
-#ifdef UMX_KPROF
-    { long long *hb = (long long *)malloc(nblk * 64); cudaMemcpy(hb, a.prof, nblk * 64, cudaMemcpyDeviceToHost);
-      double t[8] = {0}; long long mx7 = 0; for (size_t b = 0; b < nblk; b++) { for (int k = 0; k < 8; k++) t[k] += (double)hb[b * 8 + k] / nblk; if (hb[b * 8 + 7] > mx7) mx7 = hb[b * 8 + 7]; }
-      fprintf(stderr, "kprof-v1: grid %u x %u x %u ksplit %d ring %d nst %d nt %d stage_bytes %d | mma thread: stages %.0f total %.0f wait-tma %.0f wait-sf %.0f issue %.0f | epilogue: wait-acc %.0f part-store %.0f tail %.0f (max %lld)\n", grid.x, grid.y, grid.z, a.ksplit, a.ring, a.nst, a.nt, a.stage_bytes, t[4], t[3], t[0], t[1], t[2], t[5], t[6], t[7], mx7); free(hb); }
-#endif
     g_umx_launches++; g_last_kernel = 0;
     UMX_CK("umx_conv_fwd");
     if (nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);

@@ -20,11 +20,6 @@
 #include <stdlib.h>
 #include <string.h>
 
-#ifdef UMX_KPROF
-#define KP(...) __VA_ARGS__
-#else
-#define KP(...)
-#endif
 
 namespace {
 
@@ -43,8 +38,6 @@ struct ConvPArgs {
     const uint8_t *wp;
     EpiArgs e;
     int *err;
-    long long *prof;
-    int dbg;
 };
 
 /* a wait gave up (its own limit, or another role's abort flag): the first to get here names the block; every role of that block then leaves
@@ -98,15 +91,12 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             pdl_wait();      /* the only role that reads activations from global memory; every other role's data comes through this thread's loads,
                                 so the weight load, the B scale copies and the zeroing of the accumulators overlap the previous kernel */
             int s = 0, ph = 0, it = 0; bool ok = true;
-            KP(long long p_wait = 0; const long long p_t0 = clock64();)
             /* job = (row tile, column tile), column tile fastest; the indices advance incrementally (no division per job) */
             int ntile = (int)(j0 % a.ntiles), n = (int)((j0 / a.ntiles) / a.rtiles_per_n), tin = (int)((j0 / a.ntiles) % a.rtiles_per_n);
             for (long long job = j0; job < j1 && ok; job++) {
                 const int cx = tin * 256, pl0 = BITS == 8 ? n * a.nkb * 2 : n * a.nkb, cs = tin * 128, pls = n * a.nkb;
                 for (int g = 0; g < a.ngroups; g++) {
-                    KP(const long long pw0 = clock64();)
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 1, it); ok = false; break; }
-                    KP(p_wait += clock64() - pw0;)
                     const int items = min(4, a.nki - 4 * g);
                     const uint32_t sb = smem_u32(stages + (size_t)s * a.stage_bytes), bar = bar_tma + 8 * s;
                     mbar_expect_tx(bar, (uint32_t)(items * 4096 + a.sw_rows * 128));
@@ -116,7 +106,6 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                 }
                 if (++ntile == a.ntiles) { ntile = 0; if (++tin == (int)a.rtiles_per_n) { tin = 0; n++; } }
             }
-            KP(a.prof[(size_t)blockIdx.x * 32 + 16] = p_wait; a.prof[(size_t)blockIdx.x * 32 + 17] = clock64() - p_t0; a.prof[(size_t)blockIdx.x * 32 + 24] = it;)
         }
     } else if (warp == 1) {
         /* ---------------- MMA issue ---------------- */
@@ -134,19 +123,14 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             const uint32_t b_lo0 = desc_lo(wbase, (uint32_t)a.ntp * 16), b_item = 2u * (uint32_t)a.ntp, b_tile = (uint32_t)a.nki * b_item;
             int s = 0, ph = 0, it = 0, slot = 0, sph = 0;
             long long job = j0; int ntile = (int)(j0 % a.ntiles);
-            KP(long long m_full = 0, m_acce = 0, m_issue = 0; const long long m_t0 = clock64();)
             while (ok && job < j1) {
                 const int n_cur = min(a.ntp, a.cop - ntile * a.ntp);
                 const uint32_t idn = idesc_b | ((uint32_t)(n_cur >> 3) << 17), d = tmem + (uint32_t)(slot * a.ntp);
-                KP(const long long ma0 = clock64();)
                 if (!mbar_wait(bar_acce + 8 * slot, (uint32_t)(sph ^ 1), abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 7, it); break; }
-                KP(m_acce += clock64() - ma0;)
                 for (int g = 0; g < a.ngroups; g++) {
-                    KP(const long long mw0 = clock64();)
                     if (!mbar_wait(bar_sf + 8 * s, ph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 3, it); ok = false; break; }
                     if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 2, it); ok = false; break; }
                     tc_fence_after();
-                    KP(const long long mw1 = clock64(); m_full += mw1 - mw0;)
                     const uint32_t a_lo = a_lo0 + (uint32_t)s * a_step, sfa_t = tmem + (uint32_t)a.sfa_base + ((uint32_t)it & 1u) * 8u;
                     const uint32_t sfb_t = tmem + (uint32_t)a.sfb_base + (uint32_t)((ntile * a.ngroups + g) * NQ * 4);
                     const uint32_t bb = b_lo0 + (uint32_t)ntile * b_tile + (uint32_t)(4 * g) * b_item;
@@ -162,23 +146,18 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                     }
                     if (g == a.ngroups - 1) umma_commit(bar_accf + 8 * slot);
                     umma_commit(bar_empty + 8 * s);
-                    KP(m_issue += clock64() - mw1;)
                     it++; if (++s == R) { s = 0; ph ^= 1; }
                 }
                 if (++slot == NS) { slot = 0; sph ^= 1; }
                 job++; if (++ntile == a.ntiles) ntile = 0;
             }
-            KP({ long long *q = a.prof + (size_t)blockIdx.x * 32; q[18] = m_full; q[19] = m_acce; q[20] = m_issue; q[21] = clock64() - m_t0; })
         }
     } else if (warp == 2) {
         /* ---------------- A scale layout: the window holds, per block of the stage, the scale bytes of the 128 rows ---------------- */
         int s = 0, ph = 0, it = 0; bool ok = true;
         const long long nst = (j1 - j0) * a.ngroups;
-        KP(long long g_wait = 0; const long long g_t0 = clock64();)
         for (long long i = 0; i < nst && ok; i++) {
-            KP(const long long gw0 = clock64();)
             if (!mbar_wait(bar_tma + 8 * s, ph, abort_flag, kWaitLimitP)) { if (lane == 0) raise_p(a, abort_flag, 4, it); ok = false; break; }
-            KP(g_wait += clock64() - gw0;)
             uint8_t *stg = stages + (size_t)s * a.stage_bytes;
             const uint8_t *sw = stg + a.offSW;
             uint32_t *sfa = (uint32_t *)(stg + a.offSFA);
@@ -195,7 +174,6 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             if (lane == 0) mbar_arrive(bar_sf + 8 * s);
             it++; if (++s == R) { s = 0; ph ^= 1; }
         }
-        KP(if (lane == 0) { a.prof[(size_t)blockIdx.x * 32 + 22] = g_wait; a.prof[(size_t)blockIdx.x * 32 + 25] = clock64() - g_t0; })
     } else if (warp >= 4) {
         /* ---------------- epilogue: two groups of four warps; a job of two 32-column chunks gives one to each group, jobs of one chunk
            alternate between the groups.  Both groups wait for and release every accumulator slot. ---------------- */
@@ -204,21 +182,17 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
         int slot = 0, sph = 0, pc = 0; bool dead = false;
         long long job = j0; int ntile = (int)(j0 % a.ntiles), n = (int)((j0 / a.ntiles) / a.rtiles_per_n), tin = (int)((j0 / a.ntiles) % a.rtiles_per_n);
         const unsigned Su = (unsigned)a.S, HWu = (unsigned)a.HW, Wu = (unsigned)a.W;
-        KP(long long e_wait = 0, e_ld = 0, e_epi = 0; const long long e_t0 = clock64();)
         for (; job < j1 && !dead; job++, pc++) {
             const int n_cur = min(a.ntp, a.cop - ntile * a.ntp), nchunk = n_cur >> 5;
             const bool mine = nchunk > 1 ? true : (pc & 1) == eg;
             const int jc = nchunk > 1 ? eg : 0;
-            KP(const long long ew0 = clock64();)
             if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)sph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 5, pc); dead = true; break; }
-            KP(const long long ew1 = clock64(); e_wait += ew1 - ew0;)
             tc_fence_after();
             uint32_t rr[32];
             if (mine) { tmem_ld32(tlane + (uint32_t)(slot * a.ntp + jc * 32), rr); tmem_ld_wait(); }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acce + 8 * slot);     /* one arrival per warp: arrivals on one barrier serialise */
-            KP(const long long ew2 = clock64(); e_ld += ew2 - ew1;)
             if (mine) {
                 const unsigned vo = (unsigned)tin * 128u + (unsigned)r;
                 const bool row_ok = vo < Su;
@@ -235,11 +209,9 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
                 if (EPI == 6) { e.out_mode = UMX_OUT_MX; e.out_bits = 4; e.tconv = 1; }
                 epi_chunk(e, n, (int)zu, (int)oyu, (int)(rem - oyu * Wu), row_ok, ntile * (a.ntp >> 5) + jc, v);
             }
-            KP(e_epi += clock64() - ew2;)
             if (++slot == NS) { slot = 0; sph ^= 1; }
             if (++ntile == a.ntiles) { ntile = 0; if (++tin == (int)a.rtiles_per_n) { tin = 0; n++; } }
         }
-        KP(if (threadIdx.x == 128) { a.prof[(size_t)blockIdx.x * 32 + 23] = e_wait; a.prof[(size_t)blockIdx.x * 32 + 26] = clock64() - e_t0; a.prof[(size_t)blockIdx.x * 32 + 27] = pc; a.prof[(size_t)blockIdx.x * 32 + 28] = e_ld; a.prof[(size_t)blockIdx.x * 32 + 29] = e_epi; })
     }
     /* ---------------- teardown ---------------- */
     tc_fence_before();
@@ -363,10 +335,6 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     const long long slots = (long long)sms * (two ? 2 : 1);
     const int grid = (int)(a.jobs < slots ? a.jobs : slots);
     const size_t smem = (size_t)a.off_ring + (size_t)a.ring * a.stage_bytes;
-#ifdef UMX_KPROF
-    a.dbg = getenv("UMX_DBG") ? atoi(getenv("UMX_DBG")) : 0;
-    a.prof = (long long *)umx_ws(7, (size_t)grid * 256); cudaMemset(a.prof, 0, (size_t)grid * 256);
-#endif
     int epi = 0;
     if (e.out_mode == UMX_OUT_PM32 && !e.tconv) epi = 1;
     else if (e.out_mode == UMX_OUT_PM16 && !e.tconv) epi = 2;
@@ -376,11 +344,5 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; case 5: UMX_P_GO(8, 5); break; case 6: UMX_P_GO(8, 6); break; default: UMX_P_GO(8, 0); } }
     else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; case 5: UMX_P_GO(4, 5); break; case 6: UMX_P_GO(4, 6); break; default: UMX_P_GO(4, 0); } }
 #undef UMX_P_GO
-#ifdef UMX_KPROF
-    { static long long hb[512 * 32]; cudaMemcpy(hb, a.prof, (size_t)grid * 256, cudaMemcpyDeviceToHost);
-      double t[14] = {0}; for (int b = 0; b < grid; b++) for (int k = 0; k < 14; k++) t[k] += (double)hb[b * 32 + 16 + k] / grid;
-      fprintf(stderr, "kprof-p: kind %d grid %d jobs %lld ring %d slots %d tmem %d nki %d ntp %d ntiles %d smem %zu | per block: stages %.0f jobs %.0f | producer total %.0f wait-empty %.0f | mma total %.0f wait-full %.0f wait-slot %.0f issue %.0f | gather total %.0f wait %.0f | epilogue total %.0f wait %.0f ld %.0f epi %.0f\n",
-              c->kind, grid, a.jobs, a.ring, a.nslot, a.tmem_cols, a.nki, a.ntp, a.ntiles, smem, t[8], t[11], t[1], t[0], t[5], t[2], t[3], t[4], t[9], t[6], t[10], t[7], t[12], t[13]); }
-#endif
     return 0;
 }
