@@ -20,6 +20,7 @@ void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y);
 void umx_blend_add_fx(const float *logits, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, long long *acc, long long *wsum);
 void umx_emit_fx(const long long *acc, const long long *wsum, const uint8_t *mode, int want, int nh, int V, int zext, int za, int zb, int ya, int yb, int fmt, void *out);
 void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size_t spitch, size_t width, size_t height, int to_device, void *stream);
+void umx_gather_u8_h16(const uint8_t *vol_dev, int V, int z, int y, int x, int P, void *out);
 void umx_emit_rows_fx(const long long *acc, const long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int fmt, void *out);
 void umx_rows_fx(long long *acc, long long *wsum, const int *zy_dev, long nrows, int nh, int V, int zext, int dir, long long *buf);
 void umx_blend_add(const void *logits, int fmt, int nh, int P, int V, int zlo, int zext, int z0, int y0, int x0, const float *w1d, float *acc, float *wsum);
@@ -266,8 +267,11 @@ struct umx_wplan {
     umx_window w; int rank, world, first, count, zlo, zhi, nh;
     uint8_t *mode;                    /* host [zext][V]: 0 not touched by this rank, 1 this rank's alone, 2 this rank's, shared with higher ranks, 3 a lower rank's */
     long nsend[WP_MAXPEER], nrecv[WP_MAXPEER], nmine2; int *send_zy[WP_MAXPEER], *recv_zy[WP_MAXPEER], *mine2_zy;   /* (z - zlo, y) pairs in ascending order */
-    long long *acc, *wsum; uint8_t *mode_dev; void *out_dev, *fin_dev; uint8_t *fin_host, *stage[2]; float *logits; int out_fmt, batch; float *w1d; int *zy_dev; long zy_cap;
+    long long *acc, *wsum; uint8_t *mode_dev; void *out_dev, *fin_dev; uint8_t *fin_host; float *logits; int out_fmt, batch; float *w1d; int *zy_dev; long zy_cap;
     void *ev_emit;
+    /* the rank's planes of the volume on the device: uploaded piece by piece just ahead of the patches that read them (planes [zlo, zu)
+       whole; of the current patch layer's new planes [ln0, ln1) the rows [yu0, yu)), each piece followed by an event of a ring of four */
+    uint8_t *vol_dev; void *ev_vol[4]; int zu, lz0, ln0, ln1, yu0, yu, slot;
 };
 static void wp_rows_of_rank(const umx_window *w, int rank, int world, int *first, int *count) { umx_window_share(w, rank, world, first, count); }
 umx_wplan *umx_wplan_create(const umx_window *w, int rank, int world, int nh) {
@@ -325,7 +329,8 @@ void umx_wplan_free(umx_wplan *p) {
     for (int r = 0; r < WP_MAXPEER; r++) { free(p->send_zy[r]); free(p->recv_zy[r]); }
     free(p->mine2_zy); free(p->mode);
     nn_free(p->acc); nn_free(p->wsum); nn_free(p->mode_dev); nn_free(p->out_dev); nn_free(p->fin_dev); nn_free(p->logits); nn_free(p->w1d); nn_free(p->zy_dev); umx_event_free(p->ev_emit);
-    nn_free_host(p->fin_host); nn_free_host(p->stage[0]); nn_free_host(p->stage[1]);
+    nn_free_host(p->fin_host);
+    nn_free(p->vol_dev); for (int i = 0; i < 4; i++) umx_event_free(p->ev_vol[i]);
     free(p);
 }
 void umx_wplan_info(const umx_wplan *p, int *first, int *count, int *zlo, int *zhi) { *first = p->first; *count = p->count; *zlo = p->zlo; *zhi = p->zhi; }
@@ -350,7 +355,8 @@ static int wp_alloc(umx_wplan *p, int out_fmt, int batch, size_t PS) {
     if (!p->acc) {
         p->acc = nn_malloc((size_t)p->nh * zext * plane * 8); p->wsum = nn_malloc((size_t)zext * plane * 8);
         p->mode_dev = nn_malloc((size_t)zext * V); p->w1d = nn_malloc((size_t)P * 4); p->ev_emit = umx_event_new();
-        if (!p->acc || !p->wsum || !p->mode_dev || !p->w1d || !p->ev_emit) return -1;
+        p->vol_dev = nn_malloc((size_t)zext * plane); for (int i = 0; i < 4; i++) p->ev_vol[i] = umx_event_new();
+        if (!p->acc || !p->wsum || !p->mode_dev || !p->w1d || !p->ev_emit || !p->vol_dev || !p->ev_vol[3]) return -1;
         float w1d_h[1024]; if (P > 1024) abort();
         { const double s = P / 8.0, c = (double)(P / 2);   /* the reference's centre: the integer P / 2 (g1_init, src/nn_ink3dext.cu:48-56) */
           for (int i = 0; i < P; i++) { const double d = (i - c) / s; w1d_h[i] = (float)exp(-0.5 * d * d); } }
@@ -364,9 +370,9 @@ static int wp_alloc(umx_wplan *p, int out_fmt, int batch, size_t PS) {
         if (!p->out_dev || !p->fin_dev || !p->fin_host) return -1;
     }
     if (p->batch < batch) {
-        nn_sync(); nn_free(p->logits); nn_free_host(p->stage[0]); nn_free_host(p->stage[1]);
-        p->logits = nn_malloc((size_t)batch * p->nh * PS * 4); p->stage[0] = nn_malloc_host((size_t)batch * PS); p->stage[1] = nn_malloc_host((size_t)batch * PS); p->batch = batch;
-        if (!p->logits || !p->stage[0] || !p->stage[1]) { p->batch = 0; return -1; }
+        nn_sync(); nn_free(p->logits);
+        p->logits = nn_malloc((size_t)batch * p->nh * PS * 4); p->batch = batch;
+        if (!p->logits) { p->batch = 0; return -1; }
     }
     return nn_check() ? -1 : 0;
 }
@@ -392,6 +398,25 @@ static void wp_emit_box(umx_unet *u, umx_wplan *p, int za, int zb, int ya, int y
         umx_copy2d_async((uint8_t *)out_host + o, plane * el, (uint8_t *)p->out_dev + o, plane * el, (size_t)(yb - ya) * V * el, (size_t)(zb - za), 0, u->s_out);
     }
 }
+/* issues the upload of what patch q reads of the volume and has not been uploaded yet: patches come in (z, y, x) order, so a layer's new
+   planes are uploaded row range by row range as its patch rows come up (2-D copies on the copy stream; the host memory may be pageable) */
+static void wp_upload(umx_unet *u, umx_wplan *p, const uint8_t *vol, int q) {
+    const umx_window *w = &p->w; const int P = w->P, V = w->V; const size_t plane = (size_t)V * V;
+    int z0, y0, x0; umx_window_origin(w, q, &z0, &y0, &x0);
+    if (z0 != p->lz0) {
+        if (p->lz0 >= 0 && p->yu0 == 0 && p->yu >= V && p->ln1 > p->zu) p->zu = p->ln1;      /* the layer before was uploaded in full */
+        p->lz0 = z0; p->ln0 = z0 > p->zu ? z0 : p->zu; p->ln1 = z0 + P < p->zhi ? z0 + P : p->zhi;
+        if (p->ln0 > p->ln1) p->ln0 = p->ln1;
+        p->yu0 = p->yu = y0;
+    }
+    const int ye = y0 + P < V ? y0 + P : V;
+    if (ye <= p->yu || p->ln1 <= p->ln0) return;
+    const size_t off = (size_t)p->yu * V;
+    umx_copy2d_async(p->vol_dev + (size_t)(p->ln0 - p->zlo) * plane + off, plane, vol + (size_t)p->ln0 * plane + off, plane, (size_t)(ye - p->yu) * V, (size_t)(p->ln1 - p->ln0), 1, u->s_in);
+    p->yu = ye;
+    p->slot = (p->slot + 1) & 3;
+    umx_event_record(p->ev_vol[p->slot], u->s_in);
+}
 /* Forwards this rank's patches of the volume (vol_host: the V^3 uint8 volume; only the planes of the rank's extent are read), blends them,
    and delivers the rows that are this rank's alone to out_host [nh][zhi - zlo][V][V] (pinned), out_fmt UMX_F16 (blended logits) or UMX_U8OUT
    (round(254 sigmoid)).  Rows shared with other ranks are left to umx_wplan_pack / umx_wplan_add / umx_wplan_finish.  Returns 0, or -1 with
@@ -403,33 +428,23 @@ int umx_window_run_fx(umx_unet *u, umx_wplan *p, const uint8_t *vol, int batch, 
     const int zext = p->zhi - p->zlo; if (zext <= 0 || p->count <= 0) return 0;
     const size_t PS = cube(P), plane = (size_t)V * V;
     if (wp_alloc(p, out_fmt, batch, PS) || pipe_init(u)) return -1;
-    float *logits = p->logits; uint8_t **stage = p->stage;
+    float *logits = p->logits;
     nn_zero(p->acc, (size_t)nh * zext * plane * 8); nn_zero(p->wsum, (size_t)zext * plane * 8);
     /* emission: [ra, rb) the planes from the end of the previous layer's own planes to the origin of the next layer (no later layer touches
        them), lz the current layer's origin, y_done the first row of those planes not delivered yet */
     long j = 0; int lz = -1, ra = p->zlo, rb = p->zlo, y_done = 0, y_row = -1;
-    for (int q = p->first; q < p->first + p->count; q += batch, j++) {
-        const int nb = q + batch <= p->first + p->count ? batch : p->first + p->count - q, k = (int)(j & 1);
-        if (j >= 2) umx_event_sync(u->ev_up[k]);                 /* the staging buffer's upload of two batches ago has finished */
+    p->zu = p->zlo; p->lz0 = -1; p->ln0 = p->ln1 = p->zlo; p->yu0 = p->yu = 0; p->slot = 0;
+    const int last = p->first + p->count;
+    for (int q = p->first; q < last; q += batch, j++) {
+        const int nb = q + batch <= last ? batch : last - q;
+        for (int i = 0; i < nb; i++) wp_upload(u, p, vol, q + i);       /* issued a batch ago by the look-ahead below, as a rule */
+        umx_stream_wait(nullptr, p->ev_vol[p->slot]);
         for (int i = 0; i < nb; i++) {
             int z0, y0, x0; umx_window_origin(w, q + i, &z0, &y0, &x0);
-            uint8_t *dst = stage[k] + (size_t)i * PS;
-            for (int z = 0; z < P; z++) for (int y = 0; y < P; y++) {
-                const int gz = z0 + z, gy = y0 + y;
-                uint8_t *row = dst + ((size_t)z * P + y) * P;
-                if (gz >= V || gy >= V) { memset(row, 0, (size_t)P); continue; }
-                const int nx = x0 + P <= V ? P : V - x0;
-                memcpy(row, vol + (size_t)gz * plane + (size_t)gy * V + x0, (size_t)nx);
-                if (nx < P) memset(row + nx, 0, (size_t)(P - nx));
-            }
+            umx_gather_u8_h16(p->vol_dev, V, z0 - p->zlo, y0, x0, P, (uint8_t *)u->x16 + (size_t)i * PS * 2);
         }
-        umx_stream_wait(u->s_in, u->ev_used[k]);                 /* the device copy of two batches ago has been converted */
-        umx_copy_async(u->pxu8[k], stage[k], (size_t)nb * PS, 1, u->s_in);
-        umx_event_record(u->ev_up[k], u->s_in);
-        umx_stream_wait(nullptr, u->ev_up[k]);
-        umx_u8_to_h16(u->pxu8[k], (size_t)nb * PS, u->x16);
-        umx_event_record(u->ev_used[k], nullptr);
         forward(u, u->x16, nb, logits, UMX_F32);
+        for (int i = 0; i < batch && q + nb + i < last; i++) wp_upload(u, p, vol, q + nb + i);      /* while the GPU works on this batch */
         for (int i = 0; i < nb; i++) {
             int z0, y0, x0; umx_window_origin(w, q + i, &z0, &y0, &x0);
             if (z0 != lz) {           /* a new patch layer: what is left of the previous layer's own planes has had its last contribution from this rank */

@@ -15,6 +15,43 @@ extern "C" void umx_u8_to_h16(const uint8_t *x, size_t n, void *y) {
     g_umx_launches++;
     UMX_CK("umx_u8_to_h16");
 }
+/* one P^3 patch at (z, y, x) of a uint8 volume slab on the device (planes of V x V voxels, z counted from the slab's first plane) -> fp16
+   intensities x / 255, the patch contiguous; voxels beyond the volume's y / x extent read as zero.  Eight voxels of a row a thread when
+   the rows allow 8-byte loads. */
+__global__ void __launch_bounds__(256) gather_u8_h16_k(const uint8_t *__restrict__ vol, int V, int z, int y, int x, int P, __half *__restrict__ out, int vec) {
+    pdl_trigger(); pdl_wait();
+    const size_t plane = (size_t)V * V;
+    if (vec) {
+        const int P8 = P / 8; const size_t n8 = (size_t)P * P * P8;
+        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+            const int px = (int)(i % P8) * 8, py = (int)((i / P8) % P), pz = (int)(i / ((size_t)P8 * P));
+            uint2 v = make_uint2(0u, 0u);
+            if (y + py < V && x + px + 8 <= V) v = __ldg((const uint2 *)(vol + (size_t)(z + pz) * plane + (size_t)(y + py) * V + x + px));
+            __half2 h[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const unsigned w = (k < 2 ? v.x : v.y) >> (16 * (k & 1));
+                h[k] = __floats2half2_rn(__fdiv_rn((float)(w & 0xffu), 255.f), __fdiv_rn((float)((w >> 8) & 0xffu), 255.f));
+            }
+            *(uint4 *)(out + ((size_t)pz * P + py) * P + px) = *(const uint4 *)h;
+        }
+    } else {
+        const size_t n = (size_t)P * P * P;
+        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+            const int px = (int)(i % P), py = (int)((i / P) % P), pz = (int)(i / ((size_t)P * P));
+            const float v = (y + py < V && x + px < V) ? (float)vol[(size_t)(z + pz) * plane + (size_t)(y + py) * V + x + px] : 0.f;
+            out[i] = __float2half_rn(__fdiv_rn(v, 255.f));
+        }
+    }
+}
+extern "C" void umx_gather_u8_h16(const uint8_t *vol_dev, int V, int z, int y, int x, int P, void *out) {
+    if (!umx_ready("umx_gather_u8_h16")) return;
+    const int vec = !((V | P | x) & 7) && x + P <= V && !((size_t)vol_dev & 7) && !((size_t)out & 15);
+    size_t g = ((size_t)P * P * P / (vec ? 8 : 1) + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; if (!g) g = 1;
+    umx_launch(gather_u8_h16_k, dim3((unsigned)g), dim3(256), 0, vol_dev, V, z, y, x, P, (__half *)out, vec);
+    g_umx_launches++;
+    UMX_CK("umx_gather_u8_h16");
+}
 /* fp16 logits -> uint8 round(254 / (1 + exp(-l))): the per-patch form of the reference's probability output (pred_place_k, src/nn_elem.cu:1117-1125,
    rounds 255 p + 0.5 down; the blended path's k_i3_emit uses round(254 p), which is what this library uses throughout) */
 __device__ __forceinline__ unsigned prob_u8(float l) { return (unsigned)__float2int_rn(__fmul_rn(__fdiv_rn(1.f, __fadd_rn(1.f, expf(-l))), 254.f)) & 0xffu; }
