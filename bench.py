@@ -37,44 +37,47 @@ def peaks():
 
 
 class Clocks(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML; nvidia-smi as a fallback)."""
+    """SM clock and throttle reasons of one GPU during the timed regions.  One `nvidia-smi -lms` child process streams a line every
+    `interval` seconds for the whole run and this thread keeps the lines that arrive while a timed region is open (`live`): nothing in
+    this process talks to NVML then.  (In-process NVML queries turned out to hold a lock that kernel launches need: a query landing in a
+    30 ms launch loop stalled it for tens of ms, several ranks querying at once for longer.)  Without nvidia-smi: in-process NVML, queried
+    from a helper thread only after the last launch of a region."""
 
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu, interval=0.1):
+    def __init__(self, gpu, interval=0.05):
         super().__init__(daemon=True)
         self.gpu, self.rows, self.stop, self.max_mhz, self.interval = gpu, [], False, None, interval
-        self.ready = threading.Event()          # set once the sampler is initialised (NVML start-up stalls kernel launches for tens of ms)
-        self.t_on = None                         # samples before this time (warm-up) are dropped
-        self.periodic = False                    # the thread samples by itself only in long timed regions (the window run): an NVML query holds a
-                                                 # driver lock that kernel launches need, and a query that lands inside a 30 ms launch loop of several
-                                                 # ranks at once has stalled it for tens of ms; the short regions are sampled by the main thread
-                                                 # after their last launch, while the GPU is still working through them
+        self.ready = threading.Event()
+        self.live = False                        # a timed region is open
+        self.proc, self.nv, self.mode = None, None, None
         self.q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def _index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        return int(vis.split(",")[self.gpu]) if vis and all(t.strip().isdigit() for t in vis.split(",")) else self.gpu
 
     def _nvml(self):
         import pynvml as nv
         nv.nvmlInit()
-        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-        idx = int(vis.split(",")[self.gpu]) if vis and all(t.strip().isdigit() for t in vis.split(",")) else self.gpu
-        self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(idx)
+        self.h = nv.nvmlDeviceGetHandleByIndex(self._index())
         self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
         self.bits = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown, nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+        self.nv = nv
 
     def sample_aside(self, n=1):
-        """n samples from a helper thread, started now: for the moment after the last launch of a short timed region, when the GPU is
-        still working through it and the launching thread goes on to wait for it (a query can take tens of ms on a busy host)."""
+        """NVML mode only: n samples from a helper thread, started now (after the last launch of a short timed region, while the GPU is
+        still working through it and the launching thread goes on to wait for it)."""
         def go():
             for _ in range(n):
                 self.sample_once()
                 time.sleep(0.002)
-        t = threading.Thread(target=go, daemon=True)
+        t = threading.Thread(target=go if self.mode == "nvml" else (lambda: None), daemon=True)
         t.start()
         return t
 
     def sample_once(self):
-        """One sample from the calling thread (used while the timed steps are queued on the GPU, so that a short run has one too)."""
-        if getattr(self, "nv", None) is None:
+        if self.nv is None:
             return
         try:
             r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
@@ -84,26 +87,39 @@ class Clocks(threading.Thread):
 
     def run(self):
         try:
-            self._nvml()
-            self.ready.set()
-            while not self.stop:
-                if self.t_on is not None and self.periodic:
-                    self.sample_once()
-                time.sleep(self.interval)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self._index()), "--query-gpu=" + self.q, "--format=csv,noheader,nounits", "-lms", str(max(10, int(self.interval * 1000)))],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
+            for line in self.proc.stdout:
+                f = [t.strip() for t in line.strip().split(",")]
+                if len(f) >= 6 and f[0].isdigit():
+                    self.max_mhz = int(f[1]) if f[1].isdigit() else self.max_mhz
+                    if not self.ready.is_set():
+                        self.mode = "smi"
+                        self.ready.set()
+                    if self.live:
+                        self.rows.append([int(f[0])] + [t.lower().startswith("active") for t in f[2:6]])
+                if self.stop:
+                    break
+        except Exception:
+            pass
+        if self.mode == "smi":
             return
+        try:
+            self._nvml()
+            self.mode = "nvml"
         except Exception:
             self.nv = None
         self.ready.set()
         while not self.stop:
+            time.sleep(0.1)
+
+    def close(self):
+        self.stop = True
+        if self.proc is not None:
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.q, "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                f = [t.strip() for t in out.strip().split(",")]
-                if len(f) >= 6 and f[0].isdigit() and self.t_on is not None and self.periodic:
-                    self.max_mhz = int(f[1]) if f[1].isdigit() else self.max_mhz
-                    self.rows.append([int(f[0])] + [t.lower().startswith("active") for t in f[2:6]])
+                self.proc.terminate()          # the child this object started, by its handle
             except Exception:
                 pass
-            time.sleep(0.1)
 
     def summary(self):
         if not self.rows:
@@ -228,15 +244,18 @@ def run_ops(args):
     print("%-22s %d ch on %d^3 fp16 -> MX-fp%d: %.1f us, %.0f GB/s" % ("lp_h16_to_mx", Cn, D, bits, us, gbs))
 
 
-def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
+def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier, clk=None):
     from ufsm_b200 import synth
     w = L.umx_window_make(Vw, P, 16)
     plan = L.umx_wplan_create(C.byref(w), rank, world, NH)
     f, cnt, lo, hi = C.c_int(), C.c_int(), C.c_int(), C.c_int()
     L.umx_wplan_info(plan, C.byref(f), C.byref(cnt), C.byref(lo), C.byref(hi))
     zext = hi.value - lo.value
-    slab = synth.sheet_slab(500, Vw, lo.value, hi.value)                    # this rank's planes of the volume only
-    vol_ptr = slab.ctypes.data - lo.value * Vw * Vw                           # addressed with volume coordinates; only [lo, hi) is read
+    slab = synth.sheet_slab(500, Vw, lo.value, hi.value)                    # this rank's planes of the volume only,
+    vol_pin = L.nn_malloc_host(slab.size)                                    # in pinned host memory (as the e2e patches are): the run uploads them
+    C.memmove(vol_pin, slab.ctypes.data, slab.size)                          # with asynchronous copies while patches are computed
+    del slab
+    vol_ptr = vol_pin - lo.value * Vw * Vw                                    # addressed with volume coordinates; only [lo, hi) is read
     out_bytes = NH * zext * Vw * Vw
     out_host = L.nn_malloc_host(out_bytes)
     sends, recvs = [], []
@@ -260,6 +279,8 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
         torch.cuda.synchronize()
     assert L.umx_wplan_prepare(plan, u.h, B, 100) == 0, (L.lp_check() or b"").decode()      # buffers of the run, allocated once per volume
     barrier()
+    if clk is not None:
+        clk.live = True
     L.umx_timer_start(timer)
     t_a = time.time()
     rc = L.umx_window_run_fx(u.h, plan, vol_ptr, B, 100, out_host)
@@ -279,7 +300,10 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
     t_c = time.time()
     assert L.umx_wplan_finish(plan, out_host) == 0, (L.lp_check() or b"").decode()
     t_d = time.time()
-    ms = tmax(L.umx_timer_stop_ms(timer))
+    ms = L.umx_timer_stop_ms(timer)
+    if clk is not None:
+        clk.live = False
+    ms = tmax(ms)
     phases = {"forward_blend_emit_s": round(t_b - t_a, 4), "exchange_s": round(t_c - t_b, 4), "finish_shared_rows_s": round(t_d - t_c, 4)}
     # a checksum of the rows this rank delivered, so that runs at different rank counts can be compared (the volume is the same bytes)
     mode = np.zeros((zext, Vw), np.uint8)
@@ -297,6 +321,7 @@ def run_window(L, u, rank, world, local, dist, Vw, B, timer, tmax, barrier):
         csum, counts, nshared = int(sum(int(x[0]) for x in g)), [int(x[1]) for x in g], int(sum(int(x[2]) for x in g))
     L.umx_wplan_free(plan)
     L.nn_free_host(out_host)
+    L.nn_free_host(vol_pin)
     dt = ms * 1e-3
     return {"workload": "config 5: %d^3 uint8 sheet volume, 128^3 patches, overlap 16 (stride 112), %d patches, Gaussian blend, (z, y) patch rows dealt by z-slab over %d GPU(s)" % (Vw, w.npatch, world),
             "scaling": "strong", "seconds": dt, "value": Vw ** 3 / dt, "unit": "volume voxels/s", "patches_per_s": w.npatch / dt, "patches_per_rank": counts,
@@ -377,7 +402,7 @@ def run_gpu(args):
     for _ in range(args.warmup):
         L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
     ufsm_b200.check()
-    clk.t_on = time.time()
+    clk.live = True
     # ---- device-resident: K steps, events on the launching stream, barrier + synchronise on both sides, max over ranks
     barrier()
     n0 = L.umx_launch_count()
@@ -385,8 +410,9 @@ def run_gpu(args):
     for _ in range(args.steps):
         L.umx_unet_forward(u.h, xd.ptr, B, yd.ptr)
     L.umx_timer_mark(timer)            # the stop event sits behind the last launch; the GPU is still working through the steps,
-    side = clk.sample_aside(3)         # which is when the clocks and throttle reasons of this timed region are read
+    side = clk.sample_aside(3)         # which is when the clocks and throttle reasons are read where NVML has to be asked in-process
     ms = L.umx_timer_read_ms(timer)
+    clk.live = False
     side.join(5)
     launches = L.umx_launch_count() - n0
     barrier()
@@ -401,12 +427,14 @@ def run_gpu(args):
             submit(u.h, hin, B, hout if i & 1 else hout2)
         assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()
         barrier()
+        clk.live = True
         L.umx_timer_start(timer)
         for i in range(args.steps):
             submit(u.h, hin, B, hout if i & 1 else hout2)
         side = clk.sample_aside(2)
         assert L.umx_unet_wait(u.h) == 0, (L.lp_check() or b"").decode()       # waits for the last step's download: the timed work is complete
         v = tmax(L.umx_timer_stop_ms(timer))
+        clk.live = False
         side.join(5)
         barrier()
         return v
@@ -453,9 +481,7 @@ def run_gpu(args):
     # stream from the first patch to the last byte on the host, max over ranks.
     win = None
     if args.window:
-        clk.periodic = True
-        win = run_window(L, u, rank, world, local, dist, args.window, B, timer, tmax, barrier)
-        clk.periodic = False
+        win = run_window(L, u, rank, world, local, dist, args.window, B, timer, tmax, barrier, clk)
     # ---- single layers of configurations 1 and 2 and the quantiser (rank 0 reports them; parity of these shapes is in the tests)
     extra = None
     if rank == 0:
@@ -471,7 +497,7 @@ def run_gpu(args):
                  "config2_tconv2_128x64_to_96cube_mxfp4": {"us": round(u2[0], 1), "tflops": round(u2[1], 1), "gbs": round(u2[2] / u2[0] / 1e3)},
                  "quantiser_fp16_to_mx": {"config1_32x64cube_fp8": {"us": round(q1[0], 1), "gbs": round(q1[1])}, "32x128cube_fp8": {"us": round(q0[0], 1), "gbs": round(q0[1])},
                                           "32x128cube_fp4": {"us": round(q4[0], 1), "gbs": round(q4[1])}, "note": "algorithmic bytes (2 B read + MX bytes written per element) / best event time"}}
-    clk.stop = True
+    clk.close()
     clk.join(2)
     ufsm_b200.check()
     if rank != 0:
