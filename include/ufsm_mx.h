@@ -188,6 +188,15 @@ void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int ydt, gnp_t gp
    of w x with fma; cout <= 16, or a multiple of 16 for one sample; gp as above (src/nn_lp.h:138-139, src/lp_mx_conv1.cu:4-22, 422-444). */
 void lp_conv1_fwd_mx(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, float *y, gnp_t gp);
 void lp_conv1_fwd_mx_h16(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, void *y, gnp_t gp);
+/* src/nn_lp.h:140-141: the logits of voxels [vb, vb + nv) alone (nv 0: all) into planes of nv voxels (fp16) or of ly >= nv voxels (fp32, one
+   sample; returns -1 for N != 1 or nv == 0 as the reference does): per voxel the bits of the whole-tensor entries */
+void lp_conv1_fwd_mx_h16_r(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, void *y, gnp_t gp, size_t vb, size_t nv);
+int lp_conv1_fwd_mx_r(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, float *y, gnp_t gp, size_t vb, size_t nv, size_t ly);
+/* src/nn_lp.h:137: the upsample of the 32-channel blocks [b0, b0 + nbk) of x alone; y: an MX tensor of 32 nbk channels */
+void lp_up2_fwd_mx_blocks(const void *x, int xdt, shape5 xs, int b0, int nbk, void *y, int ydt);
+/* src/nn_lp.h:135, src/lp_mx_gn.cu:133-150: y += x for two MX tensors of the same format (dt 8 / 4 bits), rows re-encoded; sr (stochastic
+   rounding) must be 0 */
+void lp_add_mx(void *y, const void *x, shape5 s, int dt, unsigned sr);
 int lp_gn_sums_mx(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1);
 int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0, int cnt);
 void umx_gn_finalize(const double *sums, int NG, size_t len, float eps, float *mean, float *rstd);

@@ -82,3 +82,51 @@ def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
         assert orc.rel_l2(got, want) < 1e-5
     else:
         assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_up2_blocks_conv1_ranges_and_add(dev, bits):
+    """lp_up2_fwd_mx_blocks (the upsample of a range of 32-channel blocks), lp_conv1_fwd_mx_r / _h16_r (a range of voxels: the bits of the
+    whole-tensor call), lp_add_mx (y += x, rows re-encoded)."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp
+    L = ufsm_b200.lib()
+    dt = 3 if bits == 8 else 4
+    N, Cn, D, H, W = 2, 96, 3, 5, 9
+    S = D * H * W
+    x = (synth.rng(301).standard_normal(N * Cn * S) * 2).astype(f32)
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, bits, 32)
+    dq = orc.mx_to_pm(mx, bits, N, Cn, S, 32).reshape(N, Cn, S)
+    xd = DevBuf(data=mx)
+    # blocks 1 and 2 (channels 32 .. 95) upsampled alone
+    part = np.ascontiguousarray(dq[:, 32:96]).reshape(-1)
+    want = orc.pm_to_mx(orc.up2(part, N, 64, D, H, W), 0, N, 64, 8 * S, bits, 32)
+    yd = DevBuf(want.size).fill(0xEE)
+    L.lp_up2_fwd_mx_blocks(xd.ptr, dt, Shape5(N, Cn, D, H, W), 1, 2, yd.ptr, dt)
+    ufsm_b200.check()
+    assert np.array_equal(yd.download(), want)
+    # a range of voxels of the 1^3 conv: one sample (the fp32 form takes no batch), planes of their own length or inside a wider buffer
+    Co = 7
+    w = (synth.rng(302).standard_normal((Co, Cn)) / np.sqrt(Cn)).astype(f32)
+    b = (0.1 * synth.rng(303).standard_normal(Co)).astype(f32)
+    mx1 = orc.pm_to_mx(x[:Cn * S], 0, 1, Cn, S, bits, 32)
+    x1, wd, bd = DevBuf(data=mx1), DevBuf(data=w), DevBuf(data=b)
+    whole = orc.conv1(orc.mx_to_pm(mx1, bits, 1, Cn, S, 32), w, b, 1, Cn, Co, S).reshape(Co, S)
+    vb, nv, ly = 17, 77, 100
+    y32 = DevBuf(Co * ly * 4).fill(0xEE)
+    assert L.lp_conv1_fwd_mx_r(x1.ptr, dt, Shape5(1, Cn, D, H, W), wd.ptr, bd.ptr, Co, y32.ptr, Gnp(), vb, nv, ly) == 0
+    y16 = DevBuf(Co * nv * 2).fill(0xEE)
+    L.lp_conv1_fwd_mx_h16_r(x1.ptr, dt, Shape5(1, Cn, D, H, W), wd.ptr, bd.ptr, Co, y16.ptr, Gnp(), vb, nv)
+    ufsm_b200.check()
+    g32 = y32.download(f32).reshape(Co, ly)
+    assert np.array_equal(g32[:, :nv], whole[:, vb:vb + nv]) and (y32.download().reshape(Co, ly * 4)[:, nv * 4:] == 0xEE).all()
+    assert np.array_equal(y16.download(np.float16).reshape(Co, nv), whole[:, vb:vb + nv].astype(np.float16))
+    assert L.lp_conv1_fwd_mx_r(xd.ptr, dt, Shape5(N, Cn, D, H, W), wd.ptr, bd.ptr, Co, y32.ptr, Gnp(), vb, nv, ly) == -1       # a batch: refused as in the reference
+    # y += x
+    x2 = (synth.rng(304).standard_normal(N * Cn * S) * 3).astype(f32)
+    mx2 = orc.pm_to_mx(x2, 0, N, Cn, S, bits, 32)
+    want = orc.pm_to_mx((dq.reshape(-1) + orc.mx_to_pm(mx2, bits, N, Cn, S, 32)).astype(f32), 0, N, Cn, S, bits, 32)
+    yd, x2d = DevBuf(data=mx), DevBuf(data=mx2)
+    L.lp_add_mx(yd.ptr, x2d.ptr, Shape5(N, Cn, D, H, W), bits, 0)
+    ufsm_b200.check()
+    assert np.array_equal(yd.download(), want)

@@ -58,6 +58,10 @@ _SIG = {
     "lp_up2_fwd_mx": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_int, Gnp]),
     "lp_conv1_fwd_mx": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp]),
     "lp_conv1_fwd_mx_h16": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp]),
+    "lp_conv1_fwd_mx_h16_r": (None, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp, C.c_size_t, C.c_size_t]),
+    "lp_conv1_fwd_mx_r": (C.c_int, [C.c_void_p, C.c_int, Shape5, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, Gnp, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "lp_up2_fwd_mx_blocks": (None, [C.c_void_p, C.c_int, Shape5, C.c_int, C.c_int, C.c_void_p, C.c_int]),
+    "lp_add_mx": (None, [C.c_void_p, C.c_void_p, Shape5, C.c_int, C.c_uint]),
     "lp_gn_sums_mx": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t]),
     "lp_gn_sums_mx_n": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_int]),
     "umx_gn_finalize": (None, [C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_void_p, C.c_void_p]),

@@ -31,16 +31,18 @@ __device__ __forceinline__ int clampi(int v, int hi) { return v < 0 ? 0 : (v > h
    that two neighbouring rows read by eight lanes cover all the banks.
    grid (tiles, sample x block) */
 template <int BX, int BY, bool GN>
-__global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int N, int C, int D, int H, int W, int tx, int ty, gnp_t gp) {
+__global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int N, int C, int D, int H, int W, int tx, int ty, gnp_t gp, int nbx, int b0) {
     extern __shared__ __align__(16) float4 tile[];
+    /* y has the nb blocks of its C channels; they are blocks [b0, b0 + nb) of x, which has nbx a sample */
     const int nb = (C + 31) / 32, nbk = blockIdx.y, n = nbk / nb, blk = nbk % nb;
+    const size_t xrow0 = ((size_t)n * nbx + b0 + blk) * ((size_t)D * H * W);
     int t = blockIdx.x;
     const int c0 = (t % tx) * UX - 1; t /= tx;
-    const int b0 = (t % ty) * UY - 1, a0 = (t / ty) * UZ - 1;
+    const int bb0 = (t % ty) * UY - 1, a0 = (t / ty) * UZ - 1;
     const int q = threadIdx.x & 3, quad = threadIdx.x >> 2;
     const size_t S = (size_t)D * H * W;
     constexpr int RBX = BX == 8 ? 32 : 16, RBY = BY == 8 ? 32 : 16;
-    const uint8_t *xs = x + (size_t)N * nb * S * RBX;
+    const uint8_t *xs = x + (size_t)N * nbx * S * RBX;
 
     float2 ca[4], cb[4]; bool live[8];
     if (GN) {
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
         raw[u] = make_uint2(0u, 0u); sb[u] = 127u;
         if (s < UP2_ROWS) {
             const int ix = s % HX, iy = (s / HX) % HY, iz = s / (HX * HY);
-            const size_t row = (size_t)nbk * S + ((size_t)clampi(a0 + iz, D - 1) * H + clampi(b0 + iy, H - 1)) * W + clampi(c0 + ix, W - 1);
+            const size_t row = xrow0 + ((size_t)clampi(a0 + iz, D - 1) * H + clampi(bb0 + iy, H - 1)) * W + clampi(c0 + ix, W - 1);
             raw[u] = qrow_ld<BX>(x, row, q); sb[u] = __ldg(xs + row);
         }
     }
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
     const size_t So = 8 * S;                                /* below 2^31: voxel offsets inside a (sample, block) are 32-bit */
     /* the first fine voxel of the quad's cells on y and x, which of the two per axis lie in the grid, and this lane's store addresses
        for voxel 0 of its (sample, block): codes, and (lanes 0 and 1) the scale byte of the cell's first / second x voxel */
-    const int fy0 = 2 * (b0 + lb) + 1, fx0 = 2 * (c0 + lc) + 1;
+    const int fy0 = 2 * (bb0 + lb) + 1, fx0 = 2 * (c0 + lc) + 1;
     const bool vy[2] = {fy0 >= 0 && fy0 < Ho, fy0 + 1 < Ho}, vx[2] = {fx0 >= 0 && fx0 < Wo, fx0 + 1 < Wo};
     uint8_t *yq = y + (size_t)nbk * So * RBY + q * (RBY / 4);
     uint8_t *ysq = y + (size_t)N * nb * So * RBY + (size_t)nbk * So + (q & 1);
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
    shared memory, every read of them a broadcast */
 template <int BITS, int CO4, bool GN, typename YT>
 __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias, YT *__restrict__ y,
-                                                   int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
+                                                   int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp, size_t vb, size_t nv, size_t ly) {
     extern __shared__ __align__(16) float4 c1sm[];
     float4 *sw = c1sm; float2 *sab = (float2 *)(c1sm + (size_t)Ci * CO4);
     constexpr int CO = 4 * CO4, RB = BITS == 8 ? 32 : 16, WORDS = RB / 4;
@@ -160,8 +162,9 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
         sab[ci] = make_float2(a, __fmaf_rn(-gp.mean[ng], a, gp.beta[ci]));
     }
     __syncthreads();
+    /* voxels [vb, vb + nv) of the S; logit planes of ly voxels */
     const size_t v0 = (size_t)blockIdx.x * 512 + threadIdx.x;
-    const bool ok[2] = {v0 < S, v0 + 256 < S};
+    const bool ok[2] = {v0 < nv, v0 + 256 < nv};
     const uint8_t *xs = x + (size_t)N * nb * S * RB;
     float acc[2][CO];                                       /* scalar fma: the packed form has the same pipe rate and needs the input twice */
 #pragma unroll
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
         unsigned wd[2][WORDS]; float fx[2];
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-            const size_t row = ((size_t)n * nb + blk) * S + v0 + 256 * u;
+            const size_t row = ((size_t)n * nb + blk) * S + vb + v0 + 256 * u;
 #pragma unroll
             for (int j = 0; j < WORDS; j += 4) {
                 const uint4 t4 = ok[u] ? __ldg((const uint4 *)(x + row * RB) + j / 4) : make_uint4(0u, 0u, 0u, 0u);
@@ -211,7 +214,7 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
     for (int u = 0; u < 2; u++)
 #pragma unroll
         for (int co = 0; co < CO; co++) if (co < Co && ok[u]) {
-            const size_t o = ((size_t)n * co_all + co0 + co) * S + v0 + 256 * u;
+            const size_t o = ((size_t)n * co_all + co0 + co) * ly + v0 + 256 * u;
             if (sizeof(YT) == 4) ((float *)y)[o] = acc[u][co]; else ((__half *)y)[o] = __float2half_rn(acc[u][co]);
         }
 }
@@ -221,31 +224,31 @@ void gp_check(const char *fn, gnp_t gp, int C) {
     if (gp.G && (gp.G < 1 || C % gp.G)) { fprintf(stderr, "%s: %d channels in %d groups\n", fn, C, gp.G); abort(); }
 }
 
-template <int BX, int BY, bool GN> void up2_launch(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp) {
+template <int BX, int BY, bool GN> void up2_launch(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp, int nbx, int b0) {
     static bool sized = false;      /* per instantiation; the attribute belongs to the function, any device of this process */
     if (!sized) { cudaFuncSetAttribute(up2_dual_k<BX, BY, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UP2_SMEM); sized = true; }
-    up2_dual_k<BX, BY, GN><<<grid, 256, UP2_SMEM>>>(x, y, xs.n, xs.c, xs.d, xs.h, xs.w, tx, ty, gp);
+    up2_dual_k<BX, BY, GN><<<grid, 256, UP2_SMEM>>>(x, y, xs.n, xs.c, xs.d, xs.h, xs.w, tx, ty, gp, nbx, b0);
 }
-template <int BX, int BY> void up2_gn(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp) {
-    if (gp.G) up2_launch<BX, BY, true>(grid, x, y, xs, tx, ty, gp); else up2_launch<BX, BY, false>(grid, x, y, xs, tx, ty, gp);
+template <int BX, int BY> void up2_gn(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp, int nbx, int b0) {
+    if (gp.G) up2_launch<BX, BY, true>(grid, x, y, xs, tx, ty, gp, nbx, b0); else up2_launch<BX, BY, false>(grid, x, y, xs, tx, ty, gp, nbx, b0);
 }
 
 template <int BITS, int CO4, typename YT>
-void conv1_launch(dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
-    if (gp.G) conv1_vox_k<BITS, CO4, true, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp);
-    else conv1_vox_k<BITS, CO4, false, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp);
+void conv1_launch(dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp, size_t vb, size_t nv, size_t ly) {
+    if (gp.G) conv1_vox_k<BITS, CO4, true, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
+    else conv1_vox_k<BITS, CO4, false, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
 }
 template <int BITS, typename YT>
-void conv1_co(int co4, dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp) {
+void conv1_co(int co4, dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp, size_t vb, size_t nv, size_t ly) {
     switch (co4) {
-    case 1: conv1_launch<BITS, 1, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
-    case 2: conv1_launch<BITS, 2, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
-    case 3: conv1_launch<BITS, 3, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
-    default: conv1_launch<BITS, 4, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp); break;
+    case 1: conv1_launch<BITS, 1, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly); break;
+    case 2: conv1_launch<BITS, 2, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly); break;
+    case 3: conv1_launch<BITS, 3, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly); break;
+    default: conv1_launch<BITS, 4, YT>(grid, smem, x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly); break;
     }
 }
 
-template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, YT *y, gnp_t gp) {
+template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, YT *y, gnp_t gp, size_t vb = 0, size_t nv = 0, size_t ly = 0) {
     if (!umx_ready(fn)) return;
     if (xdt != UMX_MX8 && xdt != UMX_MX4) { fprintf(stderr, "%s: input dtype %d is not MX\n", fn, xdt); abort(); }
     if (xs.c <= 16) { fprintf(stderr, "%s: an input of 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
@@ -254,15 +257,18 @@ template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, sh
     gp_check(fn, gp, xs.c);
     const size_t S = (size_t)xs.d * xs.h * xs.w;
     if (!S || !xs.n) return;
-    const dim3 grid((unsigned)((S + 511) / 512), (unsigned)xs.n);
+    if (!nv) { vb = 0; nv = S; }
+    if (!ly) ly = nv;
+    if (vb + nv > S || ly < nv) { fprintf(stderr, "%s: voxels [%zu, %zu) of %zu into planes of %zu\n", fn, vb, vb + nv, S, ly); abort(); }
+    const dim3 grid((unsigned)((nv + 511) / 512), (unsigned)xs.n);
     /* more than 16 outputs: passes of 16 over the same input (the reference's rule, src/lp_mx_conv1.cu:422-444) */
     for (int c0 = 0; c0 < cout; c0 += 16) {
         const int co = min(16, cout - c0), co4 = (co + 3) / 4;
         const size_t smem = (size_t)xs.c * co4 * 16 + (gp.G ? (size_t)xs.c * 8 : 0);
         if (smem > 48 * 1024) { fprintf(stderr, "%s: %d input channels need more shared memory than this kernel has\n", fn, xs.c); abort(); }
         const float *wp = w + (size_t)c0 * xs.c, *bp = b ? b + c0 : nullptr;
-        if (xdt == UMX_MX8) conv1_co<8, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp);
-        else conv1_co<4, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp);
+        if (xdt == UMX_MX8) conv1_co<8, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp, vb, nv, ly);
+        else conv1_co<4, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp, vb, nv, ly);
         g_umx_launches++;
     }
     UMX_CK(fn);
@@ -270,27 +276,84 @@ template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, sh
 
 }   // namespace
 
-extern "C" void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int ydt, gnp_t gp) {
-    const char *fn = "lp_up2_fwd_mx";
+/* ys: the shape of the coarse tensor that y is the upsample of (its channels are blocks [b0, b0 + blocks of ys.c) of x, which has nbx) */
+static void up2_fwd(const char *fn, const void *x, int xdt, shape5 ys, int nbx, int b0, void *y, int ydt, gnp_t gp) {
     if (!umx_ready(fn)) return;
     if ((xdt != UMX_MX8 && xdt != UMX_MX4) || (ydt != UMX_MX8 && ydt != UMX_MX4)) { fprintf(stderr, "%s: dtypes %d -> %d are not MX\n", fn, xdt, ydt); abort(); }
-    if (xs.c <= 16) { fprintf(stderr, "%s: 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
-    gp_check(fn, gp, xs.c);
-    if (!xs.n || !xs.d || !xs.h || !xs.w) return;
-    if ((size_t)xs.d * xs.h * xs.w >= ((size_t)1 << 28)) { fprintf(stderr, "%s: 2^31 fine voxels per sample or more\n", fn); abort(); }
-    const int tx = (xs.w + 1 + UX - 1) / UX, ty = (xs.h + 1 + UY - 1) / UY, tz = (xs.d + 1 + UZ - 1) / UZ;      /* D + 1 dual cells an axis */
-    const size_t tiles = (size_t)tx * ty * tz, nbk = (size_t)xs.n * ((xs.c + 31) / 32);
+    gp_check(fn, gp, ys.c);
+    if (!ys.n || !ys.d || !ys.h || !ys.w) return;
+    if ((size_t)ys.d * ys.h * ys.w >= ((size_t)1 << 28)) { fprintf(stderr, "%s: 2^31 fine voxels per sample or more\n", fn); abort(); }
+    const int tx = (ys.w + 1 + UX - 1) / UX, ty = (ys.h + 1 + UY - 1) / UY, tz = (ys.d + 1 + UZ - 1) / UZ;      /* D + 1 dual cells an axis */
+    const size_t tiles = (size_t)tx * ty * tz, nbk = (size_t)ys.n * ((ys.c + 31) / 32);
     if (tiles > 0x7fffffffu || nbk > 65535) { fprintf(stderr, "%s: %zu tiles x %zu (sample, block) pairs exceed the grid\n", fn, tiles, nbk); abort(); }
     const dim3 grid((unsigned)tiles, (unsigned)nbk);
     const uint8_t *xq = (const uint8_t *)x; uint8_t *yq = (uint8_t *)y;
-    if (xdt == UMX_MX4) { if (ydt == UMX_MX4) up2_gn<4, 4>(grid, xq, yq, xs, tx, ty, gp); else up2_gn<4, 8>(grid, xq, yq, xs, tx, ty, gp); }
-    else { if (ydt == UMX_MX4) up2_gn<8, 4>(grid, xq, yq, xs, tx, ty, gp); else up2_gn<8, 8>(grid, xq, yq, xs, tx, ty, gp); }
+    if (xdt == UMX_MX4) { if (ydt == UMX_MX4) up2_gn<4, 4>(grid, xq, yq, ys, tx, ty, gp, nbx, b0); else up2_gn<4, 8>(grid, xq, yq, ys, tx, ty, gp, nbx, b0); }
+    else { if (ydt == UMX_MX4) up2_gn<8, 4>(grid, xq, yq, ys, tx, ty, gp, nbx, b0); else up2_gn<8, 8>(grid, xq, yq, ys, tx, ty, gp, nbx, b0); }
     g_umx_launches++;
     UMX_CK(fn);
+}
+extern "C" void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int ydt, gnp_t gp) {
+    if (xs.c <= 16) { fprintf(stderr, "lp_up2_fwd_mx: 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n"); abort(); }
+    up2_fwd("lp_up2_fwd_mx", x, xdt, xs, (xs.c + 31) / 32, 0, y, ydt, gp);
+}
+/* src/nn_lp.h:137: the upsample of the 32-channel blocks [b0, b0 + nbk) of x alone; y an MX tensor of 32 nbk channels */
+extern "C" void lp_up2_fwd_mx_blocks(const void *x, int xdt, shape5 xs, int b0, int nbk, void *y, int ydt) {
+    const int nbx = (xs.c + 31) / 32;
+    if (xs.c <= 16 || b0 < 0 || nbk < 1 || b0 + nbk > nbx) { fprintf(stderr, "lp_up2_fwd_mx_blocks: blocks %d + %d of %d channels\n", b0, nbk, xs.c); abort(); }
+    shape5 ys = xs; ys.c = 32 * nbk;
+    gnp_t none; memset(&none, 0, sizeof none);
+    up2_fwd("lp_up2_fwd_mx_blocks", x, xdt, ys, nbx, b0, y, ydt, none);
 }
 extern "C" void lp_conv1_fwd_mx(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, float *y, gnp_t gp) {
     conv1_fwd<float>("lp_conv1_fwd_mx", x, xdt, xs, w, b, cout, y, gp);
 }
 extern "C" void lp_conv1_fwd_mx_h16(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, void *y, gnp_t gp) {
     conv1_fwd<__half>("lp_conv1_fwd_mx_h16", x, xdt, xs, w, b, cout, (__half *)y, gp);
+}
+/* src/nn_lp.h:140-141: the logits of voxels [vb, vb + nv) alone (nv 0: all), into planes of nv (fp16) or ly >= nv (fp32; 0: nv) voxels: the
+   same arithmetic per voxel as the whole-tensor entries, so a voxel's logits are the same bits either way */
+extern "C" void lp_conv1_fwd_mx_h16_r(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, void *y, gnp_t gp, size_t vb, size_t nv) {
+    conv1_fwd<__half>("lp_conv1_fwd_mx_h16_r", x, xdt, xs, w, b, cout, (__half *)y, gp, vb, nv, 0);
+}
+extern "C" int lp_conv1_fwd_mx_r(const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, float *y, gnp_t gp, size_t vb, size_t nv, size_t ly) {
+    if (xs.n != 1 || !nv) return -1;
+    conv1_fwd<float>("lp_conv1_fwd_mx_r", x, xdt, xs, w, b, cout, y, gp, vb, nv, ly);
+    return 0;
+}
+
+/* lp_add_mx (src/nn_lp.h:135, src/lp_mx_gn.cu:133-150): y += x for two MX tensors of the same format, rows re-encoded (decoded y + decoded x
+   in fp32, round to nearest; the reference's stochastic rounding, sr != 0, is not built).  Four lanes a row. */
+namespace {
+template <int BITS>
+__global__ void __launch_bounds__(256) add_rows_k(uint8_t *__restrict__ y, const uint8_t *__restrict__ x, size_t rows) {
+    constexpr int RB = BITS == 8 ? 32 : 16;
+    const int q = threadIdx.x & 3;
+    const uint8_t *xs = x + rows * RB; uint8_t *ys = y + rows * RB;
+    for (size_t r0 = ((size_t)blockIdx.x * 256 + threadIdx.x) >> 2; r0 < ((rows + 63) & ~(size_t)63); r0 += (size_t)gridDim.x * 64) {
+        const bool ok = r0 < rows;                           /* all lanes of a warp stay for the shuffles */
+        const size_t r = ok ? r0 : 0;
+        float2 a[4], b[4];
+        qrow_dec<BITS>(qrow_ld<BITS>(y, r, q), mx_scale(ys[r]), a);
+        qrow_dec<BITS>(qrow_ld<BITS>(x, r, q), mx_scale(__ldg(xs + r)), b);
+#pragma unroll
+        for (int j = 0; j < 4; j++) a[j] = __fadd2_rn(a[j], b[j]);
+        uint2 w;
+        const unsigned sb = qrow_enc<BITS>(a, w);
+        if (ok) { qrow_st<BITS>(y, r, q, w); if (q == 0) ys[r] = (uint8_t)sb; }
+    }
+}
+}   // namespace
+extern "C" void lp_add_mx(void *y, const void *x, shape5 s, int dt, unsigned sr) {
+    const char *fn = "lp_add_mx";
+    if (!umx_ready(fn)) return;
+    if (sr) { fprintf(stderr, "%s: stochastic rounding is not built in this library\n", fn); abort(); }
+    if ((dt != 4 && dt != 8) || s.c <= 16) { fprintf(stderr, "%s: %d bits, %d channels (8 / 16-wide MX rows are not built in this library)\n", fn, dt, s.c); abort(); }
+    const size_t rows = (size_t)s.n * ((s.c + 31) / 32) * s.d * s.h * s.w;
+    if (!rows) return;
+    size_t g = (rows + 63) / 64; if (g > 148u * 16u) g = 148u * 16u;
+    if (dt == 8) add_rows_k<8><<<(unsigned)g, 256>>>((uint8_t *)y, (const uint8_t *)x, rows);
+    else add_rows_k<4><<<(unsigned)g, 256>>>((uint8_t *)y, (const uint8_t *)x, rows);
+    g_umx_launches++;
+    UMX_CK(fn);
 }
