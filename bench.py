@@ -133,10 +133,10 @@ KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
 OUT = {"h16b": 0, "mx": 1, "pm32": 2}
 
 
-def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0):
+def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0, x16=False):
     """One conv layer on a size^3 grid of GEMM rows (conv3s2: the input grid), MX input of arbitrary finite codes (fp8 in the split
     layout), Kaiming-normal weights: best of `reps` device times of the conv launch (events around it) in microseconds, and the
-    algorithmic TFLOP/s (2 V Cin Cout taps)."""
+    algorithmic TFLOP/s (2 V Cin Cout taps).  x16: the input is the planar fp16 tensor itself (UMX_X_H16)."""
     import ufsm_b200
     from ufsm_b200 import DevBuf
     D, S = size, size ** 3
@@ -144,6 +144,8 @@ def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0):
     rb = 32 * bits // 8
     rng = np.random.default_rng(seed)
     x = np.concatenate([rng.integers(0, 120, nbi * S * rb, dtype=np.uint8), rng.integers(100, 130, nbi * S, dtype=np.uint8)])
+    if x16:
+        x = rng.standard_normal(ci * S).astype(np.float16)
     taps = {"conv3": 27, "conv1": 1, "down2": 8, "tconv2": 8, "conv3s2": 27}[kind]
     w = (rng.standard_normal((co, ci, taps)) * np.sqrt(2.0 / (ci * taps))).astype(np.float32)
     if kind == "tconv2":
@@ -157,7 +159,7 @@ def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0):
     best, ms, fl = 1e30, C.c_double(), C.c_double()
     for _ in range(reps):
         L.umx_prof_begin()
-        rc = L.umx_conv_fwd(h, xd.ptr, 1, D, D, D, yd.ptr, mode, bits if mode == 1 else 0, 0, 0, None, 3)
+        rc = L.umx_conv_fwd(h, xd.ptr, 1, D, D, D, yd.ptr, mode, bits if mode == 1 else 0, 0, 0, None, 8 if x16 else 3)
         L.umx_prof_end(C.byref(ms), C.byref(fl))
         assert rc == 0
         best = min(best, ms.value)
@@ -190,14 +192,14 @@ def quantiser_time(L, Cn, size, bits, reps=5):
 
 
 def run_layer(args):
-    """python bench.py --layer kind,ci,co,size[,bits[,out]]: one conv layer alone (also the command of the profiler captures under profiles/)"""
+    """python bench.py --layer kind,ci,co,size[,bits[,out[,x16]]]: one conv layer alone; x16: fed the planar fp16 tensor (also the command of the profiler captures under profiles/)"""
     import ufsm_b200
     f = args.layer.split(",")
     kind, ci, co, size = f[0], int(f[1]), int(f[2]), int(f[3])
     bits, out = (int(f[4]) if len(f) > 4 else 8), (f[5] if len(f) > 5 else "h16b")
     L = ufsm_b200.lib()
     assert L.nn_init(0) == 0, (L.lp_check() or b"").decode()
-    us, tf, nbytes = layer_time(L, kind, ci, co, size, bits, out, args.reps)
+    us, tf, nbytes = layer_time(L, kind, ci, co, size, bits, out, args.reps, x16=len(f) > 6 and f[6] == "x16")
     print("%s %d->%d on %d^3 MX-fp%d out %s: %.1f us, %.0f TFLOP/s, %.0f GB/s of operand + result bytes (kernel %d)" % (kind, ci, co, size, bits, out, us, tf, nbytes / us / 1e3, L.umx_conv_last_kernel()))
 
 

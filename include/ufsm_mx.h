@@ -30,7 +30,8 @@ enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16
    The scale plane follows the codes unchanged in either layout. */
 enum { UMX_LAYOUT_REF = 0, UMX_LAYOUT_SPLIT = 1 };
 enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2,     /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
-       UMX_STATS_EPILOGUE = 4 };             /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue where the kernel can (see there) */
+       UMX_STATS_EPILOGUE = 4,               /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue where the kernel can (see there) */
+       UMX_X_H16 = 8 };                      /* x is the planar fp16 tensor [N][ci][D][H][W], not MX: the conv quantises it (UMX_CONV3 / UMX_CONV1) */
 
 /* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
 int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
@@ -135,7 +136,10 @@ void umx_conv_free(umx_conv *c);
    N x D x H x W grid.  y per out_mode; nb_dst / b0: block count of the destination tensor and first block written (0, 0: the
    conv's own co).  part: optional device doubles for InstanceNorm partial sums (umx_stats_doubles), only with UMX_OUT_H16B.
    UMX_TCONV2 writes the 2D x 2H x 2W grid.  flags: UMX_X_SPLIT / UMX_Y_SPLIT (an fp8 input in the reference layout is re-laid into
-   scratch first).  Returns 0, or -1 after latching an error. */
+   scratch first); UMX_X_H16: x is planar fp16 and is quantised to the conv's MX format on the way in (the values the quantiser gives;
+   a 3^3 MX-fp8 conv of ONE input channel into at most 32 outputs with a UMX_OUT_H16B output runs as a tap-packed kernel that reads
+   the fp16 tensor directly, the role of conv_fwd_f8s_k, src/lp_f8fwd.cuh:153-400; every other case is quantised into scratch first).
+   Returns 0, or -1 after latching an error. */
 int umx_conv_fwd(const umx_conv *c, const void *x, int N, int D, int H, int W, void *y, int out_mode, int out_bits, int nb_dst, int b0, double *part, int flags);
 /* the conv with a blocked fp16 output followed by InstanceNorm: y as UMX_OUT_H16B and coef [N][co][2] = (a, b) of the stored values
    (k_in_coef, src/nn_xnet.cu:1565-1570), in one call; part: scratch of umx_stats_doubles doubles.  By default the sums are taken by the
@@ -151,7 +155,7 @@ size_t umx_stats_doubles(int N, int co, int D, int H, int W);   /* size of part 
 /* testing aid (no counterpart in the reference): at most `cap` thread blocks per column tile in the resident-weight 3^3 kernel (0: as many as
    the device holds), so that a small volume is cut into the several-planes-a-block pieces that otherwise only 64^3 and larger volumes see */
 void umx_conv_r_block_cap(int cap);
-int umx_conv_last_kernel(void);          /* which kernel the last umx_conv_fwd on this thread's process launched: 0 general, 1 resident-weight 3^3, 2 one-tap streaming; -1 none yet */
+int umx_conv_last_kernel(void);          /* which kernel the last umx_conv_fwd on this thread's process launched: 0 general, 1 resident-weight 3^3, 2 one-tap streaming, 3 tap-packed one-channel 3^3; -1 none yet */
 /* coef [n][C][2] (device floats): a = gamma rstd, b = beta - mean a from the partial sums (k_in_coef, src/nn_xnet.cu:1565-1570);
    gamma / beta device arrays or NULL (1 / 0) */
 void umx_in_coef(const double *part, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, float *coef);

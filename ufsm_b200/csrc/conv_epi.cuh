@@ -8,6 +8,7 @@ struct umx_conv {
     uint8_t *wpk; float *bias_p;
     uint8_t *wr;                    /* weight image of the z-marching kernel, or NULL */
     uint8_t *wp;                    /* weight image of the one-tap streaming kernel, or NULL */
+    uint8_t *wstem;                 /* weight tile of the tap-packed one-channel kernel, or NULL */
 };
 
 struct EpiArgs {

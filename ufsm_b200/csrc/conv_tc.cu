@@ -387,6 +387,8 @@ int umx_conv_fwd_r(const umx_conv *c, const void *x, const CUtensorMap *m0, void
 extern "C" void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int W, const float *gamma, const float *beta, float eps, double *part, float *coef);
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part);
 uint8_t *umx_conv_p_prepare(const umx_conv *c, const float *w_dev);
+uint8_t *umx_conv_stem_prepare(const umx_conv *c, const float *w_dev);
+int umx_conv_fwd_stem(const umx_conv *c, const void *x16, int N, int D, int H, int W, void *y);
 int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, int H, int W, const EpiArgs &e);
 
 
@@ -420,6 +422,7 @@ static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev,
     g_umx_launches++;
     c->wr = umx_conv_r_prepare(c, w_dev);
     c->wp = umx_conv_p_prepare(c, w_dev);
+    c->wstem = umx_conv_stem_prepare(c, w_dev);
     UMX_CK("umx_conv_create");
     /* the conv kernels read the prepared weights and the bias before their griddepcontrol.wait (they are layer constants that may load while
        the previous kernel still runs), so the preparation kernels must have finished before a conv can be launched behind them */
@@ -438,7 +441,7 @@ extern "C" umx_conv *umx_conv_create(int kind, const float *w, const float *bias
     nn_free(wd); nn_free(bd);
     return c;
 }
-extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); free(c); }
+extern "C" void umx_conv_free(umx_conv *c) { if (!c) return; nn_free(c->wpk); nn_free(c->bias_p); nn_free(c->wr); nn_free(c->wp); nn_free(c->wstem); free(c); }
 int umx_stats_chunks(int D, int H, int W);
 /* room for 512 partial sums of two doubles per (sample, channel): the statistics pass uses up to that many voxel chunks, the conv epilogue
    one entry per block */
@@ -452,6 +455,25 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     if (!c) { umx_latch_msg("umx_conv_fwd: no conv"); return -1; }
     if (part && (out_mode != UMX_OUT_H16B || c->kind == UMX_TCONV2)) { fprintf(stderr, "umx_conv_fwd: partial sums only with a blocked fp16 output of a plain conv\n"); abort(); }
     if ((out_mode == UMX_OUT_MX || out_mode == UMX_OUT_MXRAW) && out_bits != 8 && out_bits != 4) { fprintf(stderr, "umx_conv_fwd: MX output needs out_bits 8 or 4\n"); abort(); }
+    if (flags & UMX_X_H16) {
+        /* x is the fp16 tensor [N][ci][D][H][W] itself.  The tap-packed kernel takes the one-channel 3^3 case as it is; everything else is
+           quantised into scratch first and goes the usual way. */
+        if (c->kind != UMX_CONV3 && c->kind != UMX_CONV1) { fprintf(stderr, "umx_conv_fwd: an fp16 input only for the 3^3 and 1^3 convs\n"); abort(); }
+        if (c->wstem && out_mode == UMX_OUT_H16B && !nb_dst) {
+            const int r = umx_conv_fwd_stem(c, x, N, D, H, W, y);
+            if (r < 0) return -1;
+            if (r == 0) {
+                g_last_kernel = 3;
+                if (nrm) umx_in_stats_coef(y, N, c->co, D, H, W, nrm->gamma, nrm->beta, nrm->eps, part, nrm->coef);
+                else if (part) umx_in_part(y, N, c->co, D, H, W, part);
+                return 0;
+            }
+        }
+        void *ws = umx_ws(1, umx_mx_bytes32(c->bits, N, c->ci, (size_t)D * H * W));
+        if (!ws) return -1;
+        umx_pm_to_mx32(x, UMX_F16, N, c->ci, (size_t)D * H * W, ws, c->bits, UMX_LAYOUT_SPLIT);
+        x = ws; flags |= UMX_X_SPLIT;
+    }
     encode_fn enc = get_encode(); if (!enc) return -1;
     ConvArgs a; memset(&a, 0, sizeof a);
     /* the stride-2 3^3 conv is given its input grid; its GEMM rows are the output grid ceil(D / 2) x ceil(H / 2) x ceil(W / 2) */

@@ -31,7 +31,6 @@ struct umx_unet {
     umx_unet_cfg cfg; int maxN;
     umx_conv *enc1[MAXL], *enc2[MAXL], *down[MAXL], *up[MAXL], *dec1[MAXL], *dec2[MAXL], *head;
     int Dl[MAXL];
-    void *x_mx;              /* quantised network input (one channel in a 32-wide block) */
     void *ybuf;              /* blocked fp16 conv output, reused by every conv */
     double *part; float *coef;
     void *act[MAXL];         /* MX activation between the two convs of a level (encoder and decoder reuse it) */
@@ -83,7 +82,7 @@ void umx_unet_free(umx_unet *u) {
         nn_free(u->act[l]); nn_free(u->cat[l]); nn_free(u->s2d[l]); nn_free(u->dn[l]); nn_free(u->dec[l]);
     }
     umx_conv_free(u->head);
-    nn_free(u->x_mx); nn_free(u->ybuf); nn_free(u->part); nn_free(u->coef); nn_free(u->x16); nn_free(u->xu8); nn_free(u->logits16);
+    nn_free(u->ybuf); nn_free(u->part); nn_free(u->coef); nn_free(u->x16); nn_free(u->xu8); nn_free(u->logits16);
     for (int k = 0; k < 2; k++) { nn_free(u->pxu8[k]); nn_free(u->plog[k]); nn_free(u->pprob[k]); umx_event_free(u->ev_up[k]); umx_event_free(u->ev_used[k]); umx_event_free(u->ev_ready[k]); umx_event_free(u->ev_down[k]); }
     umx_stream_free(u->s_in); umx_stream_free(u->s_out);
     free(u);
@@ -120,7 +119,6 @@ umx_unet *umx_unet_create(const umx_unet_cfg *cfg, const float *weights, int max
         if (l) u->dn[l] = nn_malloc(umx_mx_bytes32(8, N, C, S));
     }
     const size_t S0 = cube(cfg->P);
-    u->x_mx = nn_malloc(umx_mx_bytes32(8, N, 1, S0));
     u->ybuf = nn_malloc((size_t)N * ymax * 2);
     u->part = nn_malloc(pmax * sizeof(double));
     u->coef = nn_malloc((size_t)N * cmax * 2 * sizeof(float));
@@ -135,31 +133,31 @@ umx_unet *umx_unet_create(const umx_unet_cfg *cfg, const float *weights, int max
 long umx_unet_launches(const umx_unet *u) { return umx_launch_count() - u->launches0; }
 
 /* conv -> blocked fp16 + partial sums -> coefficients -> apply into q (and q_s2d) */
-static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int N, int C, int D, void *q, int bits, int nb_dst, int b0, void *q_s2d) {
+static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int xflag, int N, int C, int D, void *q, int bits, int nb_dst, int b0, void *q_s2d) {
     /* UMX_STATS_EPILOGUE=1 in the environment: InstanceNorm sums in the conv's epilogue (see umx_conv_fwd_norm); off by default */
     static int epi = -1;
     if (epi < 0) { const char *e = getenv("UMX_STATS_EPILOGUE"); epi = e && *e == '1'; }
-    umx_conv_fwd_norm(c, x, N, D, D, D, u->ybuf, u->part, nullptr, nullptr, 1e-5f, u->coef, UMX_X_SPLIT | (epi ? UMX_STATS_EPILOGUE : 0));
+    umx_conv_fwd_norm(c, x, N, D, D, D, u->ybuf, u->part, nullptr, nullptr, 1e-5f, u->coef, (xflag ? xflag : UMX_X_SPLIT) | (epi ? UMX_STATS_EPILOGUE : 0));
     umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr, UMX_LAYOUT_SPLIT);
 }
 static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) {
     const umx_unet_cfg *c = &u->cfg; const int L = c->L, bm = c->bits_mid, bl = c->bits_last;
     if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_forward: batch %d outside 1..%d\n", N, u->maxN); abort(); }
-    umx_pm_to_mx32(x_dev, UMX_F16, N, 1, cube(c->P), u->x_mx, c->bits_first, UMX_LAYOUT_SPLIT);
     for (int l = 0; l < L; l++) {
         const int D = u->Dl[l], C = c->cw[l], nb = C / 32;
-        conv_norm(u, u->enc1[l], l ? u->dn[l] : u->x_mx, N, C, D, u->act[l], bm, 0, 0, nullptr);
+        /* the first conv takes the fp16 patch itself (UMX_X_H16: quantised on the way in) */
+        conv_norm(u, u->enc1[l], l ? u->dn[l] : x_dev, l ? 0 : UMX_X_H16, N, C, D, u->act[l], bm, 0, 0, nullptr);
         if (l < L - 1) {
-            conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 2 * nb, nb, u->s2d[l]);
+            conv_norm(u, u->enc2[l], u->act[l], 0, N, C, D, u->cat[l], bm, 2 * nb, nb, u->s2d[l]);
             umx_conv_fwd(u->down[l], u->s2d[l], N, D / 2, D / 2, D / 2, u->dn[l + 1], UMX_OUT_MX, bm, 0, 0, nullptr, UMX_X_SPLIT | UMX_Y_SPLIT);
-        } else conv_norm(u, u->enc2[l], u->act[l], N, C, D, u->cat[l], bm, 0, 0, nullptr);
+        } else conv_norm(u, u->enc2[l], u->act[l], 0, N, C, D, u->cat[l], bm, 0, 0, nullptr);
     }
     const void *cur = u->cat[L - 1];
     for (int l = L - 2; l >= 0; l--) {
         const int D = u->Dl[l], C = c->cw[l], nb = C / 32, Dc = u->Dl[l + 1];
         umx_conv_fwd(u->up[l], cur, N, Dc, Dc, Dc, u->cat[l], UMX_OUT_MX, bm, 2 * nb, 0, nullptr, UMX_X_SPLIT | UMX_Y_SPLIT);
-        conv_norm(u, u->dec1[l], u->cat[l], N, C, D, u->act[l], l ? bm : bl, 0, 0, nullptr);
-        conv_norm(u, u->dec2[l], u->act[l], N, C, D, u->dec[l], l ? bm : bl, 0, 0, nullptr);
+        conv_norm(u, u->dec1[l], u->cat[l], 0, N, C, D, u->act[l], l ? bm : bl, 0, 0, nullptr);
+        conv_norm(u, u->dec2[l], u->act[l], 0, N, C, D, u->dec[l], l ? bm : bl, 0, 0, nullptr);
         cur = u->dec[l];
     }
     umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : UMX_OUT_PM32, 0, 0, 0, nullptr, UMX_X_SPLIT);

@@ -100,6 +100,23 @@ class Conv:
             out = from_split(out, N, nbo * 32, So, out_bits)
         return out, (pd if want_part else None)
 
+    def fwd_h16(self, x16, N, D, H, W, out_mode=OUT_H16B, norm=False, eps=1e-5):
+        """the conv on the planar fp16 tensor itself (UMX_X_H16: quantised on the way in).  Returns (output bytes, coef or None, the kernel
+        that ran: umx_conv_last_kernel)."""
+        xd = DevBuf(data=np.ascontiguousarray(x16, np.float16))
+        S = D * H * W
+        yd = DevBuf(N * nb32(self.co) * S * 64 if out_mode == OUT_H16B else N * self.co * S * 4).fill(0xEE)
+        cd = None
+        if norm:
+            pd = DevBuf(L().umx_stats_doubles(N, self.co, D, H, W) * 8).fill(0xEE)
+            cd = DevBuf(N * self.co * 8).fill(0xEE)
+            rc = L().umx_conv_fwd_norm(self.h, xd.ptr, N, D, H, W, yd.ptr, pd.ptr, None, None, C.c_float(eps), cd.ptr, 8)
+        else:
+            rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, 0, 0, 0, None, 8)
+        _check()
+        assert rc == 0
+        return yd.download(), (cd.download(np.float32) if cd else None), L().umx_conv_last_kernel()
+
     def fwd_norm(self, x_mx, N, D, H, W, eps=1e-5, epilogue_stats=False):
         """conv -> blocked fp16 + InstanceNorm coefficients in one call; returns (fp16 blocked values, coef [N * co * 2])"""
         xd = DevBuf(data=to_split(x_mx, N, nb32(self.ci) * 32, D * H * W, self.bits))
