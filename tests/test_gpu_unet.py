@@ -178,11 +178,15 @@ def test_unet_layers_teacher_forced(dev, bits):
     x16 = ct_patch(9, P ** 3)
     worst = {"conv": 0.0}
 
-    def conv_norm(name, x_mx, Ci, C, D, bits_in, bits_out, want_s2d=False):
+    def conv_norm(name, x_mx, Ci, C, D, bits_in, bits_out, want_s2d=False, x_h16=None):
         S = D ** 3
         w, b = W[name]
         c = G.Conv("conv3", w, b, C, Ci, bits_in)
-        y, coef = c.fwd_norm(x_mx, 1, D, D, D)
+        if x_h16 is not None:       # the first conv is handed the fp16 patch itself, as the forward does; the oracle convolves the quantiser's tensor
+            raw, coef, _ = c.fwd_h16(x_h16, 1, D, D, D, norm=True)
+            y = raw.view(np.float16)
+        else:
+            y, coef = c.fwd_norm(x_mx, 1, D, D, D)
         c.free()
         yf = y.astype(np.float32)
         acc = orc.conv_blocked(orc.mx_to_blocked(x_mx, bits_in, 1, Ci, S), 1, Ci, D, D, D, orc.prep_w(w, C, Ci, 27, bits_in), b, C, 3, 1, 1)
@@ -223,7 +227,7 @@ def test_unet_layers_teacher_forced(dev, bits):
     skip, Ccur = {}, 1
     for l in range(Lv):
         D, C = P >> l, cw[l]
-        a, _ = conv_norm("enc%d.c1" % l, cur, Ccur, C, D, bm if l else bf, bm)
+        a, _ = conv_norm("enc%d.c1" % l, cur, Ccur, C, D, bm if l else bf, bm, x_h16=None if l else x16)
         if l < Lv - 1:
             skip[l], s2d = conv_norm("enc%d.c2" % l, a, C, C, D, bm, bm, want_s2d=True)
             cur = conv_mx("down2", "down%d" % l, s2d, C, cw[l + 1], D // 2, bm, x_fine=skip[l])

@@ -255,3 +255,16 @@ def test_elementwise_operator_restatements():
     whole = orc.gn_silu(x, N, Cn, S, Gn, gamma, beta, mean, rstd, 1).reshape(N, Cn, S)
     seg = orc.gn_silu(np.ascontiguousarray(x.reshape(N, Cn, S)[:, 1:]), N, Cn - 1, S, Gn, gamma, beta, mean, rstd, 1, 1, Cn).reshape(N, Cn - 1, S)
     assert np.array_equal(seg, whole[:, 1:])
+
+
+def test_one_channel_fp8_row_is_rounding_to_four_bits():
+    """An MX-fp8 row with one real channel (the network's input) holds its value rounded to nearest-even at four significant bits: the
+    block scale puts |x| 2^-e into (224, 448], where E4M3 neither saturates nor is subnormal.  Checked for every finite fp16 value; the
+    tap-packed first conv quantises its fp16 input by this rule."""
+    h = np.arange(65536, dtype=np.uint16).view(np.float16)
+    x = h[np.isfinite(h)].astype(np.float32)
+    mx = orc.pm_to_mx(x, 0, 1, 1, x.size, 8, 32)
+    want = orc.mx_to_blocked(mx, 8, 1, 1, x.size).reshape(-1, 32)[:, 0]
+    u = x.view(np.uint32).astype(np.uint64)
+    got = ((u + 0x7FFFF + ((u >> 20) & 1)) & 0xFFF00000).astype(np.uint32).view(np.float32)
+    assert np.array_equal(got, want) and np.array_equal(np.signbit(got), np.signbit(want))

@@ -9,11 +9,13 @@
    exactly, so the tile runs as a plain tcgen05.mma.kind::f16 on bf16 operands with exact products: the same result as the
    block-scaled path up to the order of the fp32 additions.
 
-   A block walks runs of output planes of one 16 x 8 tile.  Per plane: four warps bring the next input plane's 18 x 10 halo through the
-   quantiser into a three-plane ring in shared memory (while the other four finish the previous plane's epilogue), all eight build
-   the A tile from the ring ([K chunk][voxel][16 B], the canonical K-major layout), one thread issues two MMAs (K = 16 each) and a
-   commit, and warps 0-3 take the accumulators out of TMEM, add the bias, round to fp16 and pass the rows through shared memory so that
-   they leave as 512-byte runs (the same epilogue as the z-marching kernel).  Output: blocked fp16 [n][1][voxel][32]. */
+   A block walks runs of output planes of one 16 x 8 tile with three roles and two stages.  Four producer warps bring the input planes'
+   18 x 10 halo tiles through the quantiser into a ring in shared memory (the loads run three planes ahead) and build the A tile of
+   plane z ([K chunk][voxel][16 B], the canonical K-major layout; a thread keeps its voxel's taps of planes z - 1 and z in registers and
+   reads only plane z + 1); one thread issues two MMAs (K = 16 each) and a commit; four epilogue warps take the accumulators out of
+   TMEM (the bias is already in them: three K positions of A are 1 and B holds the fp32 bias there as three bf16 pieces), round to
+   fp16 and pass the rows through shared memory so that they leave as 512-byte runs (as in the z-marching kernel).  Four blocks a
+   multiprocessor hide the latencies of each other's short dependent chains.  Output: blocked fp16 [n][1][voxel][32]. */
 #include "mx_common.cuh"
 #include "tc_ptx.cuh"
 #include "conv_epi.cuh"
@@ -41,29 +43,32 @@ __device__ __forceinline__ float fq_e4m3_one(float f) {
     const float v = __low2float(*(const __half2 *)&h2) * exp2i(e);
     return e == 128 ? __uint_as_float(0x7fc00000u) : v;
 }
+/* The same for an fp16 input, as bf16 bits.  There the rule collapses: the block scale puts |x| 2^-e into (224, 448], where E4M3 has four
+   significant bits, never saturates and is never subnormal, so the value is x rounded to nearest-even at four significant bits (every
+   finite fp16 value has been checked against the quantiser).  inf / NaN -> NaN. */
+__device__ __forceinline__ unsigned short fq_h16_one(__half x, bool live) {
+    const unsigned u = live ? __float_as_uint(__half2float(x)) : 0u;
+    const unsigned r = (u + 0x7ffffu + ((u >> 20) & 1u)) >> 20;
+    return (u & 0x7f800000u) == 0x7f800000u ? (unsigned short)0x7fc0 : (unsigned short)(r << 4);
+}
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-/* the four 16-byte K chunks (taps 0-7, 8-15, 16-23, 24-26, then 1, 1, 1 for the three bias rows of B and two zeros) of the voxel whose halo origin is `o` in the ring planes p0, p1, p2
-   (z - 1, z, z + 1); dst: the voxel's 16 bytes in chunk 0, the other chunks 2 KB apart */
-__device__ __forceinline__ void build_row(const unsigned short *p0, const unsigned short *p1, const unsigned short *p2, int o, uint4 *dst) {
-    uint32_t w[16];
+/* K layout of the tile: position 10 dz + 3 dy + dx holds tap (dz, dy, dx), positions 9, 19 and 29 hold 1 (B has the three pieces of the
+   bias there), 30 and 31 are zero.  The ten positions of an input plane are five packed words, so a voxel's part of plane z + 1 is
+   loaded once and serves as dz = 2, 1, 0 of three consecutive output planes by moving whole words. */
+__device__ __forceinline__ void load_plane9(const unsigned short *p, int o, uint32_t *P) {
+    unsigned short v[9];
 #pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-        unsigned short h2[2];
+    for (int dy = 0; dy < 3; dy++)
 #pragma unroll
-        for (int t = 0; t < 2; t++) {
-            const int tap = j + t;
-            h2[t] = tap < 30 ? (unsigned short)0x3f80 : (unsigned short)0;
-            if (tap < 27) { const int dz = tap / 9, dy = (tap / 3) % 3, dx = tap % 3; h2[t] = (dz == 0 ? p0 : dz == 1 ? p1 : p2)[o + dy * 10 + dx]; }
-        }
-        w[j >> 1] = (uint32_t)h2[0] | ((uint32_t)h2[1] << 16);
-    }
+        for (int dx = 0; dx < 3; dx++) v[dy * 3 + dx] = p[o + dy * 10 + dx];
 #pragma unroll
-    for (int k = 0; k < 4; k++) dst[128 * k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+    for (int k = 0; k < 4; k++) P[k] = (uint32_t)v[2 * k] | ((uint32_t)v[2 * k + 1] << 16);
+    P[4] = (uint32_t)v[8] | 0x3f800000u;
 }
 /* barrier 1 of the 128 producer threads, with an OR over their flags: every producer leaves its loop in the same iteration */
 __device__ __forceinline__ uint32_t producers_sync_or(uint32_t flag) {
@@ -72,17 +77,6 @@ __device__ __forceinline__ uint32_t producers_sync_or(uint32_t flag) {
     return out;
 }
 
-/* Bounded wait without a suspend-time hint: the hand-overs of this kernel are short (a tile, two MMAs), and a waiter parked with a
-   long hint was seen to come back late */
-__device__ __forceinline__ bool mbar_wait_now(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > limit) return false;
-    }
-}
 struct StemRun { int n, zb, ze, x0, y0; };
 __device__ __forceinline__ StemRun stem_run(const StemArgs &a, long long u, long long u1) {
     StemRun r;
@@ -98,13 +92,13 @@ __device__ __forceinline__ void stem_raise(const StemArgs &a, volatile int *abor
     *abort_s = 1;
 }
 
-constexpr int kStemThreads = 288;
+constexpr int kStemThreads = 288, kStemBlocks = 4;           /* blocks a multiprocessor (registers: 56 a thread) */
 /* Three roles, two stages (A tile and accumulator).  Warps 4-7 produce: input planes through the quantiser into the ring, the A tile of
    plane z from the ring, `full`.  One thread of warp 8 multiplies: waits `full` and the stage's accumulator to be free (`acce`), issues
    the two MMAs and a commit on `done`.  Warps 0-3 take the accumulators out (`done`), free them (`acce`) and store the rows.  `done` also
    tells the producers that the stage's A tile has been read.  Every wait is bounded; a wait that gives up raises the block's abort
    flag, which ends the other roles' waits, and records where in the error words. */
-__global__ void __launch_bounds__(kStemThreads, 3) conv_stem_k(const StemArgs a) {
+__global__ void __launch_bounds__(kStemThreads, kStemBlocks) conv_stem_k(const StemArgs a) {
     __shared__ __align__(128) uint8_t sA[2][8192];          /* per stage [4 K chunks][128 voxels][8 bf16] */
     __shared__ __align__(128) uint8_t sB[2048];             /* [4 K chunks][32 outputs][8 bf16] */
     __shared__ __align__(16) uint8_t stg_all[4 * 2048];     /* the epilogue warps' rows on their way out */
@@ -144,35 +138,51 @@ __global__ void __launch_bounds__(kStemThreads, 3) conv_stem_k(const StemArgs a)
             /* the halo tile of an input plane: 180 values, two a thread; plane z + 3 is requested while plane z is built */
             const int gy0 = rn.y0 - 1 + t0 / 10, gx0 = rn.x0 - 1 + t0 % 10, gy1 = rn.y0 - 1 + t1 / 10, gx1 = rn.x0 - 1 + t1 % 10;
             const bool in0 = gy0 >= 0 && gy0 < H && gx0 >= 0 && gx0 < W, in1 = t1 < 180 && gy1 >= 0 && gy1 < H && gx1 >= 0 && gx1 < W;
-            const __half *s0 = xn + (ptrdiff_t)gy0 * W + gx0, *s1 = xn + (ptrdiff_t)gy1 * W + gx1;
-            const __half hz = __ushort_as_half((unsigned short)0);
+            /* every load is issued unconditionally from an address inside the tensor (positions outside the volume read the sample's first
+               voxel) and masked when the value is used: nothing waits for a load at the place where it is issued */
+            const __half *s0 = in0 ? xn + (ptrdiff_t)gy0 * W + gx0 : xn, *s1 = in1 ? xn + (ptrdiff_t)gy1 * W + gx1 : xn;
             auto fetch = [&](int zp, __half &v0, __half &v1) {
-                const bool zin = zp >= 0 && zp < D;
-                v0 = (zin && in0) ? __ldg(s0 + (size_t)zp * HW) : hz;
-                v1 = (zin && in1) ? __ldg(s1 + (size_t)zp * HW) : hz;
+                const size_t zo = (size_t)min(max(zp, 0), D - 1) * HW;
+                v0 = __ldg(s0 + zo); v1 = __ldg(s1 + zo);
             };
             auto put = [&](int zp, __half v0, __half v1) {
-                __nv_bfloat16 *dst = ring[(zp + 4) & 3];
-                dst[t0] = __float2bfloat16_rn(fq_e4m3_one(__half2float(v0)));
-                if (t1 < 180) dst[t1] = __float2bfloat16_rn(fq_e4m3_one(__half2float(v1)));
+                const bool zin = zp >= 0 && zp < D;
+                unsigned short *dst = (unsigned short *)ring[(zp + 4) & 3];
+                dst[t0] = fq_h16_one(v0, zin && in0);
+                if (t1 < 180) dst[t1] = fq_h16_one(v1, zin && in1);
             };
-            __half a0, a1, b0, b1, c0, c1;
+            __half a0, a1, b0, b1;
             fetch(rn.zb - 1, a0, a1); fetch(rn.zb, b0, b1);
             if (producers_sync_or(dead | (uint32_t)*abort_s)) break;     /* the previous run's last tile has been built: its ring slots are free */
             put(rn.zb - 1, a0, a1); put(rn.zb, b0, b1);
             fetch(rn.zb + 1, a0, a1); fetch(rn.zb + 2, b0, b1);          /* a: plane z + 1, b: plane z + 2 */
             bool out = false;
-            for (int z = rn.zb; z < rn.ze; z++, pc++) {
-                put(z + 1, a0, a1);
-                fetch(z + 3, c0, c1);
-                a0 = b0; a1 = b1; b0 = c0; b1 = c1;
-                if (producers_sync_or(dead | (uint32_t)*abort_s)) { out = true; break; }
+            uint32_t P0[5], P1[5], P2[5];                                /* the voxel's taps in planes z - 1, z, z + 1 */
+            /* one plane; (v0, v1) holds the raw values of plane z + 1 and takes those of plane z + 3 as soon as they are used: the two register
+               pairs alternate, so a value is never moved while its load is in flight */
+            auto step = [&](int z, __half &v0, __half &v1) -> bool {
+                put(z + 1, v0, v1);
+                fetch(z + 3, v0, v1);
+                if (producers_sync_or(dead | (uint32_t)*abort_s)) return true;
                 const int s = pc & 1, k = pc >> 1;
-                if (k > 0 && !mbar_wait_now(bar_done + 8 * s, (uint32_t)((k - 1) & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 1, pc); dead = 1; continue; }
-                const unsigned short *p1 = (const unsigned short *)ring[z & 3], *p2 = (const unsigned short *)ring[(z + 1) & 3], *p0 = (const unsigned short *)ring[(z + 3) & 3];
-                build_row(p0, p1, p2, o, (uint4 *)(sA[s] + (size_t)r * 16));
+                if (k > 0 && !mbar_wait(bar_done + 8 * s, (uint32_t)((k - 1) & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 1, pc); dead = 1; pc++; return false; }
+                if (z == rn.zb) { load_plane9((const unsigned short *)ring[(z + 3) & 3], o, P0); load_plane9((const unsigned short *)ring[z & 3], o, P1); }
+                load_plane9((const unsigned short *)ring[(z + 1) & 3], o, P2);
+                uint4 *dstA = (uint4 *)(sA[s] + (size_t)r * 16);
+                dstA[0] = make_uint4(P0[0], P0[1], P0[2], P0[3]);
+                dstA[128] = make_uint4(P0[4], P1[0], P1[1], P1[2]);
+                dstA[256] = make_uint4(P1[3], P1[4], P2[0], P2[1]);
+                dstA[384] = make_uint4(P2[2], P2[3], P2[4], 0u);
+#pragma unroll
+                for (int q = 0; q < 5; q++) { P0[q] = P1[q]; P1[q] = P2[q]; }
                 fence_proxy_async();
                 mbar_arrive(bar_full + 8 * s);
+                pc++;
+                return false;
+            };
+            for (int z = rn.zb; z < rn.ze; z += 2) {
+                if (step(z, a0, a1)) { out = true; break; }
+                if (z + 1 < rn.ze && step(z + 1, b0, b1)) { out = true; break; }
             }
             if (out) break;
             u += rn.ze - rn.zb;
@@ -185,8 +195,8 @@ __global__ void __launch_bounds__(kStemThreads, 3) conv_stem_k(const StemArgs a)
             const long long planes = u1 - u0;
             for (int pc = 0; pc < planes; pc++) {
                 const int s = pc & 1, k = pc >> 1;
-                if (!mbar_wait_now(bar_full + 8 * s, (uint32_t)(k & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 2, pc); break; }
-                if (k > 0 && !mbar_wait_now(bar_acce + 8 * s, (uint32_t)((k - 1) & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 3, pc); break; }
+                if (!mbar_wait(bar_full + 8 * s, (uint32_t)(k & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 2, pc); break; }
+                if (k > 0 && !mbar_wait(bar_acce + 8 * s, (uint32_t)((k - 1) & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 3, pc); break; }
                 tc_fence_after();
                 const uint32_t sa = smem_u32(sA[s]);
                 umma_bf16(tmem + (uint32_t)(32 * s), smem_desc(sa, 2048, 128), bd0, idesc, 0u);
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(kStemThreads, 3) conv_stem_k(const StemArgs a)
             uint8_t *run_dst = a.y + (((size_t)rn.n * S + (size_t)sy * W + rn.x0 + (lane >> 2)) * 64) + cl * 16;
             for (int z = rn.zb; z < rn.ze; z++, pc++) {
                 const int s = pc & 1, k = pc >> 1;
-                if (!mbar_wait_now(bar_done + 8 * s, (uint32_t)(k & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 4, pc); dead = true; break; }
+                if (!mbar_wait(bar_done + 8 * s, (uint32_t)(k & 1), abort_s, kWaitLimitS)) { stem_raise(a, abort_s, 4, pc); dead = true; break; }
                 tc_fence_after();
                 uint32_t rr[32];
                 tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(32 * s), rr);
@@ -240,20 +250,20 @@ __global__ void __launch_bounds__(kStemThreads, 3) conv_stem_k(const StemArgs a)
     if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 64); }
 }
 
-/* weights w [co][1][27] -> the B tile [4 K chunks][32 outputs][8 bf16], K = tap: each weight quantised as the one real channel of its
-   32-channel block (src/lp_f8fwd.cu:54-71 with one channel: scale from |w| alone), as a number.  Rows 27-29 carry the fp32 bias as
+/* weights w [co][1][27] -> the B tile [4 K chunks][32 outputs][8 bf16], K as load_plane9 lays it out: each weight quantised as the one real channel of its
+   32-channel block (src/lp_f8fwd.cu:54-71 with one channel: scale from |w| alone), as a number.  Rows 9, 19 and 29 carry the fp32 bias as
    three bf16 pieces whose sum is the bias exactly (A has ones there), so the accumulator leaves the tensor core with the bias in it. */
 __global__ void prep_wstem_k(const float *__restrict__ w, const float *__restrict__ bias_p, uint8_t *__restrict__ wb, int co) {
     const int i = (int)threadIdx.x + (int)blockIdx.x * (int)blockDim.x;
     if (i >= 32 * 32) return;
-    const int c = i >> 5, tap = i & 31;
+    const int c = i >> 5, kk = i & 31, g = kk / 10, j = kk % 10;           /* K position kk: plane g, slot j (see load_plane9) */
     __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-    if (tap < 27) { if (c < co) v = __float2bfloat16_rn(fq_e4m3_one(w[(size_t)c * 27 + tap])); }
-    else if (tap < 30) {
+    if (kk < 30 && j < 9) { if (c < co) v = __float2bfloat16_rn(fq_e4m3_one(w[(size_t)c * 27 + g * 9 + j])); }
+    else if (kk < 30) {
         float rest = bias_p[c];
-        for (int k = 27; ; k++) { v = __float2bfloat16_rn(rest); if (k == tap) break; rest = __fsub_rn(rest, __bfloat162float(v)); }
+        for (int k = 0; ; k++) { v = __float2bfloat16_rn(rest); if (k == g) break; rest = __fsub_rn(rest, __bfloat162float(v)); }
     }
-    ((__nv_bfloat16 *)wb)[((tap >> 3) * 32 + c) * 8 + (tap & 7)] = v;
+    ((__nv_bfloat16 *)wb)[((kk >> 3) * 32 + c) * 8 + (kk & 7)] = v;
 }
 
 }   // namespace
@@ -276,7 +286,7 @@ int umx_conv_fwd_stem(const umx_conv *c, const void *x16, int N, int D, int H, i
     a.err = umx_errflag(); if (!a.err) return -1;
     static int slots_of[16];                                /* blocks of this kernel the device holds at once (three a multiprocessor: registers): looked up once per device */
     int dev = 0; cudaGetDevice(&dev); dev &= 15;
-    if (!slots_of[dev]) { int sms = 148; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); slots_of[dev] = 3 * sms; }
+    if (!slots_of[dev]) { int sms = 148; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); slots_of[dev] = kStemBlocks * sms; }
     long long grid = slots_of[dev]; if (grid > a.units) grid = a.units;
     const int pid = umx_prof_open(2.0 * (double)N * D * H * W * 27.0 * c->co);
     umx_launch(conv_stem_k, dim3((unsigned)grid), dim3(kStemThreads), 0, a);
