@@ -459,7 +459,11 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         /* x is the fp16 tensor [N][ci][D][H][W] itself.  The tap-packed kernel takes the one-channel 3^3 case as it is; everything else is
            quantised into scratch first and goes the usual way. */
         if (c->kind != UMX_CONV3 && c->kind != UMX_CONV1) { fprintf(stderr, "umx_conv_fwd: an fp16 input only for the 3^3 and 1^3 convs\n"); abort(); }
-        if (c->wstem && out_mode == UMX_OUT_H16B && !nb_dst) {
+        /* UMX_STEM=0 in the environment (read at every such call): always quantise first.  That path adds the taps of a one-channel conv one
+           by one in ascending order, as a sequential fp32 loop does; the tap-packed tile adds them inside one MMA. */
+        const char *env = getenv("UMX_STEM");
+        const bool stem_on = !(env && *env == '0');
+        if (stem_on && c->wstem && out_mode == UMX_OUT_H16B && !nb_dst) {
             const int r = umx_conv_fwd_stem(c, x, N, D, H, W, y);
             if (r < 0) return -1;
             if (r == 0) {
