@@ -110,9 +110,12 @@ void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);          
 int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 void lp_wmemo_clear(void);               /* src/nn_lp.h:57: drop the prepared weights kept under split_t.wkey */
-/* 3x3x3 stride-2 pad-1 conv forward (src/nn_lp.h:104; src/lp_s2.cu:647-754): E4M3 codes, fp32 accumulate.  x: xbf 3 (MX-fp8, more than 16
-   channels) or 2 (fp16 plane-major, quantised first); ys: the output shape, which must be ceil(xs / 2) per axis; y: ybf 2, 3, 4 or UMX_H16B as
-   above; gp as for lp_conv_fwd_f8.  Weights are prepared on every call, as in the reference.  Returns 0. */
+/* 3x3x3 stride-2 pad-1 conv forward (src/nn_lp.h:104; src/lp_s2.cu:647-754), fp32 accumulate.  x: xbf 3 (MX-fp8), 4 (MX-fp4) or 2 (fp16
+   plane-major, quantised to MX-fp8 first); MX tensors of 16 channels or fewer in rows of 8 / 16; ys: the output shape, which must be
+   ceil(xs / 2) per axis; y: ybf 2, 3, 4 or UMX_H16B as above (an MX output of 16 channels or fewer in rows of 8 / 16); gp as for
+   lp_conv_fwd_f8.  An MX-fp4 input without a GroupNorm transform is multiplied in MX-fp4 (E2M1 weights; the cases of the reference's
+   conv_fwd_s2_f4_k / conv_fwd_s2_f4p_k, here for every shape) and the call returns 3, the reference's "fp4 compute" report; every other
+   call computes in E4M3 and returns 0.  Weights are prepared on every call, as in the reference. */
 int lp_conv_fwd_s2_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, shape5 ys, gnp_t gp);
 
 /* ---- graph operators (the InstanceNorm / LeakyReLU / transposed-conv semantics of src/xnet.h:85-98) ---- */
@@ -120,8 +123,8 @@ enum { UMX_CONV3 = 0,      /* 3^3 stride 1 pad 1, w [co][ci][27]                
        UMX_CONV1 = 1,      /* 1^3, w [co][ci]                                            (xhead, src/nn_xnet.cu:1751-1756) */
        UMX_DOWN2 = 2,      /* 2^3 stride 2 pad 0, w [co][ci][8]; input = space-to-depth copy (src/ink3dext_net.c:104-112) */
        UMX_TCONV2 = 3,     /* ConvTranspose3d k2 s2, w [ci][co][8]                       (xtconv3_init, src/nn_xnet.cu:650-662) */
-       UMX_CONV3S2 = 4 };  /* 3^3 stride 2 pad 1, w [co][ci][27], MX-fp8 only; D, H, W of umx_conv_fwd are the input grid,
-                              the output grid is ceil(D / 2) x ceil(H / 2) x ceil(W / 2)   (conv_fwd_s2_f8_k, src/lp_s2.cu:23, 647-754) */
+       UMX_CONV3S2 = 4 };  /* 3^3 stride 2 pad 1, w [co][ci][27]; D, H, W of umx_conv_fwd are the input grid,
+                              the output grid is ceil(D / 2) x ceil(H / 2) x ceil(W / 2)   (conv_fwd_s2_f8_k, conv_fwd_s2_f4_k, src/lp_s2.cu:23, 290, 647-754) */
 enum { UMX_OUT_H16B = 0,   /* y = fp16(acc + bias), blocked fp16 */
        UMX_OUT_MX = 1,     /* y = MX(fp16(acc + bias)) into blocks [b0, ...) of an MX tensor with nb_dst blocks (xtconv_cat_q) */
        UMX_OUT_PM32 = 2,   /* y = acc + bias, plane-major fp32 [n][co][S] */

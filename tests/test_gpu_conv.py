@@ -58,16 +58,42 @@ def test_conv_parity(dev, kind, N, Ci, Co, D, H, W, bits):
     assert e < TOL, "relative L2 %.3g" % e
 
 
-@pytest.mark.parametrize("N,Ci,Co,D,H,W", S2_CASES)
-def test_conv3_stride2_parity(dev, N, Ci, Co, D, H, W):
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("N,Ci,Co,D,H,W", S2_CASES + [(2, 96, 32, 4, 8, 16)])      # three input blocks: with MX-fp4 the second K item of a tap is half padding, also at the last sample's end
+def test_conv3_stride2_parity(dev, N, Ci, Co, D, H, W, bits):
     x = synth.rng(41).standard_normal(N * Ci * D * H * W).astype(np.float32)
     w, b = synth.kaiming(42, Co, Ci, 27), synth.bias(43, Co, 0.1)
-    mx, want = oracle_conv("conv3s2", x, w, b, N, Ci, D, H, W, Co, 8)
-    got = run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, 8)
+    mx, want = oracle_conv("conv3s2", x, w, b, N, Ci, D, H, W, Co, bits)
+    got = run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, bits)
     assert got.size == want.size and np.isfinite(got).all()
     e = orc.rel_l2(got, want)
     assert e < TOL, "relative L2 %.3g" % e
-    assert np.array_equal(got, run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, 8, split=False))    # reference-layout input
+    assert np.array_equal(got, run_pm32("conv3s2", mx, w, b, N, Ci, D, H, W, Co, bits, split=False))    # reference-layout input
+
+
+@pytest.mark.parametrize("Ci,Co,ybf", [(32, 32, 3), (64, 40, 4), (96, 64, 3), (8, 16, 4), (16, 32, 3)])
+def test_lp_conv_fwd_s2_mxfp4_input(dev, Ci, Co, ybf):
+    """lp_conv_fwd_s2_f8 on an MX-fp4 tensor computes in MX-fp4 and says so (returns 3: src/lp_s2.cu:652-716), also for inputs and outputs of
+    16 channels or fewer, which are stored in rows of 8 / 16 (src/lp_common.cuh:132); exact operands, so the MX output is the oracle's bytes."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp
+    D, H, W = 6, 10, 16
+    S, So = D * H * W, (D // 2) * (H // 2) * (W // 2)
+    x = exact_operands(61, (Ci, D, H, W), 0).reshape(-1)
+    w = exact_operands(62, (Co, Ci, 27), 1)
+    b = (synth.rng(63).integers(-8, 8, Co) * 0.5).astype(np.float32)
+    mx = orc.pm_to_mx(x, 0, 1, Ci, S, 4)                       # the storage rule's row width: 8, 16 or 32 channels
+    mx32 = orc.pm_to_mx(x, 0, 1, Ci, S, 4, 32)
+    acc = orc.conv_blocked(orc.mx_to_blocked(mx32, 4, 1, Ci, S), 1, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, 4), b, Co, 3, 2, 1)
+    ob = 8 if ybf == 3 else 4
+    want = orc.pm_to_mx(orc.blocked_to_pm(acc, 1, Co, So), 0, 1, Co, So, ob)       # rows of the storage rule's width, from the accumulators
+    L = ufsm_b200.lib()
+    xd, wd, bd = DevBuf(data=mx), DevBuf(data=w), DevBuf(data=b)
+    yd = DevBuf(want.size).fill(0xEE)
+    rc = L.lp_conv_fwd_s2_f8(xd.ptr, 4, Shape5(1, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, ybf, Shape5(1, Co, D // 2, H // 2, W // 2), Gnp())
+    ufsm_b200.check()
+    assert rc == 3
+    assert np.array_equal(yd.download(), want)
 
 
 def test_conv3_stride2_exact_operands_and_lp_entry(dev):

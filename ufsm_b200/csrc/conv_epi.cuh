@@ -104,8 +104,8 @@ __device__ __forceinline__ float prep_src(const PrepArgs &p, int row, int tap, i
     if (kb >= p.nkb) return 0.f;
     if (p.kind == UMX_CONV3) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + tap] : 0.f; }
     if (p.kind == UMX_CONV1) { const int ci = kb * 32 + k; return (row < p.co && ci < p.ci) ? p.w[(size_t)row * p.ci + ci] : 0.f; }
-    if (p.kind == UMX_CONV3S2) {   /* K block = tap * blocks(ci) + block */
-        const int nbi = (p.ci + 31) / 32, t = kb / nbi, ci = (kb % nbi) * 32 + k;
+    if (p.kind == UMX_CONV3S2) {   /* K block = tap * blocks(ci) + block; MX-fp4: the blocks of a tap padded to an even count (zero weights) */
+        const int nb = (p.ci + 31) / 32, nbi = p.bits == 4 ? (nb + 1) / 2 * 2 : nb, t = kb / nbi, ci = (kb % nbi) * 32 + k;
         return (row < p.co && ci < p.ci) ? p.w[((size_t)row * p.ci + ci) * 27 + t] : 0.f;
     }
     if (p.kind == UMX_DOWN2) {   /* K block = sub-voxel tap * blocks(ci) + block */

@@ -54,7 +54,7 @@ struct ConvArgs {
        runs the epilogue (no block waits for another; the order of the additions is fixed) */
     int ksplit; float *ks_part; unsigned *ks_tickets;
     /* 3^3 stride-2 pad-1 conv: K item = (tap, input block), each item's A tile is its own strided TMA load from the input grid Di x Hi x Wi */
-    int s2, nbi, Di, Hi, Wi;
+    int s2, nbi, nit, Di, Hi, Wi;       /* stride-2 conv: blocks of the input tensor, K items per tap, input grid */
     EpiArgs e;
     int *err;
 };
@@ -136,8 +136,10 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                     for (int j = 0; j < items; j++) {
                         const int ki = 4 * st + j;
                         if (a.s2) {   /* every second voxel of the input, starting at 2 v + tap - 1 (voxels outside the grid arrive as zeros: the padding) */
-                            const int tap = ki / a.nbi, blk = ki - tap * a.nbi;
-                            tma_load_5d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, 2 * x0 + tap % 3 - 1, 2 * y0 + (tap / 3) % 3 - 1, 2 * z + tap / 9 - 1, (n * a.nbi + blk) * 2);
+                            /* K item ki = tap * a.nit + i: fp8: block i (its two half planes); fp4: blocks 2 i and 2 i + 1 (the second may lie past the
+                               sample's last block: its weights are zero and its scale is read as 1) */
+                            const int tap = ki / a.nit, blk = ki - tap * a.nit;
+                            tma_load_5d(smem_u32(sb + a.offA + j * 4096), &map0, bar, 0, 2 * x0 + tap % 3 - 1, 2 * y0 + (tap / 3) % 3 - 1, 2 * z + tap / 9 - 1, BITS == 8 ? (n * a.nbi + blk) * 2 : n * a.nbi + 2 * blk);
                         } else
                         tma_load_4d(smem_u32(sb + a.offA + j * 4096), &map0, bar, x0 * 16, y0, z, BITS == 8 ? (n * a.nkb + ki) * 2 : n * a.nkb + 2 * ki);
                     }
@@ -220,11 +222,19 @@ __global__ void __launch_bounds__(kThreads) conv_mx_k(const __grid_constant__ CU
                 for (int j = 0; j < items; j++) {
                     const int ki = 4 * st + j;
                     if (a.s2) {
-                        const int tap = ki / a.nbi, blk = ki - tap * a.nbi;
+                        const int tap = ki / a.nit, blk = ki - tap * a.nit;
                         const int iz = 2 * z + tap / 9 - 1, iy = 2 * oy + (tap / 3) % 3 - 1, ix = 2 * ox + tap % 3 - 1;
                         const bool in = row_ok && iz >= 0 && iz < a.Di && iy >= 0 && iy < a.Hi && ix >= 0 && ix < a.Wi;
-                        const unsigned b = in ? a.x_sc[((size_t)n * a.nbi + blk) * ((size_t)a.Di * a.Hi * a.Wi) + ((size_t)iz * a.Hi + iy) * a.Wi + ix] : 127u;
-                        wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
+                        const size_t Si = (size_t)a.Di * a.Hi * a.Wi, vi = ((size_t)iz * a.Hi + iy) * a.Wi + ix;
+                        if (BITS == 8) {
+                            const unsigned b = in ? a.x_sc[((size_t)n * a.nbi + blk) * Si + vi] : 127u;
+                            wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
+                        } else {
+                            const unsigned b0 = in ? a.x_sc[((size_t)n * a.nbi + 2 * blk) * Si + vi] : 127u;
+                            const unsigned b1 = (in && 2 * blk + 1 < a.nbi) ? a.x_sc[((size_t)n * a.nbi + 2 * blk + 1) * Si + vi] : 127u;
+                            const unsigned h = b0 | (b1 << 8);
+                            wq[j >> 1] = (wq[j >> 1] & ~(0xffffu << (16 * (j & 1)))) | (h << (16 * (j & 1)));
+                        }
                     } else if (BITS == 8) {
                         const unsigned b = row_ok ? a.x_sc[((size_t)n * a.nkb + ki) * S + vox] : 127u;
                         wq[j >> 2] = (wq[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (b << (8 * (j & 3)));
@@ -394,12 +404,14 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, in
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
     if (!umx_ready("umx_conv_create")) return nullptr;
-    if ((bits != 8 && bits != 4) || kind < 0 || kind > 4 || co < 1 || ci < 1 || (kind == UMX_CONV3S2 && bits != 8)) { fprintf(stderr, "umx_conv_create: bad arguments (kind %d, co %d, ci %d, bits %d)\n", kind, co, ci, bits); abort(); }
+    if ((bits != 8 && bits != 4) || kind < 0 || kind > 4 || co < 1 || ci < 1 ) { fprintf(stderr, "umx_conv_create: bad arguments (kind %d, co %d, ci %d, bits %d)\n", kind, co, ci, bits); abort(); }
     umx_conv *c = (umx_conv *)calloc(1, sizeof *c);
     c->kind = kind; c->co = co; c->ci = ci; c->bits = bits;
     c->taps = kind == UMX_CONV3 ? 27 : 1;
     const int nbi = ceil_div(ci, 32);
-    c->nkb = kind == UMX_DOWN2 ? 8 * nbi : kind == UMX_CONV3S2 ? 27 * nbi : nbi;   /* K blocks of the GEMM: (sub-voxel or tap) x input blocks */
+    /* K blocks of the GEMM: (sub-voxel or tap) x input blocks; the MX-fp4 stride-2 conv pads the blocks of a tap to an even count, so that a
+       K item of two blocks never spans two taps (two different shifts of the input) */
+    c->nkb = kind == UMX_DOWN2 ? 8 * nbi : kind == UMX_CONV3S2 ? 27 * (bits == 4 ? 2 * ceil_div(nbi, 2) : nbi) : nbi;
     c->nki = bits == 8 ? c->nkb : ceil_div(c->nkb, 2);
     c->cob_t = ceil_div(co, 32);
     c->cop = (kind == UMX_TCONV2 ? 8 : 1) * c->cob_t * 32;
@@ -482,9 +494,9 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     ConvArgs a; memset(&a, 0, sizeof a);
     /* the stride-2 3^3 conv is given its input grid; its GEMM rows are the output grid ceil(D / 2) x ceil(H / 2) x ceil(W / 2) */
     const bool s2 = c->kind == UMX_CONV3S2;
-    const int Dx = D, Hx = H, Wx = W, nbx = s2 ? c->nkb / 27 : c->nkb;          /* grid and 32-channel blocks of the tensor x */
+    const int Dx = D, Hx = H, Wx = W, nbx = s2 ? ceil_div(c->ci, 32) : c->nkb;  /* grid and 32-channel blocks of the tensor x */
     const size_t Sx = (size_t)Dx * Hx * Wx;
-    if (s2) { D = (D + 1) / 2; H = (H + 1) / 2; W = (W + 1) / 2; a.s2 = 1; a.nbi = nbx; a.Di = Dx; a.Hi = Hx; a.Wi = Wx; }
+    if (s2) { D = (D + 1) / 2; H = (H + 1) / 2; W = (W + 1) / 2; a.s2 = 1; a.nbi = nbx; a.nit = c->nki / 27; a.Di = Dx; a.Hi = Hx; a.Wi = Wx; }
     a.N = N; a.D = D; a.H = H; a.W = W; a.nkb = c->nkb; a.nki = c->nki; a.taps = c->taps; a.bits = c->bits;
     a.cop = c->cop; a.nt = c->nt; a.ntiles_n = c->ntiles_n; a.tiles_x = ceil_div(W, 8); a.tiles_y = ceil_div(H, 16);
     a.w_stage_bytes = c->w_stage_bytes; a.nst = c->nst; a.items_max = c->items_max; a.ipq = c->ipq; a.nquad = c->nquad;
@@ -527,7 +539,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     CUtensorMap m0; memset(&m0, 0, sizeof m0);
     if (s2) {
         /* [plane][z][y][x][16 B] with a traversal stride of two voxels along x and y: a box of 16 x 32 voxel positions delivers 8 x 16 voxels */
-        const cuuint64_t gd[5] = {16, (cuuint64_t)Wx, (cuuint64_t)Hx, (cuuint64_t)Dx, (cuuint64_t)N * nbx * 2};
+        const cuuint64_t gd[5] = {16, (cuuint64_t)Wx, (cuuint64_t)Hx, (cuuint64_t)Dx, (cuuint64_t)N * nbx * (c->bits == 8 ? 2 : 1)};
         const cuuint64_t gs[4] = {16, (cuuint64_t)Wx * 16, (cuuint64_t)Wx * Hx * 16, (cuuint64_t)Sx * 16};
         const cuuint32_t box[5] = {16, 16, 32, 1, 2}, es[5] = {1, 2, 2, 1, 1};
         const CUresult r0 = enc(&m0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, (void *)x, gd, gs, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -336,29 +336,44 @@ extern "C" int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w,
 extern "C" int lp_conv_fwd_s2_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, shape5 ys, gnp_t gp) {
     const char *fn = "lp_conv_fwd_s2_f8";
     if (!umx_ready(fn)) return 0;
-    if (xs.c <= 16) not_built(fn, "an input of 16 channels or fewer (8 / 16-wide MX rows)");
-    if (!gp.G && xbf != UMX_F16 && xbf != UMX_MX8) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX-fp8)\n", fn, xbf); abort(); }
+    const bool x_mx = xbf == UMX_MX8 || xbf == UMX_MX4;
+    if (xbf != UMX_F16 && !x_mx) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major, MX-fp8 or MX-fp4)\n", fn, xbf); abort(); }
     if (ys.n != xs.n || ys.c != cout || ys.d != (xs.d + 1) / 2 || ys.h != (xs.h + 1) / 2 || ys.w != (xs.w + 1) / 2) {
         fprintf(stderr, "%s: output shape %d x %d x %d x %d x %d does not follow from the input\n", fn, ys.n, ys.c, ys.d, ys.h, ys.w); abort();
     }
     int out_mode, out_bits = 0;
     if (ybf == UMX_F16) out_mode = UMX_OUT_PM16;
-    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; if (cout <= 16) not_built(fn, "an MX output of 16 channels or fewer"); }
+    else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; }
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
-    const size_t S = (size_t)xs.d * xs.h * xs.w;
-    const void *xq = x;
-    if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, 8); if (!xq) return 0; xbf = UMX_F16; }
+    const size_t S = (size_t)xs.d * xs.h * xs.w, So = (size_t)ys.d * ys.h * ys.w;
+    if (!S || !xs.n) return 0;
+    /* An MX-fp4 input that needs no GroupNorm is multiplied as MX-fp4 (weights quantised to E2M1): the reference's conv_fwd_s2_f4_k /
+       conv_fwd_s2_f4p_k cases (src/lp_s2.cu:652-716), reported by the return value 3.  Everything else computes in MX-fp8; a GroupNorm
+       input is transformed and requantised to MX-fp8 first, as the reference's s2_prenorm_k path does (src/lp_s2.cu:733-744). */
+    const int bits = (xbf == UMX_MX4 && !gp.G) ? 4 : 8;
+    const void *xq = x; int xflags = 0;
+    if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, 8); if (!xq) return 0; xflags = UMX_X_SPLIT; }
     else if (xbf == UMX_F16) {
         void *ws = umx_ws(0, umx_mx_bytes32(8, xs.n, xs.c, S));
         if (!ws) return 0;
         umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, 8, UMX_LAYOUT_SPLIT);
+        xq = ws; xflags = UMX_X_SPLIT;
+    } else if (xs.c <= 16) {                                   /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
+        void *ws = umx_ws(3, umx_mx_bytes32(bits, xs.n, xs.c, S));
+        if (!ws) return 0;
+        umx_mx_rewidth(x, bits, xs.n, xs.c, S, ws, 1);
         xq = ws;
     }
-    umx_conv *c = umx_conv_create_dev(UMX_CONV3S2, w, b, cout, xs.c, 8);
+    /* an MX output of 16 channels or fewer is stored in rows of 8 / 16: the conv writes 32-wide rows into scratch, which are narrowed */
+    const bool narrow = out_mode == UMX_OUT_MXRAW && cout <= 16;
+    void *yq = y;
+    if (narrow) { yq = umx_ws(4, umx_mx_bytes32(out_bits, xs.n, cout, So)); if (!yq) return 0; }
+    umx_conv *c = umx_conv_create_dev(UMX_CONV3S2, w, b, cout, xs.c, bits);
     if (!c) return 0;
-    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, y, out_mode, out_bits, 0, 0, nullptr, xbf == UMX_F16 ? UMX_X_SPLIT : 0);
+    umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, yq, out_mode, out_bits, 0, 0, nullptr, xflags);
+    if (narrow) umx_mx_rewidth(yq, out_bits, xs.n, cout, So, y, 0);
     cudaDeviceSynchronize();
     umx_conv_free(c);
-    return 0;
+    return bits == 4 ? 3 : 0;
 }
