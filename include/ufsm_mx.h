@@ -100,13 +100,20 @@ void umx_mx_relayout(const void *src, int bits, int N, int C, size_t S, void *ds
 void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);                   /* blocked fp16 -> plane-major fp32 */
 
 /* ---- 3x3x3 stride-1 pad-1 conv forward, the reference's entry points (src/nn_lp.h:53-54; src/lp_f8fwd.cu:26-52,
-   src/lp_f4fwd.cu:30-51).  x: device, xbf 3 / 4 (MX, more than 16 channels so that rows are 32 wide) or 2 (fp16 plane-major,
-   quantised to the conv's MX format first); w: device fp32 [cout][cin][27]; b: device fp32 [cout] or NULL; y: ybf 2 (fp16
-   plane-major), 3 / 4 (MX, acc + bias requantised per 32 output channels) or UMX_H16B.  lp_conv_fwd_f8 multiplies E4M3 codes,
-   lp_conv_fwd_f4 E2M1 codes; an MX input of the other format aborts.  gp.G != 0: the GroupNorm + SiLU input transform
-   silu(fma(x, rstd gamma, beta - mean rstd gamma)) (src/lp_common.cuh:244-261, 474-482), applied and quantised to the conv's format in a
-   pass ahead of the conv (x may then be fp32 / fp16 plane-major or either MX format).  Supported subset otherwise: osum == NULL, split_t
-   zero except wkey (prepared-weight memo key), no slab-local GroupNorm (gp.ns <= 1).  Anything else prints "not built" and aborts.  Returns 0. ---- */
+   src/lp_f4fwd.cu:30-51).  x: device, xbf 3 / 4 (MX; 16 channels or fewer in rows of 8 / 16) or 2 (fp16 plane-major, quantised to the
+   conv's MX format first); w: device fp32 [cout][cin][27]; b: device fp32 [cout] or NULL; y: ybf 2 (fp16 plane-major), 3 / 4 (MX,
+   acc + bias requantised per 32 output channels; 16 channels or fewer in rows of 8 / 16) or UMX_H16B.  lp_conv_fwd_f8 multiplies E4M3
+   codes, lp_conv_fwd_f4 E2M1 codes; an MX input of the other format needs a transform that requantises it.  gp.G != 0: the GroupNorm +
+   SiLU input transform silu(fma(x, rstd gamma, beta - mean rstd gamma)) (src/lp_common.cuh:244-261, 474-482), applied and quantised to
+   the conv's format in a pass ahead of the conv (x may then be fp32 / fp16 plane-major or either MX format).
+   split_t (src/nn_lp.h:20-41), served by passes into scratch around the conv: x2 / c_split (concat input; MX parts keep their own
+   32-channel blocks, parts of 16 channels or fewer in rows of 8 / 16), gp2, up (the x part at half resolution, read as its trilinear 2x
+   upsample), y2 / o_split / o_pad (split output, fp16 plane-major or MX, each part an MX tensor of its own rows), accum (fp16
+   plane-major y += conv), osum / Go with stored_stats (exact GroupNorm sums of the stored MX values over the planes [zlo, D - zhi); of a
+   split output when its first part ends on a 32-channel block), zi0 / Di, zw0 / zw1, yD / yzo (z range, z window, output into a deeper
+   tensor), wkey (prepared-weight memo).  What is not built prints "... is not built in this library" and aborts: stochastic rounding
+   (sr / osr), slab-local GroupNorm (gnp_t.ns > 1), osum of unrounded accumulators (stored_stats 0) or of a non-MX output, the z fields
+   together with up, a split output or osum, a transform of parts of 16 channels or fewer.  Returns 0. ---- */
 int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 void lp_wmemo_clear(void);               /* src/nn_lp.h:57: drop the prepared weights kept under split_t.wkey */

@@ -62,6 +62,8 @@ CASES = [
     (3, 8, 32, 32, False, "all"),
     (2, 8, 32, 48, False, "seg"),
     (4, 8, 32, 32, True, "seg"),        # MX-fp4 storage into an MX-fp8 conv: the transform requantises
+    (3, 8, 16, 32, False, ""),          # an MX part of 16 channels: rows of 16 (src/lp_common.cuh:132)
+    (4, 4, 8, 8, False, ""),            # two parts in rows of 8
 ]
 
 
@@ -83,8 +85,8 @@ def test_concat_input(dev, xbf, bits, Cx, C2, up, gn):
         sa, sb_ = xa.astype(np.float16), xb.astype(np.float16)
         da, db = sa.astype(f32), sb_.astype(f32)
     else:
-        sa, sb_ = orc.pm_to_mx(xa, 0, N, Cx, Sc, sb, 32), orc.pm_to_mx(xb, 0, N, C2, S, sb, 32)
-        da, db = orc.mx_to_pm(sa, sb, N, Cx, Sc, 32), orc.mx_to_pm(sb_, sb, N, C2, S, 32)
+        sa, sb_ = orc.pm_to_mx(xa, 0, N, Cx, Sc, sb), orc.pm_to_mx(xb, 0, N, C2, S, sb)           # rows of the storage rule's width
+        da, db = orc.mx_to_pm(sa, sb, N, Cx, Sc), orc.mx_to_pm(sb_, sb, N, C2, S)
     gp, sp = Gnp(), Split()
     if gn == "seg":
         pa, pb = gn_params(205, N, Cx, 8), gn_params(206, N, C2, 4)
@@ -121,7 +123,7 @@ def test_concat_input(dev, xbf, bits, Cx, C2, up, gn):
     assert e < TOL
 
 
-@pytest.mark.parametrize("ybf,Ox,O2", [(2, 40, 24), (3, 32, 32), (3, 40, 56), (4, 64, 32)])
+@pytest.mark.parametrize("ybf,Ox,O2", [(2, 40, 24), (3, 32, 32), (3, 40, 56), (4, 64, 32), (3, 16, 16), (4, 8, 40), (3, 40, 8)])
 def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp, Split
@@ -136,9 +138,11 @@ def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
     xd, wd, bd = DevBuf(data=mx), DevBuf(data=w), DevBuf(data=b)
     sp = Split()
     ob = 8 if ybf == 3 else 4
-    nbytes = (lambda c: N * c * S * 2) if ybf == 2 else (lambda c: orc.mx_bytes(ob, N, c, S, 32))
+    nbytes = (lambda c: N * c * S * 2) if ybf == 2 else (lambda c: orc.mx_bytes(ob, N, c, S))      # parts of 16 channels or fewer in rows of 8 / 16
     yd, y2d = DevBuf(nbytes(Ox)).fill(0xEE), DevBuf(nbytes(O2)).fill(0xEE)
     sp.y2, sp.o_split = y2d.ptr, Ox
+    if Ox <= 16 and O2 <= 16:
+        sp.o_pad = 16                                        # what the reference's caller passes for two such tensors (src/nn_lp.h:32)
     assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, ybf, Gnp(), None, 0, sp) == 0
     ufsm_b200.check()
     for buf, c0, c in ((yd, 0, Ox), (y2d, Ox, O2)):
@@ -148,11 +152,11 @@ def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
             assert orc.rel_l2(got, part.astype(np.float16).astype(f32)) < TOL
         else:
             got = buf.download()
-            wmx = orc.pm_to_mx(part, 0, N, c, S, ob, 32)          # each part an MX tensor of its own blocks
+            wmx = orc.pm_to_mx(part, 0, N, c, S, ob)              # each part an MX tensor of its own blocks
             assert got.size == wmx.size
             frac = np.count_nonzero(got != wmx) / got.size
             assert frac < (2e-3 if ob == 8 else 1e-3), frac           # accumulation order flips a code now and then
-            assert orc.rel_l2(orc.mx_to_pm(got, ob, N, c, S, 32), orc.mx_to_pm(wmx, ob, N, c, S, 32)) < (5e-3 if ob == 8 else 2e-2)
+            assert orc.rel_l2(orc.mx_to_pm(got, ob, N, c, S), orc.mx_to_pm(wmx, ob, N, c, S)) < (5e-3 if ob == 8 else 2e-2)
     if ybf == 2:
         return
     # the same conv, one MX output, with the GroupNorm sums of the stored values over the planes [zlo, D - zhi)
@@ -167,6 +171,17 @@ def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
     got = ws[:, 1].astype(np.int64).astype(np.float64) + ws[:, 0].astype(np.float64) * 2.0 ** -64
     exp = np.stack([stored.sum((2, 3, 4)), (stored * stored).sum((2, 3, 4))], 2).reshape(-1)
     assert (ws[:, 2] == 0).all() and np.allclose(got, exp, rtol=1e-13, atol=1e-9)
+    if Ox % 32 or O2 <= 16:
+        return
+    # and of a split output whose first part ends on a block: the same sums, the same bytes in the two tensors
+    sums2 = DevBuf(N * Go * 2 * 24).fill(0)
+    sp.y2, sp.o_split = y2d.fill(0xEE).ptr, Ox
+    assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.fill(0xEE).ptr, ybf, Gnp(), sums2.ptr, Go, sp) == 0
+    ufsm_b200.check()
+    assert np.array_equal(sums2.download(), sums.download())
+    whole = orc.mx_to_pm(yall.download(), ob, N, Co, S, 32).reshape(N, Co, S)
+    assert np.array_equal(orc.mx_to_pm(yd.download(), ob, N, Ox, S, 32).reshape(N, Ox, S), whole[:, :Ox])
+    assert np.array_equal(orc.mx_to_pm(y2d.download(), ob, N, O2, S, 32).reshape(N, O2, S), whole[:, Ox:])
 
 
 def test_unbuilt_fields_stop(dev):

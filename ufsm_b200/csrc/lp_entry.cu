@@ -111,7 +111,10 @@ __global__ void __launch_bounds__(256) h16_add_k(__half *__restrict__ y, const _
 
 static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp) {
     if (!umx_ready(fn)) return 0;
-    if (sp.sr || sp.osr || sp.o_pad) not_built(fn, "split_t.sr / osr / o_pad");
+    if (sp.sr || sp.osr) not_built(fn, "stochastic rounding (split_t.sr / osr)");
+    /* o_pad places the second output tensor's rows inside the reference's padded GEMM (src/nn_lp.h:32): here each output tensor has its own
+       blocks whatever it says; the values the reference uses are accepted */
+    if (sp.o_pad && !(sp.y2 && (sp.o_pad == 16 || sp.o_pad == (sp.o_split + 31) / 32 * 32))) { fprintf(stderr, "%s: split_t.o_pad %d with o_split %d\n", fn, (int)sp.o_pad, sp.o_split); abort(); }
     if (sp.accum) {
         /* y += conv: the conv into scratch, then one rounding of the fp16 sum (the reference adds in its epilogue, src/lp_common.cuh:1567-1571,
            and rounds once as well, but from the fp32 accumulator: the two can differ by the rounding of the conv's own fp16 result) */
@@ -181,7 +184,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     const int xb_bits = xbf == UMX_MX8 ? 8 : 4;
     const int Ci = xs.c, Cx = sp.x2 ? sp.c_split : Ci, C2 = Ci - Cx;
     if (sp.x2 && (Cx < 1 || C2 < 1)) { fprintf(stderr, "%s: c_split %d of %d input channels\n", fn, Cx, Ci); abort(); }
-    if (sp.x2 && x_mx && (Cx <= 16 || C2 <= 16)) not_built(fn, "a concat input with a part of 16 channels or fewer (8 / 16-wide MX rows)");
+    if (sp.x2 && x_mx && (Cx <= 16 || C2 <= 16) && (any_gn_(gp, sp) || sp.up)) not_built(fn, "a transform of a concat input with a part of 16 channels or fewer (8 / 16-wide MX rows)");
     if (Ci <= 16 && any_gn_(gp, sp)) not_built(fn, "a GroupNorm transform of an input of 16 channels or fewer");
     if (xbf != UMX_F16 && !x_mx) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX)\n", fn, xbf); abort(); }
     const bool any_gn = gp.G || sp.gp2.G;
@@ -192,16 +195,15 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     else if (ybf == UMX_MX8 || ybf == UMX_MX4) { out_mode = UMX_OUT_MXRAW; out_bits = ybf == UMX_MX8 ? 8 : 4; }
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
-    const bool narrow_out = out_mode == UMX_OUT_MXRAW && cout <= 16;      /* rows of 8 / 16 channels: written 32 wide into scratch, then narrowed */
-    if (narrow_out && (sp.y2 || osum)) not_built(fn, "a split output or output statistics with 16 output channels or fewer");
+    const bool narrow_out = out_mode == UMX_OUT_MXRAW && cout <= 16 && !sp.y2;      /* rows of 8 / 16 channels: written 32 wide into scratch, then narrowed */
+    if (narrow_out && osum) not_built(fn, "output statistics with 16 output channels or fewer");
     const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
     if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
     if (sp.y2 && out_mode == UMX_OUT_H16B) not_built(fn, "a split output in blocked fp16");
-    if (sp.y2 && out_mode == UMX_OUT_MXRAW && (Ox <= 16 || O2 <= 16)) not_built(fn, "a split MX output with a part of 16 channels or fewer");
     if (osum || Go) {
         if (!osum || Go < 1) { fprintf(stderr, "%s: osum %p with %d groups\n", fn, (void *)osum, Go); abort(); }
         if (out_mode != UMX_OUT_MXRAW || !sp.stored_stats) not_built(fn, "output statistics of the unrounded accumulators (osum needs an MX output and split_t.stored_stats)");
-        if (sp.y2) not_built(fn, "output statistics of a split output");
+        if (sp.y2 && ((Ox & 31) || O2 <= 16)) not_built(fn, "output statistics of a split output whose first part does not end on a 32-channel block");
         if (Go > 64 || cout % Go) { fprintf(stderr, "%s: %d output channels in %d groups\n", fn, cout, Go); abort(); }
     }
     const size_t S = (size_t)xs.d * xs.h * xs.w;
@@ -260,6 +262,12 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
             } else if (x_mx) {
                 if (xbf != mxin) { fprintf(stderr, "%s: an MX-fp%d input segment of an MX-fp%d conv without a transform\n", fn, xb_bits, bits); abort(); }
                 blocks = (const uint8_t *)src;
+                if (C <= 16) {                                 /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
+                    uint8_t *t = (uint8_t *)umx_ws(3 + seg, umx_mx_bytes32(bits, xs.n, C, S));
+                    if (!t) return 0;
+                    umx_mx_rewidth(src, bits, xs.n, C, S, t, 1);
+                    blocks = t;
+                }
             } else {
                 uint8_t *t = (uint8_t *)umx_ws(3 + seg, umx_mx_bytes32(bits, xs.n, C, S));
                 if (!t) return 0;
@@ -313,10 +321,22 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         uint8_t *t = (uint8_t *)umx_ws(4, umx_mx_bytes32(out_bits, xs.n, (nb1 + nb2) * 32, S));
         if (!t) return 0;
         umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, t, out_mode, out_bits, 0, 0, nullptr, xflags);
-        mx_blocks_copy(t, nb1 + nb2, 0, (const uint8_t *)y, nb1, xs.n, S, out_bits, true);
-        mx_blocks_copy(t, nb1 + nb2, nb1, (const uint8_t *)sp.y2, nb2, xs.n, S, out_bits, true);
+        for (int part = 0; part < 2; part++) {
+            const int Cp = part ? O2 : Ox, nbp = part ? nb2 : nb1, b0 = part ? nb1 : 0;
+            uint8_t *dst = (uint8_t *)(part ? sp.y2 : y);
+            if (Cp > 16) { mx_blocks_copy(t, nb1 + nb2, b0, dst, nbp, xs.n, S, out_bits, true); continue; }
+            uint8_t *one = (uint8_t *)umx_ws(7, umx_mx_bytes32(out_bits, xs.n, Cp, S));      /* a part of 16 channels or fewer is stored in rows of 8 / 16 */
+            if (!one) return 0;
+            mx_blocks_copy(t, nb1 + nb2, b0, one, 1, xs.n, S, out_bits, true);
+            umx_mx_rewidth(one, out_bits, xs.n, Cp, S, dst, 0);
+        }
+        if (osum) {                                            /* Ox ends on a block: the scratch tensor is the cout-channel output */
+            const size_t hw = (size_t)xs.h * xs.w, v0 = (size_t)sp.zlo * hw, v1 = S - (size_t)sp.zhi * hw;
+            if (sp.zlo < 0 || sp.zhi < 0 || sp.zlo + sp.zhi > xs.d) { fprintf(stderr, "%s: zlo %d + zhi %d of %d planes\n", fn, sp.zlo, sp.zhi, xs.d); abort(); }
+            if (lp_gn_sums_mx(t, ybf, xs.n, cout, Go, S, osum, v0, v1) != 0) { fprintf(stderr, "%s: output statistics of %d channels in %d groups\n", fn, cout, Go); abort(); }
+        }
     }
-    if (osum) {
+    if (osum && !sp.y2) {
         /* statistics of the stored values (split_t.stored_stats) over the planes [zlo, D - zhi): exact sums into the caller's slots */
         const size_t hw = (size_t)xs.h * xs.w, v0 = (size_t)sp.zlo * hw, v1 = S - (size_t)sp.zhi * hw;
         if (sp.zlo < 0 || sp.zhi < 0 || sp.zlo + sp.zhi > xs.d) { fprintf(stderr, "%s: zlo %d + zhi %d of %d planes\n", fn, sp.zlo, sp.zhi, xs.d); abort(); }
