@@ -240,6 +240,23 @@ long umx_unet_launches(const umx_unet *u);                       /* kernels laun
 long umx_launch_count(void);                                     /* kernels launched by the library in this process */
 void umx_u8_to_h16(const uint8_t *x_dev, size_t n, void *y_dev); /* CT bytes -> fp16 x / 255 */
 void umx_h16_to_prob_u8(const void *x_dev, size_t n, uint8_t *y_dev);   /* fp16 logits -> uint8 round(254 sigmoid), the probability bytes predict writes */
+/* ---- the back end of the reference's predict on the device (src/nn.h:385, 871-885; src/nn_elem.cu:1096-1178): one head's logits of a
+   D x W x W window -> probability bytes trunc(255 sigmoid(logit) + 0.5) where the CT voxel is material (0 elsewhere), the window's halo
+   cropped (hz planes at either z end, halo voxels in y and x), written at (oz + z, oy + y, ox + x) of a device shard buffer [shard]^3 as
+   far as that lies inside [0, ez) x [0, ey) x [0, ex).  lg: device fp32 logits, or fp16 after nn_set_logits_h16(1).  Material: ct >= the
+   threshold of nn_set_pred_iso (default 1: CT != 0), or bit k of a mask made by nn_pred_ctmask(_t) (word k >> 5, bit k & 31).  The flag
+   and the threshold are kept per device.  nn_pred_place_mz: the window is held from plane zoff on and only its planes [zlo, zhi) are placed. */
+void nn_set_logits_h16(int on);
+void nn_set_pred_iso(int t);
+int nn_get_pred_iso(void);
+void nn_pred_output(const float *lg, const uint8_t *ct, size_t n, uint8_t *out);             /* every voxel, no crop; material where ct != 0 */
+void nn_pred_place(const float *lg, const uint8_t *ct, int W, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
+void nn_pred_place_d(const float *lg, const uint8_t *ct, int D, int W, int hz, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
+void nn_pred_ctmask(const uint8_t *ct, size_t n, uint32_t *bits);
+void nn_pred_ctmask_t(const uint8_t *ct, size_t n, uint32_t *bits, int t);
+void nn_pred_place_m(const float *lg, const uint32_t *bits, int W, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
+void nn_pred_place_m_d(const float *lg, const uint32_t *bits, int D, int W, int hz, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
+void nn_pred_place_mz(const float *lg, const uint32_t *bits, int W, int halo, int zlo, int zhi, int zoff, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
 /* the reference's blend arithmetic, kept as an operator of its own: acc[c][z - zlo][y][x] = fma(w, logits[c][patch voxel], acc), wsum += w with
    the separable Gaussian window w1d (device, P floats) for the patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend,
    src/nn_ink3dext.cu:58-73); fp32 sums, so the result depends on the order of the calls */

@@ -267,6 +267,41 @@ def pred_input(ct, W, mean, isd, dyo, dxo, axis, z0, nz, hd):
     return out
 
 
+def prob255(lg):
+    """the probability byte of the reference's predict back end (src/nn_elem.cu:1100, 1123): trunc(255 / (1 + exp(-logit)) + 0.5), fp32"""
+    lg = np.asarray(lg, np.float32)
+    with np.errstate(over="ignore"):
+        e = np.exp(-lg, dtype=np.float32)
+    return (np.float32(255) / (np.float32(1) + e) + np.float32(0.5)).astype(np.uint8)
+
+
+def pred_place(lg, material, D, W, hz, halo, oz, oy, ox, ez, ey, ex, shard, dsh, zoff=0, zlo=None, zhi=None):
+    """nn_pred_place_d / _m_d / _mz (src/nn_elem.cu:1107-1178): the interior of a window (held from plane zoff on: lg and material are
+    [D - zoff.., W, W] arrays indexed by z - zoff) into the shard buffer dsh [shard]^3 (modified in place) at (oz, oy, ox), clipped to
+    [0, ez) x [0, ey) x [0, ex); only planes [zlo, zhi) when given."""
+    lg = np.asarray(lg, np.float32).reshape(-1, W, W)
+    material = np.asarray(material, bool).reshape(-1, W, W)
+    out = dsh.reshape(shard, shard, shard)
+    z0, z1 = max(hz, -oz), min(D - hz, ez - oz)
+    if zlo is not None:
+        z0, z1 = max(z0, zlo), min(z1, zhi)
+    y0, y1 = max(halo, -oy), min(W - halo, ey - oy)
+    x0, x1 = max(halo, -ox), min(W - halo, ex - ox)
+    if z1 <= z0 or y1 <= y0 or x1 <= x0:
+        return dsh
+    sub = (slice(z0 - zoff, z1 - zoff), slice(y0, y1), slice(x0, x1))
+    out[oz + z0:oz + z1, oy + y0:oy + y1, ox + x0:ox + x1] = np.where(material[sub], prob255(lg[sub]), 0).astype(np.uint8)
+    return dsh
+
+
+def ctmask(ct, t=1):
+    """nn_pred_ctmask_t (src/nn_elem.cu:1135-1144): bit k & 31 of word k >> 5 = ct[k] >= t"""
+    ct = np.asarray(ct, np.uint8).ravel()
+    b = np.zeros((ct.size + 31) // 32 * 32, np.uint8)
+    b[:ct.size] = ct >= max(t, 1)
+    return np.packbits(b.reshape(-1, 32), axis=1, bitorder="little").view(np.uint32).ravel()
+
+
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

@@ -268,3 +268,20 @@ def test_one_channel_fp8_row_is_rounding_to_four_bits():
     u = x.view(np.uint32).astype(np.uint64)
     got = ((u + 0x7FFFF + ((u >> 20) & 1)) & 0xFFF00000).astype(np.uint32).view(np.float32)
     assert np.array_equal(got, want) and np.array_equal(np.signbit(got), np.signbit(want))
+
+
+def test_predict_back_end_restatement():
+    """prob255 / pred_place / ctmask (the predict back end, src/nn_elem.cu:1096-1178): known answers and the box arithmetic"""
+    assert list(orc.prob255([0.0, 40.0, -40.0, -200.0, np.log(3.0)])) == [128, 255, 0, 0, 191]      # 127.5 + 0.5; 255; 0; exp overflow; 191.25 + 0.5
+    W, halo, shard = 8, 2, 10
+    lg = np.zeros(W ** 3, np.float32)
+    mat = np.ones(W ** 3, bool)
+    mat[(3 * W + 3) * W + 3] = False
+    out = orc.pred_place(lg, mat, W, W, halo, halo, -3, 0, 5, 10, 10, 9, shard, np.full(shard ** 3, 7, np.uint8)).reshape(shard, shard, shard)
+    want = np.full((shard, shard, shard), 7, np.uint8)
+    want[0:3, 2:6, 7:9] = 128                   # z: window planes 3..5 (0..2 lie below the shard), y: 2..5, x: 2..3 (the extent ends at 9)
+    want[0, 3, 8] = 0                           # the voxel that is not material
+    assert np.array_equal(out, want)
+    ct = np.arange(70, dtype=np.uint8)
+    bits = orc.ctmask(ct, 33)
+    assert bits.size == 3 and bits[0] == 0 and bits[1] == 0xFFFFFFFE and bits[2] == 0x3F

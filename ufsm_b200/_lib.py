@@ -105,6 +105,17 @@ _SIG = {
     "umx_unet_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_submit_host_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_h16_to_prob_u8": (None, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "nn_set_logits_h16": (None, [C.c_int]),
+    "nn_set_pred_iso": (None, [C.c_int]),
+    "nn_get_pred_iso": (C.c_int, []),
+    "nn_pred_output": (None, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "nn_pred_place": (None, [C.c_void_p, C.c_void_p] + [C.c_int] * 9 + [C.c_void_p]),
+    "nn_pred_place_d": (None, [C.c_void_p, C.c_void_p] + [C.c_int] * 11 + [C.c_void_p]),
+    "nn_pred_ctmask": (None, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "nn_pred_ctmask_t": (None, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]),
+    "nn_pred_place_m": (None, [C.c_void_p, C.c_void_p] + [C.c_int] * 9 + [C.c_void_p]),
+    "nn_pred_place_m_d": (None, [C.c_void_p, C.c_void_p] + [C.c_int] * 11 + [C.c_void_p]),
+    "nn_pred_place_mz": (None, [C.c_void_p, C.c_void_p] + [C.c_int] * 12 + [C.c_void_p]),
     "umx_unet_submit_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_wait": (C.c_int, [C.c_void_p]),
     "umx_wait_selftest": (C.c_int, [C.c_longlong]),

@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libufsm_mx.so")
-CU = ["runtime.cu", "quant.cu", "norm.cu", "conv_tc.cu", "conv_tcr.cu", "conv_tcp.cu", "conv_stem.cu", "lp_entry.cu", "window.cu", "in_coef_static.cu", "gn_sums.cu", "gn_apply.cu", "mx_ops.cu"]
+CU = ["runtime.cu", "quant.cu", "norm.cu", "conv_tc.cu", "conv_tcr.cu", "conv_tcp.cu", "conv_stem.cu", "lp_entry.cu", "window.cu", "pred_place.cu", "in_coef_static.cu", "gn_sums.cu", "gn_apply.cu", "mx_ops.cu"]
 C = ["unet.c"]
 NVCC = os.environ.get("UFSM_NVCC") or shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
 GCC = os.environ.get("UFSM_GCC", "gcc")
