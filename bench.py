@@ -130,7 +130,7 @@ class Clocks(threading.Thread):
 
 
 KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
-OUT = {"h16b": 0, "mx": 1, "pm32": 2}
+OUT = {"h16b": 0, "mx": 1, "pm32": 2, "pm16": 3}
 
 
 def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0, x16=False):
@@ -154,7 +154,7 @@ def layer_time(L, kind, ci, co, size, bits=8, out="h16b", reps=5, seed=0, x16=Fa
     ufsm_b200.check()
     nbo, mode = (co + 31) // 32, OUT[out]
     So = ((D + 1) // 2) ** 3 if kind == "conv3s2" else S * (8 if kind == "tconv2" else 1)
-    nbytes = {0: nbo * So * 64, 1: nbo * So * (rb + 1), 2: co * So * 4}[mode]
+    nbytes = {0: nbo * So * 64, 1: nbo * So * (rb + 1), 2: co * So * 4, 3: co * So * 2}[mode]
     xd, yd = DevBuf(data=x), DevBuf(nbytes)
     best, ms, fl = 1e30, C.c_double(), C.c_double()
     for _ in range(reps):
