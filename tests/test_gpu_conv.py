@@ -398,7 +398,7 @@ def _gn_params(seed, N, Cn, Gn):
             (0.3 * g.standard_normal(N * Gn)).astype(np.float32), (0.5 + g.random(N * Gn)).astype(np.float32))
 
 
-@pytest.mark.parametrize("shape", [(2, 64, 8, 3, 10, 12), (1, 40, 5, 5, 21, 23)])      # the second: several runs of voxels, a ragged channel block
+@pytest.mark.parametrize("shape", [(2, 64, 8, 3, 10, 12), (1, 40, 5, 5, 21, 23), (2, 16, 4, 3, 10, 12), (1, 8, 2, 2, 9, 7)])      # the second: several runs of voxels, a ragged channel block; the last two: rows of 16 / 8 channels
 @pytest.mark.parametrize("xdt,ybits", [(3, 8), (4, 4), (3, 4), (2, 8), (0, 4)])
 def test_gn_silu_apply_mx(dev, xdt, ybits, shape):
     """Tolerance: a transcendental (expf) sits between the operands and the requantiser, so codes may differ from the CPU evaluation where a
@@ -411,14 +411,14 @@ def test_gn_silu_apply_mx(dev, xdt, ybits, shape):
     x = (synth.rng(71).standard_normal(N * Cn * S) * 2).astype(np.float32)
     gamma, beta, mean, rstd = _gn_params(72, N, Cn, Gn)
     if xdt >= 3:
-        src = orc.pm_to_mx(x, 0, N, Cn, S, 8 if xdt == 3 else 4, 32)
-        dq = orc.mx_to_pm(src, 8 if xdt == 3 else 4, N, Cn, S, 32)
+        src = orc.pm_to_mx(x, 0, N, Cn, S, 8 if xdt == 3 else 4)           # rows of the storage rule's width (8, 16 or 32 channels)
+        dq = orc.mx_to_pm(src, 8 if xdt == 3 else 4, N, Cn, S)
     elif xdt == 2:
         src = x.astype(np.float16); dq = src.astype(np.float32)
     else:
         src = x; dq = x
     want_f = _gn_silu_oracle(dq, N, Cn, S, Gn, gamma, beta, mean, rstd, 0)
-    want = orc.pm_to_mx(want_f, 0, N, Cn, S, ybits, 32)
+    want = orc.pm_to_mx(want_f, 0, N, Cn, S, ybits)
     xd, yd = DevBuf(data=src), DevBuf(want.size).fill(0xEE)
     bufs = [DevBuf(data=a) for a in (gamma, beta, mean, rstd)]
     L.lp_gn_silu_apply_mx(xd.ptr, xdt, Shape5(N, Cn, D, H, W), Gn, bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bufs[3].ptr, yd.ptr, 3 if ybits == 8 else 4)
@@ -426,22 +426,23 @@ def test_gn_silu_apply_mx(dev, xdt, ybits, shape):
     got = yd.download()
     assert got.size == want.size
     assert np.count_nonzero(got != want) <= 2e-4 * want.size, "%d of %d bytes differ" % (np.count_nonzero(got != want), want.size)
-    assert orc.rel_l2(orc.mx_to_pm(got, ybits, N, Cn, S, 32), orc.mx_to_pm(want, ybits, N, Cn, S, 32)) < TOL
+    assert orc.rel_l2(orc.mx_to_pm(got, ybits, N, Cn, S), orc.mx_to_pm(want, ybits, N, Cn, S)) < TOL
 
 
+@pytest.mark.parametrize("Ci,Gn", [(64, 8), (16, 2), (8, 1)])         # 16 and 8 channels: the MX input in rows of 16 / 8
 @pytest.mark.parametrize("s2", [False, True])
-def test_conv_entry_with_gn_silu_input_transform(dev, s2):
-    """lp_conv_fwd_f8 / lp_conv_fwd_s2_f8 with gnp_t.G = 8: silu(fma(x, a, b)) quantised to MX-fp8, then the conv; fp16 plane-major out."""
+def test_conv_entry_with_gn_silu_input_transform(dev, s2, Ci, Gn):
+    """lp_conv_fwd_f8 / lp_conv_fwd_s2_f8 with gnp_t.G != 0: silu(fma(x, a, b)) quantised to MX-fp8, then the conv; fp16 plane-major out."""
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp, Split
     L = ufsm_b200.lib()
-    N, Ci, Co, Gn, D, H, W = 1, 64, 32, 8, 4, 16, 16
+    N, Co, D, H, W = 1, 32, 4, 16, 16
     S = D * H * W
     x = (synth.rng(81).standard_normal(N * Ci * S) * 2).astype(np.float32)
     w, b = synth.kaiming(82, Co, Ci, 27), synth.bias(83, Co, 0.1)
     gamma, beta, mean, rstd = _gn_params(84, N, Ci, Gn)
-    mx = orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
-    act = _gn_silu_oracle(orc.mx_to_pm(mx, 8, N, Ci, S, 32), N, Ci, S, Gn, gamma, beta, mean, rstd, 1)
+    mx = orc.pm_to_mx(x, 0, N, Ci, S, 8)                       # rows of the storage rule's width
+    act = _gn_silu_oracle(orc.mx_to_pm(mx, 8, N, Ci, S), N, Ci, S, Gn, gamma, beta, mean, rstd, 1)
     amx = orc.pm_to_mx(act, 0, N, Ci, S, 8, 32)
     st = 2 if s2 else 1
     Do, Ho, Wo = (D + st - 1) // st, (H + st - 1) // st, (W + st - 1) // st

@@ -102,7 +102,7 @@ void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, s
    mean, rstd are the larger tensor's.  Returns 0, -1 on an unsupported combination (the caller reports it). */
 int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
                           void *y, int bits, int layout, int form, int c_off, int C_all) {
-    if (C <= 16 || G < 1 || C_all % G || c_off < 0 || c_off + C > C_all || (bits != 8 && bits != 4) || (xdt != UMX_F32 && xdt != UMX_F16 && xdt != UMX_MX8 && xdt != UMX_MX4)) return -1;
+    if (C < 1 || G < 1 || C_all % G || c_off < 0 || c_off + C > C_all || (bits != 8 && bits != 4) || (xdt != UMX_F32 && xdt != UMX_F16 && xdt != UMX_MX8 && xdt != UMX_MX4)) return -1;
     const int cpg = C_all / G;
     const int nb = (C + 31) / 32;
     if (!N || !S) return 0;
@@ -126,7 +126,28 @@ int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, con
 extern "C" void lp_gn_silu_apply_mx(const void *x, int xdt, shape5 s, int G, const float *gamma, const float *beta, const float *mean, const float *rstd, void *y, int ydt) {
     if (!umx_ready("lp_gn_silu_apply_mx")) return;
     if (ydt != UMX_MX8 && ydt != UMX_MX4) { fprintf(stderr, "lp_gn_silu_apply_mx: output dtype %d is not MX\n", ydt); abort(); }
-    if (umx_gn_silu_apply(x, xdt, s.n, s.c, (size_t)s.d * s.h * s.w, G, gamma, beta, mean, rstd, y, ydt == UMX_MX8 ? 8 : 4, UMX_LAYOUT_REF, 0) != 0) {
+    const size_t S = (size_t)s.d * s.h * s.w;
+    const int ybits = ydt == UMX_MX8 ? 8 : 4;
+    if (s.c <= 16 && s.c >= 1) {
+        /* MX tensors of 16 channels or fewer are stored in rows of 8 / 16 (src/lp_common.cuh:132): widened into scratch, transformed there, narrowed */
+        const void *xin = x;
+        if (xdt == UMX_MX8 || xdt == UMX_MX4) {
+            const int xb = xdt == UMX_MX8 ? 8 : 4;
+            void *a = umx_ws(3, umx_mx_bytes32(xb, s.n, s.c, S));
+            if (!a) return;
+            umx_mx_rewidth(x, xb, s.n, s.c, S, a, 1);
+            xin = a;
+        }
+        void *b = umx_ws(4, umx_mx_bytes32(ybits, s.n, s.c, S));
+        if (!b) return;
+        if (umx_gn_silu_apply(xin, xdt, s.n, s.c, S, G, gamma, beta, mean, rstd, b, ybits, UMX_LAYOUT_REF, 0) != 0) {
+            fprintf(stderr, "lp_gn_silu_apply_mx: input dtype %d, %d channels in %d groups is not built in this library\n", xdt, s.c, G); abort();
+        }
+        umx_mx_rewidth(b, ybits, s.n, s.c, S, y, 0);
+        UMX_CK("lp_gn_silu_apply_mx");
+        return;
+    }
+    if (umx_gn_silu_apply(x, xdt, s.n, s.c, S, G, gamma, beta, mean, rstd, y, ybits, UMX_LAYOUT_REF, 0) != 0) {
         fprintf(stderr, "lp_gn_silu_apply_mx: input dtype %d, %d channels in %d groups is not built in this library\n", xdt, s.c, G); abort();
     }
     UMX_CK("lp_gn_silu_apply_mx");

@@ -185,7 +185,6 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     const int Ci = xs.c, Cx = sp.x2 ? sp.c_split : Ci, C2 = Ci - Cx;
     if (sp.x2 && (Cx < 1 || C2 < 1)) { fprintf(stderr, "%s: c_split %d of %d input channels\n", fn, Cx, Ci); abort(); }
     if (sp.x2 && x_mx && (Cx <= 16 || C2 <= 16) && (any_gn_(gp, sp) || sp.up)) not_built(fn, "a transform of a concat input with a part of 16 channels or fewer (8 / 16-wide MX rows)");
-    if (Ci <= 16 && any_gn_(gp, sp)) not_built(fn, "a GroupNorm transform of an input of 16 channels or fewer");
     if (xbf != UMX_F16 && !x_mx) { fprintf(stderr, "%s: input storage %d (this entry takes fp16 plane-major or MX)\n", fn, xbf); abort(); }
     const bool any_gn = gp.G || sp.gp2.G;
     if (!any_gn && !sp.up && x_mx && xbf != mxin) { fprintf(stderr, "%s: an MX-fp%d input of an MX-fp%d conv needs a transform that requantises it\n", fn, xb_bits, bits); abort(); }
@@ -213,12 +212,14 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     const void *xq = x; int cin = Ci, xflags = 0;
     const bool s2g = sp.x2 && sp.gp2.G;                       /* a GroupNorm per segment; otherwise gp counts its groups over all Ci channels */
     if (!sp.x2) {
+        const void *xw = x;
         if (x_mx && Ci <= 16) {                                /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
-            void *ws = umx_ws(3, umx_mx_bytes32(bits, xs.n, Ci, S));
+            void *ws = umx_ws(3, umx_mx_bytes32(xb_bits, xs.n, Ci, S));
             if (!ws) return 0;
-            umx_mx_rewidth(x, bits, xs.n, Ci, S, ws, 1);
-            xq = ws;
-        } else if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, bits); if (!xq) return 0; xflags = UMX_X_SPLIT; }
+            umx_mx_rewidth(x, xb_bits, xs.n, Ci, S, ws, 1);
+            xw = xq = ws;
+        }
+        if (gp.G) { xq = gn_input(fn, xw, xbf, xs, gp, bits); if (!xq) return 0; xflags = UMX_X_SPLIT; }
         else if (xbf == UMX_F16) {
             void *ws = umx_ws(0, umx_mx_bytes32(bits, xs.n, Ci, S));
             if (!ws) return 0;
@@ -373,17 +374,19 @@ extern "C" int lp_conv_fwd_s2_f8(const void *x, int xbf, shape5 xs, const float 
        input is transformed and requantised to MX-fp8 first, as the reference's s2_prenorm_k path does (src/lp_s2.cu:733-744). */
     const int bits = (xbf == UMX_MX4 && !gp.G) ? 4 : 8;
     const void *xq = x; int xflags = 0;
-    if (gp.G) { xq = gn_input(fn, x, xbf, xs, gp, 8); if (!xq) return 0; xflags = UMX_X_SPLIT; }
+    if (x_mx && xs.c <= 16) {                                  /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
+        const int xb = xbf == UMX_MX8 ? 8 : 4;
+        void *ws = umx_ws(3, umx_mx_bytes32(xb, xs.n, xs.c, S));
+        if (!ws) return 0;
+        umx_mx_rewidth(x, xb, xs.n, xs.c, S, ws, 1);
+        xq = ws;
+    }
+    if (gp.G) { xq = gn_input(fn, xq, xbf, xs, gp, 8); if (!xq) return 0; xflags = UMX_X_SPLIT; }
     else if (xbf == UMX_F16) {
         void *ws = umx_ws(0, umx_mx_bytes32(8, xs.n, xs.c, S));
         if (!ws) return 0;
         umx_pm_to_mx32(x, UMX_F16, xs.n, xs.c, S, ws, 8, UMX_LAYOUT_SPLIT);
         xq = ws; xflags = UMX_X_SPLIT;
-    } else if (xs.c <= 16) {                                   /* rows of 8 / 16 channels: the same codes and scale in a 32-wide row */
-        void *ws = umx_ws(3, umx_mx_bytes32(bits, xs.n, xs.c, S));
-        if (!ws) return 0;
-        umx_mx_rewidth(x, bits, xs.n, xs.c, S, ws, 1);
-        xq = ws;
     }
     /* an MX output of 16 channels or fewer is stored in rows of 8 / 16: the conv writes 32-wide rows into scratch, which are narrowed */
     const bool narrow = out_mode == UMX_OUT_MXRAW && cout <= 16;
