@@ -191,8 +191,9 @@ void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, 
    fraction in 2^-64, signed integer part, count of non-finite terms), zeroed by the caller; slot 2 (n G + g) takes the sum and the next one
    the sum of squares of group g of sample n over the voxels [v0, v1).  Returns 0, -1 when the combination is not covered (16 channels or
    fewer; G > 64 or C % G != 0 as in the reference).  umx_gn_finalize: mean and 1 / sqrt(max(var, 0) + eps) of NG groups of len elements. ---- */
-/* y = MX(silu(groupnorm(x))) (src/nn_lp.h:134, src/lp_mx_gn.cu:4-31): x xdt 0 / 2 (fp32 / fp16 plane-major) or 3 / 4 (MX); y ydt 3 / 4; more than 16
-   channels; mean, rstd per (sample, group).  SiLU is evaluated with the accurate expf and an IEEE division (the reference: __expf). */
+/* y = MX(silu(groupnorm(x))) (src/nn_lp.h:134, src/lp_mx_gn.cu:4-31): x xdt 0 / 2 (fp32 / fp16 plane-major) or 3 / 4 (MX); y ydt 3 / 4; MX tensors of
+   16 channels or fewer in rows of 8 / 16 (through a widened copy in scratch); mean, rstd per (sample, group).  SiLU is u * rcp(1 + ex2(-u log2 e))
+   with the hardware approximations (about 1e-6 relative; the reference: __expf). */
 void lp_gn_silu_apply_mx(const void *x, int xdt, shape5 s, int G, const float *gamma, const float *beta, const float *mean, const float *rstd, void *y, int ydt);
 /* exact-2x trilinear upsample of an MX tensor (align_corners = false, edge clamp: 3/4 of the coarse voxel under the fine one, 1/4 of its neighbour
    on the fine voxel's side, per axis), the eight terms added with fma in (z, y, x) order; gp.G != 0: silu(gn(x)) is upsampled
