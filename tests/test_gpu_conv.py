@@ -460,3 +460,43 @@ def test_conv_entry_with_gn_silu_input_transform(dev, s2, Ci, Gn):
     assert rc == 0
     e = orc.rel_l2(yd.download(np.float16).astype(np.float32), want)
     assert e < TOL, "relative L2 %.3g" % e
+
+
+@pytest.mark.parametrize("xbf", [3, 2])
+def test_conv_entry_with_slab_local_groupnorm(dev, xbf):
+    """gnp_t.ns != 0 (src/nn_lp.h:15-18, src/lp_slab.cuh:7-12): mean and rstd per (sample, z slab), plane z in slab (z + zo) / zs clamped to
+    [0, ns).  The expected tensor applies the oracle's transform slab by slab."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    N, Ci, Co, Gn, D, H, W = 2, 64, 32, 8, 7, 8, 16
+    ns, zs, zo = 3, 3, 1                          # planes 0-1, 2-4, 5-6
+    S, hw = D * H * W, H * W
+    x = (synth.rng(91).standard_normal(N * Ci * S) * 2).astype(np.float32)
+    w, b = synth.kaiming(92, Co, Ci, 27), synth.bias(93, Co, 0.1)
+    gamma, beta, mean, rstd = _gn_params(94, N * ns, Ci, Gn)
+    if xbf == 3:
+        src = orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
+        dq = orc.mx_to_pm(src, 8, N, Ci, S, 32)
+    else:
+        src = x.astype(np.float16)
+        dq = src.astype(np.float32)
+    dq = dq.reshape(N, Ci, D, hw)
+    act = np.zeros_like(dq)
+    for sl in range(ns):
+        zz = [z for z in range(D) if min(max((z + zo) // zs, 0), ns - 1) == sl]
+        sub = np.ascontiguousarray(dq[:, :, zz[0]:zz[-1] + 1]).reshape(-1)
+        m, r = mean.reshape(N, ns, Gn)[:, sl].reshape(-1), rstd.reshape(N, ns, Gn)[:, sl].reshape(-1)
+        act[:, :, zz[0]:zz[-1] + 1] = _gn_silu_oracle(sub, N, Ci, len(zz) * hw, Gn, gamma, beta, np.ascontiguousarray(m), np.ascontiguousarray(r), 1).reshape(N, Ci, len(zz), hw)
+    amx = orc.pm_to_mx(act.reshape(-1), 0, N, Ci, S, 8, 32)
+    acc = orc.conv_blocked(orc.mx_to_blocked(amx, 8, N, Ci, S), N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, 8), b, Co, 3, 1, 1)
+    want = orc.blocked_to_pm(orc.round_h16(acc), N, Co, S)
+    xd, wd, bd = DevBuf(data=src), DevBuf(data=w), DevBuf(data=b)
+    bufs = [DevBuf(data=a) for a in (gamma, beta, mean, rstd)]
+    gp = Gnp(); gp.gamma, gp.beta, gp.mean, gp.rstd, gp.G = bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bufs[3].ptr, Gn
+    gp.ns, gp.zs, gp.zo, gp.zhw = ns, zs, zo, hw
+    yd = DevBuf(N * Co * S * 2).fill(0xEE)
+    assert L.lp_conv_fwd_f8(xd.ptr, xbf, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, gp, None, 0, Split()) == 0
+    ufsm_b200.check()
+    e = orc.rel_l2(yd.download(np.float16).astype(np.float32), want)
+    assert e < TOL, "relative L2 %.3g" % e

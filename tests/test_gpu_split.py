@@ -251,7 +251,7 @@ def _full_conv(L, xbf, x_store, N, Ci, D, H, W, w, b, Co, ybf, gp=None):
     return yd.download()
 
 
-@pytest.mark.parametrize("xbf,ybf,gn", [(3, 2, False), (2, 2, False), (3, 3, False), (3, 2, True)])
+@pytest.mark.parametrize("xbf,ybf,gn", [(3, 2, False), (2, 2, False), (3, 3, False), (3, 2, True), (3, 2, "slabs")])
 def test_z_range_window_and_slab_output(dev, xbf, ybf, gn):
     """split_t.zi0 / Di (a conv over planes of a deeper input), zw0 / zw1 (a window of output planes), yD / yzo (the output placed in a deeper
     tensor): each run must give the planes of the whole-tensor conv, with zero padding only at the tensor's own ends."""
@@ -264,7 +264,12 @@ def test_z_range_window_and_slab_output(dev, xbf, ybf, gn):
     w, b = synth.kaiming(232, Co, Ci, 27), synth.bias(233, Co, 0.1)
     xs = x.astype(np.float16) if xbf == 2 else orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
     keep = []
-    gp = make_gp(8, gn_params(234, N, Ci, 8), keep) if gn else Gnp()
+    gp = Gnp()
+    if gn == "slabs":                        # statistics per (sample, z slab): planes 0-2, 3-7, 8-11 (gnp_t.ns / zs / zo / zhw, src/nn_lp.h:15-18)
+        gp = make_gp(8, gn_params(234, N * 3, Ci, 8), keep)
+        gp.ns, gp.zs, gp.zo, gp.zhw = 3, 5, 2, hw
+    elif gn:
+        gp = make_gp(8, gn_params(234, N, Ci, 8), keep)
     full = _full_conv(L, xbf, xs, N, Ci, D, H, W, w, b, Co, ybf, gp)
     xd, wd, bd = DevBuf(data=xs), DevBuf(data=w), DevBuf(data=b)
 

@@ -16,33 +16,46 @@ namespace {
 
 /* XK: 8 / 4 MX input of that many bits, 0 fp32 plane-major, 2 fp16 plane-major.  FORM 0: ((x - mean) rstd) gamma + beta; 1: fma(x, a, b).
    grid (runs of voxels, 32-channel blocks, samples) */
-template <int XK, int BY, int FORM>
+struct GnSlabs { int ns, zs, zo; size_t zhw; };             /* slab-local statistics (gnp_t.ns / zs / zo / zhw, src/nn_lp.h:15-18); ns 0: per sample */
+template <int XK, int BY, int FORM, bool SL>
 __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ xv, uint8_t *__restrict__ y, int C, int G, size_t S,
                                                       const float *__restrict__ gamma, const float *__restrict__ beta, const float *__restrict__ mean, const float *__restrict__ rstd, int y_split,
-                                                      int c_off, int cpg) {
+                                                      int c_off, int cpg, const GnSlabs sl) {
     const int N = gridDim.z, nb = gridDim.y, blk = blockIdx.y, n = blockIdx.z, T = gridDim.x;
     const int q = threadIdx.x & 3, ph = threadIdx.x >> 2;
     constexpr int RBY = BY == 8 ? 32 : 16;
+    const size_t nbk = (size_t)n * nb + blk, v0 = S * blockIdx.x / T, vend = S * (blockIdx.x + 1) / T;
+    const uint8_t *xq = (const uint8_t *)xv;
+    const uint8_t *xs = XK == 8 ? xq + (size_t)N * nb * S * 32 : xq + (size_t)N * nb * S * 16;
+    uint8_t *ys = y + (size_t)N * nb * S * RBY;
+    bool live[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) live[k] = blk * 32 + q * 8 + k < C;
+    /* the block's run of voxels in pieces that lie in one statistics slab each (one piece when the statistics are per sample): plane z belongs
+       to slab (z + zo) / zs clamped to [0, ns), whose statistics are row n ns + slab (gn_row, src/lp_slab.cuh:7-12) */
+    for (size_t va = v0; va < vend;) {                       /* SL false: one trip, the loop folds away */
+    int nr = n; size_t v1 = vend;
+    if (SL) {
+        int sb_ = ((int)(va / sl.zhw) + sl.zo) / sl.zs;
+        sb_ = sb_ < 0 ? 0 : sb_ >= sl.ns ? sl.ns - 1 : sb_;
+        nr = n * sl.ns + sb_;
+        if (sb_ < sl.ns - 1) { const long long zb = (long long)(sb_ + 1) * sl.zs - sl.zo; if (zb > 0) v1 = min(vend, max(va + 1, (size_t)zb * sl.zhw)); }
+    }
     /* per channel: FORM 0 (mean, rstd, gamma, beta) in (k0, k1, k2, k3); FORM 1 (a, b) in (k0, k1) */
-    float2 k0[4], k1[4], k2[4], k3[4]; bool live[8];         /* FORM 0: k0 holds -mean */
+    float2 k0[4], k1[4], k2[4], k3[4];                       /* FORM 0: k0 holds -mean */
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int c = blk * 32 + q * 8 + k;
         float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
-        live[k] = c < C;
         if (live[k]) {
-            const int cl = c_off + c, ng = n * G + cl / cpg;       /* cl: the channel's index in the tensor the groups are counted over */
+            const int cl = c_off + c, ng = nr * G + cl / cpg;      /* cl: the channel's index in the tensor the groups are counted over */
             if (FORM == 0) { t0 = -mean[ng]; t1 = rstd[ng]; t2 = gamma[cl]; t3 = beta[cl]; }
             else { t0 = __fmul_rn(rstd[ng], gamma[cl]); t1 = __fmaf_rn(-mean[ng], t0, beta[cl]); }
         }
         if (k & 1) { k0[k >> 1].y = t0; k1[k >> 1].y = t1; k2[k >> 1].y = t2; k3[k >> 1].y = t3; }
         else { k0[k >> 1].x = t0; k1[k >> 1].x = t1; k2[k >> 1].x = t2; k3[k >> 1].x = t3; }
     }
-    const size_t nbk = (size_t)n * nb + blk, v0 = S * blockIdx.x / T, v1 = S * (blockIdx.x + 1) / T;
-    const uint8_t *xq = (const uint8_t *)xv;
-    const uint8_t *xs = XK == 8 ? xq + (size_t)N * nb * S * 32 : xq + (size_t)N * nb * S * 16;
-    uint8_t *ys = y + (size_t)N * nb * S * RBY;
-    for (size_t vb = v0; vb < v1; vb += 256) {
+    for (size_t vb = va; vb < v1; vb += 256) {
         float2 r[4][4];
         if (XK == 8 || XK == 4) {
             uint2 raw[4]; unsigned sb[4];
@@ -86,12 +99,18 @@ __global__ void __launch_bounds__(256) gn_silu_rows_k(const void *__restrict__ x
             }
         }
     }
+    if (!SL) break;
+    va = v1;
+    }
 }
 
 template <int XK, int BY>
-void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, size_t S, const float *gamma, const float *beta, const float *mean, const float *rstd, int y_split, int c_off, int cpg) {
-    if (form == 0) gn_silu_rows_k<XK, BY, 0><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg);
-    else gn_silu_rows_k<XK, BY, 1><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg);
+void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, size_t S, const float *gamma, const float *beta, const float *mean, const float *rstd, int y_split, int c_off, int cpg, GnSlabs sl) {
+    if (sl.ns) {
+        if (form == 0) gn_silu_rows_k<XK, BY, 0, true><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg, sl);
+        else gn_silu_rows_k<XK, BY, 1, true><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg, sl);
+    } else if (form == 0) gn_silu_rows_k<XK, BY, 0, false><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg, sl);
+    else gn_silu_rows_k<XK, BY, 1, false><<<grid, 256>>>(x, y, C, G, S, gamma, beta, mean, rstd, y_split, c_off, cpg, sl);
 }
 
 }   // namespace
@@ -99,9 +118,13 @@ void launch_form(int form, dim3 grid, const void *x, uint8_t *y, int C, int G, s
 /* x: xdt 0 (fp32 plane-major), 2 (fp16 plane-major), 3 / 4 (MX, reference layout, 32-wide rows); y: MX of `bits` bits, `layout` as in
    umx_pm_to_mx32; form 0 / 1 as above.  The tensor may be a channel segment of a larger one the G groups are counted over (a conv's
    concat input with one GroupNorm over both parts): its channel 0 is channel c_off of C_all (0, C for a whole tensor); gamma, beta,
-   mean, rstd are the larger tensor's.  Returns 0, -1 on an unsupported combination (the caller reports it). */
-int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
-                          void *y, int bits, int layout, int form, int c_off, int C_all) {
+   mean, rstd are the larger tensor's.  ns != 0: slab-local statistics, mean and rstd [N][ns][G], plane z = voxel / zhw of the tensor in slab
+   (z + zo) / zs clamped to [0, ns) (gnp_t, src/nn_lp.h:15-18; zo may be negative here: a tensor that is a z range of the one the slabs are
+   counted in).  Returns 0, -1 on an unsupported combination (the caller reports it). */
+int umx_gn_silu_apply_seg_slabs(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                                void *y, int bits, int layout, int form, int c_off, int C_all, int ns, int zs, int zo, size_t zhw) {
+    if (ns < 0 || (ns && (zs < 1 || !zhw || S % zhw))) return -1;
+    const GnSlabs sl = {ns, zs, zo, zhw};
     if (C < 1 || G < 1 || C_all % G || c_off < 0 || c_off + C > C_all || (bits != 8 && bits != 4) || (xdt != UMX_F32 && xdt != UMX_F16 && xdt != UMX_MX8 && xdt != UMX_MX4)) return -1;
     const int cpg = C_all / G;
     const int nb = (C + 31) / 32;
@@ -112,11 +135,16 @@ int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G,
     const dim3 blocks((unsigned)T, (unsigned)nb, (unsigned)N);
     const int ys = bits == 8 && layout == UMX_LAYOUT_SPLIT;
     uint8_t *yb = (uint8_t *)y;
-#define UMX_GSA(XK) do { if (bits == 8) launch_form<XK, 8>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg); else launch_form<XK, 4>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg); } while (0)
+#define UMX_GSA(XK) do { if (bits == 8) launch_form<XK, 8>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg, sl); else launch_form<XK, 4>(form, blocks, x, yb, C, G, S, gamma, beta, mean, rstd, ys, c_off, cpg, sl); } while (0)
     if (xdt == UMX_MX8) UMX_GSA(8); else if (xdt == UMX_MX4) UMX_GSA(4); else if (xdt == UMX_F16) UMX_GSA(2); else UMX_GSA(0);
 #undef UMX_GSA
     g_umx_launches++;
     return 0;
+}
+/* statistics per sample */
+int umx_gn_silu_apply_seg(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                          void *y, int bits, int layout, int form, int c_off, int C_all) {
+    return umx_gn_silu_apply_seg_slabs(x, xdt, N, C, S, G, gamma, beta, mean, rstd, y, bits, layout, form, c_off, C_all, 0, 0, 0, 0);
 }
 int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
                       void *y, int bits, int layout, int form) {

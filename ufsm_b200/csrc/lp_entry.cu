@@ -21,12 +21,21 @@ int umx_gn_silu_apply(const void *x, int xdt, int N, int C, size_t S, int G, con
                       void *y, int bits, int layout, int form);
 /* the GroupNorm + SiLU input transform of a conv (gnp_t.G != 0): silu(fma(x, a, b)) quantised to the conv's MX format, into scratch, ahead
    of the conv (the reference applies it while staging the operand and quantises the staged rows the same way) */
+int umx_gn_silu_apply_seg_slabs(const void *x, int xdt, int N, int C, size_t S, int G, const float *gamma, const float *beta, const float *mean, const float *rstd,
+                                void *y, int bits, int layout, int form, int c_off, int C_all, int ns, int zs, int zo, size_t zhw);
+/* slab-local statistics (gnp_t.ns != 0, src/nn_lp.h:15-18): the geometry must be that of the tensor */
+static void slab_check(const char *fn, const gnp_t &gp, shape5 xs) {
+    if (!gp.ns) return;
+    if (gp.ns < 0 || gp.zs < 1 || gp.zo < 0 || gp.zo >= gp.zs || gp.zhw != xs.h * xs.w) {
+        fprintf(stderr, "%s: slab-local GroupNorm with ns %d, zs %d, zo %d, zhw %d on planes of %d voxels\n", fn, gp.ns, gp.zs, gp.zo, gp.zhw, xs.h * xs.w); abort();
+    }
+}
 static const void *gn_input(const char *fn, const void *x, int xbf, shape5 xs, gnp_t gp, int bits) {
-    if (gp.ns > 1 || gp.zs || gp.zo || gp.zhw) { fprintf(stderr, "%s: slab-local GroupNorm (gnp_t.ns / zs / zo / zhw) is not built in this library\n", fn); abort(); }
+    slab_check(fn, gp, xs);
     const size_t S = (size_t)xs.d * xs.h * xs.w;
     void *ws = umx_ws(2, umx_mx_bytes32(bits, xs.n, xs.c, S));
     if (!ws) return nullptr;
-    if (umx_gn_silu_apply(x, xbf, xs.n, xs.c, S, gp.G, gp.gamma, gp.beta, gp.mean, gp.rstd, ws, bits, UMX_LAYOUT_SPLIT, 1) != 0) {
+    if (umx_gn_silu_apply_seg_slabs(x, xbf, xs.n, xs.c, S, gp.G, gp.gamma, gp.beta, gp.mean, gp.rstd, ws, bits, UMX_LAYOUT_SPLIT, 1, 0, xs.c, gp.ns, gp.zs, gp.zo, (size_t)gp.zhw) != 0) {
         fprintf(stderr, "%s: the GroupNorm + SiLU input transform of a storage-%d tensor of %d channels in %d groups is not built in this library\n", fn, xbf, xs.c, gp.G); abort();
     }
     return ws;
@@ -155,7 +164,9 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
             const tdesc tm = tensor_desc(mxf, xs.n, xs.c, hw);
             uint8_t *g = (uint8_t *)umx_ws(9, tensor_bytes(tm, nz + 2, hw));
             if (!g) return 0;
-            if (umx_gn_silu_apply_seg(xa, xbf, xs.n, xs.c, (size_t)(nz + 2) * hw, gp.G, gp.gamma, gp.beta, gp.mean, gp.rstd, g, bits, UMX_LAYOUT_REF, 1, 0, xs.c) != 0) not_built(fn, "this GroupNorm transform");
+            slab_check(fn, gp, xs);                            /* local plane zl of the copy is plane zl + first of the tensor the slabs are counted in */
+            if (umx_gn_silu_apply_seg_slabs(xa, xbf, xs.n, xs.c, (size_t)(nz + 2) * hw, gp.G, gp.gamma, gp.beta, gp.mean, gp.rstd, g, bits, UMX_LAYOUT_REF, 1, 0, xs.c,
+                                            gp.ns, gp.zs, gp.zo + first, hw) != 0) not_built(fn, "this GroupNorm transform");
             const int lo = first < 0 ? -first : 0, hi = first + nz + 2 > Din ? first + nz + 2 - Din : 0;      /* planes before / after the tensor */
             for (int side = 0; side < 2; side++) {
                 const int np = side ? hi : lo, p0 = side ? nz + 2 - hi : 0;
@@ -175,8 +186,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         UMX_CK(fn);
         return 0;
     }
-    if (gp.G && (gp.ns > 1 || gp.zs || gp.zo || gp.zhw)) not_built(fn, "slab-local GroupNorm (gnp_t.ns / zs / zo / zhw)");
-    if (sp.gp2.G && (sp.gp2.ns > 1 || sp.gp2.zs || sp.gp2.zo || sp.gp2.zhw)) not_built(fn, "slab-local GroupNorm (split_t.gp2)");
+    if (gp.G && gp.ns && sp.up) not_built(fn, "slab-local GroupNorm (gnp_t.ns) of a part stored at half resolution (split_t.up)");
     if (sp.up && !sp.x2) { fprintf(stderr, "%s: split_t.up without x2\n", fn); abort(); }
     if (sp.gp2.G && !sp.x2) { fprintf(stderr, "%s: split_t.gp2 without x2\n", fn); abort(); }
     const int mxin = bits == 8 ? UMX_MX8 : UMX_MX4;
@@ -256,7 +266,8 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
             } else if (q.G) {
                 uint8_t *t = (uint8_t *)umx_ws(3 + seg, umx_mx_bytes32(bits, xs.n, C, S));
                 if (!t) return 0;
-                if (umx_gn_silu_apply_seg(src, xbf, xs.n, C, S, q.G, q.gamma, q.beta, q.mean, q.rstd, t, bits, UMX_LAYOUT_REF, 1, c_off, C_all) != 0) {
+                slab_check(fn, q, xs);
+                if (umx_gn_silu_apply_seg_slabs(src, xbf, xs.n, C, S, q.G, q.gamma, q.beta, q.mean, q.rstd, t, bits, UMX_LAYOUT_REF, 1, c_off, C_all, q.ns, q.zs, q.zo, (size_t)q.zhw) != 0) {
                     fprintf(stderr, "%s: the GroupNorm + SiLU input transform of a storage-%d segment of %d channels (%d groups over %d) is not built in this library\n", fn, xbf, C, q.G, C_all); abort();
                 }
                 blocks = t;
