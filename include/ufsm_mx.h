@@ -113,7 +113,7 @@ void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);          
    split output when its first part ends on a 32-channel block), zi0 / Di, zw0 / zw1, yD / yzo (z range, z window, output into a deeper
    tensor), wkey (prepared-weight memo).  What is not built prints "... is not built in this library" and aborts: stochastic rounding
    (sr / osr), slab-local GroupNorm (gnp_t.ns != 0) of a part stored at half resolution, osum of unrounded accumulators (stored_stats 0) or of a non-MX output, the z fields
-   together with up, a split output or osum, a transform of concat parts of 16 channels or fewer.  Returns 0. ---- */
+   together with up, a transform of concat parts of 16 channels or fewer.  Returns 0. ---- */
 int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 void lp_wmemo_clear(void);               /* src/nn_lp.h:57: drop the prepared weights kept under split_t.wkey */

@@ -311,6 +311,45 @@ def test_z_range_window_and_slab_output(dev, xbf, ybf, gn):
         assert same(planes(yd2.download(), zi0, zi0 + nz), want), (zi0, nz)
 
 
+def test_z_window_with_split_output_and_statistics(dev):
+    """A z window and a z range together with a split MX output and the GroupNorm sums of the stored output: the two output tensors hold the
+    window's planes of the whole-tensor conv's, and the sums are those of exactly these planes (less zlo / zhi of them)."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    L = ufsm_b200.lib()
+    N, Ci, Ox, O2, D, H, W, Go = 2, 32, 32, 32, 10, 8, 16, 8
+    Co, S, hw = Ox + O2, D * H * W, H * W
+    x = (synth.rng(251).standard_normal(N * Ci * S) * 2).astype(f32)
+    w, b = synth.kaiming(252, Co, Ci, 27), synth.bias(253, Co, 0.1)
+    xs = orc.pm_to_mx(x, 0, N, Ci, S, 8, 32)
+    full = _full_conv(L, 3, xs, N, Ci, D, H, W, w, b, Co, 3)
+    stored = orc.mx_to_pm(full, 8, N, Co, S, 32).reshape(N, Co, D, hw)
+    xd, wd, bd = DevBuf(data=xs), DevBuf(data=w), DevBuf(data=b)
+
+    def check(sp, shape_d, z0, z1, zlo, zhi, deep):
+        nz = z1 - z0
+        Dy = D if deep else nz
+        yd, y2d = DevBuf(orc.mx_bytes(8, N, Ox, Dy * hw, 32)).fill(0xEE), DevBuf(orc.mx_bytes(8, N, O2, Dy * hw, 32)).fill(0xEE)
+        sums = DevBuf(N * Go * 2 * 24).fill(0)
+        sp.y2, sp.o_split, sp.stored_stats, sp.zlo, sp.zhi = y2d.ptr, Ox, 1, zlo, zhi
+        assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, shape_d, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 3, Gnp(), sums.ptr, Go, sp) == 0
+        ufsm_b200.check()
+        for buf, c0, c in ((yd, 0, Ox), (y2d, Ox, O2)):
+            got = orc.mx_to_pm(buf.download(), 8, N, c, Dy * hw, 32).reshape(N, c, Dy, hw)
+            got = got[:, :, z0:z1] if deep else got
+            assert np.array_equal(got, stored[:, c0:c0 + c, z0:z1]), (z0, z1, c0)
+        ws = sums.download().view(np.uint64).reshape(-1, 3)
+        got = ws[:, 1].astype(np.int64).astype(np.float64) + ws[:, 0].astype(np.float64) * 2.0 ** -64
+        part = stored[:, :, z0 + zlo:z1 - zhi].astype(np.float64).reshape(N, Go, Co // Go, -1)
+        exp = np.stack([part.sum((2, 3)), (part * part).sum((2, 3))], 2).reshape(-1)
+        assert (ws[:, 2] == 0).all() and np.allclose(got, exp, rtol=1e-13, atol=1e-9)
+
+    sp = Split(); sp.zw0, sp.zw1 = 3, 8                     # a window of the output planes, written into the whole-depth tensors
+    check(sp, D, 3, 8, 1, 0, True)
+    sp = Split(); sp.zi0, sp.Di = 4, D                      # a z range of the deeper input, outputs of the range's own depth
+    check(sp, 5, 4, 9, 0, 2, False)
+
+
 def test_accumulate(dev):
     """split_t.accum: y += conv (fp16 plane-major), also on a window of planes"""
     import ufsm_b200

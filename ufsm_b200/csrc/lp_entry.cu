@@ -141,7 +141,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         return 0;
     }
     if (sp.zi0 || sp.Di || sp.zw0 || sp.zw1 || sp.yD || sp.yzo) {
-        if (sp.up || sp.y2 || osum || Go) not_built(fn, "a z range / z window / slab output together with split_t.up, a split output or output statistics");
+        if (sp.up) not_built(fn, "a z range / z window / slab output together with split_t.up");
         if ((sp.Di || sp.zi0) && sp.zw1) not_built(fn, "a z range and a z window in one call");
         if (ybf == UMX_H16B) not_built(fn, "a z range / z window with a blocked fp16 output");
         const size_t hw = (size_t)xs.h * xs.w;
@@ -178,11 +178,18 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         }
         if (sp.x2) { s2.x2 = slab_of(9, sp.x2, xbf, xs.n, xs.c - Cx, Din, hw, z0 + sp.zi0 - 1, nz + 2); if (!s2.x2) return 0; }
         shape5 s5 = xs; s5.d = nz + 2;
-        const tdesc ty = tensor_desc(ybf, xs.n, cout, hw);
-        void *t = umx_ws(10, tensor_bytes(ty, nz + 2, hw));
+        /* a split output: both parts through scratch tensors of nz + 2 planes; output statistics: the first and the last plane of the run are
+           not output planes, so they join the planes the sums skip */
+        const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
+        if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
+        const tdesc ty = tensor_desc(ybf, xs.n, Ox, hw), ty2 = tensor_desc(ybf, xs.n, sp.y2 ? O2 : 1, hw);
+        void *t = umx_ws(10, tensor_bytes(ty, nz + 2, hw)), *t2 = nullptr;
         if (!t) return 0;
-        conv_fwd(fn, bits, xa, xbf, s5, w, b, cout, t, ybf, gp, nullptr, 0, s2);
+        if (sp.y2) { t2 = umx_ws(11, tensor_bytes(ty2, nz + 2, hw)); if (!t2) return 0; s2.y2 = t2; }
+        if (osum) { s2.zlo = sp.zlo + 1; s2.zhi = sp.zhi + 1; }
+        conv_fwd(fn, bits, xa, xbf, s5, w, b, cout, t, ybf, gp, osum, Go, s2);
         planes_copy(y, Dy, yz, t, nz + 2, 1, nz, ty, hw);
+        if (sp.y2) planes_copy(sp.y2, Dy, yz, t2, nz + 2, 1, nz, ty2, hw);
         UMX_CK(fn);
         return 0;
     }
