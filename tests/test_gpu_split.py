@@ -171,6 +171,18 @@ def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
     got = ws[:, 1].astype(np.int64).astype(np.float64) + ws[:, 0].astype(np.float64) * 2.0 ** -64
     exp = np.stack([stored.sum((2, 3, 4)), (stored * stored).sum((2, 3, 4))], 2).reshape(-1)
     assert (ws[:, 2] == 0).all() and np.allclose(got, exp, rtol=1e-13, atol=1e-9)
+    # stored_stats 0: the sums of acc + bias before the rounding to MX; the output tensor is the same
+    yraw, sraw = DevBuf(orc.mx_bytes(ob, N, Co, S, 32)).fill(0xEE), DevBuf(N * Go * 2 * 24).fill(0)
+    sp0 = Split()
+    sp0.zlo, sp0.zhi = zlo, zhi
+    assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yraw.ptr, ybf, Gnp(), sraw.ptr, Go, sp0) == 0
+    ufsm_b200.check()
+    assert np.array_equal(yraw.download(), yall.download())
+    unr = want.astype(np.float64).reshape(N, Go, Co // Go, D, H * W)[:, :, :, zlo:D - zhi]
+    wr = sraw.download().view(np.uint64).reshape(-1, 3)
+    gotr = wr[:, 1].astype(np.int64).astype(np.float64) + wr[:, 0].astype(np.float64) * 2.0 ** -64
+    expr = np.stack([unr.sum((2, 3, 4)), (unr * unr).sum((2, 3, 4))], 2).reshape(-1)
+    assert (wr[:, 2] == 0).all() and np.allclose(gotr, expr, rtol=2e-5, atol=1e-3)          # the oracle's accumulators, another summation order
     if Ox % 32 or O2 <= 16:
         return
     # and of a split output whose first part ends on a block: the same sums, the same bytes in the two tensors

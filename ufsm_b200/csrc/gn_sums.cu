@@ -103,6 +103,26 @@ __global__ void __launch_bounds__(256) gn_sums_rows_k(const uint8_t *__restrict_
     }
 }
 
+/* the same sums of a plane-major fp32 tensor [N][C][S] (a conv's unrounded accumulators): block = (run of voxels, channel, sample); fp64 sums
+   (a square of an fp32 value is exact in fp64), a fixed-order reduction in the block, one slot addition per sum */
+__global__ void __launch_bounds__(256) gn_sums_pm32_k(const float *__restrict__ x, int C, int G, size_t S, double *sums, size_t v0, size_t v1) {
+    const int c = blockIdx.y, n = blockIdx.z;
+    size_t q0 = S * blockIdx.x / gridDim.x, q1 = S * (blockIdx.x + 1) / gridDim.x;
+    if (q0 < v0) q0 = v0;
+    if (q1 > v1) q1 = v1;
+    const float *p = x + ((size_t)n * C + c) * S;
+    double a = 0.0, b = 0.0;
+    for (size_t v = q0 + threadIdx.x; v < q1; v += 256) { const double t = (double)__ldg(p + v); a += t; b = fma(t, t, b); }
+    __shared__ double sa[256], sb[256];
+    sa[threadIdx.x] = a; sb[threadIdx.x] = b;
+    __syncthreads();
+    for (int h = 128; h > 0; h >>= 1) {
+        if ((int)threadIdx.x < h) { sa[threadIdx.x] += sa[threadIdx.x + h]; sb[threadIdx.x] += sb[threadIdx.x + h]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && q1 > q0) { const size_t o = 2 * ((size_t)n * G + c / (C / G)); slot_add(sums, o, sa[0]); slot_add(sums, o + 1, sb[0]); }
+}
+
 __global__ void gn_finalize_k(const double *sums, int NG, size_t len, float eps, float *mean, float *rstd) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= NG) return;
@@ -135,6 +155,17 @@ extern "C" int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size
     else { if (one) gn_sums_rows_k<4, true><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); else gn_sums_rows_k<4, false><<<grid, 256>>>(xq, N, C, G, S, sums, v0, v1, n0); }
     g_umx_launches++;
     UMX_CK("lp_gn_sums_mx");
+    return 0;
+}
+/* the same for a plane-major fp32 tensor (the unrounded output of a conv: split_t.stored_stats == 0, src/nn_lp.h:37) */
+int umx_gn_sums_pm32(const float *x, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1) {
+    if (!umx_ready("umx_gn_sums_pm32")) return -1;
+    if (G < 1 || G > 64 || C % G || C > 65535 || N > 65535) return -1;
+    if (N <= 0 || v1 <= v0 || !S) return 0;
+    size_t runs = (S + 8191) / 8192; if (runs > 4096) runs = 4096;
+    gn_sums_pm32_k<<<dim3((unsigned)runs, (unsigned)C, (unsigned)N), 256>>>(x, C, G, S, sums, v0, v1);
+    g_umx_launches++;
+    UMX_CK("umx_gn_sums_pm32");
     return 0;
 }
 extern "C" int lp_gn_sums_mx(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1) {

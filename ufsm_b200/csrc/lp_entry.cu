@@ -40,6 +40,10 @@ static const void *gn_input(const char *fn, const void *x, int xbf, shape5 xs, g
     }
     return ws;
 }
+int umx_gn_sums_pm32(const float *x, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1);
+__global__ void f32_to_h16_k(const float *__restrict__ x, __half *__restrict__ y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = __float2half_rn(x[i]);
+}
 static void not_built(const char *fn, const char *what) { fprintf(stderr, "%s: %s is not built in this library\n", fn, what); abort(); }
 
 /* ---- split_t: concat input, upsampled input segment, split output, output statistics ----
@@ -212,14 +216,16 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
     const bool narrow_out = out_mode == UMX_OUT_MXRAW && cout <= 16 && !sp.y2;      /* rows of 8 / 16 channels: written 32 wide into scratch, then narrowed */
-    if (narrow_out && osum) not_built(fn, "output statistics with 16 output channels or fewer");
+    if (narrow_out && osum && sp.stored_stats) not_built(fn, "statistics of a stored output of 16 channels or fewer");
     const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
     if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
     if (sp.y2 && out_mode == UMX_OUT_H16B) not_built(fn, "a split output in blocked fp16");
     if (osum || Go) {
         if (!osum || Go < 1) { fprintf(stderr, "%s: osum %p with %d groups\n", fn, (void *)osum, Go); abort(); }
-        if (out_mode != UMX_OUT_MXRAW || !sp.stored_stats) not_built(fn, "output statistics of the unrounded accumulators (osum needs an MX output and split_t.stored_stats)");
-        if (sp.y2 && ((Ox & 31) || O2 <= 16)) not_built(fn, "output statistics of a split output whose first part does not end on a 32-channel block");
+        if (sp.stored_stats) {
+            if (out_mode != UMX_OUT_MXRAW) not_built(fn, "statistics of a stored output that is not MX");
+            if (sp.y2 && ((Ox & 31) || O2 <= 16)) not_built(fn, "output statistics of a split output whose first part does not end on a 32-channel block");
+        } else if (sp.y2 || out_mode == UMX_OUT_H16B) not_built(fn, "statistics of the unrounded output (split_t.stored_stats 0) of a split or blocked fp16 output");
         if (Go > 64 || cout % Go) { fprintf(stderr, "%s: %d output channels in %d groups\n", fn, cout, Go); abort(); }
     }
     const size_t S = (size_t)xs.d * xs.h * xs.w;
@@ -320,7 +326,18 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         if (!c) return 0;
         if (sp.wkey && g_nmemo < 256) { memo_t m = {sp.wkey, w, b, cout_c, cin, bits, dev, c}; g_memo[g_nmemo++] = m; } else temp = true;
     }
-    if (narrow_out) {
+    if (osum && !sp.stored_stats) {
+        /* statistics of acc + bias before any rounding (the reference's epilogue sums its fp32 values, src/lp_common.cuh:1465-1598): the conv
+           into a plane-major fp32 scratch tensor, exact sums of that, and the output tensor made from it (MX(acc + bias), or its fp16 rounding) */
+        float *P = (float *)umx_ws(7, (size_t)xs.n * cout * S * 4);
+        if (!P) return 0;
+        umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, P, UMX_OUT_PM32, 0, 0, 0, nullptr, xflags);
+        const size_t hw = (size_t)xs.h * xs.w, v0 = (size_t)sp.zlo * hw, v1 = S - (size_t)sp.zhi * hw;
+        if (sp.zlo < 0 || sp.zhi < 0 || sp.zlo + sp.zhi > xs.d) { fprintf(stderr, "%s: zlo %d + zhi %d of %d planes\n", fn, sp.zlo, sp.zhi, xs.d); abort(); }
+        if (umx_gn_sums_pm32(P, xs.n, cout, Go, S, osum, v0, v1) != 0) { fprintf(stderr, "%s: output statistics of %d channels in %d groups\n", fn, cout, Go); abort(); }
+        if (out_mode == UMX_OUT_MXRAW) { if (out_bits == 8) lp_f32_to_mx8(P, xs.n, cout, S, y); else lp_f32_to_mx4(P, xs.n, cout, S, y); }
+        else { const size_t ny = (size_t)xs.n * cout * S; size_t g = (ny + 255) / 256; if (g > 148u * 16u) g = 148u * 16u; f32_to_h16_k<<<(unsigned)g, 256>>>(P, (__half *)y, ny); }
+    } else if (narrow_out) {
         void *t = umx_ws(4, umx_mx_bytes32(out_bits, xs.n, cout, S));
         if (!t) return 0;
         umx_conv_fwd(c, xq, xs.n, xs.d, xs.h, xs.w, t, out_mode, out_bits, 0, 0, nullptr, xflags);
@@ -355,7 +372,7 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
             if (lp_gn_sums_mx(t, ybf, xs.n, cout, Go, S, osum, v0, v1) != 0) { fprintf(stderr, "%s: output statistics of %d channels in %d groups\n", fn, cout, Go); abort(); }
         }
     }
-    if (osum && !sp.y2) {
+    if (osum && !sp.y2 && sp.stored_stats) {
         /* statistics of the stored values (split_t.stored_stats) over the planes [zlo, D - zhi): exact sums into the caller's slots */
         const size_t hw = (size_t)xs.h * xs.w, v0 = (size_t)sp.zlo * hw, v1 = S - (size_t)sp.zhi * hw;
         if (sp.zlo < 0 || sp.zhi < 0 || sp.zlo + sp.zhi > xs.d) { fprintf(stderr, "%s: zlo %d + zhi %d of %d planes\n", fn, sp.zlo, sp.zhi, xs.d); abort(); }
