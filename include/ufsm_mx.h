@@ -187,10 +187,10 @@ int umx_in_coef_static(const void *y, int N, int C, int D, int H, int W, const f
 void umx_in_apply(const void *x, const float *coef, int N, int C, int D, int H, int W, int act, void *q, int bits, int nb_dst, int b0, void *q_s2d, void *h, int layout);
 
 /* ---- GroupNorm statistics of an MX tensor (src/nn_lp.h:175-176, src/lp_mx_gnsums.cu:9-106; finalise: src/nn_elem.cu:5-11).  x: device, xdt 3 / 4,
-   reference layout, more than 16 channels.  sums: device, 2 N G slots of 24 bytes (the reference's exact fixed point, src/gnacc.cuh:9-27:
+   reference layout (16 channels or fewer in rows of 8 / 16).  sums: device, 2 N G slots of 24 bytes (the reference's exact fixed point, src/gnacc.cuh:9-27:
    fraction in 2^-64, signed integer part, count of non-finite terms), zeroed by the caller; slot 2 (n G + g) takes the sum and the next one
-   the sum of squares of group g of sample n over the voxels [v0, v1).  Returns 0, -1 when the combination is not covered (16 channels or
-   fewer; G > 64 or C % G != 0 as in the reference).  umx_gn_finalize: mean and 1 / sqrt(max(var, 0) + eps) of NG groups of len elements. ---- */
+   the sum of squares of group g of sample n over the voxels [v0, v1).  Returns 0, -1 when the combination is not covered (G > 64 or C % G != 0
+   as in the reference).  umx_gn_finalize: mean and 1 / sqrt(max(var, 0) + eps) of NG groups of len elements. ---- */
 /* y = MX(silu(groupnorm(x))) (src/nn_lp.h:134, src/lp_mx_gn.cu:4-31): x xdt 0 / 2 (fp32 / fp16 plane-major) or 3 / 4 (MX); y ydt 3 / 4; MX tensors of
    16 channels or fewer in rows of 8 / 16 (through a widened copy in scratch); mean, rstd per (sample, group).  SiLU is u * rcp(1 + ex2(-u log2 e))
    with the hardware approximations (about 1e-6 relative; the reference: __expf). */

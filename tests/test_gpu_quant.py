@@ -90,14 +90,14 @@ def _slots(raw):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
-@pytest.mark.parametrize("N,Cn,Gn,S", [(1, 32, 8, 5000), (2, 64, 8, 4097), (1, 40, 5, 777), (2, 96, 32, 1300), (1, 64, 64, 2000)])
+@pytest.mark.parametrize("N,Cn,Gn,S", [(1, 32, 8, 5000), (2, 64, 8, 4097), (1, 40, 5, 777), (2, 96, 32, 1300), (1, 64, 64, 2000), (2, 16, 4, 3000), (1, 8, 1, 1025)])      # the last two: rows of 16 / 8 channels
 def test_gn_sums_mx(dev, bits, N, Cn, Gn, S):
     import ufsm_b200
     from ufsm_b200 import DevBuf
     L = ufsm_b200.lib()
     x = (synth.rng(61).standard_normal(N * Cn * S) * 3 + 1.5).astype(np.float32)
-    mx = orc.pm_to_mx(x, 0, N, Cn, S, bits, 32)
-    dq = orc.mx_to_pm(mx, bits, N, Cn, S, 32).astype(np.float64).reshape(N, Gn, -1)
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, bits)
+    dq = orc.mx_to_pm(mx, bits, N, Cn, S).astype(np.float64).reshape(N, Gn, -1)
     want = np.stack([dq.sum(2), (dq * dq).sum(2)], 2).reshape(-1)
     xd, sd = DevBuf(data=mx), DevBuf(N * Gn * 2 * 24).fill(0)
     dt = 3 if bits == 8 else 4

@@ -133,13 +133,20 @@ __global__ void gn_finalize_k(const double *sums, int NG, size_t len, float eps,
 
 }   // namespace
 
-/* (sum, sum of squares) per (sample, group) of the decoded values of an MX tensor (xdt 3 MX-fp8, 4 MX-fp4; reference layout, more than 16
-   channels) over the voxels [v0, v1), added to the slots sums[2 (n G + g)], sums[2 (n G + g) + 1] (3 x 8 bytes each; the caller zeroes them
+/* (sum, sum of squares) per (sample, group) of the decoded values of an MX tensor (xdt 3 MX-fp8, 4 MX-fp4; reference layout; 16 channels
+   or fewer in rows of 8 / 16) over the voxels [v0, v1), added to the slots sums[2 (n G + g)], sums[2 (n G + g) + 1] (3 x 8 bytes each; the caller zeroes them
    before the first part).  Returns 0, or -1 for a combination this library (or the reference: G > 64, C % G != 0) does not cover. */
 extern "C" int lp_gn_sums_mx_n(const void *x, int xdt, int N, int C, int G, size_t S, double *sums, size_t v0, size_t v1, int n0, int cnt) {
     if (!umx_ready("lp_gn_sums_mx")) return -1;
-    if ((xdt != UMX_MX8 && xdt != UMX_MX4) || C <= 16 || G < 1 || G > 64 || C % G || n0 < 0 || n0 + cnt > N) return -1;
+    if ((xdt != UMX_MX8 && xdt != UMX_MX4) || C < 1 || G < 1 || G > 64 || C % G || n0 < 0 || n0 + cnt > N) return -1;
     if (cnt <= 0 || v1 <= v0 || !S) return 0;
+    if (C <= 16) {                                             /* rows of 8 / 16 channels: the same codes and scale in 32-wide rows, zeros behind them */
+        const int xb = xdt == UMX_MX8 ? 8 : 4;
+        void *wide = umx_ws(3, umx_mx_bytes32(xb, N, C, S));
+        if (!wide) return -1;
+        umx_mx_rewidth(x, xb, N, C, S, wide, 1);
+        x = wide;
+    }
     const int nb = (C + 31) / 32;
     /* runs of about 2048 voxels of S (eight trips a block; a block ends in 2 x 4 or 2 x 32 slot additions), fewer where that leaves
        the machine short of blocks, never under 256 voxels */

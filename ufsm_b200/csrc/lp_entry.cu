@@ -216,7 +216,6 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
     else if (ybf == UMX_H16B) out_mode = UMX_OUT_H16B;
     else { fprintf(stderr, "%s: output storage %d\n", fn, ybf); abort(); }
     const bool narrow_out = out_mode == UMX_OUT_MXRAW && cout <= 16 && !sp.y2;      /* rows of 8 / 16 channels: written 32 wide into scratch, then narrowed */
-    if (narrow_out && osum && sp.stored_stats) not_built(fn, "statistics of a stored output of 16 channels or fewer");
     const int Ox = sp.y2 ? sp.o_split : cout, O2 = cout - Ox;
     if (sp.y2 && (Ox < 1 || O2 < 1)) { fprintf(stderr, "%s: o_split %d of %d output channels\n", fn, Ox, cout); abort(); }
     if (sp.y2 && out_mode == UMX_OUT_H16B) not_built(fn, "a split output in blocked fp16");
