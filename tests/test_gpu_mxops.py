@@ -25,7 +25,7 @@ def make_gp(Gn, arrays):
 
 
 # the second shape spans several tiles of the kernel on every axis (4 x 4 x 16 cells of the dual grid), with ragged last tiles
-@pytest.mark.parametrize("shape", [(2, 40, 5, 3, 5, 7), (1, 64, 8, 6, 9, 35)])
+@pytest.mark.parametrize("shape", [(2, 40, 5, 3, 5, 7), (1, 64, 8, 6, 9, 35), (2, 16, 2, 3, 5, 7), (1, 8, 1, 2, 6, 5)])      # the last two: rows of 16 / 8 channels
 @pytest.mark.parametrize("xbits,ybits,gn", [(8, 8, False), (4, 4, False), (8, 4, False), (4, 8, False), (8, 8, True), (4, 4, True)])
 def test_up2_fwd_mx(dev, xbits, ybits, gn, shape):
     import ufsm_b200
@@ -34,14 +34,14 @@ def test_up2_fwd_mx(dev, xbits, ybits, gn, shape):
     N, Cn, Gn, D, H, W = shape
     S = D * H * W
     x = (synth.rng(91).standard_normal(N * Cn * S) * 2).astype(f32)
-    mx = orc.pm_to_mx(x, 0, N, Cn, S, xbits, 32)
-    dq = orc.mx_to_pm(mx, xbits, N, Cn, S, 32)
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, xbits)                 # rows of the storage rule's width
+    dq = orc.mx_to_pm(mx, xbits, N, Cn, S)
     gp, keep = Gnp(), None
     if gn:
         pr = gn_params(92, N, Cn, Gn)
         gp, keep = make_gp(Gn, pr)
         dq = orc.gn_silu(dq, N, Cn, S, Gn, *pr, 1)
-    want = orc.pm_to_mx(orc.up2(dq, N, Cn, D, H, W), 0, N, Cn, 8 * S, ybits, 32)
+    want = orc.pm_to_mx(orc.up2(dq, N, Cn, D, H, W), 0, N, Cn, 8 * S, ybits)
     xd, yd = DevBuf(data=mx), DevBuf(want.size).fill(0xEE)
     L.lp_up2_fwd_mx(xd.ptr, 3 if xbits == 8 else 4, Shape5(N, Cn, D, H, W), yd.ptr, 3 if ybits == 8 else 4, gp)
     ufsm_b200.check()
@@ -53,7 +53,8 @@ def test_up2_fwd_mx(dev, xbits, ybits, gn, shape):
         assert bad == 0, "%d of %d bytes differ" % (bad, want.size)
 
 
-@pytest.mark.parametrize("bits,Ci,Co,N,h16,gn", [(8, 32, 7, 1, False, False), (4, 64, 16, 2, False, False), (8, 40, 3, 1, True, False), (8, 64, 32, 2, False, False), (8, 64, 7, 2, False, True), (4, 96, 10, 1, False, True)])
+@pytest.mark.parametrize("bits,Ci,Co,N,h16,gn", [(8, 32, 7, 1, False, False), (4, 64, 16, 2, False, False), (8, 40, 3, 1, True, False), (8, 64, 32, 2, False, False), (8, 64, 7, 2, False, True), (4, 96, 10, 1, False, True),
+                                                   (8, 16, 7, 2, False, False), (4, 8, 3, 1, True, True)])          # rows of 16 / 8 channels
 def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
     import ufsm_b200
     from ufsm_b200 import DevBuf, Shape5, Gnp
@@ -63,8 +64,8 @@ def test_conv1_fwd_mx(dev, bits, Ci, Co, N, h16, gn):
     x = (synth.rng(95).standard_normal(N * Ci * S) * 2).astype(f32)
     w = (synth.rng(96).standard_normal((Co, Ci)) / np.sqrt(Ci)).astype(f32)
     b = (0.1 * synth.rng(97).standard_normal(Co)).astype(f32)
-    mx = orc.pm_to_mx(x, 0, N, Ci, S, bits, 32)
-    dq = orc.mx_to_pm(mx, bits, N, Ci, S, 32)
+    mx = orc.pm_to_mx(x, 0, N, Ci, S, bits)
+    dq = orc.mx_to_pm(mx, bits, N, Ci, S)
     gp, keep = Gnp(), None
     if gn:
         pr = gn_params(98, N, Ci, 8)

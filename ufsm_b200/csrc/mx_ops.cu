@@ -251,12 +251,19 @@ void conv1_co(int co4, dim3 grid, size_t smem, const uint8_t *x, const float *w,
 template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, shape5 xs, const float *w, const float *b, int cout, YT *y, gnp_t gp, size_t vb = 0, size_t nv = 0, size_t ly = 0) {
     if (!umx_ready(fn)) return;
     if (xdt != UMX_MX8 && xdt != UMX_MX4) { fprintf(stderr, "%s: input dtype %d is not MX\n", fn, xdt); abort(); }
-    if (xs.c <= 16) { fprintf(stderr, "%s: an input of 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n", fn); abort(); }
+    if (xs.c < 1) { fprintf(stderr, "%s: %d input channels\n", fn, xs.c); abort(); }
     if (cout < 1 || (cout > 16 && cout % 16)) { fprintf(stderr, "%s: cout %d is neither 1..16 nor a multiple of 16\n", fn, cout); abort(); }
     if (xs.n > 65535) { fprintf(stderr, "%s: %d samples\n", fn, xs.n); abort(); }
     gp_check(fn, gp, xs.c);
     const size_t S = (size_t)xs.d * xs.h * xs.w;
     if (!S || !xs.n) return;
+    if (xs.c <= 16) {                                          /* rows of 8 / 16 channels (src/lp_common.cuh:132): the same codes and scale in 32-wide rows */
+        const int xb = xdt == UMX_MX8 ? 8 : 4;
+        void *wide = umx_ws(3, umx_mx_bytes32(xb, xs.n, xs.c, S));
+        if (!wide) return;
+        umx_mx_rewidth(x, xb, xs.n, xs.c, S, wide, 1);
+        x = wide;
+    }
     if (!nv) { vb = 0; nv = S; }
     if (!ly) ly = nv;
     if (vb + nv > S || ly < nv) { fprintf(stderr, "%s: voxels [%zu, %zu) of %zu into planes of %zu\n", fn, vb, vb + nv, S, ly); abort(); }
@@ -294,7 +301,17 @@ static void up2_fwd(const char *fn, const void *x, int xdt, shape5 ys, int nbx, 
     UMX_CK(fn);
 }
 extern "C" void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int ydt, gnp_t gp) {
-    if (xs.c <= 16) { fprintf(stderr, "lp_up2_fwd_mx: 16 channels or fewer (8 / 16-wide MX rows) is not built in this library\n"); abort(); }
+    if (xs.c <= 16 && xs.c >= 1 && (xdt == UMX_MX8 || xdt == UMX_MX4) && (ydt == UMX_MX8 || ydt == UMX_MX4)) {
+        /* rows of 8 / 16 channels on either side: widened into scratch, blended there, narrowed */
+        const int xb = xdt == UMX_MX8 ? 8 : 4, yb = ydt == UMX_MX8 ? 8 : 4;
+        const size_t S = (size_t)xs.d * xs.h * xs.w;
+        void *a = umx_ws(3, umx_mx_bytes32(xb, xs.n, xs.c, S)), *o = umx_ws(4, umx_mx_bytes32(yb, xs.n, xs.c, 8 * S));
+        if (!a || !o || !S || !xs.n) return;
+        umx_mx_rewidth(x, xb, xs.n, xs.c, S, a, 1);
+        up2_fwd("lp_up2_fwd_mx", a, xdt, xs, 1, 0, o, ydt, gp);
+        umx_mx_rewidth(o, yb, xs.n, xs.c, 8 * S, y, 0);
+        return;
+    }
     up2_fwd("lp_up2_fwd_mx", x, xdt, xs, (xs.c + 31) / 32, 0, y, ydt, gp);
 }
 /* src/nn_lp.h:137: the upsample of the 32-channel blocks [b0, b0 + nbk) of x alone; y an MX tensor of 32 nbk channels */
