@@ -131,3 +131,13 @@ def test_up2_blocks_conv1_ranges_and_add(dev, bits):
     L.lp_add_mx(yd.ptr, x2d.ptr, Shape5(N, Cn, D, H, W), bits, 0)
     ufsm_b200.check()
     assert np.array_equal(yd.download(), want)
+    # the same on a tensor of 16 channels: rows of 16 (src/lp_common.cuh:132)
+    Cs = 16
+    a16 = (synth.rng(305).standard_normal(N * Cs * S) * 3).astype(f32)
+    b16 = (synth.rng(306).standard_normal(N * Cs * S) * 3).astype(f32)
+    ma, mb = orc.pm_to_mx(a16, 0, N, Cs, S, bits), orc.pm_to_mx(b16, 0, N, Cs, S, bits)
+    want = orc.pm_to_mx((orc.mx_to_pm(ma, bits, N, Cs, S) + orc.mx_to_pm(mb, bits, N, Cs, S)).astype(f32), 0, N, Cs, S, bits)
+    yd, x2d = DevBuf(data=ma), DevBuf(data=mb)
+    L.lp_add_mx(yd.ptr, x2d.ptr, Shape5(N, Cs, D, H, W), bits, 0)
+    ufsm_b200.check()
+    assert np.array_equal(yd.download(), want)

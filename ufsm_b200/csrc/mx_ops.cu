@@ -365,12 +365,22 @@ extern "C" void lp_add_mx(void *y, const void *x, shape5 s, int dt, unsigned sr)
     const char *fn = "lp_add_mx";
     if (!umx_ready(fn)) return;
     if (sr) { fprintf(stderr, "%s: stochastic rounding is not built in this library\n", fn); abort(); }
-    if ((dt != 4 && dt != 8) || s.c <= 16) { fprintf(stderr, "%s: %d bits, %d channels (8 / 16-wide MX rows are not built in this library)\n", fn, dt, s.c); abort(); }
+    if ((dt != 4 && dt != 8) || s.c < 1) { fprintf(stderr, "%s: %d bits, %d channels\n", fn, dt, s.c); abort(); }
     const size_t rows = (size_t)s.n * ((s.c + 31) / 32) * s.d * s.h * s.w;
     if (!rows) return;
+    void *y_narrow = nullptr;
+    if (s.c <= 16) {                                           /* rows of 8 / 16 channels: both tensors widened into scratch, the sum narrowed back */
+        const size_t S = (size_t)s.d * s.h * s.w;
+        void *a = umx_ws(3, umx_mx_bytes32(dt, s.n, s.c, S)), *b = umx_ws(4, umx_mx_bytes32(dt, s.n, s.c, S));
+        if (!a || !b) return;
+        umx_mx_rewidth(y, dt, s.n, s.c, S, a, 1);
+        umx_mx_rewidth(x, dt, s.n, s.c, S, b, 1);
+        y_narrow = y; y = a; x = b;
+    }
     size_t g = (rows + 63) / 64; if (g > 148u * 16u) g = 148u * 16u;
     if (dt == 8) add_rows_k<8><<<(unsigned)g, 256>>>((uint8_t *)y, (const uint8_t *)x, rows);
     else add_rows_k<4><<<(unsigned)g, 256>>>((uint8_t *)y, (const uint8_t *)x, rows);
     g_umx_launches++;
+    if (y_narrow) umx_mx_rewidth(y, dt, s.n, s.c, (size_t)s.d * s.h * s.w, y_narrow, 0);
     UMX_CK(fn);
 }
