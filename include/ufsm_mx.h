@@ -31,7 +31,8 @@ enum { UMX_F32 = 0, UMX_BF16 = 1, UMX_F16 = 2, UMX_MX8 = 3, UMX_MX4 = 4, UMX_H16
 enum { UMX_LAYOUT_REF = 0, UMX_LAYOUT_SPLIT = 1 };
 enum { UMX_X_SPLIT = 1, UMX_Y_SPLIT = 2,     /* flags of umx_conv_fwd: the MX-fp8 input / output tensor is in the split layout */
        UMX_STATS_EPILOGUE = 4,               /* umx_conv_fwd_norm: take the InstanceNorm sums in the conv's epilogue where the kernel can (see there) */
-       UMX_X_H16 = 8 };                      /* x is the planar fp16 tensor [N][ci][D][H][W], not MX: the conv quantises it (UMX_CONV3 / UMX_CONV1) */
+       UMX_X_H16 = 8,                        /* x is the planar fp16 tensor [N][ci][D][H][W], not MX: the conv quantises it (UMX_CONV3 / UMX_CONV1) */
+       UMX_X_U8 = 16 };                      /* x is a planar tensor of CT bytes, read as the fp16 values byte / 255 (umx_u8_to_h16), then as UMX_X_H16 */
 
 /* ---- device runtime (src/nn.h:26-38: nn_init, nn_malloc, nn_free, nn_zero, nn_h2d, nn_d2h, nn_sync, nn_check) ---- */
 int nn_init(int device);                 /* select the device, check it is sm_100; 0 on success */
@@ -136,7 +137,9 @@ enum { UMX_OUT_H16B = 0,   /* y = fp16(acc + bias), blocked fp16 */
        UMX_OUT_MX = 1,     /* y = MX(fp16(acc + bias)) into blocks [b0, ...) of an MX tensor with nb_dst blocks (xtconv_cat_q) */
        UMX_OUT_PM32 = 2,   /* y = acc + bias, plane-major fp32 [n][co][S] */
        UMX_OUT_PM16 = 3,   /* y = fp16(acc + bias), plane-major fp16 */
-       UMX_OUT_MXRAW = 4 };/* y = MX(acc + bias) without the fp16 rounding (the lp epilogue, src/lp_common.cuh:1465-1536) */
+       UMX_OUT_MXRAW = 4,  /* y = MX(acc + bias) without the fp16 rounding (the lp epilogue, src/lp_common.cuh:1465-1536) */
+       UMX_OUT_PROB8 = 5 };/* y = uint8 round(254 sigmoid(fp16(acc + bias))), plane-major [n][co][S]: the probability bytes of umx_h16_to_prob_u8 taken in
+                              the conv's epilogue (UMX_CONV1 only: the network's head) */
 typedef struct umx_conv umx_conv;
 /* w, bias: host fp32 in PyTorch order (bias NULL: zero).  bits: 8 (E4M3) or 4 (E2M1) for weights and activations alike. */
 umx_conv *umx_conv_create(int kind, const float *w, const float *bias, int co, int ci, int bits);

@@ -500,3 +500,27 @@ def test_conv_entry_with_slab_local_groupnorm(dev, xbf):
     ufsm_b200.check()
     e = orc.rel_l2(yd.download(np.float16).astype(np.float32), want)
     assert e < TOL, "relative L2 %.3g" % e
+
+
+@pytest.mark.parametrize("bits,Ci,Co,N,D,H,W", [(8, 32, 7, 2, 4, 16, 16), (4, 64, 3, 1, 3, 8, 16), (8, 32, 40, 1, 2, 8, 16), (8, 32, 7, 1, 3, 5, 7)])
+def test_probability_bytes_from_the_head(dev, bits, Ci, Co, N, D, H, W):
+    """UMX_OUT_PROB8: the 1^3 conv writes round(254 sigmoid(fp16 logit)) itself; the bytes must be those of umx_h16_to_prob_u8 on the conv's
+    fp16 plane-major output (the head's shape takes them in its epilogue from a table of all fp16 values, other shapes through that pass)."""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf
+    S = D * H * W
+    x = (synth.rng(101).standard_normal(N * Ci * S) * 2).astype(np.float32)
+    w = (synth.rng(102).standard_normal((Co, Ci, 1)) * 3 / np.sqrt(Ci)).astype(np.float32)
+    b = synth.bias(103, Co, 0.5)
+    mx = orc.pm_to_mx(x, 0, N, Ci, S, bits, 32)
+    c = G.Conv("conv1", w, b, Co, Ci, bits)
+    lg, _ = c.fwd(mx, N, D, H, W, G.OUT_PM16)
+    pb, _ = c.fwd(mx, N, D, H, W, G.OUT_PROB8)
+    c.free()
+    L = ufsm_b200.lib()
+    ld, od = DevBuf(data=lg), DevBuf(lg.size // 2).fill(0xEE)
+    L.umx_h16_to_prob_u8(ld.ptr, lg.size // 2, od.ptr)
+    ufsm_b200.check()
+    assert np.array_equal(pb, od.download())
+    p = 1.0 / (1.0 + np.exp(-lg.view(np.float16).astype(np.float64)))
+    assert np.abs(pb.astype(np.float64) - 254.0 * p).max() <= 0.5 + 1e-3

@@ -64,6 +64,12 @@ def test_stem_parity(dev, N, Co, D, H, W, kind):
     raw3, coef, k3 = c.fwd_h16(x16, N, D, H, W, norm=True)
     assert k3 == 3 and np.array_equal(raw3, raw)
     assert np.array_equal(coef, npapi.in_stats_coef(raw.view(np.float16), N, Co, D, H, W))
+    if kind == "u8":
+        # CT bytes as the input (UMX_X_U8): the bytes of the fp16 input byte / 255, in the kernel and in the quantise-first path (W = 12)
+        ct = (x16.astype(np.float32) * 255).round().astype(np.uint8)
+        assert np.array_equal((ct.astype(np.float32) / np.float32(255)).astype(np.float16), x16)
+        raw8, _, k8 = c.fwd_h16(ct, N, D, H, W, u8=True)
+        assert k8 == 3 and np.array_equal(raw8, raw)
     c.free()
 
 
@@ -85,4 +91,9 @@ def test_fp16_input_other_shapes(dev, Ci, Co, D, H, W, bits, mode):
     assert k != 3
     raw2, _ = c.fwd(mx, 1, D, H, W, om)
     assert np.array_equal(raw, raw2)
+    if Ci == 1 and bits == 8 and mode == "h16b":
+        ct = synth.ct_u8(76, S)
+        r8, _, k8 = c.fwd_h16(ct, 1, D, H, W, out_mode=om, u8=True)
+        r16, _, _ = c.fwd_h16((ct.astype(np.float32) / np.float32(255)).astype(np.float16), 1, D, H, W, out_mode=om)
+        assert (k8 == 3) == (W % 8 == 0 and Co <= 32) and np.array_equal(r8, r16)
     c.free()

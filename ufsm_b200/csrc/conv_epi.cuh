@@ -18,6 +18,7 @@ struct EpiArgs {
     int y_split;                    /* MX-fp8 output in the split layout [n][blk][half][voxel][16 B] */
     void *y;
     const float *bias;              /* [cop] */
+    const uint8_t *ptab;            /* UMX_OUT_PROB8: the probability byte of every fp16 bit pattern (65536 bytes) */
 };
 
 /* v: the 32 fp32 accumulators of GEMM row (n, z, oy, ox), 32-column block cb_g.  Adds the bias, rounds as the output mode asks (v keeps

@@ -20,6 +20,7 @@
 #include "tc_ptx.cuh"
 #include "conv_epi.cuh"
 #include <cuda_bf16.h>
+#include <type_traits>
 
 int umx_prof_open(double flops);
 void umx_prof_close(int id);
@@ -29,7 +30,7 @@ namespace {
 constexpr long long kWaitLimitS = 4000000000ll;
 
 struct StemArgs {
-    const __half *x; uint8_t *y; const uint8_t *wb;
+    const void *x; uint8_t *y; const uint8_t *wb;      /* x: fp16 [N][D][H][W], or CT bytes read as fp16(byte / 255) (the U8 kernel) */
     int N, D, H, W, tiles_x, tiles; long long units; int *err;
 };
 
@@ -98,7 +99,10 @@ constexpr int kStemThreads = 288, kStemBlocks = 4;           /* blocks a multipr
    the two MMAs and a commit on `done`.  Warps 0-3 take the accumulators out (`done`), free them (`acce`) and store the rows.  `done` also
    tells the producers that the stage's A tile has been read.  Every wait is bounded; a wait that gives up raises the block's abort
    flag, which ends the other roles' waits, and records where in the error words. */
+template <bool U8>
 __global__ void __launch_bounds__(kStemThreads, kStemBlocks) conv_stem_k(const StemArgs a) {
+    typedef typename std::conditional<U8, uint8_t, __half>::type XT;
+    __shared__ unsigned short qtab[U8 ? 256 : 1];            /* U8: the quantised value (bf16 bits) of every CT byte */
     __shared__ __align__(128) uint8_t sA[2][8192];          /* per stage [4 K chunks][128 voxels][8 bf16] */
     __shared__ __align__(128) uint8_t sB[2048];             /* [4 K chunks][32 outputs][8 bf16] */
     __shared__ __align__(16) uint8_t stg_all[4 * 2048];     /* the epilogue warps' rows on their way out */
@@ -114,6 +118,7 @@ __global__ void __launch_bounds__(kStemThreads, kStemBlocks) conv_stem_k(const S
         abort_mem = 0; fence_barrier_init();
     }
     if (threadIdx.x < 128) ((uint4 *)sB)[threadIdx.x] = __ldg((const uint4 *)a.wb + threadIdx.x);     /* layer constants: prepared and complete before any launch */
+    if (U8 && threadIdx.x < 256) qtab[threadIdx.x] = fq_h16_one(__float2half_rn(__fdiv_rn((float)threadIdx.x, 255.f)), true);     /* the value umx_u8_to_h16 gives the byte */
     if (warp == 1) { tmem_alloc(smem_u32(&tmem_slot), 64); tmem_relinquish(); }
     fence_proxy_async();
     tc_fence_before();
@@ -134,24 +139,27 @@ __global__ void __launch_bounds__(kStemThreads, kStemBlocks) conv_stem_k(const S
         uint32_t dead = 0; int pc = 0;
         for (long long u = u0; u < u1;) {
             const StemRun rn = stem_run(a, u, u1);
-            const __half *xn = a.x + (size_t)rn.n * S;
+            const XT *xn = (const XT *)a.x + (size_t)rn.n * S;
             /* the halo tile of an input plane: 180 values, two a thread; plane z + 3 is requested while plane z is built */
             const int gy0 = rn.y0 - 1 + t0 / 10, gx0 = rn.x0 - 1 + t0 % 10, gy1 = rn.y0 - 1 + t1 / 10, gx1 = rn.x0 - 1 + t1 % 10;
             const bool in0 = gy0 >= 0 && gy0 < H && gx0 >= 0 && gx0 < W, in1 = t1 < 180 && gy1 >= 0 && gy1 < H && gx1 >= 0 && gx1 < W;
             /* every load is issued unconditionally from an address inside the tensor (positions outside the volume read the sample's first
                voxel) and masked when the value is used: nothing waits for a load at the place where it is issued */
-            const __half *s0 = in0 ? xn + (ptrdiff_t)gy0 * W + gx0 : xn, *s1 = in1 ? xn + (ptrdiff_t)gy1 * W + gx1 : xn;
-            auto fetch = [&](int zp, __half &v0, __half &v1) {
+            const XT *s0 = in0 ? xn + (ptrdiff_t)gy0 * W + gx0 : xn, *s1 = in1 ? xn + (ptrdiff_t)gy1 * W + gx1 : xn;
+            auto fetch = [&](int zp, XT &v0, XT &v1) {
                 const size_t zo = (size_t)min(max(zp, 0), D - 1) * HW;
                 v0 = __ldg(s0 + zo); v1 = __ldg(s1 + zo);
             };
-            auto put = [&](int zp, __half v0, __half v1) {
+            auto quant = [&](XT v, bool live) -> unsigned short {
+                if constexpr (U8) return live ? qtab[v] : (unsigned short)0; else return fq_h16_one(v, live);
+            };
+            auto put = [&](int zp, XT v0, XT v1) {
                 const bool zin = zp >= 0 && zp < D;
                 unsigned short *dst = (unsigned short *)ring[(zp + 4) & 3];
-                dst[t0] = fq_h16_one(v0, zin && in0);
-                if (t1 < 180) dst[t1] = fq_h16_one(v1, zin && in1);
+                dst[t0] = quant(v0, zin && in0);
+                if (t1 < 180) dst[t1] = quant(v1, zin && in1);
             };
-            __half a0, a1, b0, b1;
+            XT a0, a1, b0, b1;
             fetch(rn.zb - 1, a0, a1); fetch(rn.zb, b0, b1);
             if (producers_sync_or(dead | (uint32_t)*abort_s)) break;     /* the previous run's last tile has been built: its ring slots are free */
             put(rn.zb - 1, a0, a1); put(rn.zb, b0, b1);
@@ -160,7 +168,7 @@ __global__ void __launch_bounds__(kStemThreads, kStemBlocks) conv_stem_k(const S
             uint32_t P0[5], P1[5], P2[5];                                /* the voxel's taps in planes z - 1, z, z + 1 */
             /* one plane; (v0, v1) holds the raw values of plane z + 1 and takes those of plane z + 3 as soon as they are used: the two register
                pairs alternate, so a value is never moved while its load is in flight */
-            auto step = [&](int z, __half &v0, __half &v1) -> bool {
+            auto step = [&](int z, XT &v0, XT &v1) -> bool {
                 put(z + 1, v0, v1);
                 fetch(z + 3, v0, v1);
                 if (producers_sync_or(dead | (uint32_t)*abort_s)) return true;
@@ -277,11 +285,12 @@ uint8_t *umx_conv_stem_prepare(const umx_conv *c, const float *w_dev) {
     g_umx_launches++;
     return wb;
 }
-/* y (blocked fp16, one block of 32 channels) = conv of the fp16 one-channel tensor x [N][D][H][W]; 1: this kernel does not take the shape */
-int umx_conv_fwd_stem(const umx_conv *c, const void *x16, int N, int D, int H, int W, void *y) {
+/* y (blocked fp16, one block of 32 channels) = conv of the one-channel tensor x [N][D][H][W], fp16 or (src8) CT bytes read as fp16(byte / 255);
+   1: this kernel does not take the shape */
+int umx_conv_fwd_stem(const umx_conv *c, const void *x, int src8, int N, int D, int H, int W, void *y) {
     if (!c->wstem || (W & 7) || !N || !D || !H) return 1;
     StemArgs a; memset(&a, 0, sizeof a);
-    a.x = (const __half *)x16; a.y = (uint8_t *)y; a.wb = c->wstem;
+    a.x = x; a.y = (uint8_t *)y; a.wb = c->wstem;
     a.N = N; a.D = D; a.H = H; a.W = W; a.tiles_x = W / 8; a.tiles = a.tiles_x * ((H + 15) / 16); a.units = (long long)N * a.tiles * D;
     a.err = umx_errflag(); if (!a.err) return -1;
     static int slots_of[16];                                /* blocks of this kernel the device holds at once (three a multiprocessor: registers): looked up once per device */
@@ -289,7 +298,7 @@ int umx_conv_fwd_stem(const umx_conv *c, const void *x16, int N, int D, int H, i
     if (!slots_of[dev]) { int sms = 148; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); slots_of[dev] = kStemBlocks * sms; }
     long long grid = slots_of[dev]; if (grid > a.units) grid = a.units;
     const int pid = umx_prof_open(2.0 * (double)N * D * H * W * 27.0 * c->co);
-    umx_launch(conv_stem_k, dim3((unsigned)grid), dim3(kStemThreads), 0, a);
+    if (src8) umx_launch(conv_stem_k<true>, dim3((unsigned)grid), dim3(kStemThreads), 0, a); else umx_launch(conv_stem_k<false>, dim3((unsigned)grid), dim3(kStemThreads), 0, a);
     umx_prof_close(pid);
     g_umx_launches++;
     UMX_CK("umx_conv_fwd_stem");

@@ -398,8 +398,9 @@ extern "C" void umx_in_stats_coef(const void *y, int N, int C, int D, int H, int
 void umx_in_part(const void *y, int N, int C, int D, int H, int W, double *part);
 uint8_t *umx_conv_p_prepare(const umx_conv *c, const float *w_dev);
 uint8_t *umx_conv_stem_prepare(const umx_conv *c, const float *w_dev);
-int umx_conv_fwd_stem(const umx_conv *c, const void *x16, int N, int D, int H, int W, void *y);
+int umx_conv_fwd_stem(const umx_conv *c, const void *x, int src8, int N, int D, int H, int W, void *y);
 int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc, int N, int D, int H, int W, const EpiArgs &e);
+const uint8_t *umx_prob_table(void);
 
 
 static umx_conv *conv_build(int kind, const float *w_dev, const float *bias_dev, int co, int ci, int bits) {
@@ -466,8 +467,9 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     if (!umx_ready("umx_conv_fwd")) return -1;
     if (!c) { umx_latch_msg("umx_conv_fwd: no conv"); return -1; }
     if (part && (out_mode != UMX_OUT_H16B || c->kind == UMX_TCONV2)) { fprintf(stderr, "umx_conv_fwd: partial sums only with a blocked fp16 output of a plain conv\n"); abort(); }
+    if (out_mode == UMX_OUT_PROB8 && (!c || c->kind != UMX_CONV1 || part || nb_dst)) { fprintf(stderr, "umx_conv_fwd: probability bytes only from a 1^3 conv into a tensor of its own\n"); abort(); }
     if ((out_mode == UMX_OUT_MX || out_mode == UMX_OUT_MXRAW) && out_bits != 8 && out_bits != 4) { fprintf(stderr, "umx_conv_fwd: MX output needs out_bits 8 or 4\n"); abort(); }
-    if (flags & UMX_X_H16) {
+    if (flags & (UMX_X_H16 | UMX_X_U8)) {
         /* x is the fp16 tensor [N][ci][D][H][W] itself.  The tap-packed kernel takes the one-channel 3^3 case as it is; everything else is
            quantised into scratch first and goes the usual way. */
         if (c->kind != UMX_CONV3 && c->kind != UMX_CONV1) { fprintf(stderr, "umx_conv_fwd: an fp16 input only for the 3^3 and 1^3 convs\n"); abort(); }
@@ -476,7 +478,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
         const char *env = getenv("UMX_STEM");
         const bool stem_on = !(env && *env == '0');
         if (stem_on && c->wstem && out_mode == UMX_OUT_H16B && !nb_dst) {
-            const int r = umx_conv_fwd_stem(c, x, N, D, H, W, y);
+            const int r = umx_conv_fwd_stem(c, x, (flags & UMX_X_U8) != 0, N, D, H, W, y);
             if (r < 0) return -1;
             if (r == 0) {
                 g_last_kernel = 3;
@@ -485,10 +487,17 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
                 return 0;
             }
         }
+        if (flags & UMX_X_U8) {                             /* bytes -> fp16 in scratch */
+            const size_t nx = (size_t)N * c->ci * D * H * W;
+            void *h = umx_ws(12, nx * 2);
+            if (!h) return -1;
+            umx_u8_to_h16((const uint8_t *)x, nx, h);
+            x = h;
+        }
         void *ws = umx_ws(1, umx_mx_bytes32(c->bits, N, c->ci, (size_t)D * H * W));
         if (!ws) return -1;
         umx_pm_to_mx32(x, UMX_F16, N, c->ci, (size_t)D * H * W, ws, c->bits, UMX_LAYOUT_SPLIT);
-        x = ws; flags |= UMX_X_SPLIT;
+        x = ws; flags = (flags & ~(UMX_X_H16 | UMX_X_U8)) | UMX_X_SPLIT;
     }
     encode_fn enc = get_encode(); if (!enc) return -1;
     ConvArgs a; memset(&a, 0, sizeof a);
@@ -527,6 +536,7 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
     a.e.out_mode = out_mode; a.e.out_bits = out_bits; a.e.tconv = c->kind == UMX_TCONV2; a.e.co_real = c->co; a.e.cob_t = c->cob_t;
     a.e.nb_dst = nb_dst ? nb_dst : c->cob_t; a.e.b0 = nb_dst ? b0 : 0;
     a.e.y = y; a.e.y_split = (flags & UMX_Y_SPLIT) != 0; a.err = umx_errflag();
+    if (out_mode == UMX_OUT_PROB8) { a.e.ptab = umx_prob_table(); if (!a.e.ptab) return -1; }
     if (!a.err) return -1;
     /* tensor map over the activation codes seen as 16-byte-wide planes [plane][z][y][x * 16 B]: fp8 in the split layout has two planes a
        block, fp4 one.  A box is (10 or 8 voxels) x (18 or 16 rows) x 1 plane of z x 2 planes; voxels outside the volume read as zero. */
@@ -582,6 +592,15 @@ static int conv_fwd_impl(const umx_conv *c, const void *x, int N, int D, int H, 
             else if (rc == 0 && part) umx_in_part(y, N, c->co, D, H, W, part);
             return rc;
         }
+    }
+    if (out_mode == UMX_OUT_PROB8) {
+        /* not the head's shape: fp16 plane-major logits into scratch, then the probability pass (the same bytes) */
+        const size_t ny = (size_t)N * c->co * S;
+        void *t = umx_ws(12, ny * 2);
+        if (!t) return -1;
+        const int rc = conv_fwd_impl(c, x, N, D, H, W, t, UMX_OUT_PM16, 0, 0, 0, nullptr, flags | (c->bits == 8 ? UMX_X_SPLIT : 0), nullptr);
+        if (rc == 0) umx_h16_to_prob_u8(t, ny, (uint8_t *)y);
+        return rc;
     }
     const size_t smem = 1024 + (size_t)a.ring * a.stage_bytes;
     static size_t smem_set[16];

@@ -188,6 +188,29 @@ __global__ void __launch_bounds__(kThreadsP, 2) conv_mxp_k(const __grid_constant
             const int jc = nchunk > 1 ? eg : 0;
             if (!mbar_wait(bar_accf + 8 * slot, (uint32_t)sph, abort_flag, kWaitLimitP)) { raise_p(a, abort_flag, 5, pc); dead = true; break; }
             tc_fence_after();
+            if (EPI == 7) {
+                /* probability bytes of a plane-major output of at most eight channels (the head): only those accumulator columns leave TMEM; the
+                   byte of fp16(acc + bias) comes from the table of all 65536 fp16 values; a warp's 32 voxels are 32 consecutive bytes of a plane */
+                uint32_t r8[8];
+                if (mine) { tmem_ld8(tlane + (uint32_t)(slot * a.ntp), r8); tmem_ld_wait(); }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acce + 8 * slot);
+                const unsigned vo = (unsigned)tin * 128u + (unsigned)r;
+                if (mine && vo < Su) {
+                    uint8_t *yo = (uint8_t *)a.e.y + (size_t)n * a.e.co_real * Su + vo;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        if (k < a.e.co_real) {
+                            const __half h = __float2half_rn(__fadd_rn(__uint_as_float(r8[k]), __ldg(a.e.bias + k)));
+                            yo[(size_t)k * Su] = __ldg(a.e.ptab + __half_as_ushort(h));
+                        }
+                    }
+                }
+                if (++slot == NS) { slot = 0; sph ^= 1; }
+                if (++ntile == a.ntiles) { ntile = 0; if (++tin == (int)a.rtiles_per_n) { tin = 0; n++; } }
+                continue;
+            }
             uint32_t rr[32];
             if (mine) { tmem_ld32(tlane + (uint32_t)(slot * a.ntp + jc * 32), rr); tmem_ld_wait(); }
             tc_fence_before();
@@ -292,7 +315,8 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     PGeo g; ConvPArgs a; memset(&a, 0, sizeof a);
     const size_t S = (size_t)D * H * W;
-    if (!c->wp || !p_geometry(c, &g) || (S & 15) || S > (size_t)1 << 30) return 1;       /* the scale plane's rows must be multiples of 16 bytes */
+    if (!c->wp || !p_geometry(c, &g) || (S & 15) || S > (size_t)1 << 30) return 1;
+    if (e.out_mode == UMX_OUT_PROB8 && (e.co_real > 8 || g.ntiles != 1 || e.tconv || !e.ptab)) return 1;     /* the probability epilogue is the head's: one column tile, at most eight channels */       /* the scale plane's rows must be multiples of 16 bytes */
     a.N = N; a.nkb = c->nkb; a.nki = c->nki; a.bits = c->bits; a.cop = c->cop; a.ntp = g.ntp; a.ntiles = g.ntiles; a.ngroups = g.ngroups;
     a.S = (long long)S; a.rtiles_per_n = (long long)((S + 127) / 128); a.jobs = (long long)N * a.rtiles_per_n * g.ntiles; a.HW = H * W; a.W = W;
     a.w_codes = g.w_codes; a.w_bytes = g.w_bytes; a.nquad = g.nq;
@@ -326,8 +350,8 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     if (!attr_set[dev & 15]) {
         cudaError_t er = cudaSuccess;
 #define UMX_P_ATTR(B, E) if (er == cudaSuccess) er = cudaFuncSetAttribute(conv_mxp_k<B, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
-        UMX_P_ATTR(8, 0); UMX_P_ATTR(8, 1); UMX_P_ATTR(8, 2); UMX_P_ATTR(8, 3); UMX_P_ATTR(8, 4); UMX_P_ATTR(8, 5); UMX_P_ATTR(8, 6);
-        UMX_P_ATTR(4, 0); UMX_P_ATTR(4, 1); UMX_P_ATTR(4, 2); UMX_P_ATTR(4, 3); UMX_P_ATTR(4, 4); UMX_P_ATTR(4, 5); UMX_P_ATTR(4, 6);
+        UMX_P_ATTR(8, 0); UMX_P_ATTR(8, 1); UMX_P_ATTR(8, 2); UMX_P_ATTR(8, 3); UMX_P_ATTR(8, 4); UMX_P_ATTR(8, 5); UMX_P_ATTR(8, 6); UMX_P_ATTR(8, 7);
+        UMX_P_ATTR(4, 0); UMX_P_ATTR(4, 1); UMX_P_ATTR(4, 2); UMX_P_ATTR(4, 3); UMX_P_ATTR(4, 4); UMX_P_ATTR(4, 5); UMX_P_ATTR(4, 6); UMX_P_ATTR(4, 7);
 #undef UMX_P_ATTR
         if (er != cudaSuccess) { umx_latch("umx_conv_fwd: shared memory attribute", er); return -1; }
         attr_set[dev & 15] = 1;
@@ -340,9 +364,10 @@ int umx_conv_fwd_p(const umx_conv *c, const void *x, void *enc_v, int N, int D, 
     else if (e.out_mode == UMX_OUT_PM16 && !e.tconv) epi = 2;
     else if (e.out_mode == UMX_OUT_MX && e.out_bits == 8 && e.y_split) epi = e.tconv ? 4 : 3;
     else if (e.out_mode == UMX_OUT_MX && e.out_bits == 4) epi = e.tconv ? 6 : 5;
+    else if (e.out_mode == UMX_OUT_PROB8) epi = 7;
 #define UMX_P_GO(B, E) umx_launch(conv_mxp_k<B, E>, dim3(grid), dim3(kThreadsP), smem, m0, ms, a)
-    if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; case 5: UMX_P_GO(8, 5); break; case 6: UMX_P_GO(8, 6); break; default: UMX_P_GO(8, 0); } }
-    else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; case 5: UMX_P_GO(4, 5); break; case 6: UMX_P_GO(4, 6); break; default: UMX_P_GO(4, 0); } }
+    if (c->bits == 8) { switch (epi) { case 1: UMX_P_GO(8, 1); break; case 2: UMX_P_GO(8, 2); break; case 3: UMX_P_GO(8, 3); break; case 4: UMX_P_GO(8, 4); break; case 5: UMX_P_GO(8, 5); break; case 6: UMX_P_GO(8, 6); break; case 7: UMX_P_GO(8, 7); break; default: UMX_P_GO(8, 0); } }
+    else { switch (epi) { case 1: UMX_P_GO(4, 1); break; case 2: UMX_P_GO(4, 2); break; case 3: UMX_P_GO(4, 3); break; case 4: UMX_P_GO(4, 4); break; case 5: UMX_P_GO(4, 5); break; case 6: UMX_P_GO(4, 6); break; case 7: UMX_P_GO(4, 7); break; default: UMX_P_GO(4, 0); } }
 #undef UMX_P_GO
     return 0;
 }

@@ -93,7 +93,7 @@ extern "C" void umx_copy2d_async(void *dst, size_t dpitch, const void *src, size
 }
 
 /* scratch: per device, per slot, grows on demand, never shrinks */
-enum { WS_SLOTS = 12 };
+enum { WS_SLOTS = 13 };
 static void *g_ws[16][WS_SLOTS];
 static size_t g_ws_bytes[16][WS_SLOTS];
 void *umx_ws(int slot, size_t bytes) {

@@ -140,13 +140,15 @@ static void conv_norm(umx_unet *u, const umx_conv *c, const void *x, int xflag, 
     umx_conv_fwd_norm(c, x, N, D, D, D, u->ybuf, u->part, nullptr, nullptr, 1e-5f, u->coef, (xflag ? xflag : UMX_X_SPLIT) | (epi ? UMX_STATS_EPILOGUE : 0));
     umx_in_apply(u->ybuf, u->coef, N, C, D, D, D, 2, q, bits, nb_dst, b0, q_s2d, nullptr, UMX_LAYOUT_SPLIT);
 }
-static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) {
+enum { FMT_PROB8 = -8 };     /* forward(): the head writes probability bytes (UMX_OUT_PROB8) */
+/* x_dev: the fp16 patches, or (x_u8) the CT bytes themselves, which the first conv reads as byte / 255 */
+static int forward_x(umx_unet *u, const void *x_dev, int x_u8, int N, void *logits, int logits_fmt) {
     const umx_unet_cfg *c = &u->cfg; const int L = c->L, bm = c->bits_mid, bl = c->bits_last;
     if (N < 1 || N > u->maxN) { fprintf(stderr, "umx_unet_forward: batch %d outside 1..%d\n", N, u->maxN); abort(); }
     for (int l = 0; l < L; l++) {
         const int D = u->Dl[l], C = c->cw[l], nb = C / 32;
         /* the first conv takes the fp16 patch itself (UMX_X_H16: quantised on the way in) */
-        conv_norm(u, u->enc1[l], l ? u->dn[l] : x_dev, l ? 0 : UMX_X_H16, N, C, D, u->act[l], bm, 0, 0, nullptr);
+        conv_norm(u, u->enc1[l], l ? u->dn[l] : x_dev, l ? 0 : (x_u8 ? UMX_X_U8 : UMX_X_H16), N, C, D, u->act[l], bm, 0, 0, nullptr);
         if (l < L - 1) {
             conv_norm(u, u->enc2[l], u->act[l], 0, N, C, D, u->cat[l], bm, 2 * nb, nb, u->s2d[l]);
             umx_conv_fwd(u->down[l], u->s2d[l], N, D / 2, D / 2, D / 2, u->dn[l + 1], UMX_OUT_MX, bm, 0, 0, nullptr, UMX_X_SPLIT | UMX_Y_SPLIT);
@@ -160,17 +162,17 @@ static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logi
         conv_norm(u, u->dec2[l], u->act[l], 0, N, C, D, u->dec[l], l ? bm : bl, 0, 0, nullptr);
         cur = u->dec[l];
     }
-    umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : UMX_OUT_PM32, 0, 0, 0, nullptr, UMX_X_SPLIT);
+    umx_conv_fwd(u->head, cur, N, c->P, c->P, c->P, logits, logits_fmt == UMX_F16 ? UMX_OUT_PM16 : logits_fmt == FMT_PROB8 ? UMX_OUT_PROB8 : UMX_OUT_PM32, 0, 0, 0, nullptr, UMX_X_SPLIT);
     return 0;
 }
+static int forward(umx_unet *u, const void *x_dev, int N, void *logits, int logits_fmt) { return forward_x(u, x_dev, 0, N, logits, logits_fmt); }
 int umx_unet_forward(umx_unet *u, const void *x_dev, int N, float *logits_dev) { return forward(u, x_dev, N, logits_dev, UMX_F32); }
 int umx_unet_forward_h16(umx_unet *u, const void *x_dev, int N, void *logits_dev) { return forward(u, x_dev, N, logits_dev, UMX_F16); }
 /* uint8 CT patches on the host -> fp16 logits on the host: copy in, convert, forward, copy out */
 int umx_unet_forward_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits16_host) {
     const size_t S = cube(u->cfg.P);
     nn_h2d(u->xu8, ct_host, (size_t)N * S);
-    umx_u8_to_h16(u->xu8, (size_t)N * S, u->x16);
-    forward(u, u->x16, N, u->logits16, UMX_F16);
+    forward_x(u, u->xu8, 1, N, u->logits16, UMX_F16);
     nn_d2h(logits16_host, u->logits16, (size_t)N * u->cfg.nh * S * 2);
     return nn_check() ? -1 : 0;
 }
@@ -202,11 +204,10 @@ static int submit_host(umx_unet *u, const uint8_t *ct_host, int N, void *logits1
     umx_event_record(u->ev_up[k], u->s_in);
     /* forward on the legacy default stream: after the upload, and after the slot's logits of two calls ago have left */
     umx_stream_wait(nullptr, u->ev_up[k]);
-    umx_u8_to_h16(u->pxu8[k], (size_t)N * S, u->x16);
-    umx_event_record(u->ev_used[k], nullptr);
     umx_stream_wait(nullptr, u->ev_down[k]);
-    forward(u, u->x16, N, u->plog[k], UMX_F16);
-    if (as_u8) umx_h16_to_prob_u8(u->plog[k], (size_t)N * u->cfg.nh * S, u->pprob[k]);
+    /* the first conv reads the bytes itself and the head writes the probability bytes itself: no conversion pass on either side */
+    if (as_u8) forward_x(u, u->pxu8[k], 1, N, u->pprob[k], FMT_PROB8); else forward_x(u, u->pxu8[k], 1, N, u->plog[k], UMX_F16);
+    umx_event_record(u->ev_used[k], nullptr);          /* the slot's bytes have been read (by the first conv; recorded behind the forward) */
     umx_event_record(u->ev_ready[k], nullptr);
     /* download */
     umx_stream_wait(u->s_out, u->ev_ready[k]);

@@ -69,6 +69,25 @@ __global__ void __launch_bounds__(256) h16_to_prob_u8_k(const __half *__restrict
     }
     for (size_t i = n8 * 8 + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) y[i] = (uint8_t)prob_u8(__half2float(x[i]));
 }
+__global__ void half_iota_k(unsigned short *h) { h[blockIdx.x * blockDim.x + threadIdx.x] = (unsigned short)(blockIdx.x * blockDim.x + threadIdx.x); }
+/* the probability byte of every fp16 bit pattern (65536 bytes, made once per device by the pass itself): what a conv's epilogue looks its
+   fp16 logit up in (UMX_OUT_PROB8) */
+const uint8_t *umx_prob_table(void) {
+    static uint8_t *tab[16];
+    int d = 0; if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 16) return nullptr;
+    if (tab[d]) return tab[d];
+    unsigned short *h = (unsigned short *)nn_malloc(65536 * 2);
+    uint8_t *t = (uint8_t *)nn_malloc(65536);
+    if (!h || !t) { nn_free(h); nn_free(t); return nullptr; }
+    half_iota_k<<<256, 256>>>(h);
+    h16_to_prob_u8_k<<<32, 256>>>((const __half *)h, t, 65536);
+    g_umx_launches += 2;
+    cudaStreamSynchronize(0);
+    UMX_CK("umx_prob_table");
+    nn_free(h);
+    tab[d] = t;
+    return t;
+}
 extern "C" void umx_h16_to_prob_u8(const void *x, size_t n, uint8_t *y) {
     if (!umx_ready("umx_h16_to_prob_u8")) return;
     if (((size_t)x & 15) || ((size_t)y & 7)) { fprintf(stderr, "umx_h16_to_prob_u8: x must be 16-byte and y 8-byte aligned\n"); abort(); }

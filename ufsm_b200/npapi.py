@@ -8,7 +8,7 @@ import numpy as np
 from ._lib import DevBuf, UnetCfg, check as _check, lib as _libf
 
 KIND = {"conv3": 0, "conv1": 1, "down2": 2, "tconv2": 3, "conv3s2": 4}
-OUT_H16B, OUT_MX, OUT_PM32, OUT_PM16, OUT_MXRAW = 0, 1, 2, 3, 4
+OUT_H16B, OUT_MX, OUT_PM32, OUT_PM16, OUT_MXRAW, OUT_PROB8 = 0, 1, 2, 3, 4, 5
 
 
 def nb32(Cn):
@@ -86,6 +86,8 @@ class Conv:
             nbytes = N * nbo * So * (32 * out_bits // 8 + 1)
         elif out_mode == OUT_PM32:
             nbytes = N * self.co * So * 4
+        elif out_mode == OUT_PROB8:
+            nbytes = N * self.co * So
         else:
             nbytes = N * self.co * So * 2
         yd = dst if dst is not None else DevBuf(nbytes).fill(0xEE)
@@ -100,19 +102,20 @@ class Conv:
             out = from_split(out, N, nbo * 32, So, out_bits)
         return out, (pd if want_part else None)
 
-    def fwd_h16(self, x16, N, D, H, W, out_mode=OUT_H16B, norm=False, eps=1e-5):
-        """the conv on the planar fp16 tensor itself (UMX_X_H16: quantised on the way in).  Returns (output bytes, coef or None, the kernel
-        that ran: umx_conv_last_kernel)."""
-        xd = DevBuf(data=np.ascontiguousarray(x16, np.float16))
+    def fwd_h16(self, x16, N, D, H, W, out_mode=OUT_H16B, norm=False, eps=1e-5, u8=False):
+        """the conv on the planar fp16 tensor itself (UMX_X_H16: quantised on the way in), or (u8) on CT bytes read as byte / 255 (UMX_X_U8).
+        Returns (output bytes, coef or None, the kernel that ran: umx_conv_last_kernel)."""
+        xd = DevBuf(data=np.ascontiguousarray(x16, np.uint8 if u8 else np.float16))
+        xflag = 16 if u8 else 8
         S = D * H * W
         yd = DevBuf(N * nb32(self.co) * S * 64 if out_mode == OUT_H16B else N * self.co * S * 4).fill(0xEE)
         cd = None
         if norm:
             pd = DevBuf(L().umx_stats_doubles(N, self.co, D, H, W) * 8).fill(0xEE)
             cd = DevBuf(N * self.co * 8).fill(0xEE)
-            rc = L().umx_conv_fwd_norm(self.h, xd.ptr, N, D, H, W, yd.ptr, pd.ptr, None, None, C.c_float(eps), cd.ptr, 8)
+            rc = L().umx_conv_fwd_norm(self.h, xd.ptr, N, D, H, W, yd.ptr, pd.ptr, None, None, C.c_float(eps), cd.ptr, xflag)
         else:
-            rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, 0, 0, 0, None, 8)
+            rc = L().umx_conv_fwd(self.h, xd.ptr, N, D, H, W, yd.ptr, out_mode, 0, 0, 0, None, xflag)
         _check()
         assert rc == 0
         return yd.download(), (cd.download(np.float32) if cd else None), L().umx_conv_last_kernel()
