@@ -263,6 +263,16 @@ void nn_pred_ctmask_t(const uint8_t *ct, size_t n, uint32_t *bits, int t);
 void nn_pred_place_m(const float *lg, const uint32_t *bits, int W, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
 void nn_pred_place_m_d(const float *lg, const uint32_t *bits, int D, int W, int hz, int halo, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
 void nn_pred_place_mz(const float *lg, const uint32_t *bits, int W, int halo, int zlo, int zhi, int zoff, int oz, int oy, int ox, int ez, int ey, int ex, int shard, uint8_t *dsh);
+/* the seam feather of the reference's predict (src/predict.c:282-333, there a host loop over downloaded windows) on the device.  Windows on a
+   grid with interior S per axis; e: this window's prediction bytes over [0, S + B)^3 (interior plus B voxels of its upper halo); nb[d], d = 1..7:
+   the spill of the window one step back along the axes of d's bits (bit 0 x, 1 y, 2 z), NULL where there is none: its z slab [B][S+B][S+B] if
+   d has bit 2, else its y slab [S][B][S+B] if bit 1, else its x slab [S][S][B] (what umx_feather_keep stores of a window).  The interior voxels
+   [oo, oo + on) per axis are written to out[(lz osh + ly) osh + lx]: e itself, except where a coordinate is below B, the weighted mean of e and
+   the spills present with the weights prod (back ? 1 - u : u), u(j) = sin^2(pi / 2 (j + 0.5) / B), rounded as min(255, s / w + 0.5).  All
+   pointers are device pointers.  Returns 0, -1 after latching an error. */
+typedef struct { int S, B; const uint8_t *e; const uint8_t *nb[8]; int oo[3], on[3], osh; uint8_t *out; } umx_feather_t;
+int umx_feather_blend(const umx_feather_t *f);
+void umx_feather_keep(const uint8_t *e, int S, int B, uint8_t *zslab, uint8_t *yslab, uint8_t *xslab);
 /* the reference's blend arithmetic, kept as an operator of its own: acc[c][z - zlo][y][x] = fma(w, logits[c][patch voxel], acc), wsum += w with
    the separable Gaussian window w1d (device, P floats) for the patch at (z0, y0, x0) of a V^3 volume; fmt UMX_F32 / UMX_F16 logits (k_i3_blend,
    src/nn_ink3dext.cu:58-73); fp32 sums, so the result depends on the order of the calls */

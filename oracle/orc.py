@@ -302,6 +302,55 @@ def ctmask(ct, t=1):
     return np.packbits(b.reshape(-1, 32), axis=1, bitorder="little").view(np.uint32).ravel()
 
 
+def feather_u(B):
+    """the seam feather's ramp (feather_init, src/predict.c:334-336): u[0][j] = sin^2(pi / 2 (j + 0.5) / B), u[1][j] = 1 - that, cast to fp32"""
+    j = np.arange(B, dtype=np.float64)
+    s = np.sin(np.pi / 2 * (j + 0.5) / B)
+    return np.stack([(s * s).astype(np.float32), (1 - s * s).astype(np.float32)])
+
+
+def feather_blend(e, nb, S, B, oo, on, osh, out):
+    """fe_val / fe_blend / fe_rows (src/predict.c:296-333): e [E][E][E] (E = S + B), nb[d] the spill slab of the window back by d's bits (bit 0
+    x, 1 y, 2 z) or None: z slab [B][E][E] if d & 4, else y slab [S][B][E] if d & 2, else x slab [S][S][B]; the interior box [oo, oo + on) goes to
+    out[(lz osh + ly) osh + lx] (modified in place).  fp32 products and sums in the reference's order."""
+    E = S + B
+    e = np.asarray(e, np.uint8).reshape(E, E, E)
+    u = feather_u(B)
+    o = out.reshape(osh, osh, osh)
+    f32 = np.float32
+
+    def val(d, z, y, x):
+        if not d:
+            return e[z, y, x]
+        p = nb[d]
+        uz, uy, ux = z + (S if d & 4 else 0), y + (S if d & 2 else 0), x + (S if d & 1 else 0)
+        if uz >= S:
+            return p.reshape(B, E, E)[uz - S, uy, ux]
+        if uy >= S:
+            return p.reshape(S, B, E)[uz, uy - S, ux]
+        return p.reshape(S, S, B)[uz, uy, ux - S]
+
+    for lz in range(on[0]):
+        for ly in range(on[1]):
+            for lx in range(on[2]):
+                z, y, x = oo[0] + lz, oo[1] + ly, oo[2] + lx
+                if z >= B and y >= B and x >= B:
+                    o[lz, ly, lx] = e[z, y, x]
+                    continue
+                s, w = f32(0), f32(0)
+                for d in range(8):
+                    if d and nb[d] is None:
+                        continue
+                    dz, dy, dx = d >> 2 & 1, d >> 1 & 1, d & 1
+                    if (dz and z >= B) or (dy and y >= B) or (dx and x >= B):
+                        continue
+                    wi = f32(f32(u[dz][z] if z < B else f32(1)) * f32(u[dy][y] if y < B else f32(1))) * f32(u[dx][x] if x < B else f32(1))
+                    s = f32(s + f32(wi * f32(val(d, z, y, x))))
+                    w = f32(w + wi)
+                o[lz, ly, lx] = np.uint8(min(f32(255), f32(f32(s / w) + f32(0.5)))) if w > 0 else 0
+    return out
+
+
 def rel_l2(a, b):
     a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

@@ -122,3 +122,41 @@ def test_pred_place_split_window_and_output(dev):
     L.nn_pred_ctmask_t(big.ptr + 3, n, mb.ptr, 100)
     ufsm_b200.check()
     assert np.array_equal(mb.download(np.uint32), orc.ctmask(ct[:n], 100))
+
+
+@pytest.mark.parametrize("present,oo,on", [((1, 2, 3, 4, 5, 6, 7), (0, 0, 0), (12, 12, 12)), ((4, 1), (0, 3, 0), (7, 9, 12)), ((), (5, 0, 2), (6, 12, 10)), ((2, 6, 7), (0, 0, 0), (4, 12, 5))])
+def test_feather_blend_and_keep(dev, present, oo, on):
+    """The seam feather on the device (src/predict.c:282-376): the blended interior bytes equal the restatement's (fp32 in the same order: exact),
+    for every subset of neighbours tried and for partial output boxes; the kept slabs are the window's upper slabs."""
+    import ctypes as C
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Feather
+    L = ufsm_b200.lib()
+    S, B, osh = 12, 4, 13
+    E = S + B
+    g = synth.rng(321)
+    e = g.integers(0, 256, E ** 3, dtype=np.uint8)
+    sizes = {d: (B * E * E if d & 4 else S * B * E if d & 2 else S * S * B) for d in range(1, 8)}
+    nb = [None] * 8
+    for d in present:
+        nb[d] = g.integers(0, 256, sizes[d], dtype=np.uint8)
+    want = orc.feather_blend(e, nb, S, B, oo, on, osh, np.full(osh ** 3, 0xEE, np.uint8))
+    ed, od = DevBuf(data=e), DevBuf(osh ** 3).fill(0xEE)
+    bufs = {d: DevBuf(data=nb[d]) for d in present}
+    f = Feather()
+    f.S, f.B, f.e, f.osh, f.out = S, B, ed.ptr, osh, od.ptr
+    for d in range(8):
+        f.nb[d] = bufs[d].ptr if d in bufs else None
+    for k in range(3):
+        f.oo[k], f.on[k] = oo[k], on[k]
+    assert L.umx_feather_blend(C.byref(f)) == 0
+    ufsm_b200.check()
+    assert np.array_equal(od.download(), want)
+    # what is kept of a window for those after it
+    zs, ys, xs = DevBuf(B * E * E).fill(0), DevBuf(S * B * E).fill(0), DevBuf(S * S * B).fill(0)
+    L.umx_feather_keep(ed.ptr, S, B, zs.ptr, ys.ptr, xs.ptr)
+    ufsm_b200.check()
+    e3 = e.reshape(E, E, E)
+    assert np.array_equal(zs.download(), e3[S:].ravel())
+    assert np.array_equal(ys.download(), e3[:S, S:, :].ravel())
+    assert np.array_equal(xs.download(), e3[:S, :S, S:].ravel())

@@ -285,3 +285,20 @@ def test_predict_back_end_restatement():
     ct = np.arange(70, dtype=np.uint8)
     bits = orc.ctmask(ct, 33)
     assert bits.size == 3 and bits[0] == 0 and bits[1] == 0xFFFFFFFE and bits[2] == 0x3F
+
+
+def test_feather_restatement_partition_of_unity():
+    """the seam feather's weights (src/predict.c:282-296): with every neighbour present the weights of a lower-shell voxel sum to 1, so windows
+    that all predict the same byte blend to that byte; with none present the window's own bytes come back"""
+    S, B, osh = 6, 3, 6
+    E = S + B
+    e = np.full(E ** 3, 77, np.uint8)
+    sizes = {d: (B * E * E if d & 4 else S * B * E if d & 2 else S * S * B) for d in range(1, 8)}
+    nb = [None] + [np.full(sizes[d], 77, np.uint8) for d in range(1, 8)]
+    out = orc.feather_blend(e, nb, S, B, (0, 0, 0), (S, S, S), osh, np.zeros(osh ** 3, np.uint8))
+    assert (out == 77).all()
+    u = orc.feather_u(B)
+    assert np.allclose(u[0] + u[1], 1, atol=1e-7) and u[0][0] < u[0][-1]
+    r = synth.rng(5).integers(0, 256, E ** 3, dtype=np.uint8)
+    out = orc.feather_blend(r, [None] * 8, S, B, (0, 0, 0), (S, S, S), osh, np.zeros(osh ** 3, np.uint8))
+    assert np.array_equal(out.reshape(osh, osh, osh), r.reshape(E, E, E)[:S, :S, :S])

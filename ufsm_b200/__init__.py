@@ -2,4 +2,4 @@
 
 The product is the C-ABI shared library (include/ufsm_mx.h); this package only loads it for the tests, the smoke test and the
 benchmark.  There is no fallback: a missing library raises."""
-from ._lib import lib, LIB_PATH, Shape5, Gnp, Split, UnetCfg, Window, DevBuf, check  # noqa: F401
+from ._lib import lib, LIB_PATH, Shape5, Gnp, Split, Feather, UnetCfg, Window, DevBuf, check  # noqa: F401

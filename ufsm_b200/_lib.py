@@ -24,6 +24,10 @@ class Split(C.Structure):
                 ("zw0", C.c_int16), ("zw1", C.c_int16), ("yzo", C.c_int16)]
 
 
+class Feather(C.Structure):
+    _fields_ = [("S", C.c_int), ("B", C.c_int), ("e", C.c_void_p), ("nb", C.c_void_p * 8), ("oo", C.c_int * 3), ("on", C.c_int * 3), ("osh", C.c_int), ("out", C.c_void_p)]
+
+
 class UnetCfg(C.Structure):
     _fields_ = [("L", C.c_int), ("cw", C.c_int * 8), ("nh", C.c_int), ("P", C.c_int), ("bits_first", C.c_int), ("bits_mid", C.c_int), ("bits_last", C.c_int)]
 
@@ -105,6 +109,8 @@ _SIG = {
     "umx_unet_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_unet_submit_host_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "umx_h16_to_prob_u8": (None, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "umx_feather_blend": (C.c_int, [C.POINTER(Feather)]),
+    "umx_feather_keep": (None, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "nn_set_logits_h16": (None, [C.c_int]),
     "nn_set_pred_iso": (None, [C.c_int]),
     "nn_get_pred_iso": (C.c_int, []),

@@ -70,6 +70,55 @@ __global__ void __launch_bounds__(256) ctmask_k(const uint8_t *__restrict__ ct, 
     bits[w] = m;
 }
 
+/* ---- seam feather (the blend of src/predict.c:282-333, which the reference runs on host threads over downloaded windows) ----
+   Windows lie on a grid with interior S per axis; each window's prediction E covers its interior and B voxels of its upper halo per axis
+   (E = S + B).  The output over the interior is E itself except in the lower shell (a coordinate below B), where the upper spills of the
+   windows before it are blended in: the window shifted back by delta in {0, 1}^3 (bit 0 x, 1 y, 2 z) has the weight
+   prod_axis (delta ? 1 - u(v) : u(v)), u(j) = sin^2(pi / 2 (j + 0.5) / B) for v < B (1 / 0 above), normalised over the windows present.
+   A neighbour's spill is its z slab [B][E][E] when it lies a window back in z, else its y slab [S][B][E] when back in y, else its x slab
+   [S][S][B] (fe_val).  fp32 products and sums in the reference's order, without contraction. */
+struct FeatherArgs { int S, B, E, osh; int oo[3], on[3]; const uint8_t *e; const uint8_t *nb[8]; const float *u; uint8_t *out; };
+__device__ __forceinline__ float fe_val(const FeatherArgs &f, int d, int z, int y, int x) {
+    if (!d) return (float)__ldg(f.e + ((size_t)z * f.E + y) * f.E + x);
+    const uint8_t *p = f.nb[d];
+    const int uz = z + ((d & 4) ? f.S : 0), uy = y + ((d & 2) ? f.S : 0), ux = x + ((d & 1) ? f.S : 0);
+    if (uz >= f.S) return (float)__ldg(p + ((size_t)(uz - f.S) * f.E + uy) * f.E + ux);
+    if (uy >= f.S) return (float)__ldg(p + ((size_t)uz * f.B + (uy - f.S)) * f.E + ux);
+    return (float)__ldg(p + ((size_t)uz * f.S + uy) * f.B + (ux - f.S));
+}
+__global__ void __launch_bounds__(256) feather_k(const FeatherArgs f) {
+    const size_t total = (size_t)f.on[0] * f.on[1] * f.on[2];
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int lx = (int)(i % f.on[2]), ly = (int)((i / f.on[2]) % f.on[1]), lz = (int)(i / ((size_t)f.on[2] * f.on[1]));
+        const int z = f.oo[0] + lz, y = f.oo[1] + ly, x = f.oo[2] + lx, B = f.B;
+        unsigned v;
+        if (z >= B && y >= B && x >= B) v = __ldg(f.e + ((size_t)z * f.E + y) * f.E + x);
+        else {
+            float s = 0.f, w = 0.f;
+            for (int d = 0; d < 8; d++) {
+                if (d && !f.nb[d]) continue;
+                const int dz = d >> 2 & 1, dy = d >> 1 & 1, dx = d & 1;
+                if ((dz && z >= B) || (dy && y >= B) || (dx && x >= B)) continue;
+                const float wi = __fmul_rn(__fmul_rn(z < B ? __ldg(f.u + dz * B + z) : 1.f, y < B ? __ldg(f.u + dy * B + y) : 1.f), x < B ? __ldg(f.u + dx * B + x) : 1.f);
+                s = __fadd_rn(s, __fmul_rn(wi, fe_val(f, d, z, y, x)));
+                w = __fadd_rn(w, wi);
+            }
+            v = w > 0.f ? (unsigned)fminf(255.f, __fadd_rn(__fdiv_rn(s, w), 0.5f)) : 0u;
+        }
+        f.out[((size_t)lz * f.osh + ly) * f.osh + lx] = (uint8_t)v;
+    }
+}
+/* a window's upper slabs, kept for the windows after it (feather_keep, src/predict.c:362-376) */
+__global__ void __launch_bounds__(256) feather_keep_k(const uint8_t *__restrict__ e, int S, int B, uint8_t *__restrict__ zs, uint8_t *__restrict__ ys, uint8_t *__restrict__ xs) {
+    const int E = S + B;
+    const size_t nz = (size_t)B * E * E, ny = (size_t)S * B * E, nx = (size_t)S * S * B;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nz + ny + nx; i += (size_t)gridDim.x * blockDim.x) {
+        if (i < nz) zs[i] = e[(size_t)S * E * E + i];
+        else if (i < nz + ny) { const size_t k = i - nz; const int x = (int)(k % E), y = (int)((k / E) % B), z = (int)(k / ((size_t)E * B)); ys[k] = e[((size_t)z * E + S + y) * E + x]; }
+        else { const size_t k = i - nz - ny; const int x = (int)(k % B), y = (int)((k / B) % S), z = (int)(k / ((size_t)B * S)); xs[k] = e[((size_t)z * E + y) * E + S + x]; }
+    }
+}
+
 int g_logits_h16[16], g_iso[16];
 int cur_dev() { int d = 0; cudaGetDevice(&d); return d & 15; }
 unsigned grid_of(size_t n) { const size_t g = (n + 255) / 256; return (unsigned)(g < 1 ? 1 : g > 148 * 32 ? 148 * 32 : g); }
@@ -132,4 +181,41 @@ extern "C" void nn_pred_place_mz(const float *lg, const uint32_t *bits, int W, i
     const int z0 = B.z0 > zlo ? B.z0 : zlo, z1 = B.z0 + B.nz < zhi ? B.z0 + B.nz : zhi;
     B.z0 = z0; B.nz = z1 > z0 ? z1 - z0 : 0;
     place<1>("nn_pred_place_mz", lg, nullptr, bits, B, W, zoff, oz, oy, ox, shard, dsh);
+}
+
+/* The seam feather's blend on the device (the arithmetic of fe_blend / fe_rows, src/predict.c:305-333): f->e, f->nb[1..7] (NULL: no such
+   window), f->out are device pointers; the interior voxels [oo, oo + on) per axis of this window go to out[(lz osh + ly) osh + lx].
+   The weight table of a band width is built on the host (double sin, as feather_init) and kept on the device. */
+extern "C" int umx_feather_blend(const umx_feather_t *h) {
+    if (!umx_ready("umx_feather_blend")) return -1;
+    if (!h || h->S < 1 || h->B < 1 || h->B > 1024 || h->B > h->S || !h->e || !h->out) { umx_latch_msg("umx_feather_blend: bad arguments"); return -1; }
+    for (int d = 0; d < 3; d++) if (h->oo[d] < 0 || h->on[d] < 0 || h->oo[d] + h->on[d] > h->S || h->on[d] > h->osh) { umx_latch_msg("umx_feather_blend: output box outside the interior or the shard"); return -1; }
+    static float *utab[16]; static int ub[16];
+    const int dv = cur_dev();
+    if (!utab[dv] || ub[dv] != h->B) {
+        float hu[2048];
+        for (int j = 0; j < h->B; j++) { const double s = sin(3.14159265358979323846 / 2 * (j + 0.5) / h->B); hu[j] = (float)(s * s); hu[h->B + j] = (float)(1 - s * s); }
+        cudaDeviceSynchronize();
+        if (!utab[dv]) utab[dv] = (float *)nn_malloc(2048 * sizeof(float));
+        if (!utab[dv]) return -1;
+        nn_h2d(utab[dv], hu, (size_t)2 * h->B * sizeof(float));
+        ub[dv] = h->B;
+    }
+    FeatherArgs f; memset(&f, 0, sizeof f);
+    f.S = h->S; f.B = h->B; f.E = h->S + h->B; f.osh = h->osh; f.e = h->e; f.u = utab[dv]; f.out = h->out;
+    for (int d = 0; d < 3; d++) { f.oo[d] = h->oo[d]; f.on[d] = h->on[d]; }
+    for (int d = 1; d < 8; d++) f.nb[d] = h->nb[d];
+    const size_t n = (size_t)f.on[0] * f.on[1] * f.on[2];
+    if (!n) return 0;
+    feather_k<<<grid_of(n), 256>>>(f);
+    g_umx_launches++;
+    UMX_CK("umx_feather_blend");
+    return 0;
+}
+extern "C" void umx_feather_keep(const uint8_t *e, int S, int B, uint8_t *zslab, uint8_t *yslab, uint8_t *xslab) {
+    if (!umx_ready("umx_feather_keep") || S < 1 || B < 1) return;
+    const int E = S + B;
+    feather_keep_k<<<grid_of((size_t)B * E * E + (size_t)S * B * E + (size_t)S * S * B), 256>>>(e, S, B, zslab, yslab, xslab);
+    g_umx_launches++;
+    UMX_CK("umx_feather_keep");
 }
