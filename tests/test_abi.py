@@ -33,6 +33,7 @@ def test_struct_sizes_match_the_reference():
     assert C.sizeof(ufsm_b200.Shape5) == 20
     assert C.sizeof(ufsm_b200.Split) <= 128 and C.sizeof(ufsm_b200.Split) == 128   # static_assert of src/nn_lp.h:38-41
     assert C.sizeof(ufsm_b200.Gnp) == 56
+    assert C.sizeof(ufsm_b200.Feather) == 120        # umx_feather_t: 2 ints, 9 pointers, 7 ints, padding, 1 pointer
 
 
 def test_storage_sizes():
