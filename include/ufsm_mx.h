@@ -201,7 +201,7 @@ void lp_gn_silu_apply_mx(const void *x, int xdt, shape5 s, int G, const float *g
 /* exact-2x trilinear upsample of an MX tensor (align_corners = false, edge clamp: 3/4 of the coarse voxel under the fine one, 1/4 of its neighbour
    on the fine voxel's side, per axis), the eight terms added with fma in (z, y, x) order; gp.G != 0: silu(gn(x)) is upsampled
    (src/nn_lp.h:136, src/lp_mx_gn.cu:32-72, 151-173).  xdt, ydt 3 / 4; y has the shape n x c x 2d x 2h x 2w; 16 channels or fewer in rows
-   of 8 / 16 on both sides (through widened copies in scratch); per-sample statistics only (gp.ns == 0). */
+   of 8 / 16 on both sides (through widened copies in scratch); gp.ns != 0: the statistics of the slab a coarse plane lies in. */
 void lp_up2_fwd_mx(const void *x, int xdt, shape5 xs, void *y, int ydt, gnp_t gp);
 /* 1^3 conv of an MX tensor with fp32 weights w [cout][cin] and bias b (or NULL): y [n][cout][S] fp32 (or fp16: _h16) = b + sum over ascending ci
    of w x with fma; cout <= 16, or a multiple of 16 for one sample; gp as above; an input of 16 channels or fewer in rows of 8 / 16

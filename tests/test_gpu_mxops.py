@@ -24,6 +24,62 @@ def make_gp(Gn, arrays):
     return gp, bufs
 
 
+def slab_gn_silu(dq, N, Cn, D, hw, Gn, pr, ns, zs, zo):
+    """silu(gn(x)) with statistics per (sample, z slab): plane z in slab (z + zo) // zs clamped to [0, ns) (src/lp_slab.cuh:7-12), slab by slab"""
+    gamma, beta, mean, rstd = pr
+    x = dq.reshape(N, Cn, D, hw)
+    out = np.zeros_like(x)
+    for sl in range(ns):
+        zz = [z for z in range(D) if min(max((z + zo) // zs, 0), ns - 1) == sl]
+        if not zz:
+            continue
+        sub = np.ascontiguousarray(x[:, :, zz[0]:zz[-1] + 1]).reshape(-1)
+        m = np.ascontiguousarray(mean.reshape(N, ns, Gn)[:, sl]).reshape(-1)
+        r = np.ascontiguousarray(rstd.reshape(N, ns, Gn)[:, sl]).reshape(-1)
+        out[:, :, zz[0]:zz[-1] + 1] = orc.gn_silu(sub, N, Cn, len(zz) * hw, Gn, gamma, beta, m, r, 1).reshape(N, Cn, len(zz), hw)
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_slab_local_groupnorm_in_up2_and_conv1(dev, bits):
+    """gnp_t.ns != 0 in lp_up2_fwd_mx and lp_conv1_fwd_mx: the statistics of the slab a (coarse) plane lies in"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5
+    L = ufsm_b200.lib()
+    dt = 3 if bits == 8 else 4
+    # upsample: six coarse planes in three slabs (0 | 1 2 | 3 4 5)
+    N, Cn, Gn, D, H, W, ns, zs, zo = 2, 40, 5, 6, 9, 11, 3, 2, 1
+    S, hw = D * H * W, H * W
+    x = (synth.rng(401).standard_normal(N * Cn * S) * 2).astype(f32)
+    mx = orc.pm_to_mx(x, 0, N, Cn, S, bits, 32)
+    pr = gn_params(402, N * ns, Cn, Gn)
+    gp, keep = make_gp(Gn, pr)
+    gp.ns, gp.zs, gp.zo, gp.zhw = ns, zs, zo, hw
+    act = slab_gn_silu(orc.mx_to_pm(mx, bits, N, Cn, S, 32), N, Cn, D, hw, Gn, pr, ns, zs, zo)
+    want = orc.pm_to_mx(orc.up2(act, N, Cn, D, H, W), 0, N, Cn, 8 * S, bits, 32)
+    xd, yd = DevBuf(data=mx), DevBuf(want.size).fill(0xEE)
+    L.lp_up2_fwd_mx(xd.ptr, dt, Shape5(N, Cn, D, H, W), yd.ptr, dt, gp)
+    ufsm_b200.check()
+    bad = np.count_nonzero(yd.download() != want)
+    assert bad <= 2e-4 * want.size, "%d of %d bytes differ" % (bad, want.size)
+    # 1^3 conv: planes of 117 voxels, so a block of 512 voxels touches up to three slabs (0 1 | 2 3 | 4)
+    N, Ci, Co, D, H, W, ns, zs, zo = 2, 64, 7, 5, 9, 13, 3, 2, 0
+    S, hw = D * H * W, H * W
+    x = (synth.rng(403).standard_normal(N * Ci * S) * 2).astype(f32)
+    w = (synth.rng(404).standard_normal((Co, Ci)) / np.sqrt(Ci)).astype(f32)
+    b = (0.1 * synth.rng(405).standard_normal(Co)).astype(f32)
+    mx = orc.pm_to_mx(x, 0, N, Ci, S, bits, 32)
+    pr = gn_params(406, N * ns, Ci, 8)
+    gp, keep2 = make_gp(8, pr)
+    gp.ns, gp.zs, gp.zo, gp.zhw = ns, zs, zo, hw
+    act = slab_gn_silu(orc.mx_to_pm(mx, bits, N, Ci, S, 32), N, Ci, D, hw, 8, pr, ns, zs, zo)
+    want = orc.conv1(act, w, b, N, Ci, Co, S).reshape(N, Co, S)
+    xd, wd, bd, yd = DevBuf(data=mx), DevBuf(data=w), DevBuf(data=b), DevBuf(N * Co * S * 4).fill(0xEE)
+    L.lp_conv1_fwd_mx(xd.ptr, dt, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, gp)
+    ufsm_b200.check()
+    assert orc.rel_l2(yd.download(f32).reshape(N, Co, S), want) < 1e-5
+
+
 # the second shape spans several tiles of the kernel on every axis (4 x 4 x 16 cells of the dual grid), with ragged last tiles
 @pytest.mark.parametrize("shape", [(2, 40, 5, 3, 5, 7), (1, 64, 8, 6, 9, 35), (2, 16, 2, 3, 5, 7), (1, 8, 1, 2, 6, 5)])      # the last two: rows of 16 / 8 channels
 @pytest.mark.parametrize("xbits,ybits,gn", [(8, 8, False), (4, 4, False), (8, 4, False), (4, 8, False), (8, 8, True), (4, 4, True)])

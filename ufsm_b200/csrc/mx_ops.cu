@@ -30,7 +30,13 @@ __device__ __forceinline__ int clampi(int v, int hi) { return v < 0 ? 0 : (v > h
    fine voxel of the grid each.  A staged row lives at tile[8 s + f]: eight float4, lane q's channels at f = q ^ 4 (s & 1) and f ^ 4, so
    that two neighbouring rows read by eight lanes cover all the banks.
    grid (tiles, sample x block) */
-template <int BX, int BY, bool GN>
+/* slab-local statistics (gnp_t.ns != 0, src/nn_lp.h:15-18): the statistics row of sample n at plane z (gn_row, src/lp_slab.cuh:7-12) */
+__device__ __forceinline__ int gn_row_of(const gnp_t &gp, int n, int z) {
+    int s = (z + gp.zo) / gp.zs;
+    s = s < 0 ? 0 : s >= gp.ns ? gp.ns - 1 : s;
+    return n * gp.ns + s;
+}
+template <int BX, int BY, bool GN, bool SL>
 __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int N, int C, int D, int H, int W, int tx, int ty, gnp_t gp, int nbx, int b0) {
     extern __shared__ __align__(16) float4 tile[];
     /* y has the nb blocks of its C channels; they are blocks [b0, b0 + nb) of x, which has nbx a sample */
@@ -73,6 +79,17 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
         const int s = u * 64 + quad;
         float2 r[4];
         qrow_dec<BX>(raw[u], mx_scale(sb[u]), r);
+        if (GN && SL && s < UP2_ROWS) {
+            /* the coefficients of the slab this row's coarse plane lies in */
+            const int nr = gn_row_of(gp, n, clampi(a0 + s / (HX * HY), D - 1));
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int c = blk * 32 + q * 8 + k;
+                float a = 1.f, b = 0.f;
+                if (live[k]) { const int ng = nr * gp.G + c / (C / gp.G); a = __fmul_rn(gp.rstd[ng], gp.gamma[c]); b = __fmaf_rn(-gp.mean[ng], a, gp.beta[c]); }
+                if (k & 1) { ca[k >> 1].y = a; cb[k >> 1].y = b; } else { ca[k >> 1].x = a; cb[k >> 1].x = b; }
+            }
+        }
         if (GN) {
 #pragma unroll
             for (int j = 0; j < 4; j++) { const float2 a2 = silu_ab2(r[j], ca[j], cb[j]); if (live[2 * j]) r[j].x = a2.x; if (live[2 * j + 1]) r[j].y = a2.y; }
@@ -148,7 +165,7 @@ __global__ void __launch_bounds__(256, 2) up2_dual_k(const uint8_t *__restrict__
 /* ---------------------------------------------------------------- 1^3 conv ---------------------------------------------------------------- */
 /* grid (voxels / 512, sample); outputs co0 + [0, Co) of co_all; weights as [ci][4 CO4] and the sample's GroupNorm coefficients [ci] in
    shared memory, every read of them a broadcast */
-template <int BITS, int CO4, bool GN, typename YT>
+template <int BITS, int CO4, bool GN, typename YT, bool SL = false>
 __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias, YT *__restrict__ y,
                                                    int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp, size_t vb, size_t nv, size_t ly) {
     extern __shared__ __align__(16) float4 c1sm[];
@@ -156,15 +173,28 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
     constexpr int CO = 4 * CO4, RB = BITS == 8 ? 32 : 16, WORDS = RB / 4;
     const int nb = (Ci + 31) / 32, n = blockIdx.y;
     for (int i = threadIdx.x; i < Ci * CO; i += 256) { const int ci = i / CO, co = i % CO; ((float *)sw)[i] = co < Co ? w[(size_t)co * Ci + ci] : 0.f; }
-    if (GN) for (int ci = threadIdx.x; ci < Ci; ci += 256) {
+    /* voxels [vb, vb + nv) of the S; logit planes of ly voxels */
+    const size_t v0 = (size_t)blockIdx.x * 512 + threadIdx.x;
+    const bool ok[2] = {v0 < nv, v0 + 256 < nv};
+    int sof[2] = {0, 0};                                    /* SL: where the coefficient table of each of the thread's two voxels' slabs starts */
+    if (GN && !SL) for (int ci = threadIdx.x; ci < Ci; ci += 256) {
         const int ng = n * gp.G + ci / (Ci / gp.G);
         const float a = __fmul_rn(gp.rstd[ng], gp.gamma[ci]);
         sab[ci] = make_float2(a, __fmaf_rn(-gp.mean[ng], a, gp.beta[ci]));
     }
+    if (GN && SL) {
+        /* one table per statistics slab the block's 512 voxels touch (the launcher has made room for them) */
+        const size_t lo = vb + (size_t)blockIdx.x * 512, hi = min(lo + 511, vb + nv - 1);
+        const int r_lo = gn_row_of(gp, n, (int)(lo / (size_t)gp.zhw)), r_hi = gn_row_of(gp, n, (int)(hi / (size_t)gp.zhw));
+        for (int i = threadIdx.x; i < (r_hi - r_lo + 1) * Ci; i += 256) {
+            const int ci = i % Ci, ng = (r_lo + i / Ci) * gp.G + ci / (Ci / gp.G);
+            const float a = __fmul_rn(gp.rstd[ng], gp.gamma[ci]);
+            sab[i] = make_float2(a, __fmaf_rn(-gp.mean[ng], a, gp.beta[ci]));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) if (ok[u]) sof[u] = (gn_row_of(gp, n, (int)((vb + v0 + 256 * u) / (size_t)gp.zhw)) - r_lo) * Ci;
+    }
     __syncthreads();
-    /* voxels [vb, vb + nv) of the S; logit planes of ly voxels */
-    const size_t v0 = (size_t)blockIdx.x * 512 + threadIdx.x;
-    const bool ok[2] = {v0 < nv, v0 + 256 < nv};
     const uint8_t *xs = x + (size_t)N * nb * S * RB;
     float acc[2][CO];                                       /* scalar fma: the packed form has the same pipe rate and needs the input twice */
 #pragma unroll
@@ -191,7 +221,8 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
             auto chan = [&](int k) {
                 const int ci = blk * 32 + 8 * h + k;
                 float x0 = (k & 1) ? r[0][k >> 1].y : r[0][k >> 1].x, x1 = (k & 1) ? r[1][k >> 1].y : r[1][k >> 1].x;
-                if (GN) { const float2 ab = sab[ci]; x0 = silu_hw(__fmaf_rn(x0, ab.x, ab.y)); x1 = silu_hw(__fmaf_rn(x1, ab.x, ab.y)); }
+                if (GN && !SL) { const float2 ab = sab[ci]; x0 = silu_hw(__fmaf_rn(x0, ab.x, ab.y)); x1 = silu_hw(__fmaf_rn(x1, ab.x, ab.y)); }
+                if (GN && SL) { const float2 ab0 = sab[sof[0] + ci], ab1 = sab[sof[1] + ci]; x0 = silu_hw(__fmaf_rn(x0, ab0.x, ab0.y)); x1 = silu_hw(__fmaf_rn(x1, ab1.x, ab1.y)); }
 #pragma unroll
                 for (int j = 0; j < CO4; j++) {
                     const float4 t4 = sw[ci * CO4 + j];
@@ -220,22 +251,24 @@ __global__ void __launch_bounds__(256) conv1_vox_k(const uint8_t *__restrict__ x
 }
 
 void gp_check(const char *fn, gnp_t gp, int C) {
-    if (gp.G && (gp.ns > 1 || gp.zs || gp.zo || gp.zhw)) { fprintf(stderr, "%s: slab-local GroupNorm (gnp_t.ns / zs / zo / zhw) is not built in this library\n", fn); abort(); }
+    if (gp.G && gp.ns && (gp.ns < 0 || gp.zs < 1 || gp.zo < 0 || gp.zo >= gp.zs || gp.zhw < 1)) { fprintf(stderr, "%s: slab-local GroupNorm with ns %d, zs %d, zo %d, zhw %d\n", fn, gp.ns, gp.zs, gp.zo, gp.zhw); abort(); }
     if (gp.G && (gp.G < 1 || C % gp.G)) { fprintf(stderr, "%s: %d channels in %d groups\n", fn, C, gp.G); abort(); }
 }
 
-template <int BX, int BY, bool GN> void up2_launch(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp, int nbx, int b0) {
+template <int BX, int BY, bool GN, bool SL = false> void up2_launch(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp, int nbx, int b0) {
     static bool sized = false;      /* per instantiation; the attribute belongs to the function, any device of this process */
-    if (!sized) { cudaFuncSetAttribute(up2_dual_k<BX, BY, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UP2_SMEM); sized = true; }
-    up2_dual_k<BX, BY, GN><<<grid, 256, UP2_SMEM>>>(x, y, xs.n, xs.c, xs.d, xs.h, xs.w, tx, ty, gp, nbx, b0);
+    if (!sized) { cudaFuncSetAttribute(up2_dual_k<BX, BY, GN, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)UP2_SMEM); sized = true; }
+    up2_dual_k<BX, BY, GN, SL><<<grid, 256, UP2_SMEM>>>(x, y, xs.n, xs.c, xs.d, xs.h, xs.w, tx, ty, gp, nbx, b0);
 }
 template <int BX, int BY> void up2_gn(dim3 grid, const uint8_t *x, uint8_t *y, shape5 xs, int tx, int ty, gnp_t gp, int nbx, int b0) {
-    if (gp.G) up2_launch<BX, BY, true>(grid, x, y, xs, tx, ty, gp, nbx, b0); else up2_launch<BX, BY, false>(grid, x, y, xs, tx, ty, gp, nbx, b0);
+    if (gp.G && gp.ns) up2_launch<BX, BY, true, true>(grid, x, y, xs, tx, ty, gp, nbx, b0);
+    else if (gp.G) up2_launch<BX, BY, true>(grid, x, y, xs, tx, ty, gp, nbx, b0); else up2_launch<BX, BY, false>(grid, x, y, xs, tx, ty, gp, nbx, b0);
 }
 
 template <int BITS, int CO4, typename YT>
 void conv1_launch(dim3 grid, size_t smem, const uint8_t *x, const float *w, const float *b, YT *y, int N, int Ci, int Co, int co0, int co_all, size_t S, gnp_t gp, size_t vb, size_t nv, size_t ly) {
-    if (gp.G) conv1_vox_k<BITS, CO4, true, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
+    if (gp.G && gp.ns) conv1_vox_k<BITS, CO4, true, YT, true><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
+    else if (gp.G) conv1_vox_k<BITS, CO4, true, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
     else conv1_vox_k<BITS, CO4, false, YT><<<grid, 256, smem>>>(x, w, b, y, N, Ci, Co, co0, co_all, S, gp, vb, nv, ly);
 }
 template <int BITS, typename YT>
@@ -255,6 +288,7 @@ template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, sh
     if (cout < 1 || (cout > 16 && cout % 16)) { fprintf(stderr, "%s: cout %d is neither 1..16 nor a multiple of 16\n", fn, cout); abort(); }
     if (xs.n > 65535) { fprintf(stderr, "%s: %d samples\n", fn, xs.n); abort(); }
     gp_check(fn, gp, xs.c);
+    if (gp.G && gp.ns && gp.zhw != xs.h * xs.w) { fprintf(stderr, "%s: slab-local GroupNorm with zhw %d on planes of %d voxels\n", fn, gp.zhw, xs.h * xs.w); abort(); }
     const size_t S = (size_t)xs.d * xs.h * xs.w;
     if (!S || !xs.n) return;
     if (xs.c <= 16) {                                          /* rows of 8 / 16 channels (src/lp_common.cuh:132): the same codes and scale in 32-wide rows */
@@ -271,7 +305,9 @@ template <typename YT> void conv1_fwd(const char *fn, const void *x, int xdt, sh
     /* more than 16 outputs: passes of 16 over the same input (the reference's rule, src/lp_mx_conv1.cu:422-444) */
     for (int c0 = 0; c0 < cout; c0 += 16) {
         const int co = min(16, cout - c0), co4 = (co + 3) / 4;
-        const size_t smem = (size_t)xs.c * co4 * 16 + (gp.G ? (size_t)xs.c * 8 : 0);
+        /* coefficient tables: one, or with slab-local statistics one per slab that 512 consecutive voxels can touch */
+        const int ntab = !gp.G ? 0 : !gp.ns ? 1 : min(gp.ns, (int)((511 / (size_t)gp.zhw + 1) / (size_t)gp.zs) + 2);
+        const size_t smem = (size_t)xs.c * co4 * 16 + (size_t)xs.c * 8 * ntab;
         if (smem > 48 * 1024) { fprintf(stderr, "%s: %d input channels need more shared memory than this kernel has\n", fn, xs.c); abort(); }
         const float *wp = w + (size_t)c0 * xs.c, *bp = b ? b + c0 : nullptr;
         if (xdt == UMX_MX8) conv1_co<8, YT>(co4, grid, smem, (const uint8_t *)x, wp, bp, y, xs.n, xs.c, co, c0, cout, S, gp, vb, nv, ly);
@@ -288,6 +324,7 @@ static void up2_fwd(const char *fn, const void *x, int xdt, shape5 ys, int nbx, 
     if (!umx_ready(fn)) return;
     if ((xdt != UMX_MX8 && xdt != UMX_MX4) || (ydt != UMX_MX8 && ydt != UMX_MX4)) { fprintf(stderr, "%s: dtypes %d -> %d are not MX\n", fn, xdt, ydt); abort(); }
     gp_check(fn, gp, ys.c);
+    if (gp.G && gp.ns && gp.zhw != ys.h * ys.w) { fprintf(stderr, "%s: slab-local GroupNorm with zhw %d on planes of %d voxels\n", fn, gp.zhw, ys.h * ys.w); abort(); }
     if (!ys.n || !ys.d || !ys.h || !ys.w) return;
     if ((size_t)ys.d * ys.h * ys.w >= ((size_t)1 << 28)) { fprintf(stderr, "%s: 2^31 fine voxels per sample or more\n", fn); abort(); }
     const int tx = (ys.w + 1 + UX - 1) / UX, ty = (ys.h + 1 + UY - 1) / UY, tz = (ys.d + 1 + UZ - 1) / UZ;      /* D + 1 dual cells an axis */
