@@ -113,7 +113,7 @@ void umx_h16b_to_f32(const void *x, int N, int C, size_t S, float *y);          
    plane-major y += conv), osum / Go (exact GroupNorm sums over the planes [zlo, D - zhi): stored_stats 1, of the stored MX values, also of a split
    output whose first part ends on a 32-channel block; stored_stats 0, of acc + bias before rounding, through an fp32 copy of the output), zi0 / Di, zw0 / zw1, yD / yzo (z range, z window, output into a deeper
    tensor), wkey (prepared-weight memo).  What is not built prints "... is not built in this library" and aborts: stochastic rounding
-   (sr / osr), slab-local GroupNorm (gnp_t.ns != 0) of a part stored at half resolution, osum of a stored output that is not MX or of the unrounded values of a split output, the z fields
+   (sr / osr), osum of a stored output that is not MX or of the unrounded values of a split output, the z fields
    together with up, a transform of concat parts of 16 channels or fewer.  Returns 0. ---- */
 int lp_conv_fwd_f8(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);
 int lp_conv_fwd_f4(const void *x, int xbf, shape5 xs, const float *w, const float *b, int cout, void *y, int ybf, gnp_t gp, double *osum, int Go, split_t sp);

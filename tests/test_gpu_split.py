@@ -123,6 +123,41 @@ def test_concat_input(dev, xbf, bits, Cx, C2, up, gn):
     assert e < TOL
 
 
+def test_concat_up_with_slab_local_groupnorm(dev):
+    """the decoder form [upsample(silu(gn(coarse))) | silu(gn(skip))] with the coarse part's statistics per z slab of the coarse tensor
+    (gnp_t.ns / zs / zo / zhw count its planes) and the skip part's per sample"""
+    import ufsm_b200
+    from ufsm_b200 import DevBuf, Shape5, Gnp, Split
+    from test_gpu_mxops import slab_gn_silu
+    L = ufsm_b200.lib()
+    N, Cx, C2, Co, D, H, W = 2, 32, 32, 32, 4, 8, 16
+    Dc, Hc, Wc = D // 2, H // 2, W // 2
+    Ci, S, Sc, hwc = Cx + C2, D * H * W, Dc * Hc * Wc, Hc * Wc
+    ns, zs, zo = 2, 1, 0                                     # one coarse plane a slab
+    xa = (synth.rng(261).standard_normal(N * Cx * Sc) * 2).astype(f32)
+    xb = (synth.rng(262).standard_normal(N * C2 * S) * 2).astype(f32)
+    w, b = synth.kaiming(263, Co, Ci, 27), synth.bias(264, Co, 0.1)
+    sa, sb_ = orc.pm_to_mx(xa, 0, N, Cx, Sc, 8, 32), orc.pm_to_mx(xb, 0, N, C2, S, 8, 32)
+    pa, pb = gn_params(265, N * ns, Cx, 8), gn_params(266, N, C2, 4)
+    keep = []
+    gp = make_gp(8, pa, keep)
+    gp.ns, gp.zs, gp.zo, gp.zhw = ns, zs, zo, hwc
+    sp = Split()
+    sp.gp2 = make_gp(4, pb, keep)
+    da = slab_gn_silu(orc.mx_to_pm(sa, 8, N, Cx, Sc, 32), N, Cx, Dc, hwc, 8, pa, ns, zs, zo)
+    db = orc.gn_silu(orc.mx_to_pm(sb_, 8, N, C2, S, 32), N, C2, S, 4, *pb, 1)
+    cat = padded_segments(orc.up2(da, N, Cx, Dc, Hc, Wc), db, N, Cx, C2, S)
+    amx = orc.pm_to_mx(cat, 0, N, Ci, S, 8, 32)
+    acc = orc.conv_blocked(orc.mx_to_blocked(amx, 8, N, Ci, S), N, Ci, D, H, W, orc.prep_w(w, Co, Ci, 27, 8), b, Co, 3, 1, 1)
+    want = orc.blocked_to_pm(orc.round_h16(acc), N, Co, S)
+    xd, x2d, wd, bd = DevBuf(data=sa), DevBuf(data=sb_), DevBuf(data=w), DevBuf(data=b)
+    sp.x2, sp.c_split, sp.up = x2d.ptr, Cx, 1
+    yd = DevBuf(N * Co * S * 2).fill(0xEE)
+    assert L.lp_conv_fwd_f8(xd.ptr, 3, Shape5(N, Ci, D, H, W), wd.ptr, bd.ptr, Co, yd.ptr, 2, gp, None, 0, sp) == 0
+    ufsm_b200.check()
+    assert orc.rel_l2(yd.download(np.float16).astype(f32), want) < TOL
+
+
 @pytest.mark.parametrize("ybf,Ox,O2", [(2, 40, 24), (3, 32, 32), (3, 40, 56), (4, 64, 32), (3, 16, 16), (4, 8, 40), (3, 40, 8)])
 def test_split_output_and_stored_stats(dev, ybf, Ox, O2):
     import ufsm_b200

@@ -197,7 +197,6 @@ static int conv_fwd(const char *fn, int bits, const void *x, int xbf, shape5 xs,
         UMX_CK(fn);
         return 0;
     }
-    if (gp.G && gp.ns && sp.up) not_built(fn, "slab-local GroupNorm (gnp_t.ns) of a part stored at half resolution (split_t.up)");
     if (sp.up && !sp.x2) { fprintf(stderr, "%s: split_t.up without x2\n", fn); abort(); }
     if (sp.gp2.G && !sp.x2) { fprintf(stderr, "%s: split_t.gp2 without x2\n", fn); abort(); }
     const int mxin = bits == 8 ? UMX_MX8 : UMX_MX4;
